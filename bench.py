@@ -1,0 +1,377 @@
+"""bench.py -- NNCP Transformer-XL train step on 1..8 B200: compressed symbols/s.
+
+  python bench.py --gpus N --steps K --warmup W            (N > 1: launched by torchrun)
+  python bench.py --impl reference ...                     (CPU arm: the oracle port, host cores)
+
+A step is one segment of every stream: forward over [memory | segment], loss, backward,
+RMSProp update, memory shift (fwd+bwd+RMSProp, the metric of BASELINE.json).  The workload is
+BASELINE config[2] (vocab 16384, 12 layers, d_model 512, 8 heads x 64, d_ff 2048, seg 64,
+mem 64, 32 streams, bf16 with fp32 master weights) on seeded synthetic Zipf+Markov token ids;
+streams are sharded across ranks and gradients are summed with one NCCL all-reduce per step.
+
+`value`   device-resident ids/targets, nothing read back (CUDA events, max over ranks).
+`e2e`     the same steps through the host-buffer plugin calls: ids from pinned host memory
+          every step, the coder-ready prob0 paths and the loss read back every step.
+`roofline` the tcgen05 GEMM kernel: sum of 2*M*N*K over its launches / sum of their CUDA-event
+          durations, against the measured bf16 peak.
+`cpu_baseline` the CPU oracle (port of nncp.c's graph, OpenMP) timed on a bounded sample.
+"""
+import argparse
+import ctypes as C
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+import __graft_entry__ as entry  # noqa: E402
+
+CONFIGS = {
+    # BASELINE.json configs[2]
+    "c2": dict(n_layer=12, d_model=512, n_head=8, d_key=64, d_inner=2048, d_pos=128, mem_len=64,
+               seg_len=64, n_streams=32, n_symbols=16384, use_bf16=1),
+    # BASELINE.json configs[0]
+    "c0": dict(n_layer=2, d_model=128, n_head=4, d_key=32, d_inner=512, d_pos=64, mem_len=32,
+               seg_len=32, n_streams=4, n_symbols=256, use_bf16=0),
+}
+COMMON = dict(use_bias=1, use_w_r=1, tied_w_r=0, tied_b_r=0, query_bias=1, ln_flags=1, ff_act=1,
+              init_range=0.02, init_kind=1, seed=123, lr=3e-4, beta2=0.99, eps=1e-8)
+
+
+def step_flops(c, B):
+    """Algorithmic FLOPs of one train step (2*m*n*k per contraction; bwd = dX + dW, no dX into
+    the memory rows)."""
+    D, H, dk, F, T, M, V, P = (c["d_model"], c["n_head"], c["d_key"], c["d_inner"], c["seg_len"],
+                               c["mem_len"], c["n_symbols"], c["d_pos"])
+    L, HD = M + T, c["n_head"] * c["d_key"]
+    F1 = 2 * F if c.get("ff_act", 1) == 2 else F
+    layer = (2 * B * T * D * HD + 2 * B * L * D * 2 * HD + 2 * B * H * T * L * dk + 2 * B * H * T * P * dk +
+             2 * B * H * T * L * dk + 2 * B * T * HD * D + 2 * B * T * D * F1 + 2 * B * T * F * D)
+    head = 2 * B * T * D * V
+    fwd = c["n_layer"] * layer + head
+    return 3 * fwd - c["n_layer"] * 2 * B * M * D * 2 * HD
+
+
+def synth_tokens(n, V, seed=1234, lam=0.5):
+    """Zipf(s=1.1) unigram mixed (lambda 0.5) with an order-1 Markov chain whose rows put
+    Dirichlet(0.05) mass on 512 successors drawn from the most frequent ranks."""
+    rng = np.random.default_rng(seed)
+    ranks = np.arange(1, V + 1, dtype=np.float64)
+    uni = ranks ** -1.1
+    uni /= uni.sum()
+    n_ctx = min(V, 4096)  # contexts beyond this rank share rows (bounded generator memory)
+    succ = rng.integers(0, 512, size=(n_ctx, 16))
+    w = rng.dirichlet(np.full(16, 0.05 * 32), size=n_ctx)
+    cw = np.cumsum(w, axis=1)
+    out = np.empty(n, np.int32)
+    u_draw = rng.choice(V, size=n, p=uni)
+    pick = rng.random(n)
+    mix = rng.random(n) < lam
+    prev = 0
+    for i in range(n):
+        if mix[i]:
+            prev = u_draw[i]
+        else:
+            r = prev % n_ctx
+            prev = succ[r, min(int(np.searchsorted(cw[r], pick[i])), 15)]
+        out[i] = prev
+    return out
+
+
+def make_batches(c, B_total, steps, seed=1234):
+    """ids/targets [steps][T][B_total] laid out as process_block does (nncp.c:2945-3001): stream b
+    owns a contiguous slice; the input at position t is the symbol at t-1 (0 at a stream start)."""
+    T, V = c["seg_len"], c["n_symbols"]
+    per_stream = steps * T
+    if V <= 256:
+        rng = np.random.default_rng(seed)
+        toks = rng.integers(0, V, B_total * per_stream).astype(np.int32)
+    else:
+        toks = synth_tokens(B_total * per_stream, V, seed)
+    s = toks.reshape(B_total, per_stream)
+    prev = np.concatenate([np.zeros((B_total, 1), np.int32), s[:, :-1]], 1)
+    ids = prev.reshape(B_total, steps, T).transpose(1, 2, 0)
+    tg = s.reshape(B_total, steps, T).transpose(1, 2, 0)
+    return np.ascontiguousarray(ids), np.ascontiguousarray(tg)
+
+
+class ClockSampler:
+    def __init__(self, index):
+        self.index, self.rows, self.proc = index, [], None
+
+    def start(self):
+        q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+             "clocks_event_reasons.sw_power_cap")
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={q}", "--format=csv,noheader,nounits",
+                                          "-i", str(self.index), "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([x.strip() for x in line.split(",")])
+
+    def stop(self):
+        if self.proc:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+        sm = [float(r[0]) for r in self.rows if len(r) >= 6 and r[0].replace(".", "").isdigit()]
+        mx = [float(r[1]) for r in self.rows if len(r) >= 6 and r[1].replace(".", "").isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names)
+                   if any(len(r) >= 6 and r[2 + i].lower().startswith("active") for r in self.rows)]
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": reasons, "samples": len(sm)}
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        p = json.load(open(path))
+        return p.get("bf16_tflops_sustained", 1420.5), p.get("hbm_gbs", 6453.4), "measured"
+    return 1400.0, 6650.0, "fallback"
+
+
+def cpu_port_run(c, steps, warmup, streams):
+    """Times the CPU oracle on `streams` streams of the workload's model; returns symbols/s."""
+    pkg = entry._package()
+    from oracle import oracle as orc
+    kw = dict(COMMON)
+    kw.update(c)
+    kw.update(n_streams=streams, n_streams_total=streams, use_bf16=0)
+    p = pkg.abi.make_params(**kw)
+    m = orc.OracleModel(p)
+    ids, tg = make_batches(c, streams, steps + warmup, seed=99)
+    m.reset()
+    t0 = None
+    for s in range(steps + warmup):
+        if s == warmup:
+            t0 = time.perf_counter()
+        m.L.orc_eval(m.h, -1, ids[s].ctypes.data_as(C.c_void_p), None)
+        m.eval_gradient(tg[s])
+        m.update()
+    dt = time.perf_counter() - t0
+    m.close()
+    return steps * c["seg_len"] * streams / dt, dt
+
+
+def run_reference(args, c):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    streams = 2 if args.config == "c2" else c["n_streams"]
+    val, dt = cpu_port_run(c, args.steps, min(args.warmup, 1), streams)
+    cores = os.cpu_count()
+    line = {"impl": "reference", "metric": "compressed symbols/s (fwd+bwd+RMSProp)", "value": val,
+            "unit": "symbols/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": min(args.warmup, 1),
+            "ms_per_step": 1e3 * dt / args.steps, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": f"{args.config}: NNCP Transformer-XL train step", "sample":
+                       f"{streams} of {c['n_streams']} streams per step"},
+            "cpu_baseline": {"value": val, "unit": "symbols/s", "cores": cores, "kind": "port",
+                             "sample": f"{args.steps} steps of {streams} streams x {c['seg_len']} symbols, "
+                                       f"oracle/trf_oracle.c with OpenMP; the reference's own train step "
+                                       f"needs LibNC, which its tree does not contain"},
+            "e2e": {"value": val, "unit": "symbols/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200")
+    ap.add_argument("--config", default="c2", choices=sorted(CONFIGS))
+    ap.add_argument("--backend", type=int, default=0, help="0 auto, 1 SIMT, 2 tcgen05")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    c = dict(CONFIGS[args.config])
+    if args.impl == "reference":
+        run_reference(args, c)
+        return
+
+    import torch
+    import torch.distributed as dist
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run")
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    pkg = entry._package()
+    lib = pkg.library()   # raises if the CUDA library is not built: there is no other path
+
+    Bt = c["n_streams"]
+    if Bt % world:
+        raise SystemExit("streams must divide over the ranks")
+    B = Bt // world
+    kw = dict(COMMON)
+    kw.update(c)
+    kw.update(n_streams=B, n_streams_total=Bt, gemm_backend=args.backend, device=local)
+    p = pkg.abi.make_params(**kw)
+    m = pkg.TrfModel(p)
+    stream = torch.cuda.current_stream()
+    T, V = c["seg_len"], c["n_symbols"]
+    K, W = args.steps, max(args.warmup, 3)
+    ids_all, tg_all = make_batches(c, Bt, K + W)
+    sl = slice(rank * B, (rank + 1) * B)
+    ids_h = torch.from_numpy(np.ascontiguousarray(ids_all[:, :, sl])).pin_memory()
+    tg_h = torch.from_numpy(np.ascontiguousarray(tg_all[:, :, sl])).pin_memory()
+    ids_d, tg_d = ids_h.cuda(), tg_h.cuda()
+
+    class _Wrap:   # the flat gradient buffer as a torch tensor (for the NCCL all-reduce)
+        def __init__(self, ptr, n):
+            self.__cuda_array_interface__ = {"shape": (n,), "typestr": "<f4", "data": (ptr, False),
+                                             "version": 2}
+    wptr, gptr, vptr, nfl = m.flat_buffers()
+    grads = torch.as_tensor(_Wrap(gptr, nfl), device=f"cuda:{local}") if world > 1 else None
+
+    def step_device(s):
+        m.eval_dev(-1, ids_d[s].data_ptr())
+        m.eval_gradient_dev(tg_d[s].data_ptr())
+        if world > 1:
+            dist.all_reduce(grads)      # fixed N, fixed algorithm: every rank gets the same sum
+        m.update()
+
+    nb = int(np.log2(V)) if (V & (V - 1)) == 0 else 0
+    paths = np.zeros((T * B, max(nb, 1)), np.uint16)
+    nbits = C.c_int()
+
+    def step_host(s):
+        m.eval(-1, ids_h[s].numpy(), read=False)
+        if nb:
+            lib.nncu_coder_paths(m.h, 0, T, tg_h[s].numpy().ctypes.data_as(C.c_void_p),
+                                 paths.ctypes.data_as(C.c_void_p), C.byref(nbits))
+        else:
+            m.read_probs(0, T)
+        loss = m.eval_gradient(tg_h[s].numpy())
+        if world > 1:
+            dist.all_reduce(grads)
+        m.update()
+        return loss
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    m.reset()
+    for s in range(W):
+        step_device(s)
+    barrier()
+    sampler = ClockSampler(local) if rank == 0 else None
+    if sampler:
+        sampler.start()
+    lib.nncu_profile_begin(0)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for s in range(W, W + K):
+        step_device(s)
+    e1.record(stream)
+    barrier()
+    prof = pkg.abi.Profile()
+    lib.nncu_profile_end(C.byref(prof))
+    ms = e0.elapsed_time(e1)
+    clocks = sampler.stop() if sampler else None
+    m.synchronize()
+    if world > 1:
+        t = torch.tensor([ms], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = t.item()
+    value = K * T * Bt / (ms * 1e-3)
+
+    # end to end through the host-buffer calls
+    m.reset()
+    for s in range(2):
+        step_host(s)
+    barrier()
+    t0 = time.perf_counter()
+    e0.record(stream)
+    for s in range(W, W + K):
+        step_host(s)
+    e1.record(stream)
+    barrier()
+    ms_e2e = max(e0.elapsed_time(e1), (time.perf_counter() - t0) * 1e3)
+    if world > 1:
+        t = torch.tensor([ms_e2e], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_e2e = t.item()
+    e2e = K * T * Bt / (ms_e2e * 1e-3)
+
+    # per-launch timing of the dominant kernel (separate short pass so the timed region above
+    # carries no event overhead)
+    roof = None
+    peak_tf, peak_hbm, which = peaks()
+    if p.use_bf16 and args.backend != 1:
+        lib.nncu_profile_begin(1)
+        for s in range(W, W + min(K, 3)):
+            step_device(s)
+        barrier()
+        pr = pkg.abi.Profile()
+        lib.nncu_profile_end(C.byref(pr))
+        if pr.gemm_launches:
+            ach = pr.gemm_flops / (pr.gemm_ms * 1e-3) / 1e12
+            roof = {"bound": "tensor", "kernel": "gemm_tc_kernel (tcgen05 bf16 NT GEMM)",
+                    "achieved": ach, "peak": peak_tf, "unit": "TFLOP/s", "frac": ach / peak_tf,
+                    "peak_source": f"{which} bf16_tflops_sustained", "traffic": None,
+                    "launches_per_step": pr.gemm_launches / min(K, 3),
+                    "share_of_step": (pr.gemm_ms / min(K, 3)) / (ms / K)}
+    m.synchronize()
+    whash = m.weights_hash()
+    if world > 1:
+        hs = [None] * world
+        dist.all_gather_object(hs, whash)
+        same = len(set(hs)) == 1
+    else:
+        same = True
+
+    if rank == 0:
+        fl = step_flops(dict(c, ff_act=COMMON["ff_act"]), Bt)
+        line = {"metric": "compressed symbols/s (fwd+bwd+RMSProp)", "value": value, "unit": "symbols/s",
+                "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": ms / K, "higher_is_better": True,
+                "scaling": "strong", "vs_baseline": None, "dtype": "bf16" if p.use_bf16 else "f32",
+                "data": "synthetic",
+                "config": {"workload": f"{args.config}: NNCP Transformer-XL train step, vocab {V}, "
+                                       f"{c['n_layer']} layers, d_model {c['d_model']}, {c['n_head']}x{c['d_key']} heads, "
+                                       f"d_ff {c['d_inner']}, seg {T}, mem {c['mem_len']}, {Bt} streams",
+                           "streams_per_gpu": B, "parallelism": f"dp{world} over streams",
+                           "l2": "per-step working set (weights, optimizer state, activations) exceeds the 126 MB L2",
+                           "tokens": "seeded Zipf(1.1)+order-1 Markov ids (stand-in for tokenised text)"},
+                "step_tflops": fl / (ms / K * 1e-3) / 1e12 , "step_gflop": fl / 1e9,
+                "gpu_launches": int(prof.launches), "clocks": clocks,
+                "e2e": {"value": e2e, "unit": "symbols/s", "h2d_bytes_per_step": 2 * T * B * 4 * world,
+                        "d2h_bytes_per_step": (T * B * nb * 2 + 4) * world if nb else (T * B * V * 4 + 4) * world,
+                        "ms_per_step": ms_e2e / K},
+                "ranks_hold_identical_weights": same}
+        if roof:
+            line["roofline"] = roof
+        if not args.no_cpu_baseline and world == 1:
+            streams = 2 if args.config == "c2" else c["n_streams"]
+            val, dt = cpu_port_run(c, 2, 1, streams)
+            line["cpu_baseline"] = {"value": val, "unit": "symbols/s", "cores": os.cpu_count(), "kind": "port",
+                                    "sample": f"2 steps of {streams} streams x {T} symbols of the same model "
+                                              f"(oracle/trf_oracle.c, OpenMP, {dt:.1f} s)"}
+        print(json.dumps(line), flush=True)
+    m.close()
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -269,6 +269,18 @@ int nncu_gemm_bf16_nt(int backend, int M, int N, int K, const void *A, int lda,
                       const void *B, int ldb, void *C, int ldc, int c_is_f32,
                       const float *bias, void *cuda_stream);
 
+/* ---- measurement hooks (PROF_* buckets of libnc.h:16-65 count cycles per phase; here the
+ * library counts its own kernel launches and, on request, times every launch of the
+ * tensor-core GEMM with CUDA events on the launching stream) ---- */
+typedef struct nncu_profile {
+    uint64_t launches;      /* kernels launched by this library since nncu_profile_begin */
+    uint64_t gemm_launches; /* timed tcgen05 GEMM launches */
+    double gemm_ms;         /* sum of their device durations */
+    double gemm_flops;      /* sum of 2*M*N*K over them */
+} nncu_profile;
+int nncu_profile_begin(int time_gemms);
+int nncu_profile_end(nncu_profile *out);
+
 #ifdef __cplusplus
 }
 #endif

@@ -64,6 +64,12 @@ class AttnShape(C.Structure):
     ]
 
 
+class Profile(C.Structure):
+    """struct nncu_profile (include/nncu.h)."""
+    _fields_ = [("launches", C.c_uint64), ("gemm_launches", C.c_uint64),
+                ("gemm_ms", C.c_double), ("gemm_flops", C.c_double)]
+
+
 _vp, _i, _sz = C.c_void_p, C.c_int, C.c_size_t
 _pi32, _pf = C.POINTER(C.c_int32), C.POINTER(C.c_float)
 
@@ -102,6 +108,8 @@ PROTOTYPES = {
     "nncu_attention_forward": (_i, [C.POINTER(AttnShape), _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "nncu_attention_backward": (_i, [C.POINTER(AttnShape)] + [_vp] * 13),
     "nncu_attention_reduce_tables": (_i, [C.POINTER(AttnShape), _vp, _vp, _vp, _vp, _i, _vp]),
+    "nncu_profile_begin": (_i, [_i]),
+    "nncu_profile_end": (_i, [C.POINTER(Profile)]),
     "nncu_gemm_bf16_nt": (_i, [_i, _i, _i, _i, _vp, _i, _vp, _i, _vp, _i, _i, _vp, _vp]),
 }
 

@@ -1,0 +1,75 @@
+// common.cuh -- status/error plumbing and dtype helpers shared by every kernel file.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+
+#include "nncu.h"
+
+typedef __nv_bfloat16 bf16;
+
+// last error message of the calling thread (nncu_last_error)
+extern thread_local char g_nncu_err[512];
+int nncu_fail(int code, const char *fmt, ...);
+
+#define CUDA_TRY(expr)                                                                     \
+    do {                                                                                   \
+        cudaError_t e_ = (expr);                                                           \
+        if (e_ != cudaSuccess)                                                             \
+            return nncu_fail(e_ == cudaErrorMemoryAllocation ? NNCU_ERR_NOMEM : NNCU_ERR_CUDA, \
+                             "%s:%d: %s -> %s", __FILE__, __LINE__, #expr,                 \
+                             cudaGetErrorString(e_));                                      \
+    } while (0)
+
+#define NNCU_TRY(expr)       \
+    do {                     \
+        int rc_ = (expr);    \
+        if (rc_ != NNCU_OK)  \
+            return rc_;      \
+    } while (0)
+
+// every kernel launch in the library is followed by exactly one KERNEL_CHECK
+extern unsigned long long g_nncu_launches;
+#define KERNEL_CHECK()                 \
+    do {                               \
+        g_nncu_launches++;             \
+        CUDA_TRY(cudaGetLastError());  \
+    } while (0)
+
+// optional per-launch timing of the tensor-core GEMM (nncu_profile_begin/end)
+struct GemmProfiler {
+    static const int MAX_EV = 8192;
+    cudaEvent_t ev[2 * MAX_EV];
+    double flops[MAX_EV];
+    int n;
+    bool ready;
+};
+extern GemmProfiler *g_nncu_prof;
+
+__device__ __forceinline__ float to_f(float x) { return x; }
+__device__ __forceinline__ float to_f(bf16 x) { return __bfloat162float(x); }
+template <typename T> __device__ __forceinline__ T from_f(float x);
+template <> __device__ __forceinline__ float from_f<float>(float x) { return x; }
+template <> __device__ __forceinline__ bf16 from_f<bf16>(float x) { return __float2bfloat16_rn(x); }
+// value after a round trip through the storage type
+template <typename T> __device__ __forceinline__ float round_to(float x) { return to_f(from_f<T>(x)); }
+
+static inline int ceil_div(long long a, long long b) { return (int)((a + b - 1) / b); }
+
+// fixed-order warp reductions (xor butterfly: every lane ends with the same value,
+// and the association depends on nothing but the lane count)
+__device__ __forceinline__ float warp_sum(float v)
+{
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1)
+        v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v)
+{
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1)
+        v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}

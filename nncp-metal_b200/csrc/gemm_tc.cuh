@@ -1,0 +1,454 @@
+// gemm_tc.cuh -- bf16 x bf16 -> fp32 GEMM on the 5th-generation tensor cores.
+//
+//   C[M][N] = A[M][K] . B[N][K]^T (+ bias[N])        ("NT": both operands K-major)
+//
+// Replaces nc_matmul (libnc.h:270-276) for every projection of the bf16 model.
+// sm_100a only: operands are staged by TMA (cp.async.bulk.tensor, 128-byte
+// swizzle, no cluster multicast) into a 3- or 4-stage shared-memory ring, one
+// elected thread issues tcgen05.mma (UMMA 128 x BN x 16, cta_group::1) into a
+// TMEM accumulator, and four epilogue warps read it back with tcgen05.ld.
+//
+//   warp 0      TMA producer (one lane)
+//   warp 1      TMEM allocation, MMA issue (one lane), TMEM release
+//   warps 2-5   epilogue: warp w owns TMEM lanes 32*(w%4) .. +31 = tile rows
+//
+// Out-of-range rows/columns/k are zero-filled by TMA on load and predicated
+// off on store, so M, N are arbitrary and K only needs 16-byte row strides.
+// Every wait is bounded: on expiry the kernel raises *err_flag and leaves
+// through the common exit that releases TMEM.
+//
+// Output element (m, n) is the accumulation, in k order, of UMMA K=16 steps of
+// one fixed instruction shape; it does not depend on what else is in the tile,
+// so a row of a one-symbol step equals the same row of a full-segment launch.
+#pragma once
+#include <cuda.h>
+
+#include <map>
+#include <mutex>
+#include <tuple>
+
+#include "common.cuh"
+
+namespace tc {
+
+constexpr int BM = 128;
+constexpr int BK = 64; // 64 bf16 = 128 bytes = one swizzle row
+constexpr uint32_t SPIN_LIMIT = 4000000u;
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p)
+{
+    return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count)
+{
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes)
+{
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
+                 : "memory");
+}
+// non-blocking probe of the phase with the given parity
+__device__ __forceinline__ uint32_t mbar_test(uint32_t bar, uint32_t parity)
+{
+    uint32_t ok;
+    asm volatile("{\n\t.reg .pred p;\n\t"
+                 "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+                 "selp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok)
+                 : "r"(bar), "r"(parity)
+                 : "memory");
+    return ok;
+}
+// bounded wait; returns false (and raises the flags) when the limit is hit or
+// another role of this CTA has already given up
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_s,
+                                          int *err_flag, int code)
+{
+    for (uint32_t it = 0; it < SPIN_LIMIT; it++) {
+        if (mbar_test(bar, parity))
+            return true;
+        if (it > 2048) { // back off: the limit is then about half a second
+            if (*abort_s)
+                return false;
+            __nanosleep(100);
+        }
+    }
+    *abort_s = 1;
+    atomicExch(err_flag, code);
+    return false;
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, uint32_t bar,
+                                            int x, int y)
+{
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes"
+                 " [%0], [%1, {%3, %4}], [%2];" ::"r"(dst),
+                 "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(x), "r"(y)
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t ncols)
+{
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem),
+                 "r"(ncols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols)
+{
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols)
+                 : "memory");
+}
+__device__ __forceinline__ void fence_before_sync()
+{
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void fence_after_sync()
+{
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc,
+                                          uint32_t idesc, uint32_t accumulate)
+{
+    asm volatile("{\n\t.reg .pred p;\n\t"
+                 "setp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
+                 "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+                 : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar)
+{
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
+                 : "memory");
+}
+// 32 lanes x 32 consecutive fp32 columns: thread t gets row (lane base + t)
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t *r)
+{
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+          "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+          "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]),
+          "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]),
+          "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// shared-memory matrix descriptor: K-major tile, 128-byte swizzle, rows of 128 bytes,
+// 8-row groups 1024 bytes apart
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr)
+{
+    uint64_t d = 0;
+    d |= (uint64_t)((addr & 0x3FFFFu) >> 4);  // start address
+    d |= (uint64_t)1 << 16;                   // leading-dimension byte offset (unused here)
+    d |= (uint64_t)(1024u >> 4) << 32;        // stride-dimension byte offset
+    d |= (uint64_t)1 << 46;                   // descriptor version of sm_100
+    d |= (uint64_t)2 << 61;                   // SWIZZLE_128B
+    return d;
+}
+
+template <int BN>
+struct SmemLayout {
+    static constexpr int A_BYTES = BM * BK * 2;
+    static constexpr int B_BYTES = BN * BK * 2;
+    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+    static constexpr int STAGES = (BN == 256) ? 4 : 4;
+    static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES;
+    static constexpr int TOTAL = BAR_OFFSET + 256 + 1024; // + barriers + alignment slack
+};
+
+template <int BN, typename TC>
+__global__ void __launch_bounds__(192, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+               TC *C, long ldc, const float *__restrict__ bias, const TC *addsrc, int M, int N,
+               int K, int *err_flag)
+{
+    using SL = SmemLayout<BN>;
+    extern __shared__ unsigned char smraw_[];
+    // 1024-byte alignment for the 128-byte swizzle atoms
+    unsigned char *sm = reinterpret_cast<unsigned char *>(
+        (reinterpret_cast<uintptr_t>(smraw_) + 1023) & ~(uintptr_t)1023);
+    uint64_t *bars = reinterpret_cast<uint64_t *>(sm + SL::BAR_OFFSET);
+    uint64_t *full = bars, *empty = bars + SL::STAGES, *tmem_full = bars + 2 * SL::STAGES;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * SL::STAGES + 1);
+    volatile int *abort_s = reinterpret_cast<volatile int *>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+    const int nkb = (K + BK - 1) / BK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < SL::STAGES; s++) {
+            mbar_init(smem_u32(&full[s]), 1);
+            mbar_init(smem_u32(&empty[s]), 1);
+        }
+        mbar_init(smem_u32(tmem_full), 1);
+        *abort_s = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1)
+        tmem_alloc(smem_u32(tmem_slot), BN);
+    fence_before_sync();
+    __syncthreads();
+    fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            for (int kb = 0; kb < nkb; kb++) {
+                const int s = kb % SL::STAGES;
+                const uint32_t ph = (kb / SL::STAGES) & 1;
+                if (kb >= SL::STAGES &&
+                    !mbar_wait(smem_u32(&empty[s]), ph ^ 1, abort_s, err_flag, 1))
+                    break;
+                const uint32_t fb = smem_u32(&full[s]);
+                mbar_expect_tx(fb, SL::STAGE_BYTES);
+                unsigned char *a_dst = sm + s * SL::STAGE_BYTES;
+                tma_load_2d(smem_u32(a_dst), &map_a, fb, kb * BK, m0);
+                tma_load_2d(smem_u32(a_dst + SL::A_BYTES), &map_b, fb, kb * BK, n0);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) |
+                                       ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+            bool ok = true;
+            for (int kb = 0; kb < nkb && ok; kb++) {
+                const int s = kb % SL::STAGES;
+                const uint32_t ph = (kb / SL::STAGES) & 1;
+                ok = mbar_wait(smem_u32(&full[s]), ph, abort_s, err_flag, 2);
+                if (!ok)
+                    break;
+                fence_after_sync();
+                const uint32_t a_addr = smem_u32(sm + s * SL::STAGE_BYTES);
+                const uint64_t adesc = smem_desc_sw128(a_addr);
+                const uint64_t bdesc = smem_desc_sw128(a_addr + SL::A_BYTES);
+#pragma unroll
+                for (int k = 0; k < BK / 16; k++) // 32 bytes along K per UMMA: +2 in 16-byte units
+                    umma_bf16(tmem_base, adesc + 2 * k, bdesc + 2 * k, idesc,
+                              (kb > 0 || k > 0) ? 1u : 0u);
+                umma_commit(smem_u32(&empty[s])); // frees the stage when these MMAs retire
+            }
+            if (ok)
+                umma_commit(smem_u32(tmem_full));
+        }
+    } else {
+        // epilogue warps 2..5
+        const int quarter = warp & 3;
+        bool ok = true;
+        if (nkb > 0)
+            ok = mbar_wait(smem_u32(tmem_full), 0, abort_s, err_flag, 3);
+        ok = __all_sync(0xffffffffu, ok); // tcgen05.ld below is warp-collective
+        fence_after_sync();
+        const int row = m0 + quarter * 32 + lane;
+        if (ok) {
+#pragma unroll 1
+            for (int c0 = 0; c0 < BN; c0 += 32) {
+                if (n0 + c0 >= N)
+                    break; // uniform over the warp
+                uint32_t r[32];
+                if (nkb > 0) {
+                    tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0, r);
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 32; j++)
+                        r[j] = 0u;
+                }
+                if (row < M) {
+                    TC *dst = C + (long)row * ldc + n0 + c0;
+                    const TC *add = addsrc ? addsrc + (long)row * ldc + n0 + c0 : nullptr;
+                    const int nvalid = min(32, N - (n0 + c0));
+                    float x[32];
+#pragma unroll
+                    for (int j = 0; j < 32; j++) {
+                        x[j] = __uint_as_float(r[j]);
+                        if (bias && j < nvalid)
+                            x[j] += bias[n0 + c0 + j];
+                    }
+                    const bool vec = nvalid == 32 && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0) &&
+                                     (!add || (reinterpret_cast<uintptr_t>(add) & 15) == 0);
+                    if (vec) {
+                        if (sizeof(TC) == 2) {
+                            if (add) {
+                                const uint4 *a4 = reinterpret_cast<const uint4 *>(add);
+#pragma unroll
+                                for (int v = 0; v < 4; v++) {
+                                    uint4 t = a4[v];
+                                    const uint32_t w[4] = {t.x, t.y, t.z, t.w};
+#pragma unroll
+                                    for (int u = 0; u < 4; u++) {
+                                        __nv_bfloat162 h = *reinterpret_cast<const __nv_bfloat162 *>(&w[u]);
+                                        x[v * 8 + u * 2] += __low2float(h);
+                                        x[v * 8 + u * 2 + 1] += __high2float(h);
+                                    }
+                                }
+                            }
+                            uint4 *d4 = reinterpret_cast<uint4 *>(dst);
+#pragma unroll
+                            for (int v = 0; v < 4; v++) {
+                                uint32_t pk[4];
+#pragma unroll
+                                for (int u = 0; u < 4; u++) {
+                                    __nv_bfloat162 h = __floats2bfloat162_rn(x[v * 8 + u * 2], x[v * 8 + u * 2 + 1]);
+                                    pk[u] = *reinterpret_cast<uint32_t *>(&h);
+                                }
+                                d4[v] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+                            }
+                        } else {
+                            if (add) {
+                                const float4 *a4 = reinterpret_cast<const float4 *>(add);
+#pragma unroll
+                                for (int v = 0; v < 8; v++) {
+                                    float4 t = a4[v];
+                                    x[v * 4] += t.x; x[v * 4 + 1] += t.y; x[v * 4 + 2] += t.z; x[v * 4 + 3] += t.w;
+                                }
+                            }
+                            float4 *d4 = reinterpret_cast<float4 *>(dst);
+#pragma unroll
+                            for (int v = 0; v < 8; v++)
+                                d4[v] = make_float4(x[v * 4], x[v * 4 + 1], x[v * 4 + 2], x[v * 4 + 3]);
+                        }
+                    } else {
+                        for (int j = 0; j < nvalid; j++) {
+                            float y = x[j];
+                            if (add)
+                                y += to_f(add[j]);
+                            dst[j] = from_f<TC>(y);
+                        }
+                    }
+                }
+            }
+        }
+    }
+    // common exit: nobody touches TMEM after this barrier
+    fence_before_sync();
+    __syncthreads();
+    if (*abort_s) {
+        // a wait gave up: let copies that are still in flight land before the CTA retires
+        for (int i = 0; i < 2000; i++)
+            __nanosleep(500);
+    }
+    if (warp == 1) {
+        fence_after_sync();
+        tmem_dealloc(tmem_base, BN);
+    }
+}
+
+// ---------------- host side ----------------
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *,
+                                  const cuuint64_t *, const cuuint64_t *, const cuuint32_t *,
+                                  const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn()
+{
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    });
+    return fn;
+}
+
+// tensor maps are pure functions of (pointer, extents, stride, box): cache them
+struct TmapKey {
+    const void *ptr;
+    long rows, cols, ld;
+    int box_rows;
+    bool operator<(const TmapKey &o) const
+    {
+        return std::tie(ptr, rows, cols, ld, box_rows) < std::tie(o.ptr, o.rows, o.cols, o.ld, o.box_rows);
+    }
+};
+
+static int make_tmap(const void *ptr, long rows, long cols, long ld, int box_rows, CUtensorMap *out)
+{
+    static std::map<TmapKey, CUtensorMap> cache;
+    static std::mutex mu;
+    TmapKey key{ptr, rows, cols, ld, box_rows};
+    std::lock_guard<std::mutex> lock(mu);
+    auto it = cache.find(key);
+    if (it != cache.end()) {
+        *out = it->second;
+        return NNCU_OK;
+    }
+    EncodeTiledFn fn = encode_fn();
+    if (!fn)
+        return nncu_fail(NNCU_ERR_CUDA, "cuTensorMapEncodeTiled is not available");
+    cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+    cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void *>(ptr), dims, strides,
+                    box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS)
+        return nncu_fail(NNCU_ERR_CUDA, "cuTensorMapEncodeTiled failed: %d (rows %ld cols %ld ld %ld)",
+                         (int)r, rows, cols, ld);
+    if (cache.size() > 4096)
+        cache.clear();
+    cache[key] = *out;
+    return NNCU_OK;
+}
+
+static bool usable(const void *A, long lda, const void *B, long ldb, int K)
+{
+    return K > 0 && (lda % 8) == 0 && (ldb % 8) == 0 &&
+           (reinterpret_cast<uintptr_t>(A) & 15) == 0 && (reinterpret_cast<uintptr_t>(B) & 15) == 0;
+}
+
+template <int BN, typename TC>
+static int launch(cudaStream_t st, int M, int N, int K, const bf16 *A, long lda, const bf16 *B,
+                  long ldb, TC *C, long ldc, const float *bias, const TC *addsrc, int *err_flag)
+{
+    using SL = SmemLayout<BN>;
+    CUtensorMap ma, mb;
+    NNCU_TRY(make_tmap(A, M, K, lda, BM, &ma));
+    NNCU_TRY(make_tmap(B, N, K, ldb, BN, &mb));
+    static bool attr_done = false;
+    if (!attr_done) {
+        CUDA_TRY(cudaFuncSetAttribute(gemm_tc_kernel<BN, TC>,
+                                      cudaFuncAttributeMaxDynamicSharedMemorySize, SL::TOTAL));
+        attr_done = true;
+    }
+    dim3 grid(ceil_div(N, BN), ceil_div(M, BM));
+    GemmProfiler *pr = g_nncu_prof;
+    const bool timed = pr && pr->n < GemmProfiler::MAX_EV;
+    if (timed)
+        cudaEventRecord(pr->ev[2 * pr->n], st);
+    gemm_tc_kernel<BN, TC><<<grid, 192, SL::TOTAL, st>>>(ma, mb, C, ldc, bias, addsrc, M, N, K, err_flag);
+    if (timed) {
+        cudaEventRecord(pr->ev[2 * pr->n + 1], st);
+        pr->flops[pr->n++] = 2.0 * M * N * K;
+    }
+    KERNEL_CHECK();
+    return NNCU_OK;
+}
+
+// C bf16 or fp32; addsrc (may be NULL, may alias C) is added to the product.
+// err_flag: device int raised when a bounded wait expires.
+template <typename TC>
+static int gemm_nt(cudaStream_t st, int M, int N, int K, const bf16 *A, long lda, const bf16 *B,
+                   long ldb, TC *C, long ldc, const float *bias, const TC *addsrc, int *err_flag)
+{
+    if (M <= 0 || N <= 0)
+        return NNCU_OK;
+    if (!usable(A, lda, B, ldb, K))
+        return nncu_fail(NNCU_ERR_INVALID, "tcgen05 GEMM needs 16-byte aligned operands and strides");
+    // wide tiles once there are enough of them to fill the 148 SMs
+    long wide_tiles = (long)ceil_div(M, BM) * ceil_div(N, 256);
+    if (wide_tiles >= 120)
+        return launch<256, TC>(st, M, N, K, A, lda, B, ldb, C, ldc, bias, addsrc, err_flag);
+    return launch<128, TC>(st, M, N, K, A, lda, B, ldb, C, ldc, bias, addsrc, err_flag);
+}
+
+} // namespace tc

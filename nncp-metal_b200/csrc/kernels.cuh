@@ -1,0 +1,418 @@
+// kernels.cuh -- the HBM-bound kernels of the train step: embedding, LayerNorm /
+// RMSNorm with residual, activations, output softmax, loss gradient, column
+// sums for bias gradients, the optimizer, the embedding gradient, transposes.
+//
+// Every reduction has a fixed association (warp butterflies, block trees and
+// ordered loops; no atomics on floats), so a step is reproducible run to run
+// and each forward row is independent of how many rows share the launch.
+#pragma once
+#include "common.cuh"
+
+// ------------------------------------------------------------------
+// embedding gather: x[r][:] = embed[id[r]][:] * mult        (nc_get_col, nncp.c:625-630)
+template <typename T>
+__global__ void embed_kernel(const int32_t *__restrict__ ids, const float *__restrict__ embed,
+                             T *__restrict__ x, int rows, int D, float mult, int V)
+{
+    int r = blockIdx.x;
+    if (r >= rows)
+        return;
+    int id = ids[r];
+    id = id < 0 ? 0 : (id >= V ? V - 1 : id);
+    const float *e = embed + (size_t)id * D;
+    T *o = x + (size_t)r * D;
+    for (int i = threadIdx.x; i < D; i += blockDim.x)
+        o[i] = from_f<T>(e[i] * mult);
+}
+
+// ------------------------------------------------------------------
+// s = a (+ res); y = norm(s) * g + b.  One warp per row.     (layer_norm, nncp.c:279-288)
+// mode: 0 = copy only (y = s), 1 = LayerNorm, 2 = RMSNorm.  s_out / stats may be NULL.
+// The statistics are taken from s after rounding to the storage type, so that the
+// backward pass, which reads the stored s, sees exactly the normalised values.
+template <typename T>
+__global__ void __launch_bounds__(128)
+residual_norm_kernel(const T *__restrict__ a, const T *__restrict__ res, T *__restrict__ s_out,
+                     T *__restrict__ y, const float *__restrict__ g, const float *__restrict__ b,
+                     float *__restrict__ stats, int rows, int D, int mode)
+{
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int r = blockIdx.x * 4 + warp;
+    if (r >= rows)
+        return;
+    const T *ar = a + (size_t)r * D;
+    const T *rr = res ? res + (size_t)r * D : nullptr;
+    float sum = 0.0f;
+    for (int i = lane; i < D; i += 32) {
+        float v = to_f(ar[i]);
+        if (rr)
+            v = round_to<T>(v + to_f(rr[i]));
+        sum += v;
+    }
+    float mu = 0.0f, rstd = 1.0f;
+    if (mode != 0) {
+        if (mode == 1)
+            mu = warp_sum(sum) / (float)D;
+        float var = 0.0f;
+        for (int i = lane; i < D; i += 32) {
+            float v = to_f(ar[i]);
+            if (rr)
+                v = round_to<T>(v + to_f(rr[i]));
+            var += (v - mu) * (v - mu);
+        }
+        var = warp_sum(var) / (float)D;
+        rstd = 1.0f / sqrtf(var + 1e-5f);
+        if (stats && lane == 0) {
+            stats[2 * r] = mu;
+            stats[2 * r + 1] = rstd;
+        }
+    }
+    for (int i = lane; i < D; i += 32) {
+        float v = to_f(ar[i]);
+        if (rr)
+            v = round_to<T>(v + to_f(rr[i]));
+        if (s_out)
+            s_out[(size_t)r * D + i] = from_f<T>(v);
+        float o = (mode != 0) ? (v - mu) * rstd * g[i] + b[i] : v;
+        y[(size_t)r * D + i] = from_f<T>(o);
+    }
+}
+
+// Adjoint of y = norm(x)*g + b:  dx = (base ? base : 0) + J^T dy ; per-block partial
+// dg/db in part[blockIdx][2][D].  Block = 8 warps, each warp walks rows
+// blockIdx*RPB + warp, +8, ... inside the block's RPB-row chunk.
+template <typename T>
+__global__ void __launch_bounds__(256)
+norm_bwd_kernel(const T *__restrict__ dy, const T *__restrict__ x, const float *__restrict__ g,
+                const float *__restrict__ stats, const T *__restrict__ base, T *__restrict__ dx,
+                float *__restrict__ part, int rows, int D, int mode, int rpb)
+{
+    extern __shared__ float sm[]; // [8][2][D]
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    float *mydg = sm + (size_t)warp * 2 * D, *mydb = mydg + D;
+    for (int i = lane; i < D; i += 32) {
+        mydg[i] = 0.0f;
+        mydb[i] = 0.0f;
+    }
+    const int r_end = min(rows, (blockIdx.x + 1) * rpb);
+    for (int r = blockIdx.x * rpb + warp; r < r_end; r += 8) {
+        const T *xr = x + (size_t)r * D, *dyr = dy + (size_t)r * D;
+        const float mu = stats[2 * r], rstd = stats[2 * r + 1];
+        float s1 = 0.0f, s2 = 0.0f;
+        for (int i = lane; i < D; i += 32) {
+            float xh = (to_f(xr[i]) - mu) * rstd;
+            float d = to_f(dyr[i]);
+            float dxh = d * g[i];
+            s1 += dxh;
+            s2 += dxh * xh;
+            mydg[i] += d * xh;
+            mydb[i] += d;
+        }
+        s1 = warp_sum(s1) / (float)D;
+        s2 = warp_sum(s2) / (float)D;
+        if (mode == 2)
+            s1 = 0.0f;
+        for (int i = lane; i < D; i += 32) {
+            float xh = (to_f(xr[i]) - mu) * rstd;
+            float dxh = to_f(dyr[i]) * g[i];
+            float v = rstd * (dxh - s1 - xh * s2);
+            if (base)
+                v += to_f(base[(size_t)r * D + i]);
+            dx[(size_t)r * D + i] = from_f<T>(v);
+        }
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < 2 * D; i += blockDim.x) {
+        float s = 0.0f;
+#pragma unroll
+        for (int w = 0; w < 8; w++)
+            s += sm[(size_t)w * 2 * D + i];
+        part[(size_t)blockIdx.x * 2 * D + i] = s;
+    }
+}
+
+// out[i] (+)= sum over parts p (in order) of part[p][i]; used for dg/db ([2][D] -> two
+// destinations) and every other two-stage column reduction.
+__global__ void reduce_parts_kernel(const float *__restrict__ part, int n_parts, int stride,
+                                    int n, float *__restrict__ out, int accumulate, float scale)
+{
+    int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n)
+        return;
+    float s = 0.0f;
+    for (int p = 0; p < n_parts; p++)
+        s += part[(size_t)p * stride + i];
+    s *= scale;
+    out[i] = accumulate ? out[i] + s : s;
+}
+
+// dst = a + b (elementwise), used where a residual joins without a norm
+template <typename T>
+__global__ void add_kernel(const T *__restrict__ a, const T *__restrict__ b, T *__restrict__ dst,
+                           size_t n)
+{
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n)
+        dst[i] = from_f<T>(to_f(a[i]) + to_f(b[i]));
+}
+
+// ------------------------------------------------------------------
+// feed-forward activation (nncp.c:938-966).  hpre [rows][F1], hact [rows][F].
+__device__ __forceinline__ float gelu_f(float x)
+{
+    return 0.5f * x * (1.0f + tanhf(0.7978845608028654f * (x + 0.044715f * x * x * x)));
+}
+__device__ __forceinline__ float gelu_grad_f(float x)
+{
+    float u = 0.7978845608028654f * (x + 0.044715f * x * x * x);
+    float t = tanhf(u);
+    float du = 0.7978845608028654f * (1.0f + 3.0f * 0.044715f * x * x);
+    return 0.5f * (1.0f + t) + 0.5f * x * (1.0f - t * t) * du;
+}
+
+template <typename T>
+__global__ void act_fwd_kernel(const T *__restrict__ hpre, T *__restrict__ hact, int rows, int F,
+                               int F1, int act)
+{
+    size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (size_t)rows * F)
+        return;
+    int r = (int)(idx / F), i = (int)(idx % F);
+    float a = to_f(hpre[(size_t)r * F1 + i]), o;
+    if (act == NNCU_FF_RELU)
+        o = a > 0.0f ? a : 0.0f;
+    else if (act == NNCU_FF_GELU)
+        o = gelu_f(a);
+    else
+        o = round_to<T>(gelu_f(a)) * to_f(hpre[(size_t)r * F1 + F + i]);
+    hact[idx] = from_f<T>(o);
+}
+
+template <typename T>
+__global__ void act_bwd_kernel(const T *__restrict__ hpre, const T *__restrict__ dhact,
+                               T *__restrict__ dhpre, int rows, int F, int F1, int act)
+{
+    size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (size_t)rows * F)
+        return;
+    int r = (int)(idx / F), i = (int)(idx % F);
+    float a = to_f(hpre[(size_t)r * F1 + i]), d = to_f(dhact[idx]);
+    if (act == NNCU_FF_RELU) {
+        dhpre[(size_t)r * F1 + i] = from_f<T>(a > 0.0f ? d : 0.0f);
+    } else if (act == NNCU_FF_GELU) {
+        dhpre[(size_t)r * F1 + i] = from_f<T>(d * gelu_grad_f(a));
+    } else {
+        float gate = to_f(hpre[(size_t)r * F1 + F + i]);
+        dhpre[(size_t)r * F1 + i] = from_f<T>(d * gate * gelu_grad_f(a));
+        dhpre[(size_t)r * F1 + F + i] = from_f<T>(d * gelu_f(a));
+    }
+}
+
+// ------------------------------------------------------------------
+// block-wide fixed-order reductions for 256-thread blocks
+__device__ __forceinline__ float block_sum_256(float v, float *red)
+{
+    v = warp_sum(v);
+    __syncthreads();
+    if ((threadIdx.x & 31) == 0)
+        red[threadIdx.x >> 5] = v;
+    __syncthreads();
+    float s = 0.0f;
+#pragma unroll
+    for (int w = 0; w < 8; w++)
+        s += red[w];
+    return s;
+}
+__device__ __forceinline__ float block_max_256(float v, float *red)
+{
+    v = warp_max(v);
+    __syncthreads();
+    if ((threadIdx.x & 31) == 0)
+        red[threadIdx.x >> 5] = v;
+    __syncthreads();
+    float s = red[0];
+#pragma unroll
+    for (int w = 1; w < 8; w++)
+        s = fmaxf(s, red[w]);
+    return s;
+}
+
+// in-place softmax over the V symbols of each row of fp32 logits (nc_soft_max, nncp.c:1008)
+__global__ void __launch_bounds__(256) softmax_rows_kernel(float *__restrict__ z, int rows, int V)
+{
+    __shared__ float red[8];
+    int r = blockIdx.x;
+    if (r >= rows)
+        return;
+    float *zr = z + (size_t)r * V;
+    float mx = -INFINITY;
+    for (int i = threadIdx.x; i < V; i += 256)
+        mx = fmaxf(mx, zr[i]);
+    mx = block_max_256(mx, red);
+    float s = 0.0f;
+    for (int i = threadIdx.x; i < V; i += 256) {
+        float e = expf(zr[i] - mx);
+        zr[i] = e;
+        s += e;
+    }
+    s = block_sum_256(s, red);
+    float rs = 1.0f / s;
+    for (int i = threadIdx.x; i < V; i += 256)
+        zr[i] *= rs;
+}
+
+// dz = (p - onehot(target)) * scale ; logp[r] = ln p[r][target]
+// (nc_indexed_log + the adjoint of softmax, nncp.c:1170-1175)
+template <typename T>
+__global__ void __launch_bounds__(256)
+loss_grad_kernel(const float *__restrict__ probs, const int32_t *__restrict__ targets,
+                 T *__restrict__ dz, float *__restrict__ logp, int rows, int V, float scale)
+{
+    int r = blockIdx.x;
+    if (r >= rows)
+        return;
+    int t = targets[r];
+    t = t < 0 ? 0 : (t >= V ? V - 1 : t);
+    const float *pr = probs + (size_t)r * V;
+    T *d = dz + (size_t)r * V;
+    for (int i = threadIdx.x; i < V; i += 256)
+        d[i] = from_f<T>((pr[i] - (i == t ? 1.0f : 0.0f)) * scale);
+    if (threadIdx.x == 0)
+        logp[r] = logf(pr[t]);
+}
+
+// loss = sum_r logp[r], one block, fixed order
+__global__ void __launch_bounds__(256) sum_vec_kernel(const float *__restrict__ v, int n,
+                                                      float *__restrict__ out)
+{
+    __shared__ float red[8];
+    float s = 0.0f;
+    for (int i = threadIdx.x; i < n; i += 256)
+        s += v[i];
+    s = block_sum_256(s, red);
+    if (threadIdx.x == 0)
+        *out = s;
+}
+
+// column sums of A [R][N] over row chunks: part[chunk][n]   (bias gradients)
+template <typename T>
+__global__ void colsum_part_kernel(const T *__restrict__ A, long lda, int R, int N, int rows_per,
+                                   float *__restrict__ part)
+{
+    int n = blockIdx.x * blockDim.x + threadIdx.x;
+    if (n >= N)
+        return;
+    int r0 = blockIdx.y * rows_per, r1 = min(R, r0 + rows_per);
+    float s = 0.0f;
+    for (int r = r0; r < r1; r++)
+        s += to_f(A[(long)r * lda + n]);
+    part[(size_t)blockIdx.y * N + n] = s;
+}
+
+// ------------------------------------------------------------------
+// optimizer (nc_sgd_opt_update, nncp.c:1229; constants libnc.h:547-561):
+//   g' = clamp(g) ; v = b2*v + (1-b2)*g'^2 ; w -= lr*g'/(sqrt(v*corr)+eps)
+// and the bf16 shadow of w refreshed in the same pass.
+__global__ void __launch_bounds__(256)
+rmsprop_kernel(float *__restrict__ w, const float *__restrict__ g, float *__restrict__ v,
+               bf16 *__restrict__ shadow, size_t n4, float lr, float beta2, float eps,
+               float clip, float corr)
+{
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n4)
+        return;
+    float4 ww = reinterpret_cast<float4 *>(w)[i];
+    float4 gg = reinterpret_cast<const float4 *>(g)[i];
+    float4 vv = reinterpret_cast<float4 *>(v)[i];
+    float *pw = &ww.x, *pg = &gg.x, *pv = &vv.x;
+#pragma unroll
+    for (int k = 0; k < 4; k++) {
+        float x = pg[k];
+        if (clip != 0.0f)
+            x = fminf(fmaxf(x, -clip), clip);
+        pv[k] = beta2 * pv[k] + (1.0f - beta2) * x * x;
+        if (x != 0.0f)
+            pw[k] -= lr * x / (sqrtf(pv[k] * corr) + eps);
+    }
+    reinterpret_cast<float4 *>(w)[i] = ww;
+    reinterpret_cast<float4 *>(v)[i] = vv;
+    if (shadow) {
+        __nv_bfloat162 lo = __floats2bfloat162_rn(ww.x, ww.y);
+        __nv_bfloat162 hi = __floats2bfloat162_rn(ww.z, ww.w);
+        uint2 pk;
+        pk.x = *reinterpret_cast<uint32_t *>(&lo);
+        pk.y = *reinterpret_cast<uint32_t *>(&hi);
+        reinterpret_cast<uint2 *>(shadow)[i] = pk;
+    }
+}
+
+__global__ void f32_to_bf16_kernel(const float *__restrict__ src, bf16 *__restrict__ dst, size_t n)
+{
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n)
+        dst[i] = __float2bfloat16_rn(src[i]);
+}
+
+// ------------------------------------------------------------------
+// dense embedding gradient: g[v][:] = mult * sum over rows r with id[r]==v (in row order)
+// of dx[r][:].  One block per symbol; every row of g is written (zeros included).
+template <typename T>
+__global__ void __launch_bounds__(128)
+embed_grad_kernel(const int32_t *__restrict__ ids, const T *__restrict__ dx,
+                  float *__restrict__ g, int rows, int D, float mult, int V)
+{
+    extern __shared__ int32_t sids[];
+    const int v = blockIdx.x;
+    for (int i = threadIdx.x; i < rows; i += blockDim.x) {
+        int id = ids[i];
+        sids[i] = id < 0 ? 0 : (id >= V ? V - 1 : id);
+    }
+    __syncthreads();
+    for (int c = threadIdx.x; c < D; c += blockDim.x) {
+        float s = 0.0f;
+        for (int r = 0; r < rows; r++)
+            if (sids[r] == v)
+                s += to_f(dx[(size_t)r * D + c]);
+        g[(size_t)v * D + c] = s * mult;
+    }
+}
+
+// ------------------------------------------------------------------
+// dst[c][r] = src[r][c]  (bf16 32x32 tiles through shared memory)
+__global__ void __launch_bounds__(256)
+transpose_bf16_kernel(const bf16 *__restrict__ src, long lds, bf16 *__restrict__ dst, long ldd,
+                      int R, int Ccols)
+{
+    __shared__ bf16 tile[32][33];
+    int c0 = blockIdx.x * 32, r0 = blockIdx.y * 32;
+    int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+    for (int j = ty; j < 32; j += 8) {
+        int r = r0 + j, c = c0 + tx;
+        if (r < R && c < Ccols)
+            tile[j][tx] = src[(long)r * lds + c];
+    }
+    __syncthreads();
+    for (int j = ty; j < 32; j += 8) {
+        int c = c0 + j, r = r0 + tx;
+        if (r < R && c < Ccols)
+            dst[(long)c * ldd + r] = tile[tx][j];
+    }
+}
+
+// ------------------------------------------------------------------
+// order-independent 64-bit digest of a float buffer: sum of mix(index, bits) mod 2^64
+__device__ __forceinline__ unsigned long long mix64(unsigned long long x)
+{
+    x += 0x9E3779B97F4A7C15ull;
+    x = (x ^ (x >> 30)) * 0xBF58476D1CE4E5B9ull;
+    x = (x ^ (x >> 27)) * 0x94D049BB133111EBull;
+    return x ^ (x >> 31);
+}
+__global__ void hash_kernel(const float *__restrict__ w, size_t n, unsigned long long *out)
+{
+    unsigned long long s = 0;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n;
+         i += (size_t)gridDim.x * blockDim.x)
+        s += mix64((i << 32) ^ (unsigned long long)__float_as_uint(w[i]));
+    atomicAdd(out, s); // integer addition: the order of arrival does not change the sum
+}

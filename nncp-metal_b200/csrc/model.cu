@@ -1,0 +1,1308 @@
+// model.cu -- the Transformer-XL train step behind the C ABI of include/nncu.h.
+//
+// Host-side orchestration only; every number is produced by the kernels in
+// gemm_simt.cuh, gemm_tc.cuh, attention.cuh, kernels.cuh and coder.cuh.
+//
+//   forward_range    trf_eval            nncp.c:581-1029
+//   backward         trf_eval_gradient   nncp.c:1099-1193 (hand-derived adjoint)
+//   optimizer_step   nc_sgd_opt_update   nncp.c:1229
+//   memory_shift     mem_update          nncp.c:1205-1221
+//
+// Data layout in HBM.  A "row" is one (time, stream) position, row = time*B +
+// stream, so the rows of one time step are contiguous: a one-symbol step is the
+// batched forward restricted to a row range.  Per layer, hcat = [memory ; segment]
+// rows (memory first) is the input of the K/V projection; the segment part is
+// also the query input and what becomes memory after the step.  All layers'
+// hcat live in one allocation with a twin: the memory shift copies rows
+// [T*B, L*B) of every layer into rows [0, M*B) of the twin and swaps.
+// Parameters, gradients and second moments are three flat fp32 buffers with
+// identical offsets (512-byte aligned slots); bf16 models add a bf16 shadow
+// and a transposed bf16 shadow of the matrices, refreshed by the optimizer.
+#include <math.h>
+#include <stdarg.h>
+#include <string.h>
+
+#include <algorithm>
+#include <initializer_list>
+#include <string>
+#include <vector>
+
+#include "attention.cuh"
+#include "coder.cuh"
+#include "common.cuh"
+#include "gemm_simt.cuh"
+#include "gemm_tc.cuh"
+#include "kernels.cuh"
+
+thread_local char g_nncu_err[512] = "";
+unsigned long long g_nncu_launches = 0;
+GemmProfiler *g_nncu_prof = nullptr;
+
+int nncu_fail(int code, const char *fmt, ...)
+{
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_nncu_err, sizeof(g_nncu_err), fmt, ap);
+    va_end(ap);
+    return code;
+}
+
+#define NONE ((size_t)-1)
+
+struct ParamInfo {
+    char name[32];
+    size_t numel, off;
+    int rows, cols; // matrices that get a transposed shadow: rows x cols, else rows = 0
+};
+
+struct LayerOff {
+    size_t w_q, w_kv, b_q, w_o, ff1, ff_bias1, ff2, ff_bias2, w_r, b_r, ln_g1, ln_b1, ln_g2, ln_b2;
+};
+
+struct LayerAct {
+    void *xin, *q, *kv, *o, *s1, *y, *u, *hpre, *hact, *s2;
+    float *lse, *st_pre1, *st_1, *st_pre2, *st_2;
+};
+
+struct TransposeJob {
+    unsigned long long src_off, dst_off;
+    int rows, cols, tile0, tiles_x;
+};
+
+struct nncu_model {
+    nncu_params p;
+    int D, H, dk, HD, F, F1, T, B, M, L, V, TB, LB, Bt, nl;
+    bool bf;      // bf16 model
+    bool use_tc;  // tcgen05 GEMMs
+    size_t esz;   // bytes per activation element
+    int device;
+    cudaStream_t st;
+    std::vector<ParamInfo> pinfo;
+    std::vector<LayerOff> lo;
+    size_t ln_g, ln_b, embed, embed_out, out_bias, n_floats;
+    // device memory (one arena)
+    char *arena;
+    size_t arena_bytes;
+    float *W, *G, *Vm;
+    bf16 *Wb, *WbT;
+    char *hcat[2];
+    int cur;
+    std::vector<LayerAct> act;
+    void *xlast, *xf, *pool[4], *dz, *dh, *dhp, *dof, *dq, *dkv, *tA, *tB;
+    float *st_f, *probs, *dwr_part, *dbr_part, *part, *logp, *loss_dev;
+    int32_t *ids_dev, *tgt_dev;
+    int *err_flag;
+    unsigned long long *hash_dev;
+    TransposeJob *jobs_dev;
+    int n_jobs, n_job_tiles;
+    uint16_t *coder_dev;
+    size_t coder_bytes;
+    // host staging (pinned)
+    int32_t *ids_pin, *tgt_pin;
+    float *loss_pin;
+    float lr;
+    long step;
+    int steps_done;
+    bool have_forward;
+};
+
+// ------------------------------------------------------------------ helpers
+
+template <typename AT> static inline AT *at(void *base, size_t elem) { return reinterpret_cast<AT *>(base) + elem; }
+template <typename AT> static inline const AT *atc(const void *base, size_t elem) { return reinterpret_cast<const AT *>(base) + elem; }
+
+static inline char *hcat_layer(nncu_model *m, int which, int l)
+{
+    return m->hcat[which] + (size_t)l * m->LB * m->D * m->esz;
+}
+
+// compute copy of a parameter: the fp32 master for fp32 models, the bf16 shadow otherwise
+template <typename AT> static inline const AT *wptr(nncu_model *m, size_t off);
+template <> inline const float *wptr<float>(nncu_model *m, size_t off) { return m->W + off; }
+template <> inline const bf16 *wptr<bf16>(nncu_model *m, size_t off) { return m->Wb + off; }
+
+static inline const float *wf(nncu_model *m, size_t off) { return off == NONE ? nullptr : m->W + off; }
+static inline float *gf(nncu_model *m, size_t off) { return m->G + off; }
+
+static int check_err_flag(nncu_model *m)
+{
+    int flag = 0;
+    CUDA_TRY(cudaMemcpyAsync(&flag, m->err_flag, sizeof(int), cudaMemcpyDeviceToHost, m->st));
+    CUDA_TRY(cudaStreamSynchronize(m->st));
+    if (flag != 0) {
+        cudaMemsetAsync(m->err_flag, 0, sizeof(int), m->st);
+        return nncu_fail(NNCU_ERR_TIMEOUT, "a bounded device-side wait expired (code %d)", flag);
+    }
+    return NNCU_OK;
+}
+
+// y = x W^T (+bias): C[M][N] = A[M][K] . Wt[N][K]^T
+template <typename AT, typename TC>
+static int mm_nt(nncu_model *m, int M, int N, int K, const AT *A, long lda, size_t w_off, TC *C,
+                 long ldc, const float *bias);
+
+template <typename TC>
+static int mm_nt_impl(nncu_model *m, int M, int N, int K, const float *A, long lda, size_t w_off,
+                      TC *C, long ldc, const float *bias)
+{
+    return gemm_simt<float, float, TC>(m->st, GEMM_NT, M, N, K, A, lda, m->W + w_off, K, C, ldc, bias, 0);
+}
+template <typename TC>
+static int mm_nt_impl(nncu_model *m, int M, int N, int K, const bf16 *A, long lda, size_t w_off,
+                      TC *C, long ldc, const float *bias)
+{
+    const bf16 *Wt = m->Wb + w_off;
+    if (m->use_tc && tc::usable(A, lda, Wt, K, K))
+        return tc::gemm_nt<TC>(m->st, M, N, K, A, lda, Wt, K, C, ldc, bias, nullptr, m->err_flag);
+    return gemm_simt<bf16, bf16, TC>(m->st, GEMM_NT, M, N, K, A, lda, Wt, K, C, ldc, bias, 0);
+}
+template <typename AT, typename TC>
+static int mm_nt(nncu_model *m, int M, int N, int K, const AT *A, long lda, size_t w_off, TC *C,
+                 long ldc, const float *bias)
+{
+    return mm_nt_impl<TC>(m, M, N, K, A, lda, w_off, C, ldc, bias);
+}
+
+// dx = dy W (+ addsrc): C[M][Kin] = dY[M][Nout] . W[Nout][Kin]
+static int mm_nn(nncu_model *m, int M, int Kin, int Nout, const float *dY, long ldy, size_t w_off,
+                 float *C, long ldc, const float *addsrc)
+{
+    if (addsrc && addsrc != C)
+        CUDA_TRY(cudaMemcpy2DAsync(C, ldc * 4, addsrc, ldc * 4, (size_t)Kin * 4, M,
+                                   cudaMemcpyDeviceToDevice, m->st));
+    return gemm_simt<float, float, float>(m->st, GEMM_NN, M, Kin, Nout, dY, ldy, m->W + w_off, Kin,
+                                          C, ldc, nullptr, addsrc ? 1 : 0);
+}
+static int mm_nn(nncu_model *m, int M, int Kin, int Nout, const bf16 *dY, long ldy, size_t w_off,
+                 bf16 *C, long ldc, const bf16 *addsrc)
+{
+    const bf16 *WT = m->WbT + w_off; // [Kin][Nout]
+    if (m->use_tc && tc::usable(dY, ldy, WT, Nout, Nout))
+        return tc::gemm_nt<bf16>(m->st, M, Kin, Nout, dY, ldy, WT, Nout, C, ldc, nullptr, addsrc,
+                                 m->err_flag);
+    if (addsrc && addsrc != C)
+        CUDA_TRY(cudaMemcpy2DAsync(C, ldc * 2, addsrc, ldc * 2, (size_t)Kin * 2, M,
+                                   cudaMemcpyDeviceToDevice, m->st));
+    return gemm_simt<bf16, bf16, bf16>(m->st, GEMM_NN, M, Kin, Nout, dY, ldy, m->Wb + w_off, Kin, C,
+                                       ldc, nullptr, addsrc ? 1 : 0);
+}
+
+// dW = dY^T X: G[Nout][Kin] = sum over R rows of dY[r][Nout] X[r][Kin]   (fp32 result)
+static int mm_tn(nncu_model *m, int Nout, int Kin, int R, const float *dY, long ldy, const float *X,
+                 long ldx, float *Gout)
+{
+    return gemm_simt<float, float, float>(m->st, GEMM_TN, Nout, Kin, R, dY, ldy, X, ldx, Gout, Kin,
+                                          nullptr, 0);
+}
+static int mm_tn(nncu_model *m, int Nout, int Kin, int R, const bf16 *dY, long ldy, const bf16 *X,
+                 long ldx, float *Gout)
+{
+    if (m->use_tc && (R % 8) == 0) {
+        // both operands become K-major by an explicit transpose (the contraction runs over rows)
+        bf16 *tA = reinterpret_cast<bf16 *>(m->tA), *tB = reinterpret_cast<bf16 *>(m->tB);
+        transpose_bf16_kernel<<<dim3(ceil_div(Nout, 32), ceil_div(R, 32)), 256, 0, m->st>>>(
+            dY, ldy, tA, R, R, Nout);
+        KERNEL_CHECK();
+        transpose_bf16_kernel<<<dim3(ceil_div(Kin, 32), ceil_div(R, 32)), 256, 0, m->st>>>(
+            X, ldx, tB, R, R, Kin);
+        KERNEL_CHECK();
+        return tc::gemm_nt<float>(m->st, Nout, Kin, R, tA, R, tB, R, Gout, Kin, nullptr, nullptr,
+                                  m->err_flag);
+    }
+    return gemm_simt<bf16, bf16, float>(m->st, GEMM_TN, Nout, Kin, R, dY, ldy, X, ldx, Gout, Kin,
+                                        nullptr, 0);
+}
+
+template <typename AT>
+static int colsum(nncu_model *m, const AT *A, long lda, int R, int N, float *out)
+{
+    const int rows_per = 64;
+    int chunks = ceil_div(R, rows_per);
+    colsum_part_kernel<AT><<<dim3(ceil_div(N, 128), chunks), 128, 0, m->st>>>(A, lda, R, N, rows_per,
+                                                                            m->part);
+    KERNEL_CHECK();
+    reduce_parts_kernel<<<ceil_div(N, 256), 256, 0, m->st>>>(m->part, chunks, N, N, out, 0, 1.0f);
+    KERNEL_CHECK();
+    return NNCU_OK;
+}
+
+template <typename AT>
+static int norm_fwd(nncu_model *m, const AT *a, const AT *res, AT *s_out, AT *y, size_t g_off,
+                    size_t b_off, float *stats, int rows, bool do_norm)
+{
+    int mode = !do_norm ? 0 : ((m->p.ln_flags & NNCU_LN_RMSNORM) ? 2 : 1);
+    residual_norm_kernel<AT><<<ceil_div(rows, 4), 128, 0, m->st>>>(
+        a, res, s_out, y, do_norm ? m->W + g_off : nullptr, do_norm ? m->W + b_off : nullptr, stats,
+        rows, m->D, mode);
+    KERNEL_CHECK();
+    return NNCU_OK;
+}
+
+template <typename AT>
+static int norm_bwd(nncu_model *m, const AT *dy, const AT *x, size_t g_off, size_t b_off,
+                    const float *stats, const AT *base, AT *dx, int rows)
+{
+    const int rpb = 32;
+    int blocks = ceil_div(rows, rpb);
+    int mode = (m->p.ln_flags & NNCU_LN_RMSNORM) ? 2 : 1;
+    size_t smem = (size_t)8 * 2 * m->D * sizeof(float);
+    norm_bwd_kernel<AT><<<blocks, 256, smem, m->st>>>(dy, x, m->W + g_off, stats, base, dx, m->part,
+                                                      rows, m->D, mode, rpb);
+    KERNEL_CHECK();
+    reduce_parts_kernel<<<ceil_div(m->D, 256), 256, 0, m->st>>>(m->part, blocks, 2 * m->D, m->D,
+                                                               gf(m, g_off), 0, 1.0f);
+    KERNEL_CHECK();
+    reduce_parts_kernel<<<ceil_div(m->D, 256), 256, 0, m->st>>>(m->part + m->D, blocks, 2 * m->D,
+                                                               m->D, gf(m, b_off), 0, 1.0f);
+    KERNEL_CHECK();
+    return NNCU_OK;
+}
+
+static nncu_attn_shape attn_shape(nncu_model *m, int l, int t0, int t1)
+{
+    nncu_attn_shape s;
+    s.n_streams = m->B; s.n_head = m->H; s.d_key = m->dk; s.seg_len = m->T; s.mem_len = m->M;
+    s.d_pos = m->p.d_pos; s.attn_len = m->p.attn_len[l] ? m->p.attn_len[l] : m->L;
+    s.t0 = t0; s.t1 = t1;
+    s.br_scale = sqrtf((float)m->dk * (float)m->D);
+    s.dtype_bf16 = m->bf ? 1 : 0;
+    return s;
+}
+
+// ------------------------------------------------------------------ forward
+
+template <typename AT>
+static int forward_range(nncu_model *m, int t0, int t1)
+{
+    const nncu_params &p = m->p;
+    const int D = m->D, HD = m->HD, F = m->F, F1 = m->F1, B = m->B, M = m->M, V = m->V;
+    const int r0 = t0 * B, nr = (t1 - t0) * B;
+    const bool pre = p.ln_flags & NNCU_LN_PRE, post = p.ln_flags & NNCU_LN_POST;
+    const float emul = sqrtf((float)D) * p.embed_mult;
+    AT *tmp = reinterpret_cast<AT *>(m->pool[0]); // [TB][D] scratch
+
+    embed_kernel<AT><<<nr, 128, 0, m->st>>>(m->ids_dev + r0, m->W + m->embed,
+                                            at<AT>(m->act[0].xin, (size_t)r0 * D), nr, D, emul, V);
+    KERNEL_CHECK();
+    for (int l = 0; l < m->nl; l++) {
+        const LayerOff &o = m->lo[l];
+        LayerAct &a = m->act[l];
+        AT *hc = reinterpret_cast<AT *>(hcat_layer(m, m->cur, l));
+        AT *x1 = hc + ((size_t)M * B + r0) * D;   // attention input of these rows (train_h)
+        AT *xin = at<AT>(a.xin, (size_t)r0 * D);  // residual-stream input
+        if (pre)
+            NNCU_TRY(norm_fwd<AT>(m, xin, nullptr, nullptr, x1, o.ln_g1, o.ln_b1, a.st_pre1 + 2 * r0, nr, true));
+        // fused projections over [memory ; segment]: Q for the segment rows, K|V for the
+        // memory rows (once per segment) and the segment rows (nncp.c:659-695)
+        NNCU_TRY((mm_nt<AT, AT>(m, nr, HD, D, x1, D, o.w_q, at<AT>(a.q, (size_t)r0 * HD), HD, wf(m, o.b_q))));
+        if (t0 == 0 && M > 0)
+            NNCU_TRY((mm_nt<AT, AT>(m, M * B + nr, 2 * HD, D, hc, D, o.w_kv, at<AT>(a.kv, 0), 2 * HD, nullptr)));
+        else
+            NNCU_TRY((mm_nt<AT, AT>(m, nr, 2 * HD, D, x1, D, o.w_kv,
+                                    at<AT>(a.kv, ((size_t)M * B + r0) * 2 * HD), 2 * HD, nullptr)));
+        nncu_attn_shape s = attn_shape(m, l, t0, t1);
+        NNCU_TRY(attn_forward_t<AT>(&s, a.q, a.kv, wf(m, o.w_r), m->W + o.b_r, a.o, a.lse, m->st));
+        // output projection, residual, post-LN (nncp.c:865-920)
+        NNCU_TRY((mm_nt<AT, AT>(m, nr, D, HD, at<AT>(a.o, (size_t)r0 * HD), HD, o.w_o, tmp, D, nullptr)));
+        AT *yy = at<AT>(a.y, (size_t)r0 * D);
+        NNCU_TRY(norm_fwd<AT>(m, tmp, xin, post ? at<AT>(a.s1, (size_t)r0 * D) : nullptr, yy, o.ln_g1,
+                              o.ln_b1, a.st_1 + 2 * r0, nr, post));
+        // feed-forward (nncp.c:925-986)
+        AT *u = yy;
+        if (pre) {
+            u = at<AT>(a.u, (size_t)r0 * D);
+            NNCU_TRY(norm_fwd<AT>(m, yy, nullptr, nullptr, u, o.ln_g2, o.ln_b2, a.st_pre2 + 2 * r0, nr, true));
+        }
+        AT *hpre = at<AT>(a.hpre, (size_t)r0 * F1), *hact = at<AT>(a.hact, (size_t)r0 * F);
+        NNCU_TRY((mm_nt<AT, AT>(m, nr, F1, D, u, D, o.ff1, hpre, F1, wf(m, o.ff_bias1))));
+        act_fwd_kernel<AT><<<ceil_div((long long)nr * F, 256), 256, 0, m->st>>>(hpre, hact, nr, F, F1, p.ff_act);
+        KERNEL_CHECK();
+        NNCU_TRY((mm_nt<AT, AT>(m, nr, D, F, hact, F, o.ff2, tmp, D, wf(m, o.ff_bias2))));
+        AT *xout = (l + 1 < m->nl) ? at<AT>(m->act[l + 1].xin, (size_t)r0 * D)
+                                   : at<AT>(m->xlast, (size_t)r0 * D);
+        NNCU_TRY(norm_fwd<AT>(m, tmp, yy, post ? at<AT>(a.s2, (size_t)r0 * D) : nullptr, xout, o.ln_g2,
+                              o.ln_b2, a.st_2 + 2 * r0, nr, post));
+    }
+    AT *xf = at<AT>(m->xlast, (size_t)r0 * D);
+    if (p.ln_flags & NNCU_LN_FINAL) {
+        xf = at<AT>(m->xf, (size_t)r0 * D);
+        NNCU_TRY(norm_fwd<AT>(m, at<AT>(m->xlast, (size_t)r0 * D), nullptr, nullptr, xf, m->ln_g, m->ln_b,
+                              m->st_f + 2 * r0, nr, true));
+    }
+    float *pr = m->probs + (size_t)r0 * V;
+    NNCU_TRY((mm_nt<AT, float>(m, nr, V, D, xf, D, m->embed_out, pr, V, wf(m, m->out_bias))));
+    softmax_rows_kernel<<<nr, 256, 0, m->st>>>(pr, nr, V);
+    KERNEL_CHECK();
+    return NNCU_OK;
+}
+
+// ------------------------------------------------------------------ backward
+
+template <typename AT>
+static AT *pick(nncu_model *m, std::initializer_list<const void *> used)
+{
+    for (int i = 0; i < 4; i++) {
+        bool taken = false;
+        for (const void *u : used)
+            if (u == m->pool[i])
+                taken = true;
+        if (!taken)
+            return reinterpret_cast<AT *>(m->pool[i]);
+    }
+    return nullptr;
+}
+
+template <typename AT>
+static int backward(nncu_model *m)
+{
+    const nncu_params &p = m->p;
+    const int D = m->D, HD = m->HD, F = m->F, F1 = m->F1, B = m->B, M = m->M, V = m->V;
+    const int TB = m->TB, LB = m->LB;
+    const bool pre = p.ln_flags & NNCU_LN_PRE, post = p.ln_flags & NNCU_LN_POST;
+    AT *dz = reinterpret_cast<AT *>(m->dz);
+    AT *dh = reinterpret_cast<AT *>(m->dh), *dhp = reinterpret_cast<AT *>(m->dhp);
+    AT *dof = reinterpret_cast<AT *>(m->dof), *dq = reinterpret_cast<AT *>(m->dq);
+    AT *dkv = reinterpret_cast<AT *>(m->dkv);
+
+    // loss and d logits (nncp.c:1170-1175)
+    const float sc = 1.0f / ((float)m->T * (float)m->Bt);
+    loss_grad_kernel<AT><<<TB, 256, 0, m->st>>>(m->probs, m->tgt_dev, dz, m->logp, TB, V, sc);
+    KERNEL_CHECK();
+    sum_vec_kernel<<<1, 256, 0, m->st>>>(m->logp, TB, m->loss_dev);
+    KERNEL_CHECK();
+    const AT *xf = (p.ln_flags & NNCU_LN_FINAL) ? atc<AT>(m->xf, 0) : atc<AT>(m->xlast, 0);
+    if (m->out_bias != NONE)
+        NNCU_TRY(colsum<AT>(m, dz, V, TB, V, gf(m, m->out_bias)));
+    NNCU_TRY(mm_tn(m, V, D, TB, dz, V, xf, D, gf(m, m->embed_out)));
+    AT *dx = pick<AT>(m, {});
+    NNCU_TRY(mm_nn(m, TB, D, V, dz, V, m->embed_out, dx, D, (const AT *)nullptr));
+    if (p.ln_flags & NNCU_LN_FINAL) {
+        AT *t = pick<AT>(m, {dx});
+        NNCU_TRY(norm_bwd<AT>(m, dx, atc<AT>(m->xlast, 0), m->ln_g, m->ln_b, m->st_f, nullptr, t, TB));
+        dx = t;
+    }
+    // tied tables collect the contributions of every layer
+    if (p.tied_b_r)
+        CUDA_TRY(cudaMemsetAsync(gf(m, m->lo[0].b_r), 0, sizeof(float) * (size_t)m->H * m->L, m->st));
+    if (p.use_w_r && p.tied_w_r)
+        CUDA_TRY(cudaMemsetAsync(gf(m, m->lo[0].w_r), 0, sizeof(float) * (size_t)m->H * p.d_pos * m->dk, m->st));
+
+    for (int l = m->nl - 1; l >= 0; l--) {
+        const LayerOff &o = m->lo[l];
+        LayerAct &a = m->act[l];
+        const AT *hc = reinterpret_cast<const AT *>(hcat_layer(m, m->cur, l));
+        const AT *x1 = hc + (size_t)M * B * D;
+        // ---- feed-forward block
+        AT *ds2 = dx;
+        if (post) {
+            ds2 = pick<AT>(m, {dx});
+            NNCU_TRY(norm_bwd<AT>(m, dx, atc<AT>(a.s2, 0), o.ln_g2, o.ln_b2, a.st_2, nullptr, ds2, TB));
+        }
+        if (o.ff_bias2 != NONE)
+            NNCU_TRY(colsum<AT>(m, ds2, D, TB, D, gf(m, o.ff_bias2)));
+        NNCU_TRY(mm_tn(m, D, F, TB, ds2, D, atc<AT>(a.hact, 0), F, gf(m, o.ff2)));
+        NNCU_TRY(mm_nn(m, TB, F, D, ds2, D, o.ff2, dh, F, (const AT *)nullptr));
+        act_bwd_kernel<AT><<<ceil_div((long long)TB * F, 256), 256, 0, m->st>>>(
+            atc<AT>(a.hpre, 0), dh, dhp, TB, F, F1, p.ff_act);
+        KERNEL_CHECK();
+        if (o.ff_bias1 != NONE)
+            NNCU_TRY(colsum<AT>(m, dhp, F1, TB, F1, gf(m, o.ff_bias1)));
+        const AT *u = pre ? atc<AT>(a.u, 0) : atc<AT>(a.y, 0);
+        NNCU_TRY(mm_tn(m, F1, D, TB, dhp, F1, u, D, gf(m, o.ff1)));
+        AT *dy = pick<AT>(m, {ds2});
+        if (pre) {
+            AT *du = pick<AT>(m, {ds2, dy});
+            NNCU_TRY(mm_nn(m, TB, D, F1, dhp, F1, o.ff1, du, D, (const AT *)nullptr));
+            NNCU_TRY(norm_bwd<AT>(m, du, atc<AT>(a.y, 0), o.ln_g2, o.ln_b2, a.st_pre2, ds2, dy, TB));
+        } else {
+            NNCU_TRY(mm_nn(m, TB, D, F1, dhp, F1, o.ff1, dy, D, (const AT *)ds2));
+        }
+        // ---- attention block
+        AT *ds1 = dy;
+        if (post) {
+            ds1 = pick<AT>(m, {dy});
+            NNCU_TRY(norm_bwd<AT>(m, dy, atc<AT>(a.s1, 0), o.ln_g1, o.ln_b1, a.st_1, nullptr, ds1, TB));
+        }
+        NNCU_TRY(mm_tn(m, D, HD, TB, ds1, D, atc<AT>(a.o, 0), HD, gf(m, o.w_o)));
+        NNCU_TRY(mm_nn(m, TB, HD, D, ds1, D, o.w_o, dof, HD, (const AT *)nullptr));
+        nncu_attn_shape s = attn_shape(m, l, 0, m->T);
+        NNCU_TRY(attn_backward_t<AT>(&s, a.q, a.kv, wf(m, o.w_r), m->W + o.b_r, a.o, a.lse, dof, dq, dkv,
+                                     m->dwr_part, m->dbr_part, m->st));
+        {
+            size_t nb = (size_t)m->H * m->L;
+            reduce_streams_kernel<<<ceil_div(nb, 256), 256, 0, m->st>>>(m->dbr_part, B, nb, gf(m, o.b_r),
+                                                                       p.tied_b_r ? 1 : 0);
+            KERNEL_CHECK();
+            if (o.w_r != NONE) {
+                size_t nw = (size_t)m->H * p.d_pos * m->dk;
+                reduce_streams_kernel<<<ceil_div(nw, 256), 256, 0, m->st>>>(m->dwr_part, B, nw, gf(m, o.w_r),
+                                                                           p.tied_w_r ? 1 : 0);
+                KERNEL_CHECK();
+            }
+        }
+        NNCU_TRY(mm_tn(m, HD, D, TB, dq, HD, x1, D, gf(m, o.w_q)));
+        if (o.b_q != NONE)
+            NNCU_TRY(colsum<AT>(m, dq, HD, TB, HD, gf(m, o.b_q)));
+        NNCU_TRY(mm_tn(m, 2 * HD, D, LB, dkv, 2 * HD, hc, D, gf(m, o.w_kv)));
+        // d(attention input) = dq W_q + dkv[segment rows] W_kv; the memory rows get no gradient
+        const AT *dkv_seg = dkv + (size_t)M * B * 2 * HD;
+        AT *dxn = pick<AT>(m, {ds1});
+        if (pre) {
+            AT *dx1 = pick<AT>(m, {ds1, dxn});
+            NNCU_TRY(mm_nn(m, TB, D, HD, dq, HD, o.w_q, dx1, D, (const AT *)nullptr));
+            NNCU_TRY(mm_nn(m, TB, D, 2 * HD, dkv_seg, 2 * HD, o.w_kv, dx1, D, (const AT *)dx1));
+            NNCU_TRY(norm_bwd<AT>(m, dx1, atc<AT>(a.xin, 0), o.ln_g1, o.ln_b1, a.st_pre1, ds1, dxn, TB));
+        } else {
+            NNCU_TRY(mm_nn(m, TB, D, HD, dq, HD, o.w_q, dxn, D, (const AT *)ds1));
+            NNCU_TRY(mm_nn(m, TB, D, 2 * HD, dkv_seg, 2 * HD, o.w_kv, dxn, D, (const AT *)dxn));
+        }
+        dx = dxn;
+    }
+    const float emul = sqrtf((float)D) * p.embed_mult;
+    embed_grad_kernel<AT><<<V, 128, sizeof(int32_t) * TB, m->st>>>(m->ids_dev, dx, gf(m, m->embed), TB, D, emul, V);
+    KERNEL_CHECK();
+    return NNCU_OK;
+}
+
+// ------------------------------------------------------------------ shadows
+
+__global__ void __launch_bounds__(256)
+transpose_jobs_kernel(const bf16 *__restrict__ src, bf16 *__restrict__ dst,
+                      const TransposeJob *__restrict__ jobs, int n_jobs)
+{
+    __shared__ bf16 tile[32][33];
+    int j = 0;
+    while (j + 1 < n_jobs && (int)blockIdx.x >= jobs[j + 1].tile0)
+        j++;
+    const TransposeJob jb = jobs[j];
+    int t = blockIdx.x - jb.tile0;
+    int c0 = (t % jb.tiles_x) * 32, r0 = (t / jb.tiles_x) * 32;
+    int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+    const bf16 *s = src + jb.src_off;
+    bf16 *d = dst + jb.dst_off;
+    for (int k = ty; k < 32; k += 8) {
+        int r = r0 + k, c = c0 + tx;
+        if (r < jb.rows && c < jb.cols)
+            tile[k][tx] = s[(size_t)r * jb.cols + c];
+    }
+    __syncthreads();
+    for (int k = ty; k < 32; k += 8) {
+        int c = c0 + k, r = r0 + tx;
+        if (r < jb.rows && c < jb.cols)
+            d[(size_t)c * jb.rows + r] = tile[tx][k];
+    }
+}
+
+static int refresh_transposed(nncu_model *m)
+{
+    if (m->bf && m->n_jobs > 0) {
+        transpose_jobs_kernel<<<m->n_job_tiles, 256, 0, m->st>>>(m->Wb, m->WbT, m->jobs_dev, m->n_jobs);
+        KERNEL_CHECK();
+    }
+    return NNCU_OK;
+}
+
+static int refresh_shadows(nncu_model *m)
+{
+    if (!m->bf)
+        return NNCU_OK;
+    f32_to_bf16_kernel<<<ceil_div(m->n_floats, 256), 256, 0, m->st>>>(m->W, m->Wb, m->n_floats);
+    KERNEL_CHECK();
+    return refresh_transposed(m);
+}
+
+// ------------------------------------------------------------------ parameter table
+
+static uint64_t splitmix64(uint64_t x)
+{
+    x += 0x9E3779B97F4A7C15ull;
+    x = (x ^ (x >> 30)) * 0xBF58476D1CE4E5B9ull;
+    x = (x ^ (x >> 27)) * 0x94D049BB133111EBull;
+    return x ^ (x >> 31);
+}
+static uint64_t name_hash(const char *s)
+{
+    uint64_t h = 0xcbf29ce484222325ull;
+    while (*s) {
+        h ^= (uint8_t)*s++;
+        h *= 0x100000001b3ull;
+    }
+    return h;
+}
+static inline float u01(uint64_t key, uint64_t idx, uint32_t k)
+{
+    uint64_t r = splitmix64(key ^ splitmix64(idx * 16 + k));
+    return (float)(r >> 40) * (1.0f / 16777216.0f);
+}
+// Counter-based initial values: element i of parameter `name` depends only on
+// (seed, name, i).  Integer hashing plus exactly-rounded float adds/multiplies,
+// so encoder and decoder hosts produce the same bits (trf_init draws from
+// nc_tensor_set_rnd_unif in creation order, nncp.c:263-266, whose generator is
+// not part of the reference tree).
+static void init_values(float *dst, size_t n, const char *name, uint32_t seed, int kind, float scale)
+{
+    uint64_t key = splitmix64(name_hash(name) ^ ((uint64_t)seed << 32));
+    for (size_t i = 0; i < n; i++) {
+        if (kind == NNCU_INIT_NORMAL) {
+            float s = 0.0f;
+            for (uint32_t k = 0; k < 12; k++)
+                s += u01(key, i, k);
+            dst[i] = (s - 6.0f) * scale;
+        } else {
+            dst[i] = (2.0f * u01(key, i, 0) - 1.0f) * scale;
+        }
+    }
+}
+
+static size_t add_param(nncu_model *m, const char *base, int idx, size_t numel, int rows = 0, int cols = 0)
+{
+    ParamInfo pi;
+    memset(&pi, 0, sizeof(pi));
+    if (idx >= 0)
+        snprintf(pi.name, sizeof(pi.name), "%s_%d", base, idx);
+    else
+        snprintf(pi.name, sizeof(pi.name), "%s", base);
+    pi.numel = numel;
+    pi.off = m->n_floats;
+    pi.rows = rows;
+    pi.cols = cols;
+    m->n_floats += (numel + 127) & ~(size_t)127;
+    m->pinfo.push_back(pi);
+    return pi.off;
+}
+
+static int validate(const nncu_params *p)
+{
+    if (!p)
+        return nncu_fail(NNCU_ERR_INVALID, "null parameters");
+    if (p->n_layer < 1 || p->n_layer > NNCU_N_LAYER_MAX || p->d_model < 1 || p->n_head < 1 ||
+        p->d_key < 1 || p->d_inner < 1 || p->seg_len < 1 || p->mem_len < 0 || p->n_streams < 1 ||
+        p->n_symbols < 2)
+        return nncu_fail(NNCU_ERR_INVALID, "a size is out of range");
+    if (p->d_value != p->d_key)
+        return nncu_fail(NNCU_ERR_INVALID, "d_value must equal d_key");
+    if (p->d_pos < 1 || p->d_pos > p->mem_len + p->seg_len)
+        return nncu_fail(NNCU_ERR_INVALID, "d_pos must be in [1, mem_len + seg_len]");
+    if (p->ln_flags & NNCU_LN_COEF)
+        return nncu_fail(NNCU_ERR_INVALID, "LN_COEF is not supported");
+    if ((p->ln_flags & NNCU_LN_PRE) && (p->ln_flags & NNCU_LN_POST))
+        return nncu_fail(NNCU_ERR_INVALID, "LN_PRE and LN_POST together are not supported");
+    if (p->ff_act > NNCU_FF_GEGLU)
+        return nncu_fail(NNCU_ERR_INVALID, "ff_act %d is not supported", p->ff_act);
+    if (p->use_bf16 && (p->d_key & 1))
+        return nncu_fail(NNCU_ERR_INVALID, "bf16 models need an even d_key");
+    if (p->gemm_backend == NNCU_GEMM_TCGEN05 && !p->use_bf16)
+        return nncu_fail(NNCU_ERR_INVALID, "the tcgen05 backend needs a bf16 model");
+    for (int l = 0; l < p->n_layer; l++)
+        if (p->attn_len[l] < 0 || p->attn_len[l] > p->mem_len + p->seg_len)
+            return nncu_fail(NNCU_ERR_INVALID, "attn_len[%d] out of range", l);
+    return NNCU_OK;
+}
+
+// ------------------------------------------------------------------ C ABI
+
+extern "C" {
+
+void nncu_default_params(nncu_params *p)
+{
+    memset(p, 0, sizeof(*p));
+    p->n_layer = 4; p->d_model = 256; p->n_head = 8; p->d_key = 32; p->d_value = 32;
+    p->d_inner = 512; p->d_pos = 32; p->mem_len = 32; p->seg_len = 32; p->n_streams = 16;
+    p->n_symbols = 256; p->use_bias = 1; p->use_w_r = 1; p->tied_w_r = 1; p->tied_b_r = 1;
+    p->ln_flags = NNCU_LN_POST; p->ff_act = NNCU_FF_GELU; p->embed_mult = 1.0f;
+    p->init_range = 1.0f; p->init_kind = NNCU_INIT_UNIFORM; p->seed = 123;
+    p->lr = 3e-4f; p->beta2 = 0.99f; p->eps = 1e-8f; p->device = -1;
+}
+
+int nncu_abi_version(void) { return NNCU_ABI_VERSION; }
+const char *nncu_last_error(void) { return g_nncu_err; }
+
+int nncu_destroy(nncu_model *m)
+{
+    if (!m)
+        return NNCU_OK;
+    cudaSetDevice(m->device);
+    cudaStreamSynchronize(m->st);
+    if (m->arena) cudaFree(m->arena);
+    if (m->ids_pin) cudaFreeHost(m->ids_pin);
+    if (m->tgt_pin) cudaFreeHost(m->tgt_pin);
+    if (m->loss_pin) cudaFreeHost(m->loss_pin);
+    delete m;
+    return NNCU_OK;
+}
+
+int nncu_create(const nncu_params *p, nncu_model **out)
+{
+    if (!out)
+        return nncu_fail(NNCU_ERR_INVALID, "null output pointer");
+    *out = nullptr;
+    NNCU_TRY(validate(p));
+    int ndev = 0;
+    if (cudaGetDeviceCount(&ndev) != cudaSuccess || ndev == 0)
+        return nncu_fail(NNCU_ERR_CUDA, "no CUDA device: this library has no CPU path");
+    int dev = p->device;
+    if (dev < 0)
+        CUDA_TRY(cudaGetDevice(&dev));
+    CUDA_TRY(cudaSetDevice(dev));
+    cudaDeviceProp prop;
+    CUDA_TRY(cudaGetDeviceProperties(&prop, dev));
+    if (prop.major != 10)
+        return nncu_fail(NNCU_ERR_CUDA, "device %d is sm_%d%d; this library is built for sm_100a only",
+                         dev, prop.major, prop.minor);
+
+    nncu_model *m = new nncu_model();
+    m->p = *p;
+    m->device = dev;
+    m->st = 0;
+    m->D = p->d_model; m->H = p->n_head; m->dk = p->d_key; m->HD = m->H * m->dk; m->F = p->d_inner;
+    m->F1 = (p->ff_act == NNCU_FF_GEGLU) ? 2 * m->F : m->F;
+    m->T = p->seg_len; m->B = p->n_streams; m->M = p->mem_len; m->L = m->M + m->T; m->V = p->n_symbols;
+    m->TB = m->T * m->B; m->LB = m->L * m->B; m->nl = p->n_layer;
+    m->Bt = p->n_streams_total > 0 ? p->n_streams_total : m->B;
+    m->bf = p->use_bf16 != 0;
+    m->use_tc = m->bf && p->gemm_backend != NNCU_GEMM_SIMT;
+    m->esz = m->bf ? 2 : 4;
+    m->lr = p->lr;
+    m->step = 0;
+    m->steps_done = 0;
+    m->have_forward = false;
+    m->cur = 0;
+    m->n_floats = 0;
+    const int D = m->D, HD = m->HD, F = m->F, F1 = m->F1, V = m->V, TB = m->TB, LB = m->LB;
+
+    const bool has_ln = (p->ln_flags & (NNCU_LN_POST | NNCU_LN_PRE)) != 0;
+    m->lo.resize(m->nl);
+    for (int l = 0; l < m->nl; l++) {
+        LayerOff &o = m->lo[l];
+        o.w_q = add_param(m, "w_q", l, (size_t)HD * D, HD, D);
+        o.w_kv = add_param(m, "w_kv", l, (size_t)2 * HD * D, 2 * HD, D);
+        o.b_q = p->query_bias ? add_param(m, "b_q", l, HD) : NONE;
+        o.w_o = add_param(m, "w_o", l, (size_t)D * HD, D, HD);
+        o.ff1 = add_param(m, "ff1", l, (size_t)F1 * D, F1, D);
+        o.ff_bias1 = p->use_bias ? add_param(m, "ff_bias1", l, F1) : NONE;
+        o.ff2 = add_param(m, "ff2", l, (size_t)D * F, D, F);
+        o.ff_bias2 = p->use_bias ? add_param(m, "ff_bias2", l, D) : NONE;
+        if (p->use_w_r)
+            o.w_r = (l == 0 || !p->tied_w_r) ? add_param(m, "w_r", l, (size_t)m->H * p->d_pos * m->dk)
+                                             : m->lo[0].w_r;
+        else
+            o.w_r = NONE;
+        o.b_r = (l == 0 || !p->tied_b_r) ? add_param(m, "b_r", l, (size_t)m->H * m->L) : m->lo[0].b_r;
+        if (has_ln) {
+            o.ln_g1 = add_param(m, "ln_g", 2 * l, D);
+            o.ln_b1 = add_param(m, "ln_b", 2 * l, D);
+            o.ln_g2 = add_param(m, "ln_g", 2 * l + 1, D);
+            o.ln_b2 = add_param(m, "ln_b", 2 * l + 1, D);
+        } else {
+            o.ln_g1 = o.ln_b1 = o.ln_g2 = o.ln_b2 = NONE;
+        }
+    }
+    if (p->ln_flags & NNCU_LN_FINAL) {
+        m->ln_g = add_param(m, "ln_g", 2 * m->nl, D);
+        m->ln_b = add_param(m, "ln_b", 2 * m->nl, D);
+    } else {
+        m->ln_g = m->ln_b = NONE;
+    }
+    m->embed = add_param(m, "embed", -1, (size_t)V * D);
+    m->embed_out = add_param(m, "embed_out", -1, (size_t)V * D, V, D);
+    m->out_bias = p->use_bias ? add_param(m, "out_bias", -1, V) : NONE;
+
+    // ---- arena layout
+    size_t total = 0;
+    auto take = [&](size_t bytes) {
+        size_t o = total;
+        total += (bytes + 255) & ~(size_t)255;
+        return o;
+    };
+    const size_t e = m->esz;
+    const bool pre = p->ln_flags & NNCU_LN_PRE, post = p->ln_flags & NNCU_LN_POST;
+    size_t oW = take(m->n_floats * 4), oG = take(m->n_floats * 4), oV = take(m->n_floats * 4);
+    size_t oWb = m->bf ? take(m->n_floats * 2) : 0, oWbT = m->bf ? take(m->n_floats * 2) : 0;
+    size_t oH0 = take((size_t)m->nl * LB * D * e), oH1 = take((size_t)m->nl * LB * D * e);
+    struct LOff { size_t xin, q, kv, o, s1, y, u, hpre, hact, s2, lse, sp1, s_1, sp2, s_2; };
+    std::vector<LOff> lofs(m->nl);
+    for (int l = 0; l < m->nl; l++) {
+        LOff &x = lofs[l];
+        x.xin = pre ? take((size_t)TB * D * e) : NONE;
+        x.q = take((size_t)TB * HD * e);
+        x.kv = take((size_t)LB * 2 * HD * e);
+        x.o = take((size_t)TB * HD * e);
+        x.s1 = post ? take((size_t)TB * D * e) : NONE;
+        x.y = take((size_t)TB * D * e);
+        x.u = pre ? take((size_t)TB * D * e) : NONE;
+        x.hpre = take((size_t)TB * F1 * e);
+        x.hact = take((size_t)TB * F * e);
+        x.s2 = post ? take((size_t)TB * D * e) : NONE;
+        x.lse = take((size_t)m->B * m->H * m->T * 4);
+        x.sp1 = take((size_t)TB * 2 * 4);
+        x.s_1 = take((size_t)TB * 2 * 4);
+        x.sp2 = take((size_t)TB * 2 * 4);
+        x.s_2 = take((size_t)TB * 2 * 4);
+    }
+    size_t oXlast = take((size_t)TB * D * e), oXf = take((size_t)TB * D * e), oStf = take((size_t)TB * 8);
+    size_t oProbs = take((size_t)TB * V * 4);
+    size_t oPool[4];
+    for (int i = 0; i < 4; i++)
+        oPool[i] = take((size_t)TB * D * e);
+    size_t oDz = take((size_t)TB * V * e), oDh = take((size_t)TB * F * e), oDhp = take((size_t)TB * F1 * e);
+    size_t oDof = take((size_t)TB * HD * e), oDq = take((size_t)TB * HD * e);
+    size_t oDkv = take((size_t)LB * 2 * HD * e);
+    size_t max_n = (size_t)std::max(std::max(V, F1), std::max(2 * HD, D));
+    size_t max_k = (size_t)std::max(std::max(F, D), HD);
+    size_t oTA = m->use_tc ? take(max_n * LB * 2) : 0, oTB = m->use_tc ? take(max_k * LB * 2) : 0;
+    size_t oWr = take((size_t)m->B * m->H * p->d_pos * m->dk * 4), oBr = take((size_t)m->B * m->H * m->L * 4);
+    size_t part_floats = std::max((size_t)ceil_div(LB, 64) * max_n, (size_t)ceil_div(TB, 32) * 2 * D);
+    size_t oPart = take(part_floats * 4);
+    size_t oLogp = take((size_t)TB * 4), oLoss = take(256);
+    size_t oIds = take((size_t)TB * 4), oTgt = take((size_t)TB * 4), oErr = take(256), oHash = take(256);
+    // transposed-shadow jobs
+    std::vector<TransposeJob> jobs;
+    int tiles = 0;
+    if (m->bf)
+        for (const ParamInfo &pi : m->pinfo)
+            if (pi.rows > 0) {
+                TransposeJob j;
+                j.src_off = pi.off; j.dst_off = pi.off; j.rows = pi.rows; j.cols = pi.cols;
+                j.tile0 = tiles; j.tiles_x = ceil_div(pi.cols, 32);
+                tiles += j.tiles_x * ceil_div(pi.rows, 32);
+                jobs.push_back(j);
+            }
+    size_t oJobs = take(sizeof(TransposeJob) * (jobs.size() + 1));
+    m->coder_bytes = (size_t)TB * V * 2;
+    size_t oCoder = take(m->coder_bytes);
+
+    m->arena_bytes = total;
+    cudaError_t ce = cudaMalloc(&m->arena, total);
+    if (ce != cudaSuccess) {
+        delete m;
+        return nncu_fail(NNCU_ERR_NOMEM, "cudaMalloc of %zu bytes failed: %s", total, cudaGetErrorString(ce));
+    }
+    auto fail_cleanup = [&](int rc) {
+        nncu_destroy(m);
+        return rc;
+    };
+    if (cudaMemset(m->arena, 0, total) != cudaSuccess)
+        return fail_cleanup(nncu_fail(NNCU_ERR_CUDA, "cudaMemset failed"));
+    char *A = m->arena;
+    m->W = (float *)(A + oW); m->G = (float *)(A + oG); m->Vm = (float *)(A + oV);
+    m->Wb = m->bf ? (bf16 *)(A + oWb) : nullptr;
+    m->WbT = m->bf ? (bf16 *)(A + oWbT) : nullptr;
+    m->hcat[0] = A + oH0; m->hcat[1] = A + oH1;
+    m->act.resize(m->nl);
+    m->xlast = A + oXlast; m->xf = A + oXf; m->st_f = (float *)(A + oStf); m->probs = (float *)(A + oProbs);
+    for (int i = 0; i < 4; i++)
+        m->pool[i] = A + oPool[i];
+    m->dz = A + oDz; m->dh = A + oDh; m->dhp = A + oDhp; m->dof = A + oDof; m->dq = A + oDq; m->dkv = A + oDkv;
+    m->tA = m->use_tc ? A + oTA : nullptr; m->tB = m->use_tc ? A + oTB : nullptr;
+    m->dwr_part = (float *)(A + oWr); m->dbr_part = (float *)(A + oBr); m->part = (float *)(A + oPart);
+    m->logp = (float *)(A + oLogp); m->loss_dev = (float *)(A + oLoss);
+    m->ids_dev = (int32_t *)(A + oIds); m->tgt_dev = (int32_t *)(A + oTgt);
+    m->err_flag = (int *)(A + oErr); m->hash_dev = (unsigned long long *)(A + oHash);
+    m->jobs_dev = (TransposeJob *)(A + oJobs);
+    m->n_jobs = (int)jobs.size(); m->n_job_tiles = tiles;
+    m->coder_dev = (uint16_t *)(A + oCoder);
+    for (int l = 0; l < m->nl; l++) {
+        LOff &x = lofs[l];
+        LayerAct &a = m->act[l];
+        a.q = A + x.q; a.kv = A + x.kv; a.o = A + x.o; a.y = A + x.y; a.hpre = A + x.hpre; a.hact = A + x.hact;
+        a.s1 = post ? A + x.s1 : nullptr; a.s2 = post ? A + x.s2 : nullptr; a.u = pre ? A + x.u : nullptr;
+        a.lse = (float *)(A + x.lse); a.st_pre1 = (float *)(A + x.sp1); a.st_1 = (float *)(A + x.s_1);
+        a.st_pre2 = (float *)(A + x.sp2); a.st_2 = (float *)(A + x.s_2);
+        a.xin = pre ? A + x.xin : nullptr; // without pre-LN the residual input IS the hcat segment part
+    }
+    if (cudaMallocHost(&m->ids_pin, sizeof(int32_t) * TB) != cudaSuccess ||
+        cudaMallocHost(&m->tgt_pin, sizeof(int32_t) * TB) != cudaSuccess ||
+        cudaMallocHost(&m->loss_pin, 64) != cudaSuccess)
+        return fail_cleanup(nncu_fail(NNCU_ERR_NOMEM, "pinned host allocation failed"));
+    if (!jobs.empty() &&
+        cudaMemcpy(m->jobs_dev, jobs.data(), sizeof(TransposeJob) * jobs.size(), cudaMemcpyHostToDevice) != cudaSuccess)
+        return fail_cleanup(nncu_fail(NNCU_ERR_CUDA, "job table upload failed"));
+    if ((size_t)8 * 2 * D * 4 > 48 * 1024) {
+        cudaFuncSetAttribute(norm_bwd_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 8 * 2 * D * 4);
+        cudaFuncSetAttribute(norm_bwd_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 8 * 2 * D * 4);
+    }
+    if ((size_t)2 * V * 4 > 48 * 1024) {
+        cudaFuncSetAttribute(coder_paths_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 2 * V * 4);
+        cudaFuncSetAttribute(coder_trees_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 2 * V * 4);
+    }
+    if (sizeof(int32_t) * TB > 48 * 1024) {
+        cudaFuncSetAttribute(embed_grad_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(int32_t) * TB);
+        cudaFuncSetAttribute(embed_grad_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(int32_t) * TB);
+    }
+
+    // ---- initial values (trf_init, nncp.c:341-497), computed on the host
+    {
+        std::vector<float> host(m->n_floats, 0.0f);
+        float a0 = p->init_kind == NNCU_INIT_NORMAL ? p->init_range : p->init_range / sqrtf((float)D);
+        for (const ParamInfo &pi : m->pinfo) {
+            float *dst = host.data() + pi.off;
+            if (!strncmp(pi.name, "ln_g", 4)) {
+                for (size_t k = 0; k < pi.numel; k++)
+                    dst[k] = 1.0f;
+            } else if (!strncmp(pi.name, "w_", 2) || !strncmp(pi.name, "ff1", 3) || !strncmp(pi.name, "embed", 5)) {
+                init_values(dst, pi.numel, pi.name, p->seed, p->init_kind, a0);
+            } else if (!strncmp(pi.name, "ff2", 3)) {
+                init_values(dst, pi.numel, pi.name, p->seed, p->init_kind, a0 * sqrtf((float)D / (float)F));
+            }
+        }
+        if (cudaMemcpy(m->W, host.data(), m->n_floats * 4, cudaMemcpyHostToDevice) != cudaSuccess)
+            return fail_cleanup(nncu_fail(NNCU_ERR_CUDA, "weight upload failed"));
+    }
+    int rc = refresh_shadows(m);
+    if (rc == NNCU_OK && cudaStreamSynchronize(m->st) != cudaSuccess)
+        rc = nncu_fail(NNCU_ERR_CUDA, "initialisation kernels failed: %s", cudaGetErrorString(cudaGetLastError()));
+    if (rc != NNCU_OK)
+        return fail_cleanup(rc);
+    // without pre-LN, xin aliases the hcat segment rows of the CURRENT twin; resolved per call
+    *out = m;
+    return NNCU_OK;
+}
+
+int nncu_set_stream(nncu_model *m, void *cuda_stream)
+{
+    if (!m)
+        return nncu_fail(NNCU_ERR_INVALID, "null model");
+    CUDA_TRY(cudaStreamSynchronize(m->st));
+    m->st = (cudaStream_t)cuda_stream;
+    return NNCU_OK;
+}
+
+int nncu_reset(nncu_model *m)
+{
+    if (!m)
+        return nncu_fail(NNCU_ERR_INVALID, "null model");
+    CUDA_TRY(cudaSetDevice(m->device));
+    if (m->M > 0)
+        CUDA_TRY(cudaMemset2DAsync(m->hcat[m->cur], (size_t)m->LB * m->D * m->esz, 0,
+                                   (size_t)m->M * m->B * m->D * m->esz, m->nl, m->st));
+    m->steps_done = 0;
+    m->have_forward = false;
+    return NNCU_OK;
+}
+
+int nncu_set_lr(nncu_model *m, float lr)
+{
+    if (!m)
+        return nncu_fail(NNCU_ERR_INVALID, "null model");
+    m->lr = lr;
+    return NNCU_OK;
+}
+
+static void bind_xin(nncu_model *m)
+{
+    if (m->p.ln_flags & NNCU_LN_PRE)
+        return;
+    for (int l = 0; l < m->nl; l++)
+        m->act[l].xin = hcat_layer(m, m->cur, l) + (size_t)m->M * m->B * m->D * m->esz;
+}
+
+static int eval_common(nncu_model *m, int output_index)
+{
+    if (output_index >= m->T)
+        return nncu_fail(NNCU_ERR_INVALID, "output_index %d >= seg_len %d", output_index, m->T);
+    if (output_index > 0 && output_index != m->steps_done)
+        return nncu_fail(NNCU_ERR_STATE, "step %d issued after %d steps", output_index, m->steps_done);
+    bind_xin(m);
+    int t0 = output_index < 0 ? 0 : output_index, t1 = output_index < 0 ? m->T : output_index + 1;
+    int rc = m->bf ? forward_range<bf16>(m, t0, t1) : forward_range<float>(m, t0, t1);
+    if (rc != NNCU_OK)
+        return rc;
+    m->steps_done = t1;
+    m->have_forward = (t1 == m->T);
+    return NNCU_OK;
+}
+
+int nncu_eval(nncu_model *m, int output_index, const int32_t *input_host)
+{
+    if (!m || !input_host)
+        return nncu_fail(NNCU_ERR_INVALID, "null argument");
+    CUDA_TRY(cudaSetDevice(m->device));
+    if (output_index >= m->T)
+        return nncu_fail(NNCU_ERR_INVALID, "output_index %d >= seg_len %d", output_index, m->T);
+    int t0 = output_index < 0 ? 0 : output_index, n = output_index < 0 ? m->TB : m->B;
+    // the staging buffer may still feed an earlier copy
+    CUDA_TRY(cudaStreamSynchronize(m->st));
+    memcpy(m->ids_pin + (size_t)t0 * m->B, input_host + (size_t)t0 * m->B, sizeof(int32_t) * n);
+    CUDA_TRY(cudaMemcpyAsync(m->ids_dev + (size_t)t0 * m->B, m->ids_pin + (size_t)t0 * m->B,
+                             sizeof(int32_t) * n, cudaMemcpyHostToDevice, m->st));
+    return eval_common(m, output_index);
+}
+
+int nncu_eval_dev(nncu_model *m, int output_index, const int32_t *input_dev)
+{
+    if (!m || !input_dev)
+        return nncu_fail(NNCU_ERR_INVALID, "null argument");
+    CUDA_TRY(cudaSetDevice(m->device));
+    if (output_index >= m->T)
+        return nncu_fail(NNCU_ERR_INVALID, "output_index %d >= seg_len %d", output_index, m->T);
+    int t0 = output_index < 0 ? 0 : output_index, n = output_index < 0 ? m->TB : m->B;
+    CUDA_TRY(cudaMemcpyAsync(m->ids_dev + (size_t)t0 * m->B, input_dev + (size_t)t0 * m->B,
+                             sizeof(int32_t) * n, cudaMemcpyDeviceToDevice, m->st));
+    return eval_common(m, output_index);
+}
+
+int nncu_eval_end(nncu_model *m)
+{
+    if (!m)
+        return nncu_fail(NNCU_ERR_INVALID, "null model");
+    m->steps_done = 0;
+    m->have_forward = false;
+    return NNCU_OK;
+}
+
+int nncu_read_probs(nncu_model *m, int t0, int nt, float *probs_host)
+{
+    if (!m || !probs_host || t0 < 0 || nt < 0 || t0 + nt > m->T)
+        return nncu_fail(NNCU_ERR_INVALID, "bad probability range");
+    CUDA_TRY(cudaSetDevice(m->device));
+    CUDA_TRY(cudaMemcpyAsync(probs_host, m->probs + (size_t)t0 * m->B * m->V,
+                             sizeof(float) * (size_t)nt * m->B * m->V, cudaMemcpyDeviceToHost, m->st));
+    CUDA_TRY(cudaStreamSynchronize(m->st));
+    return NNCU_OK;
+}
+
+int nncu_probs_dev(nncu_model *m, float **probs_dev)
+{
+    if (!m || !probs_dev)
+        return nncu_fail(NNCU_ERR_INVALID, "null argument");
+    *probs_dev = m->probs;
+    return NNCU_OK;
+}
+
+static int gradient_common(nncu_model *m)
+{
+    if (!m->have_forward)
+        return nncu_fail(NNCU_ERR_STATE, "eval_gradient needs a complete forward pass first");
+    bind_xin(m);
+    return m->bf ? backward<bf16>(m) : backward<float>(m);
+}
+
+int nncu_read_loss(nncu_model *m, float *loss_out)
+{
+    if (!m || !loss_out)
+        return nncu_fail(NNCU_ERR_INVALID, "null argument");
+    CUDA_TRY(cudaSetDevice(m->device));
+    CUDA_TRY(cudaMemcpyAsync(m->loss_pin, m->loss_dev, sizeof(float), cudaMemcpyDeviceToHost, m->st));
+    CUDA_TRY(cudaStreamSynchronize(m->st));
+    *loss_out = *m->loss_pin;
+    return NNCU_OK;
+}
+
+int nncu_eval_gradient(nncu_model *m, const int32_t *expected_host, float *loss_out)
+{
+    if (!m || !expected_host)
+        return nncu_fail(NNCU_ERR_INVALID, "null argument");
+    CUDA_TRY(cudaSetDevice(m->device));
+    CUDA_TRY(cudaStreamSynchronize(m->st));
+    memcpy(m->tgt_pin, expected_host, sizeof(int32_t) * m->TB);
+    CUDA_TRY(cudaMemcpyAsync(m->tgt_dev, m->tgt_pin, sizeof(int32_t) * m->TB, cudaMemcpyHostToDevice, m->st));
+    NNCU_TRY(gradient_common(m));
+    if (loss_out)
+        return nncu_read_loss(m, loss_out);
+    return NNCU_OK;
+}
+
+int nncu_eval_gradient_dev(nncu_model *m, const int32_t *expected_dev)
+{
+    if (!m || !expected_dev)
+        return nncu_fail(NNCU_ERR_INVALID, "null argument");
+    CUDA_TRY(cudaSetDevice(m->device));
+    CUDA_TRY(cudaMemcpyAsync(m->tgt_dev, expected_dev, sizeof(int32_t) * m->TB, cudaMemcpyDeviceToDevice, m->st));
+    return gradient_common(m);
+}
+
+int nncu_optimizer_step(nncu_model *m)
+{
+    if (!m)
+        return nncu_fail(NNCU_ERR_INVALID, "null model");
+    CUDA_TRY(cudaSetDevice(m->device));
+    m->step++;
+    float corr = 1.0f;
+    if (m->p.bias_correction)
+        corr = 1.0f / (1.0f - powf(m->p.beta2, (float)m->step));
+    size_t n4 = m->n_floats / 4;
+    rmsprop_kernel<<<ceil_div(n4, 256), 256, 0, m->st>>>(m->W, m->G, m->Vm, m->Wb, n4, m->lr, m->p.beta2,
+                                                         m->p.eps, m->p.gradient_clip, corr);
+    KERNEL_CHECK();
+    return refresh_transposed(m);
+}
+
+int nncu_memory_shift(nncu_model *m)
+{
+    if (!m)
+        return nncu_fail(NNCU_ERR_INVALID, "null model");
+    CUDA_TRY(cudaSetDevice(m->device));
+    if (m->M > 0) {
+        // memory <- last M time steps of [memory ; segment], every layer in one 2-D copy
+        size_t pitch = (size_t)m->LB * m->D * m->esz;
+        CUDA_TRY(cudaMemcpy2DAsync(m->hcat[m->cur ^ 1], pitch,
+                                   m->hcat[m->cur] + (size_t)m->T * m->B * m->D * m->esz, pitch,
+                                   (size_t)m->M * m->B * m->D * m->esz, m->nl, cudaMemcpyDeviceToDevice, m->st));
+        m->cur ^= 1;
+    }
+    m->steps_done = 0;
+    m->have_forward = false;
+    return NNCU_OK;
+}
+
+int nncu_update(nncu_model *m)
+{
+    NNCU_TRY(nncu_optimizer_step(m));
+    return nncu_memory_shift(m);
+}
+
+int nncu_synchronize(nncu_model *m)
+{
+    if (!m)
+        return nncu_fail(NNCU_ERR_INVALID, "null model");
+    CUDA_TRY(cudaSetDevice(m->device));
+    return check_err_flag(m);
+}
+
+int nncu_param_count(const nncu_model *m) { return m ? (int)m->pinfo.size() : 0; }
+
+int nncu_param_info(const nncu_model *m, int index, char *name_out, size_t name_cap, size_t *numel_out,
+                    size_t *offset_out)
+{
+    if (!m || index < 0 || index >= (int)m->pinfo.size())
+        return nncu_fail(NNCU_ERR_INVALID, "bad parameter index");
+    const ParamInfo &pi = m->pinfo[index];
+    if (name_out && name_cap)
+        snprintf(name_out, name_cap, "%s", pi.name);
+    if (numel_out) *numel_out = pi.numel;
+    if (offset_out) *offset_out = pi.off;
+    return NNCU_OK;
+}
+
+static int param_io(nncu_model *m, int index, float *host, size_t numel, float *base, bool to_host)
+{
+    if (!m || !host || index < 0 || index >= (int)m->pinfo.size())
+        return nncu_fail(NNCU_ERR_INVALID, "bad parameter index or buffer");
+    const ParamInfo &pi = m->pinfo[index];
+    if (numel != pi.numel)
+        return nncu_fail(NNCU_ERR_INVALID, "%s has %zu elements, caller passed %zu", pi.name, pi.numel, numel);
+    CUDA_TRY(cudaSetDevice(m->device));
+    CUDA_TRY(cudaStreamSynchronize(m->st));
+    if (to_host)
+        CUDA_TRY(cudaMemcpy(host, base + pi.off, numel * 4, cudaMemcpyDeviceToHost));
+    else
+        CUDA_TRY(cudaMemcpy(base + pi.off, host, numel * 4, cudaMemcpyHostToDevice));
+    return NNCU_OK;
+}
+
+int nncu_param_get(nncu_model *m, int index, float *host_out, size_t numel)
+{
+    return param_io(m, index, host_out, numel, m ? m->W : nullptr, true);
+}
+
+int nncu_param_set(nncu_model *m, int index, const float *host_in, size_t numel)
+{
+    NNCU_TRY(param_io(m, index, const_cast<float *>(host_in), numel, m ? m->W : nullptr, false));
+    NNCU_TRY(refresh_shadows(m));
+    CUDA_TRY(cudaStreamSynchronize(m->st));
+    return NNCU_OK;
+}
+
+int nncu_grad_get(nncu_model *m, int index, float *host_out, size_t numel)
+{
+    return param_io(m, index, host_out, numel, m ? m->G : nullptr, true);
+}
+
+int nncu_flat_buffers(nncu_model *m, float **master_dev, float **grad_dev, float **moment_dev, size_t *n_floats)
+{
+    if (!m)
+        return nncu_fail(NNCU_ERR_INVALID, "null model");
+    if (master_dev) *master_dev = m->W;
+    if (grad_dev) *grad_dev = m->G;
+    if (moment_dev) *moment_dev = m->Vm;
+    if (n_floats) *n_floats = m->n_floats;
+    return NNCU_OK;
+}
+
+int nncu_weights_hash(nncu_model *m, uint64_t *hash_out)
+{
+    if (!m || !hash_out)
+        return nncu_fail(NNCU_ERR_INVALID, "null argument");
+    CUDA_TRY(cudaSetDevice(m->device));
+    CUDA_TRY(cudaMemsetAsync(m->hash_dev, 0, 8, m->st));
+    hash_kernel<<<296, 256, 0, m->st>>>(m->W, m->n_floats, m->hash_dev);
+    KERNEL_CHECK();
+    unsigned long long h = 0;
+    CUDA_TRY(cudaMemcpyAsync(&h, m->hash_dev, 8, cudaMemcpyDeviceToHost, m->st));
+    CUDA_TRY(cudaStreamSynchronize(m->st));
+    *hash_out = h;
+    return NNCU_OK;
+}
+
+static int coder_bits(int V)
+{
+    int n = 0;
+    while ((1 << n) < V)
+        n++;
+    return ((1 << n) == V) ? n : -1;
+}
+
+int nncu_coder_paths(nncu_model *m, int t0, int nt, const int32_t *sym_host, uint16_t *prob0_host, int *n_bits_out)
+{
+    if (!m || !sym_host || !prob0_host || t0 < 0 || nt < 1 || t0 + nt > m->T)
+        return nncu_fail(NNCU_ERR_INVALID, "bad coder range");
+    int nb = coder_bits(m->V);
+    if (nb < 1)
+        return nncu_fail(NNCU_ERR_INVALID, "coder-ready output needs a power-of-two n_symbols");
+    if ((size_t)2 * m->V * 4 > 200 * 1024)
+        return nncu_fail(NNCU_ERR_RANGE, "n_symbols %d is beyond the 25600-symbol limit of the coder kernels", m->V);
+    CUDA_TRY(cudaSetDevice(m->device));
+    int rows = nt * m->B;
+    // symbols travel through the target staging area of the same rows
+    CUDA_TRY(cudaStreamSynchronize(m->st));
+    memcpy(m->tgt_pin, sym_host, sizeof(int32_t) * rows);
+    CUDA_TRY(cudaMemcpyAsync(m->tgt_dev, m->tgt_pin, sizeof(int32_t) * rows, cudaMemcpyHostToDevice, m->st));
+    coder_paths_kernel<<<rows, 256, (size_t)2 * m->V * 4, m->st>>>(m->probs + (size_t)t0 * m->B * m->V, m->tgt_dev,
+                                                                  m->coder_dev, m->V, nb);
+    KERNEL_CHECK();
+    CUDA_TRY(cudaMemcpyAsync(prob0_host, m->coder_dev, sizeof(uint16_t) * (size_t)rows * nb, cudaMemcpyDeviceToHost, m->st));
+    CUDA_TRY(cudaStreamSynchronize(m->st));
+    if (n_bits_out) *n_bits_out = nb;
+    return NNCU_OK;
+}
+
+int nncu_coder_trees(nncu_model *m, int t0, int nt, uint16_t *tree_host)
+{
+    if (!m || !tree_host || t0 < 0 || nt < 1 || t0 + nt > m->T)
+        return nncu_fail(NNCU_ERR_INVALID, "bad coder range");
+    int nb = coder_bits(m->V);
+    if (nb < 1)
+        return nncu_fail(NNCU_ERR_INVALID, "coder-ready output needs a power-of-two n_symbols");
+    if ((size_t)2 * m->V * 4 > 200 * 1024)
+        return nncu_fail(NNCU_ERR_RANGE, "n_symbols %d is beyond the 25600-symbol limit of the coder kernels", m->V);
+    CUDA_TRY(cudaSetDevice(m->device));
+    int rows = nt * m->B;
+    coder_trees_kernel<<<rows, 256, (size_t)2 * m->V * 4, m->st>>>(m->probs + (size_t)t0 * m->B * m->V, m->coder_dev, m->V);
+    KERNEL_CHECK();
+    CUDA_TRY(cudaMemcpyAsync(tree_host, m->coder_dev, sizeof(uint16_t) * (size_t)rows * m->V, cudaMemcpyDeviceToHost, m->st));
+    CUDA_TRY(cudaStreamSynchronize(m->st));
+    return NNCU_OK;
+}
+
+// ---- launch counting and per-launch timing of the dominant kernel
+
+int nncu_profile_begin(int time_gemms)
+{
+    g_nncu_launches = 0;
+    if (g_nncu_prof) {
+        g_nncu_prof->n = 0;
+    }
+    if (time_gemms) {
+        static GemmProfiler prof;
+        if (!prof.ready) {
+            for (int i = 0; i < 2 * GemmProfiler::MAX_EV; i++)
+                CUDA_TRY(cudaEventCreate(&prof.ev[i]));
+            prof.ready = true;
+        }
+        prof.n = 0;
+        g_nncu_prof = &prof;
+    } else {
+        g_nncu_prof = nullptr;
+    }
+    return NNCU_OK;
+}
+
+int nncu_profile_end(nncu_profile *out)
+{
+    if (!out)
+        return nncu_fail(NNCU_ERR_INVALID, "null argument");
+    memset(out, 0, sizeof(*out));
+    out->launches = g_nncu_launches;
+    GemmProfiler *pr = g_nncu_prof;
+    g_nncu_prof = nullptr;
+    if (pr) {
+        CUDA_TRY(cudaDeviceSynchronize());
+        for (int i = 0; i < pr->n; i++) {
+            float ms = 0.0f;
+            CUDA_TRY(cudaEventElapsedTime(&ms, pr->ev[2 * i], pr->ev[2 * i + 1]));
+            out->gemm_ms += ms;
+            out->gemm_flops += pr->flops[i];
+        }
+        out->gemm_launches = (uint64_t)pr->n;
+    }
+    return NNCU_OK;
+}
+
+// ---- isolated attention op
+
+int nncu_attention_forward(const nncu_attn_shape *s, const void *q, const void *kv, const float *w_r,
+                           const float *b_r, void *out, float *lse, void *cuda_stream)
+{
+    NNCU_TRY(attn_check_shape(s));
+    if (!q || !kv || !b_r || !out)
+        return nncu_fail(NNCU_ERR_INVALID, "null tensor");
+    cudaStream_t st = (cudaStream_t)cuda_stream;
+    return s->dtype_bf16 ? attn_forward_t<bf16>(s, q, kv, w_r, b_r, out, lse, st)
+                         : attn_forward_t<float>(s, q, kv, w_r, b_r, out, lse, st);
+}
+
+int nncu_attention_backward(const nncu_attn_shape *s, const void *q, const void *kv, const float *w_r,
+                            const float *b_r, const void *out, const float *lse, const void *dout, void *dq,
+                            void *dkv, float *dwr_part, float *dbr_part, void *cuda_stream)
+{
+    NNCU_TRY(attn_check_shape(s));
+    if (!q || !kv || !b_r || !out || !lse || !dout || !dq || !dkv)
+        return nncu_fail(NNCU_ERR_INVALID, "null tensor");
+    cudaStream_t st = (cudaStream_t)cuda_stream;
+    return s->dtype_bf16
+               ? attn_backward_t<bf16>(s, q, kv, w_r, b_r, out, lse, dout, dq, dkv, dwr_part, dbr_part, st)
+               : attn_backward_t<float>(s, q, kv, w_r, b_r, out, lse, dout, dq, dkv, dwr_part, dbr_part, st);
+}
+
+int nncu_attention_reduce_tables(const nncu_attn_shape *s, const float *dwr_part, const float *dbr_part,
+                                 float *dw_r, float *db_r, int accumulate, void *cuda_stream)
+{
+    NNCU_TRY(attn_check_shape(s));
+    cudaStream_t st = (cudaStream_t)cuda_stream;
+    const int L = s->mem_len + s->seg_len;
+    if (dbr_part && db_r) {
+        size_t n = (size_t)s->n_head * L;
+        reduce_streams_kernel<<<ceil_div(n, 256), 256, 0, st>>>(dbr_part, s->n_streams, n, db_r, accumulate);
+        KERNEL_CHECK();
+    }
+    if (dwr_part && dw_r) {
+        size_t n = (size_t)s->n_head * s->d_pos * s->d_key;
+        reduce_streams_kernel<<<ceil_div(n, 256), 256, 0, st>>>(dwr_part, s->n_streams, n, dw_r, accumulate);
+        KERNEL_CHECK();
+    }
+    return NNCU_OK;
+}
+
+// ---- dense contraction test hook
+
+int nncu_gemm_bf16_nt(int backend, int M, int N, int K, const void *A, int lda, const void *B, int ldb, void *C,
+                      int ldc, int c_is_f32, const float *bias, void *cuda_stream)
+{
+    if (!A || !B || !C || M < 0 || N < 0 || K < 0)
+        return nncu_fail(NNCU_ERR_INVALID, "bad GEMM arguments");
+    cudaStream_t st = (cudaStream_t)cuda_stream;
+    const bf16 *a = (const bf16 *)A, *b = (const bf16 *)B;
+    if (backend == NNCU_GEMM_SIMT) {
+        return c_is_f32 ? gemm_simt<bf16, bf16, float>(st, GEMM_NT, M, N, K, a, lda, b, ldb, (float *)C, ldc, bias, 0)
+                        : gemm_simt<bf16, bf16, bf16>(st, GEMM_NT, M, N, K, a, lda, b, ldb, (bf16 *)C, ldc, bias, 0);
+    }
+    static int *flag = nullptr;
+    if (!flag) {
+        CUDA_TRY(cudaMalloc(&flag, sizeof(int)));
+        CUDA_TRY(cudaMemset(flag, 0, sizeof(int)));
+    }
+    int rc = c_is_f32 ? tc::gemm_nt<float>(st, M, N, K, a, lda, b, ldb, (float *)C, ldc, bias, nullptr, flag)
+                      : tc::gemm_nt<bf16>(st, M, N, K, a, lda, b, ldb, (bf16 *)C, ldc, bias, nullptr, flag);
+    if (rc != NNCU_OK)
+        return rc;
+    int h = 0;
+    CUDA_TRY(cudaMemcpyAsync(&h, flag, sizeof(int), cudaMemcpyDeviceToHost, st));
+    CUDA_TRY(cudaStreamSynchronize(st));
+    if (h != 0) {
+        cudaMemset(flag, 0, sizeof(int));
+        return nncu_fail(NNCU_ERR_TIMEOUT, "tcgen05 GEMM: a bounded wait expired (code %d)", h);
+    }
+    return NNCU_OK;
+}
+
+} // extern "C"

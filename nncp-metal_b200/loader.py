@@ -14,7 +14,7 @@ LIB = os.path.join(PKG, "libnncu.so")
 HOSTLIB = os.path.join(PKG, "libnncp_host.so")
 
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
-              "--use_fast_math=false", "-Xcompiler", "-fPIC,-O2", "-shared"]
+              "-ccbin", "/usr/bin/g++", "-Xcompiler", "-fPIC,-O2", "-shared"]
 
 
 class LibraryMissing(RuntimeError):
@@ -47,9 +47,9 @@ def build_library(force=False, verbose=False):
         nvcc = _nvcc()
         if nvcc is None:
             raise LibraryMissing("nvcc not found and libnncu.so is not built")
-        cmd = [nvcc] + [f for f in NVCC_FLAGS if f != "--use_fast_math=false"] + \
+        cmd = [nvcc] + NVCC_FLAGS + \
               ["-I", os.path.join(ROOT, "include"), "-I", CSRC] + \
-              (["-Xptxas", "-v"] if verbose else []) + ["-o", LIB] + cu + ["-lcuda"]
+              (["-Xptxas", "-v"] if verbose else []) + ["-o", LIB] + cu
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode != 0:
             raise RuntimeError("nvcc failed:\n" + r.stdout + r.stderr)

@@ -1,0 +1,65 @@
+"""The C-ABI library: loads without a GPU, exports every symbol include/nncu.h declares,
+and refuses to work (loudly, with a status code) when there is no device."""
+import ctypes as C
+import os
+import re
+
+import pytest
+
+from conftest import ROOT
+
+
+def _declared():
+    text = open(os.path.join(ROOT, "include", "nncu.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(nncu_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_library_exports_every_declared_symbol(pkg):
+    pkg.build_library()
+    lib = C.CDLL(pkg.loader.LIB)
+    names = _declared()
+    assert len(names) >= 30
+    for n in names:
+        assert hasattr(lib, n), f"{n} is declared in include/nncu.h but not exported"
+    assert set(names) == set(pkg.abi.PROTOTYPES), "abi.py and include/nncu.h disagree"
+
+
+def test_struct_layout_matches_header(pkg):
+    # nncu_params: 12 int32 + 32 int32 + 8 uint8 + 2 float + int32 + uint32 + 4 float + 3 int32
+    assert C.sizeof(pkg.abi.Params) == 4 * 12 + 4 * 32 + 8 + 4 * 2 + 4 + 4 + 4 * 4 + 4 * 3
+    assert C.sizeof(pkg.abi.AttnShape) == 4 * 11
+
+
+def test_default_params_and_version(pkg):
+    lib = pkg.library()
+    assert lib.nncu_abi_version() == 1
+    p = pkg.abi.Params()
+    lib.nncu_default_params(C.byref(p))
+    # the "default" profile of nncp.c:2471-2513
+    assert (p.n_layer, p.d_model, p.n_head, p.d_inner, p.seg_len, p.n_streams) == (4, 256, 8, 512, 32, 16)
+    assert p.tied_w_r == 1 and p.tied_b_r == 1 and p.ln_flags == pkg.abi.LN_POST
+
+
+def test_invalid_options_are_rejected_before_any_device_work(pkg):
+    lib = pkg.library()
+    for over in (dict(d_pos=1000), dict(ln_flags=3), dict(ln_flags=8), dict(ff_act=3),
+                 dict(d_value=7), dict(n_layer=0), dict(n_layer=33)):
+        p = pkg.abi.make_params(**over)
+        h = C.c_void_p()
+        assert lib.nncu_create(C.byref(p), C.byref(h)) == pkg.abi.ERR_INVALID
+        assert lib.nncu_last_error() != b""
+        assert not h.value
+
+
+def test_no_device_means_error_not_fallback(pkg):
+    import torch
+    if torch.cuda.is_available():
+        pytest.skip("a GPU is present")
+    lib = pkg.library()
+    p = pkg.abi.make_params()
+    h = C.c_void_p()
+    assert lib.nncu_create(C.byref(p), C.byref(h)) == pkg.abi.ERR_CUDA
+    assert b"no CUDA device" in lib.nncu_last_error()
+    with pytest.raises(Exception):
+        pkg.TrfModel(p)
