@@ -106,7 +106,7 @@ PROTOTYPES = {
     "nncu_coder_paths": (_i, [_vp, _i, _i, _vp, _vp, C.POINTER(_i)]),
     "nncu_coder_trees": (_i, [_vp, _i, _i, _vp]),
     "nncu_attention_forward": (_i, [C.POINTER(AttnShape), _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
-    "nncu_attention_backward": (_i, [C.POINTER(AttnShape)] + [_vp] * 13),
+    "nncu_attention_backward": (_i, [C.POINTER(AttnShape)] + [_vp] * 12),
     "nncu_attention_reduce_tables": (_i, [C.POINTER(AttnShape), _vp, _vp, _vp, _vp, _i, _vp]),
     "nncu_profile_begin": (_i, [_i]),
     "nncu_profile_end": (_i, [C.POINTER(Profile)]),

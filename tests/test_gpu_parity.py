@@ -34,6 +34,20 @@ def _load(model, z, step=0, rounder=None):
         model.set_param(name, rounder(v) if rounder else v)
 
 
+def _check_updated_weights(w, w_ref, w_before, g_ref, tol, lr, beta2, what):
+    """RMSProp moves a weight by lr*g/sqrt(v): at the first step that is +-lr/sqrt(1-beta2)
+    whatever |g| is, so where the reference gradient is below the arithmetic noise its SIGN,
+    and with it the whole update, is not determined.  Elements with a clearly non-zero
+    gradient must match within tol of the weights plus the gradient tolerance (5*tol) of the
+    update itself; the rest may differ by at most one full update each way."""
+    scale = max(np.abs(w_ref).max(), 1e-3)
+    upd = np.abs(w_ref - w_before).max(initial=0.0)
+    sure = np.abs(g_ref) > 0.1 * max(np.abs(g_ref).max(), 1e-12)
+    d = np.abs(w - w_ref)
+    assert d[sure].max(initial=0.0) < tol * scale + 5 * tol * upd, what
+    assert d.max(initial=0.0) < tol * scale + 2.1 * lr / np.sqrt(1.0 - beta2), what
+
+
 # ---------------------------------------------------------------- dense contraction
 
 @pytest.mark.parametrize("M,N,K", [(128, 128, 64), (256, 512, 512), (2048, 512, 512), (100, 72, 40),
@@ -221,11 +235,12 @@ def test_train_step_bf16_vs_oracle(pkg, oracle, name, backend):
             g_ref = o.get_grad(pname)
             scale = max(np.abs(g_ref).max(), 1e-6)
             assert np.abs(m.get_grad(pname) - g_ref).max() / scale < 5 * BF16_TOL, (pname, s)
+        grads = {pname: o.get_grad(pname) for pname in m.info}
+        before = {pname: o.get_param(pname) for pname in m.info}
         m.update(); o.update()
         for pname in m.info:
-            w, w_ref = m.get_param(pname), o.get_param(pname)
-            bad = np.abs(w - w_ref) > BF16_TOL * max(np.abs(w_ref).max(), 1e-3)
-            assert bad.mean() < 0.05, (pname, s, bad.mean())
+            _check_updated_weights(m.get_param(pname), o.get_param(pname), before[pname], grads[pname],
+                                   BF16_TOL, cfg["lr"], cfg["beta2"], (pname, s))
         # keep the two trajectories together so that step 2 tests step 2
         for pname in m.info:
             o.set_param(pname, m.get_param(pname))
