@@ -1,0 +1,711 @@
+// attention_mma.cuh -- bf16 relative-position attention on the warp-level tensor path
+// (mma.sync m16n8k16, fp32 accumulate), forward and backward, one CTA per (stream, head).
+//
+// Same math as attention.cuh (nncp.c:722-800 and its adjoint).  Per (stream, head) the
+// contractions are 64 x 128 x 64: too small for a 128-row tcgen05 tile to pay, and the
+// relative shift needs a per-row skew of the position scores that a register-fragment
+// kernel can do through a few KB of shared memory.  Each warp owns 16 query rows:
+//
+//   S  = Q K^T                 (16 x 64 per key block)
+//   E  = Q R^T                 (16 x 80 window of the position table for that block)
+//   s  = (S + skew(E) + b_r) / sqrt(dk), masked, online softmax over key blocks of 64
+//   O += P V
+//
+// Tile origins are multiples of 16 queries / 64 keys counted from 0 whatever range of
+// queries is requested, so query row i goes through the same sequence of instructions
+// and gives the same bits in a one-symbol step as in a whole-segment launch.
+//
+// Backward stores P, dS (bf16) and the inverse-skewed dE for the whole (T <= 64) x L tile
+// in shared memory, then runs dV = P^T dO, dK = dS^T Q, dQ = dS K + dE R, dR = dE^T Q as
+// tensor-core contractions with transposed fragments from ldmatrix.trans.  All sums have
+// a fixed order; the per-(stream, head) table gradients are reduced by the caller.
+#pragma once
+#include "attention.cuh"
+
+namespace amma {
+
+__device__ __forceinline__ void ldsm4(uint32_t (&r)[4], const bf16 *p)
+{
+    uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(a));
+}
+__device__ __forceinline__ void ldsm4t(uint32_t (&r)[4], const bf16 *p)
+{
+    uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(a));
+}
+__device__ __forceinline__ void mma16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1)
+{
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 "
+                 "{%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack2(float lo, float hi)
+{
+    __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t *>(&h);
+}
+
+constexpr int EW = 88; // fp32 row stride of the per-warp skew scratch (80 columns used)
+
+struct Dims {
+    int Lp, Pr, LDS, LPS, PPS;
+};
+__host__ __device__ inline Dims dims_of(int L, int P, int dk)
+{
+    Dims d;
+    d.Lp = (L + 63) / 64 * 64;      // key rows, padded with zero rows
+    d.Pr = (P + 1 + 15) / 16 * 16;  // position rows, at least one zero row after the table
+    d.LDS = dk + 8;                 // bf16 row stride of Q, K, V, R, dO tiles
+    d.LPS = d.Lp + 8;               // bf16 row stride of the P / dS tiles
+    d.PPS = d.Pr + 8;               // bf16 row stride of the dE tile
+    return d;
+}
+
+// rows [row0, row0+nrows) of a [.. x dk] bf16 matrix with row pitch `pitch` elements ->
+// shared tile; rows that fail `valid` are zero.  16-byte chunks.
+template <typename F>
+__device__ __forceinline__ void load_tile(bf16 *dst, int lds, const bf16 *src, size_t pitch, int nrows,
+                                          int dk, F valid)
+{
+    const int cpr = dk / 8;
+    for (int idx = threadIdx.x; idx < nrows * cpr; idx += blockDim.x) {
+        int r = idx / cpr, c = (idx % cpr) * 8;
+        uint4 v = make_uint4(0u, 0u, 0u, 0u);
+        if (valid(r))
+            v = *reinterpret_cast<const uint4 *>(src + (size_t)r * pitch + c);
+        *reinterpret_cast<uint4 *>(dst + (size_t)r * lds + c) = v;
+    }
+}
+
+__device__ __forceinline__ void load_table(bf16 *dst, int lds, const float *w_r_h, int P, int Pr, int dk)
+{
+    for (int idx = threadIdx.x; idx < Pr * dk; idx += blockDim.x) {
+        int p = idx / dk, e = idx % dk;
+        dst[(size_t)p * lds + e] = (w_r_h && p < P) ? __float2bfloat16_rn(w_r_h[(size_t)p * dk + e])
+                                                     : __float2bfloat16_rn(0.0f);
+    }
+}
+
+// scores of one 16-query x 64-key block: s[nt][c], already scaled and masked (-inf).
+// qf: Q fragments of the warp's 16 rows.  es: the warp's skew scratch.
+template <int DK>
+__device__ __forceinline__ void score_block(const AttnArgs &a, const Dims &d, const uint32_t (&qf)[DK / 16][4],
+                                            const bf16 *Ks, const bf16 *Rs, const float *brs, float *es,
+                                            int i0, int j0, int iA, int iB, int jloA, int jhiA, int jloB,
+                                            int jhiB, float (&s)[8][4])
+{
+    const int lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+    constexpr int KS = DK / 16;
+#pragma unroll
+    for (int nt = 0; nt < 8; nt++)
+#pragma unroll
+        for (int c = 0; c < 4; c++)
+            s[nt][c] = 0.0f;
+#pragma unroll
+    for (int ks = 0; ks < KS; ks++)
+#pragma unroll
+        for (int np = 0; np < 4; np++) {
+            uint32_t b[4];
+            ldsm4(b, Ks + (size_t)(j0 + np * 16 + (lane & 7) + (lane >> 4) * 8) * d.LDS + ks * 16 + ((lane >> 3) & 1) * 8);
+            mma16816(s[2 * np], qf[ks], b[0], b[1]);
+            mma16816(s[2 * np + 1], qf[ks], b[2], b[3]);
+        }
+    int pbase = 0;
+    if (a.w_r) {
+        const int pmin = j0 + (a.T - 1) - (i0 + 15) - (a.L - a.P);
+        pbase = pmin > 0 ? pmin : 0;
+        float e[10][4];
+#pragma unroll
+        for (int nt = 0; nt < 10; nt++)
+#pragma unroll
+            for (int c = 0; c < 4; c++)
+                e[nt][c] = 0.0f;
+#pragma unroll
+        for (int ks = 0; ks < KS; ks++)
+#pragma unroll
+            for (int np = 0; np < 5; np++) {
+                int row = pbase + np * 16 + (lane & 7) + (lane >> 4) * 8;
+                row = row < d.Pr - 1 ? row : d.Pr - 1; // rows past the table are zero
+                uint32_t b[4];
+                ldsm4(b, Rs + (size_t)row * d.LDS + ks * 16 + ((lane >> 3) & 1) * 8);
+                mma16816(e[2 * np], qf[ks], b[0], b[1]);
+                mma16816(e[2 * np + 1], qf[ks], b[2], b[3]);
+            }
+        __syncwarp();
+#pragma unroll
+        for (int nt = 0; nt < 10; nt++) {
+            es[g * EW + nt * 8 + 2 * t] = e[nt][0];
+            es[g * EW + nt * 8 + 2 * t + 1] = e[nt][1];
+            es[(g + 8) * EW + nt * 8 + 2 * t] = e[nt][2];
+            es[(g + 8) * EW + nt * 8 + 2 * t + 1] = e[nt][3];
+        }
+        __syncwarp();
+    }
+#pragma unroll
+    for (int nt = 0; nt < 8; nt++)
+#pragma unroll
+        for (int c = 0; c < 4; c++) {
+            const int j = j0 + nt * 8 + 2 * t + (c & 1);
+            const bool hi = c >= 2;
+            const int i = hi ? iB : iA;
+            const bool vis = hi ? (j >= jloB && j <= jhiB) : (j >= jloA && j <= jhiA);
+            float v = -INFINITY;
+            if (vis) {
+                const int r = j + (a.T - 1) - i;
+                float z = brs[r];
+                if (a.w_r) {
+                    int pi = r - (a.L - a.P);
+                    pi = pi < 0 ? 0 : pi;
+                    z += es[(g + (hi ? 8 : 0)) * EW + pi - pbase];
+                }
+                v = (s[nt][c] + z) * a.inv_sqrt;
+            }
+            s[nt][c] = v;
+        }
+}
+
+template <int DK>
+size_t fwd_smem(int L, int P)
+{
+    Dims d = dims_of(L, P, DK);
+    return ((size_t)64 * d.LDS + (size_t)2 * d.Lp * d.LDS + (size_t)d.Pr * d.LDS) * sizeof(bf16) +
+           ((size_t)L + 4 * 16 * EW) * sizeof(float) + 64;
+}
+
+template <int DK>
+__global__ void __launch_bounds__(128) attn_fwd_mma_kernel(AttnArgs a)
+{
+    extern __shared__ __align__(16) unsigned char smraw[];
+    const Dims d = dims_of(a.L, a.P, DK);
+    bf16 *Qs = reinterpret_cast<bf16 *>(smraw);
+    bf16 *Ks = Qs + (size_t)64 * d.LDS;
+    bf16 *Vs = Ks + (size_t)d.Lp * d.LDS;
+    bf16 *Rs = Vs + (size_t)d.Lp * d.LDS;
+    float *brs = reinterpret_cast<float *>(Rs + (size_t)d.Pr * d.LDS);
+    float *Es = brs + ((a.L + 3) & ~3);
+    constexpr int KS = DK / 16, NT = DK / 8;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+    const int b = blockIdx.x / a.H, h = blockIdx.x % a.H;
+    const int HD = a.H * DK;
+    const int qt0 = (a.t0 / 16) * 16 + blockIdx.y * 64; // first query row of this CTA's tiles
+
+    const bf16 *q = reinterpret_cast<const bf16 *>(a.q);
+    const bf16 *kv = reinterpret_cast<const bf16 *>(a.kv);
+    load_tile(Qs, d.LDS, q + ((size_t)qt0 * a.B + b) * HD + h * DK, (size_t)a.B * HD, 64, DK,
+              [&](int r) { return qt0 + r >= a.t0 && qt0 + r < a.t1; });
+    load_tile(Ks, d.LDS, kv + (size_t)b * 2 * HD + h * DK, (size_t)a.B * 2 * HD, d.Lp, DK,
+              [&](int r) { return r < a.L; });
+    load_tile(Vs, d.LDS, kv + (size_t)b * 2 * HD + HD + h * DK, (size_t)a.B * 2 * HD, d.Lp, DK,
+              [&](int r) { return r < a.L; });
+    load_table(Rs, d.LDS, a.w_r ? a.w_r + (size_t)h * a.P * DK : nullptr, a.P, d.Pr, DK);
+    for (int r = threadIdx.x; r < a.L; r += blockDim.x)
+        brs[r] = a.br_scale * a.b_r[(size_t)h * a.L + r];
+    __syncthreads();
+
+    const int i0 = qt0 + warp * 16;
+    const int va = max(i0, a.t0), vb = min(i0 + 16, a.t1) - 1; // valid rows of this warp
+    if (va > vb)
+        return;
+    uint32_t qf[KS][4];
+#pragma unroll
+    for (int ks = 0; ks < KS; ks++)
+        ldsm4(qf[ks], Qs + (size_t)(warp * 16 + (lane & 15)) * d.LDS + ks * 16 + (lane >> 4) * 8);
+    const int iA = i0 + g, iB = i0 + g + 8;
+    int jloA = 0, jhiA = -1, jloB = 0, jhiB = -1;
+    if (iA >= a.t0 && iA < a.t1)
+        key_range(a, iA, jloA, jhiA);
+    if (iB >= a.t0 && iB < a.t1)
+        key_range(a, iB, jloB, jhiB);
+    int jmin, jmax, tmp;
+    key_range(a, va, jmin, tmp);
+    key_range(a, vb, tmp, jmax);
+    float o[NT][4];
+#pragma unroll
+    for (int nt = 0; nt < NT; nt++)
+#pragma unroll
+        for (int c = 0; c < 4; c++)
+            o[nt][c] = 0.0f;
+    float mA = -INFINITY, mB = -INFINITY, lA = 0.0f, lB = 0.0f;
+    float *es = Es + (size_t)warp * 16 * EW;
+
+    for (int kb = jmin / 64; kb <= jmax / 64; kb++) {
+        const int j0 = kb * 64;
+        float s[8][4];
+        score_block<DK>(a, d, qf, Ks, Rs, brs, es, i0, j0, iA, iB, jloA, jhiA, jloB, jhiB, s);
+        float mxA = -INFINITY, mxB = -INFINITY;
+#pragma unroll
+        for (int nt = 0; nt < 8; nt++) {
+            mxA = fmaxf(mxA, fmaxf(s[nt][0], s[nt][1]));
+            mxB = fmaxf(mxB, fmaxf(s[nt][2], s[nt][3]));
+        }
+        mxA = fmaxf(mxA, __shfl_xor_sync(0xffffffffu, mxA, 1));
+        mxA = fmaxf(mxA, __shfl_xor_sync(0xffffffffu, mxA, 2));
+        mxB = fmaxf(mxB, __shfl_xor_sync(0xffffffffu, mxB, 1));
+        mxB = fmaxf(mxB, __shfl_xor_sync(0xffffffffu, mxB, 2));
+        const float nA = fmaxf(mA, mxA), nB = fmaxf(mB, mxB);
+        const float uA = nA == -INFINITY ? 0.0f : nA, uB = nB == -INFINITY ? 0.0f : nB;
+        const float scA = expf(mA - uA), scB = expf(mB - uB);
+        mA = nA;
+        mB = nB;
+        float sumA = 0.0f, sumB = 0.0f;
+#pragma unroll
+        for (int nt = 0; nt < 8; nt++) {
+            s[nt][0] = expf(s[nt][0] - uA);
+            s[nt][1] = expf(s[nt][1] - uA);
+            s[nt][2] = expf(s[nt][2] - uB);
+            s[nt][3] = expf(s[nt][3] - uB);
+            sumA += s[nt][0] + s[nt][1];
+            sumB += s[nt][2] + s[nt][3];
+        }
+        lA = lA * scA + sumA;
+        lB = lB * scB + sumB;
+#pragma unroll
+        for (int nt = 0; nt < NT; nt++) {
+            o[nt][0] *= scA;
+            o[nt][1] *= scA;
+            o[nt][2] *= scB;
+            o[nt][3] *= scB;
+        }
+#pragma unroll
+        for (int k2 = 0; k2 < 4; k2++) {
+            uint32_t pa[4];
+            pa[0] = pack2(s[2 * k2][0], s[2 * k2][1]);
+            pa[1] = pack2(s[2 * k2][2], s[2 * k2][3]);
+            pa[2] = pack2(s[2 * k2 + 1][0], s[2 * k2 + 1][1]);
+            pa[3] = pack2(s[2 * k2 + 1][2], s[2 * k2 + 1][3]);
+#pragma unroll
+            for (int np = 0; np < NT / 2; np++) {
+                uint32_t bb[4];
+                ldsm4t(bb, Vs + (size_t)(j0 + k2 * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * d.LDS + np * 16 + (lane >> 4) * 8);
+                mma16816(o[2 * np], pa, bb[0], bb[1]);
+                mma16816(o[2 * np + 1], pa, bb[2], bb[3]);
+            }
+        }
+        __syncwarp();
+    }
+    lA += __shfl_xor_sync(0xffffffffu, lA, 1);
+    lA += __shfl_xor_sync(0xffffffffu, lA, 2);
+    lB += __shfl_xor_sync(0xffffffffu, lB, 1);
+    lB += __shfl_xor_sync(0xffffffffu, lB, 2);
+    bf16 *out = reinterpret_cast<bf16 *>(a.o);
+    if (iA >= a.t0 && iA < a.t1) {
+        const float inv = 1.0f / lA;
+        bf16 *dst = out + ((size_t)iA * a.B + b) * HD + h * DK;
+#pragma unroll
+        for (int nt = 0; nt < NT; nt++)
+            *reinterpret_cast<uint32_t *>(dst + nt * 8 + 2 * t) = pack2(o[nt][0] * inv, o[nt][1] * inv);
+        if (t == 0 && a.lse)
+            a.lse[((size_t)b * a.H + h) * a.T + iA] = mA + logf(lA);
+    }
+    if (iB >= a.t0 && iB < a.t1) {
+        const float inv = 1.0f / lB;
+        bf16 *dst = out + ((size_t)iB * a.B + b) * HD + h * DK;
+#pragma unroll
+        for (int nt = 0; nt < NT; nt++)
+            *reinterpret_cast<uint32_t *>(dst + nt * 8 + 2 * t) = pack2(o[nt][2] * inv, o[nt][3] * inv);
+        if (t == 0 && a.lse)
+            a.lse[((size_t)b * a.H + h) * a.T + iB] = mB + logf(lB);
+    }
+}
+
+template <int DK>
+size_t bwd_smem(int L, int P)
+{
+    Dims d = dims_of(L, P, DK);
+    return ((size_t)2 * 64 * d.LDS + (size_t)2 * d.Lp * d.LDS + (size_t)d.Pr * d.LDS + (size_t)2 * 64 * d.LPS +
+            (size_t)64 * d.PPS) * sizeof(bf16) +
+           ((size_t)L + 4 + 4 * 16 * EW + 128) * sizeof(float) + 64;
+}
+
+template <int DK>
+__global__ void __launch_bounds__(128) attn_bwd_mma_kernel(AttnArgs a)
+{
+    extern __shared__ __align__(16) unsigned char smraw[];
+    const Dims d = dims_of(a.L, a.P, DK);
+    bf16 *Qs = reinterpret_cast<bf16 *>(smraw);
+    bf16 *dOs = Qs + (size_t)64 * d.LDS;
+    bf16 *Ks = dOs + (size_t)64 * d.LDS;
+    bf16 *Vs = Ks + (size_t)d.Lp * d.LDS;
+    bf16 *Rs = Vs + (size_t)d.Lp * d.LDS;
+    bf16 *Pm = Rs + (size_t)d.Pr * d.LDS;
+    bf16 *dSm = Pm + (size_t)64 * d.LPS;
+    bf16 *dEm = dSm + (size_t)64 * d.LPS;
+    float *brs = reinterpret_cast<float *>(dEm + (size_t)64 * d.PPS);
+    float *Es = brs + ((a.L + 3) & ~3);
+    float *Dr = Es + 4 * 16 * EW; // [64]
+    float *lses = Dr + 64;        // [64]
+    constexpr int KS = DK / 16, NT = DK / 8;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+    const int b = blockIdx.x / a.H, h = blockIdx.x % a.H;
+    const int HD = a.H * DK, T = a.T, L = a.L, P = a.P;
+
+    const bf16 *q = reinterpret_cast<const bf16 *>(a.q);
+    const bf16 *kv = reinterpret_cast<const bf16 *>(a.kv);
+    const bf16 *dout = reinterpret_cast<const bf16 *>(a.dout);
+    const bf16 *outp = reinterpret_cast<const bf16 *>(a.out);
+    load_tile(Qs, d.LDS, q + (size_t)b * HD + h * DK, (size_t)a.B * HD, 64, DK, [&](int r) { return r < T; });
+    load_tile(dOs, d.LDS, dout + (size_t)b * HD + h * DK, (size_t)a.B * HD, 64, DK, [&](int r) { return r < T; });
+    load_tile(Ks, d.LDS, kv + (size_t)b * 2 * HD + h * DK, (size_t)a.B * 2 * HD, d.Lp, DK, [&](int r) { return r < L; });
+    load_tile(Vs, d.LDS, kv + (size_t)b * 2 * HD + HD + h * DK, (size_t)a.B * 2 * HD, d.Lp, DK,
+              [&](int r) { return r < L; });
+    load_table(Rs, d.LDS, a.w_r ? a.w_r + (size_t)h * P * DK : nullptr, P, d.Pr, DK);
+    for (int r = threadIdx.x; r < L; r += blockDim.x)
+        brs[r] = a.br_scale * a.b_r[(size_t)h * L + r];
+    {
+        uint32_t *z = reinterpret_cast<uint32_t *>(Pm); // P, dS, dE are contiguous
+        const int n = (2 * 64 * d.LPS + 64 * d.PPS) / 2;
+        for (int i = threadIdx.x; i < n; i += blockDim.x)
+            z[i] = 0u;
+    }
+    // D_i = dO_i . O_i and the saved log-sum-exp, one warp per 16 rows
+    for (int r = warp * 16; r < warp * 16 + 16; r++) {
+        float s = 0.0f;
+        if (r < T) {
+            const size_t go = ((size_t)r * a.B + b) * HD + h * DK;
+            for (int e = lane; e < DK; e += 32)
+                s += to_f(dout[go + e]) * to_f(outp[go + e]);
+        }
+        s = warp_sum(s);
+        if (lane == 0) {
+            Dr[r] = s;
+            lses[r] = r < T ? a.lse[((size_t)b * a.H + h) * T + r] : 0.0f;
+        }
+    }
+    __syncthreads();
+
+    // ---- phase A: P and dS of the warp's 16 query rows
+    {
+        const int i0 = warp * 16;
+        const int va = i0, vb = min(i0 + 16, T) - 1;
+        if (va <= vb) {
+            uint32_t qf[KS][4], df[KS][4];
+#pragma unroll
+            for (int ks = 0; ks < KS; ks++) {
+                ldsm4(qf[ks], Qs + (size_t)(i0 + (lane & 15)) * d.LDS + ks * 16 + (lane >> 4) * 8);
+                ldsm4(df[ks], dOs + (size_t)(i0 + (lane & 15)) * d.LDS + ks * 16 + (lane >> 4) * 8);
+            }
+            const int iA = i0 + g, iB = i0 + g + 8;
+            int jloA = 0, jhiA = -1, jloB = 0, jhiB = -1;
+            if (iA < T)
+                key_range(a, iA, jloA, jhiA);
+            if (iB < T)
+                key_range(a, iB, jloB, jhiB);
+            int jmin, jmax, tmp;
+            key_range(a, va, jmin, tmp);
+            key_range(a, vb, tmp, jmax);
+            const float lseA = lses[i0 + g], lseB = lses[i0 + g + 8];
+            const float DA = Dr[i0 + g], DB = Dr[i0 + g + 8];
+            float *es = Es + (size_t)warp * 16 * EW;
+            for (int kb = jmin / 64; kb <= jmax / 64; kb++) {
+                const int j0 = kb * 64;
+                float s[8][4], dp[8][4];
+                score_block<DK>(a, d, qf, Ks, Rs, brs, es, i0, j0, iA, iB, jloA, jhiA, jloB, jhiB, s);
+#pragma unroll
+                for (int nt = 0; nt < 8; nt++)
+#pragma unroll
+                    for (int c = 0; c < 4; c++)
+                        dp[nt][c] = 0.0f;
+#pragma unroll
+                for (int ks = 0; ks < KS; ks++)
+#pragma unroll
+                    for (int np = 0; np < 4; np++) {
+                        uint32_t bb[4];
+                        ldsm4(bb, Vs + (size_t)(j0 + np * 16 + (lane & 7) + (lane >> 4) * 8) * d.LDS + ks * 16 + ((lane >> 3) & 1) * 8);
+                        mma16816(dp[2 * np], df[ks], bb[0], bb[1]);
+                        mma16816(dp[2 * np + 1], df[ks], bb[2], bb[3]);
+                    }
+#pragma unroll
+                for (int nt = 0; nt < 8; nt++) {
+                    const float p0 = expf(s[nt][0] - lseA), p1 = expf(s[nt][1] - lseA);
+                    const float p2 = expf(s[nt][2] - lseB), p3 = expf(s[nt][3] - lseB);
+                    const int col = j0 + nt * 8 + 2 * t;
+                    *reinterpret_cast<uint32_t *>(Pm + (size_t)(i0 + g) * d.LPS + col) = pack2(p0, p1);
+                    *reinterpret_cast<uint32_t *>(Pm + (size_t)(i0 + g + 8) * d.LPS + col) = pack2(p2, p3);
+                    *reinterpret_cast<uint32_t *>(dSm + (size_t)(i0 + g) * d.LPS + col) =
+                        pack2(p0 * (dp[nt][0] - DA) * a.inv_sqrt, p1 * (dp[nt][1] - DA) * a.inv_sqrt);
+                    *reinterpret_cast<uint32_t *>(dSm + (size_t)(i0 + g + 8) * d.LPS + col) =
+                        pack2(p2 * (dp[nt][2] - DB) * a.inv_sqrt, p3 * (dp[nt][3] - DB) * a.inv_sqrt);
+                }
+                __syncwarp();
+            }
+        }
+    }
+    __syncthreads();
+    // ---- inverse skew: dE[i][p] collects dS[i][j] with p = max(j + T-1-i - (L-P), 0);
+    //      db_r[r] = br_scale * sum_i dS[i][r - (T-1-i)]
+    for (int idx = threadIdx.x; idx < 64 * d.Pr; idx += blockDim.x) {
+        const int i = idx / d.Pr, p = idx % d.Pr;
+        float v = 0.0f;
+        if (i < T && p < P && a.w_r) {
+            if (p >= 1) {
+                const int j = p + (L - P) - (T - 1 - i);
+                if (j >= 0 && j < L)
+                    v = to_f(dSm[(size_t)i * d.LPS + j]);
+            } else {
+                for (int r = 0; r <= L - P; r++) {
+                    const int j = r - (T - 1 - i);
+                    if (j >= 0 && j < L)
+                        v += to_f(dSm[(size_t)i * d.LPS + j]);
+                }
+            }
+        }
+        dEm[(size_t)i * d.PPS + p] = __float2bfloat16_rn(v);
+    }
+    if (a.dbr_part) {
+        float *dst = a.dbr_part + ((size_t)b * a.H + h) * L;
+        for (int r = threadIdx.x; r < L; r += blockDim.x) {
+            float acc = 0.0f;
+            for (int i = 0; i < T; i++) {
+                const int j = r - (T - 1 - i);
+                if (j >= 0 && j < L)
+                    acc += to_f(dSm[(size_t)i * d.LPS + j]);
+            }
+            dst[r] = acc * a.br_scale;
+        }
+    }
+    __syncthreads();
+
+    // ---- phase B
+    bf16 *dkv = reinterpret_cast<bf16 *>(a.dkv);
+    // dV = P^T dO and dK = dS^T Q: 16-key row tiles spread over the warps, K = 64 queries
+    for (int mt = warp; mt < d.Lp / 16; mt += 4) {
+        const int jm0 = mt * 16;
+        float dv[NT][4], dk[NT][4];
+#pragma unroll
+        for (int nt = 0; nt < NT; nt++)
+#pragma unroll
+            for (int c = 0; c < 4; c++) {
+                dv[nt][c] = 0.0f;
+                dk[nt][c] = 0.0f;
+            }
+#pragma unroll
+        for (int ks = 0; ks < 4; ks++) {
+            uint32_t ap[4], as[4];
+            const int mi = lane >> 3;
+            const size_t aoff = (size_t)(ks * 16 + (lane & 7) + (mi >> 1) * 8) * d.LPS + jm0 + (mi & 1) * 8;
+            ldsm4t(ap, Pm + aoff);
+            ldsm4t(as, dSm + aoff);
+#pragma unroll
+            for (int np = 0; np < NT / 2; np++) {
+                uint32_t bo[4], bq[4];
+                const size_t boff = (size_t)(ks * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * d.LDS + np * 16 + (lane >> 4) * 8;
+                ldsm4t(bo, dOs + boff);
+                ldsm4t(bq, Qs + boff);
+                mma16816(dv[2 * np], ap, bo[0], bo[1]);
+                mma16816(dv[2 * np + 1], ap, bo[2], bo[3]);
+                mma16816(dk[2 * np], as, bq[0], bq[1]);
+                mma16816(dk[2 * np + 1], as, bq[2], bq[3]);
+            }
+        }
+#pragma unroll
+        for (int hh = 0; hh < 2; hh++) {
+            const int j = jm0 + g + hh * 8;
+            if (j < L) {
+                bf16 *dst = dkv + ((size_t)j * a.B + b) * 2 * HD + h * DK;
+#pragma unroll
+                for (int nt = 0; nt < NT; nt++) {
+                    *reinterpret_cast<uint32_t *>(dst + nt * 8 + 2 * t) = pack2(dk[nt][2 * hh], dk[nt][2 * hh + 1]);
+                    *reinterpret_cast<uint32_t *>(dst + HD + nt * 8 + 2 * t) = pack2(dv[nt][2 * hh], dv[nt][2 * hh + 1]);
+                }
+            }
+        }
+    }
+    // dQ = dS K + dE R: one 16-query tile per warp
+    {
+        const int i0 = warp * 16;
+        float dq[NT][4];
+#pragma unroll
+        for (int nt = 0; nt < NT; nt++)
+#pragma unroll
+            for (int c = 0; c < 4; c++)
+                dq[nt][c] = 0.0f;
+        if (i0 < T) {
+            for (int ks = 0; ks < d.Lp / 16; ks++) {
+                uint32_t as[4];
+                ldsm4(as, dSm + (size_t)(i0 + (lane & 15)) * d.LPS + ks * 16 + (lane >> 4) * 8);
+#pragma unroll
+                for (int np = 0; np < NT / 2; np++) {
+                    uint32_t bk[4];
+                    ldsm4t(bk, Ks + (size_t)(ks * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * d.LDS + np * 16 + (lane >> 4) * 8);
+                    mma16816(dq[2 * np], as, bk[0], bk[1]);
+                    mma16816(dq[2 * np + 1], as, bk[2], bk[3]);
+                }
+            }
+            if (a.w_r)
+                for (int ks = 0; ks < d.Pr / 16; ks++) {
+                    uint32_t ae[4];
+                    ldsm4(ae, dEm + (size_t)(i0 + (lane & 15)) * d.PPS + ks * 16 + (lane >> 4) * 8);
+#pragma unroll
+                    for (int np = 0; np < NT / 2; np++) {
+                        uint32_t br[4];
+                        ldsm4t(br, Rs + (size_t)(ks * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * d.LDS + np * 16 + (lane >> 4) * 8);
+                        mma16816(dq[2 * np], ae, br[0], br[1]);
+                        mma16816(dq[2 * np + 1], ae, br[2], br[3]);
+                    }
+                }
+            bf16 *dqg = reinterpret_cast<bf16 *>(a.dq);
+#pragma unroll
+            for (int hh = 0; hh < 2; hh++) {
+                const int i = i0 + g + hh * 8;
+                if (i < T) {
+                    bf16 *dst = dqg + ((size_t)i * a.B + b) * HD + h * DK;
+#pragma unroll
+                    for (int nt = 0; nt < NT; nt++)
+                        *reinterpret_cast<uint32_t *>(dst + nt * 8 + 2 * t) = pack2(dq[nt][2 * hh], dq[nt][2 * hh + 1]);
+                }
+            }
+        }
+    }
+    // dR = dE^T Q (this stream's share of the table gradient), fp32
+    if (a.w_r && a.dwr_part) {
+        float *dst0 = a.dwr_part + ((size_t)b * a.H + h) * P * DK;
+        for (int mt = warp; mt < d.Pr / 16; mt += 4) {
+            const int pm0 = mt * 16;
+            float dr[NT][4];
+#pragma unroll
+            for (int nt = 0; nt < NT; nt++)
+#pragma unroll
+                for (int c = 0; c < 4; c++)
+                    dr[nt][c] = 0.0f;
+#pragma unroll
+            for (int ks = 0; ks < 4; ks++) {
+                uint32_t ae[4];
+                const int mi = lane >> 3;
+                ldsm4t(ae, dEm + (size_t)(ks * 16 + (lane & 7) + (mi >> 1) * 8) * d.PPS + pm0 + (mi & 1) * 8);
+#pragma unroll
+                for (int np = 0; np < NT / 2; np++) {
+                    uint32_t bq[4];
+                    ldsm4t(bq, Qs + (size_t)(ks * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * d.LDS + np * 16 + (lane >> 4) * 8);
+                    mma16816(dr[2 * np], ae, bq[0], bq[1]);
+                    mma16816(dr[2 * np + 1], ae, bq[2], bq[3]);
+                }
+            }
+#pragma unroll
+            for (int hh = 0; hh < 2; hh++) {
+                const int p = pm0 + g + hh * 8;
+                if (p < P)
+#pragma unroll
+                    for (int nt = 0; nt < NT; nt++) {
+                        dst0[(size_t)p * DK + nt * 8 + 2 * t] = dr[nt][2 * hh];
+                        dst0[(size_t)p * DK + nt * 8 + 2 * t + 1] = dr[nt][2 * hh + 1];
+                    }
+            }
+        }
+    }
+}
+
+inline bool supported(const AttnArgs &a, bool backward)
+{
+    if (!(a.dk == 16 || a.dk == 32 || a.dk == 64 || a.dk == 128))
+        return false;
+    if (backward && a.T > 64)
+        return false;
+    size_t smem = 0;
+    switch (a.dk) {
+    case 16: smem = backward ? bwd_smem<16>(a.L, a.P) : fwd_smem<16>(a.L, a.P); break;
+    case 32: smem = backward ? bwd_smem<32>(a.L, a.P) : fwd_smem<32>(a.L, a.P); break;
+    case 64: smem = backward ? bwd_smem<64>(a.L, a.P) : fwd_smem<64>(a.L, a.P); break;
+    default: smem = backward ? bwd_smem<128>(a.L, a.P) : fwd_smem<128>(a.L, a.P); break;
+    }
+    return smem <= 227 * 1024;
+}
+
+template <int DK>
+static int launch_fwd(const AttnArgs &a, cudaStream_t st)
+{
+    size_t smem = fwd_smem<DK>(a.L, a.P);
+    static size_t attr = 0;
+    if (smem > attr) {
+        CUDA_TRY(cudaFuncSetAttribute(attn_fwd_mma_kernel<DK>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        attr = smem;
+    }
+    const int first_tile = a.t0 / 16, last_tile = (a.t1 - 1) / 16;
+    const int groups = (last_tile - first_tile) / 4 + 1;
+    attn_fwd_mma_kernel<DK><<<dim3(a.B * a.H, groups), 128, smem, st>>>(a);
+    KERNEL_CHECK();
+    return NNCU_OK;
+}
+
+template <int DK>
+static int launch_bwd(const AttnArgs &a, cudaStream_t st)
+{
+    size_t smem = bwd_smem<DK>(a.L, a.P);
+    static size_t attr = 0;
+    if (smem > attr) {
+        CUDA_TRY(cudaFuncSetAttribute(attn_bwd_mma_kernel<DK>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        attr = smem;
+    }
+    attn_bwd_mma_kernel<DK><<<a.B * a.H, 128, smem, st>>>(a);
+    KERNEL_CHECK();
+    return NNCU_OK;
+}
+
+static int forward(const AttnArgs &a, cudaStream_t st)
+{
+    switch (a.dk) {
+    case 16: return launch_fwd<16>(a, st);
+    case 32: return launch_fwd<32>(a, st);
+    case 64: return launch_fwd<64>(a, st);
+    default: return launch_fwd<128>(a, st);
+    }
+}
+static int backward(const AttnArgs &a, cudaStream_t st)
+{
+    switch (a.dk) {
+    case 16: return launch_bwd<16>(a, st);
+    case 32: return launch_bwd<32>(a, st);
+    case 64: return launch_bwd<64>(a, st);
+    default: return launch_bwd<128>(a, st);
+    }
+}
+
+} // namespace amma
+
+// ---- dispatch: bf16 goes to the tensor-core kernels when the shape allows, everything
+// else to the CUDA-core kernels of attention.cuh.  The choice depends on the shape only,
+// never on the query range, so one-symbol steps and whole segments take the same path.
+static bool attn_force_simt()
+{
+    static int v = -1;
+    if (v < 0) {
+        const char *e = getenv("NNCU_ATTN_SIMT");
+        v = (e && e[0] == '1') ? 1 : 0;
+    }
+    return v == 1;
+}
+
+template <typename T>
+static int attn_forward_any(const nncu_attn_shape *s, const void *q, const void *kv, const float *w_r,
+                            const float *b_r, void *out, float *lse, cudaStream_t st)
+{
+    if (sizeof(T) == 2 && !attn_force_simt()) {
+        AttnArgs a = attn_args(s);
+        a.q = q; a.kv = kv; a.w_r = w_r; a.b_r = b_r; a.o = out; a.lse = lse;
+        if (amma::supported(a, false))
+            return amma::forward(a, st);
+    }
+    return attn_forward_t<T>(s, q, kv, w_r, b_r, out, lse, st);
+}
+
+template <typename T>
+static int attn_backward_any(const nncu_attn_shape *s, const void *q, const void *kv, const float *w_r,
+                             const float *b_r, const void *out, const float *lse, const void *dout,
+                             void *dq, void *dkv, float *dwr_part, float *dbr_part, cudaStream_t st)
+{
+    if (sizeof(T) == 2 && !attn_force_simt()) {
+        AttnArgs a = attn_args(s);
+        if (a.t0 == 0 && a.t1 == a.T) {
+            a.q = q; a.kv = kv; a.w_r = w_r; a.b_r = b_r; a.out = out; a.lse = const_cast<float *>(lse);
+            a.dout = dout; a.dq = dq; a.dkv = dkv; a.dwr_part = dwr_part; a.dbr_part = dbr_part;
+            if (amma::supported(a, true))
+                return amma::backward(a, st);
+        }
+    }
+    return attn_backward_t<T>(s, q, kv, w_r, b_r, out, lse, dout, dq, dkv, dwr_part, dbr_part, st);
+}

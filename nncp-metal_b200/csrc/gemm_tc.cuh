@@ -444,11 +444,13 @@ static int gemm_nt(cudaStream_t st, int M, int N, int K, const bf16 *A, long lda
         return NNCU_OK;
     if (!usable(A, lda, B, ldb, K))
         return nncu_fail(NNCU_ERR_INVALID, "tcgen05 GEMM needs 16-byte aligned operands and strides");
-    // wide tiles once there are enough of them to fill the 148 SMs
-    long wide_tiles = (long)ceil_div(M, BM) * ceil_div(N, 256);
-    if (wide_tiles >= 120)
+    // the widest tile that still gives enough CTAs to fill the 148 SMs
+    const long mt = ceil_div(M, BM);
+    if (mt * ceil_div(N, 256) >= 120)
         return launch<256, TC>(st, M, N, K, A, lda, B, ldb, C, ldc, bias, addsrc, err_flag);
-    return launch<128, TC>(st, M, N, K, A, lda, B, ldb, C, ldc, bias, addsrc, err_flag);
+    if (mt * ceil_div(N, 128) >= 120 || N <= 64)
+        return launch<128, TC>(st, M, N, K, A, lda, B, ldb, C, ldc, bias, addsrc, err_flag);
+    return launch<64, TC>(st, M, N, K, A, lda, B, ldb, C, ldc, bias, addsrc, err_flag);
 }
 
 } // namespace tc

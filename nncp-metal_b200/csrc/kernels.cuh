@@ -354,25 +354,58 @@ __global__ void f32_to_bf16_kernel(const float *__restrict__ src, bf16 *__restri
 }
 
 // ------------------------------------------------------------------
-// dense embedding gradient: g[v][:] = mult * sum over rows r with id[r]==v (in row order)
-// of dx[r][:].  One block per symbol; every row of g is written (zeros included).
+// dense embedding gradient (adjoint of nc_get_col): g[v][:] = mult * sum over rows r with
+// id[r]==v, in ascending r, of dx[r][:].  g must be zero on entry.  One block per row; the
+// block of the FIRST row carrying a symbol lists the rows of that symbol (ordered compaction
+// by warp ballots) and sums them, the others leave.
 template <typename T>
 __global__ void __launch_bounds__(128)
 embed_grad_kernel(const int32_t *__restrict__ ids, const T *__restrict__ dx,
                   float *__restrict__ g, int rows, int D, float mult, int V)
 {
-    extern __shared__ int32_t sids[];
-    const int v = blockIdx.x;
+    extern __shared__ int32_t sm_i[]; // sids[rows], list[rows]
+    int32_t *sids = sm_i, *list = sm_i + rows;
+    __shared__ int seen_before, wcnt[4], count;
+    const int r0 = blockIdx.x;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) {
+        seen_before = 0;
+        count = 0;
+    }
     for (int i = threadIdx.x; i < rows; i += blockDim.x) {
         int id = ids[i];
         sids[i] = id < 0 ? 0 : (id >= V ? V - 1 : id);
     }
     __syncthreads();
+    const int v = sids[r0];
+    for (int i = threadIdx.x; i < r0; i += blockDim.x)
+        if (sids[i] == v)
+            seen_before = 1; // benign race: every writer stores the same value
+    __syncthreads();
+    if (seen_before)
+        return;
+    for (int base = r0; base < rows; base += 128) {
+        const int r = base + threadIdx.x;
+        const bool hit = r < rows && sids[r] == v;
+        const unsigned bal = __ballot_sync(0xffffffffu, hit);
+        if (lane == 0)
+            wcnt[warp] = __popc(bal);
+        __syncthreads();
+        int pos = count;
+        for (int w = 0; w < warp; w++)
+            pos += wcnt[w];
+        if (hit)
+            list[pos + __popc(bal & ((1u << lane) - 1u))] = r;
+        __syncthreads();
+        if (threadIdx.x == 0)
+            count += wcnt[0] + wcnt[1] + wcnt[2] + wcnt[3];
+        __syncthreads();
+    }
+    const int n = count;
     for (int c = threadIdx.x; c < D; c += blockDim.x) {
         float s = 0.0f;
-        for (int r = 0; r < rows; r++)
-            if (sids[r] == v)
-                s += to_f(dx[(size_t)r * D + c]);
+        for (int k = 0; k < n; k++)
+            s += to_f(dx[(size_t)list[k] * D + c]);
         g[(size_t)v * D + c] = s * mult;
     }
 }

@@ -27,7 +27,7 @@
 #include <string>
 #include <vector>
 
-#include "attention.cuh"
+#include "attention_mma.cuh"
 #include "coder.cuh"
 #include "common.cuh"
 #include "gemm_simt.cuh"
@@ -242,7 +242,7 @@ template <typename AT>
 static int norm_bwd(nncu_model *m, const AT *dy, const AT *x, size_t g_off, size_t b_off,
                     const float *stats, const AT *base, AT *dx, int rows)
 {
-    const int rpb = 32;
+    const int rpb = 8;
     int blocks = ceil_div(rows, rpb);
     int mode = (m->p.ln_flags & NNCU_LN_RMSNORM) ? 2 : 1;
     size_t smem = (size_t)8 * 2 * m->D * sizeof(float);
@@ -301,7 +301,7 @@ static int forward_range(nncu_model *m, int t0, int t1)
             NNCU_TRY((mm_nt<AT, AT>(m, nr, 2 * HD, D, x1, D, o.w_kv,
                                     at<AT>(a.kv, ((size_t)M * B + r0) * 2 * HD), 2 * HD, nullptr)));
         nncu_attn_shape s = attn_shape(m, l, t0, t1);
-        NNCU_TRY(attn_forward_t<AT>(&s, a.q, a.kv, wf(m, o.w_r), m->W + o.b_r, a.o, a.lse, m->st));
+        NNCU_TRY(attn_forward_any<AT>(&s, a.q, a.kv, wf(m, o.w_r), m->W + o.b_r, a.o, a.lse, m->st));
         // output projection, residual, post-LN (nncp.c:865-920)
         NNCU_TRY((mm_nt<AT, AT>(m, nr, D, HD, at<AT>(a.o, (size_t)r0 * HD), HD, o.w_o, tmp, D, nullptr)));
         AT *yy = at<AT>(a.y, (size_t)r0 * D);
@@ -426,7 +426,7 @@ static int backward(nncu_model *m)
         NNCU_TRY(mm_tn(m, D, HD, TB, ds1, D, atc<AT>(a.o, 0), HD, gf(m, o.w_o)));
         NNCU_TRY(mm_nn(m, TB, HD, D, ds1, D, o.w_o, dof, HD, (const AT *)nullptr));
         nncu_attn_shape s = attn_shape(m, l, 0, m->T);
-        NNCU_TRY(attn_backward_t<AT>(&s, a.q, a.kv, wf(m, o.w_r), m->W + o.b_r, a.o, a.lse, dof, dq, dkv,
+        NNCU_TRY(attn_backward_any<AT>(&s, a.q, a.kv, wf(m, o.w_r), m->W + o.b_r, a.o, a.lse, dof, dq, dkv,
                                      m->dwr_part, m->dbr_part, m->st));
         {
             size_t nb = (size_t)m->H * m->L;
@@ -459,7 +459,8 @@ static int backward(nncu_model *m)
         dx = dxn;
     }
     const float emul = sqrtf((float)D) * p.embed_mult;
-    embed_grad_kernel<AT><<<V, 128, sizeof(int32_t) * TB, m->st>>>(m->ids_dev, dx, gf(m, m->embed), TB, D, emul, V);
+    CUDA_TRY(cudaMemsetAsync(gf(m, m->embed), 0, sizeof(float) * (size_t)V * D, m->st));
+    embed_grad_kernel<AT><<<TB, 128, 2 * sizeof(int32_t) * TB, m->st>>>(m->ids_dev, dx, gf(m, m->embed), TB, D, emul, V);
     KERNEL_CHECK();
     return NNCU_OK;
 }
@@ -751,7 +752,7 @@ int nncu_create(const nncu_params *p, nncu_model **out)
     size_t max_k = (size_t)std::max(std::max(F, D), HD);
     size_t oTA = m->use_tc ? take(max_n * LB * 2) : 0, oTB = m->use_tc ? take(max_k * LB * 2) : 0;
     size_t oWr = take((size_t)m->B * m->H * p->d_pos * m->dk * 4), oBr = take((size_t)m->B * m->H * m->L * 4);
-    size_t part_floats = std::max((size_t)ceil_div(LB, 64) * max_n, (size_t)ceil_div(TB, 32) * 2 * D);
+    size_t part_floats = std::max((size_t)ceil_div(LB, 64) * max_n, (size_t)ceil_div(TB, 8) * 2 * D);
     size_t oPart = take(part_floats * 4);
     size_t oLogp = take((size_t)TB * 4), oLoss = take(256);
     size_t oIds = take((size_t)TB * 4), oTgt = take((size_t)TB * 4), oErr = take(256), oHash = take(256);
@@ -825,9 +826,9 @@ int nncu_create(const nncu_params *p, nncu_model **out)
         cudaFuncSetAttribute(coder_paths_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 2 * V * 4);
         cudaFuncSetAttribute(coder_trees_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 2 * V * 4);
     }
-    if (sizeof(int32_t) * TB > 48 * 1024) {
-        cudaFuncSetAttribute(embed_grad_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(int32_t) * TB);
-        cudaFuncSetAttribute(embed_grad_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(int32_t) * TB);
+    if (2 * sizeof(int32_t) * TB > 48 * 1024) {
+        cudaFuncSetAttribute(embed_grad_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 2 * (int)sizeof(int32_t) * TB);
+        cudaFuncSetAttribute(embed_grad_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 2 * (int)sizeof(int32_t) * TB);
     }
 
     // ---- initial values (trf_init, nncp.c:341-497), computed on the host
@@ -1237,8 +1238,8 @@ int nncu_attention_forward(const nncu_attn_shape *s, const void *q, const void *
     if (!q || !kv || !b_r || !out)
         return nncu_fail(NNCU_ERR_INVALID, "null tensor");
     cudaStream_t st = (cudaStream_t)cuda_stream;
-    return s->dtype_bf16 ? attn_forward_t<bf16>(s, q, kv, w_r, b_r, out, lse, st)
-                         : attn_forward_t<float>(s, q, kv, w_r, b_r, out, lse, st);
+    return s->dtype_bf16 ? attn_forward_any<bf16>(s, q, kv, w_r, b_r, out, lse, st)
+                         : attn_forward_any<float>(s, q, kv, w_r, b_r, out, lse, st);
 }
 
 int nncu_attention_backward(const nncu_attn_shape *s, const void *q, const void *kv, const float *w_r,
@@ -1250,8 +1251,8 @@ int nncu_attention_backward(const nncu_attn_shape *s, const void *q, const void 
         return nncu_fail(NNCU_ERR_INVALID, "null tensor");
     cudaStream_t st = (cudaStream_t)cuda_stream;
     return s->dtype_bf16
-               ? attn_backward_t<bf16>(s, q, kv, w_r, b_r, out, lse, dout, dq, dkv, dwr_part, dbr_part, st)
-               : attn_backward_t<float>(s, q, kv, w_r, b_r, out, lse, dout, dq, dkv, dwr_part, dbr_part, st);
+               ? attn_backward_any<bf16>(s, q, kv, w_r, b_r, out, lse, dout, dq, dkv, dwr_part, dbr_part, st)
+               : attn_backward_any<float>(s, q, kv, w_r, b_r, out, lse, dout, dq, dkv, dwr_part, dbr_part, st);
 }
 
 int nncu_attention_reduce_tables(const nncu_attn_shape *s, const float *dwr_part, const float *dbr_part,

@@ -40,6 +40,13 @@ CONFIGS = {
     "short_mem_window": dict(mem_len=2, d_pos=5, seg_len=6,
                              attn_len=[3, 5] + [0] * 30, n_streams=3),
     "no_w_r_noln_clip": dict(use_w_r=0, ln_flags=0, gradient_clip=0.05, n_symbols=24),
+    # head sizes that are multiples of 16: the bf16 model takes the tensor-core attention path
+    "mma_dk16": dict(n_layer=2, d_model=32, n_head=2, d_key=16, d_inner=64, d_pos=9, mem_len=6,
+                     seg_len=6, n_streams=3, n_symbols=32),
+    "mma_two_key_blocks": dict(n_layer=2, d_model=64, n_head=2, d_key=32, d_inner=64, d_pos=50,
+                               mem_len=70, seg_len=20, n_streams=2, n_symbols=32,
+                               attn_len=[60, 0] + [0] * 30, ln_flags=tt.LN_PRE | tt.LN_FINAL,
+                               wscale=0.1),
     "c0_like": dict(n_layer=2, d_model=32, n_head=4, d_key=8, d_inner=64, d_pos=16,
                     mem_len=8, seg_len=8, n_streams=4, n_symbols=32),
 }
@@ -49,6 +56,7 @@ STEPS = 2
 def make(name, over, out_dir):
     c = dict(BASE)
     c.update(over)
+    wscale = c.pop("wscale", 0.25)
     c["d_value"] = c["d_key"]
     if c["d_pos"] > c["mem_len"] + c["seg_len"]:
         raise ValueError("d_pos > L")
@@ -62,7 +70,7 @@ def make(name, over, out_dir):
         elif pname.startswith("b_r"):
             t = 0.02 * torch.randn(shape, generator=gen, dtype=torch.float64)
         else:
-            t = 0.25 * torch.randn(shape, generator=gen, dtype=torch.float64)
+            t = wscale * torch.randn(shape, generator=gen, dtype=torch.float64)
         # keep exactly-representable fp32 starting values
         params[pname] = t.float().double()
         moments[pname] = torch.zeros(shape, dtype=torch.float64)
