@@ -7,3 +7,4 @@ tests and the benchmark use to reach that ABI.
 from . import abi  # noqa: F401
 from .loader import library, build_library, LibraryMissing  # noqa: F401
 from .model import TrfModel  # noqa: F401
+from . import host  # noqa: F401

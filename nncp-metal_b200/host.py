@@ -1,0 +1,177 @@
+"""ctypes view of include/nncp_host.h (libnncp_host.so): coder, stream layout, schedule,
+container header and the block loop, with the CUDA model bound through nch_bind_cuda."""
+import ctypes as C
+import os
+
+import numpy as np
+
+from . import abi
+from .loader import HOSTLIB, LIB, LibraryMissing
+
+INTERP_MAX_STEPS = 8
+EVAL_STEP, EVAL_SEGMENT = 0, 1
+OUT_FLOAT, OUT_CODER_READY = 0, 1
+_vp = C.c_void_p
+
+
+class InterpParams(C.Structure):
+    _fields_ = [("n_steps", C.c_int32), ("val", C.c_float * (INTERP_MAX_STEPS + 1)),
+                ("pos", C.c_int64 * INTERP_MAX_STEPS), ("decay_power", C.c_float)]
+
+    @staticmethod
+    def make(vals, pos=(), decay_power=0.0):
+        p = InterpParams()
+        p.n_steps = len(pos)
+        for i, v in enumerate(vals):
+            p.val[i] = v
+        for i, v in enumerate(pos):
+            p.pos[i] = v
+        p.decay_power = decay_power
+        return p
+
+
+class FileParams(C.Structure):
+    _fields_ = [("model", abi.Params), ("lr", InterpParams), ("block_len", InterpParams)]
+
+
+class BlockStats(C.Structure):
+    _fields_ = [("n_symbols", C.c_int64), ("train_steps", C.c_int64), ("sum_log2", C.c_double)]
+
+
+_I = C.c_int
+FN_CTX = C.CFUNCTYPE(_I, _vp)
+FN_SET_LR = C.CFUNCTYPE(_I, _vp, C.c_float)
+FN_EVAL = C.CFUNCTYPE(_I, _vp, _I, C.POINTER(C.c_int32))
+FN_PROBS = C.CFUNCTYPE(_I, _vp, _I, _I, C.POINTER(C.c_float))
+FN_PATHS = C.CFUNCTYPE(_I, _vp, _I, _I, C.POINTER(C.c_int32), C.POINTER(C.c_uint16), C.POINTER(_I))
+FN_TREES = C.CFUNCTYPE(_I, _vp, _I, _I, C.POINTER(C.c_uint16))
+FN_GRAD = C.CFUNCTYPE(_I, _vp, C.POINTER(C.c_int32), C.POINTER(C.c_float))
+
+
+class ModelOps(C.Structure):
+    _fields_ = [("ctx", _vp), ("n_streams", _I), ("seg_len", _I), ("n_symbols", _I),
+                ("reset", FN_CTX), ("set_lr", FN_SET_LR), ("eval", FN_EVAL), ("read_probs", FN_PROBS),
+                ("coder_paths", FN_PATHS), ("coder_trees", FN_TREES), ("eval_end", FN_CTX),
+                ("eval_gradient", FN_GRAD), ("update", FN_CTX)]
+
+
+_lib = None
+
+
+def library():
+    global _lib
+    if _lib is None:
+        if not os.path.exists(HOSTLIB):
+            raise LibraryMissing(f"{HOSTLIB} is not built; run __graft_entry__.build()")
+        L = C.CDLL(HOSTLIB)
+        L.nch_enc_new.restype = _vp
+        L.nch_enc_put_bit.argtypes = [_vp, _I, _I]
+        L.nch_enc_put_bit.restype = None
+        L.nch_enc_finish.argtypes = [_vp, C.POINTER(_vp)]
+        L.nch_enc_finish.restype = C.c_size_t
+        L.nch_enc_bytes.argtypes = [_vp]
+        L.nch_enc_bytes.restype = C.c_size_t
+        L.nch_enc_free.argtypes = [_vp]
+        L.nch_enc_free.restype = None
+        L.nch_dec_new.argtypes = [_vp, C.c_size_t]
+        L.nch_dec_new.restype = _vp
+        L.nch_dec_get_bit.argtypes = [_vp, _I]
+        L.nch_dec_free.argtypes = [_vp]
+        L.nch_dec_free.restype = None
+        L.nch_vec_sum_f32.argtypes = [_vp, C.c_size_t]
+        L.nch_vec_sum_f32.restype = C.c_float
+        L.nch_write_sym.argtypes = [_vp, _vp, _I, _I]
+        L.nch_write_sym.restype = None
+        L.nch_read_sym.argtypes = [_vp, _vp, _I]
+        L.nch_write_sym_path.argtypes = [_vp, _vp, _I, _I]
+        L.nch_write_sym_path.restype = None
+        L.nch_read_sym_tree.argtypes = [_vp, _vp, _I]
+        L.nch_interp.argtypes = [C.POINTER(InterpParams), C.c_int64]
+        L.nch_interp.restype = C.c_float
+        L.nch_get_symb.argtypes = [_vp, _I, _I, _I, _I]
+        L.nch_put_symb.argtypes = [_vp, _I, _I, _I, _I, _I]
+        L.nch_bind_cuda.argtypes = [C.c_char_p, C.POINTER(abi.Params), C.POINTER(ModelOps)]
+        L.nch_unbind_cuda.argtypes = [C.POINTER(ModelOps)]
+        L.nch_unbind_cuda.restype = None
+        L.nch_process_block.argtypes = [C.POINTER(ModelOps), _vp, _vp, _vp, _I, C.POINTER(InterpParams),
+                                        C.POINTER(C.c_int64), _I, _I, C.POINTER(BlockStats)]
+        L.nch_write_header.argtypes = [C.POINTER(FileParams), C.c_uint32, _vp, C.c_size_t,
+                                       C.POINTER(C.c_size_t)]
+        L.nch_read_header.argtypes = [_vp, C.c_size_t, C.POINTER(FileParams), C.POINTER(C.c_uint32),
+                                      C.POINTER(C.c_size_t)]
+        L.nch_compress.argtypes = [C.POINTER(ModelOps), C.POINTER(FileParams), _vp, C.c_size_t, _I, _I,
+                                   C.POINTER(_vp), C.POINTER(C.c_size_t), C.POINTER(BlockStats)]
+        L.nch_decompress.argtypes = [C.POINTER(ModelOps), C.POINTER(FileParams), _vp, C.c_size_t,
+                                     C.c_uint32, _I, _vp]
+        L.nch_free.argtypes = [_vp]
+        L.nch_free.restype = None
+        _lib = L
+    return _lib
+
+
+def file_params(model_params, lr=None, block_len=500000):
+    fp = FileParams()
+    fp.model = model_params
+    fp.lr = lr if lr is not None else InterpParams.make([model_params.lr])
+    fp.block_len = InterpParams.make([float(block_len)])
+    return fp
+
+
+def header_bytes(fp, n_symbols):
+    L = library()
+    n = C.c_size_t()
+    L.nch_write_header(C.byref(fp), n_symbols, None, 0, C.byref(n))
+    buf = C.create_string_buffer(n.value)
+    assert L.nch_write_header(C.byref(fp), n_symbols, buf, n.value, C.byref(n)) == 0
+    return buf.raw[: n.value]
+
+
+def read_header(data):
+    L = library()
+    fp, nsym, used = FileParams(), C.c_uint32(), C.c_size_t()
+    buf = C.create_string_buffer(data, len(data))
+    rc = L.nch_read_header(buf, len(data), C.byref(fp), C.byref(nsym), C.byref(used))
+    if rc != 0:
+        raise ValueError(f"bad header: {rc}")
+    return fp, nsym.value, used.value
+
+
+def compress(ops, fp, symbols, eval_mode=EVAL_SEGMENT, out_mode=OUT_CODER_READY):
+    """encode_file on memory: returns (bytes, BlockStats)."""
+    L = library()
+    s = np.ascontiguousarray(symbols, np.uint16)
+    out, n, st = _vp(), C.c_size_t(), BlockStats()
+    rc = L.nch_compress(C.byref(ops), C.byref(fp), s.ctypes.data_as(_vp), s.size, eval_mode, out_mode,
+                        C.byref(out), C.byref(n), C.byref(st))
+    if rc != 0:
+        raise RuntimeError(f"nch_compress: {rc}")
+    data = C.string_at(out.value, n.value)
+    L.nch_free(out)
+    return data, st
+
+
+def decompress(ops, data, out_mode=OUT_CODER_READY):
+    """decode_file on memory: returns the uint16 symbols."""
+    L = library()
+    fp, nsym, used = read_header(data)
+    payload = data[used:]
+    buf = C.create_string_buffer(payload, len(payload))
+    out = np.zeros(nsym, np.uint16)
+    rc = L.nch_decompress(C.byref(ops), C.byref(fp), buf, len(payload), nsym, out_mode,
+                          out.ctypes.data_as(_vp))
+    if rc != 0:
+        raise RuntimeError(f"nch_decompress: {rc}")
+    return out
+
+
+def bind_cuda(model_params):
+    L = library()
+    ops = ModelOps()
+    rc = L.nch_bind_cuda(LIB.encode(), C.byref(model_params), C.byref(ops))
+    if rc != 0:
+        raise LibraryMissing(f"nch_bind_cuda failed ({rc}): no CUDA model, and no other implementation")
+    return ops
+
+
+def unbind_cuda(ops):
+    library().nch_unbind_cuda(C.byref(ops))

@@ -1,0 +1,500 @@
+/*
+ * stream.c -- stream layout, learning-rate schedule, container header and the block loop.
+ *
+ *   nch_get_symb / nch_put_symb   nncp.c:2945-2965
+ *   nch_interp                    cp_utils.c:380-410
+ *   nch_process_block             nncp.c:2968-3147
+ *   header                        nncp.c:2662-2690 (file), 1297-1365 (schedules, model)
+ *   nch_compress / nch_decompress nncp.c:3414-3475, 3508-3677 (block sizing and loop)
+ */
+#include <math.h>
+#include <stdlib.h>
+#include <string.h>
+
+#include "nncp_host.h"
+
+int nch_get_symb(const uint16_t *buf, int stride, int rem, int stream_idx, int pos)
+{
+    int len = stride + (stream_idx < rem);
+    if (pos < 0 || pos >= len)
+        return 0;
+    return buf[(size_t)stride * stream_idx + (stream_idx < rem ? stream_idx : rem) + pos];
+}
+
+int nch_put_symb(uint16_t *buf, int stride, int rem, int stream_idx, int pos, int c)
+{
+    int len = stride + (stream_idx < rem);
+    if (pos < 0 || pos >= len)
+        return NCH_ERR_INVALID;
+    buf[(size_t)stride * stream_idx + (stream_idx < rem ? stream_idx : rem) + pos] = (uint16_t)c;
+    return NCH_OK;
+}
+
+float nch_interp(const nch_interp_params *p, int64_t pos)
+{
+    for (int i = 0; i < p->n_steps; i++) {
+        if (pos < p->pos[i]) {
+            int64_t from = i ? p->pos[i - 1] : 0;
+            float t = (float)(pos - from) / (float)(p->pos[i] - from);
+            return p->val[i] + t * (p->val[i + 1] - p->val[i]);
+        }
+    }
+    float last = p->val[p->n_steps];
+    if (p->decay_power == 0.0f || p->n_steps == 0)
+        return last;
+    float x = (float)pos / (float)p->pos[p->n_steps - 1];
+    if (p->decay_power == 0.5f)
+        return last / sqrtf(x); /* independent of pow() rounding, as the reference */
+    return (float)(last * pow(x, -p->decay_power));
+}
+
+/* ------------------------------------------------------------------ block loop */
+
+typedef struct {
+    const nch_model_ops *m;
+    nch_enc *enc;
+    nch_dec *dec;
+    int out_mode, n_bits;
+    float *probs;      /* [rows][V]   (float mode) */
+    uint16_t *coded;   /* paths [rows][n_bits] or trees [rows][V] */
+    int32_t *syms;     /* [rows] */
+} coder_io;
+
+static int log2_exact(int v)
+{
+    int n = 0;
+    while ((1 << n) < v)
+        n++;
+    return (1 << n) == v ? n : -1;
+}
+
+/* codes (or decodes) rows [t0, t0+nt) x streams; `limit_t`/`limit_b`: positions at
+   t == limit_t with stream >= limit_b, and all t > limit_t, are skipped (block tail). */
+static int code_rows(coder_io *io, uint16_t *buf, int stride, int rem, int base_pos, int t0, int nt,
+                     int limit_t, int limit_b, int32_t *expected)
+{
+    const nch_model_ops *m = io->m;
+    const int B = m->n_streams, V = m->n_symbols;
+    if (io->enc) {
+        for (int t = 0; t < nt; t++)
+            for (int b = 0; b < B; b++)
+                io->syms[t * B + b] = nch_get_symb(buf, stride, rem, b, base_pos + t0 + t);
+        if (io->out_mode == NCH_OUT_CODER_READY) {
+            int nb = 0;
+            if (m->coder_paths(m->ctx, t0, nt, io->syms, io->coded, &nb))
+                return NCH_ERR_MODEL;
+            io->n_bits = nb;
+        } else if (m->read_probs(m->ctx, t0, nt, io->probs)) {
+            return NCH_ERR_MODEL;
+        }
+        for (int t = 0; t < nt; t++)
+            for (int b = 0; b < B; b++) {
+                int tt = t0 + t, c = io->syms[t * B + b];
+                if (tt < limit_t || (tt == limit_t && b < limit_b)) {
+                    if (io->out_mode == NCH_OUT_CODER_READY)
+                        nch_write_sym_path(io->enc, io->coded + (size_t)(t * B + b) * io->n_bits, io->n_bits, c);
+                    else
+                        nch_write_sym(io->enc, io->probs + (size_t)(t * B + b) * V, V, c);
+                }
+                if (expected)
+                    expected[tt * B + b] = c;
+            }
+    } else {
+        if (io->out_mode == NCH_OUT_CODER_READY) {
+            if (m->coder_trees(m->ctx, t0, nt, io->coded))
+                return NCH_ERR_MODEL;
+        } else if (m->read_probs(m->ctx, t0, nt, io->probs)) {
+            return NCH_ERR_MODEL;
+        }
+        for (int t = 0; t < nt; t++)
+            for (int b = 0; b < B; b++) {
+                int tt = t0 + t, c = 0;
+                if (tt < limit_t || (tt == limit_t && b < limit_b)) {
+                    if (io->out_mode == NCH_OUT_CODER_READY)
+                        c = nch_read_sym_tree(io->dec, io->coded + (size_t)(t * B + b) * V, V);
+                    else
+                        c = nch_read_sym(io->dec, io->probs + (size_t)(t * B + b) * V, V);
+                    nch_put_symb(buf, stride, rem, b, base_pos + tt, c);
+                }
+                if (expected)
+                    expected[tt * B + b] = c;
+            }
+    }
+    return NCH_OK;
+}
+
+int nch_process_block(const nch_model_ops *m, nch_enc *enc, nch_dec *dec, uint16_t *block_buf,
+                      int block_len, const nch_interp_params *lr, int64_t *train_step, int eval_mode,
+                      int out_mode, nch_block_stats *stats)
+{
+    if (!m || (!enc) == (!dec) || !block_buf || block_len < 0 || !lr || !train_step)
+        return NCH_ERR_INVALID;
+    const int B = m->n_streams, T = m->seg_len, V = m->n_symbols;
+    if (dec)
+        eval_mode = NCH_EVAL_STEP; /* the next input is the symbol just decoded */
+    if (out_mode == NCH_OUT_CODER_READY && (log2_exact(V) < 1 || !m->coder_paths || !m->coder_trees))
+        out_mode = NCH_OUT_FLOAT;
+    const int stride = block_len / B, rem = block_len % B;
+    coder_io io;
+    memset(&io, 0, sizeof(io));
+    io.m = m; io.enc = enc; io.dec = dec; io.out_mode = out_mode;
+    const int rows = (eval_mode == NCH_EVAL_SEGMENT ? T : 1) * B;
+    int32_t *input = (int32_t *)calloc((size_t)T * B, sizeof(int32_t));
+    int32_t *expected = (int32_t *)calloc((size_t)T * B, sizeof(int32_t));
+    io.syms = (int32_t *)calloc((size_t)rows, sizeof(int32_t));
+    if (out_mode == NCH_OUT_CODER_READY)
+        io.coded = (uint16_t *)malloc(sizeof(uint16_t) * (size_t)rows * (enc ? 32 : V));
+    else
+        io.probs = (float *)malloc(sizeof(float) * (size_t)rows * V);
+    int rc = NCH_OK;
+    if (!input || !expected || !io.syms || (!io.coded && !io.probs)) {
+        rc = NCH_ERR_NOMEM;
+        goto done;
+    }
+    if (m->reset(m->ctx)) {
+        rc = NCH_ERR_MODEL;
+        goto done;
+    }
+    int pos = 0;
+    /* full segments: code, then train on what was coded */
+    while (pos + T <= stride) {
+        if (eval_mode == NCH_EVAL_SEGMENT) {
+            for (int t = 0; t < T; t++)
+                for (int b = 0; b < B; b++)
+                    input[t * B + b] = nch_get_symb(block_buf, stride, rem, b, pos + t - 1);
+            if (m->eval(m->ctx, -1, input)) { rc = NCH_ERR_MODEL; goto done; }
+            rc = code_rows(&io, block_buf, stride, rem, pos, 0, T, T, 0, expected);
+            if (rc) goto done;
+        } else {
+            for (int t = 0; t < T; t++) {
+                for (int b = 0; b < B; b++)
+                    input[t * B + b] = nch_get_symb(block_buf, stride, rem, b, pos + t - 1);
+                if (m->eval(m->ctx, t, input)) { rc = NCH_ERR_MODEL; goto done; }
+                rc = code_rows(&io, block_buf, stride, rem, pos, t, 1, T, 0, expected);
+                if (rc) goto done;
+            }
+        }
+        if (m->set_lr(m->ctx, nch_interp(lr, *train_step))) { rc = NCH_ERR_MODEL; goto done; }
+        float loss = 0.0f;
+        if (m->eval_gradient(m->ctx, expected, &loss) || m->update(m->ctx)) { rc = NCH_ERR_MODEL; goto done; }
+        (*train_step)++;
+        pos += T;
+        if (stats) {
+            stats->train_steps++;
+            stats->n_symbols += (int64_t)T * B;
+            stats->sum_log2 -= (double)loss / 0.6931471805599453;
+        }
+    }
+    /* tail: coded without training (nncp.c:3076-3143) */
+    {
+        const int tail2 = stride - pos, tail1 = tail2 + (rem != 0);
+        if (tail1 > 0) {
+            memset(input, 0, sizeof(int32_t) * (size_t)T * B);
+            if (eval_mode == NCH_EVAL_SEGMENT) {
+                for (int t = 0; t < tail1; t++)
+                    for (int b = 0; b < B; b++)
+                        input[t * B + b] = nch_get_symb(block_buf, stride, rem, b, pos + t - 1);
+                if (m->eval(m->ctx, -1, input)) { rc = NCH_ERR_MODEL; goto done; }
+                rc = code_rows(&io, block_buf, stride, rem, pos, 0, tail1, tail2, rem, NULL);
+                if (rc) goto done;
+            } else {
+                for (int t = 0; t < tail1; t++) {
+                    for (int b = 0; b < B; b++)
+                        input[t * B + b] = nch_get_symb(block_buf, stride, rem, b, pos + t - 1);
+                    if (m->eval(m->ctx, t, input)) { rc = NCH_ERR_MODEL; goto done; }
+                    rc = code_rows(&io, block_buf, stride, rem, pos, t, 1, tail2, rem, NULL);
+                    if (rc) goto done;
+                }
+            }
+            if (m->eval_end(m->ctx)) { rc = NCH_ERR_MODEL; goto done; }
+            if (stats)
+                stats->n_symbols += (int64_t)tail2 * B + rem;
+        }
+    }
+done:
+    free(input);
+    free(expected);
+    free(io.syms);
+    free(io.coded);
+    free(io.probs);
+    return rc;
+}
+
+/* ------------------------------------------------------------------ header */
+
+#define FILE_MAGIC 0xb727ac58u
+
+typedef struct {
+    uint8_t *p;
+    size_t len, cap;
+    int overflow;
+} wbuf;
+static void w8(wbuf *w, unsigned v)
+{
+    if (w->len < w->cap)
+        w->p[w->len] = (uint8_t)v;
+    else
+        w->overflow = 1;
+    w->len++;
+}
+static void w16(wbuf *w, unsigned v) { w8(w, v >> 8); w8(w, v); }
+static void w32(wbuf *w, uint32_t v) { w16(w, v >> 16); w16(w, v & 0xffff); }
+static void wf32(wbuf *w, float f) { uint32_t u; memcpy(&u, &f, 4); w32(w, u); }
+static void winterp(wbuf *w, const nch_interp_params *p)
+{
+    w8(w, p->n_steps);
+    for (int i = 0; i <= p->n_steps; i++)
+        wf32(w, p->val[i]);
+    for (int i = 0; i < p->n_steps; i++)
+        w32(w, (uint32_t)p->pos[i]);
+    wf32(w, p->decay_power);
+}
+
+typedef struct {
+    const uint8_t *p;
+    size_t len, pos;
+    int bad;
+} rbuf;
+static unsigned r8(rbuf *r)
+{
+    if (r->pos >= r->len) {
+        r->bad = 1;
+        return 0;
+    }
+    return r->p[r->pos++];
+}
+static unsigned r16(rbuf *r) { unsigned a = r8(r); return (a << 8) | r8(r); }
+static uint32_t r32(rbuf *r) { uint32_t a = r16(r); return (a << 16) | r16(r); }
+static float rf32(rbuf *r) { uint32_t u = r32(r); float f; memcpy(&f, &u, 4); return f; }
+static int rinterp(rbuf *r, nch_interp_params *p)
+{
+    memset(p, 0, sizeof(*p));
+    unsigned n = r8(r);
+    if (n > NCH_INTERP_MAX_STEPS)
+        return -1;
+    p->n_steps = (int)n;
+    for (unsigned i = 0; i <= n; i++)
+        p->val[i] = rf32(r);
+    for (unsigned i = 0; i < n; i++)
+        p->pos[i] = r32(r);
+    p->decay_power = rf32(r);
+    return 0;
+}
+
+/* Version 1 is the reference layout byte for byte.  Version 2 appends two bytes
+   (init_kind, bias_correction) for the build-defined options the reference has no field for. */
+int nch_write_header(const nch_file_params *fp, uint32_t n_symbols_in_file, uint8_t *out, size_t cap,
+                     size_t *len)
+{
+    if (!fp || !len)
+        return NCH_ERR_INVALID;
+    const nncu_params *m = &fp->model;
+    const int v2 = m->init_kind != NNCU_INIT_UNIFORM || m->bias_correction != 0;
+    wbuf w = {out, 0, out ? cap : 0, 0};
+    w32(&w, FILE_MAGIC);
+    w16(&w, v2 ? 2 : 1);
+    w8(&w, 1);                 /* use_cuda */
+    w8(&w, m->use_bf16);
+    w16(&w, m->n_streams);     /* batch_size */
+    w16(&w, m->seg_len);
+    w16(&w, m->n_symbols);
+    w32(&w, m->seed);
+    winterp(&w, &fp->lr);
+    winterp(&w, &fp->block_len);
+    w32(&w, 0);                /* retrain_period: no retrain pass */
+    w8(&w, 0);                 /* model_id of the Transformer class */
+    w8(&w, m->n_layer);
+    w8(&w, m->n_head);
+    w16(&w, m->d_key);
+    w16(&w, m->d_value);
+    w16(&w, m->d_inner);
+    w16(&w, m->d_pos);
+    w16(&w, m->mem_len);
+    for (int i = 0; i < m->n_layer; i++)
+        w16(&w, m->attn_len[i] ? m->attn_len[i] : m->mem_len + m->seg_len);
+    w8(&w, 0);                 /* tied_embed */
+    w8(&w, m->use_bias);
+    w8(&w, m->use_w_r);
+    w8(&w, m->tied_w_r);
+    w8(&w, m->tied_b_r);
+    w8(&w, m->query_bias);
+    w8(&w, 0);                 /* rotary_pos_embed */
+    w8(&w, m->ln_flags);
+    wf32(&w, m->init_range);
+    wf32(&w, m->embed_mult);
+    w8(&w, m->ff_act);
+    w8(&w, 1);                 /* SGD_OPT_ADAM, beta1 = 0: RMSProp */
+    wf32(&w, 0.0f);
+    wf32(&w, m->beta2);
+    wf32(&w, m->eps);
+    wf32(&w, m->gradient_clip);
+    w8(&w, 0);                 /* use_sparse_grad */
+    if (v2) {
+        w8(&w, m->init_kind);
+        w8(&w, m->bias_correction != 0);
+    }
+    w8(&w, 0);                 /* no preprocessing dictionary */
+    w32(&w, n_symbols_in_file);
+    *len = w.len;
+    return (out && w.overflow) ? NCH_ERR_INVALID : NCH_OK;
+}
+
+int nch_read_header(const uint8_t *in, size_t n, nch_file_params *fp, uint32_t *n_symbols_in_file,
+                    size_t *consumed)
+{
+    if (!in || !fp)
+        return NCH_ERR_INVALID;
+    rbuf r = {in, n, 0, 0};
+    memset(fp, 0, sizeof(*fp));
+    nncu_params *m = &fp->model;
+    if (r32(&r) != FILE_MAGIC)
+        return NCH_ERR_FORMAT;
+    unsigned ver = r16(&r);
+    if (ver != 1 && ver != 2)
+        return NCH_ERR_FORMAT;
+    r8(&r); /* use_cuda */
+    m->use_bf16 = (uint8_t)r8(&r);
+    m->n_streams = (int)r16(&r);
+    m->seg_len = (int)r16(&r);
+    m->n_symbols = (int)r16(&r);
+    m->seed = r32(&r);
+    if (rinterp(&r, &fp->lr) || rinterp(&r, &fp->block_len))
+        return NCH_ERR_FORMAT;
+    if (r32(&r) != 0)
+        return NCH_ERR_FORMAT; /* retrain is not supported */
+    if (r8(&r) != 0)
+        return NCH_ERR_FORMAT; /* not the Transformer class */
+    m->n_layer = (int)r8(&r);
+    m->n_head = (int)r8(&r);
+    m->d_key = (int)r16(&r);
+    m->d_value = (int)r16(&r);
+    m->d_inner = (int)r16(&r);
+    m->d_pos = (int)r16(&r);
+    m->mem_len = (int)r16(&r);
+    if (m->n_layer < 1 || m->n_layer > NNCU_N_LAYER_MAX)
+        return NCH_ERR_FORMAT;
+    for (int i = 0; i < m->n_layer; i++)
+        m->attn_len[i] = (int)r16(&r);
+    if (r8(&r) != 0)
+        return NCH_ERR_FORMAT; /* tied_embed */
+    m->use_bias = (uint8_t)r8(&r);
+    m->use_w_r = (uint8_t)r8(&r);
+    m->tied_w_r = (uint8_t)r8(&r);
+    m->tied_b_r = (uint8_t)r8(&r);
+    m->query_bias = (uint8_t)r8(&r);
+    if (r8(&r) != 0)
+        return NCH_ERR_FORMAT; /* rotary */
+    m->ln_flags = (uint8_t)r8(&r);
+    m->init_range = rf32(&r);
+    m->embed_mult = rf32(&r);
+    m->ff_act = (uint8_t)r8(&r);
+    if (r8(&r) != 1)
+        return NCH_ERR_FORMAT;
+    rf32(&r); /* beta1 */
+    m->beta2 = rf32(&r);
+    m->eps = rf32(&r);
+    m->gradient_clip = rf32(&r);
+    r8(&r); /* use_sparse_grad */
+    if (ver == 2) {
+        m->init_kind = (int)r8(&r);
+        m->bias_correction = (int)r8(&r);
+    }
+    if (r8(&r) != 0)
+        return NCH_ERR_FORMAT; /* preprocessing dictionary */
+    uint32_t nsym = r32(&r);
+    if (r.bad)
+        return NCH_ERR_FORMAT;
+    m->d_model = m->d_key * m->n_head; /* not stored (nncp.c:1383) */
+    m->n_streams_total = 0;
+    m->device = -1;
+    m->lr = fp->lr.val[0];
+    if (n_symbols_in_file)
+        *n_symbols_in_file = nsym;
+    if (consumed)
+        *consumed = r.pos;
+    return NCH_OK;
+}
+
+/* ------------------------------------------------------------------ file loops */
+
+static int next_block_len(const nch_file_params *fp, size_t file_pos, size_t remaining)
+{
+    const int unit = fp->model.seg_len * fp->model.n_streams;
+    long bl = lrintf(nch_interp(&fp->block_len, (int64_t)file_pos));
+    long k = bl / unit;
+    if (k < 1)
+        k = 1;
+    bl = k * unit;
+    if ((size_t)bl > remaining)
+        bl = (long)remaining;
+    return (int)bl;
+}
+
+void nch_free(void *p) { free(p); }
+
+int nch_compress(const nch_model_ops *m, const nch_file_params *fp, const uint16_t *symbols, size_t n,
+                 int eval_mode, int out_mode, uint8_t **out, size_t *out_len, nch_block_stats *stats)
+{
+    if (!m || !fp || (!symbols && n) || !out || !out_len)
+        return NCH_ERR_INVALID;
+    size_t hlen = 0;
+    nch_write_header(fp, (uint32_t)n, NULL, 0, &hlen);
+    nch_enc *enc = nch_enc_new();
+    if (!enc)
+        return NCH_ERR_NOMEM;
+    int rc = NCH_OK;
+    int64_t train_step = 0;
+    uint16_t *block = NULL;
+    size_t pos = 0;
+    while (pos < n) {
+        int bl = next_block_len(fp, pos, n - pos);
+        uint16_t *nb = (uint16_t *)realloc(block, sizeof(uint16_t) * (size_t)bl);
+        if (!nb) { rc = NCH_ERR_NOMEM; break; }
+        block = nb;
+        memcpy(block, symbols + pos, sizeof(uint16_t) * (size_t)bl);
+        rc = nch_process_block(m, enc, NULL, block, bl, &fp->lr, &train_step, eval_mode, out_mode, stats);
+        if (rc)
+            break;
+        pos += (size_t)bl;
+    }
+    free(block);
+    if (rc == NCH_OK) {
+        const uint8_t *payload = NULL;
+        size_t plen = nch_enc_finish(enc, &payload);
+        uint8_t *buf = (uint8_t *)malloc(hlen + plen + 1);
+        if (!buf) {
+            rc = NCH_ERR_NOMEM;
+        } else {
+            nch_write_header(fp, (uint32_t)n, buf, hlen, &hlen);
+            if (plen)
+                memcpy(buf + hlen, payload, plen);
+            *out = buf;
+            *out_len = hlen + plen;
+        }
+    }
+    nch_enc_free(enc);
+    return rc;
+}
+
+int nch_decompress(const nch_model_ops *m, const nch_file_params *fp, const uint8_t *payload, size_t n,
+                   uint32_t n_symbols_in_file, int out_mode, uint16_t *symbols_out)
+{
+    if (!m || !fp || (!payload && n) || (!symbols_out && n_symbols_in_file))
+        return NCH_ERR_INVALID;
+    nch_dec *dec = nch_dec_new(payload, n);
+    if (!dec)
+        return NCH_ERR_NOMEM;
+    int rc = NCH_OK;
+    int64_t train_step = 0;
+    size_t pos = 0, total = n_symbols_in_file;
+    while (pos < total) {
+        int bl = next_block_len(fp, pos, total - pos);
+        rc = nch_process_block(m, NULL, dec, symbols_out + pos, bl, &fp->lr, &train_step, NCH_EVAL_STEP,
+                               out_mode, NULL);
+        if (rc)
+            break;
+        pos += (size_t)bl;
+    }
+    nch_dec_free(dec);
+    return rc;
+}

@@ -1,0 +1,259 @@
+"""Host-side C code (libnncp_host.so) on the CPU: range coder and symbol coder against the
+reference's own sources (oracle/_ref) and the oracle, schedule, stream layout, container
+header, and the block loop driven by the CPU oracle as the model (test-only plumbing: the
+shipped binding, nch_bind_cuda, only ever binds the CUDA library)."""
+import ctypes as C
+import struct
+
+import numpy as np
+import pytest
+
+from conftest import load_golden, params_from_cfg
+from oracle import oracle as orc
+
+_vp = C.c_void_p
+needs_ref = pytest.mark.skipif(orc.ref_lib() is None, reason="oracle/_ref was never built")
+
+
+def _tables(rng, n, V, sharp):
+    z = rng.standard_normal((n, V)).astype(np.float32) * sharp
+    e = np.exp(z - z.max(1, keepdims=True))
+    return (e / e.sum(1, keepdims=True)).astype(np.float32)
+
+
+class HostEnc:
+    def __init__(self, L):
+        self.L, self.h = L, L.nch_enc_new()
+
+    def put_sym(self, p, s):
+        p = np.ascontiguousarray(p, np.float32)
+        self.L.nch_write_sym(self.h, p.ctypes.data_as(_vp), p.size, int(s))
+
+    def finish(self):
+        out = _vp()
+        n = self.L.nch_enc_finish(self.h, C.byref(out))
+        data = C.string_at(out.value, n) if n else b""
+        self.L.nch_enc_free(self.h)
+        return data
+
+
+@needs_ref
+@pytest.mark.parametrize("V,sharp", [(2, 1.0), (256, 3.0), (24, 2.0), (1000, 5.0), (16384, 6.0)])
+def test_host_coder_bytes_equal_reference(pkg, V, sharp):
+    L = pkg.host.library()
+    rng = np.random.default_rng(V + 1)
+    n = 400 if V <= 1000 else 30
+    probs = _tables(rng, n, V, sharp)
+    syms = rng.integers(0, V, n)
+    a, b = HostEnc(L), orc.Encoder(True)
+    for p, s in zip(probs, syms):
+        a.put_sym(p, s)
+        b.put_sym(p, s)
+    da = a.finish()
+    assert da == b.finish() and len(da) > 0
+    buf = C.create_string_buffer(da, len(da))
+    d = L.nch_dec_new(buf, len(da))
+    back = [L.nch_read_sym(d, np.ascontiguousarray(p).ctypes.data_as(_vp), V) for p in probs]
+    L.nch_dec_free(d)
+    assert back == list(syms)
+
+
+@needs_ref
+def test_host_coder_carry_runs_equal_reference(pkg):
+    L = pkg.host.library()
+    rng = np.random.default_rng(9)
+    pr = rng.choice([1, 3, 16384, 32765, 32767], size=30000)
+    bits = (rng.random(30000) < 0.5).astype(int)
+    e, r = L.nch_enc_new(), orc.Encoder(True)
+    for q, bit in zip(pr, bits):
+        L.nch_enc_put_bit(e, int(q), int(bit))
+        r.put_bit(q, bit)
+    out = _vp()
+    n = L.nch_enc_finish(e, C.byref(out))
+    data = C.string_at(out.value, n)
+    L.nch_enc_free(e)
+    assert data == r.finish()
+    buf = C.create_string_buffer(data, len(data))
+    d = L.nch_dec_new(buf, len(data))
+    assert [L.nch_dec_get_bit(d, int(q)) for q in pr] == list(bits)
+    L.nch_dec_free(d)
+
+
+def test_path_and_tree_coding_equal_table_coding(pkg):
+    L = pkg.host.library()
+    rng = np.random.default_rng(4)
+    V, nb = 64, 6
+    probs = _tables(rng, 100, V, 3.0)
+    syms = rng.integers(0, V, 100)
+    a, e = HostEnc(L), L.nch_enc_new()
+    trees = []
+    for p, s in zip(probs, syms):
+        a.put_sym(p, s)
+        path = orc.sym_path(p, s)
+        L.nch_write_sym_path(e, path.ctypes.data_as(_vp), nb, int(s))
+        tree = np.zeros(V, np.uint16)   # heap-ordered prob0 of every node, from the oracle's paths
+        for leaf in range(V):
+            pth, k = orc.sym_path(p, leaf), 1
+            for lvl in range(nb):
+                tree[k] = pth[lvl]
+                k = 2 * k + ((leaf >> (nb - 1 - lvl)) & 1)
+        trees.append(tree)
+    out = _vp()
+    n = L.nch_enc_finish(e, C.byref(out))
+    data = C.string_at(out.value, n)
+    L.nch_enc_free(e)
+    assert data == a.finish()
+    buf = C.create_string_buffer(data, len(data))
+    d = L.nch_dec_new(buf, len(data))
+    assert [L.nch_read_sym_tree(d, t.ctypes.data_as(_vp), V) for t in trees] == list(syms)
+    L.nch_dec_free(d)
+
+
+@needs_ref
+def test_schedule_equals_reference(pkg):
+    L, R = pkg.host.library(), orc.ref_lib()
+    cases = [([3e-4, 1e-4], [156250], 0.0), ([1.6e-4, 1e-4], [10000], 0.5), ([1e-3], [], 0.0),
+             ([1e-3, 5e-4, 2e-4], [100, 1000], 0.3)]
+    for vals, pos, dp in cases:
+        ip = pkg.host.InterpParams.make(vals, pos, dp)
+        v = np.array(vals, np.float32)
+        ps = np.array(pos + [0], np.int64)
+        for at in (0, 1, 50, 99, 100, 101, 999, 1000, 5000, 10000, 40000, 156249, 156250, 10 ** 7):
+            want = R.ref_interp(len(pos), v.ctypes.data, ps.ctypes.data, dp, at)
+            assert L.nch_interp(C.byref(ip), at) == want, (vals, at)
+
+
+def test_stream_layout(pkg):
+    L = pkg.host.library()
+    block_len, B = 23, 4                       # stride 5, 3 streams get one extra symbol
+    buf = np.arange(100, 100 + block_len, dtype=np.uint16)
+    stride, rem = block_len // B, block_len % B
+    seen = []
+    for s in range(B):
+        n = stride + (s < rem)
+        assert L.nch_get_symb(buf.ctypes.data_as(_vp), stride, rem, s, -1) == 0
+        assert L.nch_get_symb(buf.ctypes.data_as(_vp), stride, rem, s, n) == 0
+        seen += [L.nch_get_symb(buf.ctypes.data_as(_vp), stride, rem, s, i) for i in range(n)]
+    assert seen == list(buf)                   # streams tile the block contiguously, in order
+    out = np.zeros(block_len, np.uint16)
+    for s in range(B):
+        for i in range(stride + (s < rem)):
+            assert L.nch_put_symb(out.ctypes.data_as(_vp), stride, rem, s, i, 7 * s + i) == 0
+    assert L.nch_put_symb(out.ctypes.data_as(_vp), stride, rem, 3, stride, 1) != 0
+
+
+def test_header_layout_and_round_trip(pkg):
+    p = pkg.abi.make_params(n_layer=2, d_model=128, n_head=4, d_key=32, d_inner=512, d_pos=48, mem_len=32,
+                            seg_len=32, n_streams=4, n_symbols=256, init_kind=0, init_range=1.0,
+                            beta2=0.9999, gradient_clip=0.1, seed=123)
+    fp = pkg.host.file_params(p, lr=pkg.host.InterpParams.make([3e-4, 1e-4], [156250]))
+    h = pkg.host.header_bytes(fp, 1000)
+    # the reference layout (nncp.c:2665-2690, 1297-1365), field by field, big-endian
+    want = struct.pack(">IHBBHHHI", 0xb727ac58, 1, 1, 0, 4, 32, 256, 123)
+    want += struct.pack(">Bffif", 1, 3e-4, 1e-4, 156250, 0.0) + struct.pack(">Bff", 0, 500000.0, 0.0)
+    want += struct.pack(">IB", 0, 0) + struct.pack(">BBHHHHH", 2, 4, 32, 32, 512, 48, 32)
+    want += struct.pack(">HH", 64, 64) + bytes([0, 1, 1, 0, 0, 1, 0, 1]) + struct.pack(">ffB", 1.0, 1.0, 1)
+    want += struct.pack(">Bffff", 1, 0.0, 0.9999, 1e-8, 0.1) + bytes([0]) + bytes([0]) + struct.pack(">I", 1000)
+    assert h == want
+    fp2, nsym, used = pkg.host.read_header(h + b"payload")
+    assert nsym == 1000 and used == len(h)
+    for f in ("n_layer", "d_model", "n_head", "d_key", "d_inner", "d_pos", "mem_len", "seg_len", "n_streams",
+              "n_symbols", "use_bias", "use_w_r", "query_bias", "ln_flags", "ff_act", "init_kind", "seed"):
+        assert getattr(fp2.model, f) == getattr(p, f), f
+    assert abs(fp2.model.beta2 - 0.9999) < 1e-7 and fp2.lr.n_steps == 1 and fp2.lr.pos[0] == 156250
+    # build-defined options travel in version 2
+    h2 = pkg.host.header_bytes(pkg.host.file_params(p.copy(init_kind=1, init_range=0.02)), 5)
+    assert h2[4:6] == b"\x00\x02" and pkg.host.read_header(h2)[0].model.init_kind == 1
+    for bad in (b"", h[:10], b"\x00" + h[1:], h[:4] + b"\x00\x09" + h[6:]):
+        with pytest.raises(ValueError):
+            pkg.host.read_header(bad)
+
+
+def _oracle_ops(pkg, model):
+    """nch_model_ops backed by the CPU oracle (tests only)."""
+    H = pkg.host
+    T, B, V = model.T, model.B, model.V
+    keep = {}
+
+    def ev(ctx, oi, inp):
+        ids = np.ctypeslib.as_array(inp, shape=(T * B,)).reshape(T, B)
+        model.eval(oi, ids)
+        return 0
+
+    def probs(ctx, t0, nt, out):
+        src = np.ctypeslib.as_array(model.L.orc_probs(model.h), shape=(T * B * V,))
+        C.memmove(out, src[t0 * B * V:].ctypes.data, 4 * nt * B * V)
+        return 0
+
+    def grad(ctx, exp, loss):
+        tg = np.ctypeslib.as_array(exp, shape=(T * B,)).reshape(T, B)
+        loss[0] = model.eval_gradient(tg)
+        return 0
+
+    def setlr(ctx, lr):
+        model.set_lr(lr)
+        return 0
+
+    keep["fns"] = [H.FN_CTX(lambda c: (model.reset(), 0)[1]), H.FN_SET_LR(setlr), H.FN_EVAL(ev),
+                   H.FN_PROBS(probs), H.FN_CTX(lambda c: 0), H.FN_GRAD(grad),
+                   H.FN_CTX(lambda c: (model.update(), 0)[1])]
+    f = keep["fns"]
+    ops = H.ModelOps(None, B, T, V, f[0], f[1], f[2], f[3], H.FN_PATHS(), H.FN_TREES(), f[4], f[5], f[6])
+    ops._keep = keep
+    return ops
+
+
+@pytest.mark.parametrize("n_sym,block_len", [(0, 500), (1, 500), (37, 500), (4 * 2 * 6, 500), (301, 96),
+                                             (250, 1000)])
+def test_block_loop_round_trip_with_oracle_model(pkg, n_sym, block_len):
+    """encode with one model_eval per segment, decode one symbol at a time: identical symbols back.
+    Covers empty input, inputs shorter than one segment, ragged tails (block_len % streams != 0),
+    several blocks, and training between segments."""
+    cfg, z = load_golden("post_gelu")
+    p = params_from_cfg(pkg, cfg, n_streams=2, seg_len=4, lr=1e-2)
+    rng = np.random.default_rng(n_sym)
+    # a learnable source: mostly a short cycle, sometimes noise
+    syms = np.array([(3 * i) % 5 if rng.random() < 0.85 else rng.integers(0, 16) for i in range(n_sym)],
+                    np.uint16)
+    fp = pkg.host.file_params(p, block_len=block_len)
+    enc_model, dec_model = orc.OracleModel(p), orc.OracleModel(p)
+    data, st = pkg.host.compress(_oracle_ops(pkg, enc_model), fp, syms, pkg.host.EVAL_SEGMENT,
+                                 pkg.host.OUT_FLOAT)
+    assert st.n_symbols == n_sym
+    back = pkg.host.decompress(_oracle_ops(pkg, dec_model), data, pkg.host.OUT_FLOAT)
+    assert np.array_equal(back, syms)
+    if n_sym >= 250:
+        assert st.train_steps > 0
+        # the model learns the cycle: fewer bits than the 4 bits/symbol of a uniform coder
+        hdr = len(pkg.host.header_bytes(fp, n_sym))
+        assert (len(data) - hdr) * 8 < 0.8 * 4 * n_sym
+
+
+def test_step_mode_encoder_gives_the_same_bytes(pkg):
+    cfg, z = load_golden("post_gelu")
+    p = params_from_cfg(pkg, cfg, n_streams=2, seg_len=4)
+    syms = (np.arange(90) * 7 % 16).astype(np.uint16)
+    fp = pkg.host.file_params(p, block_len=64)
+    a, _ = pkg.host.compress(_oracle_ops(pkg, orc.OracleModel(p)), fp, syms, pkg.host.EVAL_SEGMENT, 0)
+    b, _ = pkg.host.compress(_oracle_ops(pkg, orc.OracleModel(p)), fp, syms, pkg.host.EVAL_STEP, 0)
+    assert a == b
+
+
+def test_truncated_payload_decodes_without_failing(pkg):
+    """The decoder zero-pads past the end of its input (arith.c:209-223): a truncated stream
+    yields wrong symbols, never an error or a crash."""
+    cfg, z = load_golden("post_gelu")
+    p = params_from_cfg(pkg, cfg, n_streams=2, seg_len=4)
+    syms = (np.arange(60) % 16).astype(np.uint16)
+    fp = pkg.host.file_params(p)
+    data, _ = pkg.host.compress(_oracle_ops(pkg, orc.OracleModel(p)), fp, syms, 1, 0)
+    back = pkg.host.decompress(_oracle_ops(pkg, orc.OracleModel(p)), data[:-3], 0)
+    assert back.shape == syms.shape and back.max() < 16
+
+
+def test_cuda_binding_fails_loudly_without_a_gpu(pkg):
+    import torch
+    if torch.cuda.is_available():
+        pytest.skip("a GPU is present")
+    with pytest.raises(pkg.LibraryMissing):
+        pkg.host.bind_cuda(pkg.abi.make_params())
