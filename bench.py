@@ -230,24 +230,18 @@ def main():
     T, V = c["seg_len"], c["n_symbols"]
     K, W = args.steps, max(args.warmup, 3)
     ids_all, tg_all = make_batches(c, Bt, K + W)
-    sl = slice(rank * B, (rank + 1) * B)
+    sl = pkg.dist.stream_slice(rank, world, Bt)
     ids_h = torch.from_numpy(np.ascontiguousarray(ids_all[:, :, sl])).pin_memory()
     tg_h = torch.from_numpy(np.ascontiguousarray(tg_all[:, :, sl])).pin_memory()
     ids_d, tg_d = ids_h.cuda(), tg_h.cuda()
 
-    class _Wrap:   # the flat gradient buffer as a torch tensor (for the NCCL all-reduce)
-        def __init__(self, ptr, n):
-            self.__cuda_array_interface__ = {"shape": (n,), "typestr": "<f4", "data": (ptr, False),
-                                             "version": 2}
     wptr, gptr, vptr, nfl = m.flat_buffers()
-    grads = torch.as_tensor(_Wrap(gptr, nfl), device=f"cuda:{local}") if world > 1 else None
+    # the flat gradient buffer as a torch tensor (for the NCCL all-reduce)
+    grads = torch.as_tensor(pkg.dist.CudaArray(gptr, nfl), device=f"cuda:{local}") if world > 1 else None
+    sharded = pkg.dist.ShardedStep(m, grads, world=world)
 
     def step_device(s):
-        m.eval_dev(-1, ids_d[s].data_ptr())
-        m.eval_gradient_dev(tg_d[s].data_ptr())
-        if world > 1:
-            dist.all_reduce(grads)      # fixed N, fixed algorithm: every rank gets the same sum
-        m.update()
+        sharded.step_device(ids_d[s].data_ptr(), tg_d[s].data_ptr())
 
     nb = int(np.log2(V)) if (V & (V - 1)) == 0 else 0
     paths = np.zeros((T * B, max(nb, 1)), np.uint16)
@@ -261,8 +255,7 @@ def main():
         else:
             m.read_probs(0, T)
         loss = m.eval_gradient(tg_h[s].numpy())
-        if world > 1:
-            dist.all_reduce(grads)
+        sharded.reduce_gradients()
         m.update()
         return loss
 

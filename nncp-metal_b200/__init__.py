@@ -8,3 +8,4 @@ from . import abi  # noqa: F401
 from .loader import library, build_library, LibraryMissing  # noqa: F401
 from .model import TrfModel  # noqa: F401
 from . import host  # noqa: F401
+from . import dist  # noqa: F401

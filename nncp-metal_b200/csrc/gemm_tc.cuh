@@ -4,7 +4,7 @@
 //
 // Replaces nc_matmul (libnc.h:270-276) for every projection of the bf16 model.
 // sm_100a only: operands are staged by TMA (cp.async.bulk.tensor, 128-byte
-// swizzle, no cluster multicast) into a 3- or 4-stage shared-memory ring, one
+// swizzle, each CTA loading its own tiles) into a 3- or 4-stage shared-memory ring, one
 // elected thread issues tcgen05.mma (UMMA 128 x BN x 16, cta_group::1) into a
 // TMEM accumulator, and four epilogue warps read it back with tcgen05.ld.
 //

@@ -1,0 +1,76 @@
+"""Stream sharding over 2 ranks on the CPU (gloo): each rank trains its half of the streams with
+the CPU oracle as the model, gradients are all-reduced, and both ranks must end with the same
+weights as a single process that trains all streams."""
+import os
+import sys
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from conftest import ROOT, load_golden, load_package, params_from_cfg, rel_err
+
+STEPS = 3
+
+
+def _data(cfg, B):
+    rng = np.random.default_rng(0)
+    T, V = cfg["seg_len"], cfg["n_symbols"]
+    return (rng.integers(0, V, (STEPS, T, B)).astype(np.int32),
+            rng.integers(0, V, (STEPS, T, B)).astype(np.int32))
+
+
+def _run(pkg, orc, cfg, z, ids, tg, rank, world, B_total):
+    sl = pkg.dist.stream_slice(rank, world, B_total)
+    p = params_from_cfg(pkg, cfg, n_streams=B_total // world, n_streams_total=B_total)
+    m = orc.OracleModel(p)
+    for name in m.info:
+        m.set_param(name, z[f"p0/{name}"])
+    m.reset()
+    grads = torch.from_numpy(np.ctypeslib.as_array(m.L.orc_grads(m.h), shape=(m.n_floats,)))
+    step = pkg.dist.ShardedStep(m, grads, world=world)
+    losses = [step.step_host(np.ascontiguousarray(ids[s][:, sl]), np.ascontiguousarray(tg[s][:, sl]))
+              for s in range(STEPS)]
+    return m, losses
+
+
+def _worker(rank, world, port, out_dir):
+    sys.path.insert(0, ROOT)
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    pkg = load_package()
+    from oracle import oracle as orc
+    cfg, z = load_golden("c0_like")
+    ids, tg = _data(cfg, 4)
+    m, losses = _run(pkg, orc, cfg, z, ids, tg, rank, world, 4)
+    np.savez(os.path.join(out_dir, f"rank{rank}.npz"), loss=np.array(losses),
+             **{k: m.get_param(k) for k in m.info})
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_two_ranks_equal_one_process(tmp_path, pkg, oracle):
+    port = 29500 + os.getpid() % 2000
+    mp.spawn(_worker, args=(2, port, str(tmp_path)), nprocs=2, join=True)
+    r0, r1 = np.load(tmp_path / "rank0.npz"), np.load(tmp_path / "rank1.npz")
+    cfg, z = load_golden("c0_like")
+    ids, tg = _data(cfg, 4)
+    single, losses = _run(pkg, oracle, cfg, z, ids, tg, 0, 1, 4)
+    for k in single.info:
+        assert np.array_equal(r0[k], r1[k]), k            # ranks hold identical weights
+        assert rel_err(r0[k], single.get_param(k)) < 2e-3, k   # and follow the 1-process run
+    assert abs((r0["loss"] + r1["loss"]).sum() - np.sum(losses)) < 1e-3 * abs(np.sum(losses))
+
+
+def test_stream_slice_partitions_the_streams(pkg):
+    for world in (1, 2, 4, 8):
+        cols = []
+        for r in range(world):
+            s = pkg.dist.stream_slice(r, world, 32)
+            cols += list(range(32))[s]
+        assert cols == list(range(32))
+    with pytest.raises(ValueError):
+        pkg.dist.stream_slice(0, 3, 32)
