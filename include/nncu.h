@@ -260,6 +260,37 @@ int nncu_attention_reduce_tables(const nncu_attn_shape *s, const float *dwr_part
                                  const float *dbr_part, float *dw_r, float *db_r,
                                  int accumulate, void *cuda_stream);
 
+/*
+ * nncu_attention_backward_noalloc -- no counterpart in the reference.
+ *
+ * Same result as nncu_attention_backward followed by nncu_attention_reduce_tables
+ * (accumulate = 0), for callers that cannot give the op a scratch buffer: a host that
+ * has handed all of its device memory to its own pool at start-up, or a per-segment
+ * loop that must not pay the device-wide synchronisation cudaMalloc and cudaFree imply.
+ * The per-(stream, head) partial table gradients, which the plain entry point takes from
+ * the caller, live here in one fixed array of NNCU_NOALLOC_SCRATCH_FLOATS floats (16 MiB)
+ * that is part of the library image: every GPU that loads the library holds it until the
+ * process exits.  The call allocates nothing and frees nothing.
+ *
+ *   - Needs n_streams * n_head * (d_pos * d_key + mem_len + seg_len) <= NNCU_NOALLOC_SCRATCH_FLOATS
+ *     (the d_pos * d_key term only when w_r is given); larger shapes are refused with
+ *     NNCU_ERR_RANGE and nothing is launched.
+ *   - The first call on each device looks the array's device address up
+ *     (cudaGetSymbolAddress, with that device current).  Make that first call before
+ *     starting any stream capture.
+ *   - All calls share the one array.  Nothing in it has to start at zero (every partial the
+ *     reduction reads is written first by the same call), and it keeps the last call's
+ *     contents.  Two calls that overlap on the GPU (different streams, or different host
+ *     threads) race on it: serialise them.
+ * dw_r [H][P][dk] (may be NULL when w_r is NULL) and db_r [H][L] receive the table gradients
+ * summed over streams in stream order.
+ */
+#define NNCU_NOALLOC_SCRATCH_FLOATS (4u << 20)
+int nncu_attention_backward_noalloc(const nncu_attn_shape *s, const void *q, const void *kv,
+                                    const float *w_r, const float *b_r, const void *out,
+                                    const float *lse, const void *dout, void *dq, void *dkv,
+                                    float *dw_r, float *db_r, void *cuda_stream);
+
 /* ---- dense contraction used by every projection (nc_matmul, libnc.h:270-276) ----
  * C[M][N] = A[M][K] * B[N][K]^T (+ bias[N]), bf16 operands, fp32 accumulate,
  * C bf16 (c_is_f32 == 0) or fp32.  Exposed so that the tcgen05 kernel can be

@@ -6,6 +6,7 @@ LN_POST, LN_PRE, LN_FINAL, LN_COEF, LN_RMSNORM = 1, 2, 4, 8, 16
 FF_RELU, FF_GELU, FF_GEGLU, FF_GATED_SILU = 0, 1, 2, 3
 INIT_UNIFORM, INIT_NORMAL = 0, 1
 GEMM_AUTO, GEMM_SIMT, GEMM_TCGEN05 = 0, 1, 2
+NOALLOC_SCRATCH_FLOATS = 4 << 20
 OK, ERR_INVALID, ERR_CUDA, ERR_NOMEM, ERR_STATE, ERR_TIMEOUT, ERR_RANGE = range(7)
 
 
@@ -107,6 +108,7 @@ PROTOTYPES = {
     "nncu_coder_trees": (_i, [_vp, _i, _i, _vp]),
     "nncu_attention_forward": (_i, [C.POINTER(AttnShape), _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "nncu_attention_backward": (_i, [C.POINTER(AttnShape)] + [_vp] * 12),
+    "nncu_attention_backward_noalloc": (_i, [C.POINTER(AttnShape)] + [_vp] * 12),
     "nncu_attention_reduce_tables": (_i, [C.POINTER(AttnShape), _vp, _vp, _vp, _vp, _i, _vp]),
     "nncu_profile_begin": (_i, [_i]),
     "nncu_profile_end": (_i, [C.POINTER(Profile)]),

@@ -1274,6 +1274,60 @@ int nncu_attention_reduce_tables(const nncu_attn_shape *s, const float *dwr_part
     return NNCU_OK;
 }
 
+// ---- attention backward with its scratch inside the library image
+//
+// For callers that cannot hand over a scratch buffer (all device memory already in their own
+// pool, or no room for the synchronisation an allocation implies).  The partial table
+// gradients go to a fixed file-scope device array.  In host code the array's name is only a
+// handle: its device address is fetched once per device with cudaGetSymbolAddress, with that
+// device current, and that pointer is what the kernels get.
+
+static __device__ __align__(256) float g_noalloc_scratch[NNCU_NOALLOC_SCRATCH_FLOATS];
+
+#define NNCU_MAX_DEVICES 64
+static float *g_noalloc_ptr[NNCU_MAX_DEVICES];
+
+int nncu_attention_backward_noalloc(const nncu_attn_shape *s, const void *q, const void *kv, const float *w_r,
+                                    const float *b_r, const void *out, const float *lse, const void *dout,
+                                    void *dq, void *dkv, float *dw_r, float *db_r, void *cuda_stream)
+{
+    NNCU_TRY(attn_check_shape(s));
+    if (!q || !kv || !b_r || !out || !lse || !dout || !dq || !dkv || !db_r || (w_r && !dw_r))
+        return nncu_fail(NNCU_ERR_INVALID, "null tensor");
+    const size_t L = (size_t)s->mem_len + s->seg_len;
+    const size_t bh = (size_t)s->n_streams * s->n_head;
+    const size_t n_wr = w_r ? bh * s->d_pos * s->d_key : 0, n_br = bh * L;
+    if (n_wr + n_br > (size_t)NNCU_NOALLOC_SCRATCH_FLOATS)
+        return nncu_fail(NNCU_ERR_RANGE,
+                         "attention backward without allocation: %zu scratch floats needed, the built-in "
+                         "array holds %u; use nncu_attention_backward with caller-provided buffers",
+                         n_wr + n_br, (unsigned)NNCU_NOALLOC_SCRATCH_FLOATS);
+    int dev = -1;
+    CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= NNCU_MAX_DEVICES)
+        return nncu_fail(NNCU_ERR_INVALID, "device ordinal %d out of range", dev);
+    if (!g_noalloc_ptr[dev]) { // first call on this device: resolve the array's device address
+        float *ptr = nullptr;
+        CUDA_TRY(cudaGetSymbolAddress((void **)&ptr, g_noalloc_scratch));
+        g_noalloc_ptr[dev] = ptr;
+    }
+    float *dwr_part = w_r ? g_noalloc_ptr[dev] : nullptr;
+    float *dbr_part = g_noalloc_ptr[dev] + n_wr;
+    cudaStream_t st = (cudaStream_t)cuda_stream;
+    NNCU_TRY(s->dtype_bf16
+                 ? attn_backward_any<bf16>(s, q, kv, w_r, b_r, out, lse, dout, dq, dkv, dwr_part, dbr_part, st)
+                 : attn_backward_any<float>(s, q, kv, w_r, b_r, out, lse, dout, dq, dkv, dwr_part, dbr_part, st));
+    const size_t nb = (size_t)s->n_head * L;
+    reduce_streams_kernel<<<ceil_div(nb, 256), 256, 0, st>>>(dbr_part, s->n_streams, nb, db_r, 0);
+    KERNEL_CHECK();
+    if (w_r) {
+        const size_t nw = (size_t)s->n_head * s->d_pos * s->d_key;
+        reduce_streams_kernel<<<ceil_div(nw, 256), 256, 0, st>>>(dwr_part, s->n_streams, nw, dw_r, 0);
+        KERNEL_CHECK();
+    }
+    return NNCU_OK;
+}
+
 // ---- dense contraction test hook
 
 int nncu_gemm_bf16_nt(int backend, int M, int N, int K, const void *A, int lda, const void *B, int ldb, void *C,
