@@ -299,6 +299,14 @@ int nncu_attention_backward_noalloc(const nncu_attn_shape *s, const void *q, con
 int nncu_gemm_bf16_nt(int backend, int M, int N, int K, const void *A, int lda,
                       const void *B, int ldb, void *C, int ldc, int c_is_f32,
                       const float *bias, void *cuda_stream);
+/* The three operand arrangements of the train step (mode 0, 1, 2):
+ *   0  C[m][n] = sum_k A[m][k] B[n][k]     y  = x W^T      (A [M][K], B [N][K])
+ *   1  C[m][n] = sum_k A[m][k] B[k][n]     dx = dy W       (A [M][K], B [K][N])
+ *   2  C[m][n] = sum_k A[k][m] B[k][n]     dW = dy^T x     (A [K][M], B [K][N])
+ * The tensor-core engine reads the second and third arrangement in place (MN-major
+ * operands); no transposed copies are made. */
+int nncu_gemm_bf16(int backend, int mode, int M, int N, int K, const void *A, int lda,
+                   const void *B, int ldb, void *C, int ldc, int c_is_f32, void *cuda_stream);
 
 /* ---- measurement hooks (PROF_* buckets of libnc.h:16-65 count cycles per phase; here the
  * library counts its own kernel launches and, on request, times every launch of the

@@ -112,6 +112,7 @@ PROTOTYPES = {
     "nncu_attention_reduce_tables": (_i, [C.POINTER(AttnShape), _vp, _vp, _vp, _vp, _i, _vp]),
     "nncu_profile_begin": (_i, [_i]),
     "nncu_profile_end": (_i, [C.POINTER(Profile)]),
+    "nncu_gemm_bf16": (_i, [_i, _i, _i, _i, _i, _vp, _i, _vp, _i, _vp, _i, _i, _vp]),
     "nncu_gemm_bf16_nt": (_i, [_i, _i, _i, _i, _vp, _i, _vp, _i, _vp, _i, _i, _vp, _vp]),
 }
 

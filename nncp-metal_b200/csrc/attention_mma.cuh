@@ -320,11 +320,14 @@ size_t bwd_smem(int L, int P)
     Dims d = dims_of(L, P, DK);
     return ((size_t)2 * 64 * d.LDS + (size_t)2 * d.Lp * d.LDS + (size_t)d.Pr * d.LDS + (size_t)2 * 64 * d.LPS +
             (size_t)64 * d.PPS) * sizeof(bf16) +
-           ((size_t)L + 4 + 4 * 16 * EW + 128) * sizeof(float) + 64;
+           ((size_t)L + 4 + 8 * 16 * EW + 128) * sizeof(float) + 64;
 }
 
+// 8 warps: warp w owns query tile (w & 3); in phase A the two warps of a tile take alternate
+// key blocks, in phase B the row tiles of each contraction are dealt round-robin over the
+// warps and dQ is split into its key part (warps 0-3) and position part (warps 4-7).
 template <int DK>
-__global__ void __launch_bounds__(128) attn_bwd_mma_kernel(AttnArgs a)
+__global__ void __launch_bounds__(256) attn_bwd_mma_kernel(AttnArgs a)
 {
     extern __shared__ __align__(16) unsigned char smraw[];
     const Dims d = dims_of(a.L, a.P, DK);
@@ -338,7 +341,7 @@ __global__ void __launch_bounds__(128) attn_bwd_mma_kernel(AttnArgs a)
     bf16 *dEm = dSm + (size_t)64 * d.LPS;
     float *brs = reinterpret_cast<float *>(dEm + (size_t)64 * d.PPS);
     float *Es = brs + ((a.L + 3) & ~3);
-    float *Dr = Es + 4 * 16 * EW; // [64]
+    float *Dr = Es + 8 * 16 * EW; // [64]
     float *lses = Dr + 64;        // [64]
     constexpr int KS = DK / 16, NT = DK / 8;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
@@ -363,8 +366,8 @@ __global__ void __launch_bounds__(128) attn_bwd_mma_kernel(AttnArgs a)
         for (int i = threadIdx.x; i < n; i += blockDim.x)
             z[i] = 0u;
     }
-    // D_i = dO_i . O_i and the saved log-sum-exp, one warp per 16 rows
-    for (int r = warp * 16; r < warp * 16 + 16; r++) {
+    // D_i = dO_i . O_i and the saved log-sum-exp, one warp per 8 rows
+    for (int r = warp * 8; r < warp * 8 + 8; r++) {
         float s = 0.0f;
         if (r < T) {
             const size_t go = ((size_t)r * a.B + b) * HD + h * DK;
@@ -379,9 +382,9 @@ __global__ void __launch_bounds__(128) attn_bwd_mma_kernel(AttnArgs a)
     }
     __syncthreads();
 
-    // ---- phase A: P and dS of the warp's 16 query rows
+    // ---- phase A: P and dS of the warp's 16 query rows, every second key block
     {
-        const int i0 = warp * 16;
+        const int i0 = (warp & 3) * 16, half = warp >> 2;
         const int va = i0, vb = min(i0 + 16, T) - 1;
         if (va <= vb) {
             uint32_t qf[KS][4], df[KS][4];
@@ -403,6 +406,8 @@ __global__ void __launch_bounds__(128) attn_bwd_mma_kernel(AttnArgs a)
             const float DA = Dr[i0 + g], DB = Dr[i0 + g + 8];
             float *es = Es + (size_t)warp * 16 * EW;
             for (int kb = jmin / 64; kb <= jmax / 64; kb++) {
+                if ((kb & 1) != half)
+                    continue;
                 const int j0 = kb * 64;
                 float s[8][4], dp[8][4];
                 score_block<DK>(a, d, qf, Ks, Rs, brs, es, i0, j0, iA, iB, jloA, jhiA, jloB, jhiB, s);
@@ -474,7 +479,7 @@ __global__ void __launch_bounds__(128) attn_bwd_mma_kernel(AttnArgs a)
     // ---- phase B
     bf16 *dkv = reinterpret_cast<bf16 *>(a.dkv);
     // dV = P^T dO and dK = dS^T Q: 16-key row tiles spread over the warps, K = 64 queries
-    for (int mt = warp; mt < d.Lp / 16; mt += 4) {
+    for (int mt = warp; mt < d.Lp / 16; mt += 8) {
         const int jm0 = mt * 16;
         float dv[NT][4], dk[NT][4];
 #pragma unroll
@@ -516,9 +521,11 @@ __global__ void __launch_bounds__(128) attn_bwd_mma_kernel(AttnArgs a)
             }
         }
     }
-    // dQ = dS K + dE R: one 16-query tile per warp
+    // dQ = dS K + dE R: warps 0-3 take the key part of their query tile, warps 4-7 the
+    // position part, which they pass through shared memory (the skew scratch is free now)
     {
-        const int i0 = warp * 16;
+        const int i0 = (warp & 3) * 16;
+        float *dqp = Es; // [64][DK] fp32
         float dq[NT][4];
 #pragma unroll
         for (int nt = 0; nt < NT; nt++)
@@ -526,18 +533,19 @@ __global__ void __launch_bounds__(128) attn_bwd_mma_kernel(AttnArgs a)
             for (int c = 0; c < 4; c++)
                 dq[nt][c] = 0.0f;
         if (i0 < T) {
-            for (int ks = 0; ks < d.Lp / 16; ks++) {
-                uint32_t as[4];
-                ldsm4(as, dSm + (size_t)(i0 + (lane & 15)) * d.LPS + ks * 16 + (lane >> 4) * 8);
+            if (warp < 4) {
+                for (int ks = 0; ks < d.Lp / 16; ks++) {
+                    uint32_t as[4];
+                    ldsm4(as, dSm + (size_t)(i0 + (lane & 15)) * d.LPS + ks * 16 + (lane >> 4) * 8);
 #pragma unroll
-                for (int np = 0; np < NT / 2; np++) {
-                    uint32_t bk[4];
-                    ldsm4t(bk, Ks + (size_t)(ks * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * d.LDS + np * 16 + (lane >> 4) * 8);
-                    mma16816(dq[2 * np], as, bk[0], bk[1]);
-                    mma16816(dq[2 * np + 1], as, bk[2], bk[3]);
+                    for (int np = 0; np < NT / 2; np++) {
+                        uint32_t bk[4];
+                        ldsm4t(bk, Ks + (size_t)(ks * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * d.LDS + np * 16 + (lane >> 4) * 8);
+                        mma16816(dq[2 * np], as, bk[0], bk[1]);
+                        mma16816(dq[2 * np + 1], as, bk[2], bk[3]);
+                    }
                 }
-            }
-            if (a.w_r)
+            } else if (a.w_r) {
                 for (int ks = 0; ks < d.Pr / 16; ks++) {
                     uint32_t ae[4];
                     ldsm4(ae, dEm + (size_t)(i0 + (lane & 15)) * d.PPS + ks * 16 + (lane >> 4) * 8);
@@ -549,6 +557,17 @@ __global__ void __launch_bounds__(128) attn_bwd_mma_kernel(AttnArgs a)
                         mma16816(dq[2 * np + 1], ae, br[2], br[3]);
                     }
                 }
+#pragma unroll
+                for (int nt = 0; nt < NT; nt++) {
+                    dqp[(size_t)(i0 + g) * DK + nt * 8 + 2 * t] = dq[nt][0];
+                    dqp[(size_t)(i0 + g) * DK + nt * 8 + 2 * t + 1] = dq[nt][1];
+                    dqp[(size_t)(i0 + g + 8) * DK + nt * 8 + 2 * t] = dq[nt][2];
+                    dqp[(size_t)(i0 + g + 8) * DK + nt * 8 + 2 * t + 1] = dq[nt][3];
+                }
+            }
+        }
+        __syncthreads();
+        if (i0 < T && warp < 4) {
             bf16 *dqg = reinterpret_cast<bf16 *>(a.dq);
 #pragma unroll
             for (int hh = 0; hh < 2; hh++) {
@@ -556,8 +575,14 @@ __global__ void __launch_bounds__(128) attn_bwd_mma_kernel(AttnArgs a)
                 if (i < T) {
                     bf16 *dst = dqg + ((size_t)i * a.B + b) * HD + h * DK;
 #pragma unroll
-                    for (int nt = 0; nt < NT; nt++)
-                        *reinterpret_cast<uint32_t *>(dst + nt * 8 + 2 * t) = pack2(dq[nt][2 * hh], dq[nt][2 * hh + 1]);
+                    for (int nt = 0; nt < NT; nt++) {
+                        float x0 = dq[nt][2 * hh], x1 = dq[nt][2 * hh + 1];
+                        if (a.w_r) {
+                            x0 += dqp[(size_t)i * DK + nt * 8 + 2 * t];
+                            x1 += dqp[(size_t)i * DK + nt * 8 + 2 * t + 1];
+                        }
+                        *reinterpret_cast<uint32_t *>(dst + nt * 8 + 2 * t) = pack2(x0, x1);
+                    }
                 }
             }
         }
@@ -565,7 +590,7 @@ __global__ void __launch_bounds__(128) attn_bwd_mma_kernel(AttnArgs a)
     // dR = dE^T Q (this stream's share of the table gradient), fp32
     if (a.w_r && a.dwr_part) {
         float *dst0 = a.dwr_part + ((size_t)b * a.H + h) * P * DK;
-        for (int mt = warp; mt < d.Pr / 16; mt += 4) {
+        for (int mt = warp; mt < d.Pr / 16; mt += 8) {
             const int pm0 = mt * 16;
             float dr[NT][4];
 #pragma unroll
@@ -641,7 +666,7 @@ static int launch_bwd(const AttnArgs &a, cudaStream_t st)
         CUDA_TRY(cudaFuncSetAttribute(attn_bwd_mma_kernel<DK>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         attr = smem;
     }
-    attn_bwd_mma_kernel<DK><<<a.B * a.H, 128, smem, st>>>(a);
+    attn_bwd_mma_kernel<DK><<<a.B * a.H, 256, smem, st>>>(a);
     KERNEL_CHECK();
     return NNCU_OK;
 }

@@ -1,6 +1,10 @@
 // gemm_tc.cuh -- bf16 x bf16 -> fp32 GEMM on the 5th-generation tensor cores.
 //
-//   C[M][N] = A[M][K] . B[N][K]^T (+ bias[N])        ("NT": both operands K-major)
+//   C[M][N] = sum_k A(m,k) B(n,k) (+ bias[N]) (+ addsrc)
+//
+// Each operand is either K-major (stored [rows = m or n][k], the forward y = x W^T form) or
+// MN-major (stored [k][m or n]): dx = dy W reads W MN-major, dW = dy^T x reads both operands
+// MN-major, so no transposed copy of a weight or an activation is ever made.
 //
 // Replaces nc_matmul (libnc.h:270-276) for every projection of the bf16 model.
 // sm_100a only: operands are staged by TMA (cp.async.bulk.tensor, 128-byte
@@ -150,6 +154,20 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr)
     return d;
 }
 
+// MN-major tile: [k rows][64 elements along m/n] per 8 KB box, 128-byte swizzle; boxes for
+// the next 64 m/n elements follow at +8192 bytes (leading offset), the next 8 k rows at
+// +1024 bytes (stride offset)
+__device__ __forceinline__ uint64_t smem_desc_sw128_mn(uint32_t addr)
+{
+    uint64_t d = 0;
+    d |= (uint64_t)((addr & 0x3FFFFu) >> 4);
+    d |= (uint64_t)(8192u >> 4) << 16;
+    d |= (uint64_t)(1024u >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+
 template <int BN>
 struct SmemLayout {
     static constexpr int A_BYTES = BM * BK * 2;
@@ -160,7 +178,7 @@ struct SmemLayout {
     static constexpr int TOTAL = BAR_OFFSET + 256 + 1024; // + barriers + alignment slack
 };
 
-template <int BN, typename TC>
+template <int BN, typename TC, bool AMN, bool BMN>
 __global__ void __launch_bounds__(192, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                TC *C, long ldc, const float *__restrict__ bias, const TC *addsrc, int M, int N,
@@ -208,14 +226,27 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 const uint32_t fb = smem_u32(&full[s]);
                 mbar_expect_tx(fb, SL::STAGE_BYTES);
                 unsigned char *a_dst = sm + s * SL::STAGE_BYTES;
-                tma_load_2d(smem_u32(a_dst), &map_a, fb, kb * BK, m0);
-                tma_load_2d(smem_u32(a_dst + SL::A_BYTES), &map_b, fb, kb * BK, n0);
+                if (AMN) {
+#pragma unroll
+                    for (int mb = 0; mb < BM / 64; mb++)
+                        tma_load_2d(smem_u32(a_dst + mb * 8192), &map_a, fb, m0 + mb * 64, kb * BK);
+                } else {
+                    tma_load_2d(smem_u32(a_dst), &map_a, fb, kb * BK, m0);
+                }
+                if (BMN) {
+#pragma unroll
+                    for (int nb = 0; nb < BN / 64; nb++)
+                        tma_load_2d(smem_u32(a_dst + SL::A_BYTES + nb * 8192), &map_b, fb, n0 + nb * 64, kb * BK);
+                } else {
+                    tma_load_2d(smem_u32(a_dst + SL::A_BYTES), &map_b, fb, kb * BK, n0);
+                }
             }
         }
     } else if (warp == 1) {
         if (lane == 0) {
-            constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) |
-                                       ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+            constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((AMN ? 1u : 0u) << 15) |
+                                       ((BMN ? 1u : 0u) << 16) | ((uint32_t)(BN >> 3) << 17) |
+                                       ((uint32_t)(BM >> 4) << 24);
             bool ok = true;
             for (int kb = 0; kb < nkb && ok; kb++) {
                 const int s = kb % SL::STAGES;
@@ -225,11 +256,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     break;
                 fence_after_sync();
                 const uint32_t a_addr = smem_u32(sm + s * SL::STAGE_BYTES);
-                const uint64_t adesc = smem_desc_sw128(a_addr);
-                const uint64_t bdesc = smem_desc_sw128(a_addr + SL::A_BYTES);
+                const uint64_t adesc = AMN ? smem_desc_sw128_mn(a_addr) : smem_desc_sw128(a_addr);
+                const uint64_t bdesc = BMN ? smem_desc_sw128_mn(a_addr + SL::A_BYTES)
+                                           : smem_desc_sw128(a_addr + SL::A_BYTES);
+                // one UMMA covers 16 along k: 32 bytes inside a K-major row (+2 in 16-byte units),
+                // 16 rows of 128 bytes in an MN-major tile (+128)
+                constexpr uint32_t astep = AMN ? 128u : 2u, bstep = BMN ? 128u : 2u;
 #pragma unroll
-                for (int k = 0; k < BK / 16; k++) // 32 bytes along K per UMMA: +2 in 16-byte units
-                    umma_bf16(tmem_base, adesc + 2 * k, bdesc + 2 * k, idesc,
+                for (int k = 0; k < BK / 16; k++)
+                    umma_bf16(tmem_base, adesc + astep * k, bdesc + bstep * k, idesc,
                               (kb > 0 || k > 0) ? 1u : 0u);
                 umma_commit(smem_u32(&empty[s])); // frees the stage when these MMAs retire
             }
@@ -406,17 +441,23 @@ static bool usable(const void *A, long lda, const void *B, long ldb, int K)
            (reinterpret_cast<uintptr_t>(A) & 15) == 0 && (reinterpret_cast<uintptr_t>(B) & 15) == 0;
 }
 
-template <int BN, typename TC>
+template <int BN, typename TC, bool AMN, bool BMN>
 static int launch(cudaStream_t st, int M, int N, int K, const bf16 *A, long lda, const bf16 *B,
                   long ldb, TC *C, long ldc, const float *bias, const TC *addsrc, int *err_flag)
 {
     using SL = SmemLayout<BN>;
     CUtensorMap ma, mb;
-    NNCU_TRY(make_tmap(A, M, K, lda, BM, &ma));
-    NNCU_TRY(make_tmap(B, N, K, ldb, BN, &mb));
+    if (AMN)
+        NNCU_TRY(make_tmap(A, K, M, lda, 64, &ma)); // [k rows][m], 64 x 64 boxes
+    else
+        NNCU_TRY(make_tmap(A, M, K, lda, BM, &ma));
+    if (BMN)
+        NNCU_TRY(make_tmap(B, K, N, ldb, 64, &mb));
+    else
+        NNCU_TRY(make_tmap(B, N, K, ldb, BN, &mb));
     static bool attr_done = false;
     if (!attr_done) {
-        CUDA_TRY(cudaFuncSetAttribute(gemm_tc_kernel<BN, TC>,
+        CUDA_TRY(cudaFuncSetAttribute(gemm_tc_kernel<BN, TC, AMN, BMN>,
                                       cudaFuncAttributeMaxDynamicSharedMemorySize, SL::TOTAL));
         attr_done = true;
     }
@@ -425,7 +466,7 @@ static int launch(cudaStream_t st, int M, int N, int K, const bf16 *A, long lda,
     const bool timed = pr && pr->n < GemmProfiler::MAX_EV;
     if (timed)
         cudaEventRecord(pr->ev[2 * pr->n], st);
-    gemm_tc_kernel<BN, TC><<<grid, 192, SL::TOTAL, st>>>(ma, mb, C, ldc, bias, addsrc, M, N, K, err_flag);
+    gemm_tc_kernel<BN, TC, AMN, BMN><<<grid, 192, SL::TOTAL, st>>>(ma, mb, C, ldc, bias, addsrc, M, N, K, err_flag);
     if (timed) {
         cudaEventRecord(pr->ev[2 * pr->n + 1], st);
         pr->flops[pr->n++] = 2.0 * M * N * K;
@@ -434,11 +475,12 @@ static int launch(cudaStream_t st, int M, int N, int K, const bf16 *A, long lda,
     return NNCU_OK;
 }
 
-// C bf16 or fp32; addsrc (may be NULL, may alias C) is added to the product.
-// err_flag: device int raised when a bounded wait expires.
-template <typename TC>
-static int gemm_nt(cudaStream_t st, int M, int N, int K, const bf16 *A, long lda, const bf16 *B,
-                   long ldb, TC *C, long ldc, const float *bias, const TC *addsrc, int *err_flag)
+// A: [M][K] (lda) or, AMN, [K][M]; B: [N][K] (ldb) or, BMN, [K][N].  C bf16 or fp32; addsrc
+// (may be NULL, may alias C) is added to the product.  err_flag: device int raised when a
+// bounded wait expires.
+template <typename TC, bool AMN, bool BMN>
+static int gemm(cudaStream_t st, int M, int N, int K, const bf16 *A, long lda, const bf16 *B,
+                long ldb, TC *C, long ldc, const float *bias, const TC *addsrc, int *err_flag)
 {
     if (M <= 0 || N <= 0)
         return NNCU_OK;
@@ -447,10 +489,17 @@ static int gemm_nt(cudaStream_t st, int M, int N, int K, const bf16 *A, long lda
     // the widest tile that still gives enough CTAs to fill the 148 SMs
     const long mt = ceil_div(M, BM);
     if (mt * ceil_div(N, 256) >= 120)
-        return launch<256, TC>(st, M, N, K, A, lda, B, ldb, C, ldc, bias, addsrc, err_flag);
+        return launch<256, TC, AMN, BMN>(st, M, N, K, A, lda, B, ldb, C, ldc, bias, addsrc, err_flag);
     if (mt * ceil_div(N, 128) >= 120 || N <= 64)
-        return launch<128, TC>(st, M, N, K, A, lda, B, ldb, C, ldc, bias, addsrc, err_flag);
-    return launch<64, TC>(st, M, N, K, A, lda, B, ldb, C, ldc, bias, addsrc, err_flag);
+        return launch<128, TC, AMN, BMN>(st, M, N, K, A, lda, B, ldb, C, ldc, bias, addsrc, err_flag);
+    return launch<64, TC, AMN, BMN>(st, M, N, K, A, lda, B, ldb, C, ldc, bias, addsrc, err_flag);
+}
+
+template <typename TC>
+static int gemm_nt(cudaStream_t st, int M, int N, int K, const bf16 *A, long lda, const bf16 *B,
+                   long ldb, TC *C, long ldc, const float *bias, const TC *addsrc, int *err_flag)
+{
+    return gemm<TC, false, false>(st, M, N, K, A, lda, B, ldb, C, ldc, bias, addsrc, err_flag);
 }
 
 } // namespace tc

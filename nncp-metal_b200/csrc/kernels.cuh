@@ -78,22 +78,21 @@ residual_norm_kernel(const T *__restrict__ a, const T *__restrict__ res, T *__re
     }
 }
 
-// Adjoint of y = norm(x)*g + b:  dx = (base ? base : 0) + J^T dy ; per-block partial
-// dg/db in part[blockIdx][2][D].  Block = 8 warps, each warp walks rows
-// blockIdx*RPB + warp, +8, ... inside the block's RPB-row chunk.
+// Adjoint of y = norm(x)*g + b:  dx = (base ? base : 0) + J^T dy ; per-block partial column
+// sums in part[blockIdx][3][D]: dg, db and (if want_sum) the column sums of the dx just
+// written (the bias gradient of the projection that produced x).  Block = 8 warps, each warp
+// walks rows blockIdx*RPB + warp, +8, ... inside the block's RPB-row chunk.
 template <typename T>
 __global__ void __launch_bounds__(256)
 norm_bwd_kernel(const T *__restrict__ dy, const T *__restrict__ x, const float *__restrict__ g,
                 const float *__restrict__ stats, const T *__restrict__ base, T *__restrict__ dx,
-                float *__restrict__ part, int rows, int D, int mode, int rpb)
+                float *__restrict__ part, int rows, int D, int mode, int rpb, int want_sum)
 {
-    extern __shared__ float sm[]; // [8][2][D]
+    extern __shared__ float sm[]; // [8][3][D]
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    float *mydg = sm + (size_t)warp * 2 * D, *mydb = mydg + D;
-    for (int i = lane; i < D; i += 32) {
+    float *mydg = sm + (size_t)warp * 3 * D, *mydb = mydg + D, *mydx = mydb + D;
+    for (int i = lane; i < 3 * D; i += 32)
         mydg[i] = 0.0f;
-        mydb[i] = 0.0f;
-    }
     const int r_end = min(rows, (blockIdx.x + 1) * rpb);
     for (int r = blockIdx.x * rpb + warp; r < r_end; r += 8) {
         const T *xr = x + (size_t)r * D, *dyr = dy + (size_t)r * D;
@@ -118,16 +117,51 @@ norm_bwd_kernel(const T *__restrict__ dy, const T *__restrict__ x, const float *
             float v = rstd * (dxh - s1 - xh * s2);
             if (base)
                 v += to_f(base[(size_t)r * D + i]);
-            dx[(size_t)r * D + i] = from_f<T>(v);
+            T o = from_f<T>(v);
+            dx[(size_t)r * D + i] = o;
+            if (want_sum)
+                mydx[i] += to_f(o);
         }
     }
     __syncthreads();
-    for (int i = threadIdx.x; i < 2 * D; i += blockDim.x) {
+    for (int i = threadIdx.x; i < 3 * D; i += blockDim.x) {
         float s = 0.0f;
 #pragma unroll
         for (int w = 0; w < 8; w++)
-            s += sm[(size_t)w * 2 * D + i];
-        part[(size_t)blockIdx.x * 2 * D + i] = s;
+            s += sm[(size_t)w * 3 * D + i];
+        part[(size_t)blockIdx.x * 3 * D + i] = s;
+    }
+}
+
+// Column reduction of partial sums, fixed order: out_k[c] = sum_p part[p*stride + off_k + c].
+// blockIdx.y selects the output k (up to 3); a block owns 32 columns, its 8 warps each sum
+// a contiguous range of parts, and the 8 range sums are added in range order.
+struct ReduceOut {
+    float *out[3];
+    int off[3];
+};
+__global__ void __launch_bounds__(256)
+reduce_cols_kernel(const float *__restrict__ part, int n_parts, int stride, int n, ReduceOut ro)
+{
+    __shared__ float sm[8][33];
+    const int c = blockIdx.x * 32 + (threadIdx.x & 31), grp = threadIdx.x >> 5;
+    const int k = blockIdx.y;
+    const int per = (n_parts + 7) / 8;
+    float s = 0.0f;
+    if (c < n) {
+        const float *src = part + ro.off[k] + c;
+        const int p1 = min(n_parts, (grp + 1) * per);
+        for (int p = grp * per; p < p1; p++)
+            s += src[(size_t)p * stride];
+    }
+    sm[grp][threadIdx.x & 31] = s;
+    __syncthreads();
+    if (grp == 0 && c < n) {
+        float t = 0.0f;
+#pragma unroll
+        for (int w = 0; w < 8; w++)
+            t += sm[w][threadIdx.x];
+        ro.out[k][c] = t;
     }
 }
 
@@ -184,27 +218,41 @@ __global__ void act_fwd_kernel(const T *__restrict__ hpre, T *__restrict__ hact,
     else if (act == NNCU_FF_GELU)
         o = gelu_f(a);
     else
-        o = round_to<T>(gelu_f(a)) * to_f(hpre[(size_t)r * F1 + F + i]);
+        o = gelu_f(a) * to_f(hpre[(size_t)r * F1 + F + i]);
     hact[idx] = from_f<T>(o);
 }
 
+// Adjoint of the activation, and (part != NULL) per-chunk column sums of the result for the
+// ff_bias1 gradient: part[chunk][F1].  grid (ceil(F/128), ceil(rows/32)); one column per thread.
 template <typename T>
-__global__ void act_bwd_kernel(const T *__restrict__ hpre, const T *__restrict__ dhact,
-                               T *__restrict__ dhpre, int rows, int F, int F1, int act)
+__global__ void __launch_bounds__(128)
+act_bwd_kernel(const T *__restrict__ hpre, const T *__restrict__ dhact, T *__restrict__ dhpre,
+               float *__restrict__ part, int rows, int F, int F1, int act)
 {
-    size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (idx >= (size_t)rows * F)
+    const int i = blockIdx.x * 128 + threadIdx.x;
+    if (i >= F)
         return;
-    int r = (int)(idx / F), i = (int)(idx % F);
-    float a = to_f(hpre[(size_t)r * F1 + i]), d = to_f(dhact[idx]);
-    if (act == NNCU_FF_RELU) {
-        dhpre[(size_t)r * F1 + i] = from_f<T>(a > 0.0f ? d : 0.0f);
-    } else if (act == NNCU_FF_GELU) {
-        dhpre[(size_t)r * F1 + i] = from_f<T>(d * gelu_grad_f(a));
-    } else {
-        float gate = to_f(hpre[(size_t)r * F1 + F + i]);
-        dhpre[(size_t)r * F1 + i] = from_f<T>(d * gate * gelu_grad_f(a));
-        dhpre[(size_t)r * F1 + F + i] = from_f<T>(d * gelu_f(a));
+    const int r0 = blockIdx.y * 32, r1 = min(rows, r0 + 32);
+    float s0 = 0.0f, s1 = 0.0f;
+    for (int r = r0; r < r1; r++) {
+        float a = to_f(hpre[(size_t)r * F1 + i]), d = to_f(dhact[(size_t)r * F + i]);
+        if (act == NNCU_FF_RELU || act == NNCU_FF_GELU) {
+            T o = from_f<T>(act == NNCU_FF_RELU ? (a > 0.0f ? d : 0.0f) : d * gelu_grad_f(a));
+            dhpre[(size_t)r * F1 + i] = o;
+            s0 += to_f(o);
+        } else {
+            float gate = to_f(hpre[(size_t)r * F1 + F + i]);
+            T o0 = from_f<T>(d * gate * gelu_grad_f(a)), o1 = from_f<T>(d * gelu_f(a));
+            dhpre[(size_t)r * F1 + i] = o0;
+            dhpre[(size_t)r * F1 + F + i] = o1;
+            s0 += to_f(o0);
+            s1 += to_f(o1);
+        }
+    }
+    if (part) {
+        part[(size_t)blockIdx.y * F1 + i] = s0;
+        if (F1 > F)
+            part[(size_t)blockIdx.y * F1 + F + i] = s1;
     }
 }
 

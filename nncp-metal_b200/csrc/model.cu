@@ -163,6 +163,17 @@ static int mm_nt(nncu_model *m, int M, int N, int K, const AT *A, long lda, size
     return mm_nt_impl<TC>(m, M, N, K, A, lda, w_off, C, ldc, bias);
 }
 
+// MN-major tensor-core operands (default) or explicit transposes (NNCU_TC_TRANSPOSE=1)
+static bool tc_mn_major()
+{
+    static int v = -1;
+    if (v < 0) {
+        const char *e = getenv("NNCU_TC_TRANSPOSE");
+        v = (e && e[0] == '1') ? 0 : 1;
+    }
+    return v == 1;
+}
+
 // dx = dy W (+ addsrc): C[M][Kin] = dY[M][Nout] . W[Nout][Kin]
 static int mm_nn(nncu_model *m, int M, int Kin, int Nout, const float *dY, long ldy, size_t w_off,
                  float *C, long ldc, const float *addsrc)
@@ -176,6 +187,10 @@ static int mm_nn(nncu_model *m, int M, int Kin, int Nout, const float *dY, long 
 static int mm_nn(nncu_model *m, int M, int Kin, int Nout, const bf16 *dY, long ldy, size_t w_off,
                  bf16 *C, long ldc, const bf16 *addsrc)
 {
+    if (m->use_tc && tc_mn_major() && tc::usable(dY, ldy, m->Wb + w_off, Kin, Nout))
+        // W is [Nout][Kin] = [k][n]: read in place as an MN-major operand
+        return tc::gemm<bf16, false, true>(m->st, M, Kin, Nout, dY, ldy, m->Wb + w_off, Kin, C, ldc, nullptr,
+                                           addsrc, m->err_flag);
     const bf16 *WT = m->WbT + w_off; // [Kin][Nout]
     if (m->use_tc && tc::usable(dY, ldy, WT, Nout, Nout))
         return tc::gemm_nt<bf16>(m->st, M, Kin, Nout, dY, ldy, WT, Nout, C, ldc, nullptr, addsrc,
@@ -197,6 +212,10 @@ static int mm_tn(nncu_model *m, int Nout, int Kin, int R, const float *dY, long 
 static int mm_tn(nncu_model *m, int Nout, int Kin, int R, const bf16 *dY, long ldy, const bf16 *X,
                  long ldx, float *Gout)
 {
+    if (m->use_tc && tc_mn_major() && tc::usable(dY, ldy, X, ldx, R))
+        // dY is [R][Nout] = [k][m], X is [R][Kin] = [k][n]: both MN-major, read in place
+        return tc::gemm<float, true, true>(m->st, Nout, Kin, R, dY, ldy, X, ldx, Gout, Kin, nullptr, nullptr,
+                                           m->err_flag);
     if (m->use_tc && (R % 8) == 0) {
         // both operands become K-major by an explicit transpose (the contraction runs over rows)
         bf16 *tA = reinterpret_cast<bf16 *>(m->tA), *tB = reinterpret_cast<bf16 *>(m->tB);
@@ -213,6 +232,20 @@ static int mm_tn(nncu_model *m, int Nout, int Kin, int R, const bf16 *dY, long l
                                         nullptr, 0);
 }
 
+// out_k[c] = sum over parts of part[p*stride + off_k + c], up to three outputs in one launch
+static int reduce_cols(nncu_model *m, int n_parts, int stride, int n, float *o0, int off0,
+                       float *o1 = nullptr, int off1 = 0, float *o2 = nullptr, int off2 = 0)
+{
+    ReduceOut ro;
+    ro.out[0] = o0; ro.off[0] = off0;
+    ro.out[1] = o1; ro.off[1] = off1;
+    ro.out[2] = o2; ro.off[2] = off2;
+    int nout = o2 ? 3 : (o1 ? 2 : 1);
+    reduce_cols_kernel<<<dim3(ceil_div(n, 32), nout), 256, 0, m->st>>>(m->part, n_parts, stride, n, ro);
+    KERNEL_CHECK();
+    return NNCU_OK;
+}
+
 template <typename AT>
 static int colsum(nncu_model *m, const AT *A, long lda, int R, int N, float *out)
 {
@@ -221,9 +254,7 @@ static int colsum(nncu_model *m, const AT *A, long lda, int R, int N, float *out
     colsum_part_kernel<AT><<<dim3(ceil_div(N, 128), chunks), 128, 0, m->st>>>(A, lda, R, N, rows_per,
                                                                             m->part);
     KERNEL_CHECK();
-    reduce_parts_kernel<<<ceil_div(N, 256), 256, 0, m->st>>>(m->part, chunks, N, N, out, 0, 1.0f);
-    KERNEL_CHECK();
-    return NNCU_OK;
+    return reduce_cols(m, chunks, N, N, out, 0);
 }
 
 template <typename AT>
@@ -240,22 +271,16 @@ static int norm_fwd(nncu_model *m, const AT *a, const AT *res, AT *s_out, AT *y,
 
 template <typename AT>
 static int norm_bwd(nncu_model *m, const AT *dy, const AT *x, size_t g_off, size_t b_off,
-                    const float *stats, const AT *base, AT *dx, int rows)
+                    const float *stats, const AT *base, AT *dx, int rows, float *dxsum = nullptr)
 {
     const int rpb = 8;
     int blocks = ceil_div(rows, rpb);
     int mode = (m->p.ln_flags & NNCU_LN_RMSNORM) ? 2 : 1;
-    size_t smem = (size_t)8 * 2 * m->D * sizeof(float);
+    size_t smem = (size_t)8 * 3 * m->D * sizeof(float);
     norm_bwd_kernel<AT><<<blocks, 256, smem, m->st>>>(dy, x, m->W + g_off, stats, base, dx, m->part,
-                                                      rows, m->D, mode, rpb);
+                                                      rows, m->D, mode, rpb, dxsum ? 1 : 0);
     KERNEL_CHECK();
-    reduce_parts_kernel<<<ceil_div(m->D, 256), 256, 0, m->st>>>(m->part, blocks, 2 * m->D, m->D,
-                                                               gf(m, g_off), 0, 1.0f);
-    KERNEL_CHECK();
-    reduce_parts_kernel<<<ceil_div(m->D, 256), 256, 0, m->st>>>(m->part + m->D, blocks, 2 * m->D,
-                                                               m->D, gf(m, b_off), 0, 1.0f);
-    KERNEL_CHECK();
-    return NNCU_OK;
+    return reduce_cols(m, blocks, 3 * m->D, m->D, gf(m, g_off), 0, gf(m, b_off), m->D, dxsum, 2 * m->D);
 }
 
 static nncu_attn_shape attn_shape(nncu_model *m, int l, int t0, int t1)
@@ -396,17 +421,19 @@ static int backward(nncu_model *m)
         AT *ds2 = dx;
         if (post) {
             ds2 = pick<AT>(m, {dx});
-            NNCU_TRY(norm_bwd<AT>(m, dx, atc<AT>(a.s2, 0), o.ln_g2, o.ln_b2, a.st_2, nullptr, ds2, TB));
-        }
-        if (o.ff_bias2 != NONE)
+            // the column sums of ds2 are the ff_bias2 gradient: taken in the same pass
+            NNCU_TRY(norm_bwd<AT>(m, dx, atc<AT>(a.s2, 0), o.ln_g2, o.ln_b2, a.st_2, nullptr, ds2, TB,
+                                  o.ff_bias2 != NONE ? gf(m, o.ff_bias2) : nullptr));
+        } else if (o.ff_bias2 != NONE) {
             NNCU_TRY(colsum<AT>(m, ds2, D, TB, D, gf(m, o.ff_bias2)));
+        }
         NNCU_TRY(mm_tn(m, D, F, TB, ds2, D, atc<AT>(a.hact, 0), F, gf(m, o.ff2)));
         NNCU_TRY(mm_nn(m, TB, F, D, ds2, D, o.ff2, dh, F, (const AT *)nullptr));
-        act_bwd_kernel<AT><<<ceil_div((long long)TB * F, 256), 256, 0, m->st>>>(
-            atc<AT>(a.hpre, 0), dh, dhp, TB, F, F1, p.ff_act);
+        act_bwd_kernel<AT><<<dim3(ceil_div(F, 128), ceil_div(TB, 32)), 128, 0, m->st>>>(
+            atc<AT>(a.hpre, 0), dh, dhp, o.ff_bias1 != NONE ? m->part : nullptr, TB, F, F1, p.ff_act);
         KERNEL_CHECK();
         if (o.ff_bias1 != NONE)
-            NNCU_TRY(colsum<AT>(m, dhp, F1, TB, F1, gf(m, o.ff_bias1)));
+            NNCU_TRY(reduce_cols(m, ceil_div(TB, 32), F1, F1, gf(m, o.ff_bias1), 0));
         const AT *u = pre ? atc<AT>(a.u, 0) : atc<AT>(a.y, 0);
         NNCU_TRY(mm_tn(m, F1, D, TB, dhp, F1, u, D, gf(m, o.ff1)));
         AT *dy = pick<AT>(m, {ds2});
@@ -496,7 +523,7 @@ transpose_jobs_kernel(const bf16 *__restrict__ src, bf16 *__restrict__ dst,
 
 static int refresh_transposed(nncu_model *m)
 {
-    if (m->bf && m->n_jobs > 0) {
+    if (m->bf && m->use_tc && !tc_mn_major() && m->n_jobs > 0) {
         transpose_jobs_kernel<<<m->n_job_tiles, 256, 0, m->st>>>(m->Wb, m->WbT, m->jobs_dev, m->n_jobs);
         KERNEL_CHECK();
     }
@@ -752,7 +779,7 @@ int nncu_create(const nncu_params *p, nncu_model **out)
     size_t max_k = (size_t)std::max(std::max(F, D), HD);
     size_t oTA = m->use_tc ? take(max_n * LB * 2) : 0, oTB = m->use_tc ? take(max_k * LB * 2) : 0;
     size_t oWr = take((size_t)m->B * m->H * p->d_pos * m->dk * 4), oBr = take((size_t)m->B * m->H * m->L * 4);
-    size_t part_floats = std::max((size_t)ceil_div(LB, 64) * max_n, (size_t)ceil_div(TB, 8) * 2 * D);
+    size_t part_floats = std::max((size_t)ceil_div(LB, 32) * max_n, (size_t)ceil_div(TB, 8) * 3 * D);
     size_t oPart = take(part_floats * 4);
     size_t oLogp = take((size_t)TB * 4), oLoss = take(256);
     size_t oIds = take((size_t)TB * 4), oTgt = take((size_t)TB * 4), oErr = take(256), oHash = take(256);
@@ -818,9 +845,9 @@ int nncu_create(const nncu_params *p, nncu_model **out)
     if (!jobs.empty() &&
         cudaMemcpy(m->jobs_dev, jobs.data(), sizeof(TransposeJob) * jobs.size(), cudaMemcpyHostToDevice) != cudaSuccess)
         return fail_cleanup(nncu_fail(NNCU_ERR_CUDA, "job table upload failed"));
-    if ((size_t)8 * 2 * D * 4 > 48 * 1024) {
-        cudaFuncSetAttribute(norm_bwd_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 8 * 2 * D * 4);
-        cudaFuncSetAttribute(norm_bwd_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 8 * 2 * D * 4);
+    if ((size_t)8 * 3 * D * 4 > 48 * 1024) {
+        cudaFuncSetAttribute(norm_bwd_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 8 * 3 * D * 4);
+        cudaFuncSetAttribute(norm_bwd_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 8 * 3 * D * 4);
     }
     if ((size_t)2 * V * 4 > 48 * 1024) {
         cudaFuncSetAttribute(coder_paths_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 2 * V * 4);
@@ -1328,7 +1355,45 @@ int nncu_attention_backward_noalloc(const nncu_attn_shape *s, const void *q, con
     return NNCU_OK;
 }
 
-// ---- dense contraction test hook
+// ---- dense contraction test hooks
+
+int nncu_gemm_bf16(int backend, int mode, int M, int N, int K, const void *A, int lda, const void *B, int ldb,
+                   void *C, int ldc, int c_is_f32, void *cuda_stream)
+{
+    if (!A || !B || !C || M < 0 || N < 0 || K < 0 || mode < 0 || mode > 2)
+        return nncu_fail(NNCU_ERR_INVALID, "bad GEMM arguments");
+    cudaStream_t st = (cudaStream_t)cuda_stream;
+    const bf16 *a = (const bf16 *)A, *b = (const bf16 *)B;
+    if (backend == NNCU_GEMM_SIMT)
+        return c_is_f32 ? gemm_simt<bf16, bf16, float>(st, mode, M, N, K, a, lda, b, ldb, (float *)C, ldc, nullptr, 0)
+                        : gemm_simt<bf16, bf16, bf16>(st, mode, M, N, K, a, lda, b, ldb, (bf16 *)C, ldc, nullptr, 0);
+    static int *flag = nullptr;
+    if (!flag) {
+        CUDA_TRY(cudaMalloc(&flag, sizeof(int)));
+        CUDA_TRY(cudaMemset(flag, 0, sizeof(int)));
+    }
+    int rc;
+    if (mode == GEMM_NT)
+        rc = c_is_f32 ? tc::gemm<float, false, false>(st, M, N, K, a, lda, b, ldb, (float *)C, ldc, nullptr, nullptr, flag)
+                      : tc::gemm<bf16, false, false>(st, M, N, K, a, lda, b, ldb, (bf16 *)C, ldc, nullptr, nullptr, flag);
+    else if (mode == GEMM_NN)
+        rc = c_is_f32 ? tc::gemm<float, false, true>(st, M, N, K, a, lda, b, ldb, (float *)C, ldc, nullptr, nullptr, flag)
+                      : tc::gemm<bf16, false, true>(st, M, N, K, a, lda, b, ldb, (bf16 *)C, ldc, nullptr, nullptr, flag);
+    else
+        rc = c_is_f32 ? tc::gemm<float, true, true>(st, M, N, K, a, lda, b, ldb, (float *)C, ldc, nullptr, nullptr, flag)
+                      : tc::gemm<bf16, true, true>(st, M, N, K, a, lda, b, ldb, (bf16 *)C, ldc, nullptr, nullptr, flag);
+    if (rc != NNCU_OK)
+        return rc;
+    int h = 0;
+    CUDA_TRY(cudaMemcpyAsync(&h, flag, sizeof(int), cudaMemcpyDeviceToHost, st));
+    CUDA_TRY(cudaStreamSynchronize(st));
+    if (h != 0) {
+        cudaMemset(flag, 0, sizeof(int));
+        return nncu_fail(NNCU_ERR_TIMEOUT, "tcgen05 GEMM: a bounded wait expired (code %d)", h);
+    }
+    return NNCU_OK;
+}
+
 
 int nncu_gemm_bf16_nt(int backend, int M, int N, int K, const void *A, int lda, const void *B, int ldb, void *C,
                       int ldc, int c_is_f32, const float *bias, void *cuda_stream)

@@ -64,6 +64,27 @@ def test_gemm_tcgen05_and_simt_vs_fp32(pkg, M, N, K, c_f32):
     assert d <= (1e-4 if c_f32 else 0.07) * ref.abs().max().item()
 
 
+@pytest.mark.parametrize("mode", [1, 2])
+@pytest.mark.parametrize("M,N,K", [(128, 128, 64), (2048, 512, 512), (512, 2048, 2048), (1024, 512, 4096),
+                                   (104, 72, 40), (16384, 512, 2048), (2048, 512, 16384), (200, 136, 1000)])
+def test_gemm_mn_major_operands(pkg, mode, M, N, K):
+    """dx = dy W (mode 1, B read as [K][N]) and dW = dy^T x (mode 2, both operands [K][.]) on the
+    tensor-core engine against fp32 torch and the CUDA-core engine."""
+    lib = pkg.library()
+    g = torch.Generator(device="cpu").manual_seed(M + N + K + mode)
+    a = torch.randn((M, K) if mode == 1 else (K, M), generator=g).to(torch.bfloat16).cuda()
+    b = torch.randn(K, N, generator=g).to(torch.bfloat16).cuda()
+    ref = (a.float() if mode == 1 else a.float().T) @ b.float()
+    for backend in (pkg.abi.GEMM_SIMT, pkg.abi.GEMM_TCGEN05):
+        c = torch.full((M, N), float("nan"), device="cuda")
+        rc = lib.nncu_gemm_bf16(backend, mode, M, N, K, a.data_ptr(), a.shape[1], b.data_ptr(), N, c.data_ptr(),
+                                N, 1, None)
+        assert rc == 0, lib.nncu_last_error()
+        torch.cuda.synchronize()
+        err = (c - ref).abs().max().item() / ref.abs().max().item()
+        assert err < 5e-5, (backend, err)
+
+
 def test_gemm_rows_do_not_depend_on_the_launch(pkg):
     """A row computed in a 32-row launch equals the same row of a 2048-row launch, bit for bit,
     on both engines (what lets the encoder run whole segments and the decoder single symbols)."""
