@@ -23,6 +23,7 @@ struct AttnArgs {
     void *o, *dq, *dkv;
     float *lse, *dwr_part, *dbr_part;
     int B, H, dk, T, M, L, P, attn_len, t0, t1, qchunk;
+    int qp, kvp, dqp, dkvp; // row pitches (elements) of q, kv, dq, dkv; K then V inside a kv row
     float br_scale, inv_sqrt;
 };
 
@@ -102,7 +103,7 @@ __global__ void __launch_bounds__(256) attn_fwd_kernel(AttnArgs a)
     const int nj = jhi_all - jlo_all + 1;
     for (int idx = threadIdx.x; idx < nj * a.dk; idx += blockDim.x) {
         int j = jlo_all + idx / a.dk, e = idx % a.dk;
-        const T *src = kv + ((size_t)j * a.B + b) * 2 * HD + h * a.dk + e;
+        const T *src = kv + ((size_t)j * a.B + b) * a.kvp + h * a.dk + e;
         Ks[(size_t)j * ks + e] = src[0];
         Vs[(size_t)j * a.dk + e] = src[HD];
     }
@@ -117,7 +118,7 @@ __global__ void __launch_bounds__(256) attn_fwd_kernel(AttnArgs a)
     const T *q = reinterpret_cast<const T *>(a.q);
     T *o = reinterpret_cast<T *>(a.o);
     for (int i = i_first + warp; i <= i_last; i += 8) {
-        const T *qi = q + ((size_t)i * a.B + b) * HD + h * a.dk;
+        const T *qi = q + ((size_t)i * a.B + b) * a.qp + h * a.dk;
         for (int e = lane; e < a.dk; e += 32)
             qf[e] = to_f(qi[e]);
         __syncwarp();
@@ -190,7 +191,7 @@ __global__ void __launch_bounds__(256) attn_bwd_kernel(AttnArgs a)
     const T *dout = reinterpret_cast<const T *>(a.dout);
     for (int idx = threadIdx.x; idx < L * dk; idx += blockDim.x) {
         int j = idx / dk, e = idx % dk;
-        const T *src = kv + ((size_t)j * a.B + b) * 2 * HD + h * dk + e;
+        const T *src = kv + ((size_t)j * a.B + b) * a.kvp + h * dk + e;
         Ks[(size_t)j * ks + e] = src[0];
         Vs[(size_t)j * dk + e] = src[HD];
     }
@@ -201,9 +202,8 @@ __global__ void __launch_bounds__(256) attn_bwd_kernel(AttnArgs a)
         }
     for (int idx = threadIdx.x; idx < Tn * dk; idx += blockDim.x) {
         int i = idx / dk, e = idx % dk;
-        size_t g = ((size_t)i * a.B + b) * HD + h * dk + e;
-        qs[idx] = to_f(q[g]);
-        dos[idx] = to_f(dout[g]);
+        qs[idx] = to_f(q[((size_t)i * a.B + b) * a.qp + h * dk + e]);
+        dos[idx] = to_f(dout[((size_t)i * a.B + b) * HD + h * dk + e]);
     }
     for (int idx = threadIdx.x; idx < Tn * ls; idx += blockDim.x) {
         Pm[idx] = 0.0f;
@@ -246,7 +246,7 @@ __global__ void __launch_bounds__(256) attn_bwd_kernel(AttnArgs a)
             av = fmaf(Pm[(size_t)i * ls + j], dos[(size_t)i * dk + e], av);
             ak = fmaf(dS[(size_t)i * ls + j], qs[(size_t)i * dk + e], ak);
         }
-        T *dst = dkv + ((size_t)j * a.B + b) * 2 * HD + h * dk + e;
+        T *dst = dkv + ((size_t)j * a.B + b) * a.dkvp + h * dk + e;
         dst[0] = from_f<T>(ak);
         dst[HD] = from_f<T>(av);
     }
@@ -266,7 +266,7 @@ __global__ void __launch_bounds__(256) attn_bwd_kernel(AttnArgs a)
             }
             acc = fmaf(dS[(size_t)i * ls + j], w, acc);
         }
-        dq[((size_t)i * a.B + b) * HD + h * dk + e] = from_f<T>(acc);
+        dq[((size_t)i * a.B + b) * a.dqp + h * dk + e] = from_f<T>(acc);
     }
     // table gradients of this (stream, head): slot r collects pairs (i, j = r-(T-1-i))
     if (a.w_r && a.dwr_part) {
@@ -323,7 +323,12 @@ static int attn_check_shape(const nncu_attn_shape *s)
     return NNCU_OK;
 }
 
-static AttnArgs attn_args(const nncu_attn_shape *s)
+// row pitches when q / kv / dq / dkv are column ranges of wider buffers (0 = packed)
+struct AttnPitch {
+    int qp, kvp, dqp, dkvp;
+};
+
+static AttnArgs attn_args(const nncu_attn_shape *s, const AttnPitch *pt = nullptr)
 {
     AttnArgs a;
     memset(&a, 0, sizeof(a));
@@ -333,14 +338,23 @@ static AttnArgs attn_args(const nncu_attn_shape *s)
     a.t0 = s->t0; a.t1 = s->t1;
     a.br_scale = s->br_scale;
     a.inv_sqrt = 1.0f / sqrtf((float)s->d_key);
+    a.qp = a.dqp = a.H * a.dk;
+    a.kvp = a.dkvp = 2 * a.H * a.dk;
+    if (pt) {
+        if (pt->qp) a.qp = pt->qp;
+        if (pt->kvp) a.kvp = pt->kvp;
+        if (pt->dqp) a.dqp = pt->dqp;
+        if (pt->dkvp) a.dkvp = pt->dkvp;
+    }
     return a;
 }
 
 template <typename T>
 static int attn_forward_t(const nncu_attn_shape *s, const void *q, const void *kv, const float *w_r,
-                          const float *b_r, void *out, float *lse, cudaStream_t st)
+                          const float *b_r, void *out, float *lse, cudaStream_t st,
+                          const AttnPitch *pt = nullptr)
 {
-    AttnArgs a = attn_args(s);
+    AttnArgs a = attn_args(s, pt);
     a.q = q; a.kv = kv; a.w_r = w_r; a.b_r = b_r; a.o = out; a.lse = lse;
     const int nq = a.t1 - a.t0;
     // enough CTAs to fill the GPU, but at least 8 queries (one per warp) per CTA
@@ -360,9 +374,9 @@ template <typename T>
 static int attn_backward_t(const nncu_attn_shape *s, const void *q, const void *kv,
                            const float *w_r, const float *b_r, const void *out, const float *lse,
                            const void *dout, void *dq, void *dkv, float *dwr_part,
-                           float *dbr_part, cudaStream_t st)
+                           float *dbr_part, cudaStream_t st, const AttnPitch *pt = nullptr)
 {
-    AttnArgs a = attn_args(s);
+    AttnArgs a = attn_args(s, pt);
     if (a.t0 != 0 || a.t1 != a.T)
         return nncu_fail(NNCU_ERR_INVALID, "attention backward runs over the whole segment");
     a.q = q; a.kv = kv; a.w_r = w_r; a.b_r = b_r; a.out = out; a.lse = const_cast<float *>(lse);

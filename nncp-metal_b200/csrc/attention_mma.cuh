@@ -197,11 +197,11 @@ __global__ void __launch_bounds__(128) attn_fwd_mma_kernel(AttnArgs a)
 
     const bf16 *q = reinterpret_cast<const bf16 *>(a.q);
     const bf16 *kv = reinterpret_cast<const bf16 *>(a.kv);
-    load_tile(Qs, d.LDS, q + ((size_t)qt0 * a.B + b) * HD + h * DK, (size_t)a.B * HD, 64, DK,
+    load_tile(Qs, d.LDS, q + ((size_t)qt0 * a.B + b) * a.qp + h * DK, (size_t)a.B * a.qp, 64, DK,
               [&](int r) { return qt0 + r >= a.t0 && qt0 + r < a.t1; });
-    load_tile(Ks, d.LDS, kv + (size_t)b * 2 * HD + h * DK, (size_t)a.B * 2 * HD, d.Lp, DK,
+    load_tile(Ks, d.LDS, kv + (size_t)b * a.kvp + h * DK, (size_t)a.B * a.kvp, d.Lp, DK,
               [&](int r) { return r < a.L; });
-    load_tile(Vs, d.LDS, kv + (size_t)b * 2 * HD + HD + h * DK, (size_t)a.B * 2 * HD, d.Lp, DK,
+    load_tile(Vs, d.LDS, kv + (size_t)b * a.kvp + HD + h * DK, (size_t)a.B * a.kvp, d.Lp, DK,
               [&](int r) { return r < a.L; });
     load_table(Rs, d.LDS, a.w_r ? a.w_r + (size_t)h * a.P * DK : nullptr, a.P, d.Pr, DK);
     for (int r = threadIdx.x; r < a.L; r += blockDim.x)
@@ -352,10 +352,10 @@ __global__ void __launch_bounds__(256) attn_bwd_mma_kernel(AttnArgs a)
     const bf16 *kv = reinterpret_cast<const bf16 *>(a.kv);
     const bf16 *dout = reinterpret_cast<const bf16 *>(a.dout);
     const bf16 *outp = reinterpret_cast<const bf16 *>(a.out);
-    load_tile(Qs, d.LDS, q + (size_t)b * HD + h * DK, (size_t)a.B * HD, 64, DK, [&](int r) { return r < T; });
+    load_tile(Qs, d.LDS, q + (size_t)b * a.qp + h * DK, (size_t)a.B * a.qp, 64, DK, [&](int r) { return r < T; });
     load_tile(dOs, d.LDS, dout + (size_t)b * HD + h * DK, (size_t)a.B * HD, 64, DK, [&](int r) { return r < T; });
-    load_tile(Ks, d.LDS, kv + (size_t)b * 2 * HD + h * DK, (size_t)a.B * 2 * HD, d.Lp, DK, [&](int r) { return r < L; });
-    load_tile(Vs, d.LDS, kv + (size_t)b * 2 * HD + HD + h * DK, (size_t)a.B * 2 * HD, d.Lp, DK,
+    load_tile(Ks, d.LDS, kv + (size_t)b * a.kvp + h * DK, (size_t)a.B * a.kvp, d.Lp, DK, [&](int r) { return r < L; });
+    load_tile(Vs, d.LDS, kv + (size_t)b * a.kvp + HD + h * DK, (size_t)a.B * a.kvp, d.Lp, DK,
               [&](int r) { return r < L; });
     load_table(Rs, d.LDS, a.w_r ? a.w_r + (size_t)h * P * DK : nullptr, P, d.Pr, DK);
     for (int r = threadIdx.x; r < L; r += blockDim.x)
@@ -512,7 +512,7 @@ __global__ void __launch_bounds__(256) attn_bwd_mma_kernel(AttnArgs a)
         for (int hh = 0; hh < 2; hh++) {
             const int j = jm0 + g + hh * 8;
             if (j < L) {
-                bf16 *dst = dkv + ((size_t)j * a.B + b) * 2 * HD + h * DK;
+                bf16 *dst = dkv + ((size_t)j * a.B + b) * a.dkvp + h * DK;
 #pragma unroll
                 for (int nt = 0; nt < NT; nt++) {
                     *reinterpret_cast<uint32_t *>(dst + nt * 8 + 2 * t) = pack2(dk[nt][2 * hh], dk[nt][2 * hh + 1]);
@@ -573,7 +573,7 @@ __global__ void __launch_bounds__(256) attn_bwd_mma_kernel(AttnArgs a)
             for (int hh = 0; hh < 2; hh++) {
                 const int i = i0 + g + hh * 8;
                 if (i < T) {
-                    bf16 *dst = dqg + ((size_t)i * a.B + b) * HD + h * DK;
+                    bf16 *dst = dqg + ((size_t)i * a.B + b) * a.dqp + h * DK;
 #pragma unroll
                     for (int nt = 0; nt < NT; nt++) {
                         float x0 = dq[nt][2 * hh], x1 = dq[nt][2 * hh + 1];
@@ -707,24 +707,26 @@ static bool attn_force_simt()
 
 template <typename T>
 static int attn_forward_any(const nncu_attn_shape *s, const void *q, const void *kv, const float *w_r,
-                            const float *b_r, void *out, float *lse, cudaStream_t st)
+                            const float *b_r, void *out, float *lse, cudaStream_t st,
+                            const AttnPitch *pt = nullptr)
 {
     if (sizeof(T) == 2 && !attn_force_simt()) {
-        AttnArgs a = attn_args(s);
+        AttnArgs a = attn_args(s, pt);
         a.q = q; a.kv = kv; a.w_r = w_r; a.b_r = b_r; a.o = out; a.lse = lse;
         if (amma::supported(a, false))
             return amma::forward(a, st);
     }
-    return attn_forward_t<T>(s, q, kv, w_r, b_r, out, lse, st);
+    return attn_forward_t<T>(s, q, kv, w_r, b_r, out, lse, st, pt);
 }
 
 template <typename T>
 static int attn_backward_any(const nncu_attn_shape *s, const void *q, const void *kv, const float *w_r,
                              const float *b_r, const void *out, const float *lse, const void *dout,
-                             void *dq, void *dkv, float *dwr_part, float *dbr_part, cudaStream_t st)
+                             void *dq, void *dkv, float *dwr_part, float *dbr_part, cudaStream_t st,
+                             const AttnPitch *pt = nullptr)
 {
     if (sizeof(T) == 2 && !attn_force_simt()) {
-        AttnArgs a = attn_args(s);
+        AttnArgs a = attn_args(s, pt);
         if (a.t0 == 0 && a.t1 == a.T) {
             a.q = q; a.kv = kv; a.w_r = w_r; a.b_r = b_r; a.out = out; a.lse = const_cast<float *>(lse);
             a.dout = dout; a.dq = dq; a.dkv = dkv; a.dwr_part = dwr_part; a.dbr_part = dbr_part;
@@ -732,5 +734,5 @@ static int attn_backward_any(const nncu_attn_shape *s, const void *q, const void
                 return amma::backward(a, st);
         }
     }
-    return attn_backward_t<T>(s, q, kv, w_r, b_r, out, lse, dout, dq, dkv, dwr_part, dbr_part, st);
+    return attn_backward_t<T>(s, q, kv, w_r, b_r, out, lse, dout, dq, dkv, dwr_part, dbr_part, st, pt);
 }

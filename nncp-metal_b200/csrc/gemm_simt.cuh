@@ -20,7 +20,7 @@ template <int BM, int BN, int TM, int TN, int MODE, typename TA, typename TB, ty
 __global__ void __launch_bounds__(256)
 gemm_simt_kernel(int M, int N, int K, const TA *__restrict__ A, long lda,
                  const TB *__restrict__ B, long ldb, TC *__restrict__ C, long ldc,
-                 const float *__restrict__ bias, int accumulate)
+                 const float *__restrict__ bias, int accumulate, int bias_n)
 {
     constexpr int BK = 16;
     constexpr int LDAS = BM + 4, LDBS = BN + 4;
@@ -99,7 +99,7 @@ gemm_simt_kernel(int M, int N, int K, const TA *__restrict__ A, long lda,
             if (gn >= N)
                 continue;
             float v = acc[i][j];
-            if (bias)
+            if (bias && gn < bias_n)
                 v += bias[gn];
             TC *dst = C + (long)gm * ldc + gn;
             if (accumulate)
@@ -111,17 +111,17 @@ gemm_simt_kernel(int M, int N, int K, const TA *__restrict__ A, long lda,
 
 template <int MODE, typename TA, typename TB, typename TC>
 static int gemm_simt_mode(cudaStream_t st, int M, int N, int K, const TA *A, long lda,
-                          const TB *B, long ldb, TC *C, long ldc, const float *bias, int acc)
+                          const TB *B, long ldb, TC *C, long ldc, const float *bias, int acc, int bias_n)
 {
     long big_tiles = (long)ceil_div(M, 128) * ceil_div(N, 128);
     if (big_tiles >= 96) {
         dim3 grid(ceil_div(N, 128), ceil_div(M, 128));
         gemm_simt_kernel<128, 128, 8, 8, MODE, TA, TB, TC>
-            <<<grid, 256, 0, st>>>(M, N, K, A, lda, B, ldb, C, ldc, bias, acc);
+            <<<grid, 256, 0, st>>>(M, N, K, A, lda, B, ldb, C, ldc, bias, acc, bias_n);
     } else {
         dim3 grid(ceil_div(N, 64), ceil_div(M, 64));
         gemm_simt_kernel<64, 64, 4, 4, MODE, TA, TB, TC>
-            <<<grid, 256, 0, st>>>(M, N, K, A, lda, B, ldb, C, ldc, bias, acc);
+            <<<grid, 256, 0, st>>>(M, N, K, A, lda, B, ldb, C, ldc, bias, acc, bias_n);
     }
     KERNEL_CHECK();
     return NNCU_OK;
@@ -129,14 +129,14 @@ static int gemm_simt_mode(cudaStream_t st, int M, int N, int K, const TA *A, lon
 
 template <typename TA, typename TB, typename TC>
 static int gemm_simt(cudaStream_t st, int mode, int M, int N, int K, const TA *A, long lda,
-                     const TB *B, long ldb, TC *C, long ldc, const float *bias, int acc)
+                     const TB *B, long ldb, TC *C, long ldc, const float *bias, int acc, int bias_n = 1 << 30)
 {
     if (M <= 0 || N <= 0)
         return NNCU_OK;
     switch (mode) {
-    case GEMM_NT: return gemm_simt_mode<GEMM_NT>(st, M, N, K, A, lda, B, ldb, C, ldc, bias, acc);
-    case GEMM_NN: return gemm_simt_mode<GEMM_NN>(st, M, N, K, A, lda, B, ldb, C, ldc, bias, acc);
-    case GEMM_TN: return gemm_simt_mode<GEMM_TN>(st, M, N, K, A, lda, B, ldb, C, ldc, bias, acc);
+    case GEMM_NT: return gemm_simt_mode<GEMM_NT>(st, M, N, K, A, lda, B, ldb, C, ldc, bias, acc, bias_n);
+    case GEMM_NN: return gemm_simt_mode<GEMM_NN>(st, M, N, K, A, lda, B, ldb, C, ldc, bias, acc, bias_n);
+    case GEMM_TN: return gemm_simt_mode<GEMM_TN>(st, M, N, K, A, lda, B, ldb, C, ldc, bias, acc, bias_n);
     }
     return nncu_fail(NNCU_ERR_INVALID, "gemm_simt: bad mode %d", mode);
 }

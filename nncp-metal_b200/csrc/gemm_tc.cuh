@@ -182,7 +182,7 @@ template <int BN, typename TC, bool AMN, bool BMN>
 __global__ void __launch_bounds__(192, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                TC *C, long ldc, const float *__restrict__ bias, const TC *addsrc, int M, int N,
-               int K, int *err_flag)
+               int K, int *err_flag, int bias_n)
 {
     using SL = SmemLayout<BN>;
     extern __shared__ unsigned char smraw_[];
@@ -301,7 +301,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 #pragma unroll
                     for (int j = 0; j < 32; j++) {
                         x[j] = __uint_as_float(r[j]);
-                        if (bias && j < nvalid)
+                        if (bias && j < nvalid && n0 + c0 + j < bias_n)
                             x[j] += bias[n0 + c0 + j];
                     }
                     const bool vec = nvalid == 32 && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0) &&
@@ -443,7 +443,7 @@ static bool usable(const void *A, long lda, const void *B, long ldb, int K)
 
 template <int BN, typename TC, bool AMN, bool BMN>
 static int launch(cudaStream_t st, int M, int N, int K, const bf16 *A, long lda, const bf16 *B,
-                  long ldb, TC *C, long ldc, const float *bias, const TC *addsrc, int *err_flag)
+                  long ldb, TC *C, long ldc, const float *bias, const TC *addsrc, int *err_flag, int bias_n)
 {
     using SL = SmemLayout<BN>;
     CUtensorMap ma, mb;
@@ -466,7 +466,7 @@ static int launch(cudaStream_t st, int M, int N, int K, const bf16 *A, long lda,
     const bool timed = pr && pr->n < GemmProfiler::MAX_EV;
     if (timed)
         cudaEventRecord(pr->ev[2 * pr->n], st);
-    gemm_tc_kernel<BN, TC, AMN, BMN><<<grid, 192, SL::TOTAL, st>>>(ma, mb, C, ldc, bias, addsrc, M, N, K, err_flag);
+    gemm_tc_kernel<BN, TC, AMN, BMN><<<grid, 192, SL::TOTAL, st>>>(ma, mb, C, ldc, bias, addsrc, M, N, K, err_flag, bias_n);
     if (timed) {
         cudaEventRecord(pr->ev[2 * pr->n + 1], st);
         pr->flops[pr->n++] = 2.0 * M * N * K;
@@ -480,7 +480,8 @@ static int launch(cudaStream_t st, int M, int N, int K, const bf16 *A, long lda,
 // bounded wait expires.
 template <typename TC, bool AMN, bool BMN>
 static int gemm(cudaStream_t st, int M, int N, int K, const bf16 *A, long lda, const bf16 *B,
-                long ldb, TC *C, long ldc, const float *bias, const TC *addsrc, int *err_flag)
+                long ldb, TC *C, long ldc, const float *bias, const TC *addsrc, int *err_flag,
+                int bias_n = 1 << 30)
 {
     if (M <= 0 || N <= 0)
         return NNCU_OK;
@@ -489,17 +490,18 @@ static int gemm(cudaStream_t st, int M, int N, int K, const bf16 *A, long lda, c
     // the widest tile that still gives enough CTAs to fill the 148 SMs
     const long mt = ceil_div(M, BM);
     if (mt * ceil_div(N, 256) >= 120)
-        return launch<256, TC, AMN, BMN>(st, M, N, K, A, lda, B, ldb, C, ldc, bias, addsrc, err_flag);
+        return launch<256, TC, AMN, BMN>(st, M, N, K, A, lda, B, ldb, C, ldc, bias, addsrc, err_flag, bias_n);
     if (mt * ceil_div(N, 128) >= 120 || N <= 64)
-        return launch<128, TC, AMN, BMN>(st, M, N, K, A, lda, B, ldb, C, ldc, bias, addsrc, err_flag);
-    return launch<64, TC, AMN, BMN>(st, M, N, K, A, lda, B, ldb, C, ldc, bias, addsrc, err_flag);
+        return launch<128, TC, AMN, BMN>(st, M, N, K, A, lda, B, ldb, C, ldc, bias, addsrc, err_flag, bias_n);
+    return launch<64, TC, AMN, BMN>(st, M, N, K, A, lda, B, ldb, C, ldc, bias, addsrc, err_flag, bias_n);
 }
 
 template <typename TC>
 static int gemm_nt(cudaStream_t st, int M, int N, int K, const bf16 *A, long lda, const bf16 *B,
-                   long ldb, TC *C, long ldc, const float *bias, const TC *addsrc, int *err_flag)
+                   long ldb, TC *C, long ldc, const float *bias, const TC *addsrc, int *err_flag,
+                   int bias_n = 1 << 30)
 {
-    return gemm<TC, false, false>(st, M, N, K, A, lda, B, ldb, C, ldc, bias, addsrc, err_flag);
+    return gemm<TC, false, false>(st, M, N, K, A, lda, B, ldb, C, ldc, bias, addsrc, err_flag, bias_n);
 }
 
 } // namespace tc

@@ -60,7 +60,7 @@ struct LayerOff {
 };
 
 struct LayerAct {
-    void *xin, *q, *kv, *o, *s1, *y, *u, *hpre, *hact, *s2;
+    void *xin, *qkv, *o, *s1, *y, *u, *hpre, *hact, *s2; // qkv: [L*B][q | k | v], q unused in memory rows
     float *lse, *st_pre1, *st_1, *st_pre2, *st_2;
 };
 
@@ -88,7 +88,7 @@ struct nncu_model {
     char *hcat[2];
     int cur;
     std::vector<LayerAct> act;
-    void *xlast, *xf, *pool[4], *dz, *dh, *dhp, *dof, *dq, *dkv, *tA, *tB;
+    void *xlast, *xf, *pool[4], *dz, *dh, *dhp, *dof, *dqkv, *tA, *tB;
     float *st_f, *probs, *dwr_part, *dbr_part, *part, *logp, *loss_dev;
     int32_t *ids_dev, *tgt_dev;
     int *err_flag;
@@ -139,28 +139,30 @@ static int check_err_flag(nncu_model *m)
 // y = x W^T (+bias): C[M][N] = A[M][K] . Wt[N][K]^T
 template <typename AT, typename TC>
 static int mm_nt(nncu_model *m, int M, int N, int K, const AT *A, long lda, size_t w_off, TC *C,
-                 long ldc, const float *bias);
+                 long ldc, const float *bias, int bias_n = 1 << 30);
 
 template <typename TC>
 static int mm_nt_impl(nncu_model *m, int M, int N, int K, const float *A, long lda, size_t w_off,
-                      TC *C, long ldc, const float *bias)
+                      TC *C, long ldc, const float *bias, int bias_n)
 {
-    return gemm_simt<float, float, TC>(m->st, GEMM_NT, M, N, K, A, lda, m->W + w_off, K, C, ldc, bias, 0);
+    return gemm_simt<float, float, TC>(m->st, GEMM_NT, M, N, K, A, lda, m->W + w_off, K, C, ldc, bias, 0,
+                                       bias_n);
 }
 template <typename TC>
 static int mm_nt_impl(nncu_model *m, int M, int N, int K, const bf16 *A, long lda, size_t w_off,
-                      TC *C, long ldc, const float *bias)
+                      TC *C, long ldc, const float *bias, int bias_n)
 {
     const bf16 *Wt = m->Wb + w_off;
     if (m->use_tc && tc::usable(A, lda, Wt, K, K))
-        return tc::gemm_nt<TC>(m->st, M, N, K, A, lda, Wt, K, C, ldc, bias, nullptr, m->err_flag);
-    return gemm_simt<bf16, bf16, TC>(m->st, GEMM_NT, M, N, K, A, lda, Wt, K, C, ldc, bias, 0);
+        return tc::gemm_nt<TC>(m->st, M, N, K, A, lda, Wt, K, C, ldc, bias, nullptr, m->err_flag, bias_n);
+    return gemm_simt<bf16, bf16, TC>(m->st, GEMM_NT, M, N, K, A, lda, Wt, K, C, ldc, bias, 0, bias_n);
 }
+// bias (if any) is added to output columns n < bias_n only
 template <typename AT, typename TC>
 static int mm_nt(nncu_model *m, int M, int N, int K, const AT *A, long lda, size_t w_off, TC *C,
-                 long ldc, const float *bias)
+                 long ldc, const float *bias, int bias_n)
 {
-    return mm_nt_impl<TC>(m, M, N, K, A, lda, w_off, C, ldc, bias);
+    return mm_nt_impl<TC>(m, M, N, K, A, lda, w_off, C, ldc, bias, bias_n);
 }
 
 // MN-major tensor-core operands (default) or explicit transposes (NNCU_TC_TRANSPOSE=1)
@@ -319,14 +321,18 @@ static int forward_range(nncu_model *m, int t0, int t1)
             NNCU_TRY(norm_fwd<AT>(m, xin, nullptr, nullptr, x1, o.ln_g1, o.ln_b1, a.st_pre1 + 2 * r0, nr, true));
         // fused projections over [memory ; segment]: Q for the segment rows, K|V for the
         // memory rows (once per segment) and the segment rows (nncp.c:659-695)
-        NNCU_TRY((mm_nt<AT, AT>(m, nr, HD, D, x1, D, o.w_q, at<AT>(a.q, (size_t)r0 * HD), HD, wf(m, o.b_q))));
+        // one GEMM against [w_q ; w_kv] (adjacent in the flat buffers): rows of the memory get
+        // a q they never use, which costs less than a second launch
         if (t0 == 0 && M > 0)
-            NNCU_TRY((mm_nt<AT, AT>(m, M * B + nr, 2 * HD, D, hc, D, o.w_kv, at<AT>(a.kv, 0), 2 * HD, nullptr)));
+            NNCU_TRY((mm_nt<AT, AT>(m, M * B + nr, 3 * HD, D, hc, D, o.w_q, at<AT>(a.qkv, 0), 3 * HD,
+                                    wf(m, o.b_q), HD)));
         else
-            NNCU_TRY((mm_nt<AT, AT>(m, nr, 2 * HD, D, x1, D, o.w_kv,
-                                    at<AT>(a.kv, ((size_t)M * B + r0) * 2 * HD), 2 * HD, nullptr)));
+            NNCU_TRY((mm_nt<AT, AT>(m, nr, 3 * HD, D, x1, D, o.w_q,
+                                    at<AT>(a.qkv, ((size_t)M * B + r0) * 3 * HD), 3 * HD, wf(m, o.b_q), HD)));
         nncu_attn_shape s = attn_shape(m, l, t0, t1);
-        NNCU_TRY(attn_forward_any<AT>(&s, a.q, a.kv, wf(m, o.w_r), m->W + o.b_r, a.o, a.lse, m->st));
+        const AttnPitch pt = {3 * HD, 3 * HD, 3 * HD, 3 * HD};
+        NNCU_TRY(attn_forward_any<AT>(&s, at<AT>(a.qkv, (size_t)M * B * 3 * HD), at<AT>(a.qkv, HD),
+                                      wf(m, o.w_r), m->W + o.b_r, a.o, a.lse, m->st, &pt));
         // output projection, residual, post-LN (nncp.c:865-920)
         NNCU_TRY((mm_nt<AT, AT>(m, nr, D, HD, at<AT>(a.o, (size_t)r0 * HD), HD, o.w_o, tmp, D, nullptr)));
         AT *yy = at<AT>(a.y, (size_t)r0 * D);
@@ -386,8 +392,11 @@ static int backward(nncu_model *m)
     const bool pre = p.ln_flags & NNCU_LN_PRE, post = p.ln_flags & NNCU_LN_POST;
     AT *dz = reinterpret_cast<AT *>(m->dz);
     AT *dh = reinterpret_cast<AT *>(m->dh), *dhp = reinterpret_cast<AT *>(m->dhp);
-    AT *dof = reinterpret_cast<AT *>(m->dof), *dq = reinterpret_cast<AT *>(m->dq);
-    AT *dkv = reinterpret_cast<AT *>(m->dkv);
+    AT *dof = reinterpret_cast<AT *>(m->dof);
+    // [L*B][dq | dk | dv]; the dq columns of the memory rows are never written and stay zero
+    AT *dqkv = reinterpret_cast<AT *>(m->dqkv);
+    AT *dq = dqkv + (size_t)M * B * 3 * HD, *dkv = dqkv + HD;
+    const AttnPitch pt = {3 * HD, 3 * HD, 3 * HD, 3 * HD};
 
     // loss and d logits (nncp.c:1170-1175)
     const float sc = 1.0f / ((float)m->T * (float)m->Bt);
@@ -416,7 +425,6 @@ static int backward(nncu_model *m)
         const LayerOff &o = m->lo[l];
         LayerAct &a = m->act[l];
         const AT *hc = reinterpret_cast<const AT *>(hcat_layer(m, m->cur, l));
-        const AT *x1 = hc + (size_t)M * B * D;
         // ---- feed-forward block
         AT *ds2 = dx;
         if (post) {
@@ -453,8 +461,9 @@ static int backward(nncu_model *m)
         NNCU_TRY(mm_tn(m, D, HD, TB, ds1, D, atc<AT>(a.o, 0), HD, gf(m, o.w_o)));
         NNCU_TRY(mm_nn(m, TB, HD, D, ds1, D, o.w_o, dof, HD, (const AT *)nullptr));
         nncu_attn_shape s = attn_shape(m, l, 0, m->T);
-        NNCU_TRY(attn_backward_any<AT>(&s, a.q, a.kv, wf(m, o.w_r), m->W + o.b_r, a.o, a.lse, dof, dq, dkv,
-                                     m->dwr_part, m->dbr_part, m->st));
+        NNCU_TRY(attn_backward_any<AT>(&s, at<AT>(a.qkv, (size_t)M * B * 3 * HD), at<AT>(a.qkv, HD), wf(m, o.w_r),
+                                       m->W + o.b_r, a.o, a.lse, dof, dq, dkv, m->dwr_part, m->dbr_part, m->st,
+                                       &pt));
         {
             size_t nb = (size_t)m->H * m->L;
             reduce_streams_kernel<<<ceil_div(nb, 256), 256, 0, m->st>>>(m->dbr_part, B, nb, gf(m, o.b_r),
@@ -467,21 +476,18 @@ static int backward(nncu_model *m)
                 KERNEL_CHECK();
             }
         }
-        NNCU_TRY(mm_tn(m, HD, D, TB, dq, HD, x1, D, gf(m, o.w_q)));
+        // d[w_q ; w_kv] = [dq | dk | dv]^T [memory ; segment] in one contraction over all L*B rows
+        NNCU_TRY(mm_tn(m, 3 * HD, D, LB, dqkv, 3 * HD, hc, D, gf(m, o.w_q)));
         if (o.b_q != NONE)
-            NNCU_TRY(colsum<AT>(m, dq, HD, TB, HD, gf(m, o.b_q)));
-        NNCU_TRY(mm_tn(m, 2 * HD, D, LB, dkv, 2 * HD, hc, D, gf(m, o.w_kv)));
-        // d(attention input) = dq W_q + dkv[segment rows] W_kv; the memory rows get no gradient
-        const AT *dkv_seg = dkv + (size_t)M * B * 2 * HD;
+            NNCU_TRY(colsum<AT>(m, dq, 3 * HD, TB, HD, gf(m, o.b_q)));
+        // d(attention input) = [dq | dk | dv](segment rows) [w_q ; w_kv]; the memory rows get no gradient
         AT *dxn = pick<AT>(m, {ds1});
         if (pre) {
             AT *dx1 = pick<AT>(m, {ds1, dxn});
-            NNCU_TRY(mm_nn(m, TB, D, HD, dq, HD, o.w_q, dx1, D, (const AT *)nullptr));
-            NNCU_TRY(mm_nn(m, TB, D, 2 * HD, dkv_seg, 2 * HD, o.w_kv, dx1, D, (const AT *)dx1));
+            NNCU_TRY(mm_nn(m, TB, D, 3 * HD, dq, 3 * HD, o.w_q, dx1, D, (const AT *)nullptr));
             NNCU_TRY(norm_bwd<AT>(m, dx1, atc<AT>(a.xin, 0), o.ln_g1, o.ln_b1, a.st_pre1, ds1, dxn, TB));
         } else {
-            NNCU_TRY(mm_nn(m, TB, D, HD, dq, HD, o.w_q, dxn, D, (const AT *)ds1));
-            NNCU_TRY(mm_nn(m, TB, D, 2 * HD, dkv_seg, 2 * HD, o.w_kv, dxn, D, (const AT *)dxn));
+            NNCU_TRY(mm_nn(m, TB, D, 3 * HD, dq, 3 * HD, o.w_q, dxn, D, (const AT *)ds1));
         }
         dx = dxn;
     }
@@ -582,7 +588,8 @@ static void init_values(float *dst, size_t n, const char *name, uint32_t seed, i
     }
 }
 
-static size_t add_param(nncu_model *m, const char *base, int idx, size_t numel, int rows = 0, int cols = 0)
+static size_t add_param(nncu_model *m, const char *base, int idx, size_t numel, int rows = 0, int cols = 0,
+                        bool pad = true)
 {
     ParamInfo pi;
     memset(&pi, 0, sizeof(pi));
@@ -594,7 +601,9 @@ static size_t add_param(nncu_model *m, const char *base, int idx, size_t numel, 
     pi.off = m->n_floats;
     pi.rows = rows;
     pi.cols = cols;
-    m->n_floats += (numel + 127) & ~(size_t)127;
+    m->n_floats += numel;
+    if (pad)
+        m->n_floats = (m->n_floats + 127) & ~(size_t)127; // the next slot starts 512-byte aligned
     m->pinfo.push_back(pi);
     return pi.off;
 }
@@ -619,6 +628,8 @@ static int validate(const nncu_params *p)
         return nncu_fail(NNCU_ERR_INVALID, "ff_act %d is not supported", p->ff_act);
     if (p->use_bf16 && (p->d_key & 1))
         return nncu_fail(NNCU_ERR_INVALID, "bf16 models need an even d_key");
+    if (((long)p->n_head * p->d_key * p->d_model) % 8)
+        return nncu_fail(NNCU_ERR_INVALID, "n_head * d_key * d_model must be a multiple of 8");
     if (p->gemm_backend == NNCU_GEMM_TCGEN05 && !p->use_bf16)
         return nncu_fail(NNCU_ERR_INVALID, "the tcgen05 backend needs a bf16 model");
     for (int l = 0; l < p->n_layer; l++)
@@ -702,7 +713,8 @@ int nncu_create(const nncu_params *p, nncu_model **out)
     m->lo.resize(m->nl);
     for (int l = 0; l < m->nl; l++) {
         LayerOff &o = m->lo[l];
-        o.w_q = add_param(m, "w_q", l, (size_t)HD * D, HD, D);
+        // w_q and w_kv are contiguous: together they are the [3*H*dk][D] matrix of the fused projection
+        o.w_q = add_param(m, "w_q", l, (size_t)HD * D, HD, D, false);
         o.w_kv = add_param(m, "w_kv", l, (size_t)2 * HD * D, 2 * HD, D);
         o.b_q = p->query_bias ? add_param(m, "b_q", l, HD) : NONE;
         o.w_o = add_param(m, "w_o", l, (size_t)D * HD, D, HD);
@@ -747,13 +759,12 @@ int nncu_create(const nncu_params *p, nncu_model **out)
     size_t oW = take(m->n_floats * 4), oG = take(m->n_floats * 4), oV = take(m->n_floats * 4);
     size_t oWb = m->bf ? take(m->n_floats * 2) : 0, oWbT = m->bf ? take(m->n_floats * 2) : 0;
     size_t oH0 = take((size_t)m->nl * LB * D * e), oH1 = take((size_t)m->nl * LB * D * e);
-    struct LOff { size_t xin, q, kv, o, s1, y, u, hpre, hact, s2, lse, sp1, s_1, sp2, s_2; };
+    struct LOff { size_t xin, qkv, o, s1, y, u, hpre, hact, s2, lse, sp1, s_1, sp2, s_2; };
     std::vector<LOff> lofs(m->nl);
     for (int l = 0; l < m->nl; l++) {
         LOff &x = lofs[l];
         x.xin = pre ? take((size_t)TB * D * e) : NONE;
-        x.q = take((size_t)TB * HD * e);
-        x.kv = take((size_t)LB * 2 * HD * e);
+        x.qkv = take((size_t)LB * 3 * HD * e);
         x.o = take((size_t)TB * HD * e);
         x.s1 = post ? take((size_t)TB * D * e) : NONE;
         x.y = take((size_t)TB * D * e);
@@ -773,9 +784,9 @@ int nncu_create(const nncu_params *p, nncu_model **out)
     for (int i = 0; i < 4; i++)
         oPool[i] = take((size_t)TB * D * e);
     size_t oDz = take((size_t)TB * V * e), oDh = take((size_t)TB * F * e), oDhp = take((size_t)TB * F1 * e);
-    size_t oDof = take((size_t)TB * HD * e), oDq = take((size_t)TB * HD * e);
-    size_t oDkv = take((size_t)LB * 2 * HD * e);
-    size_t max_n = (size_t)std::max(std::max(V, F1), std::max(2 * HD, D));
+    size_t oDof = take((size_t)TB * HD * e);
+    size_t oDqkv = take((size_t)LB * 3 * HD * e);
+    size_t max_n = (size_t)std::max(std::max(V, F1), std::max(3 * HD, D));
     size_t max_k = (size_t)std::max(std::max(F, D), HD);
     size_t oTA = m->use_tc ? take(max_n * LB * 2) : 0, oTB = m->use_tc ? take(max_k * LB * 2) : 0;
     size_t oWr = take((size_t)m->B * m->H * p->d_pos * m->dk * 4), oBr = take((size_t)m->B * m->H * m->L * 4);
@@ -820,7 +831,7 @@ int nncu_create(const nncu_params *p, nncu_model **out)
     m->xlast = A + oXlast; m->xf = A + oXf; m->st_f = (float *)(A + oStf); m->probs = (float *)(A + oProbs);
     for (int i = 0; i < 4; i++)
         m->pool[i] = A + oPool[i];
-    m->dz = A + oDz; m->dh = A + oDh; m->dhp = A + oDhp; m->dof = A + oDof; m->dq = A + oDq; m->dkv = A + oDkv;
+    m->dz = A + oDz; m->dh = A + oDh; m->dhp = A + oDhp; m->dof = A + oDof; m->dqkv = A + oDqkv;
     m->tA = m->use_tc ? A + oTA : nullptr; m->tB = m->use_tc ? A + oTB : nullptr;
     m->dwr_part = (float *)(A + oWr); m->dbr_part = (float *)(A + oBr); m->part = (float *)(A + oPart);
     m->logp = (float *)(A + oLogp); m->loss_dev = (float *)(A + oLoss);
@@ -832,7 +843,7 @@ int nncu_create(const nncu_params *p, nncu_model **out)
     for (int l = 0; l < m->nl; l++) {
         LOff &x = lofs[l];
         LayerAct &a = m->act[l];
-        a.q = A + x.q; a.kv = A + x.kv; a.o = A + x.o; a.y = A + x.y; a.hpre = A + x.hpre; a.hact = A + x.hact;
+        a.qkv = A + x.qkv; a.o = A + x.o; a.y = A + x.y; a.hpre = A + x.hpre; a.hact = A + x.hact;
         a.s1 = post ? A + x.s1 : nullptr; a.s2 = post ? A + x.s2 : nullptr; a.u = pre ? A + x.u : nullptr;
         a.lse = (float *)(A + x.lse); a.st_pre1 = (float *)(A + x.sp1); a.st_1 = (float *)(A + x.s_1);
         a.st_pre2 = (float *)(A + x.sp2); a.st_2 = (float *)(A + x.s_2);
