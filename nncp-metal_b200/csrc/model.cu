@@ -77,6 +77,9 @@ struct nncu_model {
     size_t esz;   // bytes per activation element
     int device;
     cudaStream_t st;
+    cudaStream_t st2;            // weight-gradient GEMMs run here, beside the dX chain
+    cudaEvent_t ev_fork, ev_join;
+    bool overlap;
     std::vector<ParamInfo> pinfo;
     std::vector<LayerOff> lo;
     size_t ln_g, ln_b, embed, embed_out, out_bias, n_floats;
@@ -205,10 +208,29 @@ static int mm_nn(nncu_model *m, int M, int Kin, int Nout, const bf16 *dY, long l
 }
 
 // dW = dY^T X: G[Nout][Kin] = sum over R rows of dY[r][Nout] X[r][Kin]   (fp32 result)
+// The weight gradients are off the critical path of the backward pass (nothing downstream
+// reads them before the optimizer), so they go to a second stream: fork after the operands
+// exist, join once per layer before any operand buffer is reused.
+static cudaStream_t side_fork(nncu_model *m)
+{
+    if (!m->overlap || g_nncu_prof)
+        return m->st;
+    cudaEventRecord(m->ev_fork, m->st);
+    cudaStreamWaitEvent(m->st2, m->ev_fork, 0);
+    return m->st2;
+}
+static void side_join(nncu_model *m)
+{
+    if (!m->overlap || g_nncu_prof)
+        return;
+    cudaEventRecord(m->ev_join, m->st2);
+    cudaStreamWaitEvent(m->st, m->ev_join, 0);
+}
+
 static int mm_tn(nncu_model *m, int Nout, int Kin, int R, const float *dY, long ldy, const float *X,
                  long ldx, float *Gout)
 {
-    return gemm_simt<float, float, float>(m->st, GEMM_TN, Nout, Kin, R, dY, ldy, X, ldx, Gout, Kin,
+    return gemm_simt<float, float, float>(side_fork(m), GEMM_TN, Nout, Kin, R, dY, ldy, X, ldx, Gout, Kin,
                                           nullptr, 0);
 }
 static int mm_tn(nncu_model *m, int Nout, int Kin, int R, const bf16 *dY, long ldy, const bf16 *X,
@@ -216,8 +238,8 @@ static int mm_tn(nncu_model *m, int Nout, int Kin, int R, const bf16 *dY, long l
 {
     if (m->use_tc && tc_mn_major() && tc::usable(dY, ldy, X, ldx, R))
         // dY is [R][Nout] = [k][m], X is [R][Kin] = [k][n]: both MN-major, read in place
-        return tc::gemm<float, true, true>(m->st, Nout, Kin, R, dY, ldy, X, ldx, Gout, Kin, nullptr, nullptr,
-                                           m->err_flag);
+        return tc::gemm<float, true, true>(side_fork(m), Nout, Kin, R, dY, ldy, X, ldx, Gout, Kin, nullptr,
+                                           nullptr, m->err_flag);
     if (m->use_tc && (R % 8) == 0) {
         // both operands become K-major by an explicit transpose (the contraction runs over rows)
         bf16 *tA = reinterpret_cast<bf16 *>(m->tA), *tB = reinterpret_cast<bf16 *>(m->tB);
@@ -230,7 +252,7 @@ static int mm_tn(nncu_model *m, int Nout, int Kin, int R, const bf16 *dY, long l
         return tc::gemm_nt<float>(m->st, Nout, Kin, R, tA, R, tB, R, Gout, Kin, nullptr, nullptr,
                                   m->err_flag);
     }
-    return gemm_simt<bf16, bf16, float>(m->st, GEMM_TN, Nout, Kin, R, dY, ldy, X, ldx, Gout, Kin,
+    return gemm_simt<bf16, bf16, float>(side_fork(m), GEMM_TN, Nout, Kin, R, dY, ldy, X, ldx, Gout, Kin,
                                         nullptr, 0);
 }
 
@@ -455,7 +477,7 @@ static int backward(nncu_model *m)
         // ---- attention block
         AT *ds1 = dy;
         if (post) {
-            ds1 = pick<AT>(m, {dy});
+            ds1 = pick<AT>(m, {dy, ds2});
             NNCU_TRY(norm_bwd<AT>(m, dy, atc<AT>(a.s1, 0), o.ln_g1, o.ln_b1, a.st_1, nullptr, ds1, TB));
         }
         NNCU_TRY(mm_tn(m, D, HD, TB, ds1, D, atc<AT>(a.o, 0), HD, gf(m, o.w_o)));
@@ -481,20 +503,22 @@ static int backward(nncu_model *m)
         if (o.b_q != NONE)
             NNCU_TRY(colsum<AT>(m, dq, 3 * HD, TB, HD, gf(m, o.b_q)));
         // d(attention input) = [dq | dk | dv](segment rows) [w_q ; w_kv]; the memory rows get no gradient
-        AT *dxn = pick<AT>(m, {ds1});
+        AT *dxn = pick<AT>(m, {ds1, ds2}); // ds1, ds2 are still read by weight-gradient GEMMs
         if (pre) {
-            AT *dx1 = pick<AT>(m, {ds1, dxn});
+            AT *dx1 = pick<AT>(m, {ds1, ds2, dxn});
             NNCU_TRY(mm_nn(m, TB, D, 3 * HD, dq, 3 * HD, o.w_q, dx1, D, (const AT *)nullptr));
             NNCU_TRY(norm_bwd<AT>(m, dx1, atc<AT>(a.xin, 0), o.ln_g1, o.ln_b1, a.st_pre1, ds1, dxn, TB));
         } else {
             NNCU_TRY(mm_nn(m, TB, D, 3 * HD, dq, 3 * HD, o.w_q, dxn, D, (const AT *)ds1));
         }
+        side_join(m); // this layer's weight gradients are done before dhp, dqkv, ds1, ds2 are rewritten
         dx = dxn;
     }
     const float emul = sqrtf((float)D) * p.embed_mult;
     CUDA_TRY(cudaMemsetAsync(gf(m, m->embed), 0, sizeof(float) * (size_t)V * D, m->st));
     embed_grad_kernel<AT><<<TB, 128, 2 * sizeof(int32_t) * TB, m->st>>>(m->ids_dev, dx, gf(m, m->embed), TB, D, emul, V);
     KERNEL_CHECK();
+    side_join(m);
     return NNCU_OK;
 }
 
@@ -662,6 +686,9 @@ int nncu_destroy(nncu_model *m)
         return NNCU_OK;
     cudaSetDevice(m->device);
     cudaStreamSynchronize(m->st);
+    if (m->st2) { cudaStreamSynchronize(m->st2); cudaStreamDestroy(m->st2); }
+    if (m->ev_fork) cudaEventDestroy(m->ev_fork);
+    if (m->ev_join) cudaEventDestroy(m->ev_join);
     if (m->arena) cudaFree(m->arena);
     if (m->ids_pin) cudaFreeHost(m->ids_pin);
     if (m->tgt_pin) cudaFreeHost(m->tgt_pin);
@@ -693,6 +720,9 @@ int nncu_create(const nncu_params *p, nncu_model **out)
     m->p = *p;
     m->device = dev;
     m->st = 0;
+    m->st2 = nullptr;
+    m->ev_fork = m->ev_join = nullptr;
+    m->overlap = false;
     m->D = p->d_model; m->H = p->n_head; m->dk = p->d_key; m->HD = m->H * m->dk; m->F = p->d_inner;
     m->F1 = (p->ff_act == NNCU_FF_GEGLU) ? 2 * m->F : m->F;
     m->T = p->seg_len; m->B = p->n_streams; m->M = p->mem_len; m->L = m->M + m->T; m->V = p->n_symbols;
@@ -848,6 +878,12 @@ int nncu_create(const nncu_params *p, nncu_model **out)
         a.lse = (float *)(A + x.lse); a.st_pre1 = (float *)(A + x.sp1); a.st_1 = (float *)(A + x.s_1);
         a.st_pre2 = (float *)(A + x.sp2); a.st_2 = (float *)(A + x.s_2);
         a.xin = pre ? A + x.xin : nullptr; // without pre-LN the residual input IS the hcat segment part
+    }
+    if (cudaStreamCreateWithFlags(&m->st2, cudaStreamNonBlocking) == cudaSuccess &&
+        cudaEventCreateWithFlags(&m->ev_fork, cudaEventDisableTiming) == cudaSuccess &&
+        cudaEventCreateWithFlags(&m->ev_join, cudaEventDisableTiming) == cudaSuccess) {
+        const char *e = getenv("NNCU_NO_OVERLAP");
+        m->overlap = !(e && e[0] == '1');
     }
     if (cudaMallocHost(&m->ids_pin, sizeof(int32_t) * TB) != cudaSuccess ||
         cudaMallocHost(&m->tgt_pin, sizeof(int32_t) * TB) != cudaSuccess ||
