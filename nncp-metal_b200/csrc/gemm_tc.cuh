@@ -173,13 +173,14 @@ struct SmemLayout {
     static constexpr int A_BYTES = BM * BK * 2;
     static constexpr int B_BYTES = BN * BK * 2;
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-    static constexpr int STAGES = (BN == 256) ? 4 : 4;
+    static constexpr int STAGES = (BN == 128) ? 3 : 4; // BN <= 128: 96 KB, two CTAs per SM
     static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES;
     static constexpr int TOTAL = BAR_OFFSET + 256 + 1024; // + barriers + alignment slack
+    static constexpr int CTAS_PER_SM = (2 * TOTAL <= 227 * 1024) ? 2 : 1;
 };
 
 template <int BN, typename TC, bool AMN, bool BMN>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(192, SmemLayout<BN>::CTAS_PER_SM)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                TC *C, long ldc, const float *__restrict__ bias, const TC *addsrc, int M, int N,
                int K, int *err_flag, int bias_n)
@@ -199,6 +200,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     const int nkb = (K + BK - 1) / BK;
 
     if (threadIdx.x == 0) {
+        asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_a)) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_b)) : "memory");
         for (int s = 0; s < SL::STAGES; s++) {
             mbar_init(smem_u32(&full[s]), 1);
             mbar_init(smem_u32(&empty[s]), 1);
