@@ -20,6 +20,7 @@
 struct AttnArgs {
     const void *q, *kv, *out, *dout;
     const float *w_r, *b_r;
+    const void *w_r16; // optional bf16 copy of w_r (same layout), used by the tensor-core kernels
     void *o, *dq, *dkv;
     float *lse, *dwr_part, *dbr_part;
     int B, H, dk, T, M, L, P, attn_len, t0, t1, qchunk;

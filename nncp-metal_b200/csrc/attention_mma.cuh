@@ -83,8 +83,15 @@ __device__ __forceinline__ void load_tile(bf16 *dst, int lds, const bf16 *src, s
     }
 }
 
-__device__ __forceinline__ void load_table(bf16 *dst, int lds, const float *w_r_h, int P, int Pr, int dk)
+// position table of one head: from the bf16 copy (16-byte chunks) when there is one,
+// else converted from fp32; rows [P, Pr) are zero
+__device__ __forceinline__ void load_table(bf16 *dst, int lds, const float *w_r_h, const bf16 *w16_h, int P,
+                                           int Pr, int dk)
 {
+    if (w16_h) {
+        load_tile(dst, lds, w16_h, (size_t)dk, Pr, dk, [&](int r) { return r < P; });
+        return;
+    }
     for (int idx = threadIdx.x; idx < Pr * dk; idx += blockDim.x) {
         int p = idx / dk, e = idx % dk;
         dst[(size_t)p * lds + e] = (w_r_h && p < P) ? __float2bfloat16_rn(w_r_h[(size_t)p * dk + e])
@@ -203,7 +210,8 @@ __global__ void __launch_bounds__(128) attn_fwd_mma_kernel(AttnArgs a)
               [&](int r) { return r < a.L; });
     load_tile(Vs, d.LDS, kv + (size_t)b * a.kvp + HD + h * DK, (size_t)a.B * a.kvp, d.Lp, DK,
               [&](int r) { return r < a.L; });
-    load_table(Rs, d.LDS, a.w_r ? a.w_r + (size_t)h * a.P * DK : nullptr, a.P, d.Pr, DK);
+    load_table(Rs, d.LDS, a.w_r ? a.w_r + (size_t)h * a.P * DK : nullptr,
+               a.w_r16 ? reinterpret_cast<const bf16 *>(a.w_r16) + (size_t)h * a.P * DK : nullptr, a.P, d.Pr, DK);
     for (int r = threadIdx.x; r < a.L; r += blockDim.x)
         brs[r] = a.br_scale * a.b_r[(size_t)h * a.L + r];
     __syncthreads();
@@ -357,23 +365,19 @@ __global__ void __launch_bounds__(256) attn_bwd_mma_kernel(AttnArgs a)
     load_tile(Ks, d.LDS, kv + (size_t)b * a.kvp + h * DK, (size_t)a.B * a.kvp, d.Lp, DK, [&](int r) { return r < L; });
     load_tile(Vs, d.LDS, kv + (size_t)b * a.kvp + HD + h * DK, (size_t)a.B * a.kvp, d.Lp, DK,
               [&](int r) { return r < L; });
-    load_table(Rs, d.LDS, a.w_r ? a.w_r + (size_t)h * P * DK : nullptr, P, d.Pr, DK);
+    load_table(Rs, d.LDS, a.w_r ? a.w_r + (size_t)h * P * DK : nullptr,
+               a.w_r16 ? reinterpret_cast<const bf16 *>(a.w_r16) + (size_t)h * P * DK : nullptr, P, d.Pr, DK);
     for (int r = threadIdx.x; r < L; r += blockDim.x)
         brs[r] = a.br_scale * a.b_r[(size_t)h * L + r];
-    {
-        uint32_t *z = reinterpret_cast<uint32_t *>(Pm); // P, dS, dE are contiguous
-        const int n = (2 * 64 * d.LPS + 64 * d.PPS) / 2;
-        for (int i = threadIdx.x; i < n; i += blockDim.x)
-            z[i] = 0u;
-    }
+    // the forward output, parked in the skew scratch (not needed before phase A)
+    bf16 *Os = reinterpret_cast<bf16 *>(Es);
+    load_tile(Os, d.LDS, outp + (size_t)b * HD + h * DK, (size_t)a.B * HD, 64, DK, [&](int r) { return r < T; });
+    __syncthreads();
     // D_i = dO_i . O_i and the saved log-sum-exp, one warp per 8 rows
     for (int r = warp * 8; r < warp * 8 + 8; r++) {
         float s = 0.0f;
-        if (r < T) {
-            const size_t go = ((size_t)r * a.B + b) * HD + h * DK;
-            for (int e = lane; e < DK; e += 32)
-                s += to_f(dout[go + e]) * to_f(outp[go + e]);
-        }
+        for (int e = lane; e < DK; e += 32)
+            s += to_f(dOs[(size_t)r * d.LDS + e]) * to_f(Os[(size_t)r * d.LDS + e]);
         s = warp_sum(s);
         if (lane == 0) {
             Dr[r] = s;
@@ -386,7 +390,15 @@ __global__ void __launch_bounds__(256) attn_bwd_mma_kernel(AttnArgs a)
     {
         const int i0 = (warp & 3) * 16, half = warp >> 2;
         const int va = i0, vb = min(i0 + 16, T) - 1;
-        if (va <= vb) {
+        if (va > vb) {
+            // no query row here: the P / dS rows of this tile are zero
+            for (int kb = half; kb < d.Lp / 64; kb += 2)
+                for (int idx = lane; idx < 16 * 32; idx += 32) {
+                    const size_t o2 = (size_t)(i0 + idx / 32) * d.LPS + kb * 64 + (idx % 32) * 2;
+                    *reinterpret_cast<uint32_t *>(Pm + o2) = 0u;
+                    *reinterpret_cast<uint32_t *>(dSm + o2) = 0u;
+                }
+        } else {
             uint32_t qf[KS][4], df[KS][4];
 #pragma unroll
             for (int ks = 0; ks < KS; ks++) {
@@ -405,10 +417,16 @@ __global__ void __launch_bounds__(256) attn_bwd_mma_kernel(AttnArgs a)
             const float lseA = lses[i0 + g], lseB = lses[i0 + g + 8];
             const float DA = Dr[i0 + g], DB = Dr[i0 + g + 8];
             float *es = Es + (size_t)warp * 16 * EW;
-            for (int kb = jmin / 64; kb <= jmax / 64; kb++) {
-                if ((kb & 1) != half)
-                    continue;
+            for (int kb = half; kb < d.Lp / 64; kb += 2) {
                 const int j0 = kb * 64;
+                if (kb < jmin / 64 || kb > jmax / 64) { // nothing visible in this block
+                    for (int idx = lane; idx < 16 * 32; idx += 32) {
+                        const size_t o2 = (size_t)(i0 + idx / 32) * d.LPS + j0 + (idx % 32) * 2;
+                        *reinterpret_cast<uint32_t *>(Pm + o2) = 0u;
+                        *reinterpret_cast<uint32_t *>(dSm + o2) = 0u;
+                    }
+                    continue;
+                }
                 float s[8][4], dp[8][4];
                 score_block<DK>(a, d, qf, Ks, Rs, brs, es, i0, j0, iA, iB, jloA, jhiA, jloB, jhiB, s);
 #pragma unroll
@@ -708,11 +726,12 @@ static bool attn_force_simt()
 template <typename T>
 static int attn_forward_any(const nncu_attn_shape *s, const void *q, const void *kv, const float *w_r,
                             const float *b_r, void *out, float *lse, cudaStream_t st,
-                            const AttnPitch *pt = nullptr)
+                            const AttnPitch *pt = nullptr, const void *w_r16 = nullptr)
 {
     if (sizeof(T) == 2 && !attn_force_simt()) {
         AttnArgs a = attn_args(s, pt);
         a.q = q; a.kv = kv; a.w_r = w_r; a.b_r = b_r; a.o = out; a.lse = lse;
+        a.w_r16 = w_r ? w_r16 : nullptr;
         if (amma::supported(a, false))
             return amma::forward(a, st);
     }
@@ -723,10 +742,11 @@ template <typename T>
 static int attn_backward_any(const nncu_attn_shape *s, const void *q, const void *kv, const float *w_r,
                              const float *b_r, const void *out, const float *lse, const void *dout,
                              void *dq, void *dkv, float *dwr_part, float *dbr_part, cudaStream_t st,
-                             const AttnPitch *pt = nullptr)
+                             const AttnPitch *pt = nullptr, const void *w_r16 = nullptr)
 {
     if (sizeof(T) == 2 && !attn_force_simt()) {
         AttnArgs a = attn_args(s, pt);
+        a.w_r16 = w_r ? w_r16 : nullptr;
         if (a.t0 == 0 && a.t1 == a.T) {
             a.q = q; a.kv = kv; a.w_r = w_r; a.b_r = b_r; a.out = out; a.lse = const_cast<float *>(lse);
             a.dout = dout; a.dq = dq; a.dkv = dkv; a.dwr_part = dwr_part; a.dbr_part = dbr_part;

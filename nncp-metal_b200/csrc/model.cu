@@ -354,7 +354,8 @@ static int forward_range(nncu_model *m, int t0, int t1)
         nncu_attn_shape s = attn_shape(m, l, t0, t1);
         const AttnPitch pt = {3 * HD, 3 * HD, 3 * HD, 3 * HD};
         NNCU_TRY(attn_forward_any<AT>(&s, at<AT>(a.qkv, (size_t)M * B * 3 * HD), at<AT>(a.qkv, HD),
-                                      wf(m, o.w_r), m->W + o.b_r, a.o, a.lse, m->st, &pt));
+                                      wf(m, o.w_r), m->W + o.b_r, a.o, a.lse, m->st, &pt,
+                                      (m->bf && o.w_r != NONE) ? m->Wb + o.w_r : nullptr));
         // output projection, residual, post-LN (nncp.c:865-920)
         NNCU_TRY((mm_nt<AT, AT>(m, nr, D, HD, at<AT>(a.o, (size_t)r0 * HD), HD, o.w_o, tmp, D, nullptr)));
         AT *yy = at<AT>(a.y, (size_t)r0 * D);
@@ -485,7 +486,7 @@ static int backward(nncu_model *m)
         nncu_attn_shape s = attn_shape(m, l, 0, m->T);
         NNCU_TRY(attn_backward_any<AT>(&s, at<AT>(a.qkv, (size_t)M * B * 3 * HD), at<AT>(a.qkv, HD), wf(m, o.w_r),
                                        m->W + o.b_r, a.o, a.lse, dof, dq, dkv, m->dwr_part, m->dbr_part, m->st,
-                                       &pt));
+                                       &pt, (m->bf && o.w_r != NONE) ? m->Wb + o.w_r : nullptr));
         {
             size_t nb = (size_t)m->H * m->L;
             reduce_streams_kernel<<<ceil_div(nb, 256), 256, 0, m->st>>>(m->dbr_part, B, nb, gf(m, o.b_r),
