@@ -16,8 +16,8 @@
 //   warp 1      TMEM allocation, MMA issue (one lane), TMEM release
 //   warps 2-5   epilogue: warp w owns TMEM lanes 32*(w%4) .. +31 = tile rows
 //
-// Out-of-range rows/columns/k are zero-filled by TMA on load and predicated
-// off on store, so M, N are arbitrary and K only needs 16-byte row strides.
+// Out-of-range rows/columns/k are zero-filled by TMA on load and clipped by TMA
+// on store (the tile is staged in the idle operand ring, 128-byte swizzled), so M, N are arbitrary and K only needs 16-byte row strides.
 // Every wait is bounded: on expiry the kernel raises *err_flag and leaves
 // through the common exit that releases TMEM.
 //
@@ -90,6 +90,11 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map
                  "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(x), "r"(y)
                  : "memory");
 }
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi)
+{
+    __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t *>(&h);
+}
 __device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t ncols)
 {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem),
@@ -124,7 +129,8 @@ __device__ __forceinline__ void umma_commit(uint32_t bar)
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
                  : "memory");
 }
-// 32 lanes x 32 consecutive fp32 columns: thread t gets row (lane base + t)
+// 32 lanes x 32 consecutive fp32 columns: thread t gets row (lane base + t).  Asynchronous:
+// the registers are valid after tmem_ld_wait().
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t *r)
 {
     asm volatile(
@@ -138,6 +144,9 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t *r)
           "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
         : "r"(taddr)
         : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait()
+{
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
@@ -168,6 +177,21 @@ __device__ __forceinline__ uint64_t smem_desc_sw128_mn(uint32_t addr)
     return d;
 }
 
+#ifdef NNCU_GEMM_TRACE
+// tuning aid (off in normal builds): per-CTA clock64() stamps of the kernel's phases
+__device__ long long *g_tc_trace = nullptr;
+#define TC_STAMP(slot)                                                   \
+    do {                                                                 \
+        long long *t_ = g_tc_trace;                                      \
+        if (t_ && blockIdx.x + blockIdx.y * gridDim.x < 128)             \
+            t_[(blockIdx.x + blockIdx.y * gridDim.x) * 16 + (slot)] = clock64(); \
+    } while (0)
+#else
+#define TC_STAMP(slot) \
+    do {               \
+    } while (0)
+#endif
+
 template <int BN>
 struct SmemLayout {
     static constexpr int A_BYTES = BM * BK * 2;
@@ -182,7 +206,7 @@ struct SmemLayout {
 template <int BN, typename TC, bool AMN, bool BMN>
 __global__ void __launch_bounds__(192, SmemLayout<BN>::CTAS_PER_SM)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-               TC *C, long ldc, const float *__restrict__ bias, const TC *addsrc, int M, int N,
+               const __grid_constant__ CUtensorMap map_c, int staged, TC *C, long ldc, const float *__restrict__ bias, const TC *addsrc, int M, int N,
                int K, int *err_flag, int bias_n)
 {
     using SL = SmemLayout<BN>;
@@ -200,6 +224,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     const int nkb = (K + BK - 1) / BK;
 
     if (threadIdx.x == 0) {
+        TC_STAMP(0);
         asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_a)) : "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_b)) : "memory");
         for (int s = 0; s < SL::STAGES; s++) {
@@ -217,6 +242,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     __syncthreads();
     fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
+    if (threadIdx.x == 0)
+        TC_STAMP(1);
 
     if (warp == 0) {
         if (lane == 0) {
@@ -227,6 +254,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     !mbar_wait(smem_u32(&empty[s]), ph ^ 1, abort_s, err_flag, 1))
                     break;
                 const uint32_t fb = smem_u32(&full[s]);
+                if (kb == 0)
+                    TC_STAMP(2);
                 mbar_expect_tx(fb, SL::STAGE_BYTES);
                 unsigned char *a_dst = sm + s * SL::STAGE_BYTES;
                 if (AMN) {
@@ -257,6 +286,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 ok = mbar_wait(smem_u32(&full[s]), ph, abort_s, err_flag, 2);
                 if (!ok)
                     break;
+                if (kb == 0)
+                    TC_STAMP(3);
                 fence_after_sync();
                 const uint32_t a_addr = smem_u32(sm + s * SL::STAGE_BYTES);
                 const uint64_t adesc = AMN ? smem_desc_sw128_mn(a_addr) : smem_desc_sw128(a_addr);
@@ -271,6 +302,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                               (kb > 0 || k > 0) ? 1u : 0u);
                 umma_commit(smem_u32(&empty[s])); // frees the stage when these MMAs retire
             }
+            TC_STAMP(4);
             if (ok)
                 umma_commit(smem_u32(tmem_full));
         }
@@ -281,90 +313,177 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         if (nkb > 0)
             ok = mbar_wait(smem_u32(tmem_full), 0, abort_s, err_flag, 3);
         ok = __all_sync(0xffffffffu, ok); // tcgen05.ld below is warp-collective
+        if (threadIdx.x == 64)
+            TC_STAMP(5);
         fence_after_sync();
         const int row = m0 + quarter * 32 + lane;
         if (ok) {
-#pragma unroll 1
-            for (int c0 = 0; c0 < BN; c0 += 32) {
-                if (n0 + c0 >= N)
-                    break; // uniform over the warp
-                uint32_t r[32];
-                if (nkb > 0) {
-                    tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0, r);
-                } else {
+            // Each thread holds one output row, so storing straight from registers would touch 32
+            // different lines per instruction.  The warp parks 32 rows x 128 bytes in shared
+            // memory (the operand ring is idle by now; 128-byte swizzle) and a TMA store, which
+            // also clips the ragged edges, takes them out; two buffers per warp.  (Reading the
+            // block back for row-wise global stores measured slower than the TMA store.)
+            constexpr int CPB = (sizeof(TC) == 2) ? 2 : 1; // 32-column chunks per 128-byte block
+            constexpr int NCH = BN / 32;
+            unsigned char *stage0 = sm + quarter * 8192;
+            const uint32_t trow = tmem_base + ((uint32_t)(quarter * 32) << 16);
+            // chunks still inside the matrix (uniform over the CTA)
+            const int nch = min(NCH, (N - n0 + 31) / 32);
+            // TMEM reads are pipelined one chunk ahead of the arithmetic and the stores.  The loop
+            // is kept rolled (two chunks per trip, one per register set): unrolled over the tile
+            // it would run once through code larger than the instruction cache.
+            uint32_t ra[32], rb[32];
+            if (nkb > 0) {
+                tmem_ld32(trow, ra);
+                tmem_ld_wait();
+            } else {
 #pragma unroll
-                    for (int j = 0; j < 32; j++)
-                        r[j] = 0u;
+                for (int j = 0; j < 32; j++)
+                    ra[j] = rb[j] = 0u;
+            }
+            auto chunk = [&](int ch, const uint32_t(&r)[32]) {
+                const int c0 = ch * 32, cc = ch % CPB, blk = ch / CPB;
+                unsigned char *stg = stage0 + (blk & 1) * 4096;
+                if (staged && cc == 0) {
+                    if (lane == 0) // the store issued two blocks ago has finished reading this buffer
+                        asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+                    __syncwarp();
                 }
-                if (row < M) {
-                    TC *dst = C + (long)row * ldc + n0 + c0;
-                    const TC *add = addsrc ? addsrc + (long)row * ldc + n0 + c0 : nullptr;
-                    const int nvalid = min(32, N - (n0 + c0));
-                    float x[32];
+                const int nvalid = N - (n0 + c0); // > 0 here, may exceed 32
+                const bool full = nvalid >= 32;
+                float x[32];
 #pragma unroll
-                    for (int j = 0; j < 32; j++) {
-                        x[j] = __uint_as_float(r[j]);
-                        if (bias && j < nvalid && n0 + c0 + j < bias_n)
-                            x[j] += bias[n0 + c0 + j];
-                    }
-                    const bool vec = nvalid == 32 && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0) &&
-                                     (!add || (reinterpret_cast<uintptr_t>(add) & 15) == 0);
-                    if (vec) {
-                        if (sizeof(TC) == 2) {
-                            if (add) {
-                                const uint4 *a4 = reinterpret_cast<const uint4 *>(add);
+                for (int j = 0; j < 32; j++)
+                    x[j] = __uint_as_float(r[j]);
+                // Straight-line vector paths for whole chunks; element-wise code (one branch per
+                // element) only at ragged edges.
+                if (bias) {
+                    const float *bp = bias + n0 + c0;
+                    if (full && n0 + c0 + 32 <= bias_n && (reinterpret_cast<uintptr_t>(bp) & 15) == 0) {
 #pragma unroll
-                                for (int v = 0; v < 4; v++) {
-                                    uint4 t = a4[v];
-                                    const uint32_t w[4] = {t.x, t.y, t.z, t.w};
-#pragma unroll
-                                    for (int u = 0; u < 4; u++) {
-                                        __nv_bfloat162 h = *reinterpret_cast<const __nv_bfloat162 *>(&w[u]);
-                                        x[v * 8 + u * 2] += __low2float(h);
-                                        x[v * 8 + u * 2 + 1] += __high2float(h);
-                                    }
-                                }
-                            }
-                            uint4 *d4 = reinterpret_cast<uint4 *>(dst);
-#pragma unroll
-                            for (int v = 0; v < 4; v++) {
-                                uint32_t pk[4];
-#pragma unroll
-                                for (int u = 0; u < 4; u++) {
-                                    __nv_bfloat162 h = __floats2bfloat162_rn(x[v * 8 + u * 2], x[v * 8 + u * 2 + 1]);
-                                    pk[u] = *reinterpret_cast<uint32_t *>(&h);
-                                }
-                                d4[v] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
-                            }
-                        } else {
-                            if (add) {
-                                const float4 *a4 = reinterpret_cast<const float4 *>(add);
-#pragma unroll
-                                for (int v = 0; v < 8; v++) {
-                                    float4 t = a4[v];
-                                    x[v * 4] += t.x; x[v * 4 + 1] += t.y; x[v * 4 + 2] += t.z; x[v * 4 + 3] += t.w;
-                                }
-                            }
-                            float4 *d4 = reinterpret_cast<float4 *>(dst);
-#pragma unroll
-                            for (int v = 0; v < 8; v++)
-                                d4[v] = make_float4(x[v * 4], x[v * 4 + 1], x[v * 4 + 2], x[v * 4 + 3]);
+                        for (int v = 0; v < 8; v++) {
+                            const float4 t = __ldg(reinterpret_cast<const float4 *>(bp) + v);
+                            x[v * 4] += t.x; x[v * 4 + 1] += t.y; x[v * 4 + 2] += t.z; x[v * 4 + 3] += t.w;
                         }
                     } else {
-                        for (int j = 0; j < nvalid; j++) {
-                            float y = x[j];
-                            if (add)
-                                y += to_f(add[j]);
-                            dst[j] = from_f<TC>(y);
-                        }
+#pragma unroll
+                        for (int j = 0; j < 32; j++)
+                            if (j < nvalid && n0 + c0 + j < bias_n)
+                                x[j] += bp[j];
                     }
                 }
+                if (addsrc && row < M) {
+                    const TC *add = addsrc + (long)row * ldc + n0 + c0;
+                    if (full && (reinterpret_cast<uintptr_t>(add) & 15) == 0) {
+                        if (sizeof(TC) == 2) {
+#pragma unroll
+                            for (int v = 0; v < 4; v++) {
+                                const uint4 t = reinterpret_cast<const uint4 *>(add)[v];
+                                const uint32_t w[4] = {t.x, t.y, t.z, t.w};
+#pragma unroll
+                                for (int u = 0; u < 4; u++) {
+                                    const __nv_bfloat162 h = *reinterpret_cast<const __nv_bfloat162 *>(&w[u]);
+                                    x[v * 8 + u * 2] += __low2float(h);
+                                    x[v * 8 + u * 2 + 1] += __high2float(h);
+                                }
+                            }
+                        } else {
+#pragma unroll
+                            for (int v = 0; v < 8; v++) {
+                                const float4 t = reinterpret_cast<const float4 *>(add)[v];
+                                x[v * 4] += t.x; x[v * 4 + 1] += t.y; x[v * 4 + 2] += t.z; x[v * 4 + 3] += t.w;
+                            }
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; j++)
+                            if (j < nvalid)
+                                x[j] += to_f(add[j]);
+                    }
+                }
+                if (staged) {
+                    unsigned char *rowp = stg + lane * 128;
+                    if (sizeof(TC) == 2) {
+#pragma unroll
+                        for (int v = 0; v < 4; v++) {
+                            uint4 pk;
+                            pk.x = pack_bf16(x[v * 8 + 0], x[v * 8 + 1]);
+                            pk.y = pack_bf16(x[v * 8 + 2], x[v * 8 + 3]);
+                            pk.z = pack_bf16(x[v * 8 + 4], x[v * 8 + 5]);
+                            pk.w = pack_bf16(x[v * 8 + 6], x[v * 8 + 7]);
+                            *reinterpret_cast<uint4 *>(rowp + (((cc * 4 + v) ^ (lane & 7)) << 4)) = pk;
+                        }
+                    } else {
+#pragma unroll
+                        for (int v = 0; v < 8; v++)
+                            *reinterpret_cast<float4 *>(rowp + ((v ^ (lane & 7)) << 4)) =
+                                make_float4(x[v * 4], x[v * 4 + 1], x[v * 4 + 2], x[v * 4 + 3]);
+                    }
+                    if (cc == CPB - 1 || ch == nch - 1) {
+                        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                        __syncwarp();
+                        if (lane == 0) {
+                            asm volatile(
+                                "cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(
+                                    reinterpret_cast<uint64_t>(&map_c)),
+                                "r"(smem_u32(stg)), "r"(n0 + blk * 32 * CPB), "r"(m0 + quarter * 32)
+                                : "memory");
+                            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+                        }
+                    }
+                } else if (row < M) {
+                    TC *dst = C + (long)row * ldc + n0 + c0;
+                    if (full && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+                        if (sizeof(TC) == 2) {
+#pragma unroll
+                            for (int v = 0; v < 4; v++)
+                                reinterpret_cast<uint4 *>(dst)[v] =
+                                    make_uint4(pack_bf16(x[v * 8], x[v * 8 + 1]), pack_bf16(x[v * 8 + 2], x[v * 8 + 3]),
+                                               pack_bf16(x[v * 8 + 4], x[v * 8 + 5]), pack_bf16(x[v * 8 + 6], x[v * 8 + 7]));
+                        } else {
+#pragma unroll
+                            for (int v = 0; v < 8; v++)
+                                reinterpret_cast<float4 *>(dst)[v] =
+                                    make_float4(x[v * 4], x[v * 4 + 1], x[v * 4 + 2], x[v * 4 + 3]);
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; j++)
+                            if (j < nvalid)
+                                dst[j] = from_f<TC>(x[j]);
+                    }
+                }
+            };
+#pragma unroll 1
+            for (int ch = 0; ch < nch; ch += 2) {
+                const bool more1 = ch + 1 < nch, more2 = ch + 2 < nch;
+                if (nkb > 0 && more1)
+                    tmem_ld32(trow + (uint32_t)((ch + 1) * 32), rb);
+                chunk(ch, ra);
+                if (more1) {
+                    if (nkb > 0)
+                        tmem_ld_wait();
+                    if (nkb > 0 && more2)
+                        tmem_ld32(trow + (uint32_t)((ch + 2) * 32), ra);
+                    chunk(ch + 1, rb);
+                    if (nkb > 0 && more2)
+                        tmem_ld_wait();
+                }
             }
+            if (threadIdx.x == 64)
+                TC_STAMP(14);
+            if (staged && lane == 0)
+                asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+            __syncwarp();
         }
     }
+    if (threadIdx.x == 64)
+        TC_STAMP(6);
     // common exit: nobody touches TMEM after this barrier
     fence_before_sync();
     __syncthreads();
+    if (threadIdx.x == 0)
+        TC_STAMP(7);
     if (*abort_s) {
         // a wait gave up: let copies that are still in flight land before the CTA retires
         for (int i = 0; i < 2000; i++)
@@ -401,18 +520,22 @@ static EncodeTiledFn encode_fn()
 struct TmapKey {
     const void *ptr;
     long rows, cols, ld;
-    int box_rows;
+    int box_rows, box_cols, elt;
     bool operator<(const TmapKey &o) const
     {
-        return std::tie(ptr, rows, cols, ld, box_rows) < std::tie(o.ptr, o.rows, o.cols, o.ld, o.box_rows);
+        return std::tie(ptr, rows, cols, ld, box_rows, box_cols, elt) <
+               std::tie(o.ptr, o.rows, o.cols, o.ld, o.box_rows, o.box_cols, o.elt);
     }
 };
 
-static int make_tmap(const void *ptr, long rows, long cols, long ld, int box_rows, CUtensorMap *out)
+// 2-D map over a row-major [rows][cols] matrix of 2-byte (bf16) or 4-byte (fp32) elements,
+// boxes of box_rows x box_cols with box_cols * elt == 128 bytes, 128-byte swizzle
+static int make_tmap(const void *ptr, long rows, long cols, long ld, int box_rows, CUtensorMap *out,
+                     int box_cols = BK, int elt = 2)
 {
     static std::map<TmapKey, CUtensorMap> cache;
     static std::mutex mu;
-    TmapKey key{ptr, rows, cols, ld, box_rows};
+    TmapKey key{ptr, rows, cols, ld, box_rows, box_cols, elt};
     std::lock_guard<std::mutex> lock(mu);
     auto it = cache.find(key);
     if (it != cache.end()) {
@@ -423,10 +546,11 @@ static int make_tmap(const void *ptr, long rows, long cols, long ld, int box_row
     if (!fn)
         return nncu_fail(NNCU_ERR_CUDA, "cuTensorMapEncodeTiled is not available");
     cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-    cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
-    cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+    cuuint64_t strides[1] = {(cuuint64_t)ld * elt};
+    cuuint32_t box[2] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows};
     cuuint32_t estr[2] = {1, 1};
-    CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void *>(ptr), dims, strides,
+    CUresult r = fn(out, elt == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2,
+                    const_cast<void *>(ptr), dims, strides,
                     box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                     CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS)
@@ -458,6 +582,11 @@ static int launch(cudaStream_t st, int M, int N, int K, const bf16 *A, long lda,
         NNCU_TRY(make_tmap(B, K, N, ldb, 64, &mb));
     else
         NNCU_TRY(make_tmap(B, N, K, ldb, BN, &mb));
+    // rows of C that are 16-byte aligned leave through shared memory and TMA stores
+    CUtensorMap mc = ma;
+    const int staged = ((reinterpret_cast<uintptr_t>(C) & 15) == 0 && (ldc * sizeof(TC)) % 16 == 0) ? 1 : 0;
+    if (staged)
+        NNCU_TRY(make_tmap(C, M, N, ldc, 32, &mc, 128 / (int)sizeof(TC), (int)sizeof(TC)));
     static bool attr_done = false;
     if (!attr_done) {
         CUDA_TRY(cudaFuncSetAttribute(gemm_tc_kernel<BN, TC, AMN, BMN>,
@@ -469,7 +598,7 @@ static int launch(cudaStream_t st, int M, int N, int K, const bf16 *A, long lda,
     const bool timed = pr && pr->n < GemmProfiler::MAX_EV;
     if (timed)
         cudaEventRecord(pr->ev[2 * pr->n], st);
-    gemm_tc_kernel<BN, TC, AMN, BMN><<<grid, 192, SL::TOTAL, st>>>(ma, mb, C, ldc, bias, addsrc, M, N, K, err_flag, bias_n);
+    gemm_tc_kernel<BN, TC, AMN, BMN><<<grid, 192, SL::TOTAL, st>>>(ma, mb, mc, staged, C, ldc, bias, addsrc, M, N, K, err_flag, bias_n);
     if (timed) {
         cudaEventRecord(pr->ev[2 * pr->n + 1], st);
         pr->flops[pr->n++] = 2.0 * M * N * K;
@@ -490,11 +619,19 @@ static int gemm(cudaStream_t st, int M, int N, int K, const bf16 *A, long lda, c
         return NNCU_OK;
     if (!usable(A, lda, B, ldb, K))
         return nncu_fail(NNCU_ERR_INVALID, "tcgen05 GEMM needs 16-byte aligned operands and strides");
-    // the widest tile that still gives enough CTAs to fill the 148 SMs
+    // UMMA instructions cost about the same whatever their N, so wide tiles use the tensor
+    // pipe best; narrower ones only when the launch would otherwise have very few CTAs
     const long mt = ceil_div(M, BM);
-    if (mt * ceil_div(N, 256) >= 120)
+    static int min_tiles = 0;
+    if (!min_tiles) {
+        const char *e = getenv("NNCU_TC_MIN_TILES"); // tuning knob
+        min_tiles = e ? atoi(e) : 96;
+        if (min_tiles < 1)
+            min_tiles = 96;
+    }
+    if (mt * ceil_div(N, 256) >= min_tiles)
         return launch<256, TC, AMN, BMN>(st, M, N, K, A, lda, B, ldb, C, ldc, bias, addsrc, err_flag, bias_n);
-    if (mt * ceil_div(N, 128) >= 120 || N <= 64)
+    if (mt * ceil_div(N, 128) >= min_tiles || N <= 64)
         return launch<128, TC, AMN, BMN>(st, M, N, K, A, lda, B, ldb, C, ldc, bias, addsrc, err_flag, bias_n);
     return launch<64, TC, AMN, BMN>(st, M, N, K, A, lda, B, ldb, C, ldc, bias, addsrc, err_flag, bias_n);
 }

@@ -1405,6 +1405,14 @@ int nncu_attention_backward_noalloc(const nncu_attn_shape *s, const void *q, con
 
 // ---- dense contraction test hooks
 
+#ifdef NNCU_GEMM_TRACE
+extern "C" int nncu_gemm_trace(long long *dev_buf)
+{
+    CUDA_TRY(cudaMemcpyToSymbol(tc::g_tc_trace, &dev_buf, sizeof(dev_buf)));
+    return NNCU_OK;
+}
+#endif
+
 int nncu_gemm_bf16(int backend, int mode, int M, int N, int K, const void *A, int lda, const void *B, int ldb,
                    void *C, int ldc, int c_is_f32, void *cuda_stream)
 {

@@ -49,7 +49,8 @@ def build_library(force=False, verbose=False):
             raise LibraryMissing("nvcc not found and libnncu.so is not built")
         cmd = [nvcc] + NVCC_FLAGS + \
               ["-I", os.path.join(ROOT, "include"), "-I", CSRC] + \
-              (["-Xptxas", "-v"] if verbose else []) + ["-o", LIB] + cu
+              (["-Xptxas", "-v"] if verbose else []) + os.environ.get("NNCU_NVCC_EXTRA", "").split() + \
+              ["-o", LIB] + cu
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode != 0:
             raise RuntimeError("nvcc failed:\n" + r.stdout + r.stderr)
