@@ -226,7 +226,10 @@ def main():
     kw.update(n_streams=B, n_streams_total=Bt, gemm_backend=args.backend, device=local)
     p = pkg.abi.make_params(**kw)
     m = pkg.TrfModel(p)
-    stream = torch.cuda.current_stream()
+    # a non-default stream: the library then replays CUDA graphs of forward and backward
+    stream = torch.cuda.Stream()
+    torch.cuda.set_stream(stream)
+    m.set_stream(stream.cuda_stream)
     T, V = c["seg_len"], c["n_symbols"]
     K, W = args.steps, max(args.warmup, 3)
     ids_all, tg_all = make_batches(c, Bt, K + W)

@@ -142,7 +142,9 @@ const char *nncu_last_error(void);
 /* ---- model lifetime (trf_init / trf_end, nncp.c:304-550) ---- */
 int nncu_create(const nncu_params *p, nncu_model **out);
 int nncu_destroy(nncu_model *m);
-/* All later launches go to this cudaStream_t (default: the legacy stream 0). */
+/* All later launches go to this cudaStream_t (default: the legacy stream 0).  On any other
+   stream the whole-segment forward and the backward pass are captured into CUDA graphs on
+   their second use and replayed afterwards (same results, fewer launch gaps). */
 int nncu_set_stream(nncu_model *m, void *cuda_stream);
 
 /* ---- the 13-pointer plugin surface (nncp.c:49-69) ---- */

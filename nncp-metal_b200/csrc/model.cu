@@ -80,6 +80,13 @@ struct nncu_model {
     cudaStream_t st2;            // weight-gradient GEMMs run here, beside the dX chain
     cudaEvent_t ev_fork, ev_join;
     bool overlap;
+    // CUDA graphs of the whole-segment forward and of the backward pass, one per memory twin
+    struct StepGraph {
+        cudaGraphExec_t exec;
+        unsigned long long launches;
+        int calls;
+    } graphs[2][2];
+    bool graphs_on;
     std::vector<ParamInfo> pinfo;
     std::vector<LayerOff> lo;
     size_t ln_g, ln_b, embed, embed_out, out_bias, n_floats;
@@ -316,6 +323,59 @@ static nncu_attn_shape attn_shape(nncu_model *m, int l, int t0, int t1)
     s.br_scale = sqrtf((float)m->dk * (float)m->D);
     s.dtype_bf16 = m->bf ? 1 : 0;
     return s;
+}
+
+// ------------------------------------------------------------------ CUDA graphs
+//
+// A train step is some 370 launches of 5-20 us kernels: launch gaps are a tenth of it.  When
+// the model runs on a capturable stream (anything but the legacy default stream), the second
+// whole-segment forward / backward issued for a memory twin is captured (side stream and
+// all) and later ones replay the graph.  Operand addresses never change: ids and targets are
+// copied into fixed staging buffers before the graph runs, and the two memory twins have
+// a graph each.  One-symbol steps, the optimizer (its learning rate is a launch argument) and
+// the timed-GEMM profiling pass stay eager.
+enum { GRAPH_FWD = 0, GRAPH_BWD = 1 };
+
+template <typename F>
+static int run_graphed(nncu_model *m, int kind, F body)
+{
+    nncu_model::StepGraph &g = m->graphs[kind][m->cur];
+    const bool can = m->graphs_on && m->st != nullptr && m->st != cudaStreamLegacy && !g_nncu_prof;
+    if (!can)
+        return body();
+    if (g.exec) {
+        CUDA_TRY(cudaGraphLaunch(g.exec, m->st));
+        g_nncu_launches += g.launches;
+        return NNCU_OK;
+    }
+    if (g.calls++ < 1)
+        return body(); // first call eager: kernel attributes and tensor maps get set up
+    const unsigned long long before = g_nncu_launches;
+    if (cudaStreamBeginCapture(m->st, cudaStreamCaptureModeThreadLocal) != cudaSuccess) {
+        cudaGetLastError();
+        m->graphs_on = false;
+        return body();
+    }
+    int rc = body();
+    cudaGraph_t graph = nullptr;
+    cudaError_t e = cudaStreamEndCapture(m->st, &graph);
+    if (rc == NNCU_OK && e == cudaSuccess && graph)
+        e = cudaGraphInstantiate(&g.exec, graph, 0);
+    if (graph)
+        cudaGraphDestroy(graph);
+    if (rc != NNCU_OK || e != cudaSuccess || !g.exec) {
+        // nothing was executed during the capture: give up on graphs and run it for real
+        cudaGetLastError();
+        g.exec = nullptr;
+        m->graphs_on = false;
+        g_nncu_launches = before;
+        return rc != NNCU_OK ? rc : body();
+    }
+    g.launches = g_nncu_launches - before;
+    g_nncu_launches = before;
+    CUDA_TRY(cudaGraphLaunch(g.exec, m->st));
+    g_nncu_launches += g.launches;
+    return NNCU_OK;
 }
 
 // ------------------------------------------------------------------ forward
@@ -687,6 +747,10 @@ int nncu_destroy(nncu_model *m)
         return NNCU_OK;
     cudaSetDevice(m->device);
     cudaStreamSynchronize(m->st);
+    for (int k = 0; k < 2; k++)
+        for (int c = 0; c < 2; c++)
+            if (m->graphs[k][c].exec)
+                cudaGraphExecDestroy(m->graphs[k][c].exec);
     if (m->st2) { cudaStreamSynchronize(m->st2); cudaStreamDestroy(m->st2); }
     if (m->ev_fork) cudaEventDestroy(m->ev_fork);
     if (m->ev_join) cudaEventDestroy(m->ev_join);
@@ -724,6 +788,11 @@ int nncu_create(const nncu_params *p, nncu_model **out)
     m->st2 = nullptr;
     m->ev_fork = m->ev_join = nullptr;
     m->overlap = false;
+    memset(m->graphs, 0, sizeof(m->graphs));
+    {
+        const char *e = getenv("NNCU_NO_GRAPH");
+        m->graphs_on = !(e && e[0] == '1');
+    }
     m->D = p->d_model; m->H = p->n_head; m->dk = p->d_key; m->HD = m->H * m->dk; m->F = p->d_inner;
     m->F1 = (p->ff_act == NNCU_FF_GEGLU) ? 2 * m->F : m->F;
     m->T = p->seg_len; m->B = p->n_streams; m->M = p->mem_len; m->L = m->M + m->T; m->V = p->n_symbols;
@@ -980,7 +1049,8 @@ static int eval_common(nncu_model *m, int output_index)
         return nncu_fail(NNCU_ERR_STATE, "step %d issued after %d steps", output_index, m->steps_done);
     bind_xin(m);
     int t0 = output_index < 0 ? 0 : output_index, t1 = output_index < 0 ? m->T : output_index + 1;
-    int rc = m->bf ? forward_range<bf16>(m, t0, t1) : forward_range<float>(m, t0, t1);
+    auto body = [&]() { return m->bf ? forward_range<bf16>(m, t0, t1) : forward_range<float>(m, t0, t1); };
+    int rc = output_index < 0 ? run_graphed(m, GRAPH_FWD, body) : body();
     if (rc != NNCU_OK)
         return rc;
     m->steps_done = t1;
@@ -1050,7 +1120,7 @@ static int gradient_common(nncu_model *m)
     if (!m->have_forward)
         return nncu_fail(NNCU_ERR_STATE, "eval_gradient needs a complete forward pass first");
     bind_xin(m);
-    return m->bf ? backward<bf16>(m) : backward<float>(m);
+    return run_graphed(m, GRAPH_BWD, [&]() { return m->bf ? backward<bf16>(m) : backward<float>(m); });
 }
 
 int nncu_read_loss(nncu_model *m, float *loss_out)

@@ -287,6 +287,36 @@ def test_two_runs_are_bit_identical(pkg):
     assert hashes[0] == hashes[1]
 
 
+@pytest.mark.parametrize("name,bf16", [("c0_like", 0), ("mma_two_key_blocks", 1), ("tied_tables_longmem", 1)])
+def test_graph_replay_equals_eager(pkg, name, bf16):
+    """On a non-default stream forward and backward are captured into CUDA graphs on their second
+    use; six steps there must give the same bits as six eager steps on the default stream."""
+    cfg, z = load_golden(name)
+    rng = np.random.default_rng(1)
+    T, B, V = cfg["seg_len"], cfg["n_streams"], cfg["n_symbols"]
+    ids = rng.integers(0, V, (6, T, B)).astype(np.int32)
+    tg = rng.integers(0, V, (6, T, B)).astype(np.int32)
+    hashes, losses = [], []
+    for use_stream in (False, True):
+        m = pkg.TrfModel(params_from_cfg(pkg, cfg, use_bf16=bf16))
+        _load(m, z)
+        s = torch.cuda.Stream()
+        if use_stream:
+            m.set_stream(s.cuda_stream)
+        m.reset()
+        ls = []
+        for k in range(6):
+            m.eval(-1, ids[k], read=False)
+            ls.append(m.eval_gradient(tg[k]))
+            m.update()
+        m.synchronize()
+        hashes.append(m.weights_hash())
+        losses.append(ls)
+        m.close()
+    assert losses[0] == losses[1]
+    assert hashes[0] == hashes[1]
+
+
 def test_initial_values_match_the_oracle(pkg, oracle):
     p = pkg.abi.make_params(n_layer=1, d_model=64, n_head=2, d_key=32, d_inner=128, d_pos=16, mem_len=8,
                             seg_len=8, n_streams=2, n_symbols=64)
