@@ -111,7 +111,7 @@ class ClockSampler:
              "clocks_event_reasons.sw_power_cap")
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={q}", "--format=csv,noheader,nounits",
-                                          "-i", str(self.index), "-lms", "100"],
+                                          "-i", str(self.index), "-lms", "20"],
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             threading.Thread(target=self._read, daemon=True).start()
         except OSError:
@@ -173,6 +173,7 @@ def run_reference(args, c):
     if rank != 0:
         return
     streams = 2 if args.config == "c2" else c["n_streams"]
+    args.steps = min(args.steps, 20)   # bounded: a c2 step of 2 streams is about a second of CPU work
     val, dt = cpu_port_run(c, args.steps, min(args.warmup, 1), streams)
     cores = os.cpu_count()
     line = {"impl": "reference", "metric": "compressed symbols/s (fwd+bwd+RMSProp)", "value": val,
@@ -192,7 +193,7 @@ def run_reference(args, c):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200")
     ap.add_argument("--config", default="c2", choices=sorted(CONFIGS))
@@ -241,6 +242,9 @@ def main():
     wptr, gptr, vptr, nfl = m.flat_buffers()
     # the flat gradient buffer as a torch tensor (for the NCCL all-reduce)
     grads = torch.as_tensor(pkg.dist.CudaArray(gptr, nfl), device=f"cuda:{local}") if world > 1 else None
+    if world > 1 and os.environ.get("NNCU_PY_ALLREDUCE") != "1":
+        # per-layer all-reduces inside the backward pass instead of one all-reduce after it
+        pkg.dist.attach_library_comm(m, lib, rank, world, torch.device("cuda", local))
     sharded = pkg.dist.ShardedStep(m, grads, world=world)
 
     def step_device(s):
@@ -284,7 +288,6 @@ def main():
     prof = pkg.abi.Profile()
     lib.nncu_profile_end(C.byref(prof))
     ms = e0.elapsed_time(e1)
-    clocks = sampler.stop() if sampler else None
     m.synchronize()
     if world > 1:
         t = torch.tensor([ms], device="cuda")
@@ -304,6 +307,7 @@ def main():
     e1.record(stream)
     barrier()
     ms_e2e = max(e0.elapsed_time(e1), (time.perf_counter() - t0) * 1e3)
+    clocks = sampler.stop() if sampler else None   # sampled over both timed regions
     if world > 1:
         t = torch.tensor([ms_e2e], device="cuda")
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -347,6 +351,9 @@ def main():
                                        f"{c['n_layer']} layers, d_model {c['d_model']}, {c['n_head']}x{c['d_key']} heads, "
                                        f"d_ff {c['d_inner']}, seg {T}, mem {c['mem_len']}, {Bt} streams",
                            "streams_per_gpu": B, "parallelism": f"dp{world} over streams",
+                           "gradient_exchange": ("none" if world == 1 else
+                                                 "per-layer ncclAllReduce overlapped with backward" if m.has_comm
+                                                 else "one all-reduce after backward"),
                            "l2": "per-step working set (weights, optimizer state, activations) exceeds the 126 MB L2",
                            "tokens": "seeded Zipf(1.1)+order-1 Markov ids (stand-in for tokenised text)"},
                 "step_tflops": fl / (ms / K * 1e-3) / 1e12 , "step_gflop": fl / 1e9,
@@ -354,7 +361,7 @@ def main():
                 "e2e": {"value": e2e, "unit": "symbols/s", "h2d_bytes_per_step": 2 * T * B * 4 * world,
                         "d2h_bytes_per_step": (T * B * nb * 2 + 4) * world if nb else (T * B * V * 4 + 4) * world,
                         "ms_per_step": ms_e2e / K},
-                "ranks_hold_identical_weights": same}
+                "ranks_hold_identical_weights": same, "weights_hash": f"{whash:016x}"}
         if roof:
             line["roofline"] = roof
         if not args.no_cpu_baseline and world == 1:
@@ -364,9 +371,14 @@ def main():
                                     "sample": f"2 steps of {streams} streams x {T} symbols of the same model "
                                               f"(oracle/trf_oracle.c, OpenMP, {dt:.1f} s)"}
         print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        torch.cuda.synchronize()
     m.close()
     if world > 1:
         dist.destroy_process_group()
+    sys.stdout.flush()
+    os._exit(0)   # the measurement is out; nothing at interpreter shutdown may hold the GPUs
 
 
 if __name__ == "__main__":

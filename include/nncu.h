@@ -204,7 +204,22 @@ int nncu_grad_get(nncu_model *m, int index, float *host_out, size_t numel);
    gradient buffer between nncu_eval_gradient and nncu_optimizer_step. */
 int nncu_flat_buffers(nncu_model *m, float **master_dev, float **grad_dev,
                       float **moment_dev, size_t *n_floats);
-/* 64-bit FNV-1a hash over the fp32 master weights (DUMP_HASH-style check that
+/*
+ * Gradient exchange inside the library -- no counterpart in the reference, which is
+ * single-device (the stream sharding of this build is described in nncp-metal_b200/dist.py).
+ * With a communicator attached, nncu_eval_gradient* sums each layer's gradient slots over
+ * the ranks (ncclAllReduce, fp32, on a stream of its own) as soon as that layer's backward
+ * is complete, so the exchange overlaps the rest of the backward pass; on return the
+ * gradient buffer holds the global sum and no separate all-reduce is needed.
+ * Rank 0 makes the 128-byte id (nncu_comm_unique_id) and passes it to the other ranks by
+ * any means (torch.distributed broadcast in bench.py); every rank then calls nncu_comm_init.
+ * NCCL is loaded with dlopen("libnccl.so.2") on first use.
+ */
+int nncu_comm_unique_id(void *id_out_128_bytes);
+int nncu_comm_init(nncu_model *m, int n_ranks, int rank, const void *id_128_bytes);
+
+/* 64-bit order-independent digest (sum of mixed (index, bit pattern) words) of the fp32
+   master weights (DUMP_HASH-style check that
    ranks / runs hold identical weights, nncp.c:1062-1071). */
 int nncu_weights_hash(nncu_model *m, uint64_t *hash_out);
 

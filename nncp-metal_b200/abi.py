@@ -103,6 +103,8 @@ PROTOTYPES = {
     "nncu_grad_get": (_i, [_vp, _i, _vp, _sz]),
     "nncu_flat_buffers": (_i, [_vp, C.POINTER(_vp), C.POINTER(_vp), C.POINTER(_vp),
                                C.POINTER(_sz)]),
+    "nncu_comm_unique_id": (_i, [_vp]),
+    "nncu_comm_init": (_i, [_vp, _i, _i, _vp]),
     "nncu_weights_hash": (_i, [_vp, C.POINTER(C.c_uint64)]),
     "nncu_coder_paths": (_i, [_vp, _i, _i, _vp, _vp, C.POINTER(_i)]),
     "nncu_coder_trees": (_i, [_vp, _i, _i, _vp]),

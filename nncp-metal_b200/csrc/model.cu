@@ -18,6 +18,7 @@
 // Parameters, gradients and second moments are three flat fp32 buffers with
 // identical offsets (512-byte aligned slots); bf16 models add a bf16 shadow
 // and a transposed bf16 shadow of the matrices, refreshed by the optimizer.
+#include <dlfcn.h>
 #include <math.h>
 #include <stdarg.h>
 #include <string.h>
@@ -48,6 +49,45 @@ int nncu_fail(int code, const char *fmt, ...)
 }
 
 #define NONE ((size_t)-1)
+
+// ------------------------------------------------------------------ NCCL (loaded at run time)
+// Only what the gradient exchange needs, resolved with dlopen so that single-GPU hosts carry no
+// NCCL dependency.  Types as in nccl.h: ncclComm_t is an opaque pointer, ncclUniqueId 128 bytes,
+// ncclFloat32 = 7, ncclSum = 0.
+typedef struct { char b[128]; } nccl_id_t;
+struct NcclApi {
+    void *dl;
+    int (*GetUniqueId)(void *id);
+    int (*CommInitRank)(void **comm, int nranks, nccl_id_t id, int rank);
+    int (*AllReduce)(const void *send, void *recv, size_t count, int dtype, int op, void *comm, cudaStream_t st);
+    int (*CommDestroy)(void *comm);
+    const char *(*GetErrorString)(int);
+};
+
+static NcclApi *nccl_api()
+{
+    static NcclApi api;
+    static int state = 0; // 0 untried, 1 ok, -1 unavailable
+    if (state == 0) {
+        void *dl = dlopen("libnccl.so.2", RTLD_NOW | RTLD_NOLOAD | RTLD_GLOBAL); // torch's copy, if loaded
+        if (!dl)
+            dl = dlopen("libnccl.so.2", RTLD_NOW | RTLD_GLOBAL);
+        if (!dl)
+            dl = dlopen("libnccl.so", RTLD_NOW | RTLD_GLOBAL);
+        state = -1;
+        if (dl) {
+            api.dl = dl;
+            *(void **)&api.GetUniqueId = dlsym(dl, "ncclGetUniqueId");
+            *(void **)&api.CommInitRank = dlsym(dl, "ncclCommInitRank");
+            *(void **)&api.AllReduce = dlsym(dl, "ncclAllReduce");
+            *(void **)&api.CommDestroy = dlsym(dl, "ncclCommDestroy");
+            *(void **)&api.GetErrorString = dlsym(dl, "ncclGetErrorString");
+            if (api.GetUniqueId && api.CommInitRank && api.AllReduce && api.CommDestroy && api.GetErrorString)
+                state = 1;
+        }
+    }
+    return state == 1 ? &api : nullptr;
+}
 
 struct ParamInfo {
     char name[32];
@@ -87,6 +127,13 @@ struct nncu_model {
         int calls;
     } graphs[2][2];
     bool graphs_on;
+    // gradient exchange between ranks (nncu_comm_init): per-layer all-reduces on a third stream,
+    // issued as soon as a layer's gradients are complete, so they overlap the rest of backward
+    void *comm;
+    int comm_ranks;
+    cudaStream_t st3;
+    cudaEvent_t ev_bucket, ev_comm;
+    size_t tail_begin; // first parameter slot after the last layer
     std::vector<ParamInfo> pinfo;
     std::vector<LayerOff> lo;
     size_t ln_g, ln_b, embed, embed_out, out_bias, n_floats;
@@ -450,6 +497,29 @@ static int forward_range(nncu_model *m, int t0, int t1)
     return NNCU_OK;
 }
 
+// sum G[begin, end) over the ranks on the communication stream, after everything queued on
+// the main stream so far
+static int exchange_bucket(nncu_model *m, size_t begin, size_t end)
+{
+    if (!m->comm || end <= begin)
+        return NNCU_OK;
+    NcclApi *nc = nccl_api();
+    CUDA_TRY(cudaEventRecord(m->ev_bucket, m->st));
+    CUDA_TRY(cudaStreamWaitEvent(m->st3, m->ev_bucket, 0));
+    int r = nc->AllReduce(m->G + begin, m->G + begin, end - begin, 7 /* ncclFloat32 */, 0 /* ncclSum */, m->comm, m->st3);
+    if (r != 0)
+        return nncu_fail(NNCU_ERR_CUDA, "ncclAllReduce: %s", nc->GetErrorString(r));
+    return NNCU_OK;
+}
+static int exchange_finish(nncu_model *m)
+{
+    if (!m->comm)
+        return NNCU_OK;
+    CUDA_TRY(cudaEventRecord(m->ev_comm, m->st3));
+    CUDA_TRY(cudaStreamWaitEvent(m->st, m->ev_comm, 0));
+    return NNCU_OK;
+}
+
 // ------------------------------------------------------------------ backward
 
 template <typename AT>
@@ -573,6 +643,12 @@ static int backward(nncu_model *m)
             NNCU_TRY(mm_nn(m, TB, D, 3 * HD, dq, 3 * HD, o.w_q, dxn, D, (const AT *)ds1));
         }
         side_join(m); // this layer's weight gradients are done before dhp, dqkv, ds1, ds2 are rewritten
+        if (m->comm) {
+            // layer l's slots are contiguous; tied tables live in layer 0, which is exchanged last
+            NNCU_TRY(exchange_bucket(m, o.w_q, l + 1 < m->nl ? m->lo[l + 1].w_q : m->tail_begin));
+            if (l == m->nl - 1) // the output head's gradients have been complete since the first join
+                NNCU_TRY(exchange_bucket(m, m->embed_out, m->n_floats));
+        }
         dx = dxn;
     }
     const float emul = sqrtf((float)D) * p.embed_mult;
@@ -580,6 +656,8 @@ static int backward(nncu_model *m)
     embed_grad_kernel<AT><<<TB, 128, 2 * sizeof(int32_t) * TB, m->st>>>(m->ids_dev, dx, gf(m, m->embed), TB, D, emul, V);
     KERNEL_CHECK();
     side_join(m);
+    NNCU_TRY(exchange_bucket(m, m->tail_begin, m->embed_out)); // final norm and the embedding
+    NNCU_TRY(exchange_finish(m));
     return NNCU_OK;
 }
 
@@ -747,10 +825,17 @@ int nncu_destroy(nncu_model *m)
         return NNCU_OK;
     cudaSetDevice(m->device);
     cudaStreamSynchronize(m->st);
+    // graphs first: a captured ncclAllReduce keeps its communicator busy until the graph is gone
     for (int k = 0; k < 2; k++)
         for (int c = 0; c < 2; c++)
             if (m->graphs[k][c].exec)
                 cudaGraphExecDestroy(m->graphs[k][c].exec);
+    if (m->st3) cudaStreamSynchronize(m->st3);
+    if (m->comm && nccl_api())
+        nccl_api()->CommDestroy(m->comm);
+    if (m->st3) cudaStreamDestroy(m->st3);
+    if (m->ev_bucket) cudaEventDestroy(m->ev_bucket);
+    if (m->ev_comm) cudaEventDestroy(m->ev_comm);
     if (m->st2) { cudaStreamSynchronize(m->st2); cudaStreamDestroy(m->st2); }
     if (m->ev_fork) cudaEventDestroy(m->ev_fork);
     if (m->ev_join) cudaEventDestroy(m->ev_join);
@@ -789,6 +874,10 @@ int nncu_create(const nncu_params *p, nncu_model **out)
     m->ev_fork = m->ev_join = nullptr;
     m->overlap = false;
     memset(m->graphs, 0, sizeof(m->graphs));
+    m->comm = nullptr;
+    m->comm_ranks = 1;
+    m->st3 = nullptr;
+    m->ev_bucket = m->ev_comm = nullptr;
     {
         const char *e = getenv("NNCU_NO_GRAPH");
         m->graphs_on = !(e && e[0] == '1');
@@ -843,6 +932,7 @@ int nncu_create(const nncu_params *p, nncu_model **out)
     } else {
         m->ln_g = m->ln_b = NONE;
     }
+    m->tail_begin = m->ln_g != NONE ? m->ln_g : m->n_floats;
     m->embed = add_param(m, "embed", -1, (size_t)V * D);
     m->embed_out = add_param(m, "embed_out", -1, (size_t)V * D, V, D);
     m->out_bias = p->use_bias ? add_param(m, "out_bias", -1, V) : NONE;
@@ -1195,6 +1285,46 @@ int nncu_update(nncu_model *m)
 {
     NNCU_TRY(nncu_optimizer_step(m));
     return nncu_memory_shift(m);
+}
+
+int nncu_comm_unique_id(void *id_out)
+{
+    NcclApi *nc = nccl_api();
+    if (!nc)
+        return nncu_fail(NNCU_ERR_CUDA, "libnccl.so.2 could not be loaded");
+    if (!id_out)
+        return nncu_fail(NNCU_ERR_INVALID, "null argument");
+    int r = nc->GetUniqueId(id_out);
+    if (r != 0)
+        return nncu_fail(NNCU_ERR_CUDA, "ncclGetUniqueId: %s", nc->GetErrorString(r));
+    return NNCU_OK;
+}
+
+int nncu_comm_init(nncu_model *m, int n_ranks, int rank, const void *id)
+{
+    if (!m || !id || n_ranks < 1 || rank < 0 || rank >= n_ranks)
+        return nncu_fail(NNCU_ERR_INVALID, "bad communicator arguments");
+    if (m->comm)
+        return nncu_fail(NNCU_ERR_STATE, "the model already has a communicator");
+    NcclApi *nc = nccl_api();
+    if (!nc)
+        return nncu_fail(NNCU_ERR_CUDA, "libnccl.so.2 could not be loaded");
+    CUDA_TRY(cudaSetDevice(m->device));
+    CUDA_TRY(cudaStreamSynchronize(m->st));
+    if (!m->st3) {
+        CUDA_TRY(cudaStreamCreateWithFlags(&m->st3, cudaStreamNonBlocking));
+        CUDA_TRY(cudaEventCreateWithFlags(&m->ev_bucket, cudaEventDisableTiming));
+        CUDA_TRY(cudaEventCreateWithFlags(&m->ev_comm, cudaEventDisableTiming));
+    }
+    nccl_id_t uid;
+    memcpy(&uid, id, sizeof(uid));
+    void *comm = nullptr;
+    int r = nc->CommInitRank(&comm, n_ranks, uid, rank);
+    if (r != 0)
+        return nncu_fail(NNCU_ERR_CUDA, "ncclCommInitRank: %s", nc->GetErrorString(r));
+    m->comm = comm;
+    m->comm_ranks = n_ranks;
+    return NNCU_OK;
 }
 
 int nncu_synchronize(nncu_model *m)

@@ -29,6 +29,8 @@ class ShardedStep:
         self.world = world if world is not None else (dist.get_world_size(group) if dist.is_initialized() else 1)
 
     def reduce_gradients(self):
+        if getattr(self.model, "has_comm", False):
+            return  # the library already summed them, layer by layer, during the backward pass
         if self.world > 1:
             dist.all_reduce(self.grads, op=dist.ReduceOp.SUM, group=self.group)
 
@@ -53,3 +55,19 @@ class CudaArray:
     def __init__(self, ptr, n_floats):
         self.__cuda_array_interface__ = {"shape": (int(n_floats),), "typestr": "<f4",
                                          "data": (int(ptr), False), "version": 2}
+
+
+def attach_library_comm(model, lib, rank, world, device):
+    """Gives `model` an NCCL communicator of its own (id made on rank 0, broadcast with
+    torch.distributed), so that the gradient exchange runs inside the backward pass."""
+    import ctypes as C
+    import torch
+    buf = torch.zeros(128, dtype=torch.uint8)
+    if rank == 0:
+        raw = C.create_string_buffer(128)
+        if lib.nncu_comm_unique_id(raw) != 0:
+            raise RuntimeError(lib.nncu_last_error().decode())
+        buf = torch.frombuffer(bytearray(raw.raw), dtype=torch.uint8).clone()
+    buf = buf.to(device)
+    dist.broadcast(buf, src=0)
+    model.comm_init(world, rank, bytes(buf.cpu().numpy().tobytes()))

@@ -25,6 +25,7 @@ class TrfModel:
         self.h = _vp()
         self._ck(self.lib.nncu_create(C.byref(params), C.byref(self.h)))
         self.T, self.B, self.V = params.seg_len, params.n_streams, params.n_symbols
+        self.has_comm = False
         self.info = {}
         self.index = {}
         name = C.create_string_buffer(32)
@@ -134,6 +135,12 @@ class TrfModel:
         self._ck(self.lib.nncu_flat_buffers(self.h, C.byref(w), C.byref(g), C.byref(v),
                                             C.byref(n)))
         return w.value, g.value, v.value, n.value
+
+    def comm_init(self, n_ranks, rank, unique_id):
+        """Attach an NCCL communicator: eval_gradient then leaves globally summed gradients."""
+        buf = C.create_string_buffer(bytes(unique_id), 128)
+        self._ck(self.lib.nncu_comm_init(self.h, n_ranks, rank, buf))
+        self.has_comm = True
 
     def weights_hash(self):
         h = C.c_uint64()
