@@ -1,0 +1,62 @@
+"""The reference's own command-line compressor (nncp.c, unmodified, built by oracle/Makefile's
+`dropin` target with its Transformer class re-pointed at libnncu.so) on the GPU: compress and
+decompress round-trip through the reference's encode_file / decode_file / process_block, and
+the file it writes is byte-identical to what this repository's host code (nch_compress, the
+restatement of those functions) writes for the same parameters."""
+import os
+import subprocess
+
+import numpy as np
+import pytest
+
+from conftest import ROOT
+
+BIN = os.path.join(ROOT, "oracle", "_ref", "nncp_b200")
+OPTS = ["--cuda", "-q", "--n_layer", "2", "--d_model", "64", "--n_head", "2", "--d_inner", "128",
+        "--batch_size", "4", "--train_len", "16", "--mem_len", "16", "--d_pos", "16"]
+
+
+def _text(n, seed):
+    rng = np.random.default_rng(seed)
+    words = [bytes(rng.integers(97, 123, rng.integers(2, 8)).astype(np.uint8)) for _ in range(60)]
+    out = b" ".join(words[i] for i in rng.integers(0, 60, n // 4))
+    return out[:n]
+
+
+@pytest.mark.gpu
+@pytest.mark.skipif(not os.path.exists(BIN), reason="oracle/_ref/nncp_b200 was never built")
+@pytest.mark.parametrize("bf16", [0, 1])
+def test_reference_cli_round_trip_and_same_file_as_host_code(pkg, tmp_path, bf16):
+    data = _text(6000, 3)
+    src, cmp_, back = tmp_path / "in.bin", tmp_path / "out.nncp", tmp_path / "back.bin"
+    src.write_bytes(data)
+    opts = OPTS + (["--bf16", "1"] if bf16 else [])
+    r = subprocess.run([BIN] + opts + ["c", str(src), str(cmp_)], capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stdout + r.stderr
+    r = subprocess.run([BIN, "-q", "--cuda", "d", str(cmp_), str(back)], capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stdout + r.stderr
+    assert back.read_bytes() == data
+    blob = cmp_.read_bytes()
+    assert len(blob) < 0.8 * len(data)
+    # the same parameters through this repository's host code
+    p = pkg.abi.make_params(n_layer=2, d_model=64, n_head=2, d_key=32, d_inner=128, d_pos=16, mem_len=16,
+                            seg_len=16, n_streams=4, n_symbols=256, use_bias=1, use_w_r=1, tied_w_r=1,
+                            tied_b_r=1, query_bias=0, ln_flags=1, ff_act=1, init_range=1.0, init_kind=0,
+                            seed=123, beta2=0.9999, eps=1e-8, gradient_clip=0.1, lr=3e-4, use_bf16=bf16)
+    fp = pkg.host.file_params(p, lr=pkg.host.InterpParams.make([3e-4, 1e-4], [156250]), block_len=500000)
+    ops = pkg.host.bind_cuda(p)
+    mine, _ = pkg.host.compress(ops, fp, np.frombuffer(data, np.uint8).astype(np.uint16), pkg.host.EVAL_SEGMENT,
+                                pkg.host.OUT_CODER_READY)
+    pkg.host.unbind_cuda(ops)
+    assert mine == blob
+
+
+@pytest.mark.skipif(not os.path.exists(BIN), reason="oracle/_ref/nncp_b200 was never built")
+def test_reference_cli_fails_loudly_without_a_gpu(tmp_path):
+    import torch
+    if torch.cuda.is_available():
+        pytest.skip("a GPU is present")
+    src = tmp_path / "in.bin"
+    src.write_bytes(b"hello world " * 50)
+    r = subprocess.run([BIN] + OPTS + ["c", str(src), str(tmp_path / "o")], capture_output=True, text=True, timeout=60)
+    assert r.returncode != 0 and "no CUDA device" in (r.stdout + r.stderr)
