@@ -39,7 +39,14 @@ CONFIGS = {
     # BASELINE.json configs[0]
     "c0": dict(n_layer=2, d_model=128, n_head=4, d_key=32, d_inner=512, d_pos=64, mem_len=32,
                seg_len=32, n_streams=4, n_symbols=256, use_bf16=0),
+    # BASELINE.json configs[3] (64 streams over all ranks) and the train step of configs[4]
+    "c3": dict(n_layer=20, d_model=1024, n_head=16, d_key=64, d_inner=4096, d_pos=320, mem_len=256,
+               seg_len=64, n_streams=64, n_symbols=16384, use_bf16=1),
+    "c4": dict(n_layer=12, d_model=512, n_head=8, d_key=64, d_inner=2048, d_pos=576, mem_len=512,
+               seg_len=64, n_streams=128, n_symbols=16384, use_bf16=1),
 }
+# streams of the bounded CPU sample (the CPU port needs about half a second per c2 stream-step)
+CPU_STREAMS = {"c2": 2, "c3": 1, "c4": 2}
 COMMON = dict(use_bias=1, use_w_r=1, tied_w_r=0, tied_b_r=0, query_bias=1, ln_flags=1, ff_act=1,
               init_range=0.02, init_kind=1, seed=123, lr=3e-4, beta2=0.99, eps=1e-8)
 
@@ -172,7 +179,7 @@ def run_reference(args, c):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    streams = 2 if args.config == "c2" else c["n_streams"]
+    streams = CPU_STREAMS.get(args.config, c["n_streams"])
     args.steps = min(args.steps, 20)   # bounded: a c2 step of 2 streams is about a second of CPU work
     val, dt = cpu_port_run(c, args.steps, min(args.warmup, 1), streams)
     cores = os.cpu_count()
@@ -369,7 +376,7 @@ def main():
         if roof:
             line["roofline"] = roof
         if not args.no_cpu_baseline and world == 1:
-            streams = 2 if args.config == "c2" else c["n_streams"]
+            streams = CPU_STREAMS.get(args.config, c["n_streams"])
             val, dt = cpu_port_run(c, 2, 1, streams)
             line["cpu_baseline"] = {"value": val, "unit": "symbols/s", "cores": os.cpu_count(), "kind": "port",
                                     "sample": f"2 steps of {streams} streams x {T} symbols of the same model "

@@ -15,10 +15,16 @@
 // queries is requested, so query row i goes through the same sequence of instructions
 // and gives the same bits in a one-symbol step as in a whole-segment launch.
 //
-// Backward stores P, dS (bf16) and the inverse-skewed dE for the whole (T <= 64) x L tile
-// in shared memory, then runs dV = P^T dO, dK = dS^T Q, dQ = dS K + dE R, dR = dE^T Q as
-// tensor-core contractions with transposed fragments from ldmatrix.trans.  All sums have
-// a fixed order; the per-(stream, head) table gradients are reduced by the caller.
+// Keys are walked in super-blocks of 128 (two key blocks): K, V and the window of the position
+// table that the super-block can touch are staged per super-block, so shared memory does not
+// grow with the memory length.
+//
+// Backward, per super-block: P and dS (bf16) of the 64 x 128 tile and the inverse-skewed dE
+// window go to shared memory, then dV = P^T dO and dK = dS^T Q (complete for these keys, all
+// queries being in the CTA) are written out, dQ += dS K + dE R stays in registers, and the
+// table gradients dR += dE^T Q, db_r are accumulated into this (stream, head)'s slice of the
+// caller's partial buffers by plain read-add-write (one CTA owns the slice; super-blocks run
+// in order).  All sums have a fixed order; the caller reduces the partials over streams.
 #pragma once
 #include "attention.cuh"
 
@@ -53,22 +59,35 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi)
 
 constexpr int EW = 88; // fp32 row stride of the per-warp skew scratch (80 columns used)
 
+// shared-memory geometry; identical on host and device
 struct Dims {
-    int Lp, Pr, LDS, LPS, PPS;
+    int SBK;  // keys per super-block: 64 or 128
+    int WR;   // rows of the staged position-table window
+    int LDS;  // bf16 row stride of Q, K, V, R, dO tiles
+    int LPS;  // bf16 row stride of the P / dS tiles
+    int PPS;  // bf16 row stride of the dE window
 };
 __host__ __device__ inline Dims dims_of(int L, int P, int dk)
 {
     Dims d;
-    d.Lp = (L + 63) / 64 * 64;      // key rows, padded with zero rows
-    d.Pr = (P + 1 + 15) / 16 * 16;  // position rows, at least one zero row after the table
-    d.LDS = dk + 8;                 // bf16 row stride of Q, K, V, R, dO tiles
-    d.LPS = d.Lp + 8;               // bf16 row stride of the P / dS tiles
-    d.PPS = d.Pr + 8;               // bf16 row stride of the dE tile
+    d.SBK = (L <= 64 || dk > 64) ? 64 : 128; // wide heads: smaller key tiles keep the backward in shared memory
+    const int whole = (P + 1 + 15) / 16 * 16;   // the table and at least one zero row
+    const int window = d.SBK + 64 + 16;         // reach of 64 query rows over SBK keys, plus slack
+    d.WR = whole < window ? whole : window;
+    d.LDS = dk + 8;
+    d.LPS = d.SBK + 8;
+    d.PPS = d.WR + 8;
     return d;
 }
+// first table row a super-block starting at key j0 can touch, for query rows up to q_last
+__device__ __forceinline__ int window_base(const AttnArgs &a, int j0, int q_last)
+{
+    const int w = j0 + (a.T - 1) - q_last - (a.L - a.P);
+    return w > 0 ? w : 0;
+}
 
-// rows [row0, row0+nrows) of a [.. x dk] bf16 matrix with row pitch `pitch` elements ->
-// shared tile; rows that fail `valid` are zero.  16-byte chunks.
+// rows [0, nrows) of a [.. x dk] bf16 matrix with row pitch `pitch` elements -> shared tile;
+// rows that fail `valid` are zero.  16-byte chunks.
 template <typename F>
 __device__ __forceinline__ void load_tile(bf16 *dst, int lds, const bf16 *src, size_t pitch, int nrows,
                                           int dk, F valid)
@@ -83,29 +102,30 @@ __device__ __forceinline__ void load_tile(bf16 *dst, int lds, const bf16 *src, s
     }
 }
 
-// position table of one head: from the bf16 copy (16-byte chunks) when there is one,
-// else converted from fp32; rows [P, Pr) are zero
+// rows [wbase, wbase + WR) of one head's position table -> shared; rows >= P are zero.  From the
+// bf16 copy (16-byte chunks) when there is one, else converted from fp32.
 __device__ __forceinline__ void load_table(bf16 *dst, int lds, const float *w_r_h, const bf16 *w16_h, int P,
-                                           int Pr, int dk)
+                                           int wbase, int WR, int dk)
 {
     if (w16_h) {
-        load_tile(dst, lds, w16_h, (size_t)dk, Pr, dk, [&](int r) { return r < P; });
+        load_tile(dst, lds, w16_h + (size_t)wbase * dk, (size_t)dk, WR, dk, [&](int r) { return wbase + r < P; });
         return;
     }
-    for (int idx = threadIdx.x; idx < Pr * dk; idx += blockDim.x) {
+    for (int idx = threadIdx.x; idx < WR * dk; idx += blockDim.x) {
         int p = idx / dk, e = idx % dk;
-        dst[(size_t)p * lds + e] = (w_r_h && p < P) ? __float2bfloat16_rn(w_r_h[(size_t)p * dk + e])
-                                                     : __float2bfloat16_rn(0.0f);
+        dst[(size_t)p * lds + e] = (w_r_h && wbase + p < P) ? __float2bfloat16_rn(w_r_h[(size_t)(wbase + p) * dk + e])
+                                                             : __float2bfloat16_rn(0.0f);
     }
 }
 
 // scores of one 16-query x 64-key block: s[nt][c], already scaled and masked (-inf).
-// qf: Q fragments of the warp's 16 rows.  es: the warp's skew scratch.
+// qf: Q fragments of the warp's 16 rows.  Ks: staged keys of the super-block starting at key
+// j0s; Rs: staged table rows starting at row wbase.  es: the warp's skew scratch.
 template <int DK>
 __device__ __forceinline__ void score_block(const AttnArgs &a, const Dims &d, const uint32_t (&qf)[DK / 16][4],
                                             const bf16 *Ks, const bf16 *Rs, const float *brs, float *es,
-                                            int i0, int j0, int iA, int iB, int jloA, int jhiA, int jloB,
-                                            int jhiB, float (&s)[8][4])
+                                            int i0, int j0, int j0s, int wbase, int iA, int iB, int jloA,
+                                            int jhiA, int jloB, int jhiB, float (&s)[8][4])
 {
     const int lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
     constexpr int KS = DK / 16;
@@ -119,7 +139,7 @@ __device__ __forceinline__ void score_block(const AttnArgs &a, const Dims &d, co
 #pragma unroll
         for (int np = 0; np < 4; np++) {
             uint32_t b[4];
-            ldsm4(b, Ks + (size_t)(j0 + np * 16 + (lane & 7) + (lane >> 4) * 8) * d.LDS + ks * 16 + ((lane >> 3) & 1) * 8);
+            ldsm4(b, Ks + (size_t)(j0 - j0s + np * 16 + (lane & 7) + (lane >> 4) * 8) * d.LDS + ks * 16 + ((lane >> 3) & 1) * 8);
             mma16816(s[2 * np], qf[ks], b[0], b[1]);
             mma16816(s[2 * np + 1], qf[ks], b[2], b[3]);
         }
@@ -137,8 +157,8 @@ __device__ __forceinline__ void score_block(const AttnArgs &a, const Dims &d, co
         for (int ks = 0; ks < KS; ks++)
 #pragma unroll
             for (int np = 0; np < 5; np++) {
-                int row = pbase + np * 16 + (lane & 7) + (lane >> 4) * 8;
-                row = row < d.Pr - 1 ? row : d.Pr - 1; // rows past the table are zero
+                int row = pbase - wbase + np * 16 + (lane & 7) + (lane >> 4) * 8;
+                row = row < d.WR - 1 ? row : d.WR - 1; // past the rows this block can use
                 uint32_t b[4];
                 ldsm4(b, Rs + (size_t)row * d.LDS + ks * 16 + ((lane >> 3) & 1) * 8);
                 mma16816(e[2 * np], qf[ks], b[0], b[1]);
@@ -181,8 +201,8 @@ template <int DK>
 size_t fwd_smem(int L, int P)
 {
     Dims d = dims_of(L, P, DK);
-    return ((size_t)64 * d.LDS + (size_t)2 * d.Lp * d.LDS + (size_t)d.Pr * d.LDS) * sizeof(bf16) +
-           ((size_t)L + 4 * 16 * EW) * sizeof(float) + 64;
+    return ((size_t)64 * d.LDS + (size_t)2 * d.SBK * d.LDS + (size_t)d.WR * d.LDS) * sizeof(bf16) +
+           ((size_t)L + 4 + 4 * 16 * EW) * sizeof(float) + 64;
 }
 
 template <int DK>
@@ -192,9 +212,9 @@ __global__ void __launch_bounds__(128) attn_fwd_mma_kernel(AttnArgs a)
     const Dims d = dims_of(a.L, a.P, DK);
     bf16 *Qs = reinterpret_cast<bf16 *>(smraw);
     bf16 *Ks = Qs + (size_t)64 * d.LDS;
-    bf16 *Vs = Ks + (size_t)d.Lp * d.LDS;
-    bf16 *Rs = Vs + (size_t)d.Lp * d.LDS;
-    float *brs = reinterpret_cast<float *>(Rs + (size_t)d.Pr * d.LDS);
+    bf16 *Vs = Ks + (size_t)d.SBK * d.LDS;
+    bf16 *Rs = Vs + (size_t)d.SBK * d.LDS;
+    float *brs = reinterpret_cast<float *>(Rs + (size_t)d.WR * d.LDS);
     float *Es = brs + ((a.L + 3) & ~3);
     constexpr int KS = DK / 16, NT = DK / 8;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
@@ -206,20 +226,14 @@ __global__ void __launch_bounds__(128) attn_fwd_mma_kernel(AttnArgs a)
     const bf16 *kv = reinterpret_cast<const bf16 *>(a.kv);
     load_tile(Qs, d.LDS, q + ((size_t)qt0 * a.B + b) * a.qp + h * DK, (size_t)a.B * a.qp, 64, DK,
               [&](int r) { return qt0 + r >= a.t0 && qt0 + r < a.t1; });
-    load_tile(Ks, d.LDS, kv + (size_t)b * a.kvp + h * DK, (size_t)a.B * a.kvp, d.Lp, DK,
-              [&](int r) { return r < a.L; });
-    load_tile(Vs, d.LDS, kv + (size_t)b * a.kvp + HD + h * DK, (size_t)a.B * a.kvp, d.Lp, DK,
-              [&](int r) { return r < a.L; });
-    load_table(Rs, d.LDS, a.w_r ? a.w_r + (size_t)h * a.P * DK : nullptr,
-               a.w_r16 ? reinterpret_cast<const bf16 *>(a.w_r16) + (size_t)h * a.P * DK : nullptr, a.P, d.Pr, DK);
     for (int r = threadIdx.x; r < a.L; r += blockDim.x)
         brs[r] = a.br_scale * a.b_r[(size_t)h * a.L + r];
     __syncthreads();
 
+    // this warp's 16 query rows
     const int i0 = qt0 + warp * 16;
-    const int va = max(i0, a.t0), vb = min(i0 + 16, a.t1) - 1; // valid rows of this warp
-    if (va > vb)
-        return;
+    const int va = max(i0, a.t0), vb = min(i0 + 16, a.t1) - 1;
+    const bool active = va <= vb;
     uint32_t qf[KS][4];
 #pragma unroll
     for (int ks = 0; ks < KS; ks++)
@@ -230,9 +244,16 @@ __global__ void __launch_bounds__(128) attn_fwd_mma_kernel(AttnArgs a)
         key_range(a, iA, jloA, jhiA);
     if (iB >= a.t0 && iB < a.t1)
         key_range(a, iB, jloB, jhiB);
-    int jmin, jmax, tmp;
-    key_range(a, va, jmin, tmp);
-    key_range(a, vb, tmp, jmax);
+    int jmin = 0, jmax = -1, tmp;
+    if (active) {
+        key_range(a, va, jmin, tmp);
+        key_range(a, vb, tmp, jmax);
+    }
+    // key range of the whole CTA (its valid query rows are contiguous)
+    const int ca = max(qt0, a.t0), cb = min(qt0 + 64, a.t1) - 1;
+    int cmin, cmax;
+    key_range(a, ca, cmin, tmp);
+    key_range(a, cb, tmp, cmax);
     float o[NT][4];
 #pragma unroll
     for (int nt = 0; nt < NT; nt++)
@@ -242,61 +263,78 @@ __global__ void __launch_bounds__(128) attn_fwd_mma_kernel(AttnArgs a)
     float mA = -INFINITY, mB = -INFINITY, lA = 0.0f, lB = 0.0f;
     float *es = Es + (size_t)warp * 16 * EW;
 
-    for (int kb = jmin / 64; kb <= jmax / 64; kb++) {
-        const int j0 = kb * 64;
-        float s[8][4];
-        score_block<DK>(a, d, qf, Ks, Rs, brs, es, i0, j0, iA, iB, jloA, jhiA, jloB, jhiB, s);
-        float mxA = -INFINITY, mxB = -INFINITY;
+    for (int sb = cmin / d.SBK; sb <= cmax / d.SBK; sb++) {
+        const int j0s = sb * d.SBK;
+        const int wbase = window_base(a, j0s, qt0 + 63);
+        __syncthreads(); // everyone is done with the previous super-block's tiles
+        load_tile(Ks, d.LDS, kv + ((size_t)j0s * a.B + b) * a.kvp + h * DK, (size_t)a.B * a.kvp, d.SBK, DK,
+                  [&](int r) { return j0s + r < a.L; });
+        load_tile(Vs, d.LDS, kv + ((size_t)j0s * a.B + b) * a.kvp + HD + h * DK, (size_t)a.B * a.kvp, d.SBK, DK,
+                  [&](int r) { return j0s + r < a.L; });
+        load_table(Rs, d.LDS, a.w_r ? a.w_r + (size_t)h * a.P * DK : nullptr,
+                   a.w_r16 ? reinterpret_cast<const bf16 *>(a.w_r16) + (size_t)h * a.P * DK : nullptr, a.P, wbase,
+                   d.WR, DK);
+        __syncthreads();
+        if (!active)
+            continue;
+        for (int kb = max(jmin / 64, j0s / 64); kb <= min(jmax / 64, (j0s + d.SBK - 1) / 64); kb++) {
+            const int j0 = kb * 64;
+            float s[8][4];
+            score_block<DK>(a, d, qf, Ks, Rs, brs, es, i0, j0, j0s, wbase, iA, iB, jloA, jhiA, jloB, jhiB, s);
+            float mxA = -INFINITY, mxB = -INFINITY;
 #pragma unroll
-        for (int nt = 0; nt < 8; nt++) {
-            mxA = fmaxf(mxA, fmaxf(s[nt][0], s[nt][1]));
-            mxB = fmaxf(mxB, fmaxf(s[nt][2], s[nt][3]));
-        }
-        mxA = fmaxf(mxA, __shfl_xor_sync(0xffffffffu, mxA, 1));
-        mxA = fmaxf(mxA, __shfl_xor_sync(0xffffffffu, mxA, 2));
-        mxB = fmaxf(mxB, __shfl_xor_sync(0xffffffffu, mxB, 1));
-        mxB = fmaxf(mxB, __shfl_xor_sync(0xffffffffu, mxB, 2));
-        const float nA = fmaxf(mA, mxA), nB = fmaxf(mB, mxB);
-        const float uA = nA == -INFINITY ? 0.0f : nA, uB = nB == -INFINITY ? 0.0f : nB;
-        const float scA = expf(mA - uA), scB = expf(mB - uB);
-        mA = nA;
-        mB = nB;
-        float sumA = 0.0f, sumB = 0.0f;
-#pragma unroll
-        for (int nt = 0; nt < 8; nt++) {
-            s[nt][0] = expf(s[nt][0] - uA);
-            s[nt][1] = expf(s[nt][1] - uA);
-            s[nt][2] = expf(s[nt][2] - uB);
-            s[nt][3] = expf(s[nt][3] - uB);
-            sumA += s[nt][0] + s[nt][1];
-            sumB += s[nt][2] + s[nt][3];
-        }
-        lA = lA * scA + sumA;
-        lB = lB * scB + sumB;
-#pragma unroll
-        for (int nt = 0; nt < NT; nt++) {
-            o[nt][0] *= scA;
-            o[nt][1] *= scA;
-            o[nt][2] *= scB;
-            o[nt][3] *= scB;
-        }
-#pragma unroll
-        for (int k2 = 0; k2 < 4; k2++) {
-            uint32_t pa[4];
-            pa[0] = pack2(s[2 * k2][0], s[2 * k2][1]);
-            pa[1] = pack2(s[2 * k2][2], s[2 * k2][3]);
-            pa[2] = pack2(s[2 * k2 + 1][0], s[2 * k2 + 1][1]);
-            pa[3] = pack2(s[2 * k2 + 1][2], s[2 * k2 + 1][3]);
-#pragma unroll
-            for (int np = 0; np < NT / 2; np++) {
-                uint32_t bb[4];
-                ldsm4t(bb, Vs + (size_t)(j0 + k2 * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * d.LDS + np * 16 + (lane >> 4) * 8);
-                mma16816(o[2 * np], pa, bb[0], bb[1]);
-                mma16816(o[2 * np + 1], pa, bb[2], bb[3]);
+            for (int nt = 0; nt < 8; nt++) {
+                mxA = fmaxf(mxA, fmaxf(s[nt][0], s[nt][1]));
+                mxB = fmaxf(mxB, fmaxf(s[nt][2], s[nt][3]));
             }
+            mxA = fmaxf(mxA, __shfl_xor_sync(0xffffffffu, mxA, 1));
+            mxA = fmaxf(mxA, __shfl_xor_sync(0xffffffffu, mxA, 2));
+            mxB = fmaxf(mxB, __shfl_xor_sync(0xffffffffu, mxB, 1));
+            mxB = fmaxf(mxB, __shfl_xor_sync(0xffffffffu, mxB, 2));
+            const float nA = fmaxf(mA, mxA), nB = fmaxf(mB, mxB);
+            const float uA = nA == -INFINITY ? 0.0f : nA, uB = nB == -INFINITY ? 0.0f : nB;
+            const float scA = expf(mA - uA), scB = expf(mB - uB);
+            mA = nA;
+            mB = nB;
+            float sumA = 0.0f, sumB = 0.0f;
+#pragma unroll
+            for (int nt = 0; nt < 8; nt++) {
+                s[nt][0] = expf(s[nt][0] - uA);
+                s[nt][1] = expf(s[nt][1] - uA);
+                s[nt][2] = expf(s[nt][2] - uB);
+                s[nt][3] = expf(s[nt][3] - uB);
+                sumA += s[nt][0] + s[nt][1];
+                sumB += s[nt][2] + s[nt][3];
+            }
+            lA = lA * scA + sumA;
+            lB = lB * scB + sumB;
+#pragma unroll
+            for (int nt = 0; nt < NT; nt++) {
+                o[nt][0] *= scA;
+                o[nt][1] *= scA;
+                o[nt][2] *= scB;
+                o[nt][3] *= scB;
+            }
+#pragma unroll
+            for (int k2 = 0; k2 < 4; k2++) {
+                uint32_t pa[4];
+                pa[0] = pack2(s[2 * k2][0], s[2 * k2][1]);
+                pa[1] = pack2(s[2 * k2][2], s[2 * k2][3]);
+                pa[2] = pack2(s[2 * k2 + 1][0], s[2 * k2 + 1][1]);
+                pa[3] = pack2(s[2 * k2 + 1][2], s[2 * k2 + 1][3]);
+#pragma unroll
+                for (int np = 0; np < NT / 2; np++) {
+                    uint32_t bb[4];
+                    ldsm4t(bb, Vs + (size_t)(j0 - j0s + k2 * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * d.LDS + np * 16 + (lane >> 4) * 8);
+                    mma16816(o[2 * np], pa, bb[0], bb[1]);
+                    mma16816(o[2 * np + 1], pa, bb[2], bb[3]);
+                }
+            }
+            __syncwarp();
         }
-        __syncwarp();
     }
+    if (!active)
+        return;
     lA += __shfl_xor_sync(0xffffffffu, lA, 1);
     lA += __shfl_xor_sync(0xffffffffu, lA, 2);
     lB += __shfl_xor_sync(0xffffffffu, lB, 1);
@@ -326,14 +364,15 @@ template <int DK>
 size_t bwd_smem(int L, int P)
 {
     Dims d = dims_of(L, P, DK);
-    return ((size_t)2 * 64 * d.LDS + (size_t)2 * d.Lp * d.LDS + (size_t)d.Pr * d.LDS + (size_t)2 * 64 * d.LPS +
+    return ((size_t)2 * 64 * d.LDS + (size_t)2 * d.SBK * d.LDS + (size_t)d.WR * d.LDS + (size_t)2 * 64 * d.LPS +
             (size_t)64 * d.PPS) * sizeof(bf16) +
            ((size_t)L + 4 + 8 * 16 * EW + 128) * sizeof(float) + 64;
 }
 
-// 8 warps: warp w owns query tile (w & 3); in phase A the two warps of a tile take alternate
-// key blocks, in phase B the row tiles of each contraction are dealt round-robin over the
-// warps and dQ is split into its key part (warps 0-3) and position part (warps 4-7).
+// 8 warps: warp w owns query tile (w & 3).  Phase A of a super-block: the two warps of a tile
+// take one key block each.  Phase B: the row tiles of dV / dK / dR are dealt round-robin over
+// the warps; dQ is split into its key part (warps 0-3) and position part (warps 4-7), kept in
+// registers over the super-blocks and combined at the end.
 template <int DK>
 __global__ void __launch_bounds__(256) attn_bwd_mma_kernel(AttnArgs a)
 {
@@ -342,9 +381,9 @@ __global__ void __launch_bounds__(256) attn_bwd_mma_kernel(AttnArgs a)
     bf16 *Qs = reinterpret_cast<bf16 *>(smraw);
     bf16 *dOs = Qs + (size_t)64 * d.LDS;
     bf16 *Ks = dOs + (size_t)64 * d.LDS;
-    bf16 *Vs = Ks + (size_t)d.Lp * d.LDS;
-    bf16 *Rs = Vs + (size_t)d.Lp * d.LDS;
-    bf16 *Pm = Rs + (size_t)d.Pr * d.LDS;
+    bf16 *Vs = Ks + (size_t)d.SBK * d.LDS;
+    bf16 *Rs = Vs + (size_t)d.SBK * d.LDS;
+    bf16 *Pm = Rs + (size_t)d.WR * d.LDS;
     bf16 *dSm = Pm + (size_t)64 * d.LPS;
     bf16 *dEm = dSm + (size_t)64 * d.LPS;
     float *brs = reinterpret_cast<float *>(dEm + (size_t)64 * d.PPS);
@@ -360,15 +399,19 @@ __global__ void __launch_bounds__(256) attn_bwd_mma_kernel(AttnArgs a)
     const bf16 *kv = reinterpret_cast<const bf16 *>(a.kv);
     const bf16 *dout = reinterpret_cast<const bf16 *>(a.dout);
     const bf16 *outp = reinterpret_cast<const bf16 *>(a.out);
+    float *dwr = (a.w_r && a.dwr_part) ? a.dwr_part + ((size_t)b * a.H + h) * P * DK : nullptr;
+    float *dbr = a.dbr_part ? a.dbr_part + ((size_t)b * a.H + h) * L : nullptr;
     load_tile(Qs, d.LDS, q + (size_t)b * a.qp + h * DK, (size_t)a.B * a.qp, 64, DK, [&](int r) { return r < T; });
     load_tile(dOs, d.LDS, dout + (size_t)b * HD + h * DK, (size_t)a.B * HD, 64, DK, [&](int r) { return r < T; });
-    load_tile(Ks, d.LDS, kv + (size_t)b * a.kvp + h * DK, (size_t)a.B * a.kvp, d.Lp, DK, [&](int r) { return r < L; });
-    load_tile(Vs, d.LDS, kv + (size_t)b * a.kvp + HD + h * DK, (size_t)a.B * a.kvp, d.Lp, DK,
-              [&](int r) { return r < L; });
-    load_table(Rs, d.LDS, a.w_r ? a.w_r + (size_t)h * P * DK : nullptr,
-               a.w_r16 ? reinterpret_cast<const bf16 *>(a.w_r16) + (size_t)h * P * DK : nullptr, P, d.Pr, DK);
     for (int r = threadIdx.x; r < L; r += blockDim.x)
         brs[r] = a.br_scale * a.b_r[(size_t)h * L + r];
+    // this (stream, head)'s table-gradient slices start at zero; super-blocks add to them
+    if (dwr)
+        for (int i = threadIdx.x; i < P * DK; i += blockDim.x)
+            dwr[i] = 0.0f;
+    if (dbr)
+        for (int i = threadIdx.x; i < L; i += blockDim.x)
+            dbr[i] = 0.0f;
     // the forward output, parked in the skew scratch (not needed before phase A)
     bf16 *Os = reinterpret_cast<bf16 *>(Es);
     load_tile(Os, d.LDS, outp + (size_t)b * HD + h * DK, (size_t)a.B * HD, 64, DK, [&](int r) { return r < T; });
@@ -384,175 +427,197 @@ __global__ void __launch_bounds__(256) attn_bwd_mma_kernel(AttnArgs a)
             lses[r] = r < T ? a.lse[((size_t)b * a.H + h) * T + r] : 0.0f;
         }
     }
-    __syncthreads();
 
-    // ---- phase A: P and dS of the warp's 16 query rows, every second key block
-    {
-        const int i0 = (warp & 3) * 16, half = warp >> 2;
-        const int va = i0, vb = min(i0 + 16, T) - 1;
-        if (va > vb) {
-            // no query row here: the P / dS rows of this tile are zero
-            for (int kb = half; kb < d.Lp / 64; kb += 2)
-                for (int idx = lane; idx < 16 * 32; idx += 32) {
-                    const size_t o2 = (size_t)(i0 + idx / 32) * d.LPS + kb * 64 + (idx % 32) * 2;
-                    *reinterpret_cast<uint32_t *>(Pm + o2) = 0u;
-                    *reinterpret_cast<uint32_t *>(dSm + o2) = 0u;
-                }
-        } else {
-            uint32_t qf[KS][4], df[KS][4];
+    // per-warp constants of phase A
+    const int i0 = (warp & 3) * 16, half = warp >> 2;
+    const int va = i0, vb = min(i0 + 16, T) - 1;
+    const bool active = va <= vb;
+    const int iA = i0 + g, iB = i0 + g + 8;
+    int jloA = 0, jhiA = -1, jloB = 0, jhiB = -1;
+    if (iA < T)
+        key_range(a, iA, jloA, jhiA);
+    if (iB < T)
+        key_range(a, iB, jloB, jhiB);
+    int jmin = 0, jmax = -1, tmp;
+    if (active) {
+        key_range(a, va, jmin, tmp);
+        key_range(a, vb, tmp, jmax);
+    }
+    uint32_t qf[KS][4], df[KS][4];
 #pragma unroll
-            for (int ks = 0; ks < KS; ks++) {
-                ldsm4(qf[ks], Qs + (size_t)(i0 + (lane & 15)) * d.LDS + ks * 16 + (lane >> 4) * 8);
-                ldsm4(df[ks], dOs + (size_t)(i0 + (lane & 15)) * d.LDS + ks * 16 + (lane >> 4) * 8);
+    for (int ks = 0; ks < KS; ks++) {
+        ldsm4(qf[ks], Qs + (size_t)(i0 + (lane & 15)) * d.LDS + ks * 16 + (lane >> 4) * 8);
+        ldsm4(df[ks], dOs + (size_t)(i0 + (lane & 15)) * d.LDS + ks * 16 + (lane >> 4) * 8);
+    }
+    float dq[NT][4]; // key part (warps 0-3) or position part (warps 4-7) of dQ for tile i0
+#pragma unroll
+    for (int nt = 0; nt < NT; nt++)
+#pragma unroll
+        for (int c = 0; c < 4; c++)
+            dq[nt][c] = 0.0f;
+    int cmin, cmax;
+    key_range(a, 0, cmin, tmp);
+    key_range(a, T - 1, tmp, cmax);
+    bf16 *dkv = reinterpret_cast<bf16 *>(a.dkv);
+    const int nsb = (L + d.SBK - 1) / d.SBK;
+
+    for (int sb = 0; sb < nsb; sb++) {
+        const int j0s = sb * d.SBK;
+        const int wbase = window_base(a, j0s, 63);
+        const bool touched = sb >= cmin / d.SBK && sb <= cmax / d.SBK; // any visible (query, key) pair here
+        __syncthreads(); // previous super-block fully consumed (first trip: prologue done)
+        if (touched) {
+            load_tile(Ks, d.LDS, kv + ((size_t)j0s * a.B + b) * a.kvp + h * DK, (size_t)a.B * a.kvp, d.SBK, DK,
+                      [&](int r) { return j0s + r < L; });
+            load_tile(Vs, d.LDS, kv + ((size_t)j0s * a.B + b) * a.kvp + HD + h * DK, (size_t)a.B * a.kvp, d.SBK, DK,
+                      [&](int r) { return j0s + r < L; });
+            load_table(Rs, d.LDS, a.w_r ? a.w_r + (size_t)h * P * DK : nullptr,
+                       a.w_r16 ? reinterpret_cast<const bf16 *>(a.w_r16) + (size_t)h * P * DK : nullptr, P, wbase,
+                       d.WR, DK);
+        }
+        __syncthreads();
+        if (!touched) {
+            // keys nobody attends to: their dK, dV are zero
+            for (int idx = threadIdx.x; idx < d.SBK * (DK / 8); idx += blockDim.x) {
+                const int j = j0s + idx / (DK / 8), c = (idx % (DK / 8)) * 8;
+                if (j < L) {
+                    bf16 *dst = dkv + ((size_t)j * a.B + b) * a.dkvp + h * DK + c;
+                    *reinterpret_cast<uint4 *>(dst) = make_uint4(0u, 0u, 0u, 0u);
+                    *reinterpret_cast<uint4 *>(dst + HD) = make_uint4(0u, 0u, 0u, 0u);
+                }
             }
-            const int iA = i0 + g, iB = i0 + g + 8;
-            int jloA = 0, jhiA = -1, jloB = 0, jhiB = -1;
-            if (iA < T)
-                key_range(a, iA, jloA, jhiA);
-            if (iB < T)
-                key_range(a, iB, jloB, jhiB);
-            int jmin, jmax, tmp;
-            key_range(a, va, jmin, tmp);
-            key_range(a, vb, tmp, jmax);
-            const float lseA = lses[i0 + g], lseB = lses[i0 + g + 8];
-            const float DA = Dr[i0 + g], DB = Dr[i0 + g + 8];
-            float *es = Es + (size_t)warp * 16 * EW;
-            for (int kb = half; kb < d.Lp / 64; kb += 2) {
-                const int j0 = kb * 64;
-                if (kb < jmin / 64 || kb > jmax / 64) { // nothing visible in this block
+            continue;
+        }
+        // ---- phase A: P and dS of (tile i0, key block `half` of this super-block)
+        {
+            const int kb = j0s / 64 + half, j0 = kb * 64;
+            if (j0 < j0s + d.SBK) {
+                const bool visible = active && kb >= jmin / 64 && kb <= jmax / 64;
+                if (!visible) {
                     for (int idx = lane; idx < 16 * 32; idx += 32) {
-                        const size_t o2 = (size_t)(i0 + idx / 32) * d.LPS + j0 + (idx % 32) * 2;
+                        const size_t o2 = (size_t)(i0 + idx / 32) * d.LPS + (j0 - j0s) + (idx % 32) * 2;
                         *reinterpret_cast<uint32_t *>(Pm + o2) = 0u;
                         *reinterpret_cast<uint32_t *>(dSm + o2) = 0u;
                     }
-                    continue;
-                }
-                float s[8][4], dp[8][4];
-                score_block<DK>(a, d, qf, Ks, Rs, brs, es, i0, j0, iA, iB, jloA, jhiA, jloB, jhiB, s);
+                } else {
+                    const float lseA = lses[i0 + g], lseB = lses[i0 + g + 8];
+                    const float DA = Dr[i0 + g], DB = Dr[i0 + g + 8];
+                    float *es = Es + (size_t)warp * 16 * EW;
+                    float s[8][4], dp[8][4];
+                    score_block<DK>(a, d, qf, Ks, Rs, brs, es, i0, j0, j0s, wbase, iA, iB, jloA, jhiA, jloB, jhiB, s);
 #pragma unroll
-                for (int nt = 0; nt < 8; nt++)
+                    for (int nt = 0; nt < 8; nt++)
 #pragma unroll
-                    for (int c = 0; c < 4; c++)
-                        dp[nt][c] = 0.0f;
+                        for (int c = 0; c < 4; c++)
+                            dp[nt][c] = 0.0f;
 #pragma unroll
-                for (int ks = 0; ks < KS; ks++)
+                    for (int ks = 0; ks < KS; ks++)
 #pragma unroll
-                    for (int np = 0; np < 4; np++) {
-                        uint32_t bb[4];
-                        ldsm4(bb, Vs + (size_t)(j0 + np * 16 + (lane & 7) + (lane >> 4) * 8) * d.LDS + ks * 16 + ((lane >> 3) & 1) * 8);
-                        mma16816(dp[2 * np], df[ks], bb[0], bb[1]);
-                        mma16816(dp[2 * np + 1], df[ks], bb[2], bb[3]);
+                        for (int np = 0; np < 4; np++) {
+                            uint32_t bb[4];
+                            ldsm4(bb, Vs + (size_t)(j0 - j0s + np * 16 + (lane & 7) + (lane >> 4) * 8) * d.LDS + ks * 16 + ((lane >> 3) & 1) * 8);
+                            mma16816(dp[2 * np], df[ks], bb[0], bb[1]);
+                            mma16816(dp[2 * np + 1], df[ks], bb[2], bb[3]);
+                        }
+#pragma unroll
+                    for (int nt = 0; nt < 8; nt++) {
+                        const float p0 = expf(s[nt][0] - lseA), p1 = expf(s[nt][1] - lseA);
+                        const float p2 = expf(s[nt][2] - lseB), p3 = expf(s[nt][3] - lseB);
+                        const int col = j0 - j0s + nt * 8 + 2 * t;
+                        *reinterpret_cast<uint32_t *>(Pm + (size_t)(i0 + g) * d.LPS + col) = pack2(p0, p1);
+                        *reinterpret_cast<uint32_t *>(Pm + (size_t)(i0 + g + 8) * d.LPS + col) = pack2(p2, p3);
+                        *reinterpret_cast<uint32_t *>(dSm + (size_t)(i0 + g) * d.LPS + col) =
+                            pack2(p0 * (dp[nt][0] - DA) * a.inv_sqrt, p1 * (dp[nt][1] - DA) * a.inv_sqrt);
+                        *reinterpret_cast<uint32_t *>(dSm + (size_t)(i0 + g + 8) * d.LPS + col) =
+                            pack2(p2 * (dp[nt][2] - DB) * a.inv_sqrt, p3 * (dp[nt][3] - DB) * a.inv_sqrt);
                     }
-#pragma unroll
-                for (int nt = 0; nt < 8; nt++) {
-                    const float p0 = expf(s[nt][0] - lseA), p1 = expf(s[nt][1] - lseA);
-                    const float p2 = expf(s[nt][2] - lseB), p3 = expf(s[nt][3] - lseB);
-                    const int col = j0 + nt * 8 + 2 * t;
-                    *reinterpret_cast<uint32_t *>(Pm + (size_t)(i0 + g) * d.LPS + col) = pack2(p0, p1);
-                    *reinterpret_cast<uint32_t *>(Pm + (size_t)(i0 + g + 8) * d.LPS + col) = pack2(p2, p3);
-                    *reinterpret_cast<uint32_t *>(dSm + (size_t)(i0 + g) * d.LPS + col) =
-                        pack2(p0 * (dp[nt][0] - DA) * a.inv_sqrt, p1 * (dp[nt][1] - DA) * a.inv_sqrt);
-                    *reinterpret_cast<uint32_t *>(dSm + (size_t)(i0 + g + 8) * d.LPS + col) =
-                        pack2(p2 * (dp[nt][2] - DB) * a.inv_sqrt, p3 * (dp[nt][3] - DB) * a.inv_sqrt);
-                }
-                __syncwarp();
-            }
-        }
-    }
-    __syncthreads();
-    // ---- inverse skew: dE[i][p] collects dS[i][j] with p = max(j + T-1-i - (L-P), 0);
-    //      db_r[r] = br_scale * sum_i dS[i][r - (T-1-i)]
-    for (int idx = threadIdx.x; idx < 64 * d.Pr; idx += blockDim.x) {
-        const int i = idx / d.Pr, p = idx % d.Pr;
-        float v = 0.0f;
-        if (i < T && p < P && a.w_r) {
-            if (p >= 1) {
-                const int j = p + (L - P) - (T - 1 - i);
-                if (j >= 0 && j < L)
-                    v = to_f(dSm[(size_t)i * d.LPS + j]);
-            } else {
-                for (int r = 0; r <= L - P; r++) {
-                    const int j = r - (T - 1 - i);
-                    if (j >= 0 && j < L)
-                        v += to_f(dSm[(size_t)i * d.LPS + j]);
                 }
             }
         }
-        dEm[(size_t)i * d.PPS + p] = __float2bfloat16_rn(v);
-    }
-    if (a.dbr_part) {
-        float *dst = a.dbr_part + ((size_t)b * a.H + h) * L;
-        for (int r = threadIdx.x; r < L; r += blockDim.x) {
-            float acc = 0.0f;
-            for (int i = 0; i < T; i++) {
-                const int j = r - (T - 1 - i);
-                if (j >= 0 && j < L)
-                    acc += to_f(dSm[(size_t)i * d.LPS + j]);
+        __syncthreads();
+        // ---- inverse skew for this super-block: dE[i][p] collects dS[i][j], p = max(j+T-1-i-(L-P), 0),
+        //      over the window rows; db_r[r] += br_scale * sum_i dS[i][r-(T-1-i)]
+        for (int idx = threadIdx.x; idx < 64 * d.WR; idx += blockDim.x) {
+            const int i = idx / d.WR, pw = idx % d.WR, p = wbase + pw;
+            float v = 0.0f;
+            if (i < T && p < P && a.w_r) {
+                if (p >= 1) {
+                    const int jl = p + (L - P) - (T - 1 - i) - j0s;
+                    if (jl >= 0 && jl < d.SBK && j0s + jl < L)
+                        v = to_f(dSm[(size_t)i * d.LPS + jl]);
+                } else {
+                    // slots 0 .. L-P share table row 0; only those whose key is in this super-block
+                    const int off = (T - 1 - i) + j0s;
+                    const int rhi = min(L - P, off + min(d.SBK, L - j0s) - 1);
+                    for (int r = max(0, off); r <= rhi; r++)
+                        v += to_f(dSm[(size_t)i * d.LPS + r - off]);
+                }
             }
-            dst[r] = acc * a.br_scale;
+            dEm[(size_t)i * d.PPS + pw] = __float2bfloat16_rn(v);
         }
-    }
-    __syncthreads();
+        if (dbr) {
+            // slots whose (query, key) pairs can fall in this super-block
+            const int rlo = j0s, rhi = min(L - 1, j0s + d.SBK - 1 + (T - 1));
+            for (int r = rlo + threadIdx.x; r <= rhi; r += blockDim.x) {
+                float acc = 0.0f;
+                for (int i = 0; i < T; i++) {
+                    const int jl = r - (T - 1 - i) - j0s;
+                    if (jl >= 0 && jl < d.SBK && j0s + jl < L)
+                        acc += to_f(dSm[(size_t)i * d.LPS + jl]);
+                }
+                dbr[r] += acc * a.br_scale;
+            }
+        }
+        __syncthreads();
 
-    // ---- phase B
-    bf16 *dkv = reinterpret_cast<bf16 *>(a.dkv);
-    // dV = P^T dO and dK = dS^T Q: 16-key row tiles spread over the warps, K = 64 queries
-    for (int mt = warp; mt < d.Lp / 16; mt += 8) {
-        const int jm0 = mt * 16;
-        float dv[NT][4], dk[NT][4];
+        // ---- phase B
+        // dV = P^T dO and dK = dS^T Q for the keys of this super-block (K = the 64 queries)
+        for (int mt = warp; mt < d.SBK / 16; mt += 8) {
+            const int jm0 = mt * 16;
+            float dv[NT][4], dk[NT][4];
 #pragma unroll
-        for (int nt = 0; nt < NT; nt++)
+            for (int nt = 0; nt < NT; nt++)
 #pragma unroll
-            for (int c = 0; c < 4; c++) {
-                dv[nt][c] = 0.0f;
-                dk[nt][c] = 0.0f;
+                for (int c = 0; c < 4; c++) {
+                    dv[nt][c] = 0.0f;
+                    dk[nt][c] = 0.0f;
+                }
+#pragma unroll
+            for (int ks = 0; ks < 4; ks++) {
+                uint32_t ap[4], as[4];
+                const int mi = lane >> 3;
+                const size_t aoff = (size_t)(ks * 16 + (lane & 7) + (mi >> 1) * 8) * d.LPS + jm0 + (mi & 1) * 8;
+                ldsm4t(ap, Pm + aoff);
+                ldsm4t(as, dSm + aoff);
+#pragma unroll
+                for (int np = 0; np < NT / 2; np++) {
+                    uint32_t bo[4], bq[4];
+                    const size_t boff = (size_t)(ks * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * d.LDS + np * 16 + (lane >> 4) * 8;
+                    ldsm4t(bo, dOs + boff);
+                    ldsm4t(bq, Qs + boff);
+                    mma16816(dv[2 * np], ap, bo[0], bo[1]);
+                    mma16816(dv[2 * np + 1], ap, bo[2], bo[3]);
+                    mma16816(dk[2 * np], as, bq[0], bq[1]);
+                    mma16816(dk[2 * np + 1], as, bq[2], bq[3]);
+                }
             }
 #pragma unroll
-        for (int ks = 0; ks < 4; ks++) {
-            uint32_t ap[4], as[4];
-            const int mi = lane >> 3;
-            const size_t aoff = (size_t)(ks * 16 + (lane & 7) + (mi >> 1) * 8) * d.LPS + jm0 + (mi & 1) * 8;
-            ldsm4t(ap, Pm + aoff);
-            ldsm4t(as, dSm + aoff);
+            for (int hh = 0; hh < 2; hh++) {
+                const int j = j0s + jm0 + g + hh * 8;
+                if (j < L) {
+                    bf16 *dst = dkv + ((size_t)j * a.B + b) * a.dkvp + h * DK;
 #pragma unroll
-            for (int np = 0; np < NT / 2; np++) {
-                uint32_t bo[4], bq[4];
-                const size_t boff = (size_t)(ks * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * d.LDS + np * 16 + (lane >> 4) * 8;
-                ldsm4t(bo, dOs + boff);
-                ldsm4t(bq, Qs + boff);
-                mma16816(dv[2 * np], ap, bo[0], bo[1]);
-                mma16816(dv[2 * np + 1], ap, bo[2], bo[3]);
-                mma16816(dk[2 * np], as, bq[0], bq[1]);
-                mma16816(dk[2 * np + 1], as, bq[2], bq[3]);
-            }
-        }
-#pragma unroll
-        for (int hh = 0; hh < 2; hh++) {
-            const int j = jm0 + g + hh * 8;
-            if (j < L) {
-                bf16 *dst = dkv + ((size_t)j * a.B + b) * a.dkvp + h * DK;
-#pragma unroll
-                for (int nt = 0; nt < NT; nt++) {
-                    *reinterpret_cast<uint32_t *>(dst + nt * 8 + 2 * t) = pack2(dk[nt][2 * hh], dk[nt][2 * hh + 1]);
-                    *reinterpret_cast<uint32_t *>(dst + HD + nt * 8 + 2 * t) = pack2(dv[nt][2 * hh], dv[nt][2 * hh + 1]);
+                    for (int nt = 0; nt < NT; nt++) {
+                        *reinterpret_cast<uint32_t *>(dst + nt * 8 + 2 * t) = pack2(dk[nt][2 * hh], dk[nt][2 * hh + 1]);
+                        *reinterpret_cast<uint32_t *>(dst + HD + nt * 8 + 2 * t) = pack2(dv[nt][2 * hh], dv[nt][2 * hh + 1]);
+                    }
                 }
             }
         }
-    }
-    // dQ = dS K + dE R: warps 0-3 take the key part of their query tile, warps 4-7 the
-    // position part, which they pass through shared memory (the skew scratch is free now)
-    {
-        const int i0 = (warp & 3) * 16;
-        float *dqp = Es; // [64][DK] fp32
-        float dq[NT][4];
-#pragma unroll
-        for (int nt = 0; nt < NT; nt++)
-#pragma unroll
-            for (int c = 0; c < 4; c++)
-                dq[nt][c] = 0.0f;
+        // dQ += dS K (warps 0-3) / dE R (warps 4-7), tile i0
         if (i0 < T) {
             if (warp < 4) {
-                for (int ks = 0; ks < d.Lp / 16; ks++) {
+                for (int ks = 0; ks < d.SBK / 16; ks++) {
                     uint32_t as[4];
                     ldsm4(as, dSm + (size_t)(i0 + (lane & 15)) * d.LPS + ks * 16 + (lane >> 4) * 8);
 #pragma unroll
@@ -564,7 +629,7 @@ __global__ void __launch_bounds__(256) attn_bwd_mma_kernel(AttnArgs a)
                     }
                 }
             } else if (a.w_r) {
-                for (int ks = 0; ks < d.Pr / 16; ks++) {
+                for (int ks = 0; ks < d.WR / 16; ks++) {
                     uint32_t ae[4];
                     ldsm4(ae, dEm + (size_t)(i0 + (lane & 15)) * d.PPS + ks * 16 + (lane >> 4) * 8);
 #pragma unroll
@@ -575,13 +640,55 @@ __global__ void __launch_bounds__(256) attn_bwd_mma_kernel(AttnArgs a)
                         mma16816(dq[2 * np + 1], ae, br[2], br[3]);
                     }
                 }
+            }
+        }
+        // dR += dE^T Q over the window rows (this stream's share of the table gradient), fp32
+        if (dwr) {
+            for (int mt = warp; mt < d.WR / 16; mt += 8) {
+                const int pm0 = mt * 16;
+                float dr[NT][4];
 #pragma unroll
-                for (int nt = 0; nt < NT; nt++) {
-                    dqp[(size_t)(i0 + g) * DK + nt * 8 + 2 * t] = dq[nt][0];
-                    dqp[(size_t)(i0 + g) * DK + nt * 8 + 2 * t + 1] = dq[nt][1];
-                    dqp[(size_t)(i0 + g + 8) * DK + nt * 8 + 2 * t] = dq[nt][2];
-                    dqp[(size_t)(i0 + g + 8) * DK + nt * 8 + 2 * t + 1] = dq[nt][3];
+                for (int nt = 0; nt < NT; nt++)
+#pragma unroll
+                    for (int c = 0; c < 4; c++)
+                        dr[nt][c] = 0.0f;
+#pragma unroll
+                for (int ks = 0; ks < 4; ks++) {
+                    uint32_t ae[4];
+                    const int mi = lane >> 3;
+                    ldsm4t(ae, dEm + (size_t)(ks * 16 + (lane & 7) + (mi >> 1) * 8) * d.PPS + pm0 + (mi & 1) * 8);
+#pragma unroll
+                    for (int np = 0; np < NT / 2; np++) {
+                        uint32_t bq[4];
+                        ldsm4t(bq, Qs + (size_t)(ks * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * d.LDS + np * 16 + (lane >> 4) * 8);
+                        mma16816(dr[2 * np], ae, bq[0], bq[1]);
+                        mma16816(dr[2 * np + 1], ae, bq[2], bq[3]);
+                    }
                 }
+#pragma unroll
+                for (int hh = 0; hh < 2; hh++) {
+                    const int p = wbase + pm0 + g + hh * 8;
+                    if (p < P)
+#pragma unroll
+                        for (int nt = 0; nt < NT; nt++) {
+                            dwr[(size_t)p * DK + nt * 8 + 2 * t] += dr[nt][2 * hh];
+                            dwr[(size_t)p * DK + nt * 8 + 2 * t + 1] += dr[nt][2 * hh + 1];
+                        }
+                }
+            }
+        }
+    }
+    // ---- combine the two parts of dQ and write it
+    __syncthreads();
+    {
+        float *dqp = Es; // [64][DK] fp32
+        if (warp >= 4 && a.w_r && i0 < T) {
+#pragma unroll
+            for (int nt = 0; nt < NT; nt++) {
+                dqp[(size_t)(i0 + g) * DK + nt * 8 + 2 * t] = dq[nt][0];
+                dqp[(size_t)(i0 + g) * DK + nt * 8 + 2 * t + 1] = dq[nt][1];
+                dqp[(size_t)(i0 + g + 8) * DK + nt * 8 + 2 * t] = dq[nt][2];
+                dqp[(size_t)(i0 + g + 8) * DK + nt * 8 + 2 * t + 1] = dq[nt][3];
             }
         }
         __syncthreads();
@@ -602,42 +709,6 @@ __global__ void __launch_bounds__(256) attn_bwd_mma_kernel(AttnArgs a)
                         *reinterpret_cast<uint32_t *>(dst + nt * 8 + 2 * t) = pack2(x0, x1);
                     }
                 }
-            }
-        }
-    }
-    // dR = dE^T Q (this stream's share of the table gradient), fp32
-    if (a.w_r && a.dwr_part) {
-        float *dst0 = a.dwr_part + ((size_t)b * a.H + h) * P * DK;
-        for (int mt = warp; mt < d.Pr / 16; mt += 8) {
-            const int pm0 = mt * 16;
-            float dr[NT][4];
-#pragma unroll
-            for (int nt = 0; nt < NT; nt++)
-#pragma unroll
-                for (int c = 0; c < 4; c++)
-                    dr[nt][c] = 0.0f;
-#pragma unroll
-            for (int ks = 0; ks < 4; ks++) {
-                uint32_t ae[4];
-                const int mi = lane >> 3;
-                ldsm4t(ae, dEm + (size_t)(ks * 16 + (lane & 7) + (mi >> 1) * 8) * d.PPS + pm0 + (mi & 1) * 8);
-#pragma unroll
-                for (int np = 0; np < NT / 2; np++) {
-                    uint32_t bq[4];
-                    ldsm4t(bq, Qs + (size_t)(ks * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * d.LDS + np * 16 + (lane >> 4) * 8);
-                    mma16816(dr[2 * np], ae, bq[0], bq[1]);
-                    mma16816(dr[2 * np + 1], ae, bq[2], bq[3]);
-                }
-            }
-#pragma unroll
-            for (int hh = 0; hh < 2; hh++) {
-                const int p = pm0 + g + hh * 8;
-                if (p < P)
-#pragma unroll
-                    for (int nt = 0; nt < NT; nt++) {
-                        dst0[(size_t)p * DK + nt * 8 + 2 * t] = dr[nt][2 * hh];
-                        dst0[(size_t)p * DK + nt * 8 + 2 * t + 1] = dr[nt][2 * hh + 1];
-                    }
             }
         }
     }

@@ -47,6 +47,12 @@ CONFIGS = {
                                mem_len=70, seg_len=20, n_streams=2, n_symbols=32,
                                attn_len=[60, 0] + [0] * 30, ln_flags=tt.LN_PRE | tt.LN_FINAL,
                                wscale=0.1),
+    # memory longer than the 128 keys the tensor-core attention stages at a time, a windowed layer
+    # whose oldest key tile is never attended, and a position table shorter than the keys
+    "mma_long_memory": dict(n_layer=2, d_model=64, n_head=2, d_key=32, d_inner=64, d_pos=160,
+                            mem_len=200, seg_len=24, n_streams=2, n_symbols=32,
+                            attn_len=[90, 0] + [0] * 30, ln_flags=tt.LN_PRE | tt.LN_FINAL,
+                            wscale=0.1),
     "c0_like": dict(n_layer=2, d_model=32, n_head=4, d_key=8, d_inner=64, d_pos=16,
                     mem_len=8, seg_len=8, n_streams=4, n_symbols=32),
 }

@@ -167,7 +167,14 @@ def test_attention_op_config1_bf16(pkg, oracle):
 
 @pytest.mark.parametrize("B,H,dk,T,M,P,alen", [(2, 2, 16, 6, 6, 9, 0), (2, 3, 32, 20, 70, 50, 60),
                                                (1, 2, 64, 64, 128, 192, 0), (2, 2, 128, 33, 31, 64, 40),
-                                               (3, 1, 32, 64, 0, 64, 0)])
+                                               (3, 1, 32, 64, 0, 64, 0),
+                                               # memories longer than one staged key tile: BASELINE config[3]
+                                               # (mem 256) and config[4] (mem 512) head geometry, a windowed
+                                               # layer whose first key tiles are never attended, a table
+                                               # shorter than the keys, and wide heads over several key tiles
+                                               (2, 2, 64, 64, 256, 320, 0), (1, 2, 64, 64, 512, 576, 0),
+                                               (2, 1, 32, 40, 300, 200, 150), (1, 2, 64, 64, 448, 64, 0),
+                                               (1, 2, 128, 48, 150, 198, 0), (1, 1, 16, 64, 200, 40, 100)])
 def test_attention_op_tensor_core_shapes_bf16(pkg, oracle, B, H, dk, T, M, P, alen):
     _attn_case(pkg, oracle, B, H, dk, T, M, P, alen, True, 3)
 
@@ -218,7 +225,7 @@ def test_train_step_fp32_vs_golden_and_oracle(pkg, oracle, name):
                                                ("c0_like", 1, 1), ("c0_like", 1, 2),
                                                ("pre_final_geglu_rms", 1, 2), ("tied_tables_longmem", 1, 2),
                                                ("mma_dk16", 1, 2), ("mma_two_key_blocks", 1, 2),
-                                               ("mma_two_key_blocks", 1, 1)])
+                                               ("mma_two_key_blocks", 1, 1), ("mma_long_memory", 1, 2)])
 def test_one_symbol_steps_equal_whole_segment_bitwise(pkg, name, bf16, backend):
     cfg, z = load_golden(name)
     p = params_from_cfg(pkg, cfg, use_bf16=bf16, gemm_backend=backend)
@@ -240,7 +247,7 @@ def test_one_symbol_steps_equal_whole_segment_bitwise(pkg, name, bf16, backend):
 
 
 @pytest.mark.parametrize("name", ["c0_like", "pre_final_geglu_rms", "tied_tables_longmem", "mma_dk16",
-                                  "mma_two_key_blocks"])
+                                  "mma_two_key_blocks", "mma_long_memory"])
 @pytest.mark.parametrize("backend", [1, 2])
 def test_train_step_bf16_vs_oracle(pkg, oracle, name, backend):
     cfg, z = load_golden(name)
@@ -287,7 +294,8 @@ def test_two_runs_are_bit_identical(pkg):
     assert hashes[0] == hashes[1]
 
 
-@pytest.mark.parametrize("name,bf16", [("c0_like", 0), ("mma_two_key_blocks", 1), ("tied_tables_longmem", 1)])
+@pytest.mark.parametrize("name,bf16", [("c0_like", 0), ("mma_two_key_blocks", 1), ("tied_tables_longmem", 1),
+                                       ("mma_long_memory", 1)])
 def test_graph_replay_equals_eager(pkg, name, bf16):
     """On a non-default stream forward and backward are captured into CUDA graphs on their second
     use; six steps there must give the same bits as six eager steps on the default stream."""
