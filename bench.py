@@ -175,6 +175,12 @@ def cpu_port_run(c, steps, warmup, streams):
     return steps * c["seg_len"] * streams / dt, dt
 
 
+def workload_name(name, c):
+    return (f"{name}: NNCP Transformer-XL train step, vocab {c['n_symbols']}, {c['n_layer']} layers, "
+            f"d_model {c['d_model']}, {c['n_head']}x{c['d_key']} heads, d_ff {c['d_inner']}, "
+            f"seg {c['seg_len']}, mem {c['mem_len']}, {c['n_streams']} streams")
+
+
 def run_reference(args, c):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
@@ -185,10 +191,11 @@ def run_reference(args, c):
     cores = os.cpu_count()
     line = {"impl": "reference", "metric": "compressed symbols/s (fwd+bwd+RMSProp)", "value": val,
             "unit": "symbols/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": min(args.warmup, 1),
-            "ms_per_step": 1e3 * dt / args.steps, "higher_is_better": True, "scaling": "weak",
+            "ms_per_step": 1e3 * dt / args.steps, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": f"{args.config}: NNCP Transformer-XL train step", "sample":
-                       f"{streams} of {c['n_streams']} streams per step"},
+            "config": {"workload": workload_name(args.config, c), "sample":
+                       f"{streams} of {c['n_streams']} streams per step",
+                       "tokens": "seeded Zipf(1.1)+order-1 Markov ids (stand-in for tokenised text)"},
             "cpu_baseline": {"value": val, "unit": "symbols/s", "cores": cores, "kind": "port",
                              "sample": f"{args.steps} steps of {streams} streams x {c['seg_len']} symbols, "
                                        f"oracle/trf_oracle.c with OpenMP; the reference's own train step "
@@ -358,9 +365,7 @@ def main():
                 "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": ms / K, "higher_is_better": True,
                 "scaling": "strong", "vs_baseline": None, "dtype": "bf16" if p.use_bf16 else "f32",
                 "data": "synthetic",
-                "config": {"workload": f"{args.config}: NNCP Transformer-XL train step, vocab {V}, "
-                                       f"{c['n_layer']} layers, d_model {c['d_model']}, {c['n_head']}x{c['d_key']} heads, "
-                                       f"d_ff {c['d_inner']}, seg {T}, mem {c['mem_len']}, {Bt} streams",
+                "config": {"workload": workload_name(args.config, c),
                            "streams_per_gpu": B, "parallelism": f"dp{world} over streams",
                            "gradient_exchange": ("none" if world == 1 else
                                                  "per-layer ncclAllReduce overlapped with backward" if m.has_comm

@@ -57,6 +57,22 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi)
     return *reinterpret_cast<uint32_t *>(&h);
 }
 
+#ifdef NNCU_ATTN_TRACE
+// tuning aid (off in normal builds): clock64() stamps of the backward kernel's phases
+__device__ long long *g_attn_trace = nullptr;
+#define AT_STAMP(slot)                                                        \
+    do {                                                                      \
+        if (at_trace_ && threadIdx.x == 0 && blockIdx.x < 64)                 \
+            at_trace_[blockIdx.x * 16 + (slot)] = clock64();                  \
+    } while (0)
+#define AT_TRACE_LOAD long long *const at_trace_ = g_attn_trace;
+#else
+#define AT_STAMP(slot) \
+    do {               \
+    } while (0)
+#define AT_TRACE_LOAD
+#endif
+
 constexpr int EW = 88; // fp32 row stride of the per-warp skew scratch (80 columns used)
 
 // shared-memory geometry; identical on host and device
@@ -377,6 +393,8 @@ template <int DK>
 __global__ void __launch_bounds__(256) attn_bwd_mma_kernel(AttnArgs a)
 {
     extern __shared__ __align__(16) unsigned char smraw[];
+    AT_TRACE_LOAD
+    AT_STAMP(0);
     const Dims d = dims_of(a.L, a.P, DK);
     bf16 *Qs = reinterpret_cast<bf16 *>(smraw);
     bf16 *dOs = Qs + (size_t)64 * d.LDS;
@@ -428,6 +446,7 @@ __global__ void __launch_bounds__(256) attn_bwd_mma_kernel(AttnArgs a)
         }
     }
 
+    AT_STAMP(1);
     // per-warp constants of phase A
     const int i0 = (warp & 3) * 16, half = warp >> 2;
     const int va = i0, vb = min(i0 + 16, T) - 1;
@@ -476,6 +495,7 @@ __global__ void __launch_bounds__(256) attn_bwd_mma_kernel(AttnArgs a)
                        d.WR, DK);
         }
         __syncthreads();
+        if (sb == 0) AT_STAMP(2);
         if (!touched) {
             // keys nobody attends to: their dK, dV are zero
             for (int idx = threadIdx.x; idx < d.SBK * (DK / 8); idx += blockDim.x) {
@@ -535,6 +555,7 @@ __global__ void __launch_bounds__(256) attn_bwd_mma_kernel(AttnArgs a)
             }
         }
         __syncthreads();
+        if (sb == 0) AT_STAMP(3);
         // ---- inverse skew for this super-block: dE[i][p] collects dS[i][j], p = max(j+T-1-i-(L-P), 0),
         //      over the window rows; db_r[r] += br_scale * sum_i dS[i][r-(T-1-i)]
         for (int idx = threadIdx.x; idx < 64 * d.WR; idx += blockDim.x) {
@@ -569,6 +590,7 @@ __global__ void __launch_bounds__(256) attn_bwd_mma_kernel(AttnArgs a)
             }
         }
         __syncthreads();
+        if (sb == 0) AT_STAMP(4);
 
         // ---- phase B
         // dV = P^T dO and dK = dS^T Q for the keys of this super-block (K = the 64 queries)
@@ -614,6 +636,7 @@ __global__ void __launch_bounds__(256) attn_bwd_mma_kernel(AttnArgs a)
                 }
             }
         }
+        if (sb == 0) AT_STAMP(5);
         // dQ += dS K (warps 0-3) / dE R (warps 4-7), tile i0
         if (i0 < T) {
             if (warp < 4) {
@@ -642,6 +665,7 @@ __global__ void __launch_bounds__(256) attn_bwd_mma_kernel(AttnArgs a)
                 }
             }
         }
+        if (sb == 0) AT_STAMP(6);
         // dR += dE^T Q over the window rows (this stream's share of the table gradient), fp32
         if (dwr) {
             for (int mt = warp; mt < d.WR / 16; mt += 8) {
@@ -680,6 +704,7 @@ __global__ void __launch_bounds__(256) attn_bwd_mma_kernel(AttnArgs a)
     }
     // ---- combine the two parts of dQ and write it
     __syncthreads();
+    AT_STAMP(7);
     {
         float *dqp = Es; // [64][DK] fp32
         if (warp >= 4 && a.w_r && i0 < T) {
@@ -712,6 +737,7 @@ __global__ void __launch_bounds__(256) attn_bwd_mma_kernel(AttnArgs a)
             }
         }
     }
+    AT_STAMP(8);
 }
 
 inline bool supported(const AttnArgs &a, bool backward)

@@ -37,7 +37,6 @@ namespace tc {
 
 constexpr int BM = 128;
 constexpr int BK = 64; // 64 bf16 = 128 bytes = one swizzle row
-constexpr uint32_t SPIN_LIMIT = 4000000u;
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p)
 {
@@ -64,23 +63,41 @@ __device__ __forceinline__ uint32_t mbar_test(uint32_t bar, uint32_t parity)
                  : "memory");
     return ok;
 }
-// bounded wait; returns false (and raises the flags) when the limit is hit or
-// another role of this CTA has already given up
+// bounded wait; returns false (and raises the flags) when the limit is hit.  The thread
+// suspends inside try_wait (up to about a microsecond per try) instead of polling; the loop is
+// PTX so that the path of a barrier that is already complete is a try and a branch.
+#ifdef NNCU_TC_SPIN
+constexpr uint32_t WAIT_TRIES = 1u << 24;
+#else
+constexpr uint32_t WAIT_TRIES = 1u << 21;
+#endif
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_s,
                                           int *err_flag, int code)
 {
-    for (uint32_t it = 0; it < SPIN_LIMIT; it++) {
-        if (mbar_test(bar, parity))
-            return true;
-        if (it > 2048) { // back off: the limit is then about half a second
-            if (*abort_s)
-                return false;
-            __nanosleep(100);
-        }
+    uint32_t ok;
+    asm volatile("{\n\t.reg .pred p, q;\n\t.reg .u32 c;\n\t"
+                 "mov.u32 c, 0;\n"
+                 "NNCU_WAIT:\n\t"
+                 #ifdef NNCU_TC_SPIN
+                 "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+#else
+                 "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %4;\n\t"
+#endif
+
+                 "@p bra NNCU_DONE;\n\t"
+                 "add.u32 c, c, 1;\n\t"
+                 "setp.lt.u32 q, c, %3;\n\t"
+                 "@q bra NNCU_WAIT;\n"
+                 "NNCU_DONE:\n\t"
+                 "selp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok)
+                 : "r"(bar), "r"(parity), "r"(WAIT_TRIES), "r"(1000u)
+                 : "memory");
+    if (!ok) {
+        *abort_s = 1;
+        atomicExch(err_flag, code);
     }
-    *abort_s = 1;
-    atomicExch(err_flag, code);
-    return false;
+    return ok != 0;
 }
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, uint32_t bar,
                                             int x, int y)
@@ -122,6 +139,39 @@ __device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint6
                  "setp.ne.b32 p, %4, 0;\n\t"
                  "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
                  "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+                 : "memory");
+}
+// The four UMMAs of one 64-wide k-block.  alo / blo: low words of the operand descriptors of the
+// block's first 16-wide slice; a later slice adds ASTEP / BSTEP to the address field.  The
+// high descriptor word is constant (DESC_HI).  `accumulate` = 0 makes the first UMMA overwrite.
+constexpr uint32_t DESC_HI = (1024u >> 4) | (1u << 14) | (2u << 29);
+template <uint32_t ASTEP, uint32_t BSTEP>
+__device__ __forceinline__ void umma_bf16_x4(uint32_t tmem_d, uint32_t alo, uint32_t blo, uint32_t idesc,
+                                             uint32_t accumulate)
+{
+    asm volatile("{\n\t.reg .pred p, t;\n\t.reg .b64 da, db;\n\t.reg .b32 la, lb;\n\t"
+                 "setp.ne.b32 p, %4, 0;\n\t"
+                 "setp.eq.b32 t, %4, %4;\n\t"
+                 "mov.b64 da, {%1, %5};\n\t"
+                 "mov.b64 db, {%2, %5};\n\t"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %3, p;\n\t"
+                 "add.u32 la, %1, %6;\n\t"
+                 "add.u32 lb, %2, %7;\n\t"
+                 "mov.b64 da, {la, %5};\n\t"
+                 "mov.b64 db, {lb, %5};\n\t"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %3, t;\n\t"
+                 "add.u32 la, %1, %8;\n\t"
+                 "add.u32 lb, %2, %9;\n\t"
+                 "mov.b64 da, {la, %5};\n\t"
+                 "mov.b64 db, {lb, %5};\n\t"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %3, t;\n\t"
+                 "add.u32 la, %1, %10;\n\t"
+                 "add.u32 lb, %2, %11;\n\t"
+                 "mov.b64 da, {la, %5};\n\t"
+                 "mov.b64 db, {lb, %5};\n\t"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %3, t;\n\t}" ::"r"(tmem_d),
+                 "r"(alo), "r"(blo), "r"(idesc), "r"(accumulate), "r"(DESC_HI), "n"(ASTEP), "n"(BSTEP),
+                 "n"(2 * ASTEP), "n"(2 * BSTEP), "n"(3 * ASTEP), "n"(3 * BSTEP)
                  : "memory");
 }
 __device__ __forceinline__ void umma_commit(uint32_t bar)
@@ -180,13 +230,18 @@ __device__ __forceinline__ uint64_t smem_desc_sw128_mn(uint32_t addr)
 #ifdef NNCU_GEMM_TRACE
 // tuning aid (off in normal builds): per-CTA clock64() stamps of the kernel's phases
 __device__ long long *g_tc_trace = nullptr;
+__device__ int g_tc_mode = 0; // 1: no loads (barriers only), 2: no MMAs (commits only)
+#define TC_MODE(bit) (tc_mode_ & (bit))
+#define TC_MODE_LOAD const int tc_mode_ = g_tc_mode; long long *const tc_trace_ = g_tc_trace;
 #define TC_STAMP(slot)                                                   \
     do {                                                                 \
-        long long *t_ = g_tc_trace;                                      \
+        long long *t_ = tc_trace_;                                       \
         if (t_ && blockIdx.x + blockIdx.y * gridDim.x < 128)             \
             t_[(blockIdx.x + blockIdx.y * gridDim.x) * 16 + (slot)] = clock64(); \
     } while (0)
 #else
+#define TC_MODE(bit) 0
+#define TC_MODE_LOAD
 #define TC_STAMP(slot) \
     do {               \
     } while (0)
@@ -222,6 +277,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
     const int nkb = (K + BK - 1) / BK;
+    TC_MODE_LOAD
 
     if (threadIdx.x == 0) {
         TC_STAMP(0);
@@ -245,32 +301,51 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     if (threadIdx.x == 0)
         TC_STAMP(1);
 
+    // The producer and the MMA issuer are single threads, and what bounds their loops is their
+    // own instruction count (one dependent instruction every 4-6 cycles): a k-block used to cost
+    // the issuer 350-600 cycles whatever the tile width, four times the tensor time of a
+    // 128 x 64 tile.  So both loops carry their state incrementally (barrier addresses and the
+    // low descriptor words step by constants, the phase bit flips at the ring's wrap), the four
+    // UMMAs of a k-block are one asm block, and a wait is a try_wait with a branch.
     if (warp == 0) {
         if (lane == 0) {
-            for (int kb = 0; kb < nkb; kb++) {
-                const int s = kb % SL::STAGES;
-                const uint32_t ph = (kb / SL::STAGES) & 1;
-                if (kb >= SL::STAGES &&
-                    !mbar_wait(smem_u32(&empty[s]), ph ^ 1, abort_s, err_flag, 1))
+            const uint32_t sm0 = smem_u32(sm), full0 = smem_u32(full), empty0 = smem_u32(empty);
+            uint32_t dst = sm0, fb = full0, eb = empty0, ph = 0;
+            int s = 0, kx = 0;
+            for (int kb = 0; kb < nkb; kb++, kx += BK) {
+                if (kb >= SL::STAGES && !mbar_wait(eb, ph, abort_s, err_flag, 1))
                     break;
-                const uint32_t fb = smem_u32(&full[s]);
                 if (kb == 0)
                     TC_STAMP(2);
-                mbar_expect_tx(fb, SL::STAGE_BYTES);
-                unsigned char *a_dst = sm + s * SL::STAGE_BYTES;
-                if (AMN) {
-#pragma unroll
-                    for (int mb = 0; mb < BM / 64; mb++)
-                        tma_load_2d(smem_u32(a_dst + mb * 8192), &map_a, fb, m0 + mb * 64, kb * BK);
+                if (TC_MODE(1)) {
+                    mbar_expect_tx(fb, 0);
                 } else {
-                    tma_load_2d(smem_u32(a_dst), &map_a, fb, kb * BK, m0);
+                    mbar_expect_tx(fb, SL::STAGE_BYTES);
+                    if (AMN) {
+#pragma unroll
+                        for (int mb = 0; mb < BM / 64; mb++)
+                            tma_load_2d(dst + mb * 8192, &map_a, fb, m0 + mb * 64, kx);
+                    } else {
+                        tma_load_2d(dst, &map_a, fb, kx, m0);
+                    }
+                    if (BMN) {
+#pragma unroll
+                        for (int nb = 0; nb < BN / 64; nb++)
+                            tma_load_2d(dst + SL::A_BYTES + nb * 8192, &map_b, fb, n0 + nb * 64, kx);
+                    } else {
+                        tma_load_2d(dst + SL::A_BYTES, &map_b, fb, kx, n0);
+                    }
                 }
-                if (BMN) {
-#pragma unroll
-                    for (int nb = 0; nb < BN / 64; nb++)
-                        tma_load_2d(smem_u32(a_dst + SL::A_BYTES + nb * 8192), &map_b, fb, n0 + nb * 64, kb * BK);
-                } else {
-                    tma_load_2d(smem_u32(a_dst + SL::A_BYTES), &map_b, fb, kb * BK, n0);
+                dst += SL::STAGE_BYTES;
+                fb += 8;
+                eb += 8;
+                if (++s == SL::STAGES) {
+                    s = 0;
+                    dst = sm0;
+                    fb = full0;
+                    eb = empty0;
+                    if (kb >= SL::STAGES)
+                        ph ^= 1;
                 }
             }
         }
@@ -279,28 +354,41 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((AMN ? 1u : 0u) << 15) |
                                        ((BMN ? 1u : 0u) << 16) | ((uint32_t)(BN >> 3) << 17) |
                                        ((uint32_t)(BM >> 4) << 24);
+            const uint32_t sm0 = smem_u32(sm), full0 = smem_u32(full), empty0 = smem_u32(empty);
+            // low descriptor words of stage 0 (address and leading offset); the high word is the
+            // same constant for both layouts (stride offset 1024, sm_100 version, 128-byte swizzle)
+            const uint32_t alo0 = (uint32_t)(AMN ? smem_desc_sw128_mn(sm0) : smem_desc_sw128(sm0));
+            const uint32_t blo0 = (uint32_t)(BMN ? smem_desc_sw128_mn(sm0 + SL::A_BYTES)
+                                                 : smem_desc_sw128(sm0 + SL::A_BYTES));
+            // one UMMA covers 16 along k: 32 bytes inside a K-major row (+2 in 16-byte units),
+            // 16 rows of 128 bytes in an MN-major tile (+128)
+            constexpr uint32_t astep = AMN ? 128u : 2u, bstep = BMN ? 128u : 2u;
+            uint32_t alo = alo0, blo = blo0, fb = full0, eb = empty0, ph = 0, acc = 0;
+            int s = 0;
             bool ok = true;
-            for (int kb = 0; kb < nkb && ok; kb++) {
-                const int s = kb % SL::STAGES;
-                const uint32_t ph = (kb / SL::STAGES) & 1;
-                ok = mbar_wait(smem_u32(&full[s]), ph, abort_s, err_flag, 2);
+            for (int kb = 0; kb < nkb; kb++) {
+                ok = mbar_wait(fb, ph, abort_s, err_flag, 2);
                 if (!ok)
                     break;
                 if (kb == 0)
                     TC_STAMP(3);
                 fence_after_sync();
-                const uint32_t a_addr = smem_u32(sm + s * SL::STAGE_BYTES);
-                const uint64_t adesc = AMN ? smem_desc_sw128_mn(a_addr) : smem_desc_sw128(a_addr);
-                const uint64_t bdesc = BMN ? smem_desc_sw128_mn(a_addr + SL::A_BYTES)
-                                           : smem_desc_sw128(a_addr + SL::A_BYTES);
-                // one UMMA covers 16 along k: 32 bytes inside a K-major row (+2 in 16-byte units),
-                // 16 rows of 128 bytes in an MN-major tile (+128)
-                constexpr uint32_t astep = AMN ? 128u : 2u, bstep = BMN ? 128u : 2u;
-#pragma unroll
-                for (int k = 0; k < BK / 16; k++)
-                    umma_bf16(tmem_base, adesc + astep * k, bdesc + bstep * k, idesc,
-                              (kb > 0 || k > 0) ? 1u : 0u);
-                umma_commit(smem_u32(&empty[s])); // frees the stage when these MMAs retire
+                if (!TC_MODE(2))
+                    umma_bf16_x4<astep, bstep>(tmem_base, alo, blo, idesc, acc);
+                acc = 1u;
+                umma_commit(eb); // frees the stage when these MMAs retire
+                alo += SL::STAGE_BYTES >> 4;
+                blo += SL::STAGE_BYTES >> 4;
+                fb += 8;
+                eb += 8;
+                if (++s == SL::STAGES) {
+                    s = 0;
+                    alo = alo0;
+                    blo = blo0;
+                    fb = full0;
+                    eb = empty0;
+                    ph ^= 1;
+                }
             }
             TC_STAMP(4);
             if (ok)
@@ -311,7 +399,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         const int quarter = warp & 3;
         bool ok = true;
         if (nkb > 0)
-            ok = mbar_wait(smem_u32(tmem_full), 0, abort_s, err_flag, 3);
+        {
+            // one lane per warp watches the barrier: every probe of a waiting thread queues in
+            // front of the producer's and the MMA thread's own barrier operations
+            if (lane == 0 || TC_MODE(4))
+                ok = mbar_wait(smem_u32(tmem_full), 0, abort_s, err_flag, 3);
+            __syncwarp();
+        }
         ok = __all_sync(0xffffffffu, ok); // tcgen05.ld below is warp-collective
         if (threadIdx.x == 64)
             TC_STAMP(5);

@@ -222,6 +222,40 @@ __global__ void act_fwd_kernel(const T *__restrict__ hpre, T *__restrict__ hact,
     hact[idx] = from_f<T>(o);
 }
 
+// Eight columns per thread (16-byte accesses); same arithmetic per element as act_fwd_kernel.
+// Needs F and F1 to be multiples of 8 and 16-byte aligned rows.
+__global__ void act_fwd_vec_kernel(const bf16 *__restrict__ hpre, bf16 *__restrict__ hact, int rows, int F,
+                                   int F1, int act)
+{
+    const int cpr = F / 8;
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (size_t)rows * cpr)
+        return;
+    const int r = (int)(idx / cpr), i = (int)(idx % cpr) * 8;
+    const uint4 va = *reinterpret_cast<const uint4 *>(hpre + (size_t)r * F1 + i);
+    const bf16 *a = reinterpret_cast<const bf16 *>(&va);
+    uint4 vo;
+    bf16 *o = reinterpret_cast<bf16 *>(&vo);
+    if (act == NNCU_FF_RELU) {
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+            const float x = to_f(a[j]);
+            o[j] = from_f<bf16>(x > 0.0f ? x : 0.0f);
+        }
+    } else if (act == NNCU_FF_GELU) {
+#pragma unroll
+        for (int j = 0; j < 8; j++)
+            o[j] = from_f<bf16>(gelu_f(to_f(a[j])));
+    } else {
+        const uint4 vg = *reinterpret_cast<const uint4 *>(hpre + (size_t)r * F1 + F + i);
+        const bf16 *g = reinterpret_cast<const bf16 *>(&vg);
+#pragma unroll
+        for (int j = 0; j < 8; j++)
+            o[j] = from_f<bf16>(gelu_f(to_f(a[j])) * to_f(g[j]));
+    }
+    *reinterpret_cast<uint4 *>(hact + (size_t)r * F + i) = vo;
+}
+
 // Adjoint of the activation, and (part != NULL) per-chunk column sums of the result for the
 // ff_bias1 gradient: part[chunk][F1].  grid (ceil(F/128), ceil(rows/32)); one column per thread.
 template <typename T>
@@ -253,6 +287,55 @@ act_bwd_kernel(const T *__restrict__ hpre, const T *__restrict__ dhact, T *__res
         part[(size_t)blockIdx.y * F1 + i] = s0;
         if (F1 > F)
             part[(size_t)blockIdx.y * F1 + F + i] = s1;
+    }
+}
+
+// Two columns per thread (4-byte accesses), ACT_BWD_ROWS rows per block (short serial chains:
+// the kernel is bound by the latency of its per-element math, not by bytes); element
+// arithmetic as in act_bwd_kernel.  F even; grid (ceil(F/256), ceil(rows/ACT_BWD_ROWS)).
+constexpr int ACT_BWD_ROWS = 8;
+__global__ void __launch_bounds__(128)
+act_bwd_vec_kernel(const bf16 *__restrict__ hpre, const bf16 *__restrict__ dhact, bf16 *__restrict__ dhpre,
+                   float *__restrict__ part, int rows, int F, int F1, int act)
+{
+    const int i = (blockIdx.x * 128 + threadIdx.x) * 2;
+    if (i >= F)
+        return;
+    const int r0 = blockIdx.y * ACT_BWD_ROWS, r1 = min(rows, r0 + ACT_BWD_ROWS);
+    float s0[2] = {0.0f, 0.0f}, s1[2] = {0.0f, 0.0f};
+    for (int r = r0; r < r1; r++) {
+        const __nv_bfloat162 a2 = *reinterpret_cast<const __nv_bfloat162 *>(hpre + (size_t)r * F1 + i);
+        const __nv_bfloat162 d2 = *reinterpret_cast<const __nv_bfloat162 *>(dhact + (size_t)r * F + i);
+        const float a[2] = {__low2float(a2), __high2float(a2)}, d[2] = {__low2float(d2), __high2float(d2)};
+        bf16 o0[2], o1[2];
+        if (act == NNCU_FF_RELU || act == NNCU_FF_GELU) {
+#pragma unroll
+            for (int j = 0; j < 2; j++) {
+                o0[j] = from_f<bf16>(act == NNCU_FF_RELU ? (a[j] > 0.0f ? d[j] : 0.0f) : d[j] * gelu_grad_f(a[j]));
+                s0[j] += to_f(o0[j]);
+            }
+        } else {
+            const __nv_bfloat162 g2 = *reinterpret_cast<const __nv_bfloat162 *>(hpre + (size_t)r * F1 + F + i);
+            const float gate[2] = {__low2float(g2), __high2float(g2)};
+#pragma unroll
+            for (int j = 0; j < 2; j++) {
+                o0[j] = from_f<bf16>(d[j] * gate[j] * gelu_grad_f(a[j]));
+                o1[j] = from_f<bf16>(d[j] * gelu_f(a[j]));
+                s0[j] += to_f(o0[j]);
+                s1[j] += to_f(o1[j]);
+            }
+            *reinterpret_cast<__nv_bfloat162 *>(dhpre + (size_t)r * F1 + F + i) = __halves2bfloat162(o1[0], o1[1]);
+        }
+        *reinterpret_cast<__nv_bfloat162 *>(dhpre + (size_t)r * F1 + i) = __halves2bfloat162(o0[0], o0[1]);
+    }
+    if (part) {
+        float *row = part + (size_t)blockIdx.y * F1;
+        row[i] = s0[0];
+        row[i + 1] = s0[1];
+        if (F1 > F) {
+            row[F + i] = s1[0];
+            row[F + i + 1] = s1[1];
+        }
     }
 }
 

@@ -147,6 +147,8 @@ struct nncu_model {
     std::vector<LayerAct> act;
     void *xlast, *xf, *pool[4], *dz, *dh, *dhp, *dof, *dqkv, *tA, *tB;
     float *st_f, *probs, *dwr_part, *dbr_part, *part, *logp, *loss_dev;
+    size_t part_floats = 0; // floats per region of `part`
+    int part_idx = 0;       // regions handed out since the last join
     int32_t *ids_dev, *tgt_dev;
     int *err_flag;
     unsigned long long *hash_dev;
@@ -275,10 +277,22 @@ static cudaStream_t side_fork(nncu_model *m)
 }
 static void side_join(nncu_model *m)
 {
+    m->part_idx = 0;
     if (!m->overlap || g_nncu_prof)
         return;
     cudaEventRecord(m->ev_join, m->st2);
     cudaStreamWaitEvent(m->st, m->ev_join, 0);
+}
+// Partial column sums go to one of PART_SLOTS scratch regions, so that the kernel that reduces
+// them can run on the side stream while the main stream's next kernel fills another region.
+// At most nine regions are taken between two joins (output bias, final norm, four norms, the
+// activation, two bias sums); a join makes all of them free again.
+constexpr int PART_SLOTS = 10;
+static float *part_slot(nncu_model *m)
+{
+    float *p = m->part + (size_t)(m->part_idx % PART_SLOTS) * m->part_floats;
+    m->part_idx++;
+    return p;
 }
 
 static int mm_tn(nncu_model *m, int Nout, int Kin, int R, const float *dY, long ldy, const float *X,
@@ -311,7 +325,8 @@ static int mm_tn(nncu_model *m, int Nout, int Kin, int R, const bf16 *dY, long l
 }
 
 // out_k[c] = sum over parts of part[p*stride + off_k + c], up to three outputs in one launch
-static int reduce_cols(nncu_model *m, int n_parts, int stride, int n, float *o0, int off0,
+// (on the side stream: only gradient buffers are written, which nobody reads before the join)
+static int reduce_cols(nncu_model *m, const float *part, int n_parts, int stride, int n, float *o0, int off0,
                        float *o1 = nullptr, int off1 = 0, float *o2 = nullptr, int off2 = 0)
 {
     ReduceOut ro;
@@ -319,7 +334,7 @@ static int reduce_cols(nncu_model *m, int n_parts, int stride, int n, float *o0,
     ro.out[1] = o1; ro.off[1] = off1;
     ro.out[2] = o2; ro.off[2] = off2;
     int nout = o2 ? 3 : (o1 ? 2 : 1);
-    reduce_cols_kernel<<<dim3(ceil_div(n, 32), nout), 256, 0, m->st>>>(m->part, n_parts, stride, n, ro);
+    reduce_cols_kernel<<<dim3(ceil_div(n, 32), nout), 256, 0, side_fork(m)>>>(part, n_parts, stride, n, ro);
     KERNEL_CHECK();
     return NNCU_OK;
 }
@@ -329,10 +344,10 @@ static int colsum(nncu_model *m, const AT *A, long lda, int R, int N, float *out
 {
     const int rows_per = 64;
     int chunks = ceil_div(R, rows_per);
-    colsum_part_kernel<AT><<<dim3(ceil_div(N, 128), chunks), 128, 0, m->st>>>(A, lda, R, N, rows_per,
-                                                                            m->part);
+    float *part = part_slot(m);
+    colsum_part_kernel<AT><<<dim3(ceil_div(N, 128), chunks), 128, 0, side_fork(m)>>>(A, lda, R, N, rows_per, part);
     KERNEL_CHECK();
-    return reduce_cols(m, chunks, N, N, out, 0);
+    return reduce_cols(m, part, chunks, N, N, out, 0);
 }
 
 template <typename AT>
@@ -355,10 +370,11 @@ static int norm_bwd(nncu_model *m, const AT *dy, const AT *x, size_t g_off, size
     int blocks = ceil_div(rows, rpb);
     int mode = (m->p.ln_flags & NNCU_LN_RMSNORM) ? 2 : 1;
     size_t smem = (size_t)8 * 3 * m->D * sizeof(float);
-    norm_bwd_kernel<AT><<<blocks, 256, smem, m->st>>>(dy, x, m->W + g_off, stats, base, dx, m->part,
+    float *part = part_slot(m);
+    norm_bwd_kernel<AT><<<blocks, 256, smem, m->st>>>(dy, x, m->W + g_off, stats, base, dx, part,
                                                       rows, m->D, mode, rpb, dxsum ? 1 : 0);
     KERNEL_CHECK();
-    return reduce_cols(m, blocks, 3 * m->D, m->D, gf(m, g_off), 0, gf(m, b_off), m->D, dxsum, 2 * m->D);
+    return reduce_cols(m, part, blocks, 3 * m->D, m->D, gf(m, g_off), 0, gf(m, b_off), m->D, dxsum, 2 * m->D);
 }
 
 static nncu_attn_shape attn_shape(nncu_model *m, int l, int t0, int t1)
@@ -476,7 +492,11 @@ static int forward_range(nncu_model *m, int t0, int t1)
         }
         AT *hpre = at<AT>(a.hpre, (size_t)r0 * F1), *hact = at<AT>(a.hact, (size_t)r0 * F);
         NNCU_TRY((mm_nt<AT, AT>(m, nr, F1, D, u, D, o.ff1, hpre, F1, wf(m, o.ff_bias1))));
-        act_fwd_kernel<AT><<<ceil_div((long long)nr * F, 256), 256, 0, m->st>>>(hpre, hact, nr, F, F1, p.ff_act);
+        if (sizeof(AT) == 2 && F % 8 == 0 && F1 % 8 == 0)
+            act_fwd_vec_kernel<<<ceil_div((long long)nr * (F / 8), 256), 256, 0, m->st>>>(
+                (const bf16 *)hpre, (bf16 *)hact, nr, F, F1, p.ff_act);
+        else
+            act_fwd_kernel<AT><<<ceil_div((long long)nr * F, 256), 256, 0, m->st>>>(hpre, hact, nr, F, F1, p.ff_act);
         KERNEL_CHECK();
         NNCU_TRY((mm_nt<AT, AT>(m, nr, D, F, hact, F, o.ff2, tmp, D, wf(m, o.ff_bias2))));
         AT *xout = (l + 1 < m->nl) ? at<AT>(m->act[l + 1].xin, (size_t)r0 * D)
@@ -590,11 +610,18 @@ static int backward(nncu_model *m)
         }
         NNCU_TRY(mm_tn(m, D, F, TB, ds2, D, atc<AT>(a.hact, 0), F, gf(m, o.ff2)));
         NNCU_TRY(mm_nn(m, TB, F, D, ds2, D, o.ff2, dh, F, (const AT *)nullptr));
-        act_bwd_kernel<AT><<<dim3(ceil_div(F, 128), ceil_div(TB, 32)), 128, 0, m->st>>>(
-            atc<AT>(a.hpre, 0), dh, dhp, o.ff_bias1 != NONE ? m->part : nullptr, TB, F, F1, p.ff_act);
+        float *apart = o.ff_bias1 != NONE ? part_slot(m) : nullptr;
+        const bool act_vec = sizeof(AT) == 2 && F % 2 == 0;
+        const int act_rows = act_vec ? ACT_BWD_ROWS : 32;
+        if (act_vec)
+            act_bwd_vec_kernel<<<dim3(ceil_div(F, 256), ceil_div(TB, act_rows)), 128, 0, m->st>>>(
+                (const bf16 *)atc<AT>(a.hpre, 0), (const bf16 *)dh, (bf16 *)dhp, apart, TB, F, F1, p.ff_act);
+        else
+            act_bwd_kernel<AT><<<dim3(ceil_div(F, 128), ceil_div(TB, act_rows)), 128, 0, m->st>>>(
+                atc<AT>(a.hpre, 0), dh, dhp, apart, TB, F, F1, p.ff_act);
         KERNEL_CHECK();
-        if (o.ff_bias1 != NONE)
-            NNCU_TRY(reduce_cols(m, ceil_div(TB, 32), F1, F1, gf(m, o.ff_bias1), 0));
+        if (apart)
+            NNCU_TRY(reduce_cols(m, apart, ceil_div(TB, act_rows), F1, F1, gf(m, o.ff_bias1), 0));
         const AT *u = pre ? atc<AT>(a.u, 0) : atc<AT>(a.y, 0);
         NNCU_TRY(mm_tn(m, F1, D, TB, dhp, F1, u, D, gf(m, o.ff1)));
         AT *dy = pick<AT>(m, {ds2});
@@ -618,14 +645,16 @@ static int backward(nncu_model *m)
                                        m->W + o.b_r, a.o, a.lse, dof, dq, dkv, m->dwr_part, m->dbr_part, m->st,
                                        &pt, (m->bf && o.w_r != NONE) ? m->Wb + o.w_r : nullptr));
         {
+            // on the side stream: the partials are next written after the join at the layer's end
+            cudaStream_t s2 = side_fork(m);
             size_t nb = (size_t)m->H * m->L;
-            reduce_streams_kernel<<<ceil_div(nb, 256), 256, 0, m->st>>>(m->dbr_part, B, nb, gf(m, o.b_r),
-                                                                       p.tied_b_r ? 1 : 0);
+            reduce_streams_kernel<<<ceil_div(nb, 256), 256, 0, s2>>>(m->dbr_part, B, nb, gf(m, o.b_r),
+                                                                    p.tied_b_r ? 1 : 0);
             KERNEL_CHECK();
             if (o.w_r != NONE) {
                 size_t nw = (size_t)m->H * p.d_pos * m->dk;
-                reduce_streams_kernel<<<ceil_div(nw, 256), 256, 0, m->st>>>(m->dwr_part, B, nw, gf(m, o.w_r),
-                                                                           p.tied_w_r ? 1 : 0);
+                reduce_streams_kernel<<<ceil_div(nw, 256), 256, 0, s2>>>(m->dwr_part, B, nw, gf(m, o.w_r),
+                                                                        p.tied_w_r ? 1 : 0);
                 KERNEL_CHECK();
             }
         }
@@ -981,7 +1010,9 @@ int nncu_create(const nncu_params *p, nncu_model **out)
     size_t oTA = m->use_tc ? take(max_n * LB * 2) : 0, oTB = m->use_tc ? take(max_k * LB * 2) : 0;
     size_t oWr = take((size_t)m->B * m->H * p->d_pos * m->dk * 4), oBr = take((size_t)m->B * m->H * m->L * 4);
     size_t part_floats = std::max((size_t)ceil_div(LB, 32) * max_n, (size_t)ceil_div(TB, 8) * 3 * D);
-    size_t oPart = take(part_floats * 4);
+    part_floats = std::max(part_floats, (size_t)ceil_div(TB, ACT_BWD_ROWS) * F1);
+    size_t oPart = take(part_floats * 4 * PART_SLOTS);
+    m->part_floats = part_floats;
     size_t oLogp = take((size_t)TB * 4), oLoss = take(256);
     size_t oIds = take((size_t)TB * 4), oTgt = take((size_t)TB * 4), oErr = take(256), oHash = take(256);
     // transposed-shadow jobs
@@ -1605,10 +1636,22 @@ int nncu_attention_backward_noalloc(const nncu_attn_shape *s, const void *q, con
 
 // ---- dense contraction test hooks
 
+#ifdef NNCU_ATTN_TRACE
+extern "C" int nncu_attn_trace(long long *dev_buf)
+{
+    CUDA_TRY(cudaMemcpyToSymbol(amma::g_attn_trace, &dev_buf, sizeof(dev_buf)));
+    return NNCU_OK;
+}
+#endif
 #ifdef NNCU_GEMM_TRACE
 extern "C" int nncu_gemm_trace(long long *dev_buf)
 {
     CUDA_TRY(cudaMemcpyToSymbol(tc::g_tc_trace, &dev_buf, sizeof(dev_buf)));
+    return NNCU_OK;
+}
+extern "C" int nncu_gemm_trace_mode(int mode)
+{
+    CUDA_TRY(cudaMemcpyToSymbol(tc::g_tc_mode, &mode, sizeof(mode)));
     return NNCU_OK;
 }
 #endif
