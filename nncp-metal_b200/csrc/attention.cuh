@@ -303,6 +303,8 @@ __global__ void __launch_bounds__(256) attn_bwd_kernel(AttnArgs a)
 __global__ void reduce_streams_kernel(const float *__restrict__ part, int B, size_t per_stream,
                                       float *__restrict__ out, int accumulate)
 {
+    pdl_trigger();
+    pdl_wait();
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= per_stream)
         return;

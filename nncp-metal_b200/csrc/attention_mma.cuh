@@ -224,6 +224,8 @@ size_t fwd_smem(int L, int P)
 template <int DK>
 __global__ void __launch_bounds__(128) attn_fwd_mma_kernel(AttnArgs a)
 {
+    pdl_trigger();
+    pdl_wait();
     extern __shared__ __align__(16) unsigned char smraw[];
     const Dims d = dims_of(a.L, a.P, DK);
     bf16 *Qs = reinterpret_cast<bf16 *>(smraw);
@@ -392,6 +394,8 @@ size_t bwd_smem(int L, int P)
 template <int DK>
 __global__ void __launch_bounds__(256) attn_bwd_mma_kernel(AttnArgs a)
 {
+    pdl_trigger();
+    pdl_wait();
     extern __shared__ __align__(16) unsigned char smraw[];
     AT_TRACE_LOAD
     AT_STAMP(0);
@@ -433,6 +437,25 @@ __global__ void __launch_bounds__(256) attn_bwd_mma_kernel(AttnArgs a)
     // the forward output, parked in the skew scratch (not needed before phase A)
     bf16 *Os = reinterpret_cast<bf16 *>(Es);
     load_tile(Os, d.LDS, outp + (size_t)b * HD + h * DK, (size_t)a.B * HD, 64, DK, [&](int r) { return r < T; });
+    // super-blocks with at least one visible (query, key) pair; the first one's keys, values and
+    // table window are fetched here, together with the query-side tiles
+    int cmin, cmax, tmp;
+    key_range(a, 0, cmin, tmp);
+    key_range(a, T - 1, tmp, cmax);
+    const int sb_first = cmin / d.SBK, sb_last = cmax / d.SBK;
+    const bool single = sb_first == sb_last; // table gradients are then stored, not accumulated
+    auto load_keys = [&](int sb) {
+        const int j0s = sb * d.SBK;
+        const int wbase = window_base(a, j0s, 63);
+        load_tile(Ks, d.LDS, kv + ((size_t)j0s * a.B + b) * a.kvp + h * DK, (size_t)a.B * a.kvp, d.SBK, DK,
+                  [&](int r) { return j0s + r < L; });
+        load_tile(Vs, d.LDS, kv + ((size_t)j0s * a.B + b) * a.kvp + HD + h * DK, (size_t)a.B * a.kvp, d.SBK, DK,
+                  [&](int r) { return j0s + r < L; });
+        load_table(Rs, d.LDS, a.w_r ? a.w_r + (size_t)h * P * DK : nullptr,
+                   a.w_r16 ? reinterpret_cast<const bf16 *>(a.w_r16) + (size_t)h * P * DK : nullptr, P, wbase,
+                   d.WR, DK);
+    };
+    load_keys(sb_first);
     __syncthreads();
     // D_i = dO_i . O_i and the saved log-sum-exp, one warp per 8 rows
     for (int r = warp * 8; r < warp * 8 + 8; r++) {
@@ -457,7 +480,7 @@ __global__ void __launch_bounds__(256) attn_bwd_mma_kernel(AttnArgs a)
         key_range(a, iA, jloA, jhiA);
     if (iB < T)
         key_range(a, iB, jloB, jhiB);
-    int jmin = 0, jmax = -1, tmp;
+    int jmin = 0, jmax = -1;
     if (active) {
         key_range(a, va, jmin, tmp);
         key_range(a, vb, tmp, jmax);
@@ -474,26 +497,16 @@ __global__ void __launch_bounds__(256) attn_bwd_mma_kernel(AttnArgs a)
 #pragma unroll
         for (int c = 0; c < 4; c++)
             dq[nt][c] = 0.0f;
-    int cmin, cmax;
-    key_range(a, 0, cmin, tmp);
-    key_range(a, T - 1, tmp, cmax);
     bf16 *dkv = reinterpret_cast<bf16 *>(a.dkv);
     const int nsb = (L + d.SBK - 1) / d.SBK;
 
     for (int sb = 0; sb < nsb; sb++) {
         const int j0s = sb * d.SBK;
         const int wbase = window_base(a, j0s, 63);
-        const bool touched = sb >= cmin / d.SBK && sb <= cmax / d.SBK; // any visible (query, key) pair here
+        const bool touched = sb >= sb_first && sb <= sb_last; // any visible (query, key) pair here
         __syncthreads(); // previous super-block fully consumed (first trip: prologue done)
-        if (touched) {
-            load_tile(Ks, d.LDS, kv + ((size_t)j0s * a.B + b) * a.kvp + h * DK, (size_t)a.B * a.kvp, d.SBK, DK,
-                      [&](int r) { return j0s + r < L; });
-            load_tile(Vs, d.LDS, kv + ((size_t)j0s * a.B + b) * a.kvp + HD + h * DK, (size_t)a.B * a.kvp, d.SBK, DK,
-                      [&](int r) { return j0s + r < L; });
-            load_table(Rs, d.LDS, a.w_r ? a.w_r + (size_t)h * P * DK : nullptr,
-                       a.w_r16 ? reinterpret_cast<const bf16 *>(a.w_r16) + (size_t)h * P * DK : nullptr, P, wbase,
-                       d.WR, DK);
-        }
+        if (touched && sb != sb_first)
+            load_keys(sb);
         __syncthreads();
         if (sb == 0) AT_STAMP(2);
         if (!touched) {
@@ -558,35 +571,41 @@ __global__ void __launch_bounds__(256) attn_bwd_mma_kernel(AttnArgs a)
         if (sb == 0) AT_STAMP(3);
         // ---- inverse skew for this super-block: dE[i][p] collects dS[i][j], p = max(j+T-1-i-(L-P), 0),
         //      over the window rows; db_r[r] += br_scale * sum_i dS[i][r-(T-1-i)]
-        for (int idx = threadIdx.x; idx < 64 * d.WR; idx += blockDim.x) {
-            const int i = idx / d.WR, pw = idx % d.WR, p = wbase + pw;
-            float v = 0.0f;
-            if (i < T && p < P && a.w_r) {
-                if (p >= 1) {
-                    const int jl = p + (L - P) - (T - 1 - i) - j0s;
-                    if (jl >= 0 && jl < d.SBK && j0s + jl < L)
-                        v = to_f(dSm[(size_t)i * d.LPS + jl]);
-                } else {
-                    // slots 0 .. L-P share table row 0; only those whose key is in this super-block
-                    const int off = (T - 1 - i) + j0s;
-                    const int rhi = min(L - P, off + min(d.SBK, L - j0s) - 1);
-                    for (int r = max(0, off); r <= rhi; r++)
-                        v += to_f(dSm[(size_t)i * d.LPS + r - off]);
+        for (int i = warp; i < 64; i += 8) {
+            const int shift = (L - P) - (T - 1 - i) - j0s; // key (local) = table row + shift, rows >= 1
+            for (int pw = lane; pw < d.WR; pw += 32) {
+                const int p = wbase + pw;
+                float v = 0.0f;
+                if (i < T && p < P && a.w_r) {
+                    if (p >= 1) {
+                        const int jl = p + shift;
+                        if (jl >= 0 && jl < d.SBK && j0s + jl < L)
+                            v = to_f(dSm[(size_t)i * d.LPS + jl]);
+                    } else {
+                        // slots 0 .. L-P share table row 0; only those whose key is in this super-block
+                        const int off = (T - 1 - i) + j0s;
+                        const int rhi = min(L - P, off + min(d.SBK, L - j0s) - 1);
+                        for (int r = max(0, off); r <= rhi; r++)
+                            v += to_f(dSm[(size_t)i * d.LPS + r - off]);
+                    }
                 }
+                dEm[(size_t)i * d.PPS + pw] = __float2bfloat16_rn(v);
             }
-            dEm[(size_t)i * d.PPS + pw] = __float2bfloat16_rn(v);
         }
         if (dbr) {
             // slots whose (query, key) pairs can fall in this super-block
             const int rlo = j0s, rhi = min(L - 1, j0s + d.SBK - 1 + (T - 1));
             for (int r = rlo + threadIdx.x; r <= rhi; r += blockDim.x) {
-                float acc = 0.0f;
-                for (int i = 0; i < T; i++) {
-                    const int jl = r - (T - 1 - i) - j0s;
+                float acc0 = 0.0f, acc1 = 0.0f;
+                for (int i = 0; i < T; i += 2) {
+                    const int jl = r - (T - 1 - i) - j0s; // key of query i; query i+1 has the next key
                     if (jl >= 0 && jl < d.SBK && j0s + jl < L)
-                        acc += to_f(dSm[(size_t)i * d.LPS + jl]);
+                        acc0 += to_f(dSm[(size_t)i * d.LPS + jl]);
+                    if (i + 1 < T && jl + 1 >= 0 && jl + 1 < d.SBK && j0s + jl + 1 < L)
+                        acc1 += to_f(dSm[(size_t)(i + 1) * d.LPS + jl + 1]);
                 }
-                dbr[r] += acc * a.br_scale;
+                const float v = (acc0 + acc1) * a.br_scale;
+                dbr[r] = single ? v : dbr[r] + v;
             }
         }
         __syncthreads();
@@ -695,8 +714,14 @@ __global__ void __launch_bounds__(256) attn_bwd_mma_kernel(AttnArgs a)
                     if (p < P)
 #pragma unroll
                         for (int nt = 0; nt < NT; nt++) {
-                            dwr[(size_t)p * DK + nt * 8 + 2 * t] += dr[nt][2 * hh];
-                            dwr[(size_t)p * DK + nt * 8 + 2 * t + 1] += dr[nt][2 * hh + 1];
+                            float2 *dst = reinterpret_cast<float2 *>(dwr + (size_t)p * DK + nt * 8 + 2 * t);
+                            float2 v = make_float2(dr[nt][2 * hh], dr[nt][2 * hh + 1]);
+                            if (!single) {
+                                const float2 old = *dst;
+                                v.x += old.x;
+                                v.y += old.y;
+                            }
+                            *dst = v;
                         }
                 }
             }
@@ -767,7 +792,7 @@ static int launch_fwd(const AttnArgs &a, cudaStream_t st)
     }
     const int first_tile = a.t0 / 16, last_tile = (a.t1 - 1) / 16;
     const int groups = (last_tile - first_tile) / 4 + 1;
-    attn_fwd_mma_kernel<DK><<<dim3(a.B * a.H, groups), 128, smem, st>>>(a);
+    launch_k(attn_fwd_mma_kernel<DK>, dim3(a.B * a.H, groups), dim3(128), smem, st, a);
     KERNEL_CHECK();
     return NNCU_OK;
 }
@@ -781,7 +806,7 @@ static int launch_bwd(const AttnArgs &a, cudaStream_t st)
         CUDA_TRY(cudaFuncSetAttribute(attn_bwd_mma_kernel<DK>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         attr = smem;
     }
-    attn_bwd_mma_kernel<DK><<<a.B * a.H, 256, smem, st>>>(a);
+    launch_k(attn_bwd_mma_kernel<DK>, dim3(a.B * a.H), dim3(256), smem, st, a);
     KERNEL_CHECK();
     return NNCU_OK;
 }

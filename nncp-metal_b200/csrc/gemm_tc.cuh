@@ -278,6 +278,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
     const int nkb = (K + BK - 1) / BK;
     TC_MODE_LOAD
+    pdl_trigger();
 
     if (threadIdx.x == 0) {
         TC_STAMP(0);
@@ -297,6 +298,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     fence_before_sync();
     __syncthreads();
     fence_after_sync();
+    // everything above (barriers, tensor-map prefetch, TMEM allocation) may overlap the tail of the
+    // kernel before this one on the stream; from here on its results are read
+    pdl_wait();
     const uint32_t tmem_base = *tmem_slot;
     if (threadIdx.x == 0)
         TC_STAMP(1);
@@ -692,7 +696,7 @@ static int launch(cudaStream_t st, int M, int N, int K, const bf16 *A, long lda,
     const bool timed = pr && pr->n < GemmProfiler::MAX_EV;
     if (timed)
         cudaEventRecord(pr->ev[2 * pr->n], st);
-    gemm_tc_kernel<BN, TC, AMN, BMN><<<grid, 192, SL::TOTAL, st>>>(ma, mb, mc, staged, C, ldc, bias, addsrc, M, N, K, err_flag, bias_n);
+    launch_k(gemm_tc_kernel<BN, TC, AMN, BMN>, dim3(grid), dim3(192), SL::TOTAL, st, ma, mb, mc, staged, C, ldc, bias, addsrc, M, N, K, err_flag, bias_n);
     if (timed) {
         cudaEventRecord(pr->ev[2 * pr->n + 1], st);
         pr->flops[pr->n++] = 2.0 * M * N * K;

@@ -14,6 +14,8 @@ template <typename T>
 __global__ void embed_kernel(const int32_t *__restrict__ ids, const float *__restrict__ embed,
                              T *__restrict__ x, int rows, int D, float mult, int V)
 {
+    pdl_trigger();
+    pdl_wait();
     int r = blockIdx.x;
     if (r >= rows)
         return;
@@ -36,6 +38,8 @@ residual_norm_kernel(const T *__restrict__ a, const T *__restrict__ res, T *__re
                      T *__restrict__ y, const float *__restrict__ g, const float *__restrict__ b,
                      float *__restrict__ stats, int rows, int D, int mode)
 {
+    pdl_trigger();
+    pdl_wait();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int r = blockIdx.x * 4 + warp;
     if (r >= rows)
@@ -88,6 +92,8 @@ norm_bwd_kernel(const T *__restrict__ dy, const T *__restrict__ x, const float *
                 const float *__restrict__ stats, const T *__restrict__ base, T *__restrict__ dx,
                 float *__restrict__ part, int rows, int D, int mode, int rpb, int want_sum)
 {
+    pdl_trigger();
+    pdl_wait();
     extern __shared__ float sm[]; // [8][3][D]
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     float *mydg = sm + (size_t)warp * 3 * D, *mydb = mydg + D, *mydx = mydb + D;
@@ -133,6 +139,183 @@ norm_bwd_kernel(const T *__restrict__ dy, const T *__restrict__ x, const float *
     }
 }
 
+// ---- bf16 rows of NC * 256 elements held in registers: 16-byte accesses, one pass over memory.
+// Lane l owns elements c*256 + l*8 .. +7 of every 256-element chunk c.
+template <int NC>
+__device__ __forceinline__ void row_load(const bf16 *row, int lane, float (&v)[NC][8])
+{
+#pragma unroll
+    for (int c = 0; c < NC; c++) {
+        const uint4 u = *reinterpret_cast<const uint4 *>(row + c * 256 + lane * 8);
+        const bf16 *h = reinterpret_cast<const bf16 *>(&u);
+#pragma unroll
+        for (int e = 0; e < 8; e++)
+            v[c][e] = to_f(h[e]);
+    }
+}
+template <int NC>
+__device__ __forceinline__ void row_store(bf16 *row, int lane, const float (&v)[NC][8])
+{
+#pragma unroll
+    for (int c = 0; c < NC; c++) {
+        uint4 u;
+        bf16 *h = reinterpret_cast<bf16 *>(&u);
+#pragma unroll
+        for (int e = 0; e < 8; e++)
+            h[e] = from_f<bf16>(v[c][e]);
+        *reinterpret_cast<uint4 *>(row + c * 256 + lane * 8) = u;
+    }
+}
+template <int NC>
+__device__ __forceinline__ void vec_load_f32(const float *p, int lane, float (&v)[NC][8])
+{
+#pragma unroll
+    for (int c = 0; c < NC; c++) {
+        const float4 a = *reinterpret_cast<const float4 *>(p + c * 256 + lane * 8);
+        const float4 b = *reinterpret_cast<const float4 *>(p + c * 256 + lane * 8 + 4);
+        v[c][0] = a.x; v[c][1] = a.y; v[c][2] = a.z; v[c][3] = a.w;
+        v[c][4] = b.x; v[c][5] = b.y; v[c][6] = b.z; v[c][7] = b.w;
+    }
+}
+
+// residual_norm_kernel for bf16 rows of D = NC * 256 elements; same arguments and rounding
+// points (s is rounded to bf16 before the statistics), sums taken per lane, then over the warp.
+template <int NC>
+__global__ void __launch_bounds__(128)
+residual_norm_vec_kernel(const bf16 *__restrict__ a, const bf16 *__restrict__ res, bf16 *__restrict__ s_out,
+                         bf16 *__restrict__ y, const float *__restrict__ g, const float *__restrict__ b,
+                         float *__restrict__ stats, int rows, int mode)
+{
+    pdl_trigger();
+    pdl_wait();
+    constexpr int D = NC * 256;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int r = blockIdx.x * 4 + warp;
+    if (r >= rows)
+        return;
+    float v[NC][8];
+    row_load<NC>(a + (size_t)r * D, lane, v);
+    if (res) {
+        float w[NC][8];
+        row_load<NC>(res + (size_t)r * D, lane, w);
+#pragma unroll
+        for (int c = 0; c < NC; c++)
+#pragma unroll
+            for (int e = 0; e < 8; e++)
+                v[c][e] = round_to<bf16>(v[c][e] + w[c][e]);
+    }
+    if (s_out)
+        row_store<NC>(s_out + (size_t)r * D, lane, v);
+    if (mode == 0) {
+        row_store<NC>(y + (size_t)r * D, lane, v);
+        return;
+    }
+    float mu = 0.0f;
+    if (mode == 1) {
+        float sum = 0.0f;
+#pragma unroll
+        for (int c = 0; c < NC; c++)
+#pragma unroll
+            for (int e = 0; e < 8; e++)
+                sum += v[c][e];
+        mu = warp_sum(sum) / (float)D;
+    }
+    float var = 0.0f;
+#pragma unroll
+    for (int c = 0; c < NC; c++)
+#pragma unroll
+        for (int e = 0; e < 8; e++)
+            var += (v[c][e] - mu) * (v[c][e] - mu);
+    var = warp_sum(var) / (float)D;
+    const float rstd = 1.0f / sqrtf(var + 1e-5f);
+    if (stats && lane == 0) {
+        stats[2 * r] = mu;
+        stats[2 * r + 1] = rstd;
+    }
+    float gv[NC][8], bv[NC][8];
+    vec_load_f32<NC>(g, lane, gv);
+    vec_load_f32<NC>(b, lane, bv);
+#pragma unroll
+    for (int c = 0; c < NC; c++)
+#pragma unroll
+        for (int e = 0; e < 8; e++)
+            v[c][e] = (v[c][e] - mu) * rstd * gv[c][e] + bv[c][e];
+    row_store<NC>(y + (size_t)r * D, lane, v);
+}
+
+// norm_bwd_kernel for bf16 rows of D = NC * 256 elements: one row per warp, eight rows per block,
+// the block's column sums (dg, db, and the sums of the dx just written) go to part[block][3][D].
+template <int NC>
+__global__ void __launch_bounds__(256)
+norm_bwd_vec_kernel(const bf16 *__restrict__ dy, const bf16 *__restrict__ x, const float *__restrict__ g,
+                    const float *__restrict__ stats, const bf16 *__restrict__ base, bf16 *__restrict__ dx,
+                    float *__restrict__ part, int rows, int mode, int want_sum)
+{
+    pdl_trigger();
+    pdl_wait();
+    constexpr int D = NC * 256;
+    extern __shared__ float sm[]; // [8][3][D]
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    float *mine = sm + (size_t)warp * 3 * D;
+    const int r = blockIdx.x * 8 + warp;
+    float xh[NC][8], d[NC][8], o[NC][8];
+    if (r < rows) {
+        const float mu = stats[2 * r], rstd = stats[2 * r + 1];
+        float gv[NC][8];
+        row_load<NC>(x + (size_t)r * D, lane, xh);
+        row_load<NC>(dy + (size_t)r * D, lane, d);
+        vec_load_f32<NC>(g, lane, gv);
+        float s1 = 0.0f, s2 = 0.0f;
+#pragma unroll
+        for (int c = 0; c < NC; c++)
+#pragma unroll
+            for (int e = 0; e < 8; e++) {
+                xh[c][e] = (xh[c][e] - mu) * rstd;
+                gv[c][e] *= d[c][e]; // dxh
+                s1 += gv[c][e];
+                s2 += gv[c][e] * xh[c][e];
+            }
+        s1 = warp_sum(s1) / (float)D;
+        s2 = warp_sum(s2) / (float)D;
+        if (mode == 2)
+            s1 = 0.0f;
+        if (base)
+            row_load<NC>(base + (size_t)r * D, lane, o);
+#pragma unroll
+        for (int c = 0; c < NC; c++)
+#pragma unroll
+            for (int e = 0; e < 8; e++) {
+                const float vv = rstd * (gv[c][e] - s1 - xh[c][e] * s2);
+                o[c][e] = round_to<bf16>(base ? vv + o[c][e] : vv);
+                xh[c][e] *= d[c][e]; // dg contribution
+            }
+        row_store<NC>(dx + (size_t)r * D, lane, o);
+    } else {
+#pragma unroll
+        for (int c = 0; c < NC; c++)
+#pragma unroll
+            for (int e = 0; e < 8; e++)
+                xh[c][e] = d[c][e] = o[c][e] = 0.0f;
+    }
+#pragma unroll
+    for (int c = 0; c < NC; c++)
+#pragma unroll
+        for (int e = 0; e < 8; e++) {
+            const int col = c * 256 + lane * 8 + e;
+            mine[col] = xh[c][e];
+            mine[D + col] = d[c][e];
+            mine[2 * D + col] = want_sum ? o[c][e] : 0.0f;
+        }
+    __syncthreads();
+    for (int i = threadIdx.x; i < 3 * D; i += blockDim.x) {
+        float s = 0.0f;
+#pragma unroll
+        for (int w = 0; w < 8; w++)
+            s += sm[(size_t)w * 3 * D + i];
+        part[(size_t)blockIdx.x * 3 * D + i] = s;
+    }
+}
+
 // Column reduction of partial sums, fixed order: out_k[c] = sum_p part[p*stride + off_k + c].
 // blockIdx.y selects the output k (up to 3); a block owns 32 columns, its 8 warps each sum
 // a contiguous range of parts, and the 8 range sums are added in range order.
@@ -143,6 +326,8 @@ struct ReduceOut {
 __global__ void __launch_bounds__(256)
 reduce_cols_kernel(const float *__restrict__ part, int n_parts, int stride, int n, ReduceOut ro)
 {
+    pdl_trigger();
+    pdl_wait();
     __shared__ float sm[8][33];
     const int c = blockIdx.x * 32 + (threadIdx.x & 31), grp = threadIdx.x >> 5;
     const int k = blockIdx.y;
@@ -227,6 +412,8 @@ __global__ void act_fwd_kernel(const T *__restrict__ hpre, T *__restrict__ hact,
 __global__ void act_fwd_vec_kernel(const bf16 *__restrict__ hpre, bf16 *__restrict__ hact, int rows, int F,
                                    int F1, int act)
 {
+    pdl_trigger();
+    pdl_wait();
     const int cpr = F / 8;
     const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= (size_t)rows * cpr)
@@ -298,6 +485,8 @@ __global__ void __launch_bounds__(128)
 act_bwd_vec_kernel(const bf16 *__restrict__ hpre, const bf16 *__restrict__ dhact, bf16 *__restrict__ dhpre,
                    float *__restrict__ part, int rows, int F, int F1, int act)
 {
+    pdl_trigger();
+    pdl_wait();
     const int i = (blockIdx.x * 128 + threadIdx.x) * 2;
     if (i >= F)
         return;
@@ -371,6 +560,8 @@ __device__ __forceinline__ float block_max_256(float v, float *red)
 // in-place softmax over the V symbols of each row of fp32 logits (nc_soft_max, nncp.c:1008)
 __global__ void __launch_bounds__(256) softmax_rows_kernel(float *__restrict__ z, int rows, int V)
 {
+    pdl_trigger();
+    pdl_wait();
     __shared__ float red[8];
     int r = blockIdx.x;
     if (r >= rows)
@@ -392,6 +583,50 @@ __global__ void __launch_bounds__(256) softmax_rows_kernel(float *__restrict__ z
         zr[i] *= rs;
 }
 
+// The same for rows of up to 16384 logits, V a multiple of 1024: the row stays in registers
+// (one read and one write of memory, 16-byte accesses).  Thread t owns logits (k*256 + t)*4 .. +3.
+__global__ void __launch_bounds__(256) softmax_rows_reg_kernel(float *__restrict__ z, int rows, int V)
+{
+    pdl_trigger();
+    pdl_wait();
+    __shared__ float red[8];
+    const int r = blockIdx.x;
+    if (r >= rows)
+        return;
+    float4 *zr = reinterpret_cast<float4 *>(z + (size_t)r * V);
+    const int nv = V / 1024;
+    float4 v[16];
+    float mx = -INFINITY;
+#pragma unroll
+    for (int k = 0; k < 16; k++)
+        if (k < nv) {
+            v[k] = zr[k * 256 + threadIdx.x];
+            mx = fmaxf(mx, fmaxf(fmaxf(v[k].x, v[k].y), fmaxf(v[k].z, v[k].w)));
+        }
+    mx = block_max_256(mx, red);
+    float s = 0.0f;
+#pragma unroll
+    for (int k = 0; k < 16; k++)
+        if (k < nv) {
+            v[k].x = expf(v[k].x - mx);
+            v[k].y = expf(v[k].y - mx);
+            v[k].z = expf(v[k].z - mx);
+            v[k].w = expf(v[k].w - mx);
+            s += (v[k].x + v[k].y) + (v[k].z + v[k].w);
+        }
+    s = block_sum_256(s, red);
+    const float rs = 1.0f / s;
+#pragma unroll
+    for (int k = 0; k < 16; k++)
+        if (k < nv) {
+            v[k].x *= rs;
+            v[k].y *= rs;
+            v[k].z *= rs;
+            v[k].w *= rs;
+            zr[k * 256 + threadIdx.x] = v[k];
+        }
+}
+
 // dz = (p - onehot(target)) * scale ; logp[r] = ln p[r][target]
 // (nc_indexed_log + the adjoint of softmax, nncp.c:1170-1175)
 template <typename T>
@@ -399,6 +634,8 @@ __global__ void __launch_bounds__(256)
 loss_grad_kernel(const float *__restrict__ probs, const int32_t *__restrict__ targets,
                  T *__restrict__ dz, float *__restrict__ logp, int rows, int V, float scale)
 {
+    pdl_trigger();
+    pdl_wait();
     int r = blockIdx.x;
     if (r >= rows)
         return;
@@ -416,6 +653,8 @@ loss_grad_kernel(const float *__restrict__ probs, const int32_t *__restrict__ ta
 __global__ void __launch_bounds__(256) sum_vec_kernel(const float *__restrict__ v, int n,
                                                       float *__restrict__ out)
 {
+    pdl_trigger();
+    pdl_wait();
     __shared__ float red[8];
     float s = 0.0f;
     for (int i = threadIdx.x; i < n; i += 256)
@@ -430,6 +669,8 @@ template <typename T>
 __global__ void colsum_part_kernel(const T *__restrict__ A, long lda, int R, int N, int rows_per,
                                    float *__restrict__ part)
 {
+    pdl_trigger();
+    pdl_wait();
     int n = blockIdx.x * blockDim.x + threadIdx.x;
     if (n >= N)
         return;
@@ -449,6 +690,8 @@ rmsprop_kernel(float *__restrict__ w, const float *__restrict__ g, float *__rest
                bf16 *__restrict__ shadow, size_t n4, float lr, float beta2, float eps,
                float clip, float corr)
 {
+    pdl_trigger();
+    pdl_wait();
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n4)
         return;
@@ -494,6 +737,8 @@ __global__ void __launch_bounds__(128)
 embed_grad_kernel(const int32_t *__restrict__ ids, const T *__restrict__ dx,
                   float *__restrict__ g, int rows, int D, float mult, int V)
 {
+    pdl_trigger();
+    pdl_wait();
     extern __shared__ int32_t sm_i[]; // sids[rows], list[rows]
     int32_t *sids = sm_i, *list = sm_i + rows;
     __shared__ int seen_before, wcnt[4], count;

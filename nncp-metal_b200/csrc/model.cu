@@ -334,7 +334,7 @@ static int reduce_cols(nncu_model *m, const float *part, int n_parts, int stride
     ro.out[1] = o1; ro.off[1] = off1;
     ro.out[2] = o2; ro.off[2] = off2;
     int nout = o2 ? 3 : (o1 ? 2 : 1);
-    reduce_cols_kernel<<<dim3(ceil_div(n, 32), nout), 256, 0, side_fork(m)>>>(part, n_parts, stride, n, ro);
+    launch_k(reduce_cols_kernel, dim3(ceil_div(n, 32), nout), dim3(256), 0, side_fork(m), part, n_parts, stride, n, ro);
     KERNEL_CHECK();
     return NNCU_OK;
 }
@@ -345,7 +345,7 @@ static int colsum(nncu_model *m, const AT *A, long lda, int R, int N, float *out
     const int rows_per = 64;
     int chunks = ceil_div(R, rows_per);
     float *part = part_slot(m);
-    colsum_part_kernel<AT><<<dim3(ceil_div(N, 128), chunks), 128, 0, side_fork(m)>>>(A, lda, R, N, rows_per, part);
+    launch_k(colsum_part_kernel<AT>, dim3(ceil_div(N, 128), chunks), dim3(128), 0, side_fork(m), A, lda, R, N, rows_per, part);
     KERNEL_CHECK();
     return reduce_cols(m, part, chunks, N, N, out, 0);
 }
@@ -355,9 +355,23 @@ static int norm_fwd(nncu_model *m, const AT *a, const AT *res, AT *s_out, AT *y,
                     size_t b_off, float *stats, int rows, bool do_norm)
 {
     int mode = !do_norm ? 0 : ((m->p.ln_flags & NNCU_LN_RMSNORM) ? 2 : 1);
-    residual_norm_kernel<AT><<<ceil_div(rows, 4), 128, 0, m->st>>>(
-        a, res, s_out, y, do_norm ? m->W + g_off : nullptr, do_norm ? m->W + b_off : nullptr, stats,
-        rows, m->D, mode);
+    const float *g = do_norm ? m->W + g_off : nullptr, *b = do_norm ? m->W + b_off : nullptr;
+    if (sizeof(AT) == 2 && (m->D == 256 || m->D == 512 || m->D == 1024 || m->D == 2048)) {
+        // rows that fit in a warp's registers: one pass, 16-byte accesses
+        const bf16 *a16 = (const bf16 *)a, *r16 = (const bf16 *)res;
+        bf16 *s16 = (bf16 *)s_out, *y16 = (bf16 *)y;
+        const dim3 grid(ceil_div(rows, 4)), block(128);
+        switch (m->D / 256) {
+        case 1: launch_k(residual_norm_vec_kernel<1>, grid, block, 0, m->st, a16, r16, s16, y16, g, b, stats, rows, mode); break;
+        case 2: launch_k(residual_norm_vec_kernel<2>, grid, block, 0, m->st, a16, r16, s16, y16, g, b, stats, rows, mode); break;
+        case 4: launch_k(residual_norm_vec_kernel<4>, grid, block, 0, m->st, a16, r16, s16, y16, g, b, stats, rows, mode); break;
+        default: launch_k(residual_norm_vec_kernel<8>, grid, block, 0, m->st, a16, r16, s16, y16, g, b, stats, rows, mode); break;
+        }
+        KERNEL_CHECK();
+        return NNCU_OK;
+    }
+    launch_k(residual_norm_kernel<AT>, dim3(ceil_div(rows, 4)), dim3(128), 0, m->st, a, res, s_out, y, g, b, stats,
+             rows, m->D, mode);
     KERNEL_CHECK();
     return NNCU_OK;
 }
@@ -371,8 +385,20 @@ static int norm_bwd(nncu_model *m, const AT *dy, const AT *x, size_t g_off, size
     int mode = (m->p.ln_flags & NNCU_LN_RMSNORM) ? 2 : 1;
     size_t smem = (size_t)8 * 3 * m->D * sizeof(float);
     float *part = part_slot(m);
-    norm_bwd_kernel<AT><<<blocks, 256, smem, m->st>>>(dy, x, m->W + g_off, stats, base, dx, part,
-                                                      rows, m->D, mode, rpb, dxsum ? 1 : 0);
+    if (sizeof(AT) == 2 && (m->D == 256 || m->D == 512 || m->D == 1024)) {
+        const bf16 *dy16 = (const bf16 *)dy, *x16 = (const bf16 *)x, *b16 = (const bf16 *)base;
+        bf16 *dx16 = (bf16 *)dx;
+        const float *g = m->W + g_off;
+        const int ws = dxsum ? 1 : 0;
+        switch (m->D / 256) {
+        case 1: launch_k(norm_bwd_vec_kernel<1>, dim3(blocks), dim3(256), smem, m->st, dy16, x16, g, stats, b16, dx16, part, rows, mode, ws); break;
+        case 2: launch_k(norm_bwd_vec_kernel<2>, dim3(blocks), dim3(256), smem, m->st, dy16, x16, g, stats, b16, dx16, part, rows, mode, ws); break;
+        default: launch_k(norm_bwd_vec_kernel<4>, dim3(blocks), dim3(256), smem, m->st, dy16, x16, g, stats, b16, dx16, part, rows, mode, ws); break;
+        }
+    } else {
+        launch_k(norm_bwd_kernel<AT>, dim3(blocks), dim3(256), smem, m->st, dy, x, m->W + g_off, stats, base, dx, part,
+                 rows, m->D, mode, rpb, dxsum ? 1 : 0);
+    }
     KERNEL_CHECK();
     return reduce_cols(m, part, blocks, 3 * m->D, m->D, gf(m, g_off), 0, gf(m, b_off), m->D, dxsum, 2 * m->D);
 }
@@ -453,7 +479,7 @@ static int forward_range(nncu_model *m, int t0, int t1)
     const float emul = sqrtf((float)D) * p.embed_mult;
     AT *tmp = reinterpret_cast<AT *>(m->pool[0]); // [TB][D] scratch
 
-    embed_kernel<AT><<<nr, 128, 0, m->st>>>(m->ids_dev + r0, m->W + m->embed,
+    launch_k(embed_kernel<AT>, dim3(nr), dim3(128), 0, m->st, m->ids_dev + r0, m->W + m->embed,
                                             at<AT>(m->act[0].xin, (size_t)r0 * D), nr, D, emul, V);
     KERNEL_CHECK();
     for (int l = 0; l < m->nl; l++) {
@@ -493,7 +519,7 @@ static int forward_range(nncu_model *m, int t0, int t1)
         AT *hpre = at<AT>(a.hpre, (size_t)r0 * F1), *hact = at<AT>(a.hact, (size_t)r0 * F);
         NNCU_TRY((mm_nt<AT, AT>(m, nr, F1, D, u, D, o.ff1, hpre, F1, wf(m, o.ff_bias1))));
         if (sizeof(AT) == 2 && F % 8 == 0 && F1 % 8 == 0)
-            act_fwd_vec_kernel<<<ceil_div((long long)nr * (F / 8), 256), 256, 0, m->st>>>(
+            launch_k(act_fwd_vec_kernel, dim3(ceil_div((long long)nr * (F / 8), 256)), dim3(256), 0, m->st, 
                 (const bf16 *)hpre, (bf16 *)hact, nr, F, F1, p.ff_act);
         else
             act_fwd_kernel<AT><<<ceil_div((long long)nr * F, 256), 256, 0, m->st>>>(hpre, hact, nr, F, F1, p.ff_act);
@@ -512,7 +538,10 @@ static int forward_range(nncu_model *m, int t0, int t1)
     }
     float *pr = m->probs + (size_t)r0 * V;
     NNCU_TRY((mm_nt<AT, float>(m, nr, V, D, xf, D, m->embed_out, pr, V, wf(m, m->out_bias))));
-    softmax_rows_kernel<<<nr, 256, 0, m->st>>>(pr, nr, V);
+    if (V % 1024 == 0 && V <= 16384)
+        launch_k(softmax_rows_reg_kernel, dim3(nr), dim3(256), 0, m->st, pr, nr, V);
+    else
+        launch_k(softmax_rows_kernel, dim3(nr), dim3(256), 0, m->st, pr, nr, V);
     KERNEL_CHECK();
     return NNCU_OK;
 }
@@ -573,9 +602,9 @@ static int backward(nncu_model *m)
 
     // loss and d logits (nncp.c:1170-1175)
     const float sc = 1.0f / ((float)m->T * (float)m->Bt);
-    loss_grad_kernel<AT><<<TB, 256, 0, m->st>>>(m->probs, m->tgt_dev, dz, m->logp, TB, V, sc);
+    launch_k(loss_grad_kernel<AT>, dim3(TB), dim3(256), 0, m->st, m->probs, m->tgt_dev, dz, m->logp, TB, V, sc);
     KERNEL_CHECK();
-    sum_vec_kernel<<<1, 256, 0, m->st>>>(m->logp, TB, m->loss_dev);
+    launch_k(sum_vec_kernel, dim3(1), dim3(256), 0, m->st, m->logp, TB, m->loss_dev);
     KERNEL_CHECK();
     const AT *xf = (p.ln_flags & NNCU_LN_FINAL) ? atc<AT>(m->xf, 0) : atc<AT>(m->xlast, 0);
     if (m->out_bias != NONE)
@@ -614,7 +643,7 @@ static int backward(nncu_model *m)
         const bool act_vec = sizeof(AT) == 2 && F % 2 == 0;
         const int act_rows = act_vec ? ACT_BWD_ROWS : 32;
         if (act_vec)
-            act_bwd_vec_kernel<<<dim3(ceil_div(F, 256), ceil_div(TB, act_rows)), 128, 0, m->st>>>(
+            launch_k(act_bwd_vec_kernel, dim3(ceil_div(F, 256), ceil_div(TB, act_rows)), dim3(128), 0, m->st, 
                 (const bf16 *)atc<AT>(a.hpre, 0), (const bf16 *)dh, (bf16 *)dhp, apart, TB, F, F1, p.ff_act);
         else
             act_bwd_kernel<AT><<<dim3(ceil_div(F, 128), ceil_div(TB, act_rows)), 128, 0, m->st>>>(
@@ -648,12 +677,12 @@ static int backward(nncu_model *m)
             // on the side stream: the partials are next written after the join at the layer's end
             cudaStream_t s2 = side_fork(m);
             size_t nb = (size_t)m->H * m->L;
-            reduce_streams_kernel<<<ceil_div(nb, 256), 256, 0, s2>>>(m->dbr_part, B, nb, gf(m, o.b_r),
+            launch_k(reduce_streams_kernel, dim3(ceil_div(nb, 256)), dim3(256), 0, s2, m->dbr_part, B, nb, gf(m, o.b_r),
                                                                     p.tied_b_r ? 1 : 0);
             KERNEL_CHECK();
             if (o.w_r != NONE) {
                 size_t nw = (size_t)m->H * p.d_pos * m->dk;
-                reduce_streams_kernel<<<ceil_div(nw, 256), 256, 0, s2>>>(m->dwr_part, B, nw, gf(m, o.w_r),
+                launch_k(reduce_streams_kernel, dim3(ceil_div(nw, 256)), dim3(256), 0, s2, m->dwr_part, B, nw, gf(m, o.w_r),
                                                                         p.tied_w_r ? 1 : 0);
                 KERNEL_CHECK();
             }
@@ -682,7 +711,7 @@ static int backward(nncu_model *m)
     }
     const float emul = sqrtf((float)D) * p.embed_mult;
     CUDA_TRY(cudaMemsetAsync(gf(m, m->embed), 0, sizeof(float) * (size_t)V * D, m->st));
-    embed_grad_kernel<AT><<<TB, 128, 2 * sizeof(int32_t) * TB, m->st>>>(m->ids_dev, dx, gf(m, m->embed), TB, D, emul, V);
+    launch_k(embed_grad_kernel<AT>, dim3(TB), dim3(128), 2 * sizeof(int32_t) * TB, m->st, m->ids_dev, dx, gf(m, m->embed), TB, D, emul, V);
     KERNEL_CHECK();
     side_join(m);
     NNCU_TRY(exchange_bucket(m, m->tail_begin, m->embed_out)); // final norm and the embedding
@@ -1086,6 +1115,8 @@ int nncu_create(const nncu_params *p, nncu_model **out)
     if ((size_t)8 * 3 * D * 4 > 48 * 1024) {
         cudaFuncSetAttribute(norm_bwd_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 8 * 3 * D * 4);
         cudaFuncSetAttribute(norm_bwd_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 8 * 3 * D * 4);
+        if (D == 1024)
+            cudaFuncSetAttribute(norm_bwd_vec_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 8 * 3 * D * 4);
     }
     if ((size_t)2 * V * 4 > 48 * 1024) {
         cudaFuncSetAttribute(coder_paths_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 2 * V * 4);
@@ -1288,7 +1319,7 @@ int nncu_optimizer_step(nncu_model *m)
     if (m->p.bias_correction)
         corr = 1.0f / (1.0f - powf(m->p.beta2, (float)m->step));
     size_t n4 = m->n_floats / 4;
-    rmsprop_kernel<<<ceil_div(n4, 256), 256, 0, m->st>>>(m->W, m->G, m->Vm, m->Wb, n4, m->lr, m->p.beta2,
+    launch_k(rmsprop_kernel, dim3(ceil_div(n4, 256)), dim3(256), 0, m->st, m->W, m->G, m->Vm, m->Wb, n4, m->lr, m->p.beta2,
                                                          m->p.eps, m->p.gradient_clip, corr);
     KERNEL_CHECK();
     return refresh_transposed(m);
@@ -1569,12 +1600,12 @@ int nncu_attention_reduce_tables(const nncu_attn_shape *s, const float *dwr_part
     const int L = s->mem_len + s->seg_len;
     if (dbr_part && db_r) {
         size_t n = (size_t)s->n_head * L;
-        reduce_streams_kernel<<<ceil_div(n, 256), 256, 0, st>>>(dbr_part, s->n_streams, n, db_r, accumulate);
+        launch_k(reduce_streams_kernel, dim3(ceil_div(n, 256)), dim3(256), 0, st, dbr_part, s->n_streams, n, db_r, accumulate);
         KERNEL_CHECK();
     }
     if (dwr_part && dw_r) {
         size_t n = (size_t)s->n_head * s->d_pos * s->d_key;
-        reduce_streams_kernel<<<ceil_div(n, 256), 256, 0, st>>>(dwr_part, s->n_streams, n, dw_r, accumulate);
+        launch_k(reduce_streams_kernel, dim3(ceil_div(n, 256)), dim3(256), 0, st, dwr_part, s->n_streams, n, dw_r, accumulate);
         KERNEL_CHECK();
     }
     return NNCU_OK;
@@ -1624,11 +1655,11 @@ int nncu_attention_backward_noalloc(const nncu_attn_shape *s, const void *q, con
                  ? attn_backward_any<bf16>(s, q, kv, w_r, b_r, out, lse, dout, dq, dkv, dwr_part, dbr_part, st)
                  : attn_backward_any<float>(s, q, kv, w_r, b_r, out, lse, dout, dq, dkv, dwr_part, dbr_part, st));
     const size_t nb = (size_t)s->n_head * L;
-    reduce_streams_kernel<<<ceil_div(nb, 256), 256, 0, st>>>(dbr_part, s->n_streams, nb, db_r, 0);
+    launch_k(reduce_streams_kernel, dim3(ceil_div(nb, 256)), dim3(256), 0, st, dbr_part, s->n_streams, nb, db_r, 0);
     KERNEL_CHECK();
     if (w_r) {
         const size_t nw = (size_t)s->n_head * s->d_pos * s->d_key;
-        reduce_streams_kernel<<<ceil_div(nw, 256), 256, 0, st>>>(dwr_part, s->n_streams, nw, dw_r, 0);
+        launch_k(reduce_streams_kernel, dim3(ceil_div(nw, 256)), dim3(256), 0, st, dwr_part, s->n_streams, nw, dw_r, 0);
         KERNEL_CHECK();
     }
     return NNCU_OK;
