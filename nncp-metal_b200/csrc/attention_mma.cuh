@@ -108,14 +108,24 @@ template <typename F>
 __device__ __forceinline__ void load_tile(bf16 *dst, int lds, const bf16 *src, size_t pitch, int nrows,
                                           int dk, F valid)
 {
+    // asynchronous 16-byte copies (no register staging, so a thread's copies are all in flight
+    // together); complete at the next tiles_ready()
     const int cpr = dk / 8;
     for (int idx = threadIdx.x; idx < nrows * cpr; idx += blockDim.x) {
         int r = idx / cpr, c = (idx % cpr) * 8;
-        uint4 v = make_uint4(0u, 0u, 0u, 0u);
-        if (valid(r))
-            v = *reinterpret_cast<const uint4 *>(src + (size_t)r * pitch + c);
-        *reinterpret_cast<uint4 *>(dst + (size_t)r * lds + c) = v;
+        bf16 *d = dst + (size_t)r * lds + c;
+        if (valid(r)) {
+            const uint32_t da = (uint32_t)__cvta_generic_to_shared(d);
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(da), "l"(src + (size_t)r * pitch + c) : "memory");
+        } else {
+            *reinterpret_cast<uint4 *>(d) = make_uint4(0u, 0u, 0u, 0u);
+        }
     }
+}
+// every load_tile copy of this thread has landed (call before the barrier that publishes the tiles)
+__device__ __forceinline__ void tiles_ready()
+{
+    asm volatile("cp.async.wait_all;" ::: "memory");
 }
 
 // rows [wbase, wbase + WR) of one head's position table -> shared; rows >= P are zero.  From the
@@ -246,6 +256,7 @@ __global__ void __launch_bounds__(128) attn_fwd_mma_kernel(AttnArgs a)
               [&](int r) { return qt0 + r >= a.t0 && qt0 + r < a.t1; });
     for (int r = threadIdx.x; r < a.L; r += blockDim.x)
         brs[r] = a.br_scale * a.b_r[(size_t)h * a.L + r];
+    tiles_ready();
     __syncthreads();
 
     // this warp's 16 query rows
@@ -292,6 +303,7 @@ __global__ void __launch_bounds__(128) attn_fwd_mma_kernel(AttnArgs a)
         load_table(Rs, d.LDS, a.w_r ? a.w_r + (size_t)h * a.P * DK : nullptr,
                    a.w_r16 ? reinterpret_cast<const bf16 *>(a.w_r16) + (size_t)h * a.P * DK : nullptr, a.P, wbase,
                    d.WR, DK);
+        tiles_ready();
         __syncthreads();
         if (!active)
             continue;
@@ -427,6 +439,8 @@ __global__ void __launch_bounds__(256) attn_bwd_mma_kernel(AttnArgs a)
     load_tile(dOs, d.LDS, dout + (size_t)b * HD + h * DK, (size_t)a.B * HD, 64, DK, [&](int r) { return r < T; });
     for (int r = threadIdx.x; r < L; r += blockDim.x)
         brs[r] = a.br_scale * a.b_r[(size_t)h * L + r];
+    if (threadIdx.x < 64)
+        lses[threadIdx.x] = threadIdx.x < T ? a.lse[((size_t)b * a.H + h) * T + threadIdx.x] : 0.0f;
     // this (stream, head)'s table-gradient slices start at zero; super-blocks add to them
     if (dwr)
         for (int i = threadIdx.x; i < P * DK; i += blockDim.x)
@@ -456,6 +470,7 @@ __global__ void __launch_bounds__(256) attn_bwd_mma_kernel(AttnArgs a)
                    d.WR, DK);
     };
     load_keys(sb_first);
+    tiles_ready();
     __syncthreads();
     // D_i = dO_i . O_i and the saved log-sum-exp, one warp per 8 rows
     for (int r = warp * 8; r < warp * 8 + 8; r++) {
@@ -463,10 +478,8 @@ __global__ void __launch_bounds__(256) attn_bwd_mma_kernel(AttnArgs a)
         for (int e = lane; e < DK; e += 32)
             s += to_f(dOs[(size_t)r * d.LDS + e]) * to_f(Os[(size_t)r * d.LDS + e]);
         s = warp_sum(s);
-        if (lane == 0) {
+        if (lane == 0)
             Dr[r] = s;
-            lses[r] = r < T ? a.lse[((size_t)b * a.H + h) * T + r] : 0.0f;
-        }
     }
 
     AT_STAMP(1);
@@ -507,6 +520,10 @@ __global__ void __launch_bounds__(256) attn_bwd_mma_kernel(AttnArgs a)
         __syncthreads(); // previous super-block fully consumed (first trip: prologue done)
         if (touched && sb != sb_first)
             load_keys(sb);
+        if (touched && a.w_r) // phase A scatters into the dE window; what it does not reach is zero
+            for (int idx = threadIdx.x; idx < 64 * d.PPS / 8; idx += blockDim.x)
+                reinterpret_cast<uint4 *>(dEm)[idx] = make_uint4(0u, 0u, 0u, 0u);
+        tiles_ready();
         __syncthreads();
         if (sb == 0) AT_STAMP(2);
         if (!touched) {
@@ -559,10 +576,32 @@ __global__ void __launch_bounds__(256) attn_bwd_mma_kernel(AttnArgs a)
                         const int col = j0 - j0s + nt * 8 + 2 * t;
                         *reinterpret_cast<uint32_t *>(Pm + (size_t)(i0 + g) * d.LPS + col) = pack2(p0, p1);
                         *reinterpret_cast<uint32_t *>(Pm + (size_t)(i0 + g + 8) * d.LPS + col) = pack2(p2, p3);
-                        *reinterpret_cast<uint32_t *>(dSm + (size_t)(i0 + g) * d.LPS + col) =
-                            pack2(p0 * (dp[nt][0] - DA) * a.inv_sqrt, p1 * (dp[nt][1] - DA) * a.inv_sqrt);
-                        *reinterpret_cast<uint32_t *>(dSm + (size_t)(i0 + g + 8) * d.LPS + col) =
-                            pack2(p2 * (dp[nt][2] - DB) * a.inv_sqrt, p3 * (dp[nt][3] - DB) * a.inv_sqrt);
+                        const __nv_bfloat162 dsA = __floats2bfloat162_rn(p0 * (dp[nt][0] - DA) * a.inv_sqrt,
+                                                                         p1 * (dp[nt][1] - DA) * a.inv_sqrt);
+                        const __nv_bfloat162 dsB = __floats2bfloat162_rn(p2 * (dp[nt][2] - DB) * a.inv_sqrt,
+                                                                         p3 * (dp[nt][3] - DB) * a.inv_sqrt);
+                        *reinterpret_cast<__nv_bfloat162 *>(dSm + (size_t)(i0 + g) * d.LPS + col) = dsA;
+                        *reinterpret_cast<__nv_bfloat162 *>(dSm + (size_t)(i0 + g + 8) * d.LPS + col) = dsB;
+                        if (a.w_r) {
+                            // inverse skew on the fly: dS[i][j] is dE[i][p] at table row p = j+T-1-i-(L-P)
+                            // when p >= 1 (row 0 collects several slots and is summed after the barrier)
+                            const int j = j0 + nt * 8 + 2 * t;
+                            const int pA = j + (T - 1) - iA - (L - P), pB = pA - 8;
+                            bf16 *eA = dEm + (size_t)(i0 + g) * d.PPS, *eB = dEm + (size_t)(i0 + g + 8) * d.PPS;
+                            const int wA = pA - wbase, wB = pB - wbase; // columns of the window
+                            if (iA < T) {
+                                if (j < L && pA >= 1 && pA < P && wA >= 0 && wA < d.WR)
+                                    eA[wA] = dsA.x;
+                                if (j + 1 < L && pA + 1 >= 1 && pA + 1 < P && wA + 1 >= 0 && wA + 1 < d.WR)
+                                    eA[wA + 1] = dsA.y;
+                            }
+                            if (iB < T) {
+                                if (j < L && pB >= 1 && pB < P && wB >= 0 && wB < d.WR)
+                                    eB[wB] = dsB.x;
+                                if (j + 1 < L && pB + 1 >= 1 && pB + 1 < P && wB + 1 >= 0 && wB + 1 < d.WR)
+                                    eB[wB + 1] = dsB.y;
+                            }
+                        }
                     }
                 }
             }
@@ -571,26 +610,17 @@ __global__ void __launch_bounds__(256) attn_bwd_mma_kernel(AttnArgs a)
         if (sb == 0) AT_STAMP(3);
         // ---- inverse skew for this super-block: dE[i][p] collects dS[i][j], p = max(j+T-1-i-(L-P), 0),
         //      over the window rows; db_r[r] += br_scale * sum_i dS[i][r-(T-1-i)]
-        for (int i = warp; i < 64; i += 8) {
-            const int shift = (L - P) - (T - 1 - i) - j0s; // key (local) = table row + shift, rows >= 1
-            for (int pw = lane; pw < d.WR; pw += 32) {
-                const int p = wbase + pw;
-                float v = 0.0f;
-                if (i < T && p < P && a.w_r) {
-                    if (p >= 1) {
-                        const int jl = p + shift;
-                        if (jl >= 0 && jl < d.SBK && j0s + jl < L)
-                            v = to_f(dSm[(size_t)i * d.LPS + jl]);
-                    } else {
-                        // slots 0 .. L-P share table row 0; only those whose key is in this super-block
-                        const int off = (T - 1 - i) + j0s;
-                        const int rhi = min(L - P, off + min(d.SBK, L - j0s) - 1);
-                        for (int r = max(0, off); r <= rhi; r++)
-                            v += to_f(dSm[(size_t)i * d.LPS + r - off]);
-                    }
-                }
-                dEm[(size_t)i * d.PPS + pw] = __float2bfloat16_rn(v);
+        if (a.w_r && wbase == 0 && threadIdx.x < 64) {
+            // table row 0 serves slots 0 .. L-P: the sum of those whose key is in this super-block
+            const int i = threadIdx.x;
+            float v = 0.0f;
+            if (i < T) {
+                const int off = (T - 1 - i) + j0s;
+                const int rhi = min(L - P, off + min(d.SBK, L - j0s) - 1);
+                for (int r = max(0, off); r <= rhi; r++)
+                    v += to_f(dSm[(size_t)i * d.LPS + r - off]);
             }
+            dEm[(size_t)i * d.PPS] = __float2bfloat16_rn(v);
         }
         if (dbr) {
             // slots whose (query, key) pairs can fall in this super-block
