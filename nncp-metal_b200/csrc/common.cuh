@@ -35,18 +35,21 @@ int nncu_fail(int code, const char *fmt, ...);
 // pdl_wait() (barrier set-up, TMEM allocation, index arithmetic) and block there until the
 // predecessor has completed and its writes are visible.  Rules for a kernel launched this way:
 // every thread executes pdl_wait() before its first global-memory access and before any early
-// return, so that the kernel cannot complete before its predecessor has.  pdl_trigger() lets the
-// successor start as soon as all CTAs of this kernel are resident.  Both are no-ops in a kernel
-// launched the ordinary way.  Off unless NNCU_PDL=1: on the c2 train step (graph replay, kernels of
-// 3-20 us) it measured 2 % slower than ordinary launches, the resident successors taking SM
-// resources from the side stream's kernels.
+// return, so that the kernel cannot complete before its predecessor has.  Both calls are no-ops in
+// a kernel launched the ordinary way.  Off unless NNCU_PDL=1: on the c2 train step (graph replay,
+// kernels of 3-20 us) it measured within 1 % of ordinary launches.  pdl_trigger() (successor
+// starts as soon as all CTAs of this kernel are resident) is compiled in only with
+// -DNNCU_PDL_TRIGGER: it measured 4 % slower, the resident successors taking SM resources from
+// the side stream's kernels.
 __device__ __forceinline__ void pdl_wait()
 {
     asm volatile("griddepcontrol.wait;" ::: "memory");
 }
 __device__ __forceinline__ void pdl_trigger()
 {
+#ifdef NNCU_PDL_TRIGGER
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+#endif
 }
 inline bool nncu_pdl_enabled()
 {

@@ -492,7 +492,11 @@ act_bwd_vec_kernel(const bf16 *__restrict__ hpre, const bf16 *__restrict__ dhact
         return;
     const int r0 = blockIdx.y * ACT_BWD_ROWS, r1 = min(rows, r0 + ACT_BWD_ROWS);
     float s0[2] = {0.0f, 0.0f}, s1[2] = {0.0f, 0.0f};
-    for (int r = r0; r < r1; r++) {
+#pragma unroll
+    for (int rr = 0; rr < ACT_BWD_ROWS; rr++) {
+        const int r = r0 + rr;
+        if (r >= r1)
+            break;
         const __nv_bfloat162 a2 = *reinterpret_cast<const __nv_bfloat162 *>(hpre + (size_t)r * F1 + i);
         const __nv_bfloat162 d2 = *reinterpret_cast<const __nv_bfloat162 *>(dhact + (size_t)r * F + i);
         const float a[2] = {__low2float(a2), __high2float(a2)}, d[2] = {__low2float(d2), __high2float(d2)};
