@@ -269,16 +269,24 @@ def main():
     nbits = C.c_int()
 
     def step_host(s):
-        m.eval(-1, ids_h[s].numpy(), read=False)
+        # encoder order: everything is queued before the host waits for anything, so the GPU
+        # never idles on the host (the range coder would run between _begin and _end)
+        ids, tg = ids_h[s].numpy(), tg_h[s].numpy()
+        m.eval(-1, ids, read=False)
         if nb:
-            lib.nncu_coder_paths(m.h, 0, T, tg_h[s].numpy().ctypes.data_as(C.c_void_p),
-                                 paths.ctypes.data_as(C.c_void_p), C.byref(nbits))
+            ck(lib.nncu_coder_paths_begin(m.h, 0, T, tg.ctypes.data_as(C.c_void_p)))
         else:
             m.read_probs(0, T)
-        loss = m.eval_gradient(tg_h[s].numpy())
+        ck(lib.nncu_eval_gradient(m.h, tg.ctypes.data_as(C.c_void_p), None))
         sharded.reduce_gradients()
         m.update()
-        return loss
+        if nb:
+            ck(lib.nncu_coder_paths_end(m.h, paths.ctypes.data_as(C.c_void_p), C.byref(nbits)))
+        return m.read_loss()
+
+    def ck(rc):
+        if rc != 0:
+            raise RuntimeError(lib.nncu_last_error().decode())
 
     def barrier():
         if world > 1:

@@ -178,7 +178,9 @@ int nncu_probs_dev(nncu_model *m, float **probs_dev);
  */
 int nncu_eval_gradient(nncu_model *m, const int32_t *expected_host, float *loss_out);
 int nncu_eval_gradient_dev(nncu_model *m, const int32_t *expected_dev);
-/* Reads the loss of the last nncu_eval_gradient*_dev (synchronises). */
+/* Reads the loss of the last nncu_eval_gradient / _dev.  The loss is copied to the host right
+   behind the backward pass, and this call waits for that copy only: work the host has queued
+   since (nncu_update, the next nncu_eval) keeps running. */
 int nncu_read_loss(nncu_model *m, float *loss_out);
 /* model_update (nncp.c:1224-1235): optimizer step, then the memory shift. */
 int nncu_update(nncu_model *m);
@@ -234,6 +236,19 @@ int nncu_weights_hash(nncu_model *m, uint64_t *hash_out);
  */
 int nncu_coder_paths(nncu_model *m, int t0, int nt, const int32_t *sym_host,
                      uint16_t *prob0_host, int *n_bits_out);
+/*
+ * The same in two halves, for an encoder: _begin queues the work behind the
+ * forward pass and returns without waiting; _end waits for it and hands the
+ * values over.  Between the two the host may call nncu_eval_gradient for
+ * the segment (an encoder knows the targets already), so that the backward
+ * pass is queued before the host starts range-coding and the GPU never
+ * idles on the host.  No counterpart in the reference, whose process_block
+ * (nncp.c:3003-3053) runs eval, coder and gradient strictly in turn; a
+ * decoder, which learns the symbols only from the coder, keeps that order.
+ * One _begin may be outstanding; NNCU_ERR_STATE otherwise.
+ */
+int nncu_coder_paths_begin(nncu_model *m, int t0, int nt, const int32_t *sym_host);
+int nncu_coder_paths_end(nncu_model *m, uint16_t *prob0_host, int *n_bits_out);
 /*
  * For the same rows writes the whole implicit tree: prob0 of node k
  * (heap order: root = 1, children 2k and 2k+1) at tree_host[row][k],

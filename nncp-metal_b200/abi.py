@@ -107,6 +107,8 @@ PROTOTYPES = {
     "nncu_comm_init": (_i, [_vp, _i, _i, _vp]),
     "nncu_weights_hash": (_i, [_vp, C.POINTER(C.c_uint64)]),
     "nncu_coder_paths": (_i, [_vp, _i, _i, _vp, _vp, C.POINTER(_i)]),
+    "nncu_coder_paths_begin": (_i, [_vp, _i, _i, _vp]),
+    "nncu_coder_paths_end": (_i, [_vp, _vp, C.POINTER(_i)]),
     "nncu_coder_trees": (_i, [_vp, _i, _i, _vp]),
     "nncu_attention_forward": (_i, [C.POINTER(AttnShape), _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "nncu_attention_backward": (_i, [C.POINTER(AttnShape)] + [_vp] * 12),

@@ -441,13 +441,6 @@ __global__ void __launch_bounds__(256) attn_bwd_mma_kernel(AttnArgs a)
         brs[r] = a.br_scale * a.b_r[(size_t)h * L + r];
     if (threadIdx.x < 64)
         lses[threadIdx.x] = threadIdx.x < T ? a.lse[((size_t)b * a.H + h) * T + threadIdx.x] : 0.0f;
-    // this (stream, head)'s table-gradient slices start at zero; super-blocks add to them
-    if (dwr)
-        for (int i = threadIdx.x; i < P * DK; i += blockDim.x)
-            dwr[i] = 0.0f;
-    if (dbr)
-        for (int i = threadIdx.x; i < L; i += blockDim.x)
-            dbr[i] = 0.0f;
     // the forward output, parked in the skew scratch (not needed before phase A)
     bf16 *Os = reinterpret_cast<bf16 *>(Es);
     load_tile(Os, d.LDS, outp + (size_t)b * HD + h * DK, (size_t)a.B * HD, 64, DK, [&](int r) { return r < T; });
@@ -470,6 +463,19 @@ __global__ void __launch_bounds__(256) attn_bwd_mma_kernel(AttnArgs a)
                    d.WR, DK);
     };
     load_keys(sb_first);
+    // This (stream, head)'s table-gradient slices start at zero and the super-blocks add to them;
+    // a single super-block whose window covers the whole table stores every entry itself.
+    {
+        const int j0f = sb_first * d.SBK;
+        const bool all_rows = single && window_base(a, j0f, 63) == 0 && d.WR >= P;
+        const bool all_slots = single && j0f == 0 && j0f + d.SBK - 1 + (T - 1) >= L - 1;
+        if (dwr && !all_rows)
+            for (int i = threadIdx.x; i < P * DK; i += blockDim.x)
+                dwr[i] = 0.0f;
+        if (dbr && !all_slots)
+            for (int i = threadIdx.x; i < L; i += blockDim.x)
+                dbr[i] = 0.0f;
+    }
     tiles_ready();
     __syncthreads();
     // D_i = dO_i . O_i and the saved log-sum-exp, one warp per 8 rows

@@ -62,6 +62,74 @@ coder_paths_kernel(const float *__restrict__ probs, const int32_t *__restrict__ 
     }
 }
 
+// The same values for V = 1024 .. 16384 without building the tree in shared memory: the row is
+// read once (coalesced float4), the pairwise sums run through registers, warp shuffles and a
+// 128-entry heap, and a thread that holds the left child of a node on the symbol's path drops it
+// into p0s[depth].  Nodes carry their heap index K (root 1, children 2K and 2K+1, leaf i = V+i),
+// so "left child of the path node at depth d" is K == 2 * ((V + sym) >> (L - d)).  Every sum is
+// S[2K] + S[2K+1] of the same heap as build_sum_tree (fp32 addition commutes, so which of the two
+// lanes adds first does not matter): the results are bit-identical to coder_paths_kernel.
+__global__ void __launch_bounds__(256)
+coder_paths_fast_kernel(const float *__restrict__ probs, const int32_t *__restrict__ sym,
+                        uint16_t *__restrict__ out, int V, int n_bits)
+{
+    __shared__ float heap[256]; // top of the tree: entries [1, 2*NW), NW = V/128 <= 128
+    __shared__ float p0s[16];
+    const int row = blockIdx.x, tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
+    const int L = n_bits, nv4 = V >> 10, NW = V >> 7;
+    int s = sym[row];
+    s = s < 0 ? 0 : (s >= V ? V - 1 : s);
+    const unsigned leafK = (unsigned)(V + s);
+    auto keep = [&](unsigned K, float v) { // K: heap index of a node at depth d+1
+        const int d = 30 - __clz((int)K);  // floor(log2 K) - 1 = depth of its parent
+        if (!(K & 1u) && (K >> 1) == (leafK >> (L - d)))
+            p0s[d] = v;
+    };
+    const float4 *pr = reinterpret_cast<const float4 *>(probs + (size_t)row * V);
+#pragma unroll
+    for (int j = 0; j < 16; j++) {
+        if (j < nv4) {
+            const unsigned g = (unsigned)(j * 256 + tid);
+            const float4 q = pr[g];
+            keep((unsigned)V + 4u * g, q.x); // a leaf that is a left child
+            keep((unsigned)V + 4u * g + 2u, q.z);
+            const float a = __fadd_rn(q.x, q.y), b = __fadd_rn(q.z, q.w);
+            keep((unsigned)(V >> 1) + 2u * g, a);
+            float v = __fadd_rn(a, b);
+            keep((unsigned)(V >> 2) + g, v);
+#pragma unroll
+            for (int q2 = 1; q2 <= 5; q2++) {
+                v = __fadd_rn(v, __shfl_xor_sync(0xffffffffu, v, 1 << (q2 - 1)));
+                if ((lane & ((1 << q2) - 1)) == 0)
+                    keep((unsigned)(V >> (2 + q2)) + (g >> q2), v);
+            }
+            if (lane == 0)
+                heap[NW + j * 8 + w] = v; // depth log2(NW): node NW + (g >> 5)
+        }
+    }
+    __syncthreads();
+    if (w == 0) {
+        for (int n = NW >> 1; n >= 1; n >>= 1) {
+            for (int k = n + lane; k < 2 * n; k += 32) {
+                const float v = __fadd_rn(heap[2 * k], heap[2 * k + 1]);
+                heap[k] = v;
+                if (k > 1)
+                    keep((unsigned)k, v);
+            }
+            __syncwarp();
+        }
+        if (lane == 0) {
+            float p = 1.0f;
+            for (int lvl = 0; lvl < n_bits; lvl++) {
+                const float p0 = p0s[lvl];
+                out[(size_t)row * n_bits + lvl] = (uint16_t)prob0_of(p0, p);
+                const int bit = (s >> (n_bits - 1 - lvl)) & 1;
+                p = bit ? __fsub_rn(p, p0) : p0;
+            }
+        }
+    }
+}
+
 // one block per row: prob0 of every internal node, heap order, entry 0 unused
 __global__ void __launch_bounds__(256)
 coder_trees_kernel(const float *__restrict__ probs, uint16_t *__restrict__ out, int V)

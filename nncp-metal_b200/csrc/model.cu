@@ -157,8 +157,14 @@ struct nncu_model {
     uint16_t *coder_dev;
     size_t coder_bytes;
     // host staging (pinned)
-    int32_t *ids_pin, *tgt_pin;
+    int32_t *ids_pin, *tgt_pin, *sym_pin; // pinned staging of ids, targets, coder symbols
+    uint16_t *coder_pin;                  // pinned landing area of nncu_coder_paths_begin
     float *loss_pin;
+    // recorded after the copy that reads (ids, tgt, sym) or writes (coder) the staging area;
+    // the next user of the area waits for the event instead of draining the stream
+    cudaEvent_t ev_ids = nullptr, ev_tgt = nullptr, ev_sym = nullptr, ev_coder = nullptr, ev_loss = nullptr;
+    int loss_pending = 0; // the loss of the last backward pass is on its way to loss_pin
+    int coder_rows = 0, coder_nb = 0; // what nncu_coder_paths_begin has in flight
     float lr;
     long step;
     int steps_done;
@@ -900,6 +906,13 @@ int nncu_destroy(nncu_model *m)
     if (m->arena) cudaFree(m->arena);
     if (m->ids_pin) cudaFreeHost(m->ids_pin);
     if (m->tgt_pin) cudaFreeHost(m->tgt_pin);
+    if (m->sym_pin) cudaFreeHost(m->sym_pin);
+    if (m->coder_pin) cudaFreeHost(m->coder_pin);
+    if (m->ev_ids) cudaEventDestroy(m->ev_ids);
+    if (m->ev_tgt) cudaEventDestroy(m->ev_tgt);
+    if (m->ev_sym) cudaEventDestroy(m->ev_sym);
+    if (m->ev_coder) cudaEventDestroy(m->ev_coder);
+    if (m->ev_loss) cudaEventDestroy(m->ev_loss);
     if (m->loss_pin) cudaFreeHost(m->loss_pin);
     delete m;
     return NNCU_OK;
@@ -1107,8 +1120,16 @@ int nncu_create(const nncu_params *p, nncu_model **out)
     }
     if (cudaMallocHost(&m->ids_pin, sizeof(int32_t) * TB) != cudaSuccess ||
         cudaMallocHost(&m->tgt_pin, sizeof(int32_t) * TB) != cudaSuccess ||
+        cudaMallocHost(&m->sym_pin, sizeof(int32_t) * TB) != cudaSuccess ||
+        cudaMallocHost(&m->coder_pin, sizeof(uint16_t) * TB * 16) != cudaSuccess ||
         cudaMallocHost(&m->loss_pin, 64) != cudaSuccess)
         return fail_cleanup(nncu_fail(NNCU_ERR_NOMEM, "pinned host allocation failed"));
+    if (cudaEventCreateWithFlags(&m->ev_ids, cudaEventDisableTiming) != cudaSuccess ||
+        cudaEventCreateWithFlags(&m->ev_tgt, cudaEventDisableTiming) != cudaSuccess ||
+        cudaEventCreateWithFlags(&m->ev_sym, cudaEventDisableTiming) != cudaSuccess ||
+        cudaEventCreateWithFlags(&m->ev_coder, cudaEventDisableTiming) != cudaSuccess ||
+        cudaEventCreateWithFlags(&m->ev_loss, cudaEventDisableTiming) != cudaSuccess)
+        return fail_cleanup(nncu_fail(NNCU_ERR_CUDA, "event creation failed"));
     if (!jobs.empty() &&
         cudaMemcpy(m->jobs_dev, jobs.data(), sizeof(TransposeJob) * jobs.size(), cudaMemcpyHostToDevice) != cudaSuccess)
         return fail_cleanup(nncu_fail(NNCU_ERR_CUDA, "job table upload failed"));
@@ -1218,11 +1239,12 @@ int nncu_eval(nncu_model *m, int output_index, const int32_t *input_host)
     if (output_index >= m->T)
         return nncu_fail(NNCU_ERR_INVALID, "output_index %d >= seg_len %d", output_index, m->T);
     int t0 = output_index < 0 ? 0 : output_index, n = output_index < 0 ? m->TB : m->B;
-    // the staging buffer may still feed an earlier copy
-    CUDA_TRY(cudaStreamSynchronize(m->st));
+    // the staging buffer may still feed the copy of the call before (an unrecorded event is complete)
+    CUDA_TRY(cudaEventSynchronize(m->ev_ids));
     memcpy(m->ids_pin + (size_t)t0 * m->B, input_host + (size_t)t0 * m->B, sizeof(int32_t) * n);
     CUDA_TRY(cudaMemcpyAsync(m->ids_dev + (size_t)t0 * m->B, m->ids_pin + (size_t)t0 * m->B,
                              sizeof(int32_t) * n, cudaMemcpyHostToDevice, m->st));
+    CUDA_TRY(cudaEventRecord(m->ev_ids, m->st));
     return eval_common(m, output_index);
 }
 
@@ -1280,9 +1302,25 @@ int nncu_read_loss(nncu_model *m, float *loss_out)
     if (!m || !loss_out)
         return nncu_fail(NNCU_ERR_INVALID, "null argument");
     CUDA_TRY(cudaSetDevice(m->device));
-    CUDA_TRY(cudaMemcpyAsync(m->loss_pin, m->loss_dev, sizeof(float), cudaMemcpyDeviceToHost, m->st));
-    CUDA_TRY(cudaStreamSynchronize(m->st));
+    if (m->loss_pending) {
+        // queued right behind the backward pass: wait for that copy, not for what the host has
+        // queued since (the optimizer step, the next segment's forward pass)
+        CUDA_TRY(cudaEventSynchronize(m->ev_loss));
+        m->loss_pending = 0;
+    } else {
+        CUDA_TRY(cudaMemcpyAsync(m->loss_pin, m->loss_dev, sizeof(float), cudaMemcpyDeviceToHost, m->st));
+        CUDA_TRY(cudaStreamSynchronize(m->st));
+    }
     *loss_out = *m->loss_pin;
+    return NNCU_OK;
+}
+
+// the loss follows the backward pass to the host; nncu_read_loss collects it
+static int queue_loss(nncu_model *m)
+{
+    CUDA_TRY(cudaMemcpyAsync(m->loss_pin, m->loss_dev, sizeof(float), cudaMemcpyDeviceToHost, m->st));
+    CUDA_TRY(cudaEventRecord(m->ev_loss, m->st));
+    m->loss_pending = 1;
     return NNCU_OK;
 }
 
@@ -1291,10 +1329,12 @@ int nncu_eval_gradient(nncu_model *m, const int32_t *expected_host, float *loss_
     if (!m || !expected_host)
         return nncu_fail(NNCU_ERR_INVALID, "null argument");
     CUDA_TRY(cudaSetDevice(m->device));
-    CUDA_TRY(cudaStreamSynchronize(m->st));
+    CUDA_TRY(cudaEventSynchronize(m->ev_tgt));
     memcpy(m->tgt_pin, expected_host, sizeof(int32_t) * m->TB);
     CUDA_TRY(cudaMemcpyAsync(m->tgt_dev, m->tgt_pin, sizeof(int32_t) * m->TB, cudaMemcpyHostToDevice, m->st));
+    CUDA_TRY(cudaEventRecord(m->ev_tgt, m->st));
     NNCU_TRY(gradient_common(m));
+    NNCU_TRY(queue_loss(m));
     if (loss_out)
         return nncu_read_loss(m, loss_out);
     return NNCU_OK;
@@ -1306,7 +1346,8 @@ int nncu_eval_gradient_dev(nncu_model *m, const int32_t *expected_dev)
         return nncu_fail(NNCU_ERR_INVALID, "null argument");
     CUDA_TRY(cudaSetDevice(m->device));
     CUDA_TRY(cudaMemcpyAsync(m->tgt_dev, expected_dev, sizeof(int32_t) * m->TB, cudaMemcpyDeviceToDevice, m->st));
-    return gradient_common(m);
+    NNCU_TRY(gradient_common(m));
+    return queue_loss(m);
 }
 
 int nncu_optimizer_step(nncu_model *m)
@@ -1480,9 +1521,10 @@ static int coder_bits(int V)
     return ((1 << n) == V) ? n : -1;
 }
 
-int nncu_coder_paths(nncu_model *m, int t0, int nt, const int32_t *sym_host, uint16_t *prob0_host, int *n_bits_out)
+// symbols up, coder kernel, 15-bit prob0 values down into the pinned landing area; no host wait
+static int coder_paths_enqueue(nncu_model *m, int t0, int nt, const int32_t *sym_host)
 {
-    if (!m || !sym_host || !prob0_host || t0 < 0 || nt < 1 || t0 + nt > m->T)
+    if (!m || !sym_host || t0 < 0 || nt < 1 || t0 + nt > m->T)
         return nncu_fail(NNCU_ERR_INVALID, "bad coder range");
     int nb = coder_bits(m->V);
     if (nb < 1)
@@ -1491,17 +1533,55 @@ int nncu_coder_paths(nncu_model *m, int t0, int nt, const int32_t *sym_host, uin
         return nncu_fail(NNCU_ERR_RANGE, "n_symbols %d is beyond the 25600-symbol limit of the coder kernels", m->V);
     CUDA_TRY(cudaSetDevice(m->device));
     int rows = nt * m->B;
-    // symbols travel through the target staging area of the same rows
-    CUDA_TRY(cudaStreamSynchronize(m->st));
-    memcpy(m->tgt_pin, sym_host, sizeof(int32_t) * rows);
-    CUDA_TRY(cudaMemcpyAsync(m->tgt_dev, m->tgt_pin, sizeof(int32_t) * rows, cudaMemcpyHostToDevice, m->st));
-    coder_paths_kernel<<<rows, 256, (size_t)2 * m->V * 4, m->st>>>(m->probs + (size_t)t0 * m->B * m->V, m->tgt_dev,
-                                                                  m->coder_dev, m->V, nb);
+    CUDA_TRY(cudaEventSynchronize(m->ev_sym));   // the symbol staging area is free again
+    CUDA_TRY(cudaEventSynchronize(m->ev_coder)); // and so is the landing area
+    memcpy(m->sym_pin, sym_host, sizeof(int32_t) * rows);
+    // on the device the symbols use the target buffer of the same rows (the targets arrive later)
+    CUDA_TRY(cudaMemcpyAsync(m->tgt_dev, m->sym_pin, sizeof(int32_t) * rows, cudaMemcpyHostToDevice, m->st));
+    CUDA_TRY(cudaEventRecord(m->ev_sym, m->st));
+    if (m->V >= 1024 && m->V <= 16384)
+        coder_paths_fast_kernel<<<rows, 256, 0, m->st>>>(m->probs + (size_t)t0 * m->B * m->V, m->tgt_dev, m->coder_dev,
+                                                         m->V, nb);
+    else
+        coder_paths_kernel<<<rows, 256, (size_t)2 * m->V * 4, m->st>>>(m->probs + (size_t)t0 * m->B * m->V,
+                                                                      m->tgt_dev, m->coder_dev, m->V, nb);
     KERNEL_CHECK();
-    CUDA_TRY(cudaMemcpyAsync(prob0_host, m->coder_dev, sizeof(uint16_t) * (size_t)rows * nb, cudaMemcpyDeviceToHost, m->st));
-    CUDA_TRY(cudaStreamSynchronize(m->st));
-    if (n_bits_out) *n_bits_out = nb;
+    CUDA_TRY(cudaMemcpyAsync(m->coder_pin, m->coder_dev, sizeof(uint16_t) * (size_t)rows * nb, cudaMemcpyDeviceToHost, m->st));
+    CUDA_TRY(cudaEventRecord(m->ev_coder, m->st));
+    m->coder_rows = rows;
+    m->coder_nb = nb;
     return NNCU_OK;
+}
+
+int nncu_coder_paths_begin(nncu_model *m, int t0, int nt, const int32_t *sym_host)
+{
+    if (m && m->coder_rows)
+        return nncu_fail(NNCU_ERR_STATE, "nncu_coder_paths_begin: the result of the call before was not collected");
+    return coder_paths_enqueue(m, t0, nt, sym_host);
+}
+
+int nncu_coder_paths_end(nncu_model *m, uint16_t *prob0_host, int *n_bits_out)
+{
+    if (!m || !prob0_host)
+        return nncu_fail(NNCU_ERR_INVALID, "null argument");
+    if (!m->coder_rows)
+        return nncu_fail(NNCU_ERR_STATE, "nncu_coder_paths_end without nncu_coder_paths_begin");
+    CUDA_TRY(cudaSetDevice(m->device));
+    CUDA_TRY(cudaEventSynchronize(m->ev_coder));
+    memcpy(prob0_host, m->coder_pin, sizeof(uint16_t) * (size_t)m->coder_rows * m->coder_nb);
+    if (n_bits_out) *n_bits_out = m->coder_nb;
+    m->coder_rows = 0;
+    return NNCU_OK;
+}
+
+int nncu_coder_paths(nncu_model *m, int t0, int nt, const int32_t *sym_host, uint16_t *prob0_host, int *n_bits_out)
+{
+    if (!prob0_host)
+        return nncu_fail(NNCU_ERR_INVALID, "bad coder range");
+    if (m && m->coder_rows)
+        return nncu_fail(NNCU_ERR_STATE, "nncu_coder_paths between nncu_coder_paths_begin and _end");
+    NNCU_TRY(coder_paths_enqueue(m, t0, nt, sym_host));
+    return nncu_coder_paths_end(m, prob0_host, n_bits_out);
 }
 
 int nncu_coder_trees(nncu_model *m, int t0, int nt, uint16_t *tree_host)

@@ -338,6 +338,48 @@ def test_initial_values_match_the_oracle(pkg, oracle):
 
 # ---------------------------------------------------------------- coder-ready output
 
+def test_encoder_order_queues_everything_and_gives_the_same_bits(pkg):
+    """eval, coder_paths_begin, eval_gradient (loss not awaited), update, coder_paths_end, read_loss
+    must give the coder values, losses and weights of the strictly sequential order of
+    process_block (eval, coder_paths, eval_gradient, update)."""
+    import ctypes as C
+    cfg, z = load_golden("c0_like")
+    lib = pkg.library()
+    res = []
+    for pipelined in (False, True):
+        m = pkg.TrfModel(params_from_cfg(pkg, cfg, use_bf16=1))
+        _load(m, z)
+        m.reset()
+        T, B = cfg["seg_len"], cfg["n_streams"]
+        out = []
+        for s in range(4):
+            ids, tg = z["ids"][s % 2], z["targets"][s % 2]
+            tgc = np.ascontiguousarray(tg, np.int32)
+            m.eval(-1, ids, read=False)
+            if not pipelined:
+                paths = m.coder_paths(0, T, tgc)
+                loss = m.eval_gradient(tgc)
+                m.update()
+            else:
+                buf = np.zeros(T * B * 32, np.uint16)
+                nb = C.c_int()
+                assert lib.nncu_coder_paths_begin(m.h, 0, T, tgc.ctypes.data_as(C.c_void_p)) == 0
+                # a second begin before the end is refused, and so is the one-call form
+                assert lib.nncu_coder_paths_begin(m.h, 0, T, tgc.ctypes.data_as(C.c_void_p)) == pkg.abi.ERR_STATE
+                assert lib.nncu_eval_gradient(m.h, tgc.ctypes.data_as(C.c_void_p), None) == 0
+                m.update()
+                assert lib.nncu_coder_paths_end(m.h, buf.ctypes.data_as(C.c_void_p), C.byref(nb)) == 0
+                paths = buf[: T * B * nb.value].reshape(T * B, nb.value).copy()
+                loss = m.read_loss()
+            out.append((paths, loss))
+        res.append((out, m.weights_hash()))
+        m.close()
+    assert res[0][1] == res[1][1]
+    for (pa, la), (pb, lb) in zip(res[0][0], res[1][0]):
+        assert np.array_equal(pa, pb)
+        assert la == lb
+
+
 def test_coder_paths_and_trees_match_the_coder_oracle(pkg, oracle):
     p = pkg.abi.make_params(n_layer=1, d_model=64, n_head=2, d_key=32, d_inner=128, d_pos=16, mem_len=8,
                             seg_len=8, n_streams=4, n_symbols=256, init_range=0.3)
@@ -371,6 +413,29 @@ def test_coder_paths_and_trees_match_the_coder_oracle(pkg, oracle):
             while k < 256:
                 k = 2 * k + dec.get_bit(int(trees[t * 4 + b, k]))
             assert k - 256 == syms[t, b]
+    m.close()
+
+
+@pytest.mark.parametrize("V", [1024, 4096, 16384])
+def test_coder_paths_large_alphabets_match_the_coder_oracle(pkg, oracle, V):
+    """The register / shuffle form of the pairwise sum tree (1024 <= V <= 16384) against write_sym's
+    arithmetic, including symbols at the edges of the alphabet; a peaked row makes the running mass
+    collapse on the unlikely side."""
+    p = pkg.abi.make_params(n_layer=1, d_model=64, n_head=2, d_key=32, d_inner=128, d_pos=16, mem_len=8,
+                            seg_len=8, n_streams=4, n_symbols=V, init_range=0.5)
+    m = pkg.TrfModel(p)
+    rng = np.random.default_rng(V)
+    ids = rng.integers(0, V, (8, 4)).astype(np.int32)
+    syms = rng.integers(0, V, (8, 4)).astype(np.int32)
+    syms[0, :] = [0, V - 1, V // 2, V // 2 - 1]
+    probs = m.eval(-1, ids)
+    paths = m.coder_paths(0, 8, syms)
+    nb = int(np.log2(V))
+    assert paths.shape == (32, nb)
+    for t in range(8):
+        for b in range(4):
+            want = oracle.sym_path(probs[t, b], syms[t, b])
+            assert np.array_equal(paths[t * 4 + b], want), (t, b)
     m.close()
 
 
