@@ -254,7 +254,8 @@ struct SmemLayout {
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
     static constexpr int STAGES = (BN == 128) ? 3 : 4; // BN <= 128: 96 KB, two CTAs per SM
     static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES;
-    static constexpr int TOTAL = BAR_OFFSET + 256 + 1024; // + barriers + alignment slack
+    static constexpr int BIAS_OFFSET = BAR_OFFSET + 256;      // BN floats of bias for the epilogue
+    static constexpr int TOTAL = BIAS_OFFSET + BN * 4 + 1024; // + alignment slack
     static constexpr int CTAS_PER_SM = (2 * TOTAL <= 227 * 1024) ? 2 : 1;
 };
 
@@ -273,6 +274,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     uint64_t *full = bars, *empty = bars + SL::STAGES, *tmem_full = bars + 2 * SL::STAGES;
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * SL::STAGES + 1);
     volatile int *abort_s = reinterpret_cast<volatile int *>(tmem_slot + 1);
+    float *bias_s = reinterpret_cast<float *>(sm + SL::BIAS_OFFSET);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
@@ -402,6 +404,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         // epilogue warps 2..5
         const int quarter = warp & 3;
         bool ok = true;
+        if (bias) {
+            // the tile's bias values go to shared memory while the mainloop runs (a load from
+            // global memory inside the chunk loop would expose its latency once per chunk)
+            const int lim = min(N, bias_n) - n0;
+            for (int i = threadIdx.x - 64; i < BN; i += 128)
+                bias_s[i] = i < lim ? __ldg(bias + n0 + i) : 0.0f;
+            asm volatile("bar.sync 1, 128;" ::: "memory"); // the four epilogue warps only
+        }
         if (nkb > 0)
         {
             // one lane per warp watches the barrier: every probe of a waiting thread queues in
@@ -456,18 +466,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 // Straight-line vector paths for whole chunks; element-wise code (one branch per
                 // element) only at ragged edges.
                 if (bias) {
-                    const float *bp = bias + n0 + c0;
-                    if (full && n0 + c0 + 32 <= bias_n && (reinterpret_cast<uintptr_t>(bp) & 15) == 0) {
+                    const float4 *bp = reinterpret_cast<const float4 *>(bias_s + c0); // zero past N or bias_n
 #pragma unroll
-                        for (int v = 0; v < 8; v++) {
-                            const float4 t = __ldg(reinterpret_cast<const float4 *>(bp) + v);
-                            x[v * 4] += t.x; x[v * 4 + 1] += t.y; x[v * 4 + 2] += t.z; x[v * 4 + 3] += t.w;
-                        }
-                    } else {
-#pragma unroll
-                        for (int j = 0; j < 32; j++)
-                            if (j < nvalid && n0 + c0 + j < bias_n)
-                                x[j] += bp[j];
+                    for (int v = 0; v < 8; v++) {
+                        const float4 t = bp[v];
+                        x[v * 4] += t.x; x[v * 4 + 1] += t.y; x[v * 4 + 2] += t.z; x[v * 4 + 3] += t.w;
                     }
                 }
                 if (addsrc && row < M) {
