@@ -323,16 +323,16 @@ __global__ void __launch_bounds__(128) attn_fwd_mma_kernel(AttnArgs a)
             mxB = fmaxf(mxB, __shfl_xor_sync(0xffffffffu, mxB, 2));
             const float nA = fmaxf(mA, mxA), nB = fmaxf(mB, mxB);
             const float uA = nA == -INFINITY ? 0.0f : nA, uB = nB == -INFINITY ? 0.0f : nB;
-            const float scA = expf(mA - uA), scB = expf(mB - uB);
+            const float scA = __expf(mA - uA), scB = __expf(mB - uB);
             mA = nA;
             mB = nB;
             float sumA = 0.0f, sumB = 0.0f;
 #pragma unroll
             for (int nt = 0; nt < 8; nt++) {
-                s[nt][0] = expf(s[nt][0] - uA);
-                s[nt][1] = expf(s[nt][1] - uA);
-                s[nt][2] = expf(s[nt][2] - uB);
-                s[nt][3] = expf(s[nt][3] - uB);
+                s[nt][0] = __expf(s[nt][0] - uA);
+                s[nt][1] = __expf(s[nt][1] - uA);
+                s[nt][2] = __expf(s[nt][2] - uB);
+                s[nt][3] = __expf(s[nt][3] - uB);
                 sumA += s[nt][0] + s[nt][1];
                 sumB += s[nt][2] + s[nt][3];
             }
@@ -577,8 +577,8 @@ __global__ void __launch_bounds__(256) attn_bwd_mma_kernel(AttnArgs a)
                         }
 #pragma unroll
                     for (int nt = 0; nt < 8; nt++) {
-                        const float p0 = expf(s[nt][0] - lseA), p1 = expf(s[nt][1] - lseA);
-                        const float p2 = expf(s[nt][2] - lseB), p3 = expf(s[nt][3] - lseB);
+                        const float p0 = __expf(s[nt][0] - lseA), p1 = __expf(s[nt][1] - lseA);
+                        const float p2 = __expf(s[nt][2] - lseB), p3 = __expf(s[nt][3] - lseB);
                         const int col = j0 - j0s + nt * 8 + 2 * t;
                         *reinterpret_cast<uint32_t *>(Pm + (size_t)(i0 + g) * d.LPS + col) = pack2(p0, p1);
                         *reinterpret_cast<uint32_t *>(Pm + (size_t)(i0 + g + 8) * d.LPS + col) = pack2(p2, p3);

@@ -45,6 +45,11 @@ __device__ __forceinline__ void pdl_wait()
 {
     asm volatile("griddepcontrol.wait;" ::: "memory");
 }
+// the same signal, given late in a kernel (its successor's launch then overlaps only the tail)
+__device__ __forceinline__ void pdl_trigger_late()
+{
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
 __device__ __forceinline__ void pdl_trigger()
 {
 #ifdef NNCU_PDL_TRIGGER

@@ -421,8 +421,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             __syncwarp();
         }
         ok = __all_sync(0xffffffffu, ok); // tcgen05.ld below is warp-collective
-        if (threadIdx.x == 64)
+        if (threadIdx.x == 64) {
             TC_STAMP(5);
+            pdl_trigger_late(); // the mainloop is over: the next kernel may set itself up
+        }
         fence_after_sync();
         const int row = m0 + quarter * 32 + lane;
         if (ok) {
