@@ -354,7 +354,7 @@ def main():
                     "peak_source": f"{which} bf16_tflops_sustained",
                     # dram__bytes_read+write per launch, averaged over the 147 GEMM launches of one c2
                     # step at 1 GPU (ncu capture summarised in profiles/gemm_tc_kernel_c2_dram_traffic.md)
-                    "traffic": 9.44e6 if (args.config == "c2" and world == 1) else None,
+                    "traffic": 9.43e6 if (args.config == "c2" and world == 1) else None,
                     "traffic_unit": "bytes/launch (ncu, cold caches; algorithmic 13.97e6)",
                     "launches_per_step": pr.gemm_launches / min(K, 3),
                     "share_of_step": (pr.gemm_ms / min(K, 3)) / (ms / K)}
