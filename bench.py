@@ -263,6 +263,12 @@ def main():
 
     def step_device(s):
         sharded.step_device(ids_d[s].data_ptr(), tg_d[s].data_ptr())
+        if world > 1:
+            # read the segment's loss (as a host would): it keeps the ranks' hosts within one step
+            # of their GPUs.  With 50 steps queued ahead the ranks drift apart and each NCCL kernel
+            # spins on SMs until its peer arrives: measured 360-770 k symbols/s from run to run at
+            # 2 GPUs, against a steady 800 k with this read.
+            m.read_loss()
 
     nb = int(np.log2(V)) if (V & (V - 1)) == 0 else 0
     paths = np.zeros((T * B, max(nb, 1)), np.uint16)
@@ -293,6 +299,14 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
+    # Initialisation, not warm-up: the library captures its CUDA graphs on the second use of each
+    # memory twin (four steps), and NCCL sets its channels up on the first collectives.  Without
+    # these steps a 3-step warm-up leaves both inside the timed region (seen at 2 GPUs as run-to-run
+    # swings of the device-resident figure between 360 k and 770 k symbols/s).
+    m.reset()
+    for s in range(6):
+        step_device(s % (W + K))
+    barrier()
     m.reset()
     for s in range(W):
         step_device(s)
