@@ -441,17 +441,20 @@ def test_coder_paths_large_alphabets_match_the_coder_oracle(pkg, oracle, V):
 
 # ---------------------------------------------------------------- full-size properties
 
-def test_config2_scale_step_properties(pkg):
-    """BASELINE config[2] sizes (fewer layers to bound the test time): probabilities are
-    normalised and finite, the loss is finite, and a second identical run gives the same bits."""
+@pytest.mark.parametrize("streams", [32, 8, 4])
+def test_config2_scale_step_properties(pkg, streams):
+    """BASELINE config[2] sizes (fewer layers to bound the test time), whole job and the 8- and
+    4-stream shards a rank holds at 4 and 8 GPUs: probabilities are normalised and finite, the
+    loss is finite, and a second identical run gives the same bits."""
     hashes = []
     for _ in range(2):
         p = pkg.abi.make_params(n_layer=3, d_model=512, n_head=8, d_key=64, d_inner=2048, d_pos=128,
-                                mem_len=64, seg_len=64, n_streams=32, n_symbols=16384, use_bf16=1)
+                                mem_len=64, seg_len=64, n_streams=streams, n_streams_total=32,
+                                n_symbols=16384, use_bf16=1)
         m = pkg.TrfModel(p)
         rng = np.random.default_rng(3)
-        ids = rng.integers(0, 16384, (64, 32)).astype(np.int32)
-        tg = rng.integers(0, 16384, (64, 32)).astype(np.int32)
+        ids = rng.integers(0, 16384, (64, streams)).astype(np.int32)
+        tg = rng.integers(0, 16384, (64, streams)).astype(np.int32)
         for _s in range(2):
             probs = m.eval(-1, ids)
             assert np.isfinite(probs).all()
