@@ -278,7 +278,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
-    const int nkb = (K + BK - 1) / BK;
+    // split-K: gridDim.z CTAs share an output tile, each taking a contiguous run of k-blocks and
+    // writing its partial product to rows [z*M, (z+1)*M) of C (a workspace of gridDim.z * M rows;
+    // the host adds the partials in z order).  gridDim.z = 1 is the plain GEMM.
+    const int nkb_all = (K + BK - 1) / BK;
+    const int kper = (nkb_all + (int)gridDim.z - 1) / (int)gridDim.z;
+    const int kb_first = (int)blockIdx.z * kper;
+    const int nkb = max(0, min(nkb_all, kb_first + kper) - kb_first);
+    const int mz = (int)blockIdx.z * M;
     TC_MODE_LOAD
     pdl_trigger();
 
@@ -317,7 +324,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         if (lane == 0) {
             const uint32_t sm0 = smem_u32(sm), full0 = smem_u32(full), empty0 = smem_u32(empty);
             uint32_t dst = sm0, fb = full0, eb = empty0, ph = 0;
-            int s = 0, kx = 0;
+            int s = 0, kx = kb_first * BK;
             for (int kb = 0; kb < nkb; kb++, kx += BK) {
                 if (kb >= SL::STAGES && !mbar_wait(eb, ph, abort_s, err_flag, 1))
                     break;
@@ -529,13 +536,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                             asm volatile(
                                 "cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(
                                     reinterpret_cast<uint64_t>(&map_c)),
-                                "r"(smem_u32(stg)), "r"(n0 + blk * 32 * CPB), "r"(m0 + quarter * 32)
+                                "r"(smem_u32(stg)), "r"(n0 + blk * 32 * CPB), "r"(mz + m0 + quarter * 32)
                                 : "memory");
                             asm volatile("cp.async.bulk.commit_group;" ::: "memory");
                         }
                     }
                 } else if (row < M) {
-                    TC *dst = C + (long)row * ldc + n0 + c0;
+                    TC *dst = C + (long)(mz + row) * ldc + n0 + c0;
                     if (full && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
                         if (sizeof(TC) == 2) {
 #pragma unroll
@@ -673,9 +680,12 @@ static bool usable(const void *A, long lda, const void *B, long ldb, int K)
 
 template <int BN, typename TC, bool AMN, bool BMN>
 static int launch(cudaStream_t st, int M, int N, int K, const bf16 *A, long lda, const bf16 *B,
-                  long ldb, TC *C, long ldc, const float *bias, const TC *addsrc, int *err_flag, int bias_n)
+                  long ldb, TC *C, long ldc, const float *bias, const TC *addsrc, int *err_flag, int bias_n,
+                  int ksplit = 1)
 {
     using SL = SmemLayout<BN>;
+    if (ksplit > 1 && (M % BM != 0 || bias || addsrc))
+        return nncu_fail(NNCU_ERR_INVALID, "split-K needs whole row tiles and a bare product");
     CUtensorMap ma, mb;
     if (AMN)
         NNCU_TRY(make_tmap(A, K, M, lda, 64, &ma)); // [k rows][m], 64 x 64 boxes
@@ -689,14 +699,14 @@ static int launch(cudaStream_t st, int M, int N, int K, const bf16 *A, long lda,
     CUtensorMap mc = ma;
     const int staged = ((reinterpret_cast<uintptr_t>(C) & 15) == 0 && (ldc * sizeof(TC)) % 16 == 0) ? 1 : 0;
     if (staged)
-        NNCU_TRY(make_tmap(C, M, N, ldc, 32, &mc, 128 / (int)sizeof(TC), (int)sizeof(TC)));
+        NNCU_TRY(make_tmap(C, (long)M * ksplit, N, ldc, 32, &mc, 128 / (int)sizeof(TC), (int)sizeof(TC)));
     static bool attr_done = false;
     if (!attr_done) {
         CUDA_TRY(cudaFuncSetAttribute(gemm_tc_kernel<BN, TC, AMN, BMN>,
                                       cudaFuncAttributeMaxDynamicSharedMemorySize, SL::TOTAL));
         attr_done = true;
     }
-    dim3 grid(ceil_div(N, BN), ceil_div(M, BM));
+    dim3 grid(ceil_div(N, BN), ceil_div(M, BM), ksplit);
     GemmProfiler *pr = g_nncu_prof;
     const bool timed = pr && pr->n < GemmProfiler::MAX_EV;
     if (timed)
@@ -739,6 +749,19 @@ static int gemm(cudaStream_t st, int M, int N, int K, const bf16 *A, long lda, c
     if (mt * ceil_div(N, 128) >= min_tiles || N <= 64)
         return launch<128, TC, AMN, BMN>(st, M, N, K, A, lda, B, ldb, C, ldc, bias, addsrc, err_flag, bias_n);
     return launch<64, TC, AMN, BMN>(st, M, N, K, A, lda, B, ldb, C, ldc, bias, addsrc, err_flag, bias_n);
+}
+
+// Long contractions with few output tiles (the output head's dX: K = n_symbols): `ksplit` CTAs
+// per 128 x 128 tile, fp32 partial products in `ws` ([ksplit][M][N], M a multiple of 128); the
+// caller adds the partials in order (splitk_reduce_kernel).
+template <bool AMN, bool BMN>
+static int gemm_splitk(cudaStream_t st, int M, int N, int K, const bf16 *A, long lda, const bf16 *B, long ldb,
+                       float *ws, int ksplit, int *err_flag)
+{
+    if (!usable(A, lda, B, ldb, K))
+        return nncu_fail(NNCU_ERR_INVALID, "tcgen05 GEMM needs 16-byte aligned operands and strides");
+    return launch<128, float, AMN, BMN>(st, M, N, K, A, lda, B, ldb, ws, N, nullptr, nullptr, err_flag, 1 << 30,
+                                        ksplit);
 }
 
 template <typename TC>

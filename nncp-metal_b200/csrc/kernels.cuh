@@ -316,6 +316,26 @@ norm_bwd_vec_kernel(const bf16 *__restrict__ dy, const bf16 *__restrict__ x, con
     }
 }
 
+// out[i] = ws[0][i] + ws[1][i] + ... (in that order) for the partial products of a split-K GEMM;
+// n a multiple of 4.
+template <typename TO>
+__global__ void splitk_reduce_kernel(const float *__restrict__ ws, int ksplit, size_t n, TO *__restrict__ out)
+{
+    pdl_wait();
+    const size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 4;
+    if (i >= n)
+        return;
+    float4 acc = *reinterpret_cast<const float4 *>(ws + i);
+    for (int z = 1; z < ksplit; z++) {
+        const float4 v = *reinterpret_cast<const float4 *>(ws + (size_t)z * n + i);
+        acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    }
+    out[i] = from_f<TO>(acc.x);
+    out[i + 1] = from_f<TO>(acc.y);
+    out[i + 2] = from_f<TO>(acc.z);
+    out[i + 3] = from_f<TO>(acc.w);
+}
+
 // Column reduction of partial sums, fixed order: out_k[c] = sum_p part[p*stride + off_k + c].
 // blockIdx.y selects the output k (up to 3); a block owns 32 columns, its 8 warps each sum
 // a contiguous range of parts, and the 8 range sums are added in range order.

@@ -109,6 +109,8 @@ struct TransposeJob {
     int rows, cols, tile0, tiles_x;
 };
 
+constexpr int SPLITK = 4, SPLITK_MIN_K = 8192; // split-K of the output head's dX GEMM
+
 struct nncu_model {
     nncu_params p;
     int D, H, dk, HD, F, F1, T, B, M, L, V, TB, LB, Bt, nl;
@@ -148,6 +150,8 @@ struct nncu_model {
     void *xlast, *xf, *pool[4], *dz, *dh, *dhp, *dof, *dqkv, *tA, *tB;
     float *st_f, *probs, *dwr_part, *dbr_part, *part, *logp, *loss_dev;
     size_t part_floats = 0; // floats per region of `part`
+    float *skw = nullptr;   // split-K workspace [SPLITK][TB][D] (models with n_symbols >= SPLITK_MIN_K)
+    size_t skw_floats = 0;
     int part_idx = 0;       // regions handed out since the last join
     int32_t *ids_dev, *tgt_dev;
     int *err_flag;
@@ -254,10 +258,22 @@ static int mm_nn(nncu_model *m, int M, int Kin, int Nout, const float *dY, long 
 static int mm_nn(nncu_model *m, int M, int Kin, int Nout, const bf16 *dY, long ldy, size_t w_off,
                  bf16 *C, long ldc, const bf16 *addsrc)
 {
-    if (m->use_tc && tc_mn_major() && tc::usable(dY, ldy, m->Wb + w_off, Kin, Nout))
+    if (m->use_tc && tc_mn_major() && tc::usable(dY, ldy, m->Wb + w_off, Kin, Nout)) {
         // W is [Nout][Kin] = [k][n]: read in place as an MN-major operand
+        if (Nout >= SPLITK_MIN_K && !addsrc && m->skw && M % 128 == 0 && ldc == Kin && Kin % 4 == 0 &&
+            (size_t)SPLITK * M * Kin <= m->skw_floats) {
+            // a long contraction into few tiles (the output head's dX): four CTAs per tile
+            NNCU_TRY((tc::gemm_splitk<false, true>(m->st, M, Kin, Nout, dY, ldy, m->Wb + w_off, Kin, m->skw, SPLITK,
+                                                   m->err_flag)));
+            const size_t n = (size_t)M * Kin;
+            launch_k(splitk_reduce_kernel<bf16>, dim3((unsigned)ceil_div((long long)(n / 4), 256)), dim3(256), 0, m->st,
+                     m->skw, SPLITK, n, C);
+            KERNEL_CHECK();
+            return NNCU_OK;
+        }
         return tc::gemm<bf16, false, true>(m->st, M, Kin, Nout, dY, ldy, m->Wb + w_off, Kin, C, ldc, nullptr,
                                            addsrc, m->err_flag);
+    }
     const bf16 *WT = m->WbT + w_off; // [Kin][Nout]
     if (m->use_tc && tc::usable(dY, ldy, WT, Nout, Nout))
         return tc::gemm_nt<bf16>(m->st, M, Kin, Nout, dY, ldy, WT, Nout, C, ldc, nullptr, addsrc,
@@ -1055,6 +1071,8 @@ int nncu_create(const nncu_params *p, nncu_model **out)
     part_floats = std::max(part_floats, (size_t)ceil_div(TB, ACT_BWD_ROWS) * F1);
     size_t oPart = take(part_floats * 4 * PART_SLOTS);
     m->part_floats = part_floats;
+    const size_t skw_floats = (m->use_tc && V >= SPLITK_MIN_K) ? (size_t)SPLITK * TB * D : 0;
+    size_t oSkw = take(skw_floats * 4 + 256);
     size_t oLogp = take((size_t)TB * 4), oLoss = take(256);
     size_t oIds = take((size_t)TB * 4), oTgt = take((size_t)TB * 4), oErr = take(256), oHash = take(256);
     // transposed-shadow jobs
@@ -1097,6 +1115,8 @@ int nncu_create(const nncu_params *p, nncu_model **out)
     m->dz = A + oDz; m->dh = A + oDh; m->dhp = A + oDhp; m->dof = A + oDof; m->dqkv = A + oDqkv;
     m->tA = m->use_tc ? A + oTA : nullptr; m->tB = m->use_tc ? A + oTB : nullptr;
     m->dwr_part = (float *)(A + oWr); m->dbr_part = (float *)(A + oBr); m->part = (float *)(A + oPart);
+    m->skw = skw_floats ? (float *)(A + oSkw) : nullptr;
+    m->skw_floats = skw_floats;
     m->logp = (float *)(A + oLogp); m->loss_dev = (float *)(A + oLoss);
     m->ids_dev = (int32_t *)(A + oIds); m->tgt_dev = (int32_t *)(A + oTgt);
     m->err_flag = (int *)(A + oErr); m->hash_dev = (unsigned long long *)(A + oHash);

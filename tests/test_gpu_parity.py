@@ -278,6 +278,31 @@ def test_train_step_bf16_vs_oracle(pkg, oracle, name, backend):
     m.close()
 
 
+def test_output_head_split_k_vs_oracle(pkg, oracle):
+    """n_symbols >= 8192 with 128 rows: the output head's dX contraction (K = n_symbols) runs as four
+    partial products per tile plus an ordered sum; every gradient below the head depends on it."""
+    kw = dict(n_layer=1, d_model=64, n_head=2, d_key=32, d_inner=128, d_pos=16, mem_len=8, seg_len=8,
+              n_streams=16, n_symbols=8192, init_range=0.05, lr=1e-3)
+    m = pkg.TrfModel(pkg.abi.make_params(use_bf16=1, gemm_backend=2, **kw))
+    o = oracle.OracleModel(pkg.abi.make_params(use_bf16=0, **kw))
+    for name in m.info:
+        w = _bf16_round(m.get_param(name))
+        m.set_param(name, w)
+        o.set_param(name, w)
+    rng = np.random.default_rng(11)
+    ids = rng.integers(0, 8192, (8, 16)).astype(np.int32)
+    tg = rng.integers(0, 8192, (8, 16)).astype(np.int32)
+    m.reset(); o.reset()
+    assert rel_err(m.eval(-1, ids), o.eval(-1, ids)) < BF16_TOL
+    loss, loss_ref = m.eval_gradient(tg), o.eval_gradient(tg)
+    assert abs(loss - loss_ref) < BF16_TOL * abs(loss_ref)
+    for name in m.info:
+        g_ref = o.get_grad(name)
+        scale = max(np.abs(g_ref).max(), 1e-6)
+        assert np.abs(m.get_grad(name) - g_ref).max() / scale < 5 * BF16_TOL, name
+    m.close()
+
+
 def test_two_runs_are_bit_identical(pkg):
     cfg, z = load_golden("c0_like")
     hashes = []
