@@ -283,9 +283,13 @@ def main():
             ck(lib.nncu_coder_paths_begin(m.h, 0, T, tg.ctypes.data_as(C.c_void_p)))
         else:
             m.read_probs(0, T)
-        ck(lib.nncu_eval_gradient(m.h, tg.ctypes.data_as(C.c_void_p), None))
-        sharded.reduce_gradients()
-        m.update()
+        if sharded.fused():
+            ck(lib.nncu_eval_gradient_update(m.h, tg.ctypes.data_as(C.c_void_p), None))
+            m.memory_shift()
+        else:
+            ck(lib.nncu_eval_gradient(m.h, tg.ctypes.data_as(C.c_void_p), None))
+            sharded.reduce_gradients()
+            m.update()
         if nb:
             ck(lib.nncu_coder_paths_end(m.h, paths.ctypes.data_as(C.c_void_p), C.byref(nbits)))
         return m.read_loss()

@@ -178,6 +178,17 @@ int nncu_probs_dev(nncu_model *m, float **probs_dev);
  */
 int nncu_eval_gradient(nncu_model *m, const int32_t *expected_host, float *loss_out);
 int nncu_eval_gradient_dev(nncu_model *m, const int32_t *expected_dev);
+/*
+ * model_eval_gradient and the optimizer half of model_update in one call (no counterpart in the
+ * reference, whose process_block always calls the two in turn, nncp.c:3052-3053): the RMSProp
+ * update of each layer's parameters is queued as soon as that layer's gradients are final
+ * (behind their all-reduce when a communicator is attached), beside the rest of the backward
+ * pass, instead of after it.  Same arithmetic, same bits as nncu_eval_gradient followed by
+ * nncu_optimizer_step.  Follow with nncu_memory_shift, not nncu_update.  The gradients stay
+ * readable (nncu_grad_get); the loss is collected with nncu_read_loss.
+ */
+int nncu_eval_gradient_update(nncu_model *m, const int32_t *expected_host, float *loss_out);
+int nncu_eval_gradient_update_dev(nncu_model *m, const int32_t *expected_dev);
 /* Reads the loss of the last nncu_eval_gradient / _dev.  The loss is copied to the host right
    behind the backward pass, and this call waits for that copy only: work the host has queued
    since (nncu_update, the next nncu_eval) keeps running. */

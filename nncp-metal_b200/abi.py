@@ -91,6 +91,8 @@ PROTOTYPES = {
     "nncu_probs_dev": (_i, [_vp, C.POINTER(_vp)]),
     "nncu_eval_gradient": (_i, [_vp, _vp, _pf]),
     "nncu_eval_gradient_dev": (_i, [_vp, _vp]),
+    "nncu_eval_gradient_update": (_i, [_vp, _vp, C.POINTER(C.c_float)]),
+    "nncu_eval_gradient_update_dev": (_i, [_vp, _vp]),
     "nncu_read_loss": (_i, [_vp, _pf]),
     "nncu_update": (_i, [_vp]),
     "nncu_optimizer_step": (_i, [_vp]),

@@ -733,13 +733,17 @@ __global__ void colsum_part_kernel(const T *__restrict__ A, long lda, int R, int
 __global__ void __launch_bounds__(256)
 rmsprop_kernel(float *__restrict__ w, const float *__restrict__ g, float *__restrict__ v,
                bf16 *__restrict__ shadow, size_t n4, float lr, float beta2, float eps,
-               float clip, float corr)
+               float clip, float corr, const float *__restrict__ hyper)
 {
     pdl_trigger();
     pdl_wait();
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n4)
         return;
+    if (hyper) { // {lr, corr} from device memory: a captured launch must not freeze them
+        lr = hyper[0];
+        corr = hyper[1];
+    }
     float4 ww = reinterpret_cast<float4 *>(w)[i];
     float4 gg = reinterpret_cast<const float4 *>(g)[i];
     float4 vv = reinterpret_cast<float4 *>(v)[i];

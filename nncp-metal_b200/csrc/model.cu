@@ -127,7 +127,7 @@ struct nncu_model {
         cudaGraphExec_t exec;
         unsigned long long launches;
         int calls;
-    } graphs[2][2];
+    } graphs[3][2]; // [forward, backward, backward with the optimizer step][memory twin]
     bool graphs_on;
     // gradient exchange between ranks (nncu_comm_init): per-layer all-reduces on a third stream,
     // issued as soon as a layer's gradients are complete, so they overlap the rest of backward
@@ -153,6 +153,8 @@ struct nncu_model {
     float *skw = nullptr;   // split-K workspace [SPLITK][TB][D] (models with n_symbols >= SPLITK_MIN_K)
     size_t skw_floats = 0;
     int part_idx = 0;       // regions handed out since the last join
+    bool fuse_update = false; // this backward pass applies the optimizer to each bucket as it completes
+    float *hyper_dev = nullptr; // {lr, bias correction} of the fused optimizer step
     int32_t *ids_dev, *tgt_dev;
     int *err_flag;
     unsigned long long *hash_dev;
@@ -445,7 +447,7 @@ static nncu_attn_shape attn_shape(nncu_model *m, int l, int t0, int t1)
 // copied into fixed staging buffers before the graph runs, and the two memory twins have
 // a graph each.  One-symbol steps, the optimizer (its learning rate is a launch argument) and
 // the timed-GEMM profiling pass stay eager.
-enum { GRAPH_FWD = 0, GRAPH_BWD = 1 };
+enum { GRAPH_FWD = 0, GRAPH_BWD = 1, GRAPH_BWD_UPD = 2, N_GRAPH_KINDS = 3 };
 
 template <typename F>
 static int run_graphed(nncu_model *m, int kind, F body)
@@ -591,6 +593,24 @@ static int exchange_finish(nncu_model *m)
     return NNCU_OK;
 }
 
+// Fused optimizer step: the RMSProp update of the gradient slots [begin, end), queued as soon as
+// they are final -- behind the bucket's all-reduce on the exchange stream, or on the side stream.
+// The update streams 22 bytes per parameter while the rest of the backward pass is latency-bound,
+// so the two overlap well.  lr and the bias correction come from device memory (the launch is
+// part of a captured graph).
+static int opt_range(nncu_model *m, size_t begin, size_t end, bool last)
+{
+    if (!m->fuse_update || end <= begin)
+        return NNCU_OK;
+    cudaStream_t st = m->comm ? m->st3 : (last ? m->st : side_fork(m));
+    const size_t n4 = (end - begin) / 4;
+    launch_k(rmsprop_kernel, dim3((unsigned)ceil_div((long long)n4, 256)), dim3(256), 0, st, m->W + begin, m->G + begin,
+             m->Vm + begin, m->Wb ? m->Wb + begin : (bf16 *)nullptr, n4, 0.0f, m->p.beta2, m->p.eps, m->p.gradient_clip,
+             1.0f, (const float *)m->hyper_dev);
+    KERNEL_CHECK();
+    return NNCU_OK;
+}
+
 // ------------------------------------------------------------------ backward
 
 template <typename AT>
@@ -723,11 +743,15 @@ static int backward(nncu_model *m)
             NNCU_TRY(mm_nn(m, TB, D, 3 * HD, dq, 3 * HD, o.w_q, dxn, D, (const AT *)ds1));
         }
         side_join(m); // this layer's weight gradients are done before dhp, dqkv, ds1, ds2 are rewritten
-        if (m->comm) {
+        {
             // layer l's slots are contiguous; tied tables live in layer 0, which is exchanged last
-            NNCU_TRY(exchange_bucket(m, o.w_q, l + 1 < m->nl ? m->lo[l + 1].w_q : m->tail_begin));
-            if (l == m->nl - 1) // the output head's gradients have been complete since the first join
+            const size_t lb = o.w_q, le = l + 1 < m->nl ? m->lo[l + 1].w_q : m->tail_begin;
+            NNCU_TRY(exchange_bucket(m, lb, le));
+            NNCU_TRY(opt_range(m, lb, le, false));
+            if (l == m->nl - 1) { // the output head's gradients have been complete since the first join
                 NNCU_TRY(exchange_bucket(m, m->embed_out, m->n_floats));
+                NNCU_TRY(opt_range(m, m->embed_out, m->n_floats, false));
+            }
         }
         dx = dxn;
     }
@@ -737,6 +761,8 @@ static int backward(nncu_model *m)
     KERNEL_CHECK();
     side_join(m);
     NNCU_TRY(exchange_bucket(m, m->tail_begin, m->embed_out)); // final norm and the embedding
+    NNCU_TRY(opt_range(m, m->tail_begin, m->embed_out, true));
+    NNCU_TRY(opt_range(m, 0, m->lo[0].w_q, true)); // (empty: layer 0 opens the parameter table)
     NNCU_TRY(exchange_finish(m));
     return NNCU_OK;
 }
@@ -906,7 +932,7 @@ int nncu_destroy(nncu_model *m)
     cudaSetDevice(m->device);
     cudaStreamSynchronize(m->st);
     // graphs first: a captured ncclAllReduce keeps its communicator busy until the graph is gone
-    for (int k = 0; k < 2; k++)
+    for (int k = 0; k < 3; k++)
         for (int c = 0; c < 2; c++)
             if (m->graphs[k][c].exec)
                 cudaGraphExecDestroy(m->graphs[k][c].exec);
@@ -1118,6 +1144,7 @@ int nncu_create(const nncu_params *p, nncu_model **out)
     m->skw = skw_floats ? (float *)(A + oSkw) : nullptr;
     m->skw_floats = skw_floats;
     m->logp = (float *)(A + oLogp); m->loss_dev = (float *)(A + oLoss);
+    m->hyper_dev = m->loss_dev + 8;
     m->ids_dev = (int32_t *)(A + oIds); m->tgt_dev = (int32_t *)(A + oTgt);
     m->err_flag = (int *)(A + oErr); m->hash_dev = (unsigned long long *)(A + oHash);
     m->jobs_dev = (TransposeJob *)(A + oJobs);
@@ -1309,12 +1336,24 @@ int nncu_probs_dev(nncu_model *m, float **probs_dev)
     return NNCU_OK;
 }
 
-static int gradient_common(nncu_model *m)
+static int gradient_common(nncu_model *m, bool fused = false)
 {
     if (!m->have_forward)
         return nncu_fail(NNCU_ERR_STATE, "eval_gradient needs a complete forward pass first");
     bind_xin(m);
-    return run_graphed(m, GRAPH_BWD, [&]() { return m->bf ? backward<bf16>(m) : backward<float>(m); });
+    if (fused) {
+        // this step's learning rate and bias correction, read by the captured optimizer launches
+        m->step++;
+        const float hyper[2] = {m->lr, m->p.bias_correction ? 1.0f / (1.0f - powf(m->p.beta2, (float)m->step)) : 1.0f};
+        CUDA_TRY(cudaMemcpyAsync(m->hyper_dev, hyper, sizeof(hyper), cudaMemcpyHostToDevice, m->st));
+    }
+    m->fuse_update = fused;
+    int rc = run_graphed(m, fused ? GRAPH_BWD_UPD : GRAPH_BWD,
+                         [&]() { return m->bf ? backward<bf16>(m) : backward<float>(m); });
+    m->fuse_update = false;
+    if (rc == NNCU_OK && fused)
+        rc = refresh_transposed(m);
+    return rc;
 }
 
 int nncu_read_loss(nncu_model *m, float *loss_out)
@@ -1370,6 +1409,32 @@ int nncu_eval_gradient_dev(nncu_model *m, const int32_t *expected_dev)
     return queue_loss(m);
 }
 
+int nncu_eval_gradient_update(nncu_model *m, const int32_t *expected_host, float *loss_out)
+{
+    if (!m || !expected_host)
+        return nncu_fail(NNCU_ERR_INVALID, "null argument");
+    CUDA_TRY(cudaSetDevice(m->device));
+    CUDA_TRY(cudaEventSynchronize(m->ev_tgt));
+    memcpy(m->tgt_pin, expected_host, sizeof(int32_t) * m->TB);
+    CUDA_TRY(cudaMemcpyAsync(m->tgt_dev, m->tgt_pin, sizeof(int32_t) * m->TB, cudaMemcpyHostToDevice, m->st));
+    CUDA_TRY(cudaEventRecord(m->ev_tgt, m->st));
+    NNCU_TRY(gradient_common(m, true));
+    NNCU_TRY(queue_loss(m));
+    if (loss_out)
+        return nncu_read_loss(m, loss_out);
+    return NNCU_OK;
+}
+
+int nncu_eval_gradient_update_dev(nncu_model *m, const int32_t *expected_dev)
+{
+    if (!m || !expected_dev)
+        return nncu_fail(NNCU_ERR_INVALID, "null argument");
+    CUDA_TRY(cudaSetDevice(m->device));
+    CUDA_TRY(cudaMemcpyAsync(m->tgt_dev, expected_dev, sizeof(int32_t) * m->TB, cudaMemcpyDeviceToDevice, m->st));
+    NNCU_TRY(gradient_common(m, true));
+    return queue_loss(m);
+}
+
 int nncu_optimizer_step(nncu_model *m)
 {
     if (!m)
@@ -1381,7 +1446,7 @@ int nncu_optimizer_step(nncu_model *m)
         corr = 1.0f / (1.0f - powf(m->p.beta2, (float)m->step));
     size_t n4 = m->n_floats / 4;
     launch_k(rmsprop_kernel, dim3(ceil_div(n4, 256)), dim3(256), 0, m->st, m->W, m->G, m->Vm, m->Wb, n4, m->lr, m->p.beta2,
-                                                         m->p.eps, m->p.gradient_clip, corr);
+                                                         m->p.eps, m->p.gradient_clip, corr, (const float *)nullptr);
     KERNEL_CHECK();
     return refresh_transposed(m);
 }

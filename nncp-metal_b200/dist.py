@@ -41,8 +41,20 @@ class ShardedStep:
         self.model.update()
         return loss
 
+    def fused(self):
+        """The optimizer may run inside the backward pass when nobody has to sum gradients after it."""
+        import os
+        if os.environ.get("NNCU_FUSED_UPDATE") != "1":
+            return False  # measured at 1 GPU on the c2 step: 2.897 ms fused, 2.889 ms separate
+        return (self.world == 1 or getattr(self.model, "has_comm", False)) and \
+            hasattr(self.model, "eval_gradient_update_dev")
+
     def step_device(self, ids_ptr, targets_ptr):
         self.model.eval_dev(-1, ids_ptr)
+        if self.fused():
+            self.model.eval_gradient_update_dev(targets_ptr)
+            self.model.memory_shift()
+            return
         self.model.eval_gradient_dev(targets_ptr)
         self.reduce_gradients()
         self.model.update()

@@ -94,6 +94,16 @@ class TrfModel:
     def eval_gradient_dev(self, targets_dev_ptr):
         self._ck(self.lib.nncu_eval_gradient_dev(self.h, _vp(targets_dev_ptr)))
 
+    def eval_gradient_update(self, targets, wait_loss=True):
+        """Backward pass with the optimizer step queued per layer; follow with memory_shift()."""
+        t = np.ascontiguousarray(targets, np.int32)
+        loss = C.c_float()
+        self._ck(self.lib.nncu_eval_gradient_update(self.h, _ptr(t), C.byref(loss) if wait_loss else None))
+        return loss.value if wait_loss else None
+
+    def eval_gradient_update_dev(self, targets_dev_ptr):
+        self._ck(self.lib.nncu_eval_gradient_update_dev(self.h, _vp(targets_dev_ptr)))
+
     def read_loss(self):
         loss = C.c_float()
         self._ck(self.lib.nncu_read_loss(self.h, C.byref(loss)))

@@ -303,6 +303,38 @@ def test_output_head_split_k_vs_oracle(pkg, oracle):
     m.close()
 
 
+@pytest.mark.parametrize("name,bf16,graphs", [("c0_like", 1, 0), ("c0_like", 1, 1), ("tied_tables_longmem", 1, 1),
+                                              ("post_gelu", 0, 1)])
+def test_fused_gradient_and_update_gives_the_same_bits(pkg, name, bf16, graphs):
+    """nncu_eval_gradient_update + nncu_memory_shift against nncu_eval_gradient + nncu_update over six
+    steps with a changing learning rate and bias correction on: same losses, same weights; eager
+    (default stream) and with the captured graphs (own stream)."""
+    cfg, z = load_golden(name)
+    res = []
+    for fused in (False, True):
+        m = pkg.TrfModel(params_from_cfg(pkg, cfg, use_bf16=bf16, bias_correction=1))
+        stream = torch.cuda.Stream() if graphs else None
+        if stream is not None:
+            m.set_stream(stream.cuda_stream)
+        _load(m, z)
+        m.reset()
+        losses = []
+        for s in range(6):
+            m.set_lr(cfg["lr"] * (1.0 + 0.25 * s))
+            m.eval(-1, z["ids"][s % 2], read=False)
+            if fused:
+                losses.append(m.eval_gradient_update(z["targets"][s % 2]))
+                m.memory_shift()
+            else:
+                losses.append(m.eval_gradient(z["targets"][s % 2]))
+                m.update()
+        m.synchronize()
+        res.append((losses, m.weights_hash()))
+        m.close()
+    assert res[0][0] == res[1][0]
+    assert res[0][1] == res[1][1]
+
+
 def test_two_runs_are_bit_identical(pkg):
     cfg, z = load_golden("c0_like")
     hashes = []
