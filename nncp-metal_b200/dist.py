@@ -44,10 +44,14 @@ class ShardedStep:
     def fused(self):
         """The optimizer may run inside the backward pass when nobody has to sum gradients after it."""
         import os
-        if os.environ.get("NNCU_FUSED_UPDATE") != "1":
-            return False  # measured at 1 GPU on the c2 step: 2.897 ms fused, 2.889 ms separate
-        return (self.world == 1 or getattr(self.model, "has_comm", False)) and \
-            hasattr(self.model, "eval_gradient_update_dev")
+        if not hasattr(self.model, "eval_gradient_update_dev"):
+            return False
+        env = os.environ.get("NNCU_FUSED_UPDATE")
+        if env is not None:
+            return env == "1" and (self.world == 1 or getattr(self.model, "has_comm", False))
+        # measured on the c2 step: 1 GPU 2.897 ms fused against 2.889 ms separate; 2 GPUs (update queued
+        # behind each layer's all-reduce) 2.470 ms against 2.493 ms
+        return self.world > 1 and getattr(self.model, "has_comm", False)
 
     def step_device(self, ids_ptr, targets_ptr):
         self.model.eval_dev(-1, ids_ptr)
