@@ -51,18 +51,6 @@ __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes)
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
                  : "memory");
 }
-// non-blocking probe of the phase with the given parity
-__device__ __forceinline__ uint32_t mbar_test(uint32_t bar, uint32_t parity)
-{
-    uint32_t ok;
-    asm volatile("{\n\t.reg .pred p;\n\t"
-                 "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-                 "selp.u32 %0, 1, 0, p;\n\t}"
-                 : "=r"(ok)
-                 : "r"(bar), "r"(parity)
-                 : "memory");
-    return ok;
-}
 // bounded wait; returns false (and raises the flags) when the limit is hit.  The thread
 // suspends inside try_wait (up to about a microsecond per try) instead of polling; the loop is
 // PTX so that the path of a barrier that is already complete is a try and a branch.

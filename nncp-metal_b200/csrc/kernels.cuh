@@ -370,21 +370,6 @@ reduce_cols_kernel(const float *__restrict__ part, int n_parts, int stride, int 
     }
 }
 
-// out[i] (+)= sum over parts p (in order) of part[p][i]; used for dg/db ([2][D] -> two
-// destinations) and every other two-stage column reduction.
-__global__ void reduce_parts_kernel(const float *__restrict__ part, int n_parts, int stride,
-                                    int n, float *__restrict__ out, int accumulate, float scale)
-{
-    int i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= n)
-        return;
-    float s = 0.0f;
-    for (int p = 0; p < n_parts; p++)
-        s += part[(size_t)p * stride + i];
-    s *= scale;
-    out[i] = accumulate ? out[i] + s : s;
-}
-
 // dst = a + b (elementwise), used where a residual joins without a norm
 template <typename T>
 __global__ void add_kernel(const T *__restrict__ a, const T *__restrict__ b, T *__restrict__ dst,
