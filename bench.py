@@ -14,12 +14,20 @@ streams are sharded across ranks and gradients are summed with one NCCL all-redu
           every step, the coder-ready prob0 paths and the loss read back every step.
 `roofline` the tcgen05 GEMM kernel: sum of 2*M*N*K over its launches / sum of their CUDA-event
           durations, against the measured bf16 peak.
+`attention` the isolated attention op of BASELINE config[1] (forward, and forward + backward)
+          through nncu_attention_forward / _backward: TFLOP/s and the fraction of its
+          min(tensor, HBM) roofline.
 `cpu_baseline` the CPU oracle (port of nncp.c's graph, OpenMP) timed on a bounded sample.
+
+The K-step timed region is measured REPEATS times in the same process (each bracketed by a
+barrier and a synchronize, CUDA events, max over ranks); `value` is the median, `value_min` /
+`value_max` the spread.
 """
 import argparse
 import ctypes as C
 import json
 import os
+import re
 import statistics
 import subprocess
 import sys
@@ -148,14 +156,17 @@ def peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
         p = json.load(open(path))
-        return p.get("bf16_tflops_sustained", 1420.5), p.get("hbm_gbs", 6453.4), "measured"
-    return 1400.0, 6650.0, "fallback"
+        return (p.get("bf16_tflops_sustained", 1420.5), p.get("hbm_gbs", 6453.4), "measured",
+                p.get("bf16_tflops", 1693.0))
+    return 1400.0, 6650.0, "fallback", 1590.0
 
 
 def cpu_port_run(c, steps, warmup, streams):
     """Times the CPU oracle on `streams` streams of the workload's model; returns symbols/s."""
     pkg = entry._package()
     from oracle import oracle as orc
+    # every host core, whatever OMP_NUM_THREADS the launcher exported (torch.distributed.run sets 1)
+    threads = orc.lib().orc_set_threads(os.cpu_count() or 1)
     kw = dict(COMMON)
     kw.update(c)
     kw.update(n_streams=streams, n_streams_total=streams, use_bf16=0)
@@ -172,7 +183,7 @@ def cpu_port_run(c, steps, warmup, streams):
         m.update()
     dt = time.perf_counter() - t0
     m.close()
-    return steps * c["seg_len"] * streams / dt, dt
+    return steps * c["seg_len"] * streams / dt, dt, threads
 
 
 def workload_name(name, c):
@@ -181,27 +192,122 @@ def workload_name(name, c):
             f"seg {c['seg_len']}, mem {c['mem_len']}, {c['n_streams']} streams")
 
 
+def job_config(name, c, world, exchange):
+    """The `config` object of the JSON line; both arms print the same one for the same N."""
+    return {"workload": workload_name(name, c), "streams_per_gpu": c["n_streams"] // world,
+            "parallelism": f"dp{world} over streams", "gradient_exchange": exchange,
+            "l2": "per-step working set (weights, optimizer state, activations) exceeds the 126 MB L2",
+            "tokens": "seeded Zipf(1.1)+order-1 Markov ids (stand-in for tokenised text)"}
+
+
+def exchange_name(world):
+    if world == 1:
+        return "none"
+    if os.environ.get("NNCU_PY_ALLREDUCE") == "1":
+        return "one all-reduce after backward"
+    return "per-layer reduce-scatter, RMSProp on the rank's shard, all-gather of the weights, overlapped with backward"
+
+
 def run_reference(args, c):
+    """The reference arm: the CPU oracle port of the train step on all host cores (the reference's
+    own train step runs on LibNC, which its tree does not contain).  Rank 0 only."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
     streams = CPU_STREAMS.get(args.config, c["n_streams"])
-    args.steps = min(args.steps, 20)   # bounded: a c2 step of 2 streams is about a second of CPU work
-    val, dt = cpu_port_run(c, args.steps, min(args.warmup, 1), streams)
-    cores = os.cpu_count()
+    K, W = min(args.steps, 100), min(args.warmup, 5)   # bounded: a c2 step of 2 streams is ~0.4 s of CPU work
+    val, dt, threads = cpu_port_run(c, K, W, streams)
+    sample = (f"{K} steps of {streams} of the {c['n_streams']} streams x {c['seg_len']} symbols, "
+              f"oracle/trf_oracle.c with OpenMP on {threads} threads; the reference's own train step "
+              f"needs LibNC, which its tree does not contain")
     line = {"impl": "reference", "metric": "compressed symbols/s (fwd+bwd+RMSProp)", "value": val,
-            "unit": "symbols/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": min(args.warmup, 1),
-            "ms_per_step": 1e3 * dt / args.steps, "higher_is_better": True, "scaling": "strong",
+            "unit": "symbols/s", "n_gpus": args.gpus, "steps": K, "warmup": W,
+            "ms_per_step": 1e3 * dt / K, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": workload_name(args.config, c), "sample":
-                       f"{streams} of {c['n_streams']} streams per step",
-                       "tokens": "seeded Zipf(1.1)+order-1 Markov ids (stand-in for tokenised text)"},
-            "cpu_baseline": {"value": val, "unit": "symbols/s", "cores": cores, "kind": "port",
-                             "sample": f"{args.steps} steps of {streams} streams x {c['seg_len']} symbols, "
-                                       f"oracle/trf_oracle.c with OpenMP; the reference's own train step "
-                                       f"needs LibNC, which its tree does not contain"},
+            "config": job_config(args.config, c, args.gpus, exchange_name(args.gpus)),
+            "cpu_baseline": {"value": val, "unit": "symbols/s", "cores": threads, "kind": "port",
+                             "sample": sample},
             "e2e": {"value": val, "unit": "symbols/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     print(json.dumps(line), flush=True)
+
+
+def profile_traffic(kernel_md):
+    """`traffic_bytes_per_launch: <number>` from a profile summary under profiles/ (ncu's
+    dram__bytes_read.sum + dram__bytes_write.sum per launch), or None."""
+    try:
+        text = open(os.path.join(ROOT, "profiles", kernel_md)).read()
+    except OSError:
+        return None
+    mt = re.search(r"traffic_bytes_per_launch:\s*([0-9.eE+]+)", text)
+    return float(mt.group(1)) if mt else None
+
+
+def attention_record(pkg, lib, torch, peak_tf_burst, peak_hbm, which, reps=120):
+    """BASELINE config[1]: the isolated relative-position attention op, 16 streams x 8 heads x
+    d_head 64, 64 queries over 64 + 64 keys, R of length 128, bf16, forward and backward through
+    the C ABI.  Twelve operand sets are used in rotation (12 x 12.7 MB > the 126 MB L2), so every
+    call reads its operands from HBM."""
+    B, H, dk, T, M, P = 16, 8, 64, 64, 64, 128
+    L, HD = M + T, H * dk
+    nsets = 12
+    g = torch.Generator(device="cpu").manual_seed(7)
+    bf = torch.bfloat16
+    mk = lambda *sh: torch.randn(nsets, *sh, generator=g).to(bf).cuda()
+    q, kv, dout = mk(T * B, HD), mk(L * B, 2 * HD), mk(T * B, HD)
+    out, dq, dkv = torch.zeros_like(q), torch.zeros_like(q), torch.zeros_like(kv)
+    lse = torch.zeros(nsets, B * H, T, device="cuda")
+    w_r = (0.02 * torch.randn(H, P, dk, generator=g)).cuda()
+    b_r = (0.02 * torch.randn(H, L, generator=g)).cuda()
+    pw, pb = torch.zeros(B, H, P, dk, device="cuda"), torch.zeros(B, H, L, device="cuda")
+    gw, gb = torch.zeros(H, P, dk, device="cuda"), torch.zeros(H, L, device="cuda")
+    shp = pkg.abi.AttnShape(B, H, dk, T, M, P, 0, 0, T, float(np.sqrt(dk * 512.0)), 1)
+    st = torch.cuda.current_stream()
+    sp = C.c_void_p(st.cuda_stream)
+
+    def ck(rc):
+        if rc != 0:
+            raise RuntimeError(lib.nncu_last_error().decode())
+
+    def fwd(i):
+        ck(lib.nncu_attention_forward(C.byref(shp), q[i].data_ptr(), kv[i].data_ptr(), w_r.data_ptr(),
+                                      b_r.data_ptr(), out[i].data_ptr(), lse[i].data_ptr(), sp))
+
+    def bwd(i):
+        ck(lib.nncu_attention_backward(C.byref(shp), q[i].data_ptr(), kv[i].data_ptr(), w_r.data_ptr(),
+                                       b_r.data_ptr(), out[i].data_ptr(), lse[i].data_ptr(), dout[i].data_ptr(),
+                                       dq[i].data_ptr(), dkv[i].data_ptr(), pw.data_ptr(), pb.data_ptr(), sp))
+        ck(lib.nncu_attention_reduce_tables(C.byref(shp), pw.data_ptr(), pb.data_ptr(), gw.data_ptr(),
+                                            gb.data_ptr(), 0, sp))
+
+    def timed(body):
+        for i in range(nsets):
+            body(i)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(st)
+        for r in range(reps):
+            body(r % nsets)
+        e1.record(st)
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) * 1e-3 / reps
+
+    t_f = timed(fwd)
+    t_fb = timed(lambda i: (fwd(i), bwd(i)))
+    fam = 2.0 * B * H * T * L * dk
+    fl_f, fl_fb = 3 * fam, 11 * fam          # QK^T, W_r^T q, PV; the backward recomputes both score products
+    byt = 2.0 * (4 * T * B * HD + 4 * L * B * HD) + 4.0 * (H * P * dk + H * L)
+    floor_f = max(fl_f / (peak_tf_burst * 1e12), 2.0 * (2 * T * B * HD + 2 * L * B * HD) / (peak_hbm * 1e9))
+    floor_fb = max(fl_fb / (peak_tf_burst * 1e12), byt / (peak_hbm * 1e9))
+    return {"config": "BASELINE config[1]: 16 streams x 8 heads x d_head 64, 64 queries, 64+64 keys, R length 128, "
+                      "bf16 operands, fp32 accumulation; 12 operand sets in rotation (working set > L2)",
+            "reps": reps, "fwd_us": t_f * 1e6, "fwd_bwd_us": t_fb * 1e6,
+            "fwd_tflops": fl_f / t_f / 1e12, "fwd_bwd_tflops": fl_fb / t_fb / 1e12,
+            "fwd_gflop": fl_f / 1e9, "fwd_bwd_gflop": fl_fb / 1e9,
+            "flops_counted": "forward 3 contraction families, backward 8 (both score products recomputed)",
+            "roofline": {"bound": "min(tensor, hbm): hbm", "floor_us_fwd": floor_f * 1e6,
+                         "floor_us_fwd_bwd": floor_fb * 1e6, "frac_fwd": floor_f / t_f,
+                         "frac_fwd_bwd": floor_fb / t_fb, "operand_bytes_fwd_bwd": byt,
+                         "peak_source": f"{which} bf16_tflops (burst) and hbm_gbs"}}
 
 
 def main():
@@ -213,6 +319,8 @@ def main():
     ap.add_argument("--config", default="c2", choices=sorted(CONFIGS))
     ap.add_argument("--backend", type=int, default=0, help="0 auto, 1 SIMT, 2 tcgen05")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-attention", action="store_true", help="skip the config[1] attention record")
+    ap.add_argument("--repeats", type=int, default=7, help="times the K-step region is measured (median reported)")
     args = ap.parse_args()
     c = dict(CONFIGS[args.config])
     if args.impl == "reference":
@@ -247,6 +355,7 @@ def main():
     m.set_stream(stream.cuda_stream)
     T, V = c["seg_len"], c["n_symbols"]
     K, W = args.steps, max(args.warmup, 3)
+    REPEATS = max(1, args.repeats)
     ids_all, tg_all = make_batches(c, Bt, K + W)
     sl = pkg.dist.stream_slice(rank, world, Bt)
     ids_h = torch.from_numpy(np.ascontiguousarray(ids_all[:, :, sl])).pin_memory()
@@ -318,46 +427,56 @@ def main():
     sampler = ClockSampler(local) if rank == 0 else None
     if sampler:
         sampler.start()
-    lib.nncu_profile_begin(0)
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record(stream)
-    for s in range(W, W + K):
-        step_device(s)
-    e1.record(stream)
-    barrier()
-    prof = pkg.abi.Profile()
-    lib.nncu_profile_end(C.byref(prof))
-    ms = e0.elapsed_time(e1)
+
+    def max_over_ranks(ms):
+        if world > 1:
+            t = torch.tensor([ms], device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            return t.item()
+        return ms
+
+    # the K-step region, REPEATS times; each repeat bracketed by barrier + synchronize
+    times = []
+    launches = 0
+    for r in range(REPEATS):
+        barrier()
+        lib.nncu_profile_begin(0)
+        e0.record(stream)
+        for s in range(W, W + K):
+            step_device(s)
+        e1.record(stream)
+        barrier()
+        prof = pkg.abi.Profile()
+        lib.nncu_profile_end(C.byref(prof))
+        launches = int(prof.launches)
+        times.append(max_over_ranks(e0.elapsed_time(e1)))
     m.synchronize()
-    if world > 1:
-        t = torch.tensor([ms], device="cuda")
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms = t.item()
+    ms = statistics.median(times)
     value = K * T * Bt / (ms * 1e-3)
 
     # end to end through the host-buffer calls
     m.reset()
     for s in range(2):
         step_host(s)
-    barrier()
-    t0 = time.perf_counter()
-    e0.record(stream)
-    for s in range(W, W + K):
-        step_host(s)
-    e1.record(stream)
-    barrier()
-    ms_e2e = max(e0.elapsed_time(e1), (time.perf_counter() - t0) * 1e3)
+    times_e2e = []
+    for r in range(REPEATS):
+        barrier()
+        t0 = time.perf_counter()
+        e0.record(stream)
+        for s in range(W, W + K):
+            step_host(s)
+        e1.record(stream)
+        barrier()
+        times_e2e.append(max_over_ranks(max(e0.elapsed_time(e1), (time.perf_counter() - t0) * 1e3)))
     clocks = sampler.stop() if sampler else None   # sampled over both timed regions
-    if world > 1:
-        t = torch.tensor([ms_e2e], device="cuda")
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms_e2e = t.item()
+    ms_e2e = statistics.median(times_e2e)
     e2e = K * T * Bt / (ms_e2e * 1e-3)
 
     # per-launch timing of the dominant kernel (separate short pass so the timed region above
     # carries no event overhead)
     roof = None
-    peak_tf, peak_hbm, which = peaks()
+    peak_tf, peak_hbm, which, peak_tf_burst = peaks()
     if p.use_bf16 and args.backend != 1:
         lib.nncu_profile_begin(1)
         for s in range(W, W + min(K, 3)):
@@ -367,15 +486,18 @@ def main():
         lib.nncu_profile_end(C.byref(pr))
         if pr.gemm_launches:
             ach = pr.gemm_flops / (pr.gemm_ms * 1e-3) / 1e12
-            roof = {"bound": "tensor", "kernel": "gemm_tc_kernel (tcgen05 bf16 NT GEMM)",
+            traffic = profile_traffic("gemm_tc_kernel_c2_dram_traffic.md") if (args.config == "c2" and world == 1) else None
+            roof = {"bound": "tensor", "kernel": "gemm_tc_kernel (tcgen05 bf16 GEMM, all operand arrangements)",
                     "achieved": ach, "peak": peak_tf, "unit": "TFLOP/s", "frac": ach / peak_tf,
                     "peak_source": f"{which} bf16_tflops_sustained",
-                    # dram__bytes_read+write per launch, averaged over the 147 GEMM launches of one c2
-                    # step at 1 GPU (ncu capture summarised in profiles/gemm_tc_kernel_c2_dram_traffic.md)
-                    "traffic": 9.43e6 if (args.config == "c2" and world == 1) else None,
-                    "traffic_unit": "bytes/launch (ncu, cold caches; algorithmic 13.97e6)",
+                    "traffic": traffic,
+                    "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum per launch, from the committed "
+                                      "profile summary of this kernel on this workload (not re-measured by this run)",
                     "launches_per_step": pr.gemm_launches / min(K, 3),
                     "share_of_step": (pr.gemm_ms / min(K, 3)) / (ms / K)}
+    attn = None
+    if rank == 0 and not args.no_attention:
+        attn = attention_record(pkg, lib, torch, peak_tf_burst, peak_hbm, which)
     m.synchronize()
     whash = m.weights_hash()
     if world > 1:
@@ -391,36 +513,35 @@ def main():
                 "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": ms / K, "higher_is_better": True,
                 "scaling": "strong", "vs_baseline": None, "dtype": "bf16" if p.use_bf16 else "f32",
                 "data": "synthetic",
-                "config": {"workload": workload_name(args.config, c),
-                           "streams_per_gpu": B, "parallelism": f"dp{world} over streams",
-                           "gradient_exchange": ("none" if world == 1 else
-                                                 "per-layer ncclAllReduce overlapped with backward" if m.has_comm
-                                                 else "one all-reduce after backward"),
-                           "l2": "per-step working set (weights, optimizer state, activations) exceeds the 126 MB L2",
-                           "tokens": "seeded Zipf(1.1)+order-1 Markov ids (stand-in for tokenised text)"},
-                "step_tflops": fl / (ms / K * 1e-3) / 1e12 , "step_gflop": fl / 1e9,
-                "gpu_launches": int(prof.launches), "clocks": clocks,
+                "config": job_config(args.config, c, world, exchange_name(world) if (world == 1 or m.has_comm)
+                                     else "one all-reduce after backward"),
+                "repeats": REPEATS, "value_min": K * T * Bt / (max(times) * 1e-3),
+                "value_max": K * T * Bt / (min(times) * 1e-3),
+                "step_tflops": fl / (ms / K * 1e-3) / 1e12, "step_gflop": fl / 1e9,
+                "gpu_launches": launches, "clocks": clocks,
                 "e2e": {"value": e2e, "unit": "symbols/s", "h2d_bytes_per_step": 2 * T * B * 4 * world,
                         "d2h_bytes_per_step": (T * B * nb * 2 + 4) * world if nb else (T * B * V * 4 + 4) * world,
-                        "ms_per_step": ms_e2e / K},
+                        "ms_per_step": ms_e2e / K, "value_min": K * T * Bt / (max(times_e2e) * 1e-3),
+                        "value_max": K * T * Bt / (min(times_e2e) * 1e-3)},
                 "ranks_hold_identical_weights": same, "weights_hash": f"{whash:016x}"}
         if roof:
             line["roofline"] = roof
+        if attn:
+            line["attention"] = attn
         if not args.no_cpu_baseline and world == 1:
             streams = CPU_STREAMS.get(args.config, c["n_streams"])
-            val, dt = cpu_port_run(c, 2, 1, streams)
-            line["cpu_baseline"] = {"value": val, "unit": "symbols/s", "cores": os.cpu_count(), "kind": "port",
-                                    "sample": f"2 steps of {streams} streams x {T} symbols of the same model "
-                                              f"(oracle/trf_oracle.c, OpenMP, {dt:.1f} s)"}
+            val, dt, threads = cpu_port_run(c, 6, 1, streams)
+            line["cpu_baseline"] = {"value": val, "unit": "symbols/s", "cores": threads, "kind": "port",
+                                    "sample": f"6 steps of {streams} of the {c['n_streams']} streams x {T} symbols "
+                                              f"of the same model (oracle/trf_oracle.c, OpenMP on {threads} "
+                                              f"threads, {dt:.1f} s)"}
         print(json.dumps(line), flush=True)
-    if world > 1:
-        dist.barrier()
-        torch.cuda.synchronize()
+    barrier()
     m.close()
     if world > 1:
+        dist.barrier()
         dist.destroy_process_group()
     sys.stdout.flush()
-    os._exit(0)   # the measurement is out; nothing at interpreter shutdown may hold the GPUs
 
 
 if __name__ == "__main__":

@@ -914,3 +914,30 @@ static int attn_backward_any(const nncu_attn_shape *s, const void *q, const void
     }
     return attn_backward_t<T>(s, q, kv, w_r, b_r, out, lse, dout, dq, dkv, dwr_part, dbr_part, st, pt);
 }
+
+// Whether some kernel pair can run the forward and the backward pass of this shape (asked once,
+// when a model is created, so that an unsupported shape is refused there and not in the middle
+// of a file).  Mirrors the dispatch of attn_forward_any / attn_backward_any.
+template <typename T>
+static int attn_shape_supported(const nncu_attn_shape *s, bool has_wr)
+{
+    AttnArgs a = attn_args(s, nullptr);
+    const bool mma = sizeof(T) == 2 && !attn_force_simt();
+    if (!(mma && amma::supported(a, false))) {
+        const size_t smem = attn_fwd_smem<T>(a.L, a.P, a.dk, has_wr);
+        if (smem > 227 * 1024)
+            return nncu_fail(NNCU_ERR_RANGE,
+                             "attention forward of this shape (%d keys, d_pos %d, d_key %d) needs %zu bytes of "
+                             "shared memory; the limit is %d",
+                             a.L, a.P, a.dk, smem, 227 * 1024);
+    }
+    if (!(mma && amma::supported(a, true))) {
+        const size_t smem = attn_bwd_smem<T>(a.T, a.L, a.P, a.dk, has_wr);
+        if (smem > 227 * 1024)
+            return nncu_fail(NNCU_ERR_RANGE,
+                             "attention backward of this shape (seg_len %d, %d keys, d_pos %d, d_key %d) needs %zu "
+                             "bytes of shared memory; the limit is %d",
+                             a.T, a.L, a.P, a.dk, smem, 227 * 1024);
+    }
+    return NNCU_OK;
+}

@@ -966,6 +966,15 @@ int nncu_create(const nncu_params *p, nncu_model **out)
         return nncu_fail(NNCU_ERR_INVALID, "null output pointer");
     *out = nullptr;
     NNCU_TRY(validate(p));
+    {
+        // shapes no attention kernel pair can run are refused here, not at the first segment
+        nncu_attn_shape s;
+        s.n_streams = p->n_streams; s.n_head = p->n_head; s.d_key = p->d_key; s.seg_len = p->seg_len;
+        s.mem_len = p->mem_len; s.d_pos = p->d_pos; s.attn_len = 0; s.t0 = 0; s.t1 = p->seg_len;
+        s.br_scale = 1.0f; s.dtype_bf16 = p->use_bf16 ? 1 : 0;
+        NNCU_TRY(p->use_bf16 ? attn_shape_supported<bf16>(&s, p->use_w_r != 0)
+                             : attn_shape_supported<float>(&s, p->use_w_r != 0));
+    }
     int ndev = 0;
     if (cudaGetDeviceCount(&ndev) != cudaSuccess || ndev == 0)
         return nncu_fail(NNCU_ERR_CUDA, "no CUDA device: this library has no CPU path");
@@ -1832,6 +1841,39 @@ int nncu_attention_backward_noalloc(const nncu_attn_shape *s, const void *q, con
 
 // ---- dense contraction test hooks
 
+// the time-out flag of the stand-alone GEMM entry points: one int per device inside the library
+// image (no allocation; a flag allocated on one device must not be handed to a kernel on another)
+static __device__ int g_gemm_flag;
+static int *g_gemm_flag_ptr[NNCU_MAX_DEVICES];
+
+static int gemm_flag(int **out)
+{
+    int dev = -1;
+    CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= NNCU_MAX_DEVICES)
+        return nncu_fail(NNCU_ERR_INVALID, "device ordinal %d out of range", dev);
+    if (!g_gemm_flag_ptr[dev]) {
+        int *ptr = nullptr;
+        CUDA_TRY(cudaGetSymbolAddress((void **)&ptr, g_gemm_flag));
+        CUDA_TRY(cudaMemset(ptr, 0, sizeof(int)));
+        g_gemm_flag_ptr[dev] = ptr;
+    }
+    *out = g_gemm_flag_ptr[dev];
+    return NNCU_OK;
+}
+
+static int gemm_flag_check(int *flag, cudaStream_t st)
+{
+    int h = 0;
+    CUDA_TRY(cudaMemcpyAsync(&h, flag, sizeof(int), cudaMemcpyDeviceToHost, st));
+    CUDA_TRY(cudaStreamSynchronize(st));
+    if (h != 0) {
+        CUDA_TRY(cudaMemsetAsync(flag, 0, sizeof(int), st));
+        return nncu_fail(NNCU_ERR_TIMEOUT, "tcgen05 GEMM: a bounded wait expired (code %d)", h);
+    }
+    return NNCU_OK;
+}
+
 #ifdef NNCU_ATTN_TRACE
 extern "C" int nncu_attn_trace(long long *dev_buf)
 {
@@ -1862,11 +1904,8 @@ int nncu_gemm_bf16(int backend, int mode, int M, int N, int K, const void *A, in
     if (backend == NNCU_GEMM_SIMT)
         return c_is_f32 ? gemm_simt<bf16, bf16, float>(st, mode, M, N, K, a, lda, b, ldb, (float *)C, ldc, nullptr, 0)
                         : gemm_simt<bf16, bf16, bf16>(st, mode, M, N, K, a, lda, b, ldb, (bf16 *)C, ldc, nullptr, 0);
-    static int *flag = nullptr;
-    if (!flag) {
-        CUDA_TRY(cudaMalloc(&flag, sizeof(int)));
-        CUDA_TRY(cudaMemset(flag, 0, sizeof(int)));
-    }
+    int *flag = nullptr;
+    NNCU_TRY(gemm_flag(&flag));
     int rc;
     if (mode == GEMM_NT)
         rc = c_is_f32 ? tc::gemm<float, false, false>(st, M, N, K, a, lda, b, ldb, (float *)C, ldc, nullptr, nullptr, flag)
@@ -1879,14 +1918,7 @@ int nncu_gemm_bf16(int backend, int mode, int M, int N, int K, const void *A, in
                       : tc::gemm<bf16, true, true>(st, M, N, K, a, lda, b, ldb, (bf16 *)C, ldc, nullptr, nullptr, flag);
     if (rc != NNCU_OK)
         return rc;
-    int h = 0;
-    CUDA_TRY(cudaMemcpyAsync(&h, flag, sizeof(int), cudaMemcpyDeviceToHost, st));
-    CUDA_TRY(cudaStreamSynchronize(st));
-    if (h != 0) {
-        cudaMemset(flag, 0, sizeof(int));
-        return nncu_fail(NNCU_ERR_TIMEOUT, "tcgen05 GEMM: a bounded wait expired (code %d)", h);
-    }
-    return NNCU_OK;
+    return gemm_flag_check(flag, st);
 }
 
 
@@ -1901,23 +1933,13 @@ int nncu_gemm_bf16_nt(int backend, int M, int N, int K, const void *A, int lda, 
         return c_is_f32 ? gemm_simt<bf16, bf16, float>(st, GEMM_NT, M, N, K, a, lda, b, ldb, (float *)C, ldc, bias, 0)
                         : gemm_simt<bf16, bf16, bf16>(st, GEMM_NT, M, N, K, a, lda, b, ldb, (bf16 *)C, ldc, bias, 0);
     }
-    static int *flag = nullptr;
-    if (!flag) {
-        CUDA_TRY(cudaMalloc(&flag, sizeof(int)));
-        CUDA_TRY(cudaMemset(flag, 0, sizeof(int)));
-    }
+    int *flag = nullptr;
+    NNCU_TRY(gemm_flag(&flag));
     int rc = c_is_f32 ? tc::gemm_nt<float>(st, M, N, K, a, lda, b, ldb, (float *)C, ldc, bias, nullptr, flag)
                       : tc::gemm_nt<bf16>(st, M, N, K, a, lda, b, ldb, (bf16 *)C, ldc, bias, nullptr, flag);
     if (rc != NNCU_OK)
         return rc;
-    int h = 0;
-    CUDA_TRY(cudaMemcpyAsync(&h, flag, sizeof(int), cudaMemcpyDeviceToHost, st));
-    CUDA_TRY(cudaStreamSynchronize(st));
-    if (h != 0) {
-        cudaMemset(flag, 0, sizeof(int));
-        return nncu_fail(NNCU_ERR_TIMEOUT, "tcgen05 GEMM: a bounded wait expired (code %d)", h);
-    }
-    return NNCU_OK;
+    return gemm_flag_check(flag, st);
 }
 
 } // extern "C"

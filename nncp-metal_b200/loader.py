@@ -67,6 +67,24 @@ def build_library(force=False, verbose=False):
     return LIB
 
 
+DROPIN_DIR = os.path.join(HOST, "dropin")
+DROPIN_BIN = os.path.join(DROPIN_DIR, "_build", "nncp_b200")
+
+
+def build_dropin(reference_dir=None):
+    """Builds the reference's own `nncp` command-line tool on this backend (host/dropin/Makefile):
+    its unmodified nncp.c, compiled where it lies under `reference_dir` (default
+    $NNCP_REFERENCE_DIR), with the Transformer class re-pointed at libnncu.so.  Returns the path
+    of the binary, or None when no reference tree is available (a prebuilt binary is kept)."""
+    ref = reference_dir or os.environ.get("NNCP_REFERENCE_DIR")
+    if not ref or not os.path.isfile(os.path.join(ref, "nncp.c")) or not os.path.exists(LIB):
+        return DROPIN_BIN if os.path.exists(DROPIN_BIN) else None
+    r = subprocess.run(["make", "-C", DROPIN_DIR, "all", f"REF={ref}"], capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError("drop-in build failed:\n" + r.stdout + r.stderr)
+    return DROPIN_BIN if os.path.exists(DROPIN_BIN) else None
+
+
 _lib = None
 
 

@@ -13,14 +13,27 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 _vp, _i, _sz = C.c_void_p, C.c_int, C.c_size_t
 
 
+def reference_dir():
+    """Directory of the reference project's sources, or None: $NNCP_REFERENCE_DIR, else the
+    `reference_path` the repository's BASELINE.json records, when that directory exists."""
+    import json
+    cand = os.environ.get("NNCP_REFERENCE_DIR")
+    if not cand:
+        try:
+            cand = json.load(open(os.path.join(os.path.dirname(HERE), "BASELINE.json"))).get("reference_path")
+        except (OSError, ValueError):
+            cand = None
+    return cand if cand and os.path.isfile(os.path.join(cand, "arith.c")) else None
+
+
 def build(force=False):
     """Compiles liboracle.so (and _ref/ when the reference tree is present)."""
     so = os.path.join(HERE, "liboracle.so")
     srcs = [os.path.join(HERE, f) for f in ("trf_oracle.c", "coder_oracle.c")]
     stale = (not os.path.exists(so)) or any(os.path.getmtime(s) > os.path.getmtime(so) for s in srcs)
-    if force or stale or (os.path.exists("/root/reference/arith.c") and
-                          not os.path.exists(os.path.join(HERE, "_ref", "libref_coder.so"))):
-        subprocess.run(["make", "-C", HERE, "all"], check=True, capture_output=True)
+    ref = reference_dir()
+    if force or stale or (ref and not os.path.exists(os.path.join(HERE, "_ref", "libref_coder.so"))):
+        subprocess.run(["make", "-C", HERE, "all", f"REF={ref or ''}"], check=True, capture_output=True)
     return so
 
 
@@ -73,6 +86,9 @@ def lib():
         L.orc_dec_free.argtypes = [_vp]
         L.orc_dec_free.restype = None
         L.orc_sym_path.argtypes = [_vp, _i, _i, _vp]
+        L.orc_set_threads.argtypes = [_i]
+        L.orc_set_threads.restype = _i
+        L.orc_get_threads.restype = _i
         _lib = L
     return _lib
 

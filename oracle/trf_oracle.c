@@ -595,6 +595,24 @@ float *orc_probs(orc_model *m) { return m->probs; }
 /* memory of layer l: [M*B][D] */
 float *orc_mem(orc_model *m, int l) { return m->layers[l].hcat; }
 
+/* OpenMP team size of the oracle's loops.  orc_set_threads(n > 0) fixes it for later calls
+ * whatever OMP_NUM_THREADS said when the library was loaded (a launcher such as
+ * torch.distributed.run exports OMP_NUM_THREADS=1 to its children); both return the size in
+ * force. */
+#ifdef _OPENMP
+#include <omp.h>
+int orc_set_threads(int n)
+{
+    if (n > 0)
+        omp_set_num_threads(n);
+    return omp_get_max_threads();
+}
+int orc_get_threads(void) { return omp_get_max_threads(); }
+#else
+int orc_set_threads(int n) { (void)n; return 1; }
+int orc_get_threads(void) { return 1; }
+#endif
+
 void orc_reset(orc_model *m)
 {
     for (int l = 0; l < m->p.n_layer; l++)

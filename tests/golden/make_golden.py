@@ -13,6 +13,12 @@ Each file holds, for a two-step run of one small configuration:
   g<s>/<name>        gradients of -loss/(T*B) at step s
   p<s+1>/<name>      parameters after the update of step s
   mem<s+1>           [n_layer, M, B, D] memory after step s
+
+Digest goldens (dig_*.npz) cover the BASELINE geometries, whose tensors are too large to store:
+the parameters are rebuilt from a seed (seeded_params.py) and the file keeps the loss, the
+probabilities of sampled columns plus the target column, and a strided subsample of every
+gradient and updated parameter (with each gradient's max-abs as the error scale).
+  python tests/golden/make_golden.py digest
 """
 import json
 import os
@@ -106,8 +112,69 @@ def make(name, over, out_dir):
     print(f"{path}: {os.path.getsize(path)} bytes, loss {losses}")
 
 
+# BASELINE.json geometries (config[0] exactly; config[2]'s widths with one layer and four streams)
+DIGESTS = {
+    "c0": dict(n_layer=2, d_model=128, n_head=4, d_key=32, d_inner=512, d_pos=64, mem_len=32, seg_len=32,
+               n_streams=4, n_symbols=256, lr=3e-4, wscale=0.09, param_seed=1001, steps=2),
+    "c2_geometry": dict(n_layer=1, d_model=512, n_head=8, d_key=64, d_inner=2048, d_pos=128, mem_len=64,
+                        seg_len=64, n_streams=4, n_symbols=16384, lr=3e-4, wscale=0.044, param_seed=1002,
+                        steps=2),
+}
+N_COLS = 48
+
+
+def make_digest(name, over, out_dir):
+    sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))))
+    from oracle import oracle as orc
+    import seeded_params as sp
+    c = dict(BASE)
+    c.update(over)
+    steps = c.pop("steps")
+    c["d_value"] = c["d_key"]
+    shapes = tt.param_shapes(c)
+    p32 = sp.seeded_params(orc, shapes, c["param_seed"], c["wscale"])
+    params = {k: torch.from_numpy(v).double() for k, v in p32.items()}
+    moments = {k: torch.zeros_like(v) for k, v in params.items()}
+    T, B, V = c["seg_len"], c["n_streams"], c["n_symbols"]
+    gen = torch.Generator().manual_seed(c["param_seed"])
+    ids = torch.randint(0, V, (steps, T, B), generator=gen)
+    targets = torch.randint(0, V, (steps, T, B), generator=gen)
+    cols = torch.randperm(V, generator=gen)[:N_COLS].sort().values
+    mem = [torch.zeros(c["mem_len"], B, c["d_model"], dtype=torch.float64) for _ in range(c["n_layer"])]
+    out = {"cfg_json": np.array(json.dumps(c)), "ids": ids.numpy().astype(np.int32),
+           "targets": targets.numpy().astype(np.int32), "prob_cols": cols.numpy().astype(np.int32)}
+    losses, ps, pt, pmax = [], [], [], []
+    for s in range(steps):
+        r = tt.train_step(params, moments, c, ids[s], targets[s], mem, c["lr"])
+        mem = r["mem"]
+        losses.append(r["loss"])
+        ps.append(r["probs"][..., cols].numpy().astype(np.float32))
+        pt.append(torch.gather(r["probs"], 2, targets[s].unsqueeze(-1)).squeeze(-1).numpy().astype(np.float32))
+        pmax.append(r["probs"].max(-1).values.numpy().astype(np.float32))
+        for k in params:
+            g = r["grads"][k].numpy()
+            stride, sub = sp.subsample(g)
+            out[f"stride/{k}"] = np.array(stride, np.int64)
+            out[f"g{s}/{k}"] = sub.astype(np.float32)
+            out[f"gmax{s}/{k}"] = np.array(np.abs(g).max(), np.float32)
+            out[f"p{s+1}/{k}"] = sp.subsample(params[k].detach().numpy())[1].astype(np.float32)
+        # later steps start from the stored-precision state the tests can rebuild: keep going in
+        # float64 here; the tests re-synchronise their weights only through these subsamples
+    out["probs_sample"] = np.stack(ps)
+    out["probs_target"] = np.stack(pt)
+    out["probs_rowmax"] = np.stack(pmax)
+    out["loss"] = np.array(losses, dtype=np.float64)
+    path = os.path.join(out_dir, f"dig_{name}.npz")
+    np.savez_compressed(path, **out)
+    print(f"{path}: {os.path.getsize(path)} bytes, loss {losses}")
+
+
 if __name__ == "__main__":
     torch.manual_seed(0)
     d = os.path.dirname(os.path.abspath(__file__))
-    for n, o in CONFIGS.items():
-        make(n, o, d)
+    if len(sys.argv) > 1 and sys.argv[1] == "digest":
+        for n, o in DIGESTS.items():
+            make_digest(n, o, d)
+    else:
+        for n, o in CONFIGS.items():
+            make(n, o, d)

@@ -52,6 +52,21 @@ def test_invalid_options_are_rejected_before_any_device_work(pkg):
         assert not h.value
 
 
+def test_shapes_no_attention_kernel_can_run_are_refused_at_create(pkg):
+    """An fp32 model with several hundred keys per row, or a bf16 model with more than 64 queries
+    per segment and a long memory, exceeds the shared memory of every attention kernel pair:
+    nncu_create says so (NNCU_ERR_RANGE), instead of the first nncu_eval_gradient failing after the
+    encoder has already coded a segment."""
+    lib = pkg.library()
+    for over in (dict(use_bf16=0, mem_len=1024, seg_len=64, d_pos=64),
+                 dict(use_bf16=1, mem_len=2048, seg_len=128, d_pos=128, d_key=64)):
+        p = pkg.abi.make_params(**over)
+        h = C.c_void_p()
+        assert lib.nncu_create(C.byref(p), C.byref(h)) == pkg.abi.ERR_RANGE, over
+        assert b"shared memory" in lib.nncu_last_error()
+        assert not h.value
+
+
 def test_no_device_means_error_not_fallback(pkg):
     import torch
     if torch.cuda.is_available():

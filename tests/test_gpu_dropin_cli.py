@@ -1,5 +1,5 @@
-"""The reference's own command-line compressor (nncp.c, unmodified, built by oracle/Makefile's
-`dropin` target with its Transformer class re-pointed at libnncu.so) on the GPU: compress and
+"""The reference's own command-line compressor (nncp.c, unmodified, built by
+nncp-metal_b200/host/dropin/Makefile with its Transformer class re-pointed at libnncu.so) on the GPU: compress and
 decompress round-trip through the reference's encode_file / decode_file / process_block, and
 the file it writes is byte-identical to what this repository's host code (nch_compress, the
 restatement of those functions) writes for the same parameters."""
@@ -11,7 +11,7 @@ import pytest
 
 from conftest import ROOT
 
-BIN = os.path.join(ROOT, "oracle", "_ref", "nncp_b200")
+BIN = os.path.join(ROOT, "nncp-metal_b200", "host", "dropin", "_build", "nncp_b200")
 OPTS = ["--cuda", "-q", "--n_layer", "2", "--d_model", "64", "--n_head", "2", "--d_inner", "128",
         "--batch_size", "4", "--train_len", "16", "--mem_len", "16", "--d_pos", "16"]
 
@@ -24,7 +24,7 @@ def _text(n, seed):
 
 
 @pytest.mark.gpu
-@pytest.mark.skipif(not os.path.exists(BIN), reason="oracle/_ref/nncp_b200 was never built")
+@pytest.mark.skipif(not os.path.exists(BIN), reason="host/dropin/_build/nncp_b200 was never built")
 @pytest.mark.parametrize("bf16", [0, 1])
 def test_reference_cli_round_trip_and_same_file_as_host_code(pkg, tmp_path, bf16):
     data = _text(6000, 3)
@@ -51,7 +51,7 @@ def test_reference_cli_round_trip_and_same_file_as_host_code(pkg, tmp_path, bf16
     assert mine == blob
 
 
-@pytest.mark.skipif(not os.path.exists(BIN), reason="oracle/_ref/nncp_b200 was never built")
+@pytest.mark.skipif(not os.path.exists(BIN), reason="host/dropin/_build/nncp_b200 was never built")
 def test_reference_cli_fails_loudly_without_a_gpu(tmp_path):
     import torch
     if torch.cuda.is_available():

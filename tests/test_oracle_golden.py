@@ -6,7 +6,8 @@ fp32, so 2e-4 relative (max-abs-diff over max-abs-ref) covers fp32 accumulation 
 import numpy as np
 import pytest
 
-from conftest import GOLDEN_NAMES, check_updated_weights, load_golden, params_from_cfg, rel_err
+from conftest import (DIGEST_NAMES, GOLDEN_NAMES, check_digest_step, check_updated_weights, load_digest,
+                      load_golden, params_from_cfg, rel_err)
 
 TOL = 2e-4
 
@@ -46,6 +47,33 @@ def test_oracle_two_steps(pkg, oracle, name):
         # from step-1 rounding differences
         for pname in m.info:
             m.set_param(pname, z[f"p{s+1}/{pname}"])
+    m.close()
+
+
+@pytest.mark.parametrize("name", DIGEST_NAMES)
+def test_oracle_at_baseline_geometries(pkg, oracle, name):
+    """BASELINE config[0] exactly and config[2]'s widths (d_model 512, 8 x 64 heads, d_ff 2048,
+    vocab 16384, seg 64, mem 64): the oracle against float64 digests of the PyTorch restatement.
+    The second step continues from the oracle's own updated weights, so it also checks the update."""
+    cfg, z, params = load_digest(name)
+    m = oracle.OracleModel(params_from_cfg(pkg, cfg))
+    for pname in m.info:
+        m.set_param(pname, params[pname])
+    m.reset()
+    m.set_lr(cfg["lr"])
+    for s in range(z["ids"].shape[0]):
+        probs = m.eval(-1, z["ids"][s])
+        loss = m.eval_gradient(z["targets"][s])
+        # step 2 starts from fp32 weights whose least-determined elements moved by one RMSProp
+        # step of either sign: twice the tolerance there
+        k = 1 if s == 0 else 2
+        check_digest_step(m, z, s, k * TOL, k * 5e-4, probs, loss)
+        m.update()
+        for pname in m.info:
+            stride = int(z[f"stride/{pname}"])
+            w, w_ref = m.get_param(pname)[::stride], z[f"p{s+1}/{pname}"]
+            bound = k * TOL * max(np.abs(w_ref).max(), 1e-3) + 2.1 * cfg["lr"] / np.sqrt(1 - cfg["beta2"])
+            assert np.abs(w - w_ref).max() < bound, (pname, s)
     m.close()
 
 
