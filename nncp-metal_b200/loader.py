@@ -12,6 +12,7 @@ CSRC = os.path.join(PKG, "csrc")
 HOST = os.path.join(PKG, "host")
 LIB = os.path.join(PKG, "libnncu.so")
 HOSTLIB = os.path.join(PKG, "libnncp_host.so")
+CLI = os.path.join(PKG, "nncp-metal")   # the command-line tool (host/cli/nncp_metal_main.c)
 
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-ccbin", "/usr/bin/g++", "-Xcompiler", "-fPIC,-O2", "-shared"]
@@ -58,9 +59,17 @@ def build_library(force=False, verbose=False):
             print(r.stderr)
     hc = _sources(HOST, (".c",)) if os.path.isdir(HOST) else []
     if hc and (force or _stale(HOSTLIB, hc + _sources(HOST, (".h",)) +
-                               [os.path.join(ROOT, "include", "nncp_host.h")])):
+                               [os.path.join(ROOT, "include", "nncp_host.h"),
+                                os.path.join(ROOT, "include", "nncp_metal_frontend.h")])):
         cmd = ["gcc", "-O2", "-fPIC", "-shared", "-Wall", "-I", os.path.join(ROOT, "include"),
                "-I", HOST, "-o", HOSTLIB] + hc + ["-lm", "-ldl"]
+        r = subprocess.run(cmd, capture_output=True, text=True)
+        if r.returncode != 0:
+            raise RuntimeError("gcc failed:\n" + r.stdout + r.stderr)
+    cli_src = os.path.join(HOST, "cli", "nncp_metal_main.c")
+    if os.path.exists(cli_src) and (force or _stale(CLI, [cli_src, HOSTLIB])):
+        cmd = ["gcc", "-O2", "-Wall", "-I", os.path.join(ROOT, "include"), "-o", CLI, cli_src,
+               "-L", PKG, "-l:libnncp_host.so", "-Wl,-rpath,$ORIGIN"]
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode != 0:
             raise RuntimeError("gcc failed:\n" + r.stdout + r.stderr)
