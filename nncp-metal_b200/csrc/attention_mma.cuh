@@ -27,6 +27,7 @@
 // in order).  All sums have a fixed order; the caller reduces the partials over streams.
 #pragma once
 #include "attention.cuh"
+#include "attention_tc.cuh"
 
 namespace amma {
 
@@ -884,12 +885,15 @@ static bool attn_force_simt()
 template <typename T>
 static int attn_forward_any(const nncu_attn_shape *s, const void *q, const void *kv, const float *w_r,
                             const float *b_r, void *out, float *lse, cudaStream_t st,
-                            const AttnPitch *pt = nullptr, const void *w_r16 = nullptr)
+                            const AttnPitch *pt = nullptr, const void *w_r16 = nullptr, int *err_flag = nullptr)
 {
     if (sizeof(T) == 2 && !attn_force_simt()) {
         AttnArgs a = attn_args(s, pt);
         a.q = q; a.kv = kv; a.w_r = w_r; a.b_r = b_r; a.o = out; a.lse = lse;
         a.w_r16 = w_r ? w_r16 : nullptr;
+        // d_head 64: tcgen05 / TMEM / TMA kernel (the choice depends on the shape only)
+        if (attc::enabled() && attc::supported(a, q, kv, a.w_r16))
+            return attc::forward_any(a, a.w_r16, err_flag, st);
         if (amma::supported(a, false))
             return amma::forward(a, st);
     }
@@ -900,7 +904,7 @@ template <typename T>
 static int attn_backward_any(const nncu_attn_shape *s, const void *q, const void *kv, const float *w_r,
                              const float *b_r, const void *out, const float *lse, const void *dout,
                              void *dq, void *dkv, float *dwr_part, float *dbr_part, cudaStream_t st,
-                             const AttnPitch *pt = nullptr, const void *w_r16 = nullptr)
+                             const AttnPitch *pt = nullptr, const void *w_r16 = nullptr, int *err_flag = nullptr)
 {
     if (sizeof(T) == 2 && !attn_force_simt()) {
         AttnArgs a = attn_args(s, pt);
@@ -908,6 +912,8 @@ static int attn_backward_any(const nncu_attn_shape *s, const void *q, const void
         if (a.t0 == 0 && a.t1 == a.T) {
             a.q = q; a.kv = kv; a.w_r = w_r; a.b_r = b_r; a.out = out; a.lse = const_cast<float *>(lse);
             a.dout = dout; a.dq = dq; a.dkv = dkv; a.dwr_part = dwr_part; a.dbr_part = dbr_part;
+            if (attc::enabled() && attc::bwd_enabled() && attc::supported_bwd(a, a.w_r16))
+                return attc::backward_any(a, a.w_r16, err_flag, st);
             if (amma::supported(a, true))
                 return amma::backward(a, st);
         }

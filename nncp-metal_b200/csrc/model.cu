@@ -528,7 +528,7 @@ static int forward_range(nncu_model *m, int t0, int t1)
         const AttnPitch pt = {3 * HD, 3 * HD, 3 * HD, 3 * HD};
         NNCU_TRY(attn_forward_any<AT>(&s, at<AT>(a.qkv, (size_t)M * B * 3 * HD), at<AT>(a.qkv, HD),
                                       wf(m, o.w_r), m->W + o.b_r, a.o, a.lse, m->st, &pt,
-                                      (m->bf && o.w_r != NONE) ? m->Wb + o.w_r : nullptr));
+                                      (m->bf && o.w_r != NONE) ? m->Wb + o.w_r : nullptr, m->err_flag));
         // output projection, residual, post-LN (nncp.c:865-920)
         NNCU_TRY((mm_nt<AT, AT>(m, nr, D, HD, at<AT>(a.o, (size_t)r0 * HD), HD, o.w_o, tmp, D, nullptr)));
         AT *yy = at<AT>(a.y, (size_t)r0 * D);
@@ -714,7 +714,7 @@ static int backward(nncu_model *m)
         nncu_attn_shape s = attn_shape(m, l, 0, m->T);
         NNCU_TRY(attn_backward_any<AT>(&s, at<AT>(a.qkv, (size_t)M * B * 3 * HD), at<AT>(a.qkv, HD), wf(m, o.w_r),
                                        m->W + o.b_r, a.o, a.lse, dof, dq, dkv, m->dwr_part, m->dbr_part, m->st,
-                                       &pt, (m->bf && o.w_r != NONE) ? m->Wb + o.w_r : nullptr));
+                                       &pt, (m->bf && o.w_r != NONE) ? m->Wb + o.w_r : nullptr, m->err_flag));
         {
             // on the side stream: the partials are next written after the join at the layer's end
             cudaStream_t s2 = side_fork(m);
@@ -1878,6 +1878,7 @@ static int gemm_flag_check(int *flag, cudaStream_t st)
 extern "C" int nncu_attn_trace(long long *dev_buf)
 {
     CUDA_TRY(cudaMemcpyToSymbol(amma::g_attn_trace, &dev_buf, sizeof(dev_buf)));
+    CUDA_TRY(cudaMemcpyToSymbol(attc::g_trace, &dev_buf, sizeof(dev_buf)));
     return NNCU_OK;
 }
 #endif

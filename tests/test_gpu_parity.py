@@ -174,7 +174,12 @@ def test_attention_op_config1_bf16(pkg, oracle):
                                                # shorter than the keys, and wide heads over several key tiles
                                                (2, 2, 64, 64, 256, 320, 0), (1, 2, 64, 64, 512, 576, 0),
                                                (2, 1, 32, 40, 300, 200, 150), (1, 2, 64, 64, 448, 64, 0),
-                                               (1, 2, 128, 48, 150, 198, 0), (1, 1, 16, 64, 200, 40, 100)])
+                                               (1, 2, 128, 48, 150, 198, 0), (1, 1, 16, 64, 200, 40, 100),
+                                               # d_head 64 (the tcgen05 kernels): an attention window over
+                                               # three key blocks, fewer than 64 queries with an odd stream
+                                               # count, and a table far shorter than the memory
+                                               (2, 2, 64, 64, 256, 320, 150), (3, 2, 64, 40, 100, 90, 0),
+                                               (4, 1, 64, 64, 300, 20, 0)])
 def test_attention_op_tensor_core_shapes_bf16(pkg, oracle, B, H, dk, T, M, P, alen):
     _attn_case(pkg, oracle, B, H, dk, T, M, P, alen, True, 3)
 
