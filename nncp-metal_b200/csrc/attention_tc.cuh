@@ -26,9 +26,11 @@
 // and on the sequence of key blocks, and a key block in which the row sees nothing leaves its
 // running maximum, sum and output unchanged bit for bit.
 //
-// Roles (192 threads): warp 0 lane 0 issues the TMA loads, warp 1 lane 0 the MMAs (warp 1 also
-// owns the TMEM allocation), warps 2-5 are the 128 row threads.  Every wait is bounded; on
-// expiry the kernel raises *err_flag and leaves through the common exit that frees TMEM.
+// Roles (320 threads): warp 0 lane 0 issues the TMA loads, warp 1 lane 0 the MMAs (warp 1 also
+// owns the TMEM allocation), warps 2-9 are 256 row threads: two per row (a warp reaches the TMEM
+// lanes 32 * (warp % 4) .. +31, so warps w and w + 4 share rows), each taking two of the four
+// 32-key chunks of a block and half of the output columns.  Every wait is bounded; on expiry the
+// kernel raises *err_flag and leaves through the common exit that frees TMEM.
 #pragma once
 #include "attention.cuh"
 #include "gemm_tc.cuh"
@@ -136,6 +138,51 @@ __host__ __device__ constexpr uint32_t idesc_of(int n, bool a_mn, bool b_mn)
            ((uint32_t)(n >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
 }
 
+constexpr int NROW = 256;          // row threads
+constexpr int BRS_PAD = 64;        // b_r staging starts at index -64 ...
+constexpr int BRS_LEN = MAXL + 256; // ... and runs past the last slot a masked pair can name
+
+// Masked scores (log2 domain) of the 32 keys [jc, jc + 32) for one row, in place over the S chunk.
+// x: the skewed E chunk (barrel_skew done); e0: E of table row 0 (left pad); kclamp: keys k < kclamp
+// of the chunk fall on the pad; [klo, khi]: visible keys of the chunk; brp[k]: the scaled b_r term.
+// Warp-uniform shortcuts: no lane on the pad, every lane seeing the whole chunk.
+__device__ __forceinline__ void score_chunk(uint32_t (&sv)[32], const uint32_t (&x)[64], bool has_wr, bool clampable,
+                                            float e0, int kclamp, int klo, int khi, const float *brp, float sc2)
+{
+    const bool any_pad = clampable && __any_sync(0xffffffffu, kclamp > 0);
+    const bool all_vis = __all_sync(0xffffffffu, klo <= 0 && khi >= 31);
+    if (has_wr) {
+        if (any_pad) {
+#pragma unroll
+            for (int k = 0; k < 32; k++)
+                sv[k] = __float_as_uint(__uint_as_float(sv[k]) + (k < kclamp ? e0 : __uint_as_float(x[k])));
+        } else {
+#pragma unroll
+            for (int k = 0; k < 32; k++)
+                sv[k] = __float_as_uint(__uint_as_float(sv[k]) + __uint_as_float(x[k]));
+        }
+    }
+    if (all_vis) {
+#pragma unroll
+        for (int k = 0; k < 32; k++)
+            sv[k] = __float_as_uint(fmaf(__uint_as_float(sv[k]), sc2, brp[k]));
+    } else {
+#pragma unroll
+        for (int k = 0; k < 32; k++) {
+            const float v = fmaf(__uint_as_float(sv[k]), sc2, brp[k]);
+            sv[k] = __float_as_uint((k >= klo && k <= khi) ? v : -INFINITY);
+        }
+    }
+}
+
+__device__ __forceinline__ uint4 pack8(const uint32_t *r)
+{
+    return make_uint4(tc::pack_bf16(__uint_as_float(r[0]), __uint_as_float(r[1])),
+                      tc::pack_bf16(__uint_as_float(r[2]), __uint_as_float(r[3])),
+                      tc::pack_bf16(__uint_as_float(r[4]), __uint_as_float(r[5])),
+                      tc::pack_bf16(__uint_as_float(r[6]), __uint_as_float(r[7])));
+}
+
 // shared-memory map of the forward kernel (bytes from the 1024-aligned base)
 struct FwdSmem {
     static constexpr int Q = 0;                   // [128][64] bf16: stream b0 rows, then b0 + 1
@@ -143,8 +190,9 @@ struct FwdSmem {
     static constexpr int V = K + 256 * 128;       // [256][64]
     static constexpr int R = V + 256 * 128;       // [192][64] table window
     static constexpr int P = R + WIN * 128;       // two K-major atoms [128][64] (keys 0-63, 64-127)
-    static constexpr int BRS = P + 2 * 128 * 128; // MAXL floats: br_scale * b_r[h][.]
-    static constexpr int BAR = BRS + MAXL * 4;    // mbarriers, TMEM slot, abort flag
+    static constexpr int BRS = P + 2 * 128 * 128; // BRS_LEN floats: scaled b_r[h][.], index + BRS_PAD
+    static constexpr int XCH = BRS + BRS_LEN * 4; // [4][128] floats: what the two threads of a row exchange
+    static constexpr int BAR = XCH + 4 * 128 * 4; // mbarriers, TMEM slot, abort flag
     static constexpr int TOTAL = BAR + 128 + 1024; // + alignment slack
 };
 
@@ -163,7 +211,7 @@ __host__ __device__ inline KeyBlocks key_blocks(int M, int L, int attn_len, int 
     return kb;
 }
 
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(320, 1)
 attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kv,
                    const __grid_constant__ CUtensorMap map_wr, AttnArgs a, int has_wr, int *err_flag)
 {
@@ -175,6 +223,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 6);
     volatile int *abort_s = reinterpret_cast<volatile int *>(tmem_slot + 1);
     float *brs = reinterpret_cast<float *>(sm + FwdSmem::BRS);
+    float *xch = reinterpret_cast<float *>(sm + FwdSmem::XCH);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int b0 = blockIdx.x * 2, h = blockIdx.y;
@@ -193,9 +242,9 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         mbar_init(smem_u32(&bars[0]), 1);
         mbar_init(smem_u32(&bars[1]), 1);
         mbar_init(smem_u32(&bars[2]), 1);
-        mbar_init(smem_u32(&bars[3]), 128);
+        mbar_init(smem_u32(&bars[3]), NROW);
         mbar_init(smem_u32(&bars[4]), 1);
-        mbar_init(smem_u32(&bars[5]), 128);
+        mbar_init(smem_u32(&bars[5]), NROW);
         *abort_s = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -230,10 +279,10 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                 }
                 tma_load_3d(sm0 + FwdSmem::K, &map_kv, bar_load, h * DK, b0, j0);
                 tma_load_3d(sm0 + FwdSmem::K + 128 * 128, &map_kv, bar_load, h * DK, b0 + 1, j0);
-                tma_load_3d(sm0 + FwdSmem::V, &map_kv, bar_load, HD + h * DK, b0, j0);
-                tma_load_3d(sm0 + FwdSmem::V + 128 * 128, &map_kv, bar_load, HD + h * DK, b0 + 1, j0);
                 if (has_wr)
                     tma_load_3d(sm0 + FwdSmem::R, &map_wr, bar_load, 0, wrow, h);
+                tma_load_3d(sm0 + FwdSmem::V, &map_kv, bar_load, HD + h * DK, b0, j0);
+                tma_load_3d(sm0 + FwdSmem::V + 128 * 128, &map_kv, bar_load, HD + h * DK, b0 + 1, j0);
             }
         }
     } else if (warp == 1) {
@@ -279,19 +328,23 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             }
         }
     } else {
-        // row threads: TMEM lane = 32 * (warp % 4) + lane
-        const int quarter = warp & 3;
+        // row threads: TMEM lane = 32 * (warp % 4) + lane; `half` picks the chunks and output columns
+        const int quarter = warp & 3, half = (warp - 2) >> 2;
         const int row = quarter * 32 + lane, s = row >> 6, i = row & 63, i_base = i - lane;
         const int b = b0 + s;
+        const int tid = threadIdx.x - 64;
         const uint32_t trow = tmem + ((uint32_t)(quarter * 32) << 16);
-        for (int r = threadIdx.x - 64; r < L; r += 128)
-            brs[r] = a.br_scale * a.b_r[(size_t)h * L + r];
-        asm volatile("bar.sync 1, 128;" ::: "memory");
         const float sc2 = a.inv_sqrt * 1.4426950408889634f; // scores in the log2 domain
+        const int brs_n = min(BRS_LEN, BRS_PAD + (kbs.hi + 1) * KB + 64);
+        for (int r = tid; r < brs_n; r += NROW) {
+            const int rr = r - BRS_PAD;
+            brs[r] = (rr >= 0 && rr < L) ? a.br_scale * a.b_r[(size_t)h * L + rr] * sc2 : 0.0f;
+        }
+        asm volatile("bar.sync 1, 256;" ::: "memory");
         float m_run = -INFINITY, l_run = 0.0f;
-        float o[64];
+        float o[32];
 #pragma unroll
-        for (int k = 0; k < 64; k++)
+        for (int k = 0; k < 32; k++)
             o[k] = 0.0f;
         bool ok = true;
         int it = 0;
@@ -313,10 +366,11 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                 e0 = __uint_as_float(tmem_ld1(trow + 256 + (all_clamp ? 0 : -wlo)));
                 tmem_ld_wait();
             }
-            // ---- pass 1: masked, scaled scores back into the S columns; block maximum
+            // ---- pass 1: masked, scaled scores back into the S columns; maximum of this half
             float m_blk = -INFINITY;
 #pragma unroll 1
-            for (int c = 0; c < 4; c++) {
+            for (int cc = 0; cc < 2; cc++) {
+                const int c = half * 2 + cc;
                 uint32_t sv[32], x[64];
                 tmem_ld32(trow + s * 128 + c * 32, sv);
                 if (has_wr && !all_clamp) {
@@ -328,27 +382,17 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                 if (has_wr && !all_clamp)
                     barrel_skew(x, lane);
                 const int jc = j0 + c * 32;
+                score_chunk(sv, x, has_wr, clampable, e0, all_clamp ? 32 : i - c0 - jc,
+                            i + M - a.attn_len + 1 - jc, i + M - jc, brs + BRS_PAD + jc + (T - 1) - i, sc2);
 #pragma unroll
-                for (int k = 0; k < 32; k++) {
-                    const int j = jc + k;
-                    const int d = i + M - j;
-                    float e = 0.0f;
-                    if (has_wr) {
-                        e = all_clamp ? e0 : __uint_as_float(x[k]);
-                        if (clampable && (j - i + c0 < 0))
-                            e = e0;
-                    }
-                    int r = j + (T - 1) - i;
-                    r = r < L ? r : L - 1;
-                    r = r < 0 ? 0 : r;
-                    float v = (__uint_as_float(sv[k]) + e + brs[r]) * sc2;
-                    v = (d >= 0 && d < a.attn_len) ? v : -INFINITY;
-                    m_blk = fmaxf(m_blk, v);
-                    sv[k] = __float_as_uint(v);
-                }
+                for (int k = 0; k < 32; k++)
+                    m_blk = fmaxf(m_blk, __uint_as_float(sv[k]));
                 tmem_st32(trow + s * 128 + c * 32, sv);
             }
+            xch[half * 128 + row] = m_blk;
             tmem_st_wait();
+            asm volatile("bar.sync 1, 256;" ::: "memory");
+            m_blk = fmaxf(m_blk, xch[(half ^ 1) * 128 + row]);
             if (it == 0 && threadIdx.x == 64) ATC_STAMP(7);
             // ---- pass 2: probabilities (bf16, K-major atoms in shared memory), running sum
             const float m_new = fmaxf(m_run, m_blk);
@@ -356,26 +400,21 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             const float alpha = ex2(m_run - m_use);
             float sum = 0.0f;
 #pragma unroll 1
-            for (int c = 0; c < 4; c++) {
+            for (int cc = 0; cc < 2; cc++) {
+                const int c = half * 2 + cc;
                 uint32_t sv[32];
                 tmem_ld32(trow + s * 128 + c * 32, sv);
                 tmem_ld_wait();
                 unsigned char *prow = sm + FwdSmem::P + (c >> 1) * 128 * 128 + row * 128;
 #pragma unroll
-                for (int v4 = 0; v4 < 4; v4++) {
-                    float p[8];
-#pragma unroll
-                    for (int u = 0; u < 8; u++) {
-                        p[u] = ex2(__uint_as_float(sv[v4 * 8 + u]) - m_use);
-                        sum += p[u];
-                    }
-                    uint4 pk;
-                    pk.x = tc::pack_bf16(p[0], p[1]);
-                    pk.y = tc::pack_bf16(p[2], p[3]);
-                    pk.z = tc::pack_bf16(p[4], p[5]);
-                    pk.w = tc::pack_bf16(p[6], p[7]);
-                    *reinterpret_cast<uint4 *>(prow + ((((c & 1) * 4 + v4) ^ (row & 7)) << 4)) = pk;
+                for (int k = 0; k < 32; k++) {
+                    const float p = ex2(__uint_as_float(sv[k]) - m_use);
+                    sum += p;
+                    sv[k] = __float_as_uint(p);
                 }
+#pragma unroll
+                for (int v4 = 0; v4 < 4; v4++)
+                    *reinterpret_cast<uint4 *>(prow + ((((c & 1) * 4 + v4) ^ (row & 7)) << 4)) = pack8(sv + v4 * 8);
             }
             l_run = l_run * alpha + sum;
             m_run = m_new;
@@ -383,7 +422,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             fence_before_sync();
             mbar_arrive(bar_p);
             if (it == 0 && threadIdx.x == 64) ATC_STAMP(8);
-            // ---- O block of this row's stream
+            // ---- O block of this row's stream: this thread's 32 output columns
             if (lane == 0)
                 ok = mbar_wait(bar_o, (uint32_t)(it & 1), abort_s, err_flag, 16);
             ok = __all_sync(0xffffffffu, ok);
@@ -392,30 +431,33 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             fence_after_sync();
             if (it == 0 && threadIdx.x == 64) ATC_STAMP(9);
             {
-                uint32_t y[64];
-                tmem_ld32(trow + s * 64, y);
-                tmem_ld32(trow + s * 64 + 32, y + 32);
+                uint32_t y[32];
+                tmem_ld32(trow + s * 64 + half * 32, y);
                 tmem_ld_wait();
 #pragma unroll
-                for (int k = 0; k < 64; k++)
+                for (int k = 0; k < 32; k++)
                     o[k] = o[k] * alpha + __uint_as_float(y[k]);
             }
             fence_before_sync();
             mbar_arrive(bar_tfree);
             if (it == 0 && threadIdx.x == 64) ATC_STAMP(10);
         }
+        // the row's sum is the two halves' (same sequence of maxima on both sides)
+        xch[(2 + half) * 128 + row] = l_run;
+        asm volatile("bar.sync 1, 256;" ::: "memory");
+        const float l_tot = half == 0 ? l_run + xch[3 * 128 + row] : xch[2 * 128 + row] + l_run;
         if (ok && i >= a.t0 && i < a.t1 && i < T && b < a.B) {
-            const float inv = 1.0f / l_run;
-            bf16 *dst = reinterpret_cast<bf16 *>(a.o) + ((size_t)i * a.B + b) * HD + h * DK;
+            const float inv = 1.0f / l_tot;
+            bf16 *dst = reinterpret_cast<bf16 *>(a.o) + ((size_t)i * a.B + b) * HD + h * DK + half * 32;
 #pragma unroll
-            for (int v4 = 0; v4 < 8; v4++)
+            for (int v4 = 0; v4 < 4; v4++)
                 reinterpret_cast<uint4 *>(dst)[v4] =
                     make_uint4(tc::pack_bf16(o[v4 * 8] * inv, o[v4 * 8 + 1] * inv),
                                tc::pack_bf16(o[v4 * 8 + 2] * inv, o[v4 * 8 + 3] * inv),
                                tc::pack_bf16(o[v4 * 8 + 4] * inv, o[v4 * 8 + 5] * inv),
                                tc::pack_bf16(o[v4 * 8 + 6] * inv, o[v4 * 8 + 7] * inv));
-            if (a.lse)
-                a.lse[((size_t)b * a.H + h) * T + i] = (m_run + __log2f(l_run)) * 0.6931471805599453f;
+            if (a.lse && half == 0)
+                a.lse[((size_t)b * a.H + h) * T + i] = (m_run + __log2f(l_tot)) * 0.6931471805599453f;
         }
     }
     if (threadIdx.x == 64)
@@ -437,22 +479,23 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
 
 // ---------------- backward ----------------
 //
-// Same CTA shape (one head of two streams, 128 row threads) and the same score pass as the
-// forward kernel; the saved log-sum-exp gives the probabilities directly.  Per key block:
+// Same CTA shape (one head of two streams, two row threads per row) and the same score pass as
+// the forward kernel; the saved log-sum-exp gives the probabilities directly.  Per key block:
 //
 //   G1  S, E                                   as in the forward pass
-//   r1  P = exp(a - lse): bf16 to shared memory (PS), fp32 to TMEM columns 256..383
+//   r1  P = exp(a - lse), bf16, to shared memory (PS)
 //   G2  dP = dO [V_b0 ; V_b1]^T    128 x 256    -> columns   0..255
 //       dV_b = P_b^T dO_b          128 x 64     -> columns 384..511   (rows = keys)
-//   r2  dV out; dS = P (dP - D) / sqrt(dk): bf16 over P in PS, and scattered into the window
+//   r2  dV out; dS = P (dP - D) / sqrt(dk) (P as the MMAs saw it): bf16 over P in PS, and scattered into the window
 //       layout dE[row][jj + 63 - i] (the inverse of the forward skew; zero elsewhere); the
 //       entries whose table row is negative (left pad) are also summed into column 191
 //   G3  dK_b = dS_b^T Q_b  -> 0..127 (rows = keys);  dQ_b = dS K_b -> 128..255;
 //       dQ  += dE Rwin -> 256..319;  dRwin = dE^T Q -> 320..447 (rows = window rows, two
 //       128-row halves);  column sums of dE (an all-ones operand) -> 448..479
-//   r3  dK out; dQ accumulated in registers; dRwin and the column sums added into this CTA's
-//       slices of the partial table gradients (window row c is table row wlo + c; row 191 is
-//       the left pad's share of table row 0; the column sums are db_r)
+//   r3  dK out; dQ accumulated in registers; dRwin and the column sums go to this CTA's slices
+//       of the partial table gradients (window row c is table row wlo + c; row 191 is the left
+//       pad's share of table row 0; the column sums are db_r): stored when one block covers
+//       the whole table, added block after block otherwise
 //
 // Window row 191 of Rwin is loaded with table row 0 (a one-row TMA box), so that the left pad
 // costs nothing extra: the forward term of a padded entry is E[.,191], dQ gets its share
@@ -469,7 +512,8 @@ struct BwdSmem {
     static constexpr int PS = R + WIN * 128;        // P, later dS: two K-major atoms [128][64]
     static constexpr int ONES = PS + 2 * 128 * 128; // 2 KB of bf16 1.0
     static constexpr int BRS = ONES + 2048;
-    static constexpr int BAR = BRS + MAXL * 4;
+    static constexpr int XCH = BRS + BRS_LEN * 4;   // [2][128] floats
+    static constexpr int BAR = XCH + 2 * 128 * 4;
     static constexpr int TOTAL = BAR + 256 + 1024;
 };
 
@@ -484,7 +528,57 @@ __device__ __forceinline__ uint64_t desc_sw128(uint32_t addr, uint32_t lbo_bytes
     return d;
 }
 
-__global__ void __launch_bounds__(192, 1)
+// dst[0..63] (+)= y[0..63] (fp32, 16-byte accesses; all loads first, then the stores)
+// dst[0..63] (+)= TMEM row (this thread's lane, columns taddr .. taddr + 63), fp32, 16-byte
+// accesses.  The TMEM loads are warp-collective: every lane runs them, `active` lanes store.
+__device__ __forceinline__ void tmem_row_to_global(uint32_t taddr, float *dst, bool active, bool accumulate)
+{
+#pragma unroll 1
+    for (int h2 = 0; h2 < 2; h2++) {
+        uint32_t y[32];
+        tmem_ld32(taddr + 32 * h2, y);
+        tmem_ld_wait();
+        if (active) {
+            float4 *d4 = reinterpret_cast<float4 *>(dst) + 8 * h2;
+            float4 t[8];
+            if (accumulate) {
+#pragma unroll
+                for (int v4 = 0; v4 < 8; v4++)
+                    t[v4] = d4[v4];
+            }
+#pragma unroll
+            for (int v4 = 0; v4 < 8; v4++) {
+                float4 r = make_float4(__uint_as_float(y[v4 * 4]), __uint_as_float(y[v4 * 4 + 1]),
+                                       __uint_as_float(y[v4 * 4 + 2]), __uint_as_float(y[v4 * 4 + 3]));
+                if (accumulate) {
+                    r.x += t[v4].x; r.y += t[v4].y; r.z += t[v4].z; r.w += t[v4].w;
+                }
+                d4[v4] = r;
+            }
+        }
+    }
+}
+
+// dst[0..63] (bf16) = TMEM row (columns taddr .. taddr + 63); warp-collective loads, `active` lanes store
+__device__ __forceinline__ void tmem_row_to_global_bf16(uint32_t taddr, bf16 *dst, bool active)
+{
+#pragma unroll 1
+    for (int h2 = 0; h2 < 2; h2++) {
+        uint32_t y[32];
+        tmem_ld32(taddr + 32 * h2, y);
+        tmem_ld_wait();
+        if (active) {
+            uint4 *d4 = reinterpret_cast<uint4 *>(dst) + 4 * h2;
+#pragma unroll
+            for (int v4 = 0; v4 < 4; v4++)
+                d4[v4] = pack8(y + v4 * 8);
+        }
+    }
+}
+
+// SINGLE: the queries see one key block only, so dQ needs no accumulator across blocks
+template <bool SINGLE>
+__global__ void __launch_bounds__(320, 1)
 attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_do,
                    const __grid_constant__ CUtensorMap map_kv, const __grid_constant__ CUtensorMap map_wr,
                    const __grid_constant__ CUtensorMap map_wr0, AttnArgs a, int has_wr, int *err_flag)
@@ -492,15 +586,21 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     extern __shared__ unsigned char smraw_[];
     unsigned char *sm = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smraw_) + 1023) & ~(uintptr_t)1023);
     uint64_t *bars = reinterpret_cast<uint64_t *>(sm + BwdSmem::BAR);
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 8);
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 10);
     volatile int *abort_s = reinterpret_cast<volatile int *>(tmem_slot + 1);
     float *brs = reinterpret_cast<float *>(sm + BwdSmem::BRS);
+    float *xch = reinterpret_cast<float *>(sm + BwdSmem::XCH);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int b0 = blockIdx.x * 2, h = blockIdx.y;
     const int T = a.T, M = a.M, L = a.L, P = a.P, HD = a.H * DK;
     const KeyBlocks kbs = key_blocks(M, L, a.attn_len, 0, T);
     const int c0 = P - M - 1;
+    // one key block whose window covers the whole table and every b_r slot: the table gradients
+    // are stored, not accumulated (and need no zero fill)
+    const int wlo_first = kbs.lo * KB - 63 + c0;
+    const bool direct = kbs.lo == kbs.hi && wlo_first <= 0 && wlo_first + 190 >= P - 1 &&
+                        kbs.lo * KB + T - 64 <= 0 && kbs.lo * KB + 190 + T - 64 >= L - 1;
     pdl_trigger();
     if (threadIdx.x == 0)
         ATC_STAMP(0);
@@ -509,14 +609,16 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_q)) : "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_do)) : "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_kv)) : "memory");
-        mbar_init(smem_u32(&bars[0]), 1);   // load
-        mbar_init(smem_u32(&bars[1]), 1);   // free
-        mbar_init(smem_u32(&bars[2]), 1);   // g1
-        mbar_init(smem_u32(&bars[3]), 128); // r1
-        mbar_init(smem_u32(&bars[4]), 1);   // g2
-        mbar_init(smem_u32(&bars[5]), 128); // r2
-        mbar_init(smem_u32(&bars[6]), 1);   // g3
-        mbar_init(smem_u32(&bars[7]), 128); // r3
+        mbar_init(smem_u32(&bars[0]), 1);    // load
+        mbar_init(smem_u32(&bars[1]), 1);    // free
+        mbar_init(smem_u32(&bars[2]), 1);    // g1
+        mbar_init(smem_u32(&bars[3]), NROW); // r1
+        mbar_init(smem_u32(&bars[4]), 1);    // g2
+        mbar_init(smem_u32(&bars[5]), NROW); // r2
+        mbar_init(smem_u32(&bars[6]), 1);    // g3
+        mbar_init(smem_u32(&bars[7]), NROW); // r3
+        mbar_init(smem_u32(&bars[8]), 1);    // g2b: dV
+        mbar_init(smem_u32(&bars[9]), 1);    // g3b: dQ (table part), dRwin, column sums
         *abort_s = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -536,7 +638,8 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         ATC_STAMP(1);
     const uint32_t bar_load = smem_u32(&bars[0]), bar_free = smem_u32(&bars[1]), bar_g1 = smem_u32(&bars[2]),
                    bar_r1 = smem_u32(&bars[3]), bar_g2 = smem_u32(&bars[4]), bar_r2 = smem_u32(&bars[5]),
-                   bar_g3 = smem_u32(&bars[6]), bar_r3 = smem_u32(&bars[7]);
+                   bar_g3 = smem_u32(&bars[6]), bar_r3 = smem_u32(&bars[7]), bar_g2b = smem_u32(&bars[8]),
+                   bar_g3b = smem_u32(&bars[9]);
 
     if (warp == 0) {
         if (lane == 0) {
@@ -551,23 +654,26 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                 if (it == 0) {
                     tma_load_3d(sm0 + BwdSmem::Q, &map_q, bar_load, h * DK, b0, 0);
                     tma_load_3d(sm0 + BwdSmem::Q + 64 * 128, &map_q, bar_load, h * DK, b0 + 1, 0);
-                    tma_load_3d(sm0 + BwdSmem::DO, &map_do, bar_load, h * DK, b0, 0);
-                    tma_load_3d(sm0 + BwdSmem::DO + 64 * 128, &map_do, bar_load, h * DK, b0 + 1, 0);
                 }
                 tma_load_3d(sm0 + BwdSmem::K, &map_kv, bar_load, h * DK, b0, j0);
                 tma_load_3d(sm0 + BwdSmem::K + 128 * 128, &map_kv, bar_load, h * DK, b0 + 1, j0);
-                tma_load_3d(sm0 + BwdSmem::V, &map_kv, bar_load, HD + h * DK, b0, j0);
-                tma_load_3d(sm0 + BwdSmem::V + 128 * 128, &map_kv, bar_load, HD + h * DK, b0 + 1, j0);
                 if (has_wr) {
                     tma_load_3d(sm0 + BwdSmem::R, &map_wr, bar_load, 0, wlo, h);             // 191 rows
                     tma_load_3d(sm0 + BwdSmem::R + 191 * 128, &map_wr0, bar_load, 0, 0, h); // table row 0
                 }
+                if (it == 0) {
+                    tma_load_3d(sm0 + BwdSmem::DO, &map_do, bar_load, h * DK, b0, 0);
+                    tma_load_3d(sm0 + BwdSmem::DO + 64 * 128, &map_do, bar_load, h * DK, b0 + 1, 0);
+                }
+                tma_load_3d(sm0 + BwdSmem::V, &map_kv, bar_load, HD + h * DK, b0, j0);
+                tma_load_3d(sm0 + BwdSmem::V + 128 * 128, &map_kv, bar_load, HD + h * DK, b0 + 1, j0);
             }
         }
     } else if (warp == 1) {
         if (lane == 0) {
             constexpr uint32_t idS = idesc_of(256, false, false), idE = idesc_of(WIN, false, false),
                                idMM = idesc_of(64, true, true), idKM = idesc_of(64, false, true),
+                               idKM2 = idesc_of(128, false, true),
                                idCS = idesc_of(16, true, true);
             const uint64_t dQk = desc_sw128(sm0 + BwdSmem::Q, 16), dDOk = desc_sw128(sm0 + BwdSmem::DO, 16),
                            dKk = desc_sw128(sm0 + BwdSmem::K, 16), dVk = desc_sw128(sm0 + BwdSmem::V, 16),
@@ -598,6 +704,7 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
 #pragma unroll
                 for (int k = 0; k < 4; k++)
                     umma_bf16(tmem, dDOk + 2 * k, dVk + 2 * k, idS, k > 0);
+                umma_commit(bar_g2); // dP: the row threads start on dS while dV is computed
 #pragma unroll
                 for (int s = 0; s < 2; s++) {
                     const uint64_t aP = desc_sw128(sm0 + BwdSmem::PS + s * 64 * 128, 128 * 128);
@@ -606,7 +713,7 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                     for (int k = 0; k < 4; k++)
                         umma_bf16(tmem + 384 + 64 * s, aP + 128 * k, bDO + 128 * k, idMM, k > 0);
                 }
-                umma_commit(bar_g2);
+                umma_commit(bar_g2b);
                 if (!mbar_wait(bar_r2, (uint32_t)(it & 1), abort_s, err_flag, 25))
                     break;
                 fence_after_sync();
@@ -618,13 +725,18 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
 #pragma unroll
                     for (int k = 0; k < 4; k++)
                         umma_bf16(tmem + 64 * s, aS + 128 * k, bQ + 128 * k, idMM, k > 0);
-                    const uint64_t bK = desc_sw128(sm0 + BwdSmem::K + s * 128 * 128, 8192);
+                }
+                {
+                    // dQ (key part) of both streams in one product: B = [K_b0 | K_b1], the second
+                    // stream's keys being the next 64-column block of the MN-major operand
+                    const uint64_t bK = desc_sw128(sm0 + BwdSmem::K, 128 * 128);
 #pragma unroll
                     for (int k = 0; k < 8; k++) {
                         const uint64_t aSk = desc_sw128(sm0 + BwdSmem::PS + (k >> 2) * 128 * 128, 16) + 2 * (k & 3);
-                        umma_bf16(tmem + 128 + 64 * s, aSk, bK + 128 * k, idKM, k > 0);
+                        umma_bf16(tmem + 128, aSk, bK + 128 * k, idKM2, k > 0);
                     }
                 }
+                umma_commit(bar_g3);
                 if (has_wr) {
                     const uint64_t bR = desc_sw128(sm0 + BwdSmem::R, 8192);
 #pragma unroll
@@ -648,56 +760,74 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                             umma_bf16(tmem + 448 + 16 * w, aE + 128 * k, dOnes, idCS, k > 0);
                     }
                 }
-                umma_commit(bar_g3);
+                umma_commit(bar_g3b);
                 umma_commit(bar_free);
             }
         }
     } else {
-        const int quarter = warp & 3;
+        const int quarter = warp & 3, half = (warp - 2) >> 2;
         const int row = quarter * 32 + lane, s = row >> 6, i = row & 63, i_base = i - lane;
         const int b = b0 + s;
         const bool rowvalid = i < T && b < a.B;
         const uint32_t trow = tmem + ((uint32_t)(quarter * 32) << 16);
         const int tid = threadIdx.x - 64;
-        for (int r = tid; r < L; r += 128)
-            brs[r] = a.br_scale * a.b_r[(size_t)h * L + r];
-        // this pair's slices of the partial table gradients start at zero; the second stream's stay zero
+        const float sc2 = a.inv_sqrt * 1.4426950408889634f;
+        // D_i = dO_i . O_i and the saved log-sum-exp (log2 domain); both threads of a row compute them.
+        // Their loads go out first; everything else of the prologue runs under their latency.
+        uint4 ox[8], dx[8];
+        float lse2 = 0.0f;
+        if (rowvalid) {
+            const uint4 *po = reinterpret_cast<const uint4 *>(reinterpret_cast<const bf16 *>(a.out) + ((size_t)i * a.B + b) * HD + h * DK);
+            const uint4 *pd = reinterpret_cast<const uint4 *>(reinterpret_cast<const bf16 *>(a.dout) + ((size_t)i * a.B + b) * HD + h * DK);
+#pragma unroll
+            for (int v4 = 0; v4 < 8; v4++) {
+                ox[v4] = po[v4];
+                dx[v4] = pd[v4];
+            }
+            lse2 = a.lse[((size_t)b * a.H + h) * T + i] * 1.4426950408889634f;
+        }
+        if (threadIdx.x == 64) ATC_STAMP(14);
+        // scaled b_r, slots -64 .. what the last key block can name
+        const int brs_n = min(BRS_LEN, BRS_PAD + (kbs.hi + 1) * KB + 64);
+        for (int r = tid; r < brs_n; r += NROW) {
+            const int rr = r - BRS_PAD;
+            brs[r] = (rr >= 0 && rr < L) ? a.br_scale * a.b_r[(size_t)h * L + rr] * sc2 : 0.0f;
+        }
+        if (threadIdx.x == 64) ATC_STAMP(15);
+        // this pair's slices of the partial table gradients; the second stream's slice stays zero
         float *dwr = (has_wr && a.dwr_part) ? a.dwr_part + ((size_t)b0 * a.H + h) * P * DK : nullptr;
         float *dbr = a.dbr_part ? a.dbr_part + ((size_t)b0 * a.H + h) * L : nullptr;
-        for (int s2 = 0; s2 < 2 && b0 + s2 < a.B; s2++) {
+        for (int s2 = direct ? 1 : 0; s2 < 2 && b0 + s2 < a.B; s2++) {
             if (dwr)
-                for (int idx = tid; idx < P * DK; idx += 128)
-                    dwr[(size_t)s2 * a.H * P * DK + idx] = 0.0f;
+                for (int idx = tid; idx < P * DK / 4; idx += NROW)
+                    reinterpret_cast<float4 *>(dwr + (size_t)s2 * a.H * P * DK)[idx] = make_float4(0.f, 0.f, 0.f, 0.f);
             if (dbr)
-                for (int idx = tid; idx < L; idx += 128)
+                for (int idx = tid; idx < L; idx += NROW)
                     dbr[(size_t)s2 * a.H * L + idx] = 0.0f;
         }
+        if (threadIdx.x == 64) ATC_STAMP(16);
         // keys no query attends to get zero gradients
         bf16 *dkv = reinterpret_cast<bf16 *>(a.dkv);
         for (int kb = 0; kb * KB < L; kb++) {
             if (kb >= kbs.lo && kb <= kbs.hi)
                 continue;
             const int j = kb * KB + row;
-            if (j < L)
-                for (int s2 = 0; s2 < 2 && b0 + s2 < a.B; s2++) {
-                    uint4 *dst = reinterpret_cast<uint4 *>(dkv + ((size_t)j * a.B + b0 + s2) * a.dkvp + h * DK);
-                    uint4 *dst2 = reinterpret_cast<uint4 *>(dkv + ((size_t)j * a.B + b0 + s2) * a.dkvp + HD + h * DK);
+            if (j < L && b0 + half < a.B) {
+                uint4 *dst = reinterpret_cast<uint4 *>(dkv + ((size_t)j * a.B + b0 + half) * a.dkvp + h * DK);
+                uint4 *dst2 = reinterpret_cast<uint4 *>(dkv + ((size_t)j * a.B + b0 + half) * a.dkvp + HD + h * DK);
 #pragma unroll
-                    for (int v4 = 0; v4 < 8; v4++) {
-                        dst[v4] = make_uint4(0u, 0u, 0u, 0u);
-                        dst2[v4] = make_uint4(0u, 0u, 0u, 0u);
-                    }
+                for (int v4 = 0; v4 < 8; v4++) {
+                    dst[v4] = make_uint4(0u, 0u, 0u, 0u);
+                    dst2[v4] = make_uint4(0u, 0u, 0u, 0u);
                 }
+            }
         }
-        // D_i = dO_i . O_i and the saved log-sum-exp (log2 domain)
-        float Di = 0.0f, lse2 = 0.0f;
+        if (threadIdx.x == 64) ATC_STAMP(17);
+        float Di = 0.0f;
         if (rowvalid) {
-            const uint4 *po = reinterpret_cast<const uint4 *>(reinterpret_cast<const bf16 *>(a.out) + ((size_t)i * a.B + b) * HD + h * DK);
-            const uint4 *pd = reinterpret_cast<const uint4 *>(reinterpret_cast<const bf16 *>(a.dout) + ((size_t)i * a.B + b) * HD + h * DK);
 #pragma unroll
             for (int v4 = 0; v4 < 8; v4++) {
-                const uint4 x = po[v4], y = pd[v4];
-                const uint32_t xw[4] = {x.x, x.y, x.z, x.w}, yw[4] = {y.x, y.y, y.z, y.w};
+                const uint32_t xw[4] = {ox[v4].x, ox[v4].y, ox[v4].z, ox[v4].w}, yw[4] = {dx[v4].x, dx[v4].y, dx[v4].z, dx[v4].w};
 #pragma unroll
                 for (int u = 0; u < 4; u++) {
                     const __nv_bfloat162 xa = *reinterpret_cast<const __nv_bfloat162 *>(&xw[u]);
@@ -705,26 +835,27 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                     Di += __low2float(xa) * __low2float(ya) + __high2float(xa) * __high2float(ya);
                 }
             }
-            lse2 = a.lse[((size_t)b * a.H + h) * T + i] * 1.4426950408889634f;
         }
-        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (threadIdx.x == 64) ATC_STAMP(18);
+        asm volatile("bar.sync 1, 256;" ::: "memory");
         if (threadIdx.x == 64) ATC_STAMP(3);
-        const float sc2 = a.inv_sqrt * 1.4426950408889634f;
-        float dq[64];
+        float dq_acc[SINGLE ? 1 : 32];
 #pragma unroll
-        for (int k = 0; k < 64; k++)
-            dq[k] = 0.0f;
+        for (int k = 0; k < (SINGLE ? 1 : 32); k++)
+            dq_acc[k] = 0.0f;
+        bf16 *erow = reinterpret_cast<bf16 *>(sm + BwdSmem::DE);
         bool ok = true;
         int it = 0;
         for (int kb = kbs.lo; kb <= kbs.hi && ok; kb++, it++) {
             const int j0 = kb * KB;
             const int wlo = j0 - 63 + c0;
-            // this row's dE window cells: zero (the previous block's MMAs are done with them)
+            // this row's dE window cells: zero (the previous block's MMAs are done with them); each
+            // thread takes half of the row's 24 16-byte pieces, rotated by lane against bank conflicts
 #pragma unroll
-            for (int at = 0; at < 3; at++)
-#pragma unroll
-                for (int v4 = 0; v4 < 8; v4++)
-                    *reinterpret_cast<uint4 *>(sm + BwdSmem::DE + at * 128 * 128 + row * 128 + (v4 << 4)) = make_uint4(0u, 0u, 0u, 0u);
+            for (int q12 = 0; q12 < 12; q12++) {
+                const int piece = half * 12 + q12, at = piece >> 3, v4 = ((piece & 7) + lane) & 7;
+                *reinterpret_cast<uint4 *>(sm + BwdSmem::DE + at * 128 * 128 + row * 128 + (v4 << 4)) = make_uint4(0u, 0u, 0u, 0u);
+            }
             if (lane == 0)
                 ok = mbar_wait(bar_g1, (uint32_t)(it & 1), abort_s, err_flag, 26);
             ok = __all_sync(0xffffffffu, ok);
@@ -738,9 +869,10 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                 e0 = __uint_as_float(tmem_ld1(trow + 256 + 191));
                 tmem_ld_wait();
             }
-            // ---- r1: probabilities
+            // ---- r1: probabilities of this thread's two chunks, bf16, into the K-major atoms of PS
 #pragma unroll 1
-            for (int c = 0; c < 4; c++) {
+            for (int cc = 0; cc < 2; cc++) {
+                const int c = half * 2 + cc;
                 uint32_t sv[32], x[64];
                 tmem_ld32(trow + s * 128 + c * 32, sv);
                 if (has_wr) {
@@ -752,36 +884,16 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                 if (has_wr)
                     barrel_skew(x, lane);
                 const int jc = j0 + c * 32;
+                score_chunk(sv, x, has_wr, clampable, e0, i - c0 - jc, i + M - a.attn_len + 1 - jc,
+                            rowvalid ? i + M - jc : -1, brs + BRS_PAD + jc + (T - 1) - i, sc2);
 #pragma unroll
-                for (int k = 0; k < 32; k++) {
-                    const int j = jc + k;
-                    const int d = i + M - j;
-                    float e = 0.0f;
-                    if (has_wr) {
-                        e = __uint_as_float(x[k]);
-                        if (clampable && (j - i + c0 < 0))
-                            e = e0;
-                    }
-                    int r = j + (T - 1) - i;
-                    r = r < L ? r : L - 1;
-                    r = r < 0 ? 0 : r;
-                    const float v = (__uint_as_float(sv[k]) + e + brs[r]) * sc2;
-                    const float p = (rowvalid && d >= 0 && d < a.attn_len) ? ex2(v - lse2) : 0.0f;
-                    sv[k] = __float_as_uint(p);
-                }
-                tmem_st32(trow + 256 + c * 32, sv);
+                for (int k = 0; k < 32; k++)
+                    sv[k] = __float_as_uint(ex2(__uint_as_float(sv[k]) - lse2));
                 unsigned char *prow = sm + BwdSmem::PS + (c >> 1) * 128 * 128 + row * 128;
 #pragma unroll
-                for (int v4 = 0; v4 < 4; v4++) {
-                    uint4 pk;
-                    pk.x = tc::pack_bf16(__uint_as_float(sv[v4 * 8 + 0]), __uint_as_float(sv[v4 * 8 + 1]));
-                    pk.y = tc::pack_bf16(__uint_as_float(sv[v4 * 8 + 2]), __uint_as_float(sv[v4 * 8 + 3]));
-                    pk.z = tc::pack_bf16(__uint_as_float(sv[v4 * 8 + 4]), __uint_as_float(sv[v4 * 8 + 5]));
-                    pk.w = tc::pack_bf16(__uint_as_float(sv[v4 * 8 + 6]), __uint_as_float(sv[v4 * 8 + 7]));
-                    *reinterpret_cast<uint4 *>(prow + ((((c & 1) * 4 + v4) ^ (row & 7)) << 4)) = pk;
-                }
+                for (int v4 = 0; v4 < 4; v4++)
+                    *reinterpret_cast<uint4 *>(prow + ((((c & 1) * 4 + v4) ^ (row & 7)) << 4)) = pack8(sv + v4 * 8);
             }
-            tmem_st_wait();
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             fence_before_sync();
             mbar_arrive(bar_r1);
@@ -794,62 +906,64 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                 break;
             fence_after_sync();
             if (it == 0 && threadIdx.x == 64) ATC_STAMP(6);
-            {
-                // dV of key j0 + row, both streams
-                const int j = j0 + row;
-#pragma unroll 1
-                for (int s2 = 0; s2 < 2; s2++) {
-                    uint32_t y[64];
-                    tmem_ld32(trow + 384 + 64 * s2, y);
-                    tmem_ld32(trow + 384 + 64 * s2 + 32, y + 32);
-                    tmem_ld_wait();
-                    if (j < L && b0 + s2 < a.B) {
-                        uint4 *dst = reinterpret_cast<uint4 *>(dkv + ((size_t)j * a.B + b0 + s2) * a.dkvp + HD + h * DK);
-#pragma unroll
-                        for (int v4 = 0; v4 < 8; v4++)
-                            dst[v4] = make_uint4(tc::pack_bf16(__uint_as_float(y[v4 * 8]), __uint_as_float(y[v4 * 8 + 1])),
-                                                 tc::pack_bf16(__uint_as_float(y[v4 * 8 + 2]), __uint_as_float(y[v4 * 8 + 3])),
-                                                 tc::pack_bf16(__uint_as_float(y[v4 * 8 + 4]), __uint_as_float(y[v4 * 8 + 5])),
-                                                 tc::pack_bf16(__uint_as_float(y[v4 * 8 + 6]), __uint_as_float(y[v4 * 8 + 7])));
-                    }
-                }
-            }
             if (it == 0 && threadIdx.x == 64) ATC_STAMP(7);
             float sclamp = 0.0f;
-            bf16 *erow = reinterpret_cast<bf16 *>(sm + BwdSmem::DE);
 #pragma unroll 1
-            for (int c = 0; c < 4; c++) {
-                uint32_t dp[32], pf[32];
+            for (int cc = 0; cc < 2; cc++) {
+                const int c = half * 2 + cc;
+                uint32_t dp[32];
                 tmem_ld32(trow + s * 128 + c * 32, dp);
-                tmem_ld32(trow + 256 + c * 32, pf);
-                tmem_ld_wait();
                 unsigned char *prow = sm + BwdSmem::PS + (c >> 1) * 128 * 128 + row * 128;
+                // the probabilities as the MMAs saw them (bf16), read back from this thread's own cells
+                uint32_t pw[16];
+#pragma unroll
+                for (int v4 = 0; v4 < 4; v4++) {
+                    const uint4 t4 = *reinterpret_cast<const uint4 *>(prow + ((((c & 1) * 4 + v4) ^ (row & 7)) << 4));
+                    pw[v4 * 4] = t4.x; pw[v4 * 4 + 1] = t4.y; pw[v4 * 4 + 2] = t4.z; pw[v4 * 4 + 3] = t4.w;
+                }
+                tmem_ld_wait();
+                // window column of key jj is jj + 63 - i; keys below kpad are on the left pad
+                const int wc0 = c * 32 + 63 - i, kpad = -wlo - wc0;
                 uint32_t pk[16];
 #pragma unroll
                 for (int k = 0; k < 32; k += 2) {
-                    const float d0 = __uint_as_float(pf[k]) * (__uint_as_float(dp[k]) - Di) * a.inv_sqrt;
-                    const float d1 = __uint_as_float(pf[k + 1]) * (__uint_as_float(dp[k + 1]) - Di) * a.inv_sqrt;
+                    const __nv_bfloat162 pp = *reinterpret_cast<const __nv_bfloat162 *>(&pw[k >> 1]);
+                    const float d0 = __low2float(pp) * (__uint_as_float(dp[k]) - Di) * a.inv_sqrt;
+                    const float d1 = __high2float(pp) * (__uint_as_float(dp[k + 1]) - Di) * a.inv_sqrt;
                     const __nv_bfloat162 hh = __floats2bfloat162_rn(d0, d1);
                     pk[k >> 1] = *reinterpret_cast<const uint32_t *>(&hh);
-                    // window column of key jj is jj + 63 - i; a negative table row belongs to the left pad
-#pragma unroll
-                    for (int u = 0; u < 2; u++) {
-                        const int wc = c * 32 + k + u + 63 - i;
-                        const bf16 val = u ? hh.y : hh.x;
-                        if (wlo + wc < 0)
-                            sclamp += __bfloat162float(val);
-                        const int at = wc >> 6, cc = wc & 63;
-                        erow[(size_t)at * 128 * 64 + row * 64 + ((((cc >> 3) ^ (row & 7)) << 3) | (cc & 7))] = val;
-                    }
+                    if (k < kpad)
+                        sclamp += __low2float(hh);
+                    if (k + 1 < kpad)
+                        sclamp += __high2float(hh);
+                    const int w0 = wc0 + k, w1 = w0 + 1;
+                    erow[(size_t)(w0 >> 6) * 128 * 64 + row * 64 + (((((w0 & 63) >> 3) ^ (row & 7)) << 3) | (w0 & 7))] = hh.x;
+                    erow[(size_t)(w1 >> 6) * 128 * 64 + row * 64 + (((((w1 & 63) >> 3) ^ (row & 7)) << 3) | (w1 & 7))] = hh.y;
                 }
 #pragma unroll
                 for (int v4 = 0; v4 < 4; v4++)
                     *reinterpret_cast<uint4 *>(prow + ((((c & 1) * 4 + v4) ^ (row & 7)) << 4)) =
                         make_uint4(pk[v4 * 4], pk[v4 * 4 + 1], pk[v4 * 4 + 2], pk[v4 * 4 + 3]);
             }
+            xch[half * 128 + row] = sclamp;
+            if (lane == 0)
+                ok = mbar_wait(bar_g2b, (uint32_t)(it & 1), abort_s, err_flag, 29);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok)
+                break;
+            fence_after_sync();
             {
-                const int wc = 191, at = wc >> 6, cc = wc & 63;
-                erow[(size_t)at * 128 * 64 + row * 64 + ((((cc >> 3) ^ (row & 7)) << 3) | (cc & 7))] = __float2bfloat16_rn(sclamp);
+                // dV of key j0 + row, stream b0 + half
+                const int j = j0 + row;
+                const bool act = j < L && b0 + half < a.B;
+                tmem_row_to_global_bf16(trow + 384 + 64 * half,
+                                        dkv + ((size_t)(act ? j : 0) * a.B + (act ? b0 + half : 0)) * a.dkvp + HD + h * DK, act);
+            }
+            asm volatile("bar.sync 1, 256;" ::: "memory");
+            if (half == 0) {
+                const int w = 191;
+                erow[(size_t)(w >> 6) * 128 * 64 + row * 64 + (((((w & 63) >> 3) ^ (row & 7)) << 3) | (w & 7))] =
+                    __float2bfloat16_rn(sclamp + xch[128 + row]);
             }
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             fence_before_sync();
@@ -864,127 +978,88 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             fence_after_sync();
             if (it == 0 && threadIdx.x == 64) ATC_STAMP(9);
             {
+                // dK of key j0 + row, stream b0 + half
                 const int j = j0 + row;
-#pragma unroll 1
-                for (int s2 = 0; s2 < 2; s2++) {
-                    uint32_t y[64];
-                    tmem_ld32(trow + 64 * s2, y);
-                    tmem_ld32(trow + 64 * s2 + 32, y + 32);
-                    tmem_ld_wait();
-                    if (j < L && b0 + s2 < a.B) {
-                        uint4 *dst = reinterpret_cast<uint4 *>(dkv + ((size_t)j * a.B + b0 + s2) * a.dkvp + h * DK);
-#pragma unroll
-                        for (int v4 = 0; v4 < 8; v4++)
-                            dst[v4] = make_uint4(tc::pack_bf16(__uint_as_float(y[v4 * 8]), __uint_as_float(y[v4 * 8 + 1])),
-                                                 tc::pack_bf16(__uint_as_float(y[v4 * 8 + 2]), __uint_as_float(y[v4 * 8 + 3])),
-                                                 tc::pack_bf16(__uint_as_float(y[v4 * 8 + 4]), __uint_as_float(y[v4 * 8 + 5])),
-                                                 tc::pack_bf16(__uint_as_float(y[v4 * 8 + 6]), __uint_as_float(y[v4 * 8 + 7])));
-                    }
-                }
+                const bool act = j < L && b0 + half < a.B;
+                tmem_row_to_global_bf16(trow + 64 * half,
+                                        dkv + ((size_t)(act ? j : 0) * a.B + (act ? b0 + half : 0)) * a.dkvp + h * DK, act);
             }
+            float dq[32];
             {
-                uint32_t y[64];
-                tmem_ld32(trow + 128 + 64 * s, y);
-                tmem_ld32(trow + 128 + 64 * s + 32, y + 32);
+                uint32_t y[32];
+                tmem_ld32(trow + 128 + 64 * s + 32 * half, y);
                 tmem_ld_wait();
 #pragma unroll
-                for (int k = 0; k < 64; k++)
-                    dq[k] += __uint_as_float(y[k]);
-                if (has_wr) {
-                    tmem_ld32(trow + 256, y);
-                    tmem_ld32(trow + 256 + 32, y + 32);
-                    tmem_ld_wait();
+                for (int k = 0; k < 32; k++)
+                    dq[k] = __uint_as_float(y[k]) + (SINGLE ? 0.0f : dq_acc[SINGLE ? 0 : k]);
+            }
+            if (lane == 0)
+                ok = mbar_wait(bar_g3b, (uint32_t)(it & 1), abort_s, err_flag, 30);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok)
+                break;
+            fence_after_sync();
+            if (has_wr) {
+                uint32_t z[32];
+                tmem_ld32(trow + 256 + 32 * half, z);
+                tmem_ld_wait();
 #pragma unroll
-                    for (int k = 0; k < 64; k++)
-                        dq[k] += __uint_as_float(y[k]);
+                for (int k = 0; k < 32; k++)
+                    dq[k] += __uint_as_float(z[k]);
+            }
+            if (SINGLE || kb == kbs.hi) {
+                if (rowvalid) {
+                    bf16 *dst = reinterpret_cast<bf16 *>(a.dq) + ((size_t)i * a.B + b) * a.dqp + h * DK + half * 32;
+#pragma unroll
+                    for (int v4 = 0; v4 < 4; v4++)
+                        reinterpret_cast<uint4 *>(dst)[v4] =
+                            make_uint4(tc::pack_bf16(dq[v4 * 8], dq[v4 * 8 + 1]), tc::pack_bf16(dq[v4 * 8 + 2], dq[v4 * 8 + 3]),
+                                       tc::pack_bf16(dq[v4 * 8 + 4], dq[v4 * 8 + 5]), tc::pack_bf16(dq[v4 * 8 + 6], dq[v4 * 8 + 7]));
                 }
+            } else {
+#pragma unroll
+                for (int k = 0; k < (SINGLE ? 1 : 32); k++)
+                    dq_acc[k] = dq[k];
             }
             if (it == 0 && threadIdx.x == 64) ATC_STAMP(10);
-            // table gradients: window row c = row (first half), then 128 + row (second half, rows
-            // 0..63 of it exist), then window row 191 = the left pad's share of table row 0; a
-            // barrier between the three, since they may meet in the same table row
-            {
-                uint32_t y[64];
-                if (has_wr) {
-                    tmem_ld32(trow + 320, y);
-                    tmem_ld32(trow + 320 + 32, y + 32);
-                }
+            // table gradients: window rows 0..127 by the first thread of each row, then window rows
+            // 128..190 by the second threads of rows 0..62, then window row 191 = the left pad's
+            // share of table row 0.  When they are accumulated (several key blocks) the parts may
+            // meet in one table row, hence the barriers; a single block that stores them needs one
+            // only in front of the pad row's addition.
+            if (half == 0) {
+                const int x = wlo + row;
+                if (has_wr)
+                    tmem_row_to_global(trow + 320, dwr + (size_t)(x >= 0 && x < P ? x : 0) * DK, dwr && x >= 0 && x < P, !direct);
                 const float cs = __uint_as_float(tmem_ld1(trow + 448));
                 tmem_ld_wait();
-                const int x = wlo + row;
-                if (dwr && x >= 0 && x < P) {
-                    float4 *dst = reinterpret_cast<float4 *>(dwr + (size_t)x * DK);
-#pragma unroll
-                    for (int v4 = 0; v4 < 16; v4++) {
-                        float4 t4 = dst[v4];
-                        t4.x += __uint_as_float(y[v4 * 4]);
-                        t4.y += __uint_as_float(y[v4 * 4 + 1]);
-                        t4.z += __uint_as_float(y[v4 * 4 + 2]);
-                        t4.w += __uint_as_float(y[v4 * 4 + 3]);
-                        dst[v4] = t4;
-                    }
-                }
                 const int r = j0 + row + T - 64;
                 if (dbr && r >= 0 && r < L)
-                    dbr[r] += a.br_scale * cs;
+                    dbr[r] = a.br_scale * cs + (direct ? 0.0f : dbr[r]);
             }
-            asm volatile("bar.sync 1, 128;" ::: "memory");
-            {
-                uint32_t y[64];
-                float cs = 0.0f;
-                if (quarter < 2) { // warp-uniform
-                    if (has_wr) {
-                        tmem_ld32(trow + 384, y);
-                        tmem_ld32(trow + 384 + 32, y + 32);
-                    }
-                    cs = __uint_as_float(tmem_ld1(trow + 464));
-                    tmem_ld_wait();
-                }
-                fence_before_sync();
-                mbar_arrive(bar_r3); // every TMEM read of this block is done
-                const int c = 128 + row;
-                if (quarter < 2 && c <= 190) {
-                    const int x = wlo + c;
-                    if (dwr && x >= 0 && x < P) {
-                        float4 *dst = reinterpret_cast<float4 *>(dwr + (size_t)x * DK);
-#pragma unroll
-                        for (int v4 = 0; v4 < 16; v4++) {
-                            float4 t4 = dst[v4];
-                            t4.x += __uint_as_float(y[v4 * 4]);
-                            t4.y += __uint_as_float(y[v4 * 4 + 1]);
-                            t4.z += __uint_as_float(y[v4 * 4 + 2]);
-                            t4.w += __uint_as_float(y[v4 * 4 + 3]);
-                            dst[v4] = t4;
-                        }
-                    }
-                    const int r = j0 + c + T - 64;
-                    if (dbr && r >= 0 && r < L)
-                        dbr[r] += a.br_scale * cs;
-                }
-                asm volatile("bar.sync 1, 128;" ::: "memory");
-                if (quarter < 2 && c == 191 && dwr && clampable) {
-                    float4 *dst = reinterpret_cast<float4 *>(dwr);
-#pragma unroll
-                    for (int v4 = 0; v4 < 16; v4++) {
-                        float4 t4 = dst[v4];
-                        t4.x += __uint_as_float(y[v4 * 4]);
-                        t4.y += __uint_as_float(y[v4 * 4 + 1]);
-                        t4.z += __uint_as_float(y[v4 * 4 + 2]);
-                        t4.w += __uint_as_float(y[v4 * 4 + 3]);
-                        dst[v4] = t4;
-                    }
-                }
+            if (!direct)
+                asm volatile("bar.sync 1, 256;" ::: "memory");
+            if (half == 1 && quarter < 2) { // warp-uniform
+                const int c = 128 + row, x = wlo + c;
+                if (has_wr)
+                    tmem_row_to_global(trow + 384, dwr + (size_t)(x >= 0 && x < P ? x : 0) * DK,
+                                       dwr && c <= 190 && x >= 0 && x < P, !direct);
+                const float cs = __uint_as_float(tmem_ld1(trow + 464));
+                tmem_ld_wait();
+                const int r = j0 + c + T - 64;
+                if (dbr && c <= 190 && r >= 0 && r < L)
+                    dbr[r] = a.br_scale * cs + (direct ? 0.0f : dbr[r]);
             }
-            asm volatile("bar.sync 1, 128;" ::: "memory");
+            if (clampable) { // CTA-uniform
+                asm volatile("bar.sync 1, 256;" ::: "memory");
+                if (half == 1 && quarter == 1) // warp-uniform; lane 31 holds window row 191
+                    tmem_row_to_global(trow + 384, dwr, dwr && row == 63, true);
+            }
+            fence_before_sync();
+            mbar_arrive(bar_r3); // every TMEM read of this block is done
+            if (!direct)
+                asm volatile("bar.sync 1, 256;" ::: "memory");
             if (it == 0 && threadIdx.x == 64) ATC_STAMP(11);
-        }
-        if (ok && rowvalid) {
-            bf16 *dst = reinterpret_cast<bf16 *>(a.dq) + ((size_t)i * a.B + b) * a.dqp + h * DK;
-#pragma unroll
-            for (int v4 = 0; v4 < 8; v4++)
-                reinterpret_cast<uint4 *>(dst)[v4] =
-                    make_uint4(tc::pack_bf16(dq[v4 * 8], dq[v4 * 8 + 1]), tc::pack_bf16(dq[v4 * 8 + 2], dq[v4 * 8 + 3]),
-                               tc::pack_bf16(dq[v4 * 8 + 4], dq[v4 * 8 + 5]), tc::pack_bf16(dq[v4 * 8 + 6], dq[v4 * 8 + 7]));
         }
     }
     if (threadIdx.x == 64)
@@ -1068,7 +1143,7 @@ static int forward(const AttnArgs &a, const void *w_r16, int *err_flag, cudaStre
         CUDA_TRY(cudaFuncSetAttribute(attn_fwd_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, FwdSmem::TOTAL));
         attr_done = true;
     }
-    launch_k(attn_fwd_tc_kernel, dim3((a.B + 1) / 2, a.H), dim3(192), FwdSmem::TOTAL, st, mq, mkv, mwr, a,
+    launch_k(attn_fwd_tc_kernel, dim3((a.B + 1) / 2, a.H), dim3(320), FwdSmem::TOTAL, st, mq, mkv, mwr, a,
              w_r16 ? 1 : 0, err_flag);
     KERNEL_CHECK();
     return NNCU_OK;
@@ -1088,11 +1163,17 @@ static int backward(const AttnArgs &a, const void *w_r16, int *err_flag, cudaStr
     }
     static bool attr_done = false;
     if (!attr_done) {
-        CUDA_TRY(cudaFuncSetAttribute(attn_bwd_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, BwdSmem::TOTAL));
+        CUDA_TRY(cudaFuncSetAttribute(attn_bwd_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, BwdSmem::TOTAL));
+        CUDA_TRY(cudaFuncSetAttribute(attn_bwd_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, BwdSmem::TOTAL));
         attr_done = true;
     }
-    launch_k(attn_bwd_tc_kernel, dim3((a.B + 1) / 2, a.H), dim3(192), BwdSmem::TOTAL, st, mq, mdo, mkv, mwr, mwr0, a,
-             w_r16 ? 1 : 0, err_flag);
+    const KeyBlocks kbs = key_blocks(a.M, a.L, a.attn_len, 0, a.T);
+    if (kbs.lo == kbs.hi)
+        launch_k(attn_bwd_tc_kernel<true>, dim3((a.B + 1) / 2, a.H), dim3(320), BwdSmem::TOTAL, st, mq, mdo, mkv, mwr, mwr0,
+                 a, w_r16 ? 1 : 0, err_flag);
+    else
+        launch_k(attn_bwd_tc_kernel<false>, dim3((a.B + 1) / 2, a.H), dim3(320), BwdSmem::TOTAL, st, mq, mdo, mkv, mwr, mwr0,
+                 a, w_r16 ? 1 : 0, err_flag);
     KERNEL_CHECK();
     return NNCU_OK;
 }
@@ -1157,7 +1238,7 @@ inline bool bwd_enabled()
     static int v = -1;
     if (v < 0) {
         const char *e = getenv("NNCU_ATTN_TC_BWD");
-        v = (e && e[0] == '1') ? 1 : 0;
+        v = (e && e[0] == '0') ? 0 : 1;
     }
     return v == 1;
 }

@@ -13,8 +13,10 @@
 // TMEM accumulator, and four epilogue warps read it back with tcgen05.ld.
 //
 //   warp 0      TMA producer (one lane)
-//   warp 1      TMEM allocation, MMA issue (one lane), TMEM release
+//   warp 1      TMEM allocation, MMA issue of the even k-blocks (one lane), TMEM release
 //   warps 2-5   epilogue: warp w owns TMEM lanes 32*(w%4) .. +31 = tile rows
+//   warp 6      MMA issue of the odd k-blocks (one lane), into a second accumulator
+//   warp 7      TMA producer of the odd k-blocks (one lane); warp 0 loads the even ones
 //
 // Out-of-range rows/columns/k are zero-filled by TMA on load and clipped by TMA
 // on store (the tile is staged in the idle operand ring, 128-byte swizzled), so M, N are arbitrary and K only needs 16-byte row strides.
@@ -187,6 +189,22 @@ __device__ __forceinline__ void tmem_ld_wait()
 {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
+// r = 32 columns at taddr (+ the same columns of the second accumulator `other` columns further
+// on, when `dual`), complete on return
+__device__ __forceinline__ void tmem_ld32_pair(uint32_t taddr, uint32_t other, bool dual, uint32_t *r)
+{
+    tmem_ld32(taddr, r);
+    if (dual) {
+        uint32_t q[32];
+        tmem_ld32(taddr + other, q);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 32; j++)
+            r[j] = __float_as_uint(__uint_as_float(r[j]) + __uint_as_float(q[j]));
+    } else {
+        tmem_ld_wait();
+    }
+}
 
 // shared-memory matrix descriptor: K-major tile, 128-byte swizzle, rows of 128 bytes,
 // 8-row groups 1024 bytes apart
@@ -240,7 +258,13 @@ struct SmemLayout {
     static constexpr int A_BYTES = BM * BK * 2;
     static constexpr int B_BYTES = BN * BK * 2;
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-    static constexpr int STAGES = (BN == 128) ? 3 : 4; // BN <= 128: 96 KB, two CTAs per SM
+#ifndef NNCU_TC_STAGES64
+#define NNCU_TC_STAGES64 8
+#endif
+    // The ring is bound by its round trip (commit -> empty -> TMA issue -> data -> full), about 2000
+    // cycles, divided by its depth: a 64-wide tile, whose launches have at most one CTA per SM anyway,
+    // takes the whole shared memory (8 x 24 KB); 128-wide tiles keep 3 x 32 KB so that two CTAs share an SM
+    static constexpr int STAGES = (BN == 128) ? 3 : (BN == 64 ? NNCU_TC_STAGES64 : 4);
     static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES;
     static constexpr int BIAS_OFFSET = BAR_OFFSET + 256;      // BN floats of bias for the epilogue
     static constexpr int TOTAL = BIAS_OFFSET + BN * 4 + 1024; // + alignment slack
@@ -248,7 +272,7 @@ struct SmemLayout {
 };
 
 template <int BN, typename TC, bool AMN, bool BMN>
-__global__ void __launch_bounds__(192, SmemLayout<BN>::CTAS_PER_SM)
+__global__ void __launch_bounds__(256, SmemLayout<BN>::CTAS_PER_SM)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                const __grid_constant__ CUtensorMap map_c, int staged, TC *C, long ldc, const float *__restrict__ bias, const TC *addsrc, int M, int N,
                int K, int *err_flag, int bias_n)
@@ -285,13 +309,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             mbar_init(smem_u32(&full[s]), 1);
             mbar_init(smem_u32(&empty[s]), 1);
         }
-        mbar_init(smem_u32(tmem_full), 1);
+        mbar_init(smem_u32(tmem_full), (SL::STAGES % 2) == 0 ? 2 : 1); // one commit from each issuing thread
         *abort_s = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
     if (warp == 1)
-        tmem_alloc(smem_u32(tmem_slot), BN);
+        tmem_alloc(smem_u32(tmem_slot), 2 * BN);
     fence_before_sync();
     __syncthreads();
     fence_after_sync();
@@ -308,13 +332,23 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     // 128 x 64 tile.  So both loops carry their state incrementally (barrier addresses and the
     // low descriptor words step by constants, the phase bit flips at the ring's wrap), the four
     // UMMAs of a k-block are one asm block, and a wait is a try_wait with a branch.
-    if (warp == 0) {
+    // Two loading and two issuing threads when the ring has an even number of stages: each pair then
+    // owns its own stages (even / odd k-blocks).  With an odd ring the pairs would share stages, and
+    // a thread two rounds ahead of its partner would mistake the parity of a barrier that has not
+    // completed once for a completion: there one thread loads and one issues, as before.
+    constexpr bool DUAL = (SL::STAGES % 2) == 0;
+    constexpr int KSTEP = DUAL ? 2 : 1;
+    if (warp == 0 || (DUAL && warp == 7)) {
         if (lane == 0) {
+            // warp 0 fills the stages of the even k-blocks, warp 7 those of the odd ones (a k-block
+            // costs its loading thread some 360 cycles of barrier handshake and TMA issue)
+            const int which = warp == 0 ? 0 : 1;
             const uint32_t sm0 = smem_u32(sm), full0 = smem_u32(full), empty0 = smem_u32(empty);
-            uint32_t dst = sm0, fb = full0, eb = empty0, ph = 0;
-            int s = 0, kx = kb_first * BK;
-            for (int kb = 0; kb < nkb; kb++, kx += BK) {
-                if (kb >= SL::STAGES && !mbar_wait(eb, ph, abort_s, err_flag, 1))
+            int s = which % SL::STAGES;
+            int kx = (kb_first + which) * BK;
+            for (int kb = which; kb < nkb; kb += KSTEP, kx += KSTEP * BK) {
+                const uint32_t fb = full0 + 8 * s, eb = empty0 + 8 * s, dst = sm0 + s * SL::STAGE_BYTES;
+                if (kb >= SL::STAGES && !mbar_wait(eb, (uint32_t)(((kb / SL::STAGES) - 1) & 1), abort_s, err_flag, 1))
                     break;
                 if (kb == 0)
                     TC_STAMP(2);
@@ -337,21 +371,22 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                         tma_load_2d(dst + SL::A_BYTES, &map_b, fb, kx, n0);
                     }
                 }
-                dst += SL::STAGE_BYTES;
-                fb += 8;
-                eb += 8;
-                if (++s == SL::STAGES) {
-                    s = 0;
-                    dst = sm0;
-                    fb = full0;
-                    eb = empty0;
-                    if (kb >= SL::STAGES)
-                        ph ^= 1;
-                }
+                s += KSTEP;
+                if (s >= SL::STAGES)
+                    s -= SL::STAGES;
             }
         }
-    } else if (warp == 1) {
+    } else if (warp == 1 || (DUAL && warp == 6)) {
         if (lane == 0) {
+            // Two issuing threads (even ring): warp 1 takes the even k-blocks into the accumulator at
+            // TMEM column 0, warp 6 the odd ones into the accumulator at column BN (with an odd ring
+            // warp 1 issues both, alternating); the epilogue adds the two.  A
+            // k-block costs its issuing thread some 470 cycles (barrier handshake plus four UMMAs of
+            // 57 cycles of issue each) whatever the tile width, more than the tensor pipe needs below
+            // 256 columns, and the two threads' streams run side by side.  The association, (sum of
+            // the even k-blocks) + (sum of the odd ones), each in k order, is the same for every tile
+            // width and launch, so a row's bits still do not depend on what is computed with it.
+            const int which = warp == 1 ? 0 : 1;
             constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((AMN ? 1u : 0u) << 15) |
                                        ((BMN ? 1u : 0u) << 16) | ((uint32_t)(BN >> 3) << 17) |
                                        ((uint32_t)(BM >> 4) << 24);
@@ -364,38 +399,36 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             // one UMMA covers 16 along k: 32 bytes inside a K-major row (+2 in 16-byte units),
             // 16 rows of 128 bytes in an MN-major tile (+128)
             constexpr uint32_t astep = AMN ? 128u : 2u, bstep = BMN ? 128u : 2u;
-            uint32_t alo = alo0, blo = blo0, fb = full0, eb = empty0, ph = 0, acc = 0;
-            int s = 0;
+            int s = which % SL::STAGES;
+            uint32_t ph = (uint32_t)((which / SL::STAGES) & 1);
             bool ok = true;
-            for (int kb = 0; kb < nkb; kb++) {
-                ok = mbar_wait(fb, ph, abort_s, err_flag, 2);
+            for (int kb = which; kb < nkb; kb += KSTEP) {
+                // even k-blocks into the accumulator at column 0, odd ones into the one at column BN;
+                // the first k-block of each overwrites
+                const uint32_t tacc = tmem_base + (uint32_t)((kb & 1) * BN), acc = kb >= 2 ? 1u : 0u;
+                ok = mbar_wait(full0 + 8 * s, ph, abort_s, err_flag, 2);
                 if (!ok)
                     break;
                 if (kb == 0)
                     TC_STAMP(3);
                 fence_after_sync();
                 if (!TC_MODE(2))
-                    umma_bf16_x4<astep, bstep>(tmem_base, alo, blo, idesc, acc);
-                acc = 1u;
-                umma_commit(eb); // frees the stage when these MMAs retire
-                alo += SL::STAGE_BYTES >> 4;
-                blo += SL::STAGE_BYTES >> 4;
-                fb += 8;
-                eb += 8;
-                if (++s == SL::STAGES) {
-                    s = 0;
-                    alo = alo0;
-                    blo = blo0;
-                    fb = full0;
-                    eb = empty0;
+                    umma_bf16_x4<astep, bstep>(tacc, alo0 + s * (SL::STAGE_BYTES >> 4), blo0 + s * (SL::STAGE_BYTES >> 4), idesc,
+                                               acc);
+                umma_commit(empty0 + 8 * s); // frees the stage when these MMAs retire
+                s += KSTEP;
+                if (s >= SL::STAGES) {
+                    s -= SL::STAGES;
                     ph ^= 1;
                 }
             }
-            TC_STAMP(4);
+            if (which == 0)
+                TC_STAMP(4);
             if (ok)
                 umma_commit(smem_u32(tmem_full));
         }
-    } else {
+    }
+    if (warp >= 2 && warp < 6) {
         // epilogue warps 2..5
         const int quarter = warp & 3;
         bool ok = true;
@@ -434,18 +467,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             const uint32_t trow = tmem_base + ((uint32_t)(quarter * 32) << 16);
             // chunks still inside the matrix (uniform over the CTA)
             const int nch = min(NCH, (N - n0 + 31) / 32);
-            // TMEM reads are pipelined one chunk ahead of the arithmetic and the stores.  The loop
-            // is kept rolled (two chunks per trip, one per register set): unrolled over the tile
-            // it would run once through code larger than the instruction cache.
-            uint32_t ra[32], rb[32];
-            if (nkb > 0) {
-                tmem_ld32(trow, ra);
-                tmem_ld_wait();
-            } else {
-#pragma unroll
-                for (int j = 0; j < 32; j++)
-                    ra[j] = rb[j] = 0u;
-            }
+            // Each chunk is the sum of the two issuing threads' accumulators (the second one only
+            // exists from two k-blocks on).  The loop is kept rolled: unrolled over the tile it would
+            // run once through code larger than the instruction cache.
+            const bool dual = nkb > 1;
+            uint32_t ra[32];
             auto chunk = [&](int ch, const uint32_t(&r)[32]) {
                 const int c0 = ch * 32, cc = ch % CPB, blk = ch / CPB;
                 unsigned char *stg = stage0 + (blk & 1) * 4096;
@@ -553,20 +579,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 }
             };
 #pragma unroll 1
-            for (int ch = 0; ch < nch; ch += 2) {
-                const bool more1 = ch + 1 < nch, more2 = ch + 2 < nch;
-                if (nkb > 0 && more1)
-                    tmem_ld32(trow + (uint32_t)((ch + 1) * 32), rb);
-                chunk(ch, ra);
-                if (more1) {
-                    if (nkb > 0)
-                        tmem_ld_wait();
-                    if (nkb > 0 && more2)
-                        tmem_ld32(trow + (uint32_t)((ch + 2) * 32), ra);
-                    chunk(ch + 1, rb);
-                    if (nkb > 0 && more2)
-                        tmem_ld_wait();
+            for (int ch = 0; ch < nch; ch++) {
+                if (nkb > 0) {
+                    tmem_ld32_pair(trow + (uint32_t)(ch * 32), (uint32_t)BN, dual, ra);
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 32; j++)
+                        ra[j] = 0u;
                 }
+                chunk(ch, ra);
             }
             if (threadIdx.x == 64)
                 TC_STAMP(14);
@@ -589,7 +610,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     }
     if (warp == 1) {
         fence_after_sync();
-        tmem_dealloc(tmem_base, BN);
+        tmem_dealloc(tmem_base, 2 * BN);
     }
 }
 
@@ -699,7 +720,8 @@ static int launch(cudaStream_t st, int M, int N, int K, const bf16 *A, long lda,
     const bool timed = pr && pr->n < GemmProfiler::MAX_EV;
     if (timed)
         cudaEventRecord(pr->ev[2 * pr->n], st);
-    launch_k(gemm_tc_kernel<BN, TC, AMN, BMN>, dim3(grid), dim3(192), SL::TOTAL, st, ma, mb, mc, staged, C, ldc, bias, addsrc, M, N, K, err_flag, bias_n);
+    launch_k(gemm_tc_kernel<BN, TC, AMN, BMN>, dim3(grid), dim3(256), SL::TOTAL, st, ma, mb, mc, staged, C, ldc, bias, addsrc,
+             M, N, K, err_flag, bias_n);
     if (timed) {
         cudaEventRecord(pr->ev[2 * pr->n + 1], st);
         pr->flops[pr->n++] = 2.0 * M * N * K;

@@ -38,7 +38,10 @@ def _load(model, z, step=0, rounder=None):
 
 @pytest.mark.parametrize("M,N,K", [(128, 128, 64), (256, 512, 512), (2048, 512, 512), (100, 72, 40),
                                    (32, 16384, 512), (2048, 2048, 512), (4096, 1024, 512), (8, 16, 16),
-                                   (300, 200, 1000)])
+                                   (300, 200, 1000),
+                                   # long contractions into narrow outputs (many k-blocks per tile)
+                                   (2048, 512, 2048), (32, 512, 2048), (100, 72, 2048), (4096, 1024, 4096),
+                                   (130, 200, 1544)])
 @pytest.mark.parametrize("c_f32", [0, 1])
 def test_gemm_tcgen05_and_simt_vs_fp32(pkg, M, N, K, c_f32):
     lib = pkg.library()
@@ -105,6 +108,20 @@ def test_gemm_rows_do_not_depend_on_the_launch(pkg):
                                          part.data_ptr(), N, c_f32, None, None) == 0, lib.nncu_last_error()
             torch.cuda.synchronize()
             assert torch.equal(full[off:off + 32], part), (backend, N)
+    # the second feed-forward projection (K = 2048 into N = 512, with its bias): 32 k-blocks dealt to
+    # the two issuing threads, for 2048 rows and for 32 rows alike
+    a2 = torch.randn(2048, 2048, generator=g).to(torch.bfloat16).cuda()
+    b2 = torch.randn(512, 2048, generator=g).to(torch.bfloat16).cuda()
+    bias = torch.randn(512, generator=g).cuda()
+    full = torch.zeros(2048, 512, device="cuda", dtype=torch.bfloat16)
+    part = torch.zeros(32, 512, device="cuda", dtype=torch.bfloat16)
+    tcg = pkg.abi.GEMM_TCGEN05
+    assert lib.nncu_gemm_bf16_nt(tcg, 2048, 512, 2048, a2.data_ptr(), 2048, b2.data_ptr(), 2048, full.data_ptr(), 512, 0,
+                                 bias.data_ptr(), None) == 0, lib.nncu_last_error()
+    assert lib.nncu_gemm_bf16_nt(tcg, 32, 512, 2048, a2[1000:].data_ptr(), 2048, b2.data_ptr(), 2048, part.data_ptr(), 512,
+                                 0, bias.data_ptr(), None) == 0, lib.nncu_last_error()
+    torch.cuda.synchronize()
+    assert torch.equal(full[1000:1032], part)
 
 
 # ---------------------------------------------------------------- attention op
