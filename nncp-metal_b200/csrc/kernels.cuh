@@ -370,6 +370,62 @@ reduce_cols_kernel(const float *__restrict__ part, int n_parts, int stride, int 
     }
 }
 
+// Every column / stream reduction of one layer's backward pass in one launch.  Job kinds:
+//   0  out[c] = sum over parts p of part[p*stride + off + c], the parts dealt to 8 groups of
+//      consecutive parts whose sums are added in group order (reduce_cols_kernel's association)
+//   1  out[i] (+)= sum over parts (streams) in order of part[p*stride + i]   (reduce_streams_kernel)
+// blk0 is the job's first block; a block finds its job by a short scan (the table is a kernel
+// argument, so the launch can sit in a captured graph).
+struct ReduceJob {
+    const float *part;
+    float *out;
+    int n_parts, stride, n, off, kind, accumulate, blk0;
+};
+constexpr int MAX_REDUCE_JOBS = 16;
+struct ReduceJobs {
+    int n_jobs;
+    ReduceJob job[MAX_REDUCE_JOBS];
+};
+__global__ void __launch_bounds__(256) reduce_jobs_kernel(const __grid_constant__ ReduceJobs jobs)
+{
+    pdl_trigger();
+    pdl_wait();
+    __shared__ float sm[8][33];
+    int j = 0;
+    while (j + 1 < jobs.n_jobs && (int)blockIdx.x >= jobs.job[j + 1].blk0)
+        j++;
+    const ReduceJob &jb = jobs.job[j];
+    const int blk = blockIdx.x - jb.blk0;
+    if (jb.kind == 1) {
+        const int i = blk * 256 + threadIdx.x;
+        if (i < jb.n) {
+            float s = 0.0f;
+            for (int p = 0; p < jb.n_parts; p++)
+                s += jb.part[(size_t)p * jb.stride + i];
+            jb.out[i] = jb.accumulate ? jb.out[i] + s : s;
+        }
+        return;
+    }
+    const int c = blk * 32 + (threadIdx.x & 31), grp = threadIdx.x >> 5;
+    const int per = (jb.n_parts + 7) / 8;
+    float s = 0.0f;
+    if (c < jb.n) {
+        const float *src = jb.part + jb.off + c;
+        const int p1 = min(jb.n_parts, (grp + 1) * per);
+        for (int p = grp * per; p < p1; p++)
+            s += src[(size_t)p * jb.stride];
+    }
+    sm[grp][threadIdx.x & 31] = s;
+    __syncthreads();
+    if (grp == 0 && c < jb.n) {
+        float t = 0.0f;
+#pragma unroll
+        for (int w = 0; w < 8; w++)
+            t += sm[w][threadIdx.x];
+        jb.out[c] = t;
+    }
+}
+
 // dst = a + b (elementwise), used where a residual joins without a norm
 template <typename T>
 __global__ void add_kernel(const T *__restrict__ a, const T *__restrict__ b, T *__restrict__ dst,

@@ -153,6 +153,8 @@ struct nncu_model {
     float *skw = nullptr;   // split-K workspace [SPLITK][TB][D] (models with n_symbols >= SPLITK_MIN_K)
     size_t skw_floats = 0;
     int part_idx = 0;       // regions handed out since the last join
+    ReduceJobs rjobs;       // column / stream reductions queued since the last flush (one launch per layer)
+    int rjob_blocks = 0;
     bool fuse_update = false; // this backward pass applies the optimizer to each bucket as it completes
     float *hyper_dev = nullptr; // {lr, bias correction} of the fused optimizer step
     int32_t *ids_dev, *tgt_dev;
@@ -348,18 +350,39 @@ static int mm_tn(nncu_model *m, int Nout, int Kin, int R, const bf16 *dY, long l
                                         nullptr, 0);
 }
 
-// out_k[c] = sum over parts of part[p*stride + off_k + c], up to three outputs in one launch
-// (on the side stream: only gradient buffers are written, which nobody reads before the join)
+// The column and stream reductions of the backward pass only write gradient buffers, which nobody
+// reads before the optimizer: they are queued and run as ONE launch per layer on the side stream
+// (flush_reductions, in front of the layer's join), instead of a 5 us launch each.
+static int flush_reductions(nncu_model *m)
+{
+    if (m->rjobs.n_jobs == 0)
+        return NNCU_OK;
+    launch_k(reduce_jobs_kernel, dim3(m->rjob_blocks), dim3(256), 0, side_fork(m), m->rjobs);
+    m->rjobs.n_jobs = 0;
+    m->rjob_blocks = 0;
+    KERNEL_CHECK();
+    return NNCU_OK;
+}
+static int queue_reduction(nncu_model *m, int kind, const float *part, int n_parts, int stride, int n, int off, float *out,
+                           int accumulate)
+{
+    if (m->rjobs.n_jobs == MAX_REDUCE_JOBS)
+        NNCU_TRY(flush_reductions(m));
+    ReduceJob &j = m->rjobs.job[m->rjobs.n_jobs++];
+    j.part = part; j.out = out; j.n_parts = n_parts; j.stride = stride; j.n = n; j.off = off; j.kind = kind;
+    j.accumulate = accumulate; j.blk0 = m->rjob_blocks;
+    m->rjob_blocks += kind == 1 ? ceil_div(n, 256) : ceil_div(n, 32);
+    return NNCU_OK;
+}
+// out_k[c] = sum over parts of part[p*stride + off_k + c], up to three outputs
 static int reduce_cols(nncu_model *m, const float *part, int n_parts, int stride, int n, float *o0, int off0,
                        float *o1 = nullptr, int off1 = 0, float *o2 = nullptr, int off2 = 0)
 {
-    ReduceOut ro;
-    ro.out[0] = o0; ro.off[0] = off0;
-    ro.out[1] = o1; ro.off[1] = off1;
-    ro.out[2] = o2; ro.off[2] = off2;
-    int nout = o2 ? 3 : (o1 ? 2 : 1);
-    launch_k(reduce_cols_kernel, dim3(ceil_div(n, 32), nout), dim3(256), 0, side_fork(m), part, n_parts, stride, n, ro);
-    KERNEL_CHECK();
+    NNCU_TRY(queue_reduction(m, 0, part, n_parts, stride, n, off0, o0, 0));
+    if (o1)
+        NNCU_TRY(queue_reduction(m, 0, part, n_parts, stride, n, off1, o1, 0));
+    if (o2)
+        NNCU_TRY(queue_reduction(m, 0, part, n_parts, stride, n, off2, o2, 0));
     return NNCU_OK;
 }
 
@@ -543,8 +566,8 @@ static int forward_range(nncu_model *m, int t0, int t1)
         AT *hpre = at<AT>(a.hpre, (size_t)r0 * F1), *hact = at<AT>(a.hact, (size_t)r0 * F);
         NNCU_TRY((mm_nt<AT, AT>(m, nr, F1, D, u, D, o.ff1, hpre, F1, wf(m, o.ff_bias1))));
         if (sizeof(AT) == 2 && F % 8 == 0 && F1 % 8 == 0)
-            launch_k(act_fwd_vec_kernel, dim3(ceil_div((long long)nr * (F / 8), 256)), dim3(256), 0, m->st, 
-                (const bf16 *)hpre, (bf16 *)hact, nr, F, F1, p.ff_act);
+            launch_k(act_fwd_vec_kernel, dim3(ceil_div((long long)nr * (F / 8), 256)), dim3(256), 0, m->st,
+                     (const bf16 *)hpre, (bf16 *)hact, nr, F, F1, p.ff_act);
         else
             act_fwd_kernel<AT><<<ceil_div((long long)nr * F, 256), 256, 0, m->st>>>(hpre, hact, nr, F, F1, p.ff_act);
         KERNEL_CHECK();
@@ -685,8 +708,8 @@ static int backward(nncu_model *m)
         const bool act_vec = sizeof(AT) == 2 && F % 2 == 0;
         const int act_rows = act_vec ? ACT_BWD_ROWS : 32;
         if (act_vec)
-            launch_k(act_bwd_vec_kernel, dim3(ceil_div(F, 256), ceil_div(TB, act_rows)), dim3(128), 0, m->st, 
-                (const bf16 *)atc<AT>(a.hpre, 0), (const bf16 *)dh, (bf16 *)dhp, apart, TB, F, F1, p.ff_act);
+            launch_k(act_bwd_vec_kernel, dim3(ceil_div(F, 256), ceil_div(TB, act_rows)), dim3(128), 0, m->st,
+                     (const bf16 *)atc<AT>(a.hpre, 0), (const bf16 *)dh, (bf16 *)dhp, apart, TB, F, F1, p.ff_act);
         else
             act_bwd_kernel<AT><<<dim3(ceil_div(F, 128), ceil_div(TB, act_rows)), 128, 0, m->st>>>(
                 atc<AT>(a.hpre, 0), dh, dhp, apart, TB, F, F1, p.ff_act);
@@ -716,17 +739,12 @@ static int backward(nncu_model *m)
                                        m->W + o.b_r, a.o, a.lse, dof, dq, dkv, m->dwr_part, m->dbr_part, m->st,
                                        &pt, (m->bf && o.w_r != NONE) ? m->Wb + o.w_r : nullptr, m->err_flag));
         {
-            // on the side stream: the partials are next written after the join at the layer's end
-            cudaStream_t s2 = side_fork(m);
+            // the partials are next written after the join at the layer's end
             size_t nb = (size_t)m->H * m->L;
-            launch_k(reduce_streams_kernel, dim3(ceil_div(nb, 256)), dim3(256), 0, s2, m->dbr_part, B, nb, gf(m, o.b_r),
-                                                                    p.tied_b_r ? 1 : 0);
-            KERNEL_CHECK();
+            NNCU_TRY(queue_reduction(m, 1, m->dbr_part, B, (int)nb, (int)nb, 0, gf(m, o.b_r), p.tied_b_r ? 1 : 0));
             if (o.w_r != NONE) {
                 size_t nw = (size_t)m->H * p.d_pos * m->dk;
-                launch_k(reduce_streams_kernel, dim3(ceil_div(nw, 256)), dim3(256), 0, s2, m->dwr_part, B, nw, gf(m, o.w_r),
-                                                                        p.tied_w_r ? 1 : 0);
-                KERNEL_CHECK();
+                NNCU_TRY(queue_reduction(m, 1, m->dwr_part, B, (int)nw, (int)nw, 0, gf(m, o.w_r), p.tied_w_r ? 1 : 0));
             }
         }
         // d[w_q ; w_kv] = [dq | dk | dv]^T [memory ; segment] in one contraction over all L*B rows
@@ -742,6 +760,7 @@ static int backward(nncu_model *m)
         } else {
             NNCU_TRY(mm_nn(m, TB, D, 3 * HD, dq, 3 * HD, o.w_q, dxn, D, (const AT *)ds1));
         }
+        NNCU_TRY(flush_reductions(m));
         side_join(m); // this layer's weight gradients are done before dhp, dqkv, ds1, ds2 are rewritten
         {
             // layer l's slots are contiguous; tied tables live in layer 0, which is exchanged last
@@ -759,6 +778,7 @@ static int backward(nncu_model *m)
     CUDA_TRY(cudaMemsetAsync(gf(m, m->embed), 0, sizeof(float) * (size_t)V * D, m->st));
     launch_k(embed_grad_kernel<AT>, dim3(TB), dim3(128), 2 * sizeof(int32_t) * TB, m->st, m->ids_dev, dx, gf(m, m->embed), TB, D, emul, V);
     KERNEL_CHECK();
+    NNCU_TRY(flush_reductions(m));
     side_join(m);
     NNCU_TRY(exchange_bucket(m, m->tail_begin, m->embed_out)); // final norm and the embedding
     NNCU_TRY(opt_range(m, m->tail_begin, m->embed_out, true));
