@@ -205,7 +205,7 @@ def exchange_name(world):
         return "none"
     if os.environ.get("NNCU_PY_ALLREDUCE") == "1":
         return "one all-reduce after backward"
-    return "per-layer reduce-scatter, RMSProp on the rank's shard, all-gather of the weights, overlapped with backward"
+    return "per-layer NCCL all-reduce inside the backward pass (overlapped), every rank applies the whole RMSProp step"
 
 
 def run_reference(args, c):
@@ -228,6 +228,153 @@ def run_reference(args, c):
             "cpu_baseline": {"value": val, "unit": "symbols/s", "cores": threads, "kind": "port",
                              "sample": sample},
             "e2e": {"value": val, "unit": "symbols/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line), flush=True)
+
+
+def decode_step_bytes(c, n_floats):
+    """Algorithmic HBM bytes of one decode step of all streams: every bf16 weight once except the
+    input-embedding table (B rows of it), K and V of the memory and of the segment so far (average
+    T/2 rows), the probability tables written once and read once, the prob0 trees written and read."""
+    D, T, M, V, B, nl = c["d_model"], c["seg_len"], c["mem_len"], c["n_symbols"], c["n_streams"], c["n_layer"]
+    HD = c["n_head"] * c["d_key"]
+    weights = 2 * (n_floats - V * D) + 2 * B * D
+    kv = nl * B * (M + T // 2) * 2 * HD * 2
+    tables = 2 * B * V * 4 + 2 * B * V * 2
+    return weights + kv + tables
+
+
+def run_decode(args, c, name):
+    """Decoding: one-symbol steps (forward, prob0 trees and the range decoder on the device, each
+    step a CUDA graph), then the train step on the decoded segment.  The stream decoded is the one
+    the encoder of the same library produced from seeded synthetic ids; the symbols must come back
+    exactly.  One GPU: a single bit stream decodes serially."""
+    import torch
+    if int(os.environ.get("WORLD_SIZE", "1")) != 1 or args.gpus != 1:
+        if int(os.environ.get("RANK", "0")) == 0:
+            print(json.dumps({"mode": "decode", "unavailable": "one coded stream decodes on one GPU"}), flush=True)
+        return
+    torch.cuda.set_device(0)
+    pkg = entry._package()
+    lib = pkg.library()
+    host = pkg.host
+    kw = dict(COMMON)
+    kw.update(c)
+    kw.update(n_streams_total=c["n_streams"], gemm_backend=args.backend, device=0)
+    p = pkg.abi.make_params(**kw)
+    T, B, V = c["seg_len"], c["n_streams"], c["n_symbols"]
+    K, W = args.steps, max(args.warmup, 3)
+    n_seg = W + K
+    n = n_seg * T * B
+    toks = (synth_tokens(n, V, 4321) if V > 256 else np.random.default_rng(1).integers(0, V, n)).astype(np.uint16)
+    fp = host.file_params(p, block_len=n)
+    ops = host.bind_cuda(p)
+    t0 = time.perf_counter()
+    data, st = host.compress(ops, fp, toks, host.EVAL_SEGMENT, host.OUT_CODER_READY)
+    t_enc = time.perf_counter() - t0
+    host.unbind_cuda(ops)
+    _, nsym, used = host.read_header(data)
+    payload = data[used:]
+
+    # (1) the segment loop on the model's entry points, K segments timed after W
+    m = pkg.TrfModel(p)
+    stream = torch.cuda.Stream()
+    torch.cuda.set_stream(stream)
+    m.set_stream(stream.cuda_stream)
+    stride = n // B
+    lay = toks.reshape(B, stride)            # stream b owns a contiguous slice (block_len % B == 0 here)
+    sampler = ClockSampler(0)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    m.reset()
+    m.decoder_begin(payload)
+    m.set_lr(p.lr)
+    ids0 = np.zeros(B, np.int32)
+    out = np.zeros((n_seg, T, B), np.int32)
+    lib.nncu_profile_begin(0)
+    for sgm in range(n_seg):
+        if sgm == W:
+            torch.cuda.synchronize()
+            lib.nncu_profile_begin(0)
+            sampler.start()
+            tw = time.perf_counter()
+            e0.record(stream)
+        out[sgm] = m.decode_steps(0, T, ids0)
+        m.eval_gradient(out[sgm])
+        m.update()
+        ids0 = out[sgm, T - 1]
+    e1.record(stream)
+    torch.cuda.synchronize()
+    wall = time.perf_counter() - tw
+    clocks = sampler.stop()
+    prof = pkg.abi.Profile()
+    lib.nncu_profile_end(C.byref(prof))
+    consumed = m.decoder_end()
+    ms = max(e0.elapsed_time(e1), wall * 1e3)
+    exact = bool(np.array_equal(out.transpose(2, 0, 1).reshape(B, stride), lay))
+    value = K * T * B / (ms * 1e-3)
+
+    # (2) the decode steps alone (no train step): what the HBM figure is quoted on
+    m.reset()
+    m.decoder_begin(payload)
+    m.decode_steps(0, T, np.zeros(B, np.int32))
+    m.eval_end()
+    torch.cuda.synchronize()
+    e0.record(stream)
+    reps = 3
+    for _ in range(reps):
+        m.decode_steps(0, T, np.zeros(B, np.int32))
+        m.eval_end()
+    e1.record(stream)
+    torch.cuda.synchronize()
+    step_ms = e0.elapsed_time(e1) / (reps * T)
+    m.decoder_end()
+    _, _, _, nfl = m.flat_buffers()
+    m.close()
+    peak_tf, peak_hbm, which, _ = peaks()
+    step_bytes = decode_step_bytes(c, nfl)
+    ach = step_bytes / (step_ms * 1e-3) / 1e9
+
+    # (3) the file-level call a user makes: header parsing, payload upload, block walk, all segments
+    ops = host.bind_cuda(p)
+    t0 = time.perf_counter()
+    back = host.decompress(ops, data, host.OUT_DEVICE)
+    t_file = time.perf_counter() - t0
+    host.unbind_cuda(ops)
+    exact = exact and bool(np.array_equal(back, toks))
+    # and the walk on the host over trees copied back each step (what the device decoder replaces), 2 segments
+    small = toks[: 2 * T * B]
+    fp2 = host.file_params(p, block_len=small.size)
+    ops = host.bind_cuda(p)
+    d2, _ = host.compress(ops, fp2, small, host.EVAL_SEGMENT, host.OUT_CODER_READY)
+    host.unbind_cuda(ops)
+    ops = host.bind_cuda(p)
+    t0 = time.perf_counter()
+    back2 = host.decompress(ops, d2, host.OUT_CODER_READY)
+    t_walk = time.perf_counter() - t0
+    host.unbind_cuda(ops)
+    exact = exact and bool(np.array_equal(back2, small))
+
+    line = {"mode": "decode", "metric": "decoded symbols/s (one-symbol steps + train step per segment)",
+            "value": value, "unit": "symbols/s", "n_gpus": 1, "steps": K, "warmup": W, "ms_per_step": ms / K,
+            "higher_is_better": True, "scaling": "replicas only", "vs_baseline": None,
+            "dtype": "bf16" if p.use_bf16 else "f32", "data": "synthetic",
+            "config": {"workload": workload_name(name, c).replace("train step", "decode (step mode) + train step"),
+                       "tokens": "seeded Zipf(1.1)+order-1 Markov ids, encoded by this library's encoder first",
+                       "l2": "the bf16 weights read by every step exceed the 126 MB L2" if 2 * nfl > 126e6 else
+                             "the bf16 weights fit the 126 MB L2: DRAM traffic is below the algorithmic bytes"},
+            "round_trip_exact": exact, "payload_bytes": len(payload), "payload_bytes_consumed": int(consumed),
+            "bits_per_symbol": 8.0 * len(payload) / n, "gpu_launches": int(prof.launches), "clocks": clocks,
+            "ms_per_symbol_step": step_ms,
+            "e2e": {"value": n / t_file, "unit": "symbols/s", "h2d_bytes_per_step": B * 4 + T * B * 4,
+                    "d2h_bytes_per_step": T * B * 4 + 4, "seconds": t_file,
+                    "what": "nch_decompress over the whole file (bind excluded): payload upload, every segment, "
+                            "symbols written to the host buffer"},
+            "host_walk": {"value": small.size / t_walk, "unit": "symbols/s",
+                          "what": "the same file format decoded with the trees copied to the host every step "
+                                  "(nncu_coder_trees + nch_read_sym_tree), 2 segments"},
+            "encode_symbols_per_s": n / t_enc,
+            "roofline": {"bound": "hbm", "kernel": "one decode step (all kernels of the CUDA graph)", "achieved": ach,
+                         "peak": peak_hbm, "unit": "GB/s", "frac": ach / peak_hbm, "traffic": None,
+                         "peak_source": f"{which} hbm_gbs", "algorithmic_bytes_per_step": step_bytes}}
     print(json.dumps(line), flush=True)
 
 
@@ -331,13 +478,21 @@ def main():
     ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200")
-    ap.add_argument("--config", default="c2", choices=sorted(CONFIGS))
+    ap.add_argument("--config", default=None, choices=sorted(CONFIGS), help="default: c2 (train), c4 (decode)")
+    ap.add_argument("--mode", default="train", choices=["train", "decode"])
     ap.add_argument("--backend", type=int, default=0, help="0 auto, 1 SIMT, 2 tcgen05")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-attention", action="store_true", help="skip the config[1] attention record")
     ap.add_argument("--repeats", type=int, default=7, help="times the K-step region is measured (median reported)")
     args = ap.parse_args()
+    if args.config is None:
+        args.config = "c4" if args.mode == "decode" else "c2"
     c = dict(CONFIGS[args.config])
+    if args.mode == "decode" and args.impl != "reference":
+        if args.steps == 100:
+            args.steps = 8
+        run_decode(args, c, args.config)
+        return
     if args.impl == "reference":
         run_reference(args, c)
         return

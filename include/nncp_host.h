@@ -81,6 +81,11 @@ typedef struct nch_model_ops {
     int (*eval_end)(void *ctx);
     int (*eval_gradient)(void *ctx, const int32_t *expected, float *loss);
     int (*update)(void *ctx);
+    /* range decoder on the device (nncu_decoder_begin / nncu_decode_steps / nncu_decoder_end);
+       all three NULL for a model without one */
+    int (*decoder_begin)(void *ctx, const uint8_t *payload, size_t len);
+    int (*decode_steps)(void *ctx, int t0, int nt, const int32_t *ids_t0, int limit_t, int limit_b, int32_t *symbols);
+    int (*decoder_end)(void *ctx, size_t *bytes_consumed);
 } nch_model_ops;
 
 /* Loads libnncu.so (dlopen), creates a model and fills *ops.  nch_unbind_cuda destroys it. */
@@ -93,6 +98,9 @@ void nch_unbind_cuda(nch_model_ops *ops);
 #define NCH_EVAL_SEGMENT 1  /* one model_eval per segment: --encode_only (nncp.c:3023-3046) */
 #define NCH_OUT_FLOAT 0     /* float tables to the host, write_sym/read_sym on them */
 #define NCH_OUT_CODER_READY 1 /* prob0 paths (encode) / trees (decode) from the device */
+#define NCH_OUT_DEVICE 2      /* decode: the range decoder runs on the device too (encode: as CODER_READY).
+                                 Falls back to CODER_READY when the model has no device decoder or
+                                 refuses the geometry. */
 
 typedef struct nch_block_stats {
     int64_t n_symbols, train_steps;

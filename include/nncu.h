@@ -266,6 +266,35 @@ int nncu_coder_paths_end(nncu_model *m, uint16_t *prob0_host, int *n_bits_out);
  * [nt*B][V] uint16 (entry 0 unused).  read_sym then needs no float math.
  */
 int nncu_coder_trees(nncu_model *m, int t0, int nt, uint16_t *tree_host);
+/*
+ * The range decoder itself on the device (get_bit and read_sym, arith.c:241-310,
+ * cp_utils.c:326-349): decoding needs the symbol of step t before step t+1 can
+ * run, and the reference's decode loop (nncp.c:2996-3022) pays a device-to-host
+ * round trip of the whole probability table for every symbol.  Here the coded
+ * bytes are uploaded once, and each step runs forward, trees and the tree walk
+ * back to back on the device, the decoded symbols feeding the next step's
+ * input there; the host only collects the symbols of the steps it asked for.
+ *
+ * nncu_decoder_begin   uploads payload_host[0, len) and initialises low/range
+ *                      as get_bit_init does.  NNCU_ERR_RANGE when the trees of
+ *                      this n_symbols / n_streams do not fit shared memory (the
+ *                      caller then decodes through nncu_coder_trees).
+ * nncu_decode_steps    steps t0 .. t0+nt-1 of the current segment, t0 == the
+ *                      number of steps done so far.  ids_t0_host [B] are the
+ *                      inputs of step t0 (required when t0 == 0, else optional:
+ *                      NULL keeps the symbols decoded at t0-1).  Streams past
+ *                      the end of a block are skipped and yield 0: at step
+ *                      t == limit_t those with index >= limit_b, and every
+ *                      stream at t > limit_t (limit_t >= seg_len: none).
+ *                      symbols_host [nt][B] receives the symbols; they are also
+ *                      left in place as the targets of the gradient pass, which
+ *                      nncu_eval_gradient overwrites with the same values.
+ * nncu_decoder_end     reports how many payload bytes were consumed.
+ */
+int nncu_decoder_begin(nncu_model *m, const uint8_t *payload_host, size_t len);
+int nncu_decode_steps(nncu_model *m, int t0, int nt, const int32_t *ids_t0_host,
+                      int limit_t, int limit_b, int32_t *symbols_host);
+int nncu_decoder_end(nncu_model *m, size_t *bytes_consumed);
 
 /* ---- isolated attention op (the sub-graph nncp.c:722-800 and its autograd) ----
  * All pointers are device memory.  dtype_bf16 selects bf16 or fp32 for

@@ -112,6 +112,9 @@ PROTOTYPES = {
     "nncu_coder_paths_begin": (_i, [_vp, _i, _i, _vp]),
     "nncu_coder_paths_end": (_i, [_vp, _vp, C.POINTER(_i)]),
     "nncu_coder_trees": (_i, [_vp, _i, _i, _vp]),
+    "nncu_decoder_begin": (_i, [_vp, _vp, C.c_size_t]),
+    "nncu_decode_steps": (_i, [_vp, _i, _i, _vp, _i, _i, _vp]),
+    "nncu_decoder_end": (_i, [_vp, C.POINTER(C.c_size_t)]),
     "nncu_attention_forward": (_i, [C.POINTER(AttnShape), _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "nncu_attention_backward": (_i, [C.POINTER(AttnShape)] + [_vp] * 12),
     "nncu_attention_backward_noalloc": (_i, [C.POINTER(AttnShape)] + [_vp] * 12),

@@ -218,9 +218,10 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     extern __shared__ unsigned char smraw_[];
     unsigned char *sm = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smraw_) + 1023) & ~(uintptr_t)1023);
     uint64_t *bars = reinterpret_cast<uint64_t *>(sm + FwdSmem::BAR);
-    // bars: 0 load, 1 free (smem reusable), 2 se (S and E in TMEM), 3 p (P in smem, S/E consumed),
-    //       4 o (O block in TMEM), 5 tfree (O block consumed)
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 6);
+    // bars: 0 load (Q, K, table window), 1 free (V reusable), 2 se (S and E in TMEM: K and the window
+    //       reusable), 3 p (P in smem, S/E consumed), 4 o (O block in TMEM), 5 tfree (O block consumed),
+    //       6 load of V
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 7);
     volatile int *abort_s = reinterpret_cast<volatile int *>(tmem_slot + 1);
     float *brs = reinterpret_cast<float *>(sm + FwdSmem::BRS);
     float *xch = reinterpret_cast<float *>(sm + FwdSmem::XCH);
@@ -245,6 +246,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         mbar_init(smem_u32(&bars[3]), NROW);
         mbar_init(smem_u32(&bars[4]), 1);
         mbar_init(smem_u32(&bars[5]), NROW);
+        mbar_init(smem_u32(&bars[6]), 1);
         *abort_s = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -260,18 +262,21 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     if (threadIdx.x == 0)
         ATC_STAMP(1);
     const uint32_t bar_load = smem_u32(&bars[0]), bar_free = smem_u32(&bars[1]), bar_se = smem_u32(&bars[2]),
-                   bar_p = smem_u32(&bars[3]), bar_o = smem_u32(&bars[4]), bar_tfree = smem_u32(&bars[5]);
+                   bar_p = smem_u32(&bars[3]), bar_o = smem_u32(&bars[4]), bar_tfree = smem_u32(&bars[5]),
+                   bar_loadv = smem_u32(&bars[6]);
 
     if (warp == 0) {
         if (lane == 0) {
             int it = 0;
+            // K and the table window of the next block are fetched as soon as this block's S and E are in
+            // TMEM, under its softmax and PV product; only V waits for the PV product to finish
             for (int kb = kbs.lo; kb <= kbs.hi; kb++, it++) {
                 const int j0 = kb * KB;
-                if (it > 0 && !mbar_wait(bar_free, (uint32_t)((it - 1) & 1), abort_s, err_flag, 11))
+                if (it > 0 && !mbar_wait(bar_se, (uint32_t)((it - 1) & 1), abort_s, err_flag, 11))
                     break;
                 const int wlo = j0 - 63 + c0;
                 const int wrow = wlo < -(WIN - 2) ? 0 : wlo; // a window wholly below the table: row 0 alone is used
-                uint32_t bytes = 2 * 256 * 128 + (has_wr ? WIN * 128 : 0) + (it == 0 ? 128 * 128 : 0);
+                uint32_t bytes = 256 * 128 + (has_wr ? WIN * 128 : 0) + (it == 0 ? 128 * 128 : 0);
                 mbar_expect_tx(bar_load, bytes);
                 if (it == 0) {
                     tma_load_3d(sm0 + FwdSmem::Q, &map_q, bar_load, h * DK, b0, 0);
@@ -281,8 +286,11 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                 tma_load_3d(sm0 + FwdSmem::K + 128 * 128, &map_kv, bar_load, h * DK, b0 + 1, j0);
                 if (has_wr)
                     tma_load_3d(sm0 + FwdSmem::R, &map_wr, bar_load, 0, wrow, h);
-                tma_load_3d(sm0 + FwdSmem::V, &map_kv, bar_load, HD + h * DK, b0, j0);
-                tma_load_3d(sm0 + FwdSmem::V + 128 * 128, &map_kv, bar_load, HD + h * DK, b0 + 1, j0);
+                if (it > 0 && !mbar_wait(bar_free, (uint32_t)((it - 1) & 1), abort_s, err_flag, 17))
+                    break;
+                mbar_expect_tx(bar_loadv, 256 * 128);
+                tma_load_3d(sm0 + FwdSmem::V, &map_kv, bar_loadv, HD + h * DK, b0, j0);
+                tma_load_3d(sm0 + FwdSmem::V + 128 * 128, &map_kv, bar_loadv, HD + h * DK, b0 + 1, j0);
             }
         }
     } else if (warp == 1) {
@@ -310,6 +318,8 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                 umma_commit(bar_se);
                 if (it == 0) ATC_STAMP(3);
                 if (!mbar_wait(bar_p, (uint32_t)(it & 1), abort_s, err_flag, 14))
+                    break;
+                if (!mbar_wait(bar_loadv, (uint32_t)(it & 1), abort_s, err_flag, 18))
                     break;
                 fence_after_sync();
                 if (it == 0) ATC_STAMP(5);

@@ -34,6 +34,7 @@
 #include "gemm_simt.cuh"
 #include "gemm_tc.cuh"
 #include "kernels.cuh"
+#include "decoder.cuh"
 
 thread_local char g_nncu_err[512] = "";
 unsigned long long g_nncu_launches = 0;
@@ -129,6 +130,12 @@ struct nncu_model {
         int calls;
     } graphs[3][2]; // [forward, backward, backward with the optimizer step][memory twin]
     bool graphs_on;
+    std::vector<StepGraph> step_graphs; // device decoder: one-symbol step + trees + decode, [t][memory twin]
+    uint8_t *dec_payload = nullptr;     // the coded bytes on the device (nncu_decoder_begin)
+    size_t dec_cap = 0;
+    dec::State *dec_state = nullptr;
+    int dec_ring = 0;
+    bool dec_open = false;
     // gradient exchange between ranks (nncu_comm_init): per-layer all-reduces on a third stream,
     // issued as soon as a layer's gradients are complete, so they overlap the rest of backward
     void *comm;
@@ -473,9 +480,8 @@ static nncu_attn_shape attn_shape(nncu_model *m, int l, int t0, int t1)
 enum { GRAPH_FWD = 0, GRAPH_BWD = 1, GRAPH_BWD_UPD = 2, N_GRAPH_KINDS = 3 };
 
 template <typename F>
-static int run_graphed(nncu_model *m, int kind, F body)
+static int run_graphed(nncu_model *m, nncu_model::StepGraph &g, F body)
 {
-    nncu_model::StepGraph &g = m->graphs[kind][m->cur];
     const bool can = m->graphs_on && m->st != nullptr && m->st != cudaStreamLegacy && !g_nncu_prof;
     if (!can)
         return body();
@@ -512,6 +518,12 @@ static int run_graphed(nncu_model *m, int kind, F body)
     CUDA_TRY(cudaGraphLaunch(g.exec, m->st));
     g_nncu_launches += g.launches;
     return NNCU_OK;
+}
+
+template <typename F>
+static int run_graphed(nncu_model *m, int kind, F body)
+{
+    return run_graphed(m, m->graphs[kind][m->cur], body);
 }
 
 // ------------------------------------------------------------------ forward
@@ -956,6 +968,11 @@ int nncu_destroy(nncu_model *m)
         for (int c = 0; c < 2; c++)
             if (m->graphs[k][c].exec)
                 cudaGraphExecDestroy(m->graphs[k][c].exec);
+    for (auto &g : m->step_graphs)
+        if (g.exec)
+            cudaGraphExecDestroy(g.exec);
+    if (m->dec_payload) cudaFree(m->dec_payload);
+    if (m->dec_state) cudaFree(m->dec_state);
     if (m->st3) cudaStreamSynchronize(m->st3);
     if (m->comm && nccl_api())
         nccl_api()->CommDestroy(m->comm);
@@ -1713,6 +1730,123 @@ int nncu_coder_trees(nncu_model *m, int t0, int nt, uint16_t *tree_host)
     KERNEL_CHECK();
     CUDA_TRY(cudaMemcpyAsync(tree_host, m->coder_dev, sizeof(uint16_t) * (size_t)rows * m->V, cudaMemcpyDeviceToHost, m->st));
     CUDA_TRY(cudaStreamSynchronize(m->st));
+    return NNCU_OK;
+}
+
+// ---- range decoder on the device (decoder.cuh)
+
+int nncu_decoder_begin(nncu_model *m, const uint8_t *payload_host, size_t len)
+{
+    if (!m || (!payload_host && len))
+        return nncu_fail(NNCU_ERR_INVALID, "null argument");
+    const int nb = coder_bits(m->V);
+    if (nb < 1)
+        return nncu_fail(NNCU_ERR_INVALID, "the device decoder needs a power-of-two n_symbols");
+    const int ring = dec::ring_slots(m->B, m->V, nb);
+    if (ring < 2 || (size_t)2 * m->V * 4 > 200 * 1024)
+        return nncu_fail(NNCU_ERR_RANGE, "n_symbols %d with %d streams does not fit the decoder's shared memory", m->V, m->B);
+    CUDA_TRY(cudaSetDevice(m->device));
+    CUDA_TRY(cudaStreamSynchronize(m->st));
+    const size_t need = len + 16;
+    if (need > m->dec_cap) {
+        if (m->dec_payload)
+            cudaFree(m->dec_payload);
+        m->dec_payload = nullptr;
+        m->dec_cap = 0;
+        CUDA_TRY(cudaMalloc(&m->dec_payload, need));
+        m->dec_cap = need;
+    }
+    if (!m->dec_state)
+        CUDA_TRY(cudaMalloc(&m->dec_state, sizeof(dec::State)));
+    if (len)
+        CUDA_TRY(cudaMemcpyAsync(m->dec_payload, payload_host, len, cudaMemcpyHostToDevice, m->st));
+    // the state after get_bit_init (arith.c:241-262): three bytes pulled into low, range at its top
+    dec::State s0;
+    memset(&s0, 0, sizeof(s0));
+    s0.len = len;
+    for (int i = 0; i < 3; i++) {
+        s0.low <<= 8;
+        if (s0.pos < len)
+            s0.low += payload_host[s0.pos++];
+    }
+    s0.range = dec::R_TOP;
+    CUDA_TRY(cudaMemcpyAsync(m->dec_state, &s0, sizeof(s0), cudaMemcpyHostToDevice, m->st));
+    CUDA_TRY(cudaStreamSynchronize(m->st));
+    CUDA_TRY(cudaFuncSetAttribute(dec::decode_step_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                  (int)dec::smem_bytes(m->B, m->V, nb, ring)));
+    m->dec_ring = ring;
+    m->dec_open = true;
+    if (m->step_graphs.empty())
+        m->step_graphs.assign((size_t)2 * m->T, nncu_model::StepGraph{nullptr, 0, 0});
+    return NNCU_OK;
+}
+
+// one decode step: the model's one-symbol forward, the prob0 trees of its B rows, and the walk that
+// turns them into symbols (left in the target rows and, for t+1 < seg_len, the next step's input)
+static int decode_step(nncu_model *m, int t, int limit_t, int limit_b)
+{
+    const int B = m->B, V = m->V, nb = coder_bits(V);
+    NNCU_TRY(m->bf ? forward_range<bf16>(m, t, t + 1) : forward_range<float>(m, t, t + 1));
+    launch_k(coder_trees_kernel, dim3(B), dim3(256), (size_t)2 * V * 4, m->st, (const float *)(m->probs + (size_t)t * B * V),
+             m->coder_dev, V);
+    KERNEL_CHECK();
+    launch_k(dec::decode_step_kernel, dim3(1), dim3(32), dec::smem_bytes(B, V, nb, m->dec_ring), m->st,
+             (const uint16_t *)m->coder_dev, (const uint8_t *)m->dec_payload, m->dec_state, m->tgt_dev + (size_t)t * B,
+             t + 1 < m->T ? m->ids_dev + (size_t)(t + 1) * B : (int32_t *)nullptr, t, limit_t, limit_b, B, V, nb,
+             m->dec_ring, m->err_flag);
+    KERNEL_CHECK();
+    return NNCU_OK;
+}
+
+int nncu_decode_steps(nncu_model *m, int t0, int nt, const int32_t *ids_t0_host, int limit_t, int limit_b,
+                      int32_t *symbols_host)
+{
+    if (!m || !symbols_host || t0 < 0 || nt < 1 || t0 + nt > m->T || limit_t < 0 || limit_b < 0)
+        return nncu_fail(NNCU_ERR_INVALID, "bad decode range");
+    if (!m->dec_open)
+        return nncu_fail(NNCU_ERR_STATE, "nncu_decode_steps without nncu_decoder_begin");
+    if (t0 != m->steps_done)
+        return nncu_fail(NNCU_ERR_STATE, "step %d issued after %d steps", t0, m->steps_done);
+    if (t0 == 0 && !ids_t0_host)
+        return nncu_fail(NNCU_ERR_INVALID, "the first step of a segment needs its input symbols");
+    CUDA_TRY(cudaSetDevice(m->device));
+    const int B = m->B;
+    if (ids_t0_host) {
+        CUDA_TRY(cudaEventSynchronize(m->ev_ids));
+        memcpy(m->ids_pin + (size_t)t0 * B, ids_t0_host, sizeof(int32_t) * B);
+        CUDA_TRY(cudaMemcpyAsync(m->ids_dev + (size_t)t0 * B, m->ids_pin + (size_t)t0 * B, sizeof(int32_t) * B,
+                                 cudaMemcpyHostToDevice, m->st));
+        CUDA_TRY(cudaEventRecord(m->ev_ids, m->st));
+    }
+    bind_xin(m);
+    const bool full = limit_t >= m->T; // every stream active at every step: the shape the graphs hold
+    for (int t = t0; t < t0 + nt; t++) {
+        auto body = [&]() { return decode_step(m, t, limit_t, limit_b); };
+        NNCU_TRY(full ? run_graphed(m, m->step_graphs[(size_t)2 * t + m->cur], body) : body());
+        m->steps_done = t + 1;
+    }
+    m->have_forward = (m->steps_done == m->T);
+    CUDA_TRY(cudaEventSynchronize(m->ev_sym));
+    CUDA_TRY(cudaMemcpyAsync(m->sym_pin, m->tgt_dev + (size_t)t0 * B, sizeof(int32_t) * (size_t)nt * B, cudaMemcpyDeviceToHost,
+                             m->st));
+    NNCU_TRY(check_err_flag(m)); // drains the stream
+    memcpy(symbols_host, m->sym_pin, sizeof(int32_t) * (size_t)nt * B);
+    return NNCU_OK;
+}
+
+int nncu_decoder_end(nncu_model *m, size_t *bytes_consumed)
+{
+    if (!m)
+        return nncu_fail(NNCU_ERR_INVALID, "null model");
+    if (!m->dec_open)
+        return nncu_fail(NNCU_ERR_STATE, "nncu_decoder_end without nncu_decoder_begin");
+    CUDA_TRY(cudaSetDevice(m->device));
+    dec::State s;
+    CUDA_TRY(cudaMemcpyAsync(&s, m->dec_state, sizeof(s), cudaMemcpyDeviceToHost, m->st));
+    CUDA_TRY(cudaStreamSynchronize(m->st));
+    if (bytes_consumed)
+        *bytes_consumed = (size_t)s.pos;
+    m->dec_open = false;
     return NNCU_OK;
 }
 

@@ -10,7 +10,7 @@ from .loader import HOSTLIB, LIB, LibraryMissing
 
 INTERP_MAX_STEPS = 8
 EVAL_STEP, EVAL_SEGMENT = 0, 1
-OUT_FLOAT, OUT_CODER_READY = 0, 1
+OUT_FLOAT, OUT_CODER_READY, OUT_DEVICE = 0, 1, 2
 _vp = C.c_void_p
 
 
@@ -46,13 +46,17 @@ FN_PROBS = C.CFUNCTYPE(_I, _vp, _I, _I, C.POINTER(C.c_float))
 FN_PATHS = C.CFUNCTYPE(_I, _vp, _I, _I, C.POINTER(C.c_int32), C.POINTER(C.c_uint16), C.POINTER(_I))
 FN_TREES = C.CFUNCTYPE(_I, _vp, _I, _I, C.POINTER(C.c_uint16))
 FN_GRAD = C.CFUNCTYPE(_I, _vp, C.POINTER(C.c_int32), C.POINTER(C.c_float))
+FN_DEC_BEGIN = C.CFUNCTYPE(_I, _vp, C.POINTER(C.c_uint8), C.c_size_t)
+FN_DEC_STEPS = C.CFUNCTYPE(_I, _vp, _I, _I, C.POINTER(C.c_int32), _I, _I, C.POINTER(C.c_int32))
+FN_DEC_END = C.CFUNCTYPE(_I, _vp, C.POINTER(C.c_size_t))
 
 
 class ModelOps(C.Structure):
     _fields_ = [("ctx", _vp), ("n_streams", _I), ("seg_len", _I), ("n_symbols", _I),
                 ("reset", FN_CTX), ("set_lr", FN_SET_LR), ("eval", FN_EVAL), ("read_probs", FN_PROBS),
                 ("coder_paths", FN_PATHS), ("coder_trees", FN_TREES), ("eval_end", FN_CTX),
-                ("eval_gradient", FN_GRAD), ("update", FN_CTX)]
+                ("eval_gradient", FN_GRAD), ("update", FN_CTX), ("decoder_begin", FN_DEC_BEGIN),
+                ("decode_steps", FN_DEC_STEPS), ("decoder_end", FN_DEC_END)]
 
 
 _lib = None

@@ -215,7 +215,7 @@ size_t nncpm_lossless_decompress(const uint8_t *in, size_t n, uint8_t *out, size
     if (!sym) {
         set_err("out of memory");
     } else {
-        int rc = nch_decompress(&ops, &fp, stream + used, slen - used, nsym, NCH_OUT_CODER_READY, sym);
+        int rc = nch_decompress(&ops, &fp, stream + used, slen - used, nsym, NCH_OUT_DEVICE, sym);
         if (rc != NCH_OK) {
             set_err("decompression failed (status %d)", rc);
         } else {

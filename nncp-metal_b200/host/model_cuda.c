@@ -23,6 +23,9 @@ typedef struct {
     int (*eval_end)(nncu_model *);
     int (*eval_gradient)(nncu_model *, const int32_t *, float *);
     int (*update)(nncu_model *);
+    int (*decoder_begin)(nncu_model *, const uint8_t *, size_t);
+    int (*decode_steps)(nncu_model *, int, int, const int32_t *, int, int, int32_t *);
+    int (*decoder_end)(nncu_model *, size_t *);
 } cuda_ctx;
 
 static int c_reset(void *c) { cuda_ctx *x = c; return x->reset(x->model); }
@@ -38,6 +41,13 @@ static int c_trees(void *c, int t0, int nt, uint16_t *o) { cuda_ctx *x = c; retu
 static int c_eval_end(void *c) { cuda_ctx *x = c; return x->eval_end(x->model); }
 static int c_grad(void *c, const int32_t *e, float *l) { cuda_ctx *x = c; return x->eval_gradient(x->model, e, l); }
 static int c_update(void *c) { cuda_ctx *x = c; return x->update(x->model); }
+static int c_dec_begin(void *c, const uint8_t *p, size_t n) { cuda_ctx *x = c; return x->decoder_begin(x->model, p, n); }
+static int c_dec_steps(void *c, int t0, int nt, const int32_t *ids, int lt, int lb, int32_t *out)
+{
+    cuda_ctx *x = c;
+    return x->decode_steps(x->model, t0, nt, ids, lt, lb, out);
+}
+static int c_dec_end(void *c, size_t *n) { cuda_ctx *x = c; return x->decoder_end(x->model, n); }
 
 int nch_bind_cuda(const char *libnncu_path, const nncu_params *p, nch_model_ops *ops)
 {
@@ -63,6 +73,9 @@ int nch_bind_cuda(const char *libnncu_path, const nncu_params *p, nch_model_ops 
     x->eval_end = dlsym(x->dl, "nncu_eval_end");
     x->eval_gradient = dlsym(x->dl, "nncu_eval_gradient");
     x->update = dlsym(x->dl, "nncu_update");
+    x->decoder_begin = dlsym(x->dl, "nncu_decoder_begin");
+    x->decode_steps = dlsym(x->dl, "nncu_decode_steps");
+    x->decoder_end = dlsym(x->dl, "nncu_decoder_end");
     if (!create || !x->destroy || !x->reset || !x->set_lr || !x->eval || !x->read_probs || !x->coder_paths ||
         !x->coder_trees || !x->eval_end || !x->eval_gradient || !x->update || create(p, &x->model) != NNCU_OK) {
         dlclose(x->dl);
@@ -82,6 +95,11 @@ int nch_bind_cuda(const char *libnncu_path, const nncu_params *p, nch_model_ops 
     ops->eval_end = c_eval_end;
     ops->eval_gradient = c_grad;
     ops->update = c_update;
+    if (x->decoder_begin && x->decode_steps && x->decoder_end) {
+        ops->decoder_begin = c_dec_begin;
+        ops->decode_steps = c_dec_steps;
+        ops->decoder_end = c_dec_end;
+    }
     return NCH_OK;
 }
 

@@ -132,6 +132,8 @@ int nch_process_block(const nch_model_ops *m, nch_enc *enc, nch_dec *dec, uint16
     const int B = m->n_streams, T = m->seg_len, V = m->n_symbols;
     if (dec)
         eval_mode = NCH_EVAL_STEP; /* the next input is the symbol just decoded */
+    if (out_mode == NCH_OUT_DEVICE)
+        out_mode = NCH_OUT_CODER_READY; /* the device decoder is nch_decompress's; here the walk is the host's */
     if (out_mode == NCH_OUT_CODER_READY && (log2_exact(V) < 1 || !m->coder_paths || !m->coder_trees))
         out_mode = NCH_OUT_FLOAT;
     const int stride = block_len / B, rem = block_len % B;
@@ -217,6 +219,58 @@ done:
     free(io.syms);
     free(io.coded);
     free(io.probs);
+    return rc;
+}
+
+/* The decode side of process_block with the range decoder on the device: the same walk over the
+   block (full segments decoded and trained on, then the untrained tail), one decode_steps call per
+   segment instead of one eval + tree download + host walk per symbol. */
+static int decode_block_device(const nch_model_ops *m, uint16_t *block_buf, int block_len,
+                               const nch_interp_params *lr, int64_t *train_step)
+{
+    const int B = m->n_streams, T = m->seg_len;
+    const int stride = block_len / B, rem = block_len % B;
+    int32_t *ids0 = (int32_t *)calloc((size_t)B, sizeof(int32_t));
+    int32_t *syms = (int32_t *)calloc((size_t)T * B, sizeof(int32_t));
+    int rc = NCH_OK;
+    if (!ids0 || !syms) {
+        rc = NCH_ERR_NOMEM;
+        goto done;
+    }
+    if (m->reset(m->ctx)) { rc = NCH_ERR_MODEL; goto done; }
+    int pos = 0;
+    while (pos + T <= stride) {
+        for (int b = 0; b < B; b++)
+            ids0[b] = nch_get_symb(block_buf, stride, rem, b, pos - 1);
+        if (m->decode_steps(m->ctx, 0, T, ids0, T, 0, syms)) { rc = NCH_ERR_MODEL; goto done; }
+        for (int t = 0; t < T; t++)
+            for (int b = 0; b < B; b++)
+                nch_put_symb(block_buf, stride, rem, b, pos + t, syms[t * B + b]);
+        float loss = 0.0f;
+        if (m->set_lr(m->ctx, nch_interp(lr, *train_step)) || m->eval_gradient(m->ctx, syms, &loss) ||
+            m->update(m->ctx)) {
+            rc = NCH_ERR_MODEL;
+            goto done;
+        }
+        (*train_step)++;
+        pos += T;
+    }
+    {
+        const int tail2 = stride - pos, tail1 = tail2 + (rem != 0);
+        if (tail1 > 0) {
+            for (int b = 0; b < B; b++)
+                ids0[b] = nch_get_symb(block_buf, stride, rem, b, pos - 1);
+            if (m->decode_steps(m->ctx, 0, tail1, ids0, tail2, rem, syms)) { rc = NCH_ERR_MODEL; goto done; }
+            for (int t = 0; t < tail1; t++)
+                for (int b = 0; b < B; b++)
+                    if (t < tail2 || b < rem)
+                        nch_put_symb(block_buf, stride, rem, b, pos + t, syms[t * B + b]);
+            if (m->eval_end(m->ctx)) { rc = NCH_ERR_MODEL; goto done; }
+        }
+    }
+done:
+    free(ids0);
+    free(syms);
     return rc;
 }
 
@@ -481,12 +535,30 @@ int nch_decompress(const nch_model_ops *m, const nch_file_params *fp, const uint
 {
     if (!m || !fp || (!payload && n) || (!symbols_out && n_symbols_in_file))
         return NCH_ERR_INVALID;
-    nch_dec *dec = nch_dec_new(payload, n);
-    if (!dec)
-        return NCH_ERR_NOMEM;
     int rc = NCH_OK;
     int64_t train_step = 0;
     size_t pos = 0, total = n_symbols_in_file;
+    if (out_mode == NCH_OUT_DEVICE) {
+        /* a model without a device decoder, or one that refuses this geometry, decodes on the host */
+        if (m->decoder_begin && m->decode_steps && m->decoder_end && log2_exact(m->n_symbols) >= 1 &&
+            m->decoder_begin(m->ctx, payload, n) == 0) {
+            while (pos < total) {
+                int bl = next_block_len(fp, pos, total - pos);
+                rc = decode_block_device(m, symbols_out + pos, bl, &fp->lr, &train_step);
+                if (rc)
+                    break;
+                pos += (size_t)bl;
+            }
+            size_t used = 0;
+            if (m->decoder_end(m->ctx, &used) && !rc)
+                rc = NCH_ERR_MODEL;
+            return rc;
+        }
+        out_mode = NCH_OUT_CODER_READY;
+    }
+    nch_dec *dec = nch_dec_new(payload, n);
+    if (!dec)
+        return NCH_ERR_NOMEM;
     while (pos < total) {
         int bl = next_block_len(fp, pos, total - pos);
         rc = nch_process_block(m, NULL, dec, symbols_out + pos, bl, &fp->lr, &train_step, NCH_EVAL_STEP,

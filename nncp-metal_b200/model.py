@@ -170,3 +170,21 @@ class TrfModel:
         out = np.zeros((nt * self.B, self.V), np.uint16)
         self._ck(self.lib.nncu_coder_trees(self.h, t0, nt, _ptr(out)))
         return out
+
+    # --- range decoder on the device ------------------------------------
+    def decoder_begin(self, payload):
+        buf = np.frombuffer(bytes(payload), np.uint8)
+        self._ck(self.lib.nncu_decoder_begin(self.h, _ptr(buf) if buf.size else None, buf.size))
+
+    def decode_steps(self, t0, nt, ids_t0=None, limit_t=None, limit_b=0):
+        """Steps t0 .. t0+nt-1: returns the decoded symbols [nt][B]."""
+        ids = None if ids_t0 is None else np.ascontiguousarray(ids_t0, np.int32)
+        out = np.zeros((nt, self.B), np.int32)
+        self._ck(self.lib.nncu_decode_steps(self.h, t0, nt, None if ids is None else _ptr(ids),
+                                            self.T if limit_t is None else limit_t, limit_b, _ptr(out)))
+        return out
+
+    def decoder_end(self):
+        n = C.c_size_t()
+        self._ck(self.lib.nncu_decoder_end(self.h, C.byref(n)))
+        return n.value

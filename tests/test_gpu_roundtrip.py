@@ -32,8 +32,9 @@ CASES = {
 
 
 @pytest.mark.parametrize("name", sorted(CASES))
-@pytest.mark.parametrize("out_mode", [0, 1])
+@pytest.mark.parametrize("out_mode", [0, 1, 2])
 def test_round_trip_is_bit_exact(pkg, name, out_mode):
+    """out_mode 2: the range decoder runs on the device as well (nncu_decode_steps)."""
     kw, n, block_len = CASES[name]
     if out_mode == 0 and kw["n_symbols"] > 256:
         pytest.skip("float tables of 4096 symbols per position: covered by the coder-ready mode")
@@ -48,6 +49,60 @@ def test_round_trip_is_bit_exact(pkg, name, out_mode):
     back = pkg.host.decompress(dec, data, out_mode)
     pkg.host.unbind_cuda(dec)
     assert np.array_equal(back, syms)
+
+
+def test_device_decoder_steps_match_the_host_walk(pkg):
+    """nncu_decode_steps against nch_read_sym_tree over nncu_coder_trees, step by step on two models
+    with identical weights: the same symbols, and the same number of payload bytes consumed.  The
+    payload is random bytes (any byte string decodes to something), the second call starts in the
+    middle of a segment, and the last one has a ragged limit."""
+    import ctypes as C
+    kw = dict(n_layer=1, d_model=64, n_head=2, d_key=32, d_inner=128, d_pos=24, mem_len=16, seg_len=8,
+              n_streams=5, n_symbols=512, use_bf16=0, lr=2e-3, init_range=0.05)
+    p = pkg.abi.make_params(**kw)
+    T, B, V = 8, 5, 512
+    rng = np.random.default_rng(11)
+    payload = rng.integers(0, 256, 4000, dtype=np.uint8).tobytes()
+    L = pkg.host.library()
+    dev, ref = pkg.TrfModel(p), pkg.TrfModel(p)
+    for m in (dev, ref):
+        m.reset()
+    dev.decoder_begin(payload)
+    buf = C.create_string_buffer(payload, len(payload))
+    hd = L.nch_dec_new(buf, len(payload))
+    ids0 = rng.integers(0, V, B).astype(np.int32)
+
+    def host_steps(t0, nt, ids_first, limit_t, limit_b):
+        out = np.zeros((nt, B), np.int32)
+        ids = np.zeros((T, B), np.int32)
+        for t in range(t0, t0 + nt):
+            ids[t] = ids_first if t == t0 else out[t - t0 - 1]
+            ref.eval(t, ids, read=False)
+            trees = np.ascontiguousarray(ref.coder_trees(t, 1))
+            for b in range(B):
+                if t < limit_t or (t == limit_t and b < limit_b):
+                    out[t - t0, b] = L.nch_read_sym_tree(hd, trees[b].ctypes.data_as(C.c_void_p), V)
+        return out
+
+    a = dev.decode_steps(0, 3, ids0)
+    b = host_steps(0, 3, ids0, T, 0)
+    assert np.array_equal(a, b)
+    a2 = dev.decode_steps(3, 5)                      # continues from the symbols decoded at step 2
+    b2 = host_steps(3, 5, b[-1], T, 0)
+    assert np.array_equal(a2, b2)
+    tg = np.concatenate([a, a2]).astype(np.int32)
+    for m in (dev, ref):
+        m.set_lr(2e-3)
+        m.eval_gradient(tg)
+        m.update()
+    assert dev.weights_hash() == ref.weights_hash()
+    a3 = dev.decode_steps(0, 4, a2[-1], limit_t=3, limit_b=2)   # a block tail: 3 full steps + 2 streams
+    b3 = host_steps(0, 4, b2[-1], 3, 2)
+    assert np.array_equal(a3, b3) and not a3[3, 2:].any()
+    assert dev.decoder_end() > 0
+    L.nch_dec_free(hd)
+    dev.close()
+    ref.close()
 
 
 def test_coder_ready_and_float_output_give_the_same_file(pkg):

@@ -169,7 +169,7 @@ def test_header_layout_and_round_trip(pkg):
             pkg.host.read_header(bad)
 
 
-def _oracle_ops(pkg, model):
+def _oracle_ops(pkg, model, with_decoder=False):
     """nch_model_ops backed by the CPU oracle (tests only)."""
     H = pkg.host
     T, B, V = model.T, model.B, model.V
@@ -199,6 +199,40 @@ def _oracle_ops(pkg, model):
                    H.FN_CTX(lambda c: (model.update(), 0)[1])]
     f = keep["fns"]
     ops = H.ModelOps(None, B, T, V, f[0], f[1], f[2], f[3], H.FN_PATHS(), H.FN_TREES(), f[4], f[5], f[6])
+    if with_decoder:
+        # the three decoder ops as a model with its own decoder would provide them: here the oracle's
+        # tables and the host's read_sym, holding the decoder state on the model's side of the boundary
+        L = H.library()
+        st = {}
+
+        def dbegin(ctx, payload, n):
+            st["buf"] = C.create_string_buffer(C.string_at(payload, n), n) if n else C.create_string_buffer(1)
+            st["dec"] = L.nch_dec_new(st["buf"], n)
+            st["ids"] = np.zeros((T, B), np.int32)
+            return 0
+
+        def dsteps(ctx, t0, nt, ids0, limit_t, limit_b, out):
+            o = np.ctypeslib.as_array(out, shape=(nt * B,)).reshape(nt, B)
+            o[:] = 0
+            if ids0:
+                st["ids"][t0] = np.ctypeslib.as_array(ids0, shape=(B,))
+            for t in range(t0, t0 + nt):
+                model.eval(t, st["ids"])
+                pr = np.ctypeslib.as_array(model.L.orc_probs(model.h), shape=(T * B * V,)).reshape(T, B, V)
+                for b in range(B):
+                    if t < limit_t or (t == limit_t and b < limit_b):
+                        row = np.ascontiguousarray(pr[t, b])
+                        o[t - t0, b] = L.nch_read_sym(st["dec"], row.ctypes.data_as(C.c_void_p), V)
+                if t + 1 < T:
+                    st["ids"][t + 1] = o[t - t0]
+            return 0
+
+        def dend(ctx, used):
+            L.nch_dec_free(st.pop("dec"))
+            return 0
+
+        keep["dec"] = [H.FN_DEC_BEGIN(dbegin), H.FN_DEC_STEPS(dsteps), H.FN_DEC_END(dend)]
+        ops.decoder_begin, ops.decode_steps, ops.decoder_end = keep["dec"]
     ops._keep = keep
     return ops
 
@@ -221,6 +255,12 @@ def test_block_loop_round_trip_with_oracle_model(pkg, n_sym, block_len):
                                  pkg.host.OUT_FLOAT)
     assert st.n_symbols == n_sym
     back = pkg.host.decompress(_oracle_ops(pkg, dec_model), data, pkg.host.OUT_FLOAT)
+    assert np.array_equal(back, syms)
+    # the block walk that hands whole segments to a decoder on the model's side
+    # (NCH_OUT_DEVICE), and its fallback when the model has no such decoder
+    back = pkg.host.decompress(_oracle_ops(pkg, orc.OracleModel(p), with_decoder=True), data, pkg.host.OUT_DEVICE)
+    assert np.array_equal(back, syms)
+    back = pkg.host.decompress(_oracle_ops(pkg, orc.OracleModel(p)), data, pkg.host.OUT_DEVICE)
     assert np.array_equal(back, syms)
     if n_sym >= 250:
         assert st.train_steps > 0
