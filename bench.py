@@ -205,7 +205,8 @@ def exchange_name(world):
         return "none"
     if os.environ.get("NNCU_PY_ALLREDUCE") == "1":
         return "one all-reduce after backward"
-    return "per-layer NCCL all-reduce inside the backward pass (overlapped), every rank applies the whole RMSProp step"
+    return ("per-layer NCCL all-reduce inside the backward pass (overlapped; Ring / LL128 / 32 channels pinned), "
+            "every rank applies the whole RMSProp step")
 
 
 def run_reference(args, c):
@@ -506,6 +507,12 @@ def main():
         raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run")
     torch.cuda.set_device(local)
     if world > 1:
+        # the library pins NCCL's algorithm, protocol and channel count when its communicator is made;
+        # NCCL reads some of them once per process, so they go in before torch's communicator exists
+        if os.environ.get("NNCU_NCCL_PIN") != "0":
+            for k, v in (("NCCL_ALGO", "Ring"), ("NCCL_PROTO", "LL128"), ("NCCL_MIN_NCHANNELS", "32"),
+                         ("NCCL_MAX_NCHANNELS", "32")):
+                os.environ.setdefault(k, v)
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     pkg = entry._package()
     lib = pkg.library()   # raises if the CUDA library is not built: there is no other path

@@ -32,6 +32,7 @@ extern "C" {
 #define NCH_ERR_NOMEM 3
 #define NCH_ERR_FORMAT 7   /* bad magic, version or truncated header */
 #define NCH_ERR_MODEL 8    /* a model call failed; see nncu_last_error */
+#define NCH_ERR_RANKS 9    /* the file was coded by a different number of ranks than is decoding it */
 
 /* ---- range coder (arith.c) ---- */
 typedef struct nch_enc nch_enc;
@@ -53,6 +54,9 @@ int nch_read_sym(nch_dec *d, const float *prob, int n_symb);
 /* the same walk fed by coder-ready device output (nncu_coder_paths / nncu_coder_trees) */
 void nch_write_sym_path(nch_enc *e, const uint16_t *prob0, int n_bits, int sym);
 int nch_read_sym_tree(nch_dec *d, const uint16_t *tree, int n_symb);
+/* n symbols in a row: prob0 [n][n_bits] / trees [n][n_symb] (the coding rank of a sharded job) */
+void nch_write_sym_paths(nch_enc *e, const uint16_t *prob0, int n_bits, const int32_t *sym, size_t n);
+void nch_read_sym_trees(nch_dec *d, const uint16_t *trees, int n_symb, size_t n, int32_t *sym_out);
 
 /* ---- schedule (cp_utils.h:60-71, cp_utils.c:380-410) ---- */
 #define NCH_INTERP_MAX_STEPS 8
@@ -117,13 +121,20 @@ int nch_process_block(const nch_model_ops *m, nch_enc *enc, nch_dec *dec, uint16
 typedef struct nch_file_params {
     nncu_params model;            /* n_streams is batch_size; d_model = d_key * n_head on read */
     nch_interp_params lr, block_len;
+    int32_t n_ranks;              /* ranks the streams were sharded over; 0 or 1: one process (header version 3 otherwise) */
 } nch_file_params;
 int nch_write_header(const nch_file_params *fp, uint32_t n_symbols_in_file, uint8_t *out, size_t cap,
                      size_t *len);
 int nch_read_header(const uint8_t *in, size_t n, nch_file_params *fp, uint32_t *n_symbols_in_file,
                     size_t *consumed);
 
-/* encode_file / decode_file, memory to memory.  *out is malloc'ed (free with nch_free). */
+/* length of the block that starts at symbol file_pos (schedule value rounded down to whole
+   segments of all streams, at least one, at most what remains; nncp.c:3428-3441) */
+int nch_next_block_len(const nch_file_params *fp, size_t file_pos, size_t remaining);
+
+/* encode_file / decode_file, memory to memory.  *out is malloc'ed (free with nch_free).
+   NCH_ERR_RANKS when fp->n_ranks > 1: a file of a sharded job is coded and decoded by that many
+   processes together. */
 int nch_compress(const nch_model_ops *m, const nch_file_params *fp, const uint16_t *symbols, size_t n,
                  int eval_mode, int out_mode, uint8_t **out, size_t *out_len, nch_block_stats *stats);
 int nch_decompress(const nch_model_ops *m, const nch_file_params *fp, const uint8_t *payload, size_t n,

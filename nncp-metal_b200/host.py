@@ -31,7 +31,7 @@ class InterpParams(C.Structure):
 
 
 class FileParams(C.Structure):
-    _fields_ = [("model", abi.Params), ("lr", InterpParams), ("block_len", InterpParams)]
+    _fields_ = [("model", abi.Params), ("lr", InterpParams), ("block_len", InterpParams), ("n_ranks", C.c_int32)]
 
 
 class BlockStats(C.Structure):
@@ -90,6 +90,11 @@ def library():
         L.nch_write_sym_path.argtypes = [_vp, _vp, _I, _I]
         L.nch_write_sym_path.restype = None
         L.nch_read_sym_tree.argtypes = [_vp, _vp, _I]
+        L.nch_write_sym_paths.argtypes = [_vp, _vp, _I, _vp, C.c_size_t]
+        L.nch_write_sym_paths.restype = None
+        L.nch_read_sym_trees.argtypes = [_vp, _vp, _I, C.c_size_t, _vp]
+        L.nch_read_sym_trees.restype = None
+        L.nch_next_block_len.argtypes = [C.POINTER(FileParams), C.c_size_t, C.c_size_t]
         L.nch_interp.argtypes = [C.POINTER(InterpParams), C.c_int64]
         L.nch_interp.restype = C.c_float
         L.nch_get_symb.argtypes = [_vp, _I, _I, _I, _I]

@@ -230,3 +230,16 @@ int nch_read_sym_tree(nch_dec *d, const uint16_t *tree, int n_symb)
         k = 2 * k + nch_dec_get_bit(d, tree[k]);
     return k - n_symb;
 }
+
+/* n symbols in a row, as a rank that codes for every rank of a sharded job does after the gather */
+void nch_write_sym_paths(nch_enc *e, const uint16_t *prob0, int n_bits, const int32_t *sym, size_t n)
+{
+    for (size_t i = 0; i < n; i++)
+        nch_write_sym_path(e, prob0 + i * (size_t)n_bits, n_bits, sym[i]);
+}
+
+void nch_read_sym_trees(nch_dec *d, const uint16_t *trees, int n_symb, size_t n, int32_t *sym_out)
+{
+    for (size_t i = 0; i < n; i++)
+        sym_out[i] = nch_read_sym_tree(d, trees + i * (size_t)n_symb, n_symb);
+}

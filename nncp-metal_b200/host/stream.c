@@ -336,17 +336,24 @@ static int rinterp(rbuf *r, nch_interp_params *p)
 }
 
 /* Version 1 is the reference layout byte for byte.  Version 2 appends two bytes
-   (init_kind, bias_correction) for the build-defined options the reference has no field for. */
+   (init_kind, bias_correction) for the build-defined options the reference has no field for.
+   Version 3 appends a third: the number of ranks the streams were sharded over.  The gradient sum
+   over ranks has an order that depends on that number, so a file decodes only with the same one
+   (the reference records use_cuda for the same reason and refuses a mismatch, nncp.c:2669,
+   3543-3550). */
 int nch_write_header(const nch_file_params *fp, uint32_t n_symbols_in_file, uint8_t *out, size_t cap,
                      size_t *len)
 {
     if (!fp || !len)
         return NCH_ERR_INVALID;
     const nncu_params *m = &fp->model;
-    const int v2 = m->init_kind != NNCU_INIT_UNIFORM || m->bias_correction != 0;
+    const int v3 = fp->n_ranks > 1;
+    const int v2 = v3 || m->init_kind != NNCU_INIT_UNIFORM || m->bias_correction != 0;
+    if (fp->n_ranks > 255)
+        return NCH_ERR_INVALID;
     wbuf w = {out, 0, out ? cap : 0, 0};
     w32(&w, FILE_MAGIC);
-    w16(&w, v2 ? 2 : 1);
+    w16(&w, v3 ? 3 : (v2 ? 2 : 1));
     w8(&w, 1);                 /* use_cuda */
     w8(&w, m->use_bf16);
     w16(&w, m->n_streams);     /* batch_size */
@@ -387,6 +394,8 @@ int nch_write_header(const nch_file_params *fp, uint32_t n_symbols_in_file, uint
         w8(&w, m->init_kind);
         w8(&w, m->bias_correction != 0);
     }
+    if (v3)
+        w8(&w, fp->n_ranks);
     w8(&w, 0);                 /* no preprocessing dictionary */
     w32(&w, n_symbols_in_file);
     *len = w.len;
@@ -404,7 +413,7 @@ int nch_read_header(const uint8_t *in, size_t n, nch_file_params *fp, uint32_t *
     if (r32(&r) != FILE_MAGIC)
         return NCH_ERR_FORMAT;
     unsigned ver = r16(&r);
-    if (ver != 1 && ver != 2)
+    if (ver < 1 || ver > 3)
         return NCH_ERR_FORMAT;
     r8(&r); /* use_cuda */
     m->use_bf16 = (uint8_t)r8(&r);
@@ -449,10 +458,13 @@ int nch_read_header(const uint8_t *in, size_t n, nch_file_params *fp, uint32_t *
     m->eps = rf32(&r);
     m->gradient_clip = rf32(&r);
     r8(&r); /* use_sparse_grad */
-    if (ver == 2) {
+    if (ver >= 2) {
         m->init_kind = (int)r8(&r);
         m->bias_correction = (int)r8(&r);
     }
+    fp->n_ranks = ver >= 3 ? (int)r8(&r) : 1;
+    if (fp->n_ranks < 1)
+        return NCH_ERR_FORMAT;
     if (r8(&r) != 0)
         return NCH_ERR_FORMAT; /* preprocessing dictionary */
     uint32_t nsym = r32(&r);
@@ -471,7 +483,7 @@ int nch_read_header(const uint8_t *in, size_t n, nch_file_params *fp, uint32_t *
 
 /* ------------------------------------------------------------------ file loops */
 
-static int next_block_len(const nch_file_params *fp, size_t file_pos, size_t remaining)
+int nch_next_block_len(const nch_file_params *fp, size_t file_pos, size_t remaining)
 {
     const int unit = fp->model.seg_len * fp->model.n_streams;
     long bl = lrintf(nch_interp(&fp->block_len, (int64_t)file_pos));
@@ -491,6 +503,8 @@ int nch_compress(const nch_model_ops *m, const nch_file_params *fp, const uint16
 {
     if (!m || !fp || (!symbols && n) || !out || !out_len)
         return NCH_ERR_INVALID;
+    if (fp->n_ranks > 1)
+        return NCH_ERR_RANKS; /* one process cannot produce the sums of n_ranks */
     size_t hlen = 0;
     nch_write_header(fp, (uint32_t)n, NULL, 0, &hlen);
     nch_enc *enc = nch_enc_new();
@@ -501,7 +515,7 @@ int nch_compress(const nch_model_ops *m, const nch_file_params *fp, const uint16
     uint16_t *block = NULL;
     size_t pos = 0;
     while (pos < n) {
-        int bl = next_block_len(fp, pos, n - pos);
+        int bl = nch_next_block_len(fp, pos, n - pos);
         uint16_t *nb = (uint16_t *)realloc(block, sizeof(uint16_t) * (size_t)bl);
         if (!nb) { rc = NCH_ERR_NOMEM; break; }
         block = nb;
@@ -535,6 +549,8 @@ int nch_decompress(const nch_model_ops *m, const nch_file_params *fp, const uint
 {
     if (!m || !fp || (!payload && n) || (!symbols_out && n_symbols_in_file))
         return NCH_ERR_INVALID;
+    if (fp->n_ranks > 1)
+        return NCH_ERR_RANKS; /* coded by a job of n_ranks processes: this single-process loop cannot repeat its sums */
     int rc = NCH_OK;
     int64_t train_step = 0;
     size_t pos = 0, total = n_symbols_in_file;
@@ -543,7 +559,7 @@ int nch_decompress(const nch_model_ops *m, const nch_file_params *fp, const uint
         if (m->decoder_begin && m->decode_steps && m->decoder_end && log2_exact(m->n_symbols) >= 1 &&
             m->decoder_begin(m->ctx, payload, n) == 0) {
             while (pos < total) {
-                int bl = next_block_len(fp, pos, total - pos);
+                int bl = nch_next_block_len(fp, pos, total - pos);
                 rc = decode_block_device(m, symbols_out + pos, bl, &fp->lr, &train_step);
                 if (rc)
                     break;
@@ -560,7 +576,7 @@ int nch_decompress(const nch_model_ops *m, const nch_file_params *fp, const uint
     if (!dec)
         return NCH_ERR_NOMEM;
     while (pos < total) {
-        int bl = next_block_len(fp, pos, total - pos);
+        int bl = nch_next_block_len(fp, pos, total - pos);
         rc = nch_process_block(m, NULL, dec, symbols_out + pos, bl, &fp->lr, &train_step, NCH_EVAL_STEP,
                                out_mode, NULL);
         if (rc)

@@ -74,3 +74,81 @@ def test_stream_slice_partitions_the_streams(pkg):
         assert cols == list(range(32))
     with pytest.raises(ValueError):
         pkg.dist.stream_slice(0, 3, 32)
+
+
+# ---- the coder side of a sharded job: paths / tables to rank 0 when encoding, symbols back when decoding
+
+def _codec_source(n):
+    rng = np.random.default_rng(3)
+    return np.array([(5 * i) % 7 if rng.random() < 0.8 else rng.integers(0, 16) for i in range(n)], np.uint16)
+
+
+def _codec(pkg, orc, cfg, z, rank, world, B_total):
+    p = params_from_cfg(pkg, cfg, n_streams=B_total // world, n_streams_total=B_total, lr=1e-2)
+    m = orc.OracleModel(p)
+    for name in m.info:
+        m.set_param(name, z[f"p0/{name}"])
+    grads = torch.from_numpy(np.ctypeslib.as_array(m.L.orc_grads(m.h), shape=(m.n_floats,)))
+    step = pkg.dist.ShardedStep(m, grads, world=world)
+    return pkg.dist.ShardedCodec(pkg.host, m, p, step), p
+
+
+def _codec_worker(rank, world, port, out_dir):
+    sys.path.insert(0, ROOT)
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    pkg = load_package()
+    from oracle import oracle as orc
+    cfg, z = load_golden("post_gelu")
+    syms = _codec_source(301)
+    enc, p = _codec(pkg, orc, cfg, z, rank, world, 4)
+    data = enc.compress(pkg.host.file_params(p, block_len=96), syms)
+    box = [data]
+    dist.broadcast_object_list(box, src=0)        # every rank decodes the same file
+    dec, _ = _codec(pkg, orc, cfg, z, rank, world, 4)
+    back = dec.decompress(box[0])
+    if rank == 0:
+        np.savez(os.path.join(out_dir, "codec.npz"), data=np.frombuffer(data, np.uint8), back=back)
+    else:
+        assert data is None and np.array_equal(back, syms)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_sharded_codec_round_trip_and_rank_count_in_header(tmp_path, pkg, oracle):
+    """Two ranks code one file between them (ragged blocks, several blocks, training in between) and
+    decode it again; the header says 2 ranks, and neither the single-process decoder nor a
+    one-rank codec accepts the file."""
+    port = 31500 + os.getpid() % 2000
+    mp.spawn(_codec_worker, args=(2, port, str(tmp_path)), nprocs=2, join=True)
+    zf = np.load(tmp_path / "codec.npz")
+    data, syms = zf["data"].tobytes(), _codec_source(301)
+    assert np.array_equal(zf["back"], syms)
+    fp, n, used = pkg.host.read_header(data)
+    assert data[4:6] == b"\x00\x03" and fp.n_ranks == 2 and fp.model.n_streams == 4 and n == 301
+    cfg, z = load_golden("post_gelu")
+    one, p1 = _codec(pkg, oracle, cfg, z, 0, 1, 4)
+    with pytest.raises(ValueError):
+        one.decompress(data)
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    from test_host_code import _oracle_ops
+    with pytest.raises(RuntimeError):
+        pkg.host.decompress(_oracle_ops(pkg, oracle.OracleModel(p1)), data, pkg.host.OUT_FLOAT)
+
+
+def test_one_rank_codec_writes_the_single_process_file(pkg, oracle):
+    """With one rank the sharded block walk must produce the bytes of nch_compress."""
+    from test_host_code import _oracle_ops
+    cfg, z = load_golden("post_gelu")
+    syms = _codec_source(230)
+    codec, p = _codec(pkg, oracle, cfg, z, 0, 1, 4)
+    a = codec.compress(pkg.host.file_params(p, block_len=96), syms)
+    m = oracle.OracleModel(p)
+    for name in m.info:
+        m.set_param(name, z[f"p0/{name}"])
+    b, _ = pkg.host.compress(_oracle_ops(pkg, m), pkg.host.file_params(p, block_len=96), syms,
+                             pkg.host.EVAL_SEGMENT, pkg.host.OUT_FLOAT)
+    assert a == b and a[4:6] != b"\x00\x03"      # no rank count in a one-process file
+    codec2, _ = _codec(pkg, oracle, cfg, z, 0, 1, 4)
+    assert np.array_equal(codec2.decompress(a), syms)
