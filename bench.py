@@ -205,8 +205,11 @@ def exchange_name(world):
         return "none"
     if os.environ.get("NNCU_PY_ALLREDUCE") == "1":
         return "one all-reduce after backward"
-    return ("per-layer NCCL all-reduce inside the backward pass (overlapped; Ring / LL128 / 32 channels pinned), "
-            "every rank applies the whole RMSProp step")
+    if os.environ.get("NNCU_SHARDED_UPDATE") == "1":
+        return ("per-layer reduce-scatter, RMSProp on the rank's shard, all-gather of the bf16 weights; small parameters "
+                "all-reduced; embedding gradient from gathered ids and rows (Ring / LL128 / 32 channels pinned)")
+    return ("per-layer NCCL all-reduce inside the backward pass (overlapped; Ring / LL128 / 32 channels pinned), every rank "
+            "applies the whole RMSProp step; embedding gradient from gathered ids and rows instead of the dense table")
 
 
 def run_reference(args, c):

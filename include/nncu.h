@@ -230,6 +230,23 @@ int nncu_flat_buffers(nncu_model *m, float **master_dev, float **grad_dev,
  */
 int nncu_comm_unique_id(void *id_out_128_bytes);
 int nncu_comm_init(nncu_model *m, int n_ranks, int rank, const void *id_128_bytes);
+/*
+ * With NNCU_SHARDED_UPDATE=1 in the environment, nncu_eval_gradient_update[_dev]
+ * under a communicator shards the optimizer: each layer's matrices are
+ * reduce-scattered, every rank updates its 1/N of them and the updated bf16
+ * weights (fp32 in an fp32 model) are all-gathered; small parameters are
+ * all-reduced and updated whole; the embedding gradient is rebuilt on every
+ * rank from the gathered input ids and input gradients (that part alone is
+ * the default; NNCU_SPARSE_EMBED=0 returns to the dense all-reduce).  Second moments and fp32 master weights of the
+ * matrices are then current on the owning rank only.
+ * nncu_comm_gather_master -- a collective: every rank calls it -- completes
+ * them everywhere; nncu_param_get / _set, nncu_weights_hash,
+ * nncu_eval_gradient and nncu_optimizer_step return NNCU_ERR_STATE until it
+ * has run.  The default is one all-reduce per layer and the whole update on
+ * every rank, which measured faster at 2 and 4 GPUs on the 55 M-parameter
+ * model (csrc/model.cu, shard_enabled).
+ */
+int nncu_comm_gather_master(nncu_model *m);
 
 /* 64-bit order-independent digest (sum of mixed (index, bit pattern) words) of the fp32
    master weights (DUMP_HASH-style check that

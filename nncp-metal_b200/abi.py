@@ -107,6 +107,7 @@ PROTOTYPES = {
                                C.POINTER(_sz)]),
     "nncu_comm_unique_id": (_i, [_vp]),
     "nncu_comm_init": (_i, [_vp, _i, _i, _vp]),
+    "nncu_comm_gather_master": (_i, [_vp]),
     "nncu_weights_hash": (_i, [_vp, C.POINTER(C.c_uint64)]),
     "nncu_coder_paths": (_i, [_vp, _i, _i, _vp, _vp, C.POINTER(_i)]),
     "nncu_coder_paths_begin": (_i, [_vp, _i, _i, _vp]),

@@ -152,7 +152,14 @@ class TrfModel:
         self._ck(self.lib.nncu_comm_init(self.h, n_ranks, rank, buf))
         self.has_comm = True
 
+    def gather_master(self):
+        """Collective (every rank calls it): completes the sharded optimizer state on every rank."""
+        self._ck(self.lib.nncu_comm_gather_master(self.h))
+
     def weights_hash(self):
+        """Under a communicator this is a collective: the sharded master weights are gathered first."""
+        if self.has_comm:
+            self.gather_master()
         h = C.c_uint64()
         self._ck(self.lib.nncu_weights_hash(self.h, C.byref(h)))
         return h.value
