@@ -202,6 +202,12 @@ int nncu_memory_shift(nncu_model *m);
 /* Blocks until everything queued on the model's stream has finished and
    reports a device-side error flag if one was raised. */
 int nncu_synchronize(nncu_model *m);
+/* Queues a one-thread kernel whose bounded wait (the mbar_wait of the GEMM and
+   attention kernels, with a limit of 256 tries) runs out on a barrier nothing
+   completes: the next nncu_synchronize returns NNCU_ERR_TIMEOUT, the one after
+   NNCU_OK, and the model keeps working.  For tests of the error path; it has
+   no counterpart in the reference, whose device waits are unbounded. */
+int nncu_selftest_expired_wait(nncu_model *m);
 
 /* ---- parameters (NCParamList, libnc.h:499-536) ---- */
 int nncu_param_count(const nncu_model *m);

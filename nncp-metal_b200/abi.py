@@ -98,6 +98,7 @@ PROTOTYPES = {
     "nncu_optimizer_step": (_i, [_vp]),
     "nncu_memory_shift": (_i, [_vp]),
     "nncu_synchronize": (_i, [_vp]),
+    "nncu_selftest_expired_wait": (_i, [_vp]),
     "nncu_param_count": (_i, [_vp]),
     "nncu_param_info": (_i, [_vp, _i, C.c_char_p, _sz, C.POINTER(_sz), C.POINTER(_sz)]),
     "nncu_param_get": (_i, [_vp, _i, _vp, _sz]),

@@ -62,7 +62,7 @@ constexpr uint32_t WAIT_TRIES = 1u << 24;
 constexpr uint32_t WAIT_TRIES = 1u << 21;
 #endif
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_s,
-                                          int *err_flag, int code)
+                                          int *err_flag, int code, uint32_t tries = WAIT_TRIES)
 {
     uint32_t ok;
     asm volatile("{\n\t.reg .pred p, q;\n\t.reg .u32 c;\n\t"
@@ -81,7 +81,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
                  "NNCU_DONE:\n\t"
                  "selp.u32 %0, 1, 0, p;\n\t}"
                  : "=r"(ok)
-                 : "r"(bar), "r"(parity), "r"(WAIT_TRIES), "r"(1000u)
+                 : "r"(bar), "r"(parity), "r"(tries), "r"(1000u)
                  : "memory");
     if (!ok) {
         *abort_s = 1;

@@ -778,13 +778,13 @@ rmsprop_kernel(float *__restrict__ w, const float *__restrict__ g, float *__rest
 {
     pdl_trigger();
     pdl_wait();
-    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= n4)
-        return;
     if (hyper) { // {lr, corr} from device memory: a captured launch must not freeze them
         lr = hyper[0];
         corr = hyper[1];
     }
+    // grid-stride: correct for any grid; the library launches one thread per group of four
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += stride) {
     float4 ww = reinterpret_cast<float4 *>(w)[i];
     float4 gg = reinterpret_cast<const float4 *>(g)[i];
     float4 vv = reinterpret_cast<float4 *>(v)[i];
@@ -807,6 +807,7 @@ rmsprop_kernel(float *__restrict__ w, const float *__restrict__ g, float *__rest
         pk.x = *reinterpret_cast<uint32_t *>(&lo);
         pk.y = *reinterpret_cast<uint32_t *>(&hi);
         reinterpret_cast<uint2 *>(shadow)[i] = pk;
+    }
     }
 }
 
