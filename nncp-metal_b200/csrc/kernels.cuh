@@ -643,8 +643,20 @@ __device__ __forceinline__ float block_max_256(float v, float *red)
     return s;
 }
 
-// in-place softmax over the V symbols of each row of fp32 logits (nc_soft_max, nncp.c:1008)
-__global__ void __launch_bounds__(256) softmax_rows_kernel(float *__restrict__ z, int rows, int V)
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi)
+{
+    __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t *>(&h);
+}
+
+// in-place softmax over the V symbols of each row of fp32 logits (nc_soft_max, nncp.c:1008).
+// The output kernel of the forward pass: besides the probabilities it leaves dz = p * scale, the
+// gradient of the loss with respect to the logits of every symbol but the target (which
+// loss_fix_kernel corrects once the targets are known), so that the backward pass does not read
+// the probability tables again.  *dz_fixed = 0 says that dz holds no target correction.
+template <typename T>
+__global__ void __launch_bounds__(256) softmax_rows_kernel(float *__restrict__ z, int rows, int V, T *__restrict__ dz, float scale,
+                                                           int *__restrict__ dz_fixed)
 {
     pdl_trigger();
     pdl_wait();
@@ -652,6 +664,8 @@ __global__ void __launch_bounds__(256) softmax_rows_kernel(float *__restrict__ z
     int r = blockIdx.x;
     if (r >= rows)
         return;
+    if (r == 0 && threadIdx.x == 0)
+        *dz_fixed = 0;
     float *zr = z + (size_t)r * V;
     float mx = -INFINITY;
     for (int i = threadIdx.x; i < V; i += 256)
@@ -665,13 +679,19 @@ __global__ void __launch_bounds__(256) softmax_rows_kernel(float *__restrict__ z
     }
     s = block_sum_256(s, red);
     float rs = 1.0f / s;
-    for (int i = threadIdx.x; i < V; i += 256)
-        zr[i] *= rs;
+    T *d = dz + (size_t)r * V;
+    for (int i = threadIdx.x; i < V; i += 256) {
+        const float pv = zr[i] * rs;
+        zr[i] = pv;
+        d[i] = from_f<T>(pv * scale);
+    }
 }
 
 // The same for rows of up to 16384 logits, V a multiple of 1024: the row stays in registers
 // (one read and one write of memory, 16-byte accesses).  Thread t owns logits (k*256 + t)*4 .. +3.
-__global__ void __launch_bounds__(256) softmax_rows_reg_kernel(float *__restrict__ z, int rows, int V)
+template <typename T>
+__global__ void __launch_bounds__(256) softmax_rows_reg_kernel(float *__restrict__ z, int rows, int V, T *__restrict__ dz,
+                                                               float scale, int *__restrict__ dz_fixed)
 {
     pdl_trigger();
     pdl_wait();
@@ -679,6 +699,8 @@ __global__ void __launch_bounds__(256) softmax_rows_reg_kernel(float *__restrict
     const int r = blockIdx.x;
     if (r >= rows)
         return;
+    if (r == 0 && threadIdx.x == 0)
+        *dz_fixed = 0;
     float4 *zr = reinterpret_cast<float4 *>(z + (size_t)r * V);
     const int nv = V / 1024;
     float4 v[16];
@@ -710,44 +732,55 @@ __global__ void __launch_bounds__(256) softmax_rows_reg_kernel(float *__restrict
             v[k].z *= rs;
             v[k].w *= rs;
             zr[k * 256 + threadIdx.x] = v[k];
+            T *d = dz + (size_t)r * V + (size_t)(k * 256 + threadIdx.x) * 4;
+            if (sizeof(T) == 2) {
+                uint2 pk;
+                pk.x = pack_bf16x2(v[k].x * scale, v[k].y * scale);
+                pk.y = pack_bf16x2(v[k].z * scale, v[k].w * scale);
+                *reinterpret_cast<uint2 *>(d) = pk;
+            } else {
+                *reinterpret_cast<float4 *>(d) = make_float4(v[k].x * scale, v[k].y * scale, v[k].z * scale, v[k].w * scale);
+            }
         }
 }
 
-// dz = (p - onehot(target)) * scale ; logp[r] = ln p[r][target]
-// (nc_indexed_log + the adjoint of softmax, nncp.c:1170-1175)
+// The target correction of dz and the loss in one block: for every row r, dz[r][t_r] =
+// (p[r][t_r] - 1) * scale and logp[r] = ln p[r][t_r] (nc_indexed_log and the adjoint of the softmax,
+// nncp.c:1170-1175); loss = sum_r logp[r] in a fixed order (thread i adds rows i, i + 256, ...;
+// then the block sum).  A second call for
+// the same forward pass (*dz_fixed != 0) first puts the old targets' entries back to p * scale.
 template <typename T>
 __global__ void __launch_bounds__(256)
-loss_grad_kernel(const float *__restrict__ probs, const int32_t *__restrict__ targets,
-                 T *__restrict__ dz, float *__restrict__ logp, int rows, int V, float scale)
-{
-    pdl_trigger();
-    pdl_wait();
-    int r = blockIdx.x;
-    if (r >= rows)
-        return;
-    int t = targets[r];
-    t = t < 0 ? 0 : (t >= V ? V - 1 : t);
-    const float *pr = probs + (size_t)r * V;
-    T *d = dz + (size_t)r * V;
-    for (int i = threadIdx.x; i < V; i += 256)
-        d[i] = from_f<T>((pr[i] - (i == t ? 1.0f : 0.0f)) * scale);
-    if (threadIdx.x == 0)
-        logp[r] = logf(pr[t]);
-}
-
-// loss = sum_r logp[r], one block, fixed order
-__global__ void __launch_bounds__(256) sum_vec_kernel(const float *__restrict__ v, int n,
-                                                      float *__restrict__ out)
+loss_fix_kernel(const float *__restrict__ probs, const int32_t *__restrict__ targets, int32_t *__restrict__ fixed_targets,
+                int *__restrict__ dz_fixed, T *__restrict__ dz, float *__restrict__ logp, float *__restrict__ loss, int rows,
+                int V, float scale)
 {
     pdl_trigger();
     pdl_wait();
     __shared__ float red[8];
+    const bool undo = *dz_fixed != 0;
     float s = 0.0f;
-    for (int i = threadIdx.x; i < n; i += 256)
-        s += v[i];
+    for (int r = threadIdx.x; r < rows; r += 256) {
+        const float *pr = probs + (size_t)r * V;
+        T *d = dz + (size_t)r * V;
+        if (undo) {
+            const int old = fixed_targets[r];
+            d[old] = from_f<T>(pr[old] * scale);
+        }
+        int t = targets[r];
+        t = t < 0 ? 0 : (t >= V ? V - 1 : t);
+        const float pt = pr[t];
+        d[t] = from_f<T>((pt - 1.0f) * scale);
+        fixed_targets[r] = t;
+        const float lp = logf(pt);
+        logp[r] = lp;
+        s += lp;
+    }
     s = block_sum_256(s, red);
-    if (threadIdx.x == 0)
-        *out = s;
+    if (threadIdx.x == 0) {
+        *loss = s;
+        *dz_fixed = 1;
+    }
 }
 
 // column sums of A [R][N] over row chunks: part[chunk][n]   (bias gradients)

@@ -177,6 +177,8 @@ struct nncu_model {
     bool fuse_update = false; // this backward pass applies the optimizer to each bucket as it completes
     float *hyper_dev = nullptr; // {lr, bias correction} of the fused optimizer step
     int32_t *ids_dev, *tgt_dev;
+    int32_t *tgt_fixed; // the targets whose entries of dz carry the (p - 1) correction
+    int *dz_fixed;      // device flag: dz has been corrected since the last forward pass
     int *err_flag;
     unsigned long long *hash_dev;
     TransposeJob *jobs_dev;
@@ -609,10 +611,13 @@ static int forward_range(nncu_model *m, int t0, int t1)
     }
     float *pr = m->probs + (size_t)r0 * V;
     NNCU_TRY((mm_nt<AT, float>(m, nr, V, D, xf, D, m->embed_out, pr, V, wf(m, m->out_bias))));
+    // the output kernel: probabilities for the coder, and p / (T * B) for the backward pass
+    AT *dzr = reinterpret_cast<AT *>(m->dz) + (size_t)r0 * V;
+    const float sc = 1.0f / ((float)m->T * (float)m->Bt);
     if (V % 1024 == 0 && V <= 16384)
-        launch_k(softmax_rows_reg_kernel, dim3(nr), dim3(256), 0, m->st, pr, nr, V);
+        launch_k(softmax_rows_reg_kernel<AT>, dim3(nr), dim3(256), 0, m->st, pr, nr, V, dzr, sc, m->dz_fixed);
     else
-        launch_k(softmax_rows_kernel, dim3(nr), dim3(256), 0, m->st, pr, nr, V);
+        launch_k(softmax_rows_kernel<AT>, dim3(nr), dim3(256), 0, m->st, pr, nr, V, dzr, sc, m->dz_fixed);
     KERNEL_CHECK();
     return NNCU_OK;
 }
@@ -745,9 +750,8 @@ static int backward(nncu_model *m)
 
     // loss and d logits (nncp.c:1170-1175)
     const float sc = 1.0f / ((float)m->T * (float)m->Bt);
-    launch_k(loss_grad_kernel<AT>, dim3(TB), dim3(256), 0, m->st, m->probs, m->tgt_dev, dz, m->logp, TB, V, sc);
-    KERNEL_CHECK();
-    launch_k(sum_vec_kernel, dim3(1), dim3(256), 0, m->st, m->logp, TB, m->loss_dev);
+    launch_k(loss_fix_kernel<AT>, dim3(1), dim3(256), 0, m->st, (const float *)m->probs, (const int32_t *)m->tgt_dev, m->tgt_fixed,
+             m->dz_fixed, dz, m->logp, m->loss_dev, TB, V, sc);
     KERNEL_CHECK();
     const AT *xf = (p.ln_flags & NNCU_LN_FINAL) ? atc<AT>(m->xf, 0) : atc<AT>(m->xlast, 0);
     if (m->out_bias != NONE)
@@ -1234,6 +1238,7 @@ int nncu_create(const nncu_params *p, nncu_model **out)
     size_t oSkw = take(skw_floats * 4 + 256);
     size_t oLogp = take((size_t)TB * 4), oLoss = take(256);
     size_t oIds = take((size_t)TB * 4), oTgt = take((size_t)TB * 4), oErr = take(256), oHash = take(256);
+    size_t oTgtFixed = take((size_t)TB * 4);
     // transposed-shadow jobs
     std::vector<TransposeJob> jobs;
     int tiles = 0;
@@ -1280,6 +1285,8 @@ int nncu_create(const nncu_params *p, nncu_model **out)
     m->hyper_dev = m->loss_dev + 8;
     m->ids_dev = (int32_t *)(A + oIds); m->tgt_dev = (int32_t *)(A + oTgt);
     m->err_flag = (int *)(A + oErr); m->hash_dev = (unsigned long long *)(A + oHash);
+    m->dz_fixed = m->err_flag + 16; // same 256-byte slot, zeroed with the arena
+    m->tgt_fixed = (int32_t *)(A + oTgtFixed);
     m->jobs_dev = (TransposeJob *)(A + oJobs);
     m->n_jobs = (int)jobs.size(); m->n_job_tiles = tiles;
     m->coder_dev = (uint16_t *)(A + oCoder);
