@@ -65,7 +65,7 @@ def step_flops(c, B):
     D, H, dk, F, T, M, V, P = (c["d_model"], c["n_head"], c["d_key"], c["d_inner"], c["seg_len"],
                                c["mem_len"], c["n_symbols"], c["d_pos"])
     L, HD = M + T, c["n_head"] * c["d_key"]
-    F1 = 2 * F if c.get("ff_act", 1) == 2 else F
+    F1 = 2 * F if c.get("ff_act", 1) in (2, 3) else F
     layer = (2 * B * T * D * HD + 2 * B * L * D * 2 * HD + 2 * B * H * T * L * dk + 2 * B * H * T * P * dk +
              2 * B * H * T * L * dk + 2 * B * T * HD * D + 2 * B * T * D * F1 + 2 * B * T * F * D)
     head = 2 * B * T * D * V

@@ -71,7 +71,7 @@ extern "C" {
 #define NNCU_FF_RELU 0
 #define NNCU_FF_GELU 1
 #define NNCU_FF_GEGLU 2
-#define NNCU_FF_GATED_SILU 3 /* not supported: nncu_create returns INVALID */
+#define NNCU_FF_GATED_SILU 3 /* ff1 has 2 * d_inner rows: silu(first half) * second half */
 
 #define NNCU_N_LAYER_MAX 32 /* N_LAYER_MAX nncp.c:80 */
 

@@ -471,6 +471,26 @@ __device__ __forceinline__ float gelu_grad_hw(float x)
     return 0.5f * (1.0f + t) + 0.5f * x * (1.0f - t * t) * du;
 }
 
+// x * sigmoid(x), the gate function of FF_ACT_GATED_SILU (nc_gated_swish with beta 1, nncp.c:957-962),
+// and its derivative; the _hw forms take the sigmoid from the hardware tanh.
+__device__ __forceinline__ float silu_f(float x) { return x / (1.0f + expf(-x)); }
+__device__ __forceinline__ float silu_grad_f(float x)
+{
+    const float s = 1.0f / (1.0f + expf(-x));
+    return s * (1.0f + x * (1.0f - s));
+}
+__device__ __forceinline__ float silu_hw(float x) { return x * (0.5f + 0.5f * tanh_hw(0.5f * x)); }
+__device__ __forceinline__ float silu_grad_hw(float x)
+{
+    const float s = 0.5f + 0.5f * tanh_hw(0.5f * x);
+    return s * (1.0f + x * (1.0f - s));
+}
+// the gated activations: value and derivative of the function applied to the first half
+__device__ __forceinline__ float gate_f(float x, int act) { return act == NNCU_FF_GATED_SILU ? silu_f(x) : gelu_f(x); }
+__device__ __forceinline__ float gate_grad_f(float x, int act) { return act == NNCU_FF_GATED_SILU ? silu_grad_f(x) : gelu_grad_f(x); }
+__device__ __forceinline__ float gate_hw(float x, int act) { return act == NNCU_FF_GATED_SILU ? silu_hw(x) : gelu_hw(x); }
+__device__ __forceinline__ float gate_grad_hw(float x, int act) { return act == NNCU_FF_GATED_SILU ? silu_grad_hw(x) : gelu_grad_hw(x); }
+
 template <typename T>
 __global__ void act_fwd_kernel(const T *__restrict__ hpre, T *__restrict__ hact, int rows, int F,
                                int F1, int act)
@@ -485,7 +505,7 @@ __global__ void act_fwd_kernel(const T *__restrict__ hpre, T *__restrict__ hact,
     else if (act == NNCU_FF_GELU)
         o = gelu_f(a);
     else
-        o = gelu_f(a) * to_f(hpre[(size_t)r * F1 + F + i]);
+        o = gate_f(a, act) * to_f(hpre[(size_t)r * F1 + F + i]);
     hact[idx] = from_f<T>(o);
 }
 
@@ -520,7 +540,7 @@ __global__ void act_fwd_vec_kernel(const bf16 *__restrict__ hpre, bf16 *__restri
         const bf16 *g = reinterpret_cast<const bf16 *>(&vg);
 #pragma unroll
         for (int j = 0; j < 8; j++)
-            o[j] = from_f<bf16>(gelu_hw(to_f(a[j])) * to_f(g[j]));
+            o[j] = from_f<bf16>(gate_hw(to_f(a[j]), act) * to_f(g[j]));
     }
     *reinterpret_cast<uint4 *>(hact + (size_t)r * F + i) = vo;
 }
@@ -545,7 +565,7 @@ act_bwd_kernel(const T *__restrict__ hpre, const T *__restrict__ dhact, T *__res
             s0 += to_f(o);
         } else {
             float gate = to_f(hpre[(size_t)r * F1 + F + i]);
-            T o0 = from_f<T>(d * gate * gelu_grad_f(a)), o1 = from_f<T>(d * gelu_f(a));
+            T o0 = from_f<T>(d * gate * gate_grad_f(a, act)), o1 = from_f<T>(d * gate_f(a, act));
             dhpre[(size_t)r * F1 + i] = o0;
             dhpre[(size_t)r * F1 + F + i] = o1;
             s0 += to_f(o0);
@@ -594,8 +614,8 @@ act_bwd_vec_kernel(const bf16 *__restrict__ hpre, const bf16 *__restrict__ dhact
             const float gate[2] = {__low2float(g2), __high2float(g2)};
 #pragma unroll
             for (int j = 0; j < 2; j++) {
-                o0[j] = from_f<bf16>(d[j] * gate[j] * gelu_grad_hw(a[j]));
-                o1[j] = from_f<bf16>(d[j] * gelu_hw(a[j]));
+                o0[j] = from_f<bf16>(d[j] * gate[j] * gate_grad_hw(a[j], act));
+                o1[j] = from_f<bf16>(d[j] * gate_hw(a[j], act));
                 s0[j] += to_f(o0[j]);
                 s1[j] += to_f(o1[j]);
             }

@@ -1011,7 +1011,7 @@ static int validate(const nncu_params *p)
         return nncu_fail(NNCU_ERR_INVALID, "LN_COEF is not supported");
     if ((p->ln_flags & NNCU_LN_PRE) && (p->ln_flags & NNCU_LN_POST))
         return nncu_fail(NNCU_ERR_INVALID, "LN_PRE and LN_POST together are not supported");
-    if (p->ff_act > NNCU_FF_GEGLU)
+    if (p->ff_act > NNCU_FF_GATED_SILU)
         return nncu_fail(NNCU_ERR_INVALID, "ff_act %d is not supported", p->ff_act);
     if (p->use_bf16 && (p->d_key & 1))
         return nncu_fail(NNCU_ERR_INVALID, "bf16 models need an even d_key");
@@ -1130,7 +1130,7 @@ int nncu_create(const nncu_params *p, nncu_model **out)
         m->graphs_on = !(e && e[0] == '1');
     }
     m->D = p->d_model; m->H = p->n_head; m->dk = p->d_key; m->HD = m->H * m->dk; m->F = p->d_inner;
-    m->F1 = (p->ff_act == NNCU_FF_GEGLU) ? 2 * m->F : m->F;
+    m->F1 = (p->ff_act == NNCU_FF_GEGLU || p->ff_act == NNCU_FF_GATED_SILU) ? 2 * m->F : m->F;
     m->T = p->seg_len; m->B = p->n_streams; m->M = p->mem_len; m->L = m->M + m->T; m->V = p->n_symbols;
     m->TB = m->T * m->B; m->LB = m->L * m->B; m->nl = p->n_layer;
     m->Bt = p->n_streams_total > 0 ? p->n_streams_total : m->B;

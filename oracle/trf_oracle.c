@@ -75,6 +75,14 @@ typedef struct orc_model {
 
 #define NONE ((size_t)-1)
 
+/* x * sigmoid(x): the gate function of FF_ACT_GATED_SILU (nc_gated_swish with beta 1, nncp.c:957-962) */
+static float silu_f(float x) { return x / (1.0f + expf(-x)); }
+static float silu_grad(float x)
+{
+    float s = 1.0f / (1.0f + expf(-x));
+    return s * (1.0f + x * (1.0f - s));
+}
+
 /* ------------------------------------------------------------------ */
 /* deterministic parameter initialisation (counter-based, integer hash) */
 
@@ -439,7 +447,7 @@ int orc_validate(const nncu_params *p)
         return NNCU_ERR_INVALID;
     if ((p->ln_flags & NNCU_LN_COEF) || ((p->ln_flags & NNCU_LN_PRE) && (p->ln_flags & NNCU_LN_POST)))
         return NNCU_ERR_INVALID;
-    if (p->ff_act > NNCU_FF_GEGLU)
+    if (p->ff_act > NNCU_FF_GATED_SILU)
         return NNCU_ERR_INVALID;
     return NNCU_OK;
 }
@@ -455,7 +463,7 @@ int orc_create(const nncu_params *p, orc_model **out)
     const int B = p->n_streams, V = p->n_symbols;
     m->L = p->mem_len + T;
     m->HD = H * dk;
-    m->F1 = (p->ff_act == NNCU_FF_GEGLU) ? 2 * F : F;
+    m->F1 = (p->ff_act == NNCU_FF_GEGLU || p->ff_act == NNCU_FF_GATED_SILU) ? 2 * F : F;
     m->TB = T * B;
     m->LB = m->L * B;
     m->Bt = p->n_streams_total > 0 ? p->n_streams_total : B;
@@ -685,8 +693,10 @@ static void forward_range(orc_model *m, const int32_t *input, int t0, int t1)
                     o = a > 0 ? a : 0;
                 else if (p->ff_act == NNCU_FF_GELU)
                     o = gelu_f(a);
-                else
+                else if (p->ff_act == NNCU_FF_GEGLU)
                     o = gelu_f(a) * hpre[(size_t)r * m->F1 + F + i]; /* nncp.c:945-951 */
+                else
+                    o = silu_f(a) * hpre[(size_t)r * m->F1 + F + i]; /* nncp.c:957-962 */
                 hact[(size_t)r * F + i] = o;
             }
         }
@@ -804,9 +814,10 @@ int orc_eval_gradient(orc_model *m, const int32_t *targets, float *loss_out)
                 } else if (p->ff_act == NNCU_FF_GELU) {
                     dhp[(size_t)r * F1 + i] = d * gelu_grad(a);
                 } else {
+                    const int silu = p->ff_act == NNCU_FF_GATED_SILU;
                     float gate = y->hpre[(size_t)r * F1 + F + i];
-                    dhp[(size_t)r * F1 + i] = d * gate * gelu_grad(a);
-                    dhp[(size_t)r * F1 + F + i] = d * gelu_f(a);
+                    dhp[(size_t)r * F1 + i] = d * gate * (silu ? silu_grad(a) : gelu_grad(a));
+                    dhp[(size_t)r * F1 + F + i] = d * (silu ? silu_f(a) : gelu_f(a));
                 }
             }
         }

@@ -19,7 +19,7 @@ import math
 import torch
 
 LN_POST, LN_PRE, LN_FINAL, LN_COEF, LN_RMSNORM = 1, 2, 4, 8, 16
-FF_RELU, FF_GELU, FF_GEGLU = 0, 1, 2
+FF_RELU, FF_GELU, FF_GEGLU, FF_GATED_SILU = 0, 1, 2, 3
 
 
 def param_shapes(c):
@@ -27,7 +27,7 @@ def param_shapes(c):
     D, H, dk, F, P = c["d_model"], c["n_head"], c["d_key"], c["d_inner"], c["d_pos"]
     L = c["mem_len"] + c["seg_len"]
     V = c["n_symbols"]
-    F1 = 2 * F if c["ff_act"] == FF_GEGLU else F
+    F1 = 2 * F if c["ff_act"] in (FF_GEGLU, FF_GATED_SILU) else F
     out = []
     for l in range(c["n_layer"]):
         out.append((f"w_q_{l}", (H * dk, D)))
@@ -136,9 +136,12 @@ def forward(params, c, ids, mem):
             h = torch.relu(h)
         elif c["ff_act"] == FF_GELU:
             h = gelu(h)
-        else:
+        elif c["ff_act"] == FF_GEGLU:
             F = c["d_inner"]
             h = gelu(h[..., :F]) * h[..., F:]                         # nncp.c:945-951
+        else:
+            F = c["d_inner"]
+            h = h[..., :F] * torch.sigmoid(h[..., :F]) * h[..., F:]   # nncp.c:957-962
         z = h @ g("ff2").T
         if c["use_bias"]:
             z = z + g("ff_bias2")

@@ -51,6 +51,25 @@ def test_reference_cli_round_trip_and_same_file_as_host_code(pkg, tmp_path, bf16
     assert mine == blob
 
 
+@pytest.mark.gpu
+@pytest.mark.skipif(not os.path.exists(BIN), reason="host/dropin/_build/nncp_b200 was never built")
+def test_reference_cli_with_its_tokenizer_round_trips(tmp_path):
+    """--preprocess: the reference's own word tokenizer (preprocess.c, compiled unmodified into the
+    drop-in) turns the text into 16-bit symbols of a dictionary it builds, the container carries the
+    dictionary (nncp.c:3357-3413), and the B200 model codes an alphabet that is neither 256 nor a
+    power of two ((n_words + 7) & ~7 symbols, nncp.c:3382)."""
+    data = _text(30000, 5)
+    src, cmp_, back = tmp_path / "in.txt", tmp_path / "out.nncp", tmp_path / "back.txt"
+    src.write_bytes(data)
+    opts = OPTS + ["--preprocess", "300,2"]
+    r = subprocess.run([BIN] + opts + ["c", str(src), str(cmp_)], capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stdout + r.stderr
+    r = subprocess.run([BIN, "-q", "--cuda", "d", str(cmp_), str(back)], capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stdout + r.stderr
+    assert back.read_bytes() == data
+    assert cmp_.stat().st_size < 0.5 * len(data)
+
+
 @pytest.mark.skipif(not os.path.exists(BIN), reason="host/dropin/_build/nncp_b200 was never built")
 def test_reference_cli_fails_loudly_without_a_gpu(tmp_path):
     import torch

@@ -269,7 +269,7 @@ def test_one_symbol_steps_equal_whole_segment_bitwise(pkg, name, bf16, backend):
 
 
 @pytest.mark.parametrize("name", ["c0_like", "pre_final_geglu_rms", "tied_tables_longmem", "mma_dk16",
-                                  "mma_two_key_blocks", "mma_long_memory", "post_gelu"])
+                                  "mma_two_key_blocks", "mma_long_memory", "post_gelu", "gated_silu_wide"])
 @pytest.mark.parametrize("backend", [1, 2])
 def test_train_step_bf16_vs_oracle(pkg, oracle, name, backend):
     cfg, z = load_golden(name)
