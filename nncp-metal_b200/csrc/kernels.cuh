@@ -873,60 +873,106 @@ __global__ void f32_to_bf16_kernel(const float *__restrict__ src, bf16 *__restri
 
 // ------------------------------------------------------------------
 // dense embedding gradient (adjoint of nc_get_col): g[v][:] = mult * sum over rows r with
-// id[r]==v, in ascending r, of dx[r][:].  g must be zero on entry.  One block per row; the
-// block of the FIRST row carrying a symbol lists the rows of that symbol (ordered compaction
-// by warp ballots) and sums them, the others leave.
+// id[r]==v, in ascending r, of dx[r][:].  g must be zero on entry.
+// first_rows_kernel leaves in first[v] the smallest row that carries symbol v (first[] holds a
+// value >= rows on entry; integer atomicMin, so the result does not depend on the order of
+// arrival).  embed_grad_kernel runs one block per row: the block of a symbol's first row lists the
+// rows behind it that carry the symbol (ordered compaction by warp ballots), and every thread adds
+// them, in ascending order, into the four columns it owns; the other blocks leave after two loads.
+__global__ void first_rows_kernel(const int32_t *__restrict__ ids, int rows, int V, int *__restrict__ first)
+{
+    const int r = blockIdx.x * blockDim.x + threadIdx.x;
+    if (r >= rows)
+        return;
+    int id = ids[r];
+    id = id < 0 ? 0 : (id >= V ? V - 1 : id);
+    atomicMin(first + id, r);
+}
+
 template <typename T>
 __global__ void __launch_bounds__(128)
-embed_grad_kernel(const int32_t *__restrict__ ids, const T *__restrict__ dx,
-                  float *__restrict__ g, int rows, int D, float mult, int V)
+embed_grad_kernel(const int32_t *__restrict__ ids, const T *__restrict__ dx, float *__restrict__ g,
+                  const int *__restrict__ first, int rows, int D, float mult, int V)
 {
     pdl_trigger();
     pdl_wait();
-    extern __shared__ int32_t sm_i[]; // sids[rows], list[rows]
-    int32_t *sids = sm_i, *list = sm_i + rows;
-    __shared__ int seen_before, wcnt[4], count;
+    constexpr int SPAN = 2048; // rows listed per pass
+    __shared__ int list[SPAN];
+    __shared__ int wcnt[4], total;
     const int r0 = blockIdx.x;
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    if (threadIdx.x == 0) {
-        seen_before = 0;
-        count = 0;
-    }
-    for (int i = threadIdx.x; i < rows; i += blockDim.x) {
-        int id = ids[i];
-        sids[i] = id < 0 ? 0 : (id >= V ? V - 1 : id);
-    }
-    __syncthreads();
-    const int v = sids[r0];
-    for (int i = threadIdx.x; i < r0; i += blockDim.x)
-        if (sids[i] == v)
-            seen_before = 1; // benign race: every writer stores the same value
-    __syncthreads();
-    if (seen_before)
+    int v = ids[r0];
+    v = v < 0 ? 0 : (v >= V ? V - 1 : v);
+    if (first[v] != r0)
         return;
-    for (int base = r0; base < rows; base += 128) {
-        const int r = base + threadIdx.x;
-        const bool hit = r < rows && sids[r] == v;
-        const unsigned bal = __ballot_sync(0xffffffffu, hit);
-        if (lane == 0)
-            wcnt[warp] = __popc(bal);
-        __syncthreads();
-        int pos = count;
-        for (int w = 0; w < warp; w++)
-            pos += wcnt[w];
-        if (hit)
-            list[pos + __popc(bal & ((1u << lane) - 1u))] = r;
-        __syncthreads();
-        if (threadIdx.x == 0)
-            count += wcnt[0] + wcnt[1] + wcnt[2] + wcnt[3];
-        __syncthreads();
-    }
-    const int n = count;
-    for (int c = threadIdx.x; c < D; c += blockDim.x) {
-        float s = 0.0f;
-        for (int k = 0; k < n; k++)
-            s += to_f(dx[(size_t)list[k] * D + c]);
-        g[(size_t)v * D + c] = s * mult;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (int c0 = 0; c0 < D; c0 += 512) { // four columns per thread and pass
+        float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        for (int span0 = r0; span0 < rows; span0 += SPAN) {
+            // ordered list of the rows of this span that carry the symbol (compaction by warp ballots)
+            __syncthreads(); // the list of the span before has been read
+            if (threadIdx.x == 0)
+                total = 0;
+            const int span1 = min(rows, span0 + SPAN);
+            int idr[SPAN / 128]; // all of the span's ids are requested before the first is looked at
+#pragma unroll
+            for (int j = 0; j < SPAN / 128; j++) {
+                const int r = span0 + 128 * j + threadIdx.x;
+                idr[j] = r < span1 ? ids[r] : -1;
+            }
+#pragma unroll
+            for (int j = 0; j < SPAN / 128; j++) {
+                const int base = span0 + 128 * j;
+                if (base >= span1)
+                    break;
+                const int r = base + threadIdx.x;
+                int id = idr[j];
+                if (r < span1)
+                    id = id < 0 ? 0 : (id >= V ? V - 1 : id);
+                const bool hit = id == v;
+                const unsigned bal = __ballot_sync(0xffffffffu, hit);
+                if (lane == 0)
+                    wcnt[warp] = __popc(bal);
+                __syncthreads();
+                int pos = total;
+#pragma unroll
+                for (int w = 0; w < 4; w++)
+                    pos += w < warp ? wcnt[w] : 0;
+                if (hit)
+                    list[pos + __popc(bal & ((1u << lane) - 1u))] = r;
+                __syncthreads();
+                if (threadIdx.x == 0)
+                    total += wcnt[0] + wcnt[1] + wcnt[2] + wcnt[3];
+            }
+            __syncthreads();
+            const int n = total;
+            // sixteen rows' loads go out before the first is added: the sum of a frequent symbol is a
+            // chain of additions in row order, but its loads need not wait for one another
+            for (int k0 = 0; k0 < n; k0 += 16) {
+                float x[16][4];
+#pragma unroll
+                for (int u = 0; u < 16; u++) {
+                    const T *src = dx + (size_t)list[min(k0 + u, n - 1)] * D + c0;
+#pragma unroll
+                    for (int k = 0; k < 4; k++) {
+                        const int c = threadIdx.x + 128 * k;
+                        x[u][k] = (c0 + c < D) ? to_f(src[c]) : 0.0f;
+                    }
+                }
+#pragma unroll
+                for (int u = 0; u < 16; u++)
+                    if (k0 + u < n) {
+#pragma unroll
+                        for (int k = 0; k < 4; k++)
+                            acc[k] += x[u][k];
+                    }
+            }
+        }
+#pragma unroll
+        for (int k = 0; k < 4; k++) {
+            const int c = c0 + threadIdx.x + 128 * k;
+            if (c < D)
+                g[(size_t)v * D + c] = acc[k] * mult;
+        }
     }
 }
 

@@ -179,6 +179,7 @@ struct nncu_model {
     int32_t *ids_dev, *tgt_dev;
     int32_t *tgt_fixed; // the targets whose entries of dz carry the (p - 1) correction
     int *dz_fixed;      // device flag: dz has been corrected since the last forward pass
+    int *first_dev;     // [V] smallest row carrying each symbol (embedding gradient)
     int *err_flag;
     unsigned long long *hash_dev;
     TransposeJob *jobs_dev;
@@ -567,6 +568,10 @@ static int forward_range(nncu_model *m, int t0, int t1)
         // memory rows (once per segment) and the segment rows (nncp.c:659-695)
         // one GEMM against [w_q ; w_kv] (adjacent in the flat buffers): rows of the memory get
         // a q they never use, which costs less than a second launch
+        // one GEMM over [memory ; segment] rows.  Measured alternative: the memory rows' K|V projections of
+        // all layers on the side stream at the start of the pass, the main chain projecting the segment
+        // rows only -- 2.686 against 2.594 ms per step: twelve more launches competing for SMs cost the
+        // latency-bound main chain more than the shorter projection saves.
         if (t0 == 0 && M > 0)
             NNCU_TRY((mm_nt<AT, AT>(m, M * B + nr, 3 * HD, D, hc, D, o.w_q, at<AT>(a.qkv, 0), 3 * HD,
                                     wf(m, o.b_q), HD)));
@@ -750,6 +755,13 @@ static int backward(nncu_model *m)
 
     // loss and d logits (nncp.c:1170-1175)
     const float sc = 1.0f / ((float)m->T * (float)m->Bt);
+    if (!(m->comm && m->sparse_embed)) {
+        // which row carries each symbol first: needed only by the embedding gradient at the very end
+        cudaStream_t s2 = side_fork(m);
+        CUDA_TRY(cudaMemsetAsync(m->first_dev, 0x7f, sizeof(int) * (size_t)V, s2));
+        launch_k(first_rows_kernel, dim3(ceil_div(TB, 256)), dim3(256), 0, s2, (const int32_t *)m->ids_dev, TB, V, m->first_dev);
+        KERNEL_CHECK();
+    }
     launch_k(loss_fix_kernel<AT>, dim3(1), dim3(256), 0, m->st, (const float *)m->probs, (const int32_t *)m->tgt_dev, m->tgt_fixed,
              m->dz_fixed, dz, m->logp, m->loss_dev, TB, V, sc);
     KERNEL_CHECK();
@@ -867,13 +879,17 @@ static int backward(nncu_model *m)
         NNCU_TRY(nccl_ok(nc->AllGather(dx, m->dx_all, (size_t)TB * D, sizeof(AT) == 2 ? NCCL_BF16 : NCCL_F32, m->comm, m->st3),
                          "ncclAllGather"));
         CUDA_TRY(cudaMemsetAsync(gf(m, m->embed), 0, sizeof(float) * (size_t)V * D, m->st3));
-        launch_k(embed_grad_kernel<AT>, dim3(rows), dim3(128), 2 * sizeof(int32_t) * rows, m->st3, (const int32_t *)m->ids_all,
-                 (const AT *)m->dx_all, gf(m, m->embed), rows, D, emul, V);
+        CUDA_TRY(cudaMemsetAsync(m->first_dev, 0x7f, sizeof(int) * (size_t)V, m->st3));
+        launch_k(first_rows_kernel, dim3(ceil_div(rows, 256)), dim3(256), 0, m->st3, (const int32_t *)m->ids_all, rows, V, m->first_dev);
+        KERNEL_CHECK();
+        launch_k(embed_grad_kernel<AT>, dim3(rows), dim3(128), 0, m->st3, (const int32_t *)m->ids_all, (const AT *)m->dx_all,
+                 gf(m, m->embed), (const int *)m->first_dev, rows, D, emul, V);
         KERNEL_CHECK();
         NNCU_TRY(opt_range(m, m->embed, m->embed_out, false));
     } else {
         CUDA_TRY(cudaMemsetAsync(gf(m, m->embed), 0, sizeof(float) * (size_t)V * D, m->st));
-        launch_k(embed_grad_kernel<AT>, dim3(TB), dim3(128), 2 * sizeof(int32_t) * TB, m->st, m->ids_dev, dx, gf(m, m->embed), TB, D, emul, V);
+        launch_k(embed_grad_kernel<AT>, dim3(TB), dim3(128), 0, m->st, (const int32_t *)m->ids_dev, (const AT *)dx, gf(m, m->embed),
+                 (const int *)m->first_dev, TB, D, emul, V);
         KERNEL_CHECK();
         NNCU_TRY(flush_reductions(m));
         side_join(m);
@@ -1238,7 +1254,7 @@ int nncu_create(const nncu_params *p, nncu_model **out)
     size_t oSkw = take(skw_floats * 4 + 256);
     size_t oLogp = take((size_t)TB * 4), oLoss = take(256);
     size_t oIds = take((size_t)TB * 4), oTgt = take((size_t)TB * 4), oErr = take(256), oHash = take(256);
-    size_t oTgtFixed = take((size_t)TB * 4);
+    size_t oTgtFixed = take((size_t)TB * 4), oFirst = take((size_t)V * 4);
     // transposed-shadow jobs
     std::vector<TransposeJob> jobs;
     int tiles = 0;
@@ -1287,6 +1303,7 @@ int nncu_create(const nncu_params *p, nncu_model **out)
     m->err_flag = (int *)(A + oErr); m->hash_dev = (unsigned long long *)(A + oHash);
     m->dz_fixed = m->err_flag + 16; // same 256-byte slot, zeroed with the arena
     m->tgt_fixed = (int32_t *)(A + oTgtFixed);
+    m->first_dev = (int *)(A + oFirst);
     m->jobs_dev = (TransposeJob *)(A + oJobs);
     m->n_jobs = (int)jobs.size(); m->n_job_tiles = tiles;
     m->coder_dev = (uint16_t *)(A + oCoder);
@@ -1329,10 +1346,6 @@ int nncu_create(const nncu_params *p, nncu_model **out)
     if ((size_t)2 * V * 4 > 48 * 1024) {
         cudaFuncSetAttribute(coder_paths_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 2 * V * 4);
         cudaFuncSetAttribute(coder_trees_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 2 * V * 4);
-    }
-    if (2 * sizeof(int32_t) * TB > 48 * 1024) {
-        cudaFuncSetAttribute(embed_grad_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 2 * (int)sizeof(int32_t) * TB);
-        cudaFuncSetAttribute(embed_grad_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 2 * (int)sizeof(int32_t) * TB);
     }
 
     // ---- initial values (trf_init, nncp.c:341-497), computed on the host
@@ -1718,15 +1731,6 @@ int nncu_comm_init(nncu_model *m, int n_ranks, int rank, const void *id)
     if (n_ranks > 1) { // landing areas of the embedding-gradient gather
         CUDA_TRY(cudaMalloc(&m->ids_all, sizeof(int32_t) * (size_t)m->TB * n_ranks));
         CUDA_TRY(cudaMalloc(&m->dx_all, m->esz * (size_t)m->TB * m->D * n_ranks));
-        const size_t sm = 2 * sizeof(int32_t) * (size_t)m->TB * n_ranks;
-        if (sm > 200 * 1024)
-            return nncu_fail(NNCU_ERR_RANGE, "%d rows of all ranks do not fit the embedding-gradient kernel", m->TB * n_ranks);
-        if (sm > 48 * 1024) {
-            if (m->bf)
-                CUDA_TRY(cudaFuncSetAttribute(embed_grad_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm));
-            else
-                CUDA_TRY(cudaFuncSetAttribute(embed_grad_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm));
-        }
     }
     return NNCU_OK;
 }
