@@ -596,7 +596,7 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     extern __shared__ unsigned char smraw_[];
     unsigned char *sm = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smraw_) + 1023) & ~(uintptr_t)1023);
     uint64_t *bars = reinterpret_cast<uint64_t *>(sm + BwdSmem::BAR);
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 10);
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 11);
     volatile int *abort_s = reinterpret_cast<volatile int *>(tmem_slot + 1);
     float *brs = reinterpret_cast<float *>(sm + BwdSmem::BRS);
     float *xch = reinterpret_cast<float *>(sm + BwdSmem::XCH);
@@ -629,6 +629,7 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         mbar_init(smem_u32(&bars[7]), NROW); // r3
         mbar_init(smem_u32(&bars[8]), 1);    // g2b: dV
         mbar_init(smem_u32(&bars[9]), 1);    // g3b: dQ (table part), dRwin, column sums
+        mbar_init(smem_u32(&bars[10]), 1);   // load of dO and V (needed from G2 on)
         *abort_s = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -649,7 +650,7 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     const uint32_t bar_load = smem_u32(&bars[0]), bar_free = smem_u32(&bars[1]), bar_g1 = smem_u32(&bars[2]),
                    bar_r1 = smem_u32(&bars[3]), bar_g2 = smem_u32(&bars[4]), bar_r2 = smem_u32(&bars[5]),
                    bar_g3 = smem_u32(&bars[6]), bar_r3 = smem_u32(&bars[7]), bar_g2b = smem_u32(&bars[8]),
-                   bar_g3b = smem_u32(&bars[9]);
+                   bar_g3b = smem_u32(&bars[9]), bar_load2 = smem_u32(&bars[10]);
 
     if (warp == 0) {
         if (lane == 0) {
@@ -659,8 +660,9 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                 if (it > 0 && !mbar_wait(bar_free, (uint32_t)((it - 1) & 1), abort_s, err_flag, 21))
                     break;
                 const int wlo = j0 - 63 + c0;
-                const uint32_t bytes = 2 * 256 * 128 + (has_wr ? WIN * 128 : 0) + (it == 0 ? 2 * 128 * 128 : 0);
-                mbar_expect_tx(bar_load, bytes);
+                // Q, K and the table window complete the first barrier (S and E can start), dO and V the second
+                mbar_expect_tx(bar_load, 256 * 128 + (has_wr ? WIN * 128 : 0) + (it == 0 ? 128 * 128 : 0));
+                mbar_expect_tx(bar_load2, 256 * 128 + (it == 0 ? 128 * 128 : 0));
                 if (it == 0) {
                     tma_load_3d(sm0 + BwdSmem::Q, &map_q, bar_load, h * DK, b0, 0);
                     tma_load_3d(sm0 + BwdSmem::Q + 64 * 128, &map_q, bar_load, h * DK, b0 + 1, 0);
@@ -672,11 +674,11 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                     tma_load_3d(sm0 + BwdSmem::R + 191 * 128, &map_wr0, bar_load, 0, 0, h); // table row 0
                 }
                 if (it == 0) {
-                    tma_load_3d(sm0 + BwdSmem::DO, &map_do, bar_load, h * DK, b0, 0);
-                    tma_load_3d(sm0 + BwdSmem::DO + 64 * 128, &map_do, bar_load, h * DK, b0 + 1, 0);
+                    tma_load_3d(sm0 + BwdSmem::DO, &map_do, bar_load2, h * DK, b0, 0);
+                    tma_load_3d(sm0 + BwdSmem::DO + 64 * 128, &map_do, bar_load2, h * DK, b0 + 1, 0);
                 }
-                tma_load_3d(sm0 + BwdSmem::V, &map_kv, bar_load, HD + h * DK, b0, j0);
-                tma_load_3d(sm0 + BwdSmem::V + 128 * 128, &map_kv, bar_load, HD + h * DK, b0 + 1, j0);
+                tma_load_3d(sm0 + BwdSmem::V, &map_kv, bar_load2, HD + h * DK, b0, j0);
+                tma_load_3d(sm0 + BwdSmem::V + 128 * 128, &map_kv, bar_load2, HD + h * DK, b0 + 1, j0);
             }
         }
     } else if (warp == 1) {
@@ -707,6 +709,8 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                         umma_bf16(tmem + 256, dQk + 2 * k, dRk + 2 * k, idE, k > 0);
                 }
                 umma_commit(bar_g1);
+                if (!mbar_wait(bar_load2, (uint32_t)(it & 1), abort_s, err_flag, 31))
+                    break;
                 if (!mbar_wait(bar_r1, (uint32_t)(it & 1), abort_s, err_flag, 24))
                     break;
                 fence_after_sync();
