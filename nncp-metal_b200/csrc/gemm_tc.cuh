@@ -754,7 +754,14 @@ static int gemm(cudaStream_t st, int M, int N, int K, const bf16 *A, long lda, c
         if (min_tiles < 1)
             min_tiles = 200;
     }
-    if (mt * ceil_div(N, 256) >= min_tiles)
+    // fp32 output doubles the epilogue's bytes per tile: two 128-wide CTAs per SM, one's epilogue under
+    // the other's mainloop, beat one 256-wide CTA (output head, 2048 x 16384 x 512, cold: 80.7 against 91.2 us)
+    static int f32_wide = -1;
+    if (f32_wide < 0) {
+        const char *e = getenv("NNCU_TC_F32_256");
+        f32_wide = (e && e[0] == '1') ? 1 : 0;
+    }
+    if (mt * ceil_div(N, 256) >= min_tiles && (sizeof(TC) == 2 || f32_wide))
         return launch<256, TC, AMN, BMN>(st, M, N, K, A, lda, B, ldb, C, ldc, bias, addsrc, err_flag, bias_n);
     if (mt * ceil_div(N, 128) >= min_tiles || N <= 64)
         return launch<128, TC, AMN, BMN>(st, M, N, K, A, lda, B, ldb, C, ldc, bias, addsrc, err_flag, bias_n);
