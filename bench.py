@@ -208,8 +208,10 @@ def exchange_name(world):
     if os.environ.get("NNCU_SHARDED_UPDATE") == "1":
         return ("per-layer reduce-scatter, RMSProp on the rank's shard, all-gather of the bf16 weights; small parameters "
                 "all-reduced; embedding gradient from gathered ids and rows (Ring / LL128 / 32 channels pinned)")
-    return ("per-layer NCCL all-reduce inside the backward pass (overlapped; Ring / LL128 / 32 channels pinned), every rank "
-            "applies the whole RMSProp step; embedding gradient from gathered ids and rows instead of the dense table")
+    per = os.environ.get("NNCU_BUCKET_LAYERS") or ("2" if world >= 8 else "1")
+    return (f"NCCL all-reduce of {per} layer(s) at a time inside the backward pass (overlapped; Ring / LL128 / 32 channels "
+            "pinned), every rank applies the whole RMSProp step; embedding gradient from gathered ids and rows instead of "
+            "the dense table")
 
 
 def run_reference(args, c):

@@ -722,6 +722,23 @@ static int exchange_update(nncu_model *m, size_t begin, size_t mid, size_t end)
     return NNCU_OK;
 }
 
+// Layers per gradient exchange.  One all-reduce per layer overlaps best, but each NCCL operation has
+// a fixed cost that grows with the number of ranks (a ring all-reduce is 2(N-1) hops), so at 8
+// ranks several layers share one.  NNCU_BUCKET_LAYERS overrides.  The sharded update keeps one.
+static int bucket_layers(nncu_model *m)
+{
+    if (!m->comm || m->shard_update)
+        return 1;
+    static int env = -1;
+    if (env < 0) {
+        const char *e = getenv("NNCU_BUCKET_LAYERS");
+        env = e ? std::max(1, atoi(e)) : 0;
+    }
+    if (env)
+        return env;
+    return m->comm_ranks >= 8 ? 2 : 1; // measured at 8 GPUs (symbols/s): 1 layer 907 k, 2 layers 979 k, 4 layers 973 k, 12 layers 845 k
+}
+
 // ------------------------------------------------------------------ backward
 
 template <typename AT>
@@ -856,7 +873,19 @@ static int backward(nncu_model *m)
         }
         NNCU_TRY(flush_reductions(m));
         side_join(m); // this layer's weight gradients are done before dhp, dqkv, ds1, ds2 are rewritten
-        {
+        const int G = bucket_layers(m);
+        if (G > 1) {
+            // several layers per exchange: their slots are contiguous, and the group is complete when its
+            // lowest layer is (the pass runs from the last layer down)
+            if (l % G == 0) {
+                const int l1 = std::min(l + G, m->nl);
+                const size_t lb = o.w_q, le = l1 < m->nl ? m->lo[l1].w_q : m->tail_begin;
+                NNCU_TRY(exchange_bucket(m, lb, le));
+                NNCU_TRY(opt_range(m, lb, le, false));
+            }
+            if (l == m->nl - 1)
+                NNCU_TRY(exchange_update(m, m->embed_out, m->out_bias != NONE ? m->out_bias : m->n_floats, m->n_floats));
+        } else {
             // layer l's slots are contiguous; tied tables live in layer 0, which is exchanged last
             const size_t lb = o.w_q, le = l + 1 < m->nl ? m->lo[l + 1].w_q : m->tail_begin;
             NNCU_TRY(exchange_update(m, lb, o.small, le));
