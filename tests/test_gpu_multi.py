@@ -2,7 +2,7 @@
 identical weights on both, and the sharded codec round-trips a file whose header names the rank count.
 
 NVLS is off (NCCL_NVLS_ENABLE=0): a rank that dies in a test must not leave its memory bound to an
-NVLink multicast object."""
+NVLS group of the switch."""
 import os
 import sys
 
