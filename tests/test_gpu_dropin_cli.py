@@ -70,6 +70,31 @@ def test_reference_cli_with_its_tokenizer_round_trips(tmp_path):
     assert cmp_.stat().st_size < 0.5 * len(data)
 
 
+@pytest.mark.gpu
+@pytest.mark.skipif(not os.path.exists(BIN), reason="host/dropin/_build/nncp_b200 was never built")
+def test_reference_cli_retrain_without_dropout_round_trips(tmp_path):
+    """--retrain_period / --retrain_len: the reference's retrain_block (nncp.c:2821-2941, host code
+    compiled unmodified into the drop-in) re-trains the model on the symbols already coded, on both
+    sides; the file must still round-trip, must differ from the file coded without retraining, and
+    retraining with dropout is refused."""
+    data = _text(40000, 9)
+    src, plain, cmp_, back = tmp_path / "in.bin", tmp_path / "plain.nncp", tmp_path / "out.nncp", tmp_path / "back.bin"
+    src.write_bytes(data)
+    small = OPTS + ["--block_len", "8192"]
+    r = subprocess.run([BIN] + small + ["c", str(src), str(plain)], capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stdout + r.stderr
+    opts = small + ["--retrain_period", "8192", "--retrain_len", "16384", "--retrain_dropout", "0", "--retrain_dropout_att", "0"]
+    r = subprocess.run([BIN] + opts + ["c", str(src), str(cmp_)], capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stdout + r.stderr
+    r = subprocess.run([BIN, "-q", "--cuda", "d", str(cmp_), str(back)], capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stdout + r.stderr
+    assert back.read_bytes() == data
+    assert cmp_.read_bytes()[64:] != plain.read_bytes()[64:]
+    bad = small + ["--retrain_period", "8192", "--retrain_len", "16384", "--retrain_dropout", "0.1"]
+    r = subprocess.run([BIN] + bad + ["c", str(src), str(tmp_path / "x")], capture_output=True, text=True, timeout=600)
+    assert r.returncode != 0 and "dropout" in (r.stdout + r.stderr)
+
+
 @pytest.mark.skipif(not os.path.exists(BIN), reason="host/dropin/_build/nncp_b200 was never built")
 def test_reference_cli_fails_loudly_without_a_gpu(tmp_path):
     import torch
