@@ -764,41 +764,47 @@ __global__ void __launch_bounds__(256) softmax_rows_reg_kernel(float *__restrict
         }
 }
 
-// The target correction of dz and the loss in one block: for every row r, dz[r][t_r] =
-// (p[r][t_r] - 1) * scale and logp[r] = ln p[r][t_r] (nc_indexed_log and the adjoint of the softmax,
-// nncp.c:1170-1175); loss = sum_r logp[r] in a fixed order (thread i adds rows i, i + 256, ...;
-// then the block sum).  A second call for
-// the same forward pass (*dz_fixed != 0) first puts the old targets' entries back to p * scale.
+// The target correction of dz: for every row r, dz[r][t_r] = (p[r][t_r] - 1) * scale and
+// logp[r] = ln p[r][t_r] (nc_indexed_log and the adjoint of the softmax, nncp.c:1170-1175).  A
+// second call for the same forward pass (*dz_fixed != 0) first puts the old targets' entries back
+// to p * scale.  loss_sum_kernel, queued behind it, adds the logp in a fixed order (thread i adds
+// rows i, i + 256, ...; then the block sum) and raises the flag.
 template <typename T>
 __global__ void __launch_bounds__(256)
 loss_fix_kernel(const float *__restrict__ probs, const int32_t *__restrict__ targets, int32_t *__restrict__ fixed_targets,
-                int *__restrict__ dz_fixed, T *__restrict__ dz, float *__restrict__ logp, float *__restrict__ loss, int rows,
-                int V, float scale)
+                const int *__restrict__ dz_fixed, T *__restrict__ dz, float *__restrict__ logp, int rows, int V, float scale)
+{
+    pdl_trigger();
+    pdl_wait();
+    const int r = blockIdx.x * 256 + threadIdx.x;
+    if (r >= rows)
+        return;
+    const float *pr = probs + (size_t)r * V;
+    T *d = dz + (size_t)r * V;
+    if (*dz_fixed != 0) {
+        const int old = fixed_targets[r];
+        d[old] = from_f<T>(pr[old] * scale);
+    }
+    int t = targets[r];
+    t = t < 0 ? 0 : (t >= V ? V - 1 : t);
+    const float pt = pr[t];
+    d[t] = from_f<T>((pt - 1.0f) * scale);
+    fixed_targets[r] = t;
+    logp[r] = logf(pt);
+}
+
+__global__ void __launch_bounds__(256) loss_sum_kernel(const float *__restrict__ v, int n, float *__restrict__ out,
+                                                       int *__restrict__ dz_fixed)
 {
     pdl_trigger();
     pdl_wait();
     __shared__ float red[8];
-    const bool undo = *dz_fixed != 0;
     float s = 0.0f;
-    for (int r = threadIdx.x; r < rows; r += 256) {
-        const float *pr = probs + (size_t)r * V;
-        T *d = dz + (size_t)r * V;
-        if (undo) {
-            const int old = fixed_targets[r];
-            d[old] = from_f<T>(pr[old] * scale);
-        }
-        int t = targets[r];
-        t = t < 0 ? 0 : (t >= V ? V - 1 : t);
-        const float pt = pr[t];
-        d[t] = from_f<T>((pt - 1.0f) * scale);
-        fixed_targets[r] = t;
-        const float lp = logf(pt);
-        logp[r] = lp;
-        s += lp;
-    }
+    for (int i = threadIdx.x; i < n; i += 256)
+        s += v[i];
     s = block_sum_256(s, red);
     if (threadIdx.x == 0) {
-        *loss = s;
+        *out = s;
         *dz_fixed = 1;
     }
 }

@@ -779,8 +779,10 @@ static int backward(nncu_model *m)
         launch_k(first_rows_kernel, dim3(ceil_div(TB, 256)), dim3(256), 0, s2, (const int32_t *)m->ids_dev, TB, V, m->first_dev);
         KERNEL_CHECK();
     }
-    launch_k(loss_fix_kernel<AT>, dim3(1), dim3(256), 0, m->st, (const float *)m->probs, (const int32_t *)m->tgt_dev, m->tgt_fixed,
-             m->dz_fixed, dz, m->logp, m->loss_dev, TB, V, sc);
+    launch_k(loss_fix_kernel<AT>, dim3(ceil_div(TB, 256)), dim3(256), 0, m->st, (const float *)m->probs, (const int32_t *)m->tgt_dev,
+             m->tgt_fixed, (const int *)m->dz_fixed, dz, m->logp, TB, V, sc);
+    KERNEL_CHECK();
+    launch_k(loss_sum_kernel, dim3(1), dim3(256), 0, m->st, (const float *)m->logp, TB, m->loss_dev, m->dz_fixed);
     KERNEL_CHECK();
     const AT *xf = (p.ln_flags & NNCU_LN_FINAL) ? atc<AT>(m->xf, 0) : atc<AT>(m->xlast, 0);
     if (m->out_bias != NONE)
