@@ -11,7 +11,8 @@ streams are sharded across ranks and gradients are summed with one NCCL all-redu
 
 `value`   device-resident ids/targets, nothing read back (CUDA events, max over ranks).
 `e2e`     the same steps through the host-buffer plugin calls: ids from pinned host memory
-          every step, the coder-ready prob0 paths and the loss read back every step.
+          every step, the coder-ready prob0 paths and the loss read back every step (encoder order:
+          the next segment's forward pass is queued before the host waits for this segment's results).
 `roofline` the tcgen05 GEMM kernel: sum of 2*M*N*K over its launches / sum of their CUDA-event
           durations, against the measured bf16 peak.
 `attention` the isolated attention op of BASELINE config[1] (forward, and forward + backward)
@@ -565,11 +566,15 @@ def main():
     paths = np.zeros((T * B, max(nb, 1)), np.uint16)
     nbits = C.c_int()
 
-    def step_host(s):
+    def step_host(s, last=True):
         # encoder order: everything is queued before the host waits for anything, so the GPU
-        # never idles on the host (the range coder would run between _begin and _end)
+        # never idles on the host (the range coder would run between _begin and _end).  An encoder
+        # knows the next segment's symbols too: its forward pass is queued (last=False) before the host
+        # waits for this segment's coder values and loss.
         ids, tg = ids_h[s].numpy(), tg_h[s].numpy()
-        m.eval(-1, ids, read=False)
+        if not step_host.queued:
+            m.eval(-1, ids, read=False)
+        step_host.queued = False
         if nb:
             ck(lib.nncu_coder_paths_begin(m.h, 0, T, tg.ctypes.data_as(C.c_void_p)))
         else:
@@ -581,9 +586,14 @@ def main():
             ck(lib.nncu_eval_gradient(m.h, tg.ctypes.data_as(C.c_void_p), None))
             sharded.reduce_gradients()
             m.update()
+        if not last:
+            m.eval(-1, ids_h[s + 1].numpy(), read=False)
+            step_host.queued = True
         if nb:
             ck(lib.nncu_coder_paths_end(m.h, paths.ctypes.data_as(C.c_void_p), C.byref(nbits)))
         return m.read_loss()
+
+    step_host.queued = False
 
     def ck(rc):
         if rc != 0:
@@ -647,7 +657,7 @@ def main():
         t0 = time.perf_counter()
         e0.record(stream)
         for s in range(W, W + K):
-            step_host(s)
+            step_host(s, last=(s == W + K - 1))
         e1.record(stream)
         barrier()
         times_e2e.append(max_over_ranks(max(e0.elapsed_time(e1), (time.perf_counter() - t0) * 1e3)))

@@ -177,6 +177,7 @@ struct nncu_model {
     bool fuse_update = false; // this backward pass applies the optimizer to each bucket as it completes
     float *hyper_dev = nullptr; // {lr, bias correction} of the fused optimizer step
     int32_t *ids_dev, *tgt_dev;
+    int32_t *sym_dev;   // [TB] symbols whose coder paths are wanted (nncu_coder_paths*)
     int32_t *tgt_fixed; // the targets whose entries of dz carry the (p - 1) correction
     int *dz_fixed;      // device flag: dz has been corrected since the last forward pass
     int *first_dev;     // [V] smallest row carrying each symbol (embedding gradient)
@@ -1285,7 +1286,7 @@ int nncu_create(const nncu_params *p, nncu_model **out)
     size_t oSkw = take(skw_floats * 4 + 256);
     size_t oLogp = take((size_t)TB * 4), oLoss = take(256);
     size_t oIds = take((size_t)TB * 4), oTgt = take((size_t)TB * 4), oErr = take(256), oHash = take(256);
-    size_t oTgtFixed = take((size_t)TB * 4), oFirst = take((size_t)V * 4);
+    size_t oTgtFixed = take((size_t)TB * 4), oFirst = take((size_t)V * 4), oSym = take((size_t)TB * 4);
     // transposed-shadow jobs
     std::vector<TransposeJob> jobs;
     int tiles = 0;
@@ -1335,6 +1336,7 @@ int nncu_create(const nncu_params *p, nncu_model **out)
     m->dz_fixed = m->err_flag + 16; // same 256-byte slot, zeroed with the arena
     m->tgt_fixed = (int32_t *)(A + oTgtFixed);
     m->first_dev = (int *)(A + oFirst);
+    m->sym_dev = (int32_t *)(A + oSym);
     m->jobs_dev = (TransposeJob *)(A + oJobs);
     m->n_jobs = (int)jobs.size(); m->n_job_tiles = tiles;
     m->coder_dev = (uint16_t *)(A + oCoder);
@@ -1452,6 +1454,8 @@ static int eval_common(nncu_model *m, int output_index)
     if (output_index > 0 && output_index != m->steps_done)
         return nncu_fail(NNCU_ERR_STATE, "step %d issued after %d steps", output_index, m->steps_done);
     bind_xin(m);
+    if (m->coder_rows) // coder values of the pass before are still being produced from its probabilities
+        CUDA_TRY(cudaStreamWaitEvent(m->st, m->ev_coder, 0));
     int t0 = output_index < 0 ? 0 : output_index, t1 = output_index < 0 ? m->T : output_index + 1;
     auto body = [&]() { return m->bf ? forward_range<bf16>(m, t0, t1) : forward_range<float>(m, t0, t1); };
     int rc = output_index < 0 ? run_graphed(m, GRAPH_FWD, body) : body();
@@ -1907,18 +1911,21 @@ static int coder_paths_enqueue(nncu_model *m, int t0, int nt, const int32_t *sym
     CUDA_TRY(cudaEventSynchronize(m->ev_sym));   // the symbol staging area is free again
     CUDA_TRY(cudaEventSynchronize(m->ev_coder)); // and so is the landing area
     memcpy(m->sym_pin, sym_host, sizeof(int32_t) * rows);
-    // on the device the symbols use the target buffer of the same rows (the targets arrive later)
-    CUDA_TRY(cudaMemcpyAsync(m->tgt_dev, m->sym_pin, sizeof(int32_t) * rows, cudaMemcpyHostToDevice, m->st));
-    CUDA_TRY(cudaEventRecord(m->ev_sym, m->st));
+    // The coder values only read the probabilities: they are produced on the side stream, beside the
+    // backward pass the caller queues next.  The next forward pass, which overwrites the
+    // probabilities, is ordered behind them either by nncu_coder_paths_end (the host has waited for
+    // them) or, if it is queued earlier, by a wait on their event in nncu_eval.
+    cudaStream_t st = side_fork(m);
+    CUDA_TRY(cudaMemcpyAsync(m->sym_dev, m->sym_pin, sizeof(int32_t) * rows, cudaMemcpyHostToDevice, st));
+    CUDA_TRY(cudaEventRecord(m->ev_sym, st));
     if (m->V >= 1024 && m->V <= 16384)
-        coder_paths_fast_kernel<<<rows, 256, 0, m->st>>>(m->probs + (size_t)t0 * m->B * m->V, m->tgt_dev, m->coder_dev,
-                                                         m->V, nb);
+        coder_paths_fast_kernel<<<rows, 256, 0, st>>>(m->probs + (size_t)t0 * m->B * m->V, m->sym_dev, m->coder_dev, m->V, nb);
     else
-        coder_paths_kernel<<<rows, 256, (size_t)2 * m->V * 4, m->st>>>(m->probs + (size_t)t0 * m->B * m->V,
-                                                                      m->tgt_dev, m->coder_dev, m->V, nb);
+        coder_paths_kernel<<<rows, 256, (size_t)2 * m->V * 4, st>>>(m->probs + (size_t)t0 * m->B * m->V, m->sym_dev,
+                                                                   m->coder_dev, m->V, nb);
     KERNEL_CHECK();
-    CUDA_TRY(cudaMemcpyAsync(m->coder_pin, m->coder_dev, sizeof(uint16_t) * (size_t)rows * nb, cudaMemcpyDeviceToHost, m->st));
-    CUDA_TRY(cudaEventRecord(m->ev_coder, m->st));
+    CUDA_TRY(cudaMemcpyAsync(m->coder_pin, m->coder_dev, sizeof(uint16_t) * (size_t)rows * nb, cudaMemcpyDeviceToHost, st));
+    CUDA_TRY(cudaEventRecord(m->ev_coder, st));
     m->coder_rows = rows;
     m->coder_nb = nb;
     return NNCU_OK;
