@@ -87,6 +87,13 @@ typedef struct nch_model_ops {
     int (*update)(void *ctx);
     /* range decoder on the device (nncu_decoder_begin / nncu_decode_steps / nncu_decoder_end);
        all three NULL for a model without one */
+    /* encoder order (nncu_coder_paths_begin / _end, nncu_eval_gradient without its loss, nncu_read_loss):
+       lets nch_process_block queue the backward pass and the next forward pass before it range-codes a
+       segment; all four NULL for a model without them */
+    int (*coder_paths_begin)(void *ctx, int t0, int nt, const int32_t *sym);
+    int (*coder_paths_end)(void *ctx, uint16_t *prob0, int *n_bits);
+    int (*eval_gradient_queue)(void *ctx, const int32_t *expected);
+    int (*read_loss)(void *ctx, float *loss);
     int (*decoder_begin)(void *ctx, const uint8_t *payload, size_t len);
     int (*decode_steps)(void *ctx, int t0, int nt, const int32_t *ids_t0, int limit_t, int limit_b, int32_t *symbols);
     int (*decoder_end)(void *ctx, size_t *bytes_consumed);

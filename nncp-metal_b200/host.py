@@ -46,6 +46,10 @@ FN_PROBS = C.CFUNCTYPE(_I, _vp, _I, _I, C.POINTER(C.c_float))
 FN_PATHS = C.CFUNCTYPE(_I, _vp, _I, _I, C.POINTER(C.c_int32), C.POINTER(C.c_uint16), C.POINTER(_I))
 FN_TREES = C.CFUNCTYPE(_I, _vp, _I, _I, C.POINTER(C.c_uint16))
 FN_GRAD = C.CFUNCTYPE(_I, _vp, C.POINTER(C.c_int32), C.POINTER(C.c_float))
+FN_PATHS_BEGIN = C.CFUNCTYPE(_I, _vp, _I, _I, C.POINTER(C.c_int32))
+FN_PATHS_END = C.CFUNCTYPE(_I, _vp, C.POINTER(C.c_uint16), C.POINTER(_I))
+FN_GRAD_QUEUE = C.CFUNCTYPE(_I, _vp, C.POINTER(C.c_int32))
+FN_READ_LOSS = C.CFUNCTYPE(_I, _vp, C.POINTER(C.c_float))
 FN_DEC_BEGIN = C.CFUNCTYPE(_I, _vp, C.POINTER(C.c_uint8), C.c_size_t)
 FN_DEC_STEPS = C.CFUNCTYPE(_I, _vp, _I, _I, C.POINTER(C.c_int32), _I, _I, C.POINTER(C.c_int32))
 FN_DEC_END = C.CFUNCTYPE(_I, _vp, C.POINTER(C.c_size_t))
@@ -55,7 +59,9 @@ class ModelOps(C.Structure):
     _fields_ = [("ctx", _vp), ("n_streams", _I), ("seg_len", _I), ("n_symbols", _I),
                 ("reset", FN_CTX), ("set_lr", FN_SET_LR), ("eval", FN_EVAL), ("read_probs", FN_PROBS),
                 ("coder_paths", FN_PATHS), ("coder_trees", FN_TREES), ("eval_end", FN_CTX),
-                ("eval_gradient", FN_GRAD), ("update", FN_CTX), ("decoder_begin", FN_DEC_BEGIN),
+                ("eval_gradient", FN_GRAD), ("update", FN_CTX), ("coder_paths_begin", FN_PATHS_BEGIN),
+                ("coder_paths_end", FN_PATHS_END), ("eval_gradient_queue", FN_GRAD_QUEUE), ("read_loss", FN_READ_LOSS),
+                ("decoder_begin", FN_DEC_BEGIN),
                 ("decode_steps", FN_DEC_STEPS), ("decoder_end", FN_DEC_END)]
 
 
@@ -145,6 +151,16 @@ def read_header(data):
     return fp, nsym.value, used.value
 
 
+def _model_error():
+    """What the CUDA library last complained about (status 8 of the host code means a model call failed)."""
+    try:
+        L = C.CDLL(LIB)
+        L.nncu_last_error.restype = C.c_char_p
+        return L.nncu_last_error().decode()
+    except OSError:
+        return "libnncu.so not loaded"
+
+
 def compress(ops, fp, symbols, eval_mode=EVAL_SEGMENT, out_mode=OUT_CODER_READY):
     """encode_file on memory: returns (bytes, BlockStats)."""
     L = library()
@@ -153,7 +169,7 @@ def compress(ops, fp, symbols, eval_mode=EVAL_SEGMENT, out_mode=OUT_CODER_READY)
     rc = L.nch_compress(C.byref(ops), C.byref(fp), s.ctypes.data_as(_vp), s.size, eval_mode, out_mode,
                         C.byref(out), C.byref(n), C.byref(st))
     if rc != 0:
-        raise RuntimeError(f"nch_compress: {rc}")
+        raise RuntimeError(f"nch_compress: {rc} ({_model_error()})")
     data = C.string_at(out.value, n.value)
     L.nch_free(out)
     return data, st
@@ -169,7 +185,7 @@ def decompress(ops, data, out_mode=OUT_CODER_READY):
     rc = L.nch_decompress(C.byref(ops), C.byref(fp), buf, len(payload), nsym, out_mode,
                           out.ctypes.data_as(_vp))
     if rc != 0:
-        raise RuntimeError(f"nch_decompress: {rc}")
+        raise RuntimeError(f"nch_decompress: {rc} ({_model_error()})")
     return out
 
 

@@ -23,6 +23,9 @@ typedef struct {
     int (*eval_end)(nncu_model *);
     int (*eval_gradient)(nncu_model *, const int32_t *, float *);
     int (*update)(nncu_model *);
+    int (*paths_begin)(nncu_model *, int, int, const int32_t *);
+    int (*paths_end)(nncu_model *, uint16_t *, int *);
+    int (*read_loss)(nncu_model *, float *);
     int (*decoder_begin)(nncu_model *, const uint8_t *, size_t);
     int (*decode_steps)(nncu_model *, int, int, const int32_t *, int, int, int32_t *);
     int (*decoder_end)(nncu_model *, size_t *);
@@ -41,6 +44,10 @@ static int c_trees(void *c, int t0, int nt, uint16_t *o) { cuda_ctx *x = c; retu
 static int c_eval_end(void *c) { cuda_ctx *x = c; return x->eval_end(x->model); }
 static int c_grad(void *c, const int32_t *e, float *l) { cuda_ctx *x = c; return x->eval_gradient(x->model, e, l); }
 static int c_update(void *c) { cuda_ctx *x = c; return x->update(x->model); }
+static int c_paths_begin(void *c, int t0, int nt, const int32_t *s) { cuda_ctx *x = c; return x->paths_begin(x->model, t0, nt, s); }
+static int c_paths_end(void *c, uint16_t *o, int *nb) { cuda_ctx *x = c; return x->paths_end(x->model, o, nb); }
+static int c_grad_queue(void *c, const int32_t *e) { cuda_ctx *x = c; return x->eval_gradient(x->model, e, NULL); }
+static int c_read_loss(void *c, float *l) { cuda_ctx *x = c; return x->read_loss(x->model, l); }
 static int c_dec_begin(void *c, const uint8_t *p, size_t n) { cuda_ctx *x = c; return x->decoder_begin(x->model, p, n); }
 static int c_dec_steps(void *c, int t0, int nt, const int32_t *ids, int lt, int lb, int32_t *out)
 {
@@ -73,6 +80,9 @@ int nch_bind_cuda(const char *libnncu_path, const nncu_params *p, nch_model_ops 
     x->eval_end = dlsym(x->dl, "nncu_eval_end");
     x->eval_gradient = dlsym(x->dl, "nncu_eval_gradient");
     x->update = dlsym(x->dl, "nncu_update");
+    x->paths_begin = dlsym(x->dl, "nncu_coder_paths_begin");
+    x->paths_end = dlsym(x->dl, "nncu_coder_paths_end");
+    x->read_loss = dlsym(x->dl, "nncu_read_loss");
     x->decoder_begin = dlsym(x->dl, "nncu_decoder_begin");
     x->decode_steps = dlsym(x->dl, "nncu_decode_steps");
     x->decoder_end = dlsym(x->dl, "nncu_decoder_end");
@@ -95,6 +105,12 @@ int nch_bind_cuda(const char *libnncu_path, const nncu_params *p, nch_model_ops 
     ops->eval_end = c_eval_end;
     ops->eval_gradient = c_grad;
     ops->update = c_update;
+    if (x->paths_begin && x->paths_end && x->read_loss) {
+        ops->coder_paths_begin = c_paths_begin;
+        ops->coder_paths_end = c_paths_end;
+        ops->eval_gradient_queue = c_grad_queue;
+        ops->read_loss = c_read_loss;
+    }
     if (x->decoder_begin && x->decode_steps && x->decoder_end) {
         ops->decoder_begin = c_dec_begin;
         ops->decode_steps = c_dec_steps;

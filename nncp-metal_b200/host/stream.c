@@ -158,6 +158,53 @@ int nch_process_block(const nch_model_ops *m, nch_enc *enc, nch_dec *dec, uint16
         goto done;
     }
     int pos = 0;
+    /* Encoder order.  An encoder knows a segment's symbols before it codes them, and the next
+       segment's too, so per full segment it queues: the coder values of this segment, its backward
+       pass and update, and the next segment's forward pass -- and only then waits for the coder values
+       and range-codes them, while the GPU trains.  Same kernels in the same order on the device, so
+       the coded bytes are those of the loop below (process_block, nncp.c:3003-3053, runs eval, coder
+       and gradient strictly in turn). */
+    if (enc && eval_mode == NCH_EVAL_SEGMENT && out_mode == NCH_OUT_CODER_READY && m->coder_paths_begin &&
+        m->coder_paths_end && m->eval_gradient_queue && m->read_loss) {
+        int32_t *next_input = (int32_t *)calloc((size_t)T * B, sizeof(int32_t));
+        if (!next_input) { rc = NCH_ERR_NOMEM; goto done; }
+        int queued = 0;
+        while (pos + T <= stride) {
+            if (!queued) {
+                for (int t = 0; t < T; t++)
+                    for (int b = 0; b < B; b++)
+                        input[t * B + b] = nch_get_symb(block_buf, stride, rem, b, pos + t - 1);
+                if (m->eval(m->ctx, -1, input)) { rc = NCH_ERR_MODEL; break; }
+            }
+            queued = 0;
+            for (int t = 0; t < T; t++)
+                for (int b = 0; b < B; b++)
+                    expected[t * B + b] = nch_get_symb(block_buf, stride, rem, b, pos + t);
+            if (m->coder_paths_begin(m->ctx, 0, T, expected) || m->set_lr(m->ctx, nch_interp(lr, *train_step)) ||
+                m->eval_gradient_queue(m->ctx, expected) || m->update(m->ctx)) { rc = NCH_ERR_MODEL; break; }
+            if (pos + 2 * T <= stride) { /* the next full segment of this block */
+                for (int t = 0; t < T; t++)
+                    for (int b = 0; b < B; b++)
+                        next_input[t * B + b] = nch_get_symb(block_buf, stride, rem, b, pos + T + t - 1);
+                if (m->eval(m->ctx, -1, next_input)) { rc = NCH_ERR_MODEL; break; }
+                queued = 1;
+            }
+            int nbits = 0;
+            if (m->coder_paths_end(m->ctx, io.coded, &nbits)) { rc = NCH_ERR_MODEL; break; }
+            nch_write_sym_paths(enc, io.coded, nbits, expected, (size_t)T * B);
+            float loss = 0.0f;
+            if (m->read_loss(m->ctx, &loss)) { rc = NCH_ERR_MODEL; break; }
+            (*train_step)++;
+            pos += T;
+            if (stats) {
+                stats->train_steps++;
+                stats->n_symbols += (int64_t)T * B;
+                stats->sum_log2 -= (double)loss / 0.6931471805599453;
+            }
+        }
+        free(next_input);
+        if (rc) goto done;
+    }
     /* full segments: code, then train on what was coded */
     while (pos + T <= stride) {
         if (eval_mode == NCH_EVAL_SEGMENT) {
