@@ -169,7 +169,7 @@ def test_header_layout_and_round_trip(pkg):
             pkg.host.read_header(bad)
 
 
-def _oracle_ops(pkg, model, with_decoder=False):
+def _oracle_ops(pkg, model, with_decoder=False, with_encoder_order=False):
     """nch_model_ops backed by the CPU oracle (tests only)."""
     H = pkg.host
     T, B, V = model.T, model.B, model.V
@@ -233,6 +233,58 @@ def _oracle_ops(pkg, model, with_decoder=False):
 
         keep["dec"] = [H.FN_DEC_BEGIN(dbegin), H.FN_DEC_STEPS(dsteps), H.FN_DEC_END(dend)]
         ops.decoder_begin, ops.decode_steps, ops.decoder_end = keep["dec"]
+    if with_encoder_order:
+        # coder-ready paths from the oracle's tables (sym_path = write_sym's prob0 values) and the four
+        # ops of the encoder order; the log records the order in which the block loop calls the model
+        st2 = {}
+        log = keep.setdefault("log", [])
+
+        def paths(ctx, t0, nt, sym, out, nbp):
+            pr = np.ctypeslib.as_array(model.L.orc_probs(model.h), shape=(T * B * V,)).reshape(T * B, V)
+            sy = np.ctypeslib.as_array(sym, shape=(nt * B,))
+            rows = [orc.sym_path(pr[t0 * B + i], int(sy[i])) for i in range(nt * B)]
+            nb = len(rows[0])
+            flat = np.concatenate(rows).astype(np.uint16)
+            C.memmove(out, flat.ctypes.data, flat.nbytes)
+            nbp[0] = nb
+            return 0
+
+        def pbegin(ctx, t0, nt, sym):
+            log.append("paths_begin")
+            sy = np.ctypeslib.as_array(sym, shape=(nt * B,)).copy()
+            pr = np.ctypeslib.as_array(model.L.orc_probs(model.h), shape=(T * B * V,)).reshape(T * B, V)
+            st2["rows"] = [orc.sym_path(pr[t0 * B + i], int(sy[i])) for i in range(nt * B)]   # computed now: the
+            return 0                                                       # next forward pass overwrites the tables
+
+        def pend(ctx, out, nbp):
+            log.append("paths_end")
+            flat = np.concatenate(st2["rows"]).astype(np.uint16)
+            C.memmove(out, flat.ctypes.data, flat.nbytes)
+            nbp[0] = len(st2["rows"][0])
+            return 0
+
+        def gqueue(ctx, exp):
+            log.append("gradient")
+            tg = np.ctypeslib.as_array(exp, shape=(T * B,)).reshape(T, B)
+            st2["loss"] = model.eval_gradient(tg)
+            return 0
+
+        def rloss(ctx, loss):
+            log.append("read_loss")
+            loss[0] = st2["loss"]
+            return 0
+
+        def ev_logged(ctx, oi, inp):
+            log.append("eval")
+            return ev(ctx, oi, inp)
+
+        def trees(ctx, t0, nt, out):
+            return 1   # an encoder never asks for trees
+
+        keep["enc"] = [H.FN_PATHS(paths), H.FN_TREES(trees), H.FN_PATHS_BEGIN(pbegin), H.FN_PATHS_END(pend),
+                       H.FN_GRAD_QUEUE(gqueue), H.FN_READ_LOSS(rloss), H.FN_EVAL(ev_logged)]
+        (ops.coder_paths, ops.coder_trees, ops.coder_paths_begin, ops.coder_paths_end, ops.eval_gradient_queue,
+         ops.read_loss, ops.eval) = keep["enc"]
     ops._keep = keep
     return ops
 
@@ -267,6 +319,28 @@ def test_block_loop_round_trip_with_oracle_model(pkg, n_sym, block_len):
         # the model learns the cycle: fewer bits than the 4 bits/symbol of a uniform coder
         hdr = len(pkg.host.header_bytes(fp, n_sym))
         assert (len(data) - hdr) * 8 < 0.8 * 4 * n_sym
+
+
+def test_encoder_order_block_loop_gives_the_same_bytes(pkg):
+    """A model that offers the encoder order (coder values begun / collected separately, gradient queued,
+    loss read later): the block loop queues the next segment's forward pass before it collects and codes
+    the current one, never across a block boundary or into the tail, and writes the same bytes."""
+    cfg, z = load_golden("post_gelu")
+    p = params_from_cfg(pkg, cfg, n_streams=2, seg_len=4, lr=1e-2)
+    syms = np.array([(3 * i) % 5 for i in range(77)], np.uint16)     # blocks of 32: 4 segments each, then a ragged tail
+    fp = pkg.host.file_params(p, block_len=32)
+    plain, _ = pkg.host.compress(_oracle_ops(pkg, orc.OracleModel(p)), fp, syms, pkg.host.EVAL_SEGMENT, pkg.host.OUT_FLOAT)
+    ops = _oracle_ops(pkg, orc.OracleModel(p), with_encoder_order=True)
+    fast, st = pkg.host.compress(ops, fp, syms, pkg.host.EVAL_SEGMENT, pkg.host.OUT_CODER_READY)
+    assert fast == plain and st.n_symbols == 77 and st.train_steps == 9
+    log = ops._keep["log"]
+    per_block = ["eval", "paths_begin", "gradient", "eval", "paths_end", "read_loss"] + \
+                ["paths_begin", "gradient", "eval", "paths_end", "read_loss"] * 2 + \
+                ["paths_begin", "gradient", "paths_end", "read_loss"]
+    assert log[:len(per_block)] == per_block           # block 1: the last segment queues nothing
+    assert log[len(per_block):2 * len(per_block)] == per_block
+    back = pkg.host.decompress(_oracle_ops(pkg, orc.OracleModel(p)), fast, pkg.host.OUT_FLOAT)
+    assert np.array_equal(back, syms)
 
 
 def test_step_mode_encoder_gives_the_same_bytes(pkg):
