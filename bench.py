@@ -274,6 +274,9 @@ def run_decode(args, c, name):
     n = n_seg * T * B
     toks = (synth_tokens(n, V, 4321) if V > 256 else np.random.default_rng(1).integers(0, V, n)).astype(np.uint16)
     fp = host.file_params(p, block_len=n)
+    ops = host.bind_cuda(p)      # first use of every kernel in this process: not part of the encode figure
+    host.compress(ops, host.file_params(p, block_len=2 * T * B), toks[: 2 * T * B], host.EVAL_SEGMENT, host.OUT_CODER_READY)
+    host.unbind_cuda(ops)
     ops = host.bind_cuda(p)
     t0 = time.perf_counter()
     data, st = host.compress(ops, fp, toks, host.EVAL_SEGMENT, host.OUT_CODER_READY)
@@ -346,7 +349,7 @@ def run_decode(args, c, name):
     back = host.decompress(ops, data, host.OUT_DEVICE)
     t_file = time.perf_counter() - t0
     host.unbind_cuda(ops)
-    exact = exact and bool(np.array_equal(back, toks))
+    exact_file = bool(np.array_equal(back, toks))
     # and the walk on the host over trees copied back each step (what the device decoder replaces), 2 segments
     small = toks[: 2 * T * B]
     fp2 = host.file_params(p, block_len=small.size)
@@ -358,7 +361,9 @@ def run_decode(args, c, name):
     back2 = host.decompress(ops, d2, host.OUT_CODER_READY)
     t_walk = time.perf_counter() - t0
     host.unbind_cuda(ops)
-    exact = exact and bool(np.array_equal(back2, small))
+    exact_walk = bool(np.array_equal(back2, small))
+    exact_parts = {"step_graphs": exact, "nch_decompress": exact_file, "host_walk": exact_walk}
+    exact = exact and exact_file and exact_walk
 
     line = {"mode": "decode", "metric": "decoded symbols/s (one-symbol steps + train step per segment)",
             "value": value, "unit": "symbols/s", "n_gpus": 1, "steps": K, "warmup": W, "ms_per_step": ms / K,
@@ -368,7 +373,7 @@ def run_decode(args, c, name):
                        "tokens": "seeded Zipf(1.1)+order-1 Markov ids, encoded by this library's encoder first",
                        "l2": "the bf16 weights read by every step exceed the 126 MB L2" if 2 * nfl > 126e6 else
                              "the bf16 weights fit the 126 MB L2: DRAM traffic is below the algorithmic bytes"},
-            "round_trip_exact": exact, "payload_bytes": len(payload), "payload_bytes_consumed": int(consumed),
+            "round_trip_exact": exact, "round_trip_exact_parts": exact_parts, "payload_bytes": len(payload), "payload_bytes_consumed": int(consumed),
             "bits_per_symbol": 8.0 * len(payload) / n, "gpu_launches": int(prof.launches), "clocks": clocks,
             "ms_per_symbol_step": step_ms,
             "e2e": {"value": n / t_file, "unit": "symbols/s", "h2d_bytes_per_step": B * 4 + T * B * 4,

@@ -904,7 +904,7 @@ embed_grad_kernel(const int32_t *__restrict__ ids, const T *__restrict__ dx, flo
     pdl_wait();
     constexpr int SPAN = 2048; // rows listed per pass
     __shared__ int list[SPAN];
-    __shared__ int wcnt[4], total;
+    __shared__ int wcnt[2][4]; // per-warp hit counts of a chunk, double-buffered by chunk parity
     const int r0 = blockIdx.x;
     int v = ids[r0];
     v = v < 0 ? 0 : (v >= V ? V - 1 : v);
@@ -914,10 +914,11 @@ embed_grad_kernel(const int32_t *__restrict__ ids, const T *__restrict__ dx, flo
     for (int c0 = 0; c0 < D; c0 += 512) { // four columns per thread and pass
         float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
         for (int span0 = r0; span0 < rows; span0 += SPAN) {
-            // ordered list of the rows of this span that carry the symbol (compaction by warp ballots)
+            // ordered list of the rows of this span that carry the symbol (compaction by warp ballots).
+            // Every thread keeps the running total in a register: the counts of a chunk are read by all
+            // threads after one barrier, and the buffer they sit in is not written again before the
+            // barrier of the next chunk has been passed by everyone.
             __syncthreads(); // the list of the span before has been read
-            if (threadIdx.x == 0)
-                total = 0;
             const int span1 = min(rows, span0 + SPAN);
             int idr[SPAN / 128]; // all of the span's ids are requested before the first is looked at
 #pragma unroll
@@ -925,6 +926,7 @@ embed_grad_kernel(const int32_t *__restrict__ ids, const T *__restrict__ dx, flo
                 const int r = span0 + 128 * j + threadIdx.x;
                 idr[j] = r < span1 ? ids[r] : -1;
             }
+            int n = 0;
 #pragma unroll
             for (int j = 0; j < SPAN / 128; j++) {
                 const int base = span0 + 128 * j;
@@ -937,20 +939,15 @@ embed_grad_kernel(const int32_t *__restrict__ ids, const T *__restrict__ dx, flo
                 const bool hit = id == v;
                 const unsigned bal = __ballot_sync(0xffffffffu, hit);
                 if (lane == 0)
-                    wcnt[warp] = __popc(bal);
+                    wcnt[j & 1][warp] = __popc(bal);
                 __syncthreads();
-                int pos = total;
-#pragma unroll
-                for (int w = 0; w < 4; w++)
-                    pos += w < warp ? wcnt[w] : 0;
+                const int w0 = wcnt[j & 1][0], w1 = wcnt[j & 1][1], w2 = wcnt[j & 1][2], w3 = wcnt[j & 1][3];
+                const int pos = n + (warp > 0 ? w0 : 0) + (warp > 1 ? w1 : 0) + (warp > 2 ? w2 : 0);
                 if (hit)
                     list[pos + __popc(bal & ((1u << lane) - 1u))] = r;
-                __syncthreads();
-                if (threadIdx.x == 0)
-                    total += wcnt[0] + wcnt[1] + wcnt[2] + wcnt[3];
+                n += w0 + w1 + w2 + w3;
             }
-            __syncthreads();
-            const int n = total;
+            __syncthreads(); // the list is complete
             // sixteen rows' loads go out before the first is added: the sum of a frequent symbol is a
             // chain of additions in row order, but its loads need not wait for one another
             for (int k0 = 0; k0 < n; k0 += 16) {
