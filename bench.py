@@ -7,7 +7,7 @@ A step is one segment of every stream: forward over [memory | segment], loss, ba
 RMSProp update, memory shift (fwd+bwd+RMSProp, the metric of BASELINE.json).  The workload is
 BASELINE config[2] (vocab 16384, 12 layers, d_model 512, 8 heads x 64, d_ff 2048, seg 64,
 mem 64, 32 streams, bf16 with fp32 master weights) on seeded synthetic Zipf+Markov token ids;
-streams are sharded across ranks and gradients are summed with one NCCL all-reduce per step.
+streams are sharded across ranks and gradients are summed by NCCL all-reduces inside the backward pass.
 
 `value`   device-resident ids/targets, nothing read back (CUDA events, max over ranks).
 `e2e`     the same steps through the host-buffer plugin calls: ids from pinned host memory
