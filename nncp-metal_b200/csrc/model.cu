@@ -2021,6 +2021,12 @@ int nncu_decoder_begin(nncu_model *m, const uint8_t *payload_host, size_t len)
     CUDA_TRY(cudaStreamSynchronize(m->st));
     const size_t need = len + 16;
     if (need > m->dec_cap) {
+        // the captured step graphs hold the old buffer's address: they are dropped and captured again
+        for (auto &g : m->step_graphs) {
+            if (g.exec)
+                cudaGraphExecDestroy(g.exec);
+            g = nncu_model::StepGraph{nullptr, 0, 0};
+        }
         if (m->dec_payload)
             cudaFree(m->dec_payload);
         m->dec_payload = nullptr;
