@@ -105,6 +105,40 @@ def test_device_decoder_steps_match_the_host_walk(pkg):
     ref.close()
 
 
+def test_device_decoder_graphs_survive_a_larger_second_payload(pkg):
+    """On a non-default stream every decode step replays a CUDA graph that holds the payload buffer's
+    address; a second, larger payload moves the buffer, so the graphs must be captured again.  Two
+    files of different sizes decoded by one model, each compared with a model that decodes it eagerly."""
+    import torch
+    kw = dict(n_layer=1, d_model=64, n_head=2, d_key=32, d_inner=128, d_pos=24, mem_len=16, seg_len=8,
+              n_streams=4, n_symbols=256, use_bf16=0, lr=2e-3, init_range=0.05)
+    p = pkg.abi.make_params(**kw)
+    T, B = 8, 4
+    rng = np.random.default_rng(21)
+    m = pkg.TrfModel(p)
+    st = torch.cuda.Stream()
+    m.set_stream(st.cuda_stream)
+    for n_bytes in (300, 5000):
+        payload = rng.integers(0, 256, n_bytes, dtype=np.uint8).tobytes()
+        ref = pkg.TrfModel(p)
+        outs = []
+        for mod in (m, ref):
+            mod.reset()
+            mod.decoder_begin(payload)
+            ids0, segs = np.zeros(B, np.int32), []
+            for _seg in range(4):                      # graphs are captured on the second use of a memory twin
+                sy = mod.decode_steps(0, T, ids0)
+                mod.set_lr(2e-3)
+                mod.eval_gradient(sy)
+                mod.update()
+                ids0 = sy[-1]
+                segs.append(sy)
+            outs.append((np.stack(segs), mod.decoder_end()))
+        ref.close()
+        assert np.array_equal(outs[0][0], outs[1][0]) and outs[0][1] == outs[1][1]
+    m.close()
+
+
 def test_coder_ready_and_float_output_give_the_same_file(pkg):
     kw, n, block_len = CASES["fp32_bytes"]
     p = pkg.abi.make_params(**kw)
