@@ -115,12 +115,11 @@ def test_device_decoder_graphs_survive_a_larger_second_payload(pkg):
     p = pkg.abi.make_params(**kw)
     T, B = 8, 4
     rng = np.random.default_rng(21)
-    m = pkg.TrfModel(p)
+    m, ref = pkg.TrfModel(p), pkg.TrfModel(p)      # both see both payloads, so their weights stay equal
     st = torch.cuda.Stream()
     m.set_stream(st.cuda_stream)
     for n_bytes in (300, 5000):
         payload = rng.integers(0, 256, n_bytes, dtype=np.uint8).tobytes()
-        ref = pkg.TrfModel(p)
         outs = []
         for mod in (m, ref):
             mod.reset()
@@ -134,9 +133,10 @@ def test_device_decoder_graphs_survive_a_larger_second_payload(pkg):
                 ids0 = sy[-1]
                 segs.append(sy)
             outs.append((np.stack(segs), mod.decoder_end()))
-        ref.close()
         assert np.array_equal(outs[0][0], outs[1][0]) and outs[0][1] == outs[1][1]
+    assert m.weights_hash() == ref.weights_hash()
     m.close()
+    ref.close()
 
 
 def test_coder_ready_and_float_output_give_the_same_file(pkg):
