@@ -64,7 +64,7 @@ extern "C" {
 #define NNCU_LN_POST (1 << 0)
 #define NNCU_LN_PRE (1 << 1)
 #define NNCU_LN_FINAL (1 << 2)
-#define NNCU_LN_COEF (1 << 3) /* not supported: nncu_create returns INVALID */
+#define NNCU_LN_COEF (1 << 3) /* per-layer scalar alpha (starts at 0) on both sub-layer outputs before the residual */
 #define NNCU_LN_RMSNORM (1 << 4)
 
 /* ff_act, same values as FFActivationEnum nncp.c:82-87 */

@@ -437,6 +437,47 @@ __global__ void add_kernel(const T *__restrict__ a, const T *__restrict__ b, T *
 }
 
 // ------------------------------------------------------------------
+// LN_COEF (nncp.c:892-894, 975-977): a sub-layer's output is multiplied by the layer's learned
+// scalar alpha before the residual sum.  Forward: dst = alpha * src.  Backward, one block per row:
+// dt = alpha * ds for the branch, and part[r] = sum_c ds[r][c] * a[r][c] (the row's share of
+// d alpha, columns added in a fixed order); the rows are summed later by one ordered job.
+template <typename T>
+__global__ void scale_rows_kernel(const T *__restrict__ src, const float *__restrict__ alpha, T *__restrict__ dst, size_t n)
+{
+    pdl_trigger();
+    pdl_wait();
+    const float al = alpha[0];
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
+        dst[i] = from_f<T>(al * to_f(src[i]));
+}
+
+template <typename T>
+__global__ void __launch_bounds__(128)
+scale_dot_kernel(const T *__restrict__ ds, const T *__restrict__ a, const float *__restrict__ alpha, T *__restrict__ dt,
+                 float *__restrict__ part, int rows, int D)
+{
+    pdl_trigger();
+    pdl_wait();
+    __shared__ float red[4];
+    const int r = blockIdx.x;
+    if (r >= rows)
+        return;
+    const float al = alpha[0];
+    float s = 0.0f;
+    for (int c = threadIdx.x; c < D; c += 128) {
+        const float d = to_f(ds[(size_t)r * D + c]);
+        s += d * to_f(a[(size_t)r * D + c]);
+        dt[(size_t)r * D + c] = from_f<T>(al * d);
+    }
+    s = warp_sum(s);
+    if ((threadIdx.x & 31) == 0)
+        red[threadIdx.x >> 5] = s;
+    __syncthreads();
+    if (threadIdx.x == 0)
+        part[r] = (red[0] + red[1]) + (red[2] + red[3]);
+}
+
+// ------------------------------------------------------------------
 // feed-forward activation (nncp.c:938-966).  hpre [rows][F1], hact [rows][F].
 __device__ __forceinline__ float gelu_f(float x)
 {

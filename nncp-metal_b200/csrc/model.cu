@@ -103,11 +103,13 @@ struct ParamInfo {
 
 struct LayerOff {
     size_t w_q, w_kv, b_q, w_o, ff1, ff_bias1, ff2, ff_bias2, w_r, b_r, ln_g1, ln_b1, ln_g2, ln_b2;
+    size_t alpha; // LN_COEF: the scalar both sub-layer outputs are multiplied by (NONE without the flag)
     size_t small; // the layer's slots are [w_q, small): the four matrices, then [small, next layer): everything else
 };
 
 struct LayerAct {
     void *xin, *qkv, *o, *s1, *y, *u, *hpre, *hact, *s2; // qkv: [L*B][q | k | v], q unused in memory rows
+    void *ao = nullptr, *aff = nullptr;                  // LN_COEF: the sub-layer outputs before the multiplication
     float *lse, *st_pre1, *st_1, *st_pre2, *st_2;
 };
 
@@ -177,6 +179,8 @@ struct nncu_model {
     bool fuse_update = false; // this backward pass applies the optimizer to each bucket as it completes
     float *hyper_dev = nullptr; // {lr, bias correction} of the fused optimizer step
     int32_t *ids_dev, *tgt_dev;
+    void *dt_ff = nullptr, *dt_at = nullptr; // LN_COEF: alpha * d(residual sum) of the two sub-layers, [TB][D]
+    float *alpha_part = nullptr;             // LN_COEF: per-row shares of d alpha, [2][TB]
     int32_t *sym_dev;   // [TB] symbols whose coder paths are wanted (nncu_coder_paths*)
     int32_t *tgt_fixed; // the targets whose entries of dz carry the (p - 1) correction
     int *dz_fixed;      // device flag: dz has been corrected since the last forward pass
@@ -585,7 +589,15 @@ static int forward_range(nncu_model *m, int t0, int t1)
                                       wf(m, o.w_r), m->W + o.b_r, a.o, a.lse, m->st, &pt,
                                       (m->bf && o.w_r != NONE) ? m->Wb + o.w_r : nullptr, m->err_flag));
         // output projection, residual, post-LN (nncp.c:865-920)
-        NNCU_TRY((mm_nt<AT, AT>(m, nr, D, HD, at<AT>(a.o, (size_t)r0 * HD), HD, o.w_o, tmp, D, nullptr)));
+        if (o.alpha != NONE) { // LN_COEF: the projection is kept as it is for the backward pass, tmp = alpha * it
+            AT *ao = at<AT>(a.ao, (size_t)r0 * D);
+            NNCU_TRY((mm_nt<AT, AT>(m, nr, D, HD, at<AT>(a.o, (size_t)r0 * HD), HD, o.w_o, ao, D, nullptr)));
+            launch_k(scale_rows_kernel<AT>, dim3(ceil_div((long long)nr * D, 256)), dim3(256), 0, m->st, (const AT *)ao,
+                     (const float *)(m->W + o.alpha), tmp, (size_t)nr * D);
+            KERNEL_CHECK();
+        } else {
+            NNCU_TRY((mm_nt<AT, AT>(m, nr, D, HD, at<AT>(a.o, (size_t)r0 * HD), HD, o.w_o, tmp, D, nullptr)));
+        }
         AT *yy = at<AT>(a.y, (size_t)r0 * D);
         NNCU_TRY(norm_fwd<AT>(m, tmp, xin, post ? at<AT>(a.s1, (size_t)r0 * D) : nullptr, yy, o.ln_g1,
                               o.ln_b1, a.st_1 + 2 * r0, nr, post));
@@ -603,7 +615,15 @@ static int forward_range(nncu_model *m, int t0, int t1)
         else
             act_fwd_kernel<AT><<<ceil_div((long long)nr * F, 256), 256, 0, m->st>>>(hpre, hact, nr, F, F1, p.ff_act);
         KERNEL_CHECK();
-        NNCU_TRY((mm_nt<AT, AT>(m, nr, D, F, hact, F, o.ff2, tmp, D, wf(m, o.ff_bias2))));
+        if (o.alpha != NONE) {
+            AT *aff = at<AT>(a.aff, (size_t)r0 * D);
+            NNCU_TRY((mm_nt<AT, AT>(m, nr, D, F, hact, F, o.ff2, aff, D, wf(m, o.ff_bias2))));
+            launch_k(scale_rows_kernel<AT>, dim3(ceil_div((long long)nr * D, 256)), dim3(256), 0, m->st, (const AT *)aff,
+                     (const float *)(m->W + o.alpha), tmp, (size_t)nr * D);
+            KERNEL_CHECK();
+        } else {
+            NNCU_TRY((mm_nt<AT, AT>(m, nr, D, F, hact, F, o.ff2, tmp, D, wf(m, o.ff_bias2))));
+        }
         AT *xout = (l + 1 < m->nl) ? at<AT>(m->act[l + 1].xin, (size_t)r0 * D)
                                    : at<AT>(m->xlast, (size_t)r0 * D);
         NNCU_TRY(norm_fwd<AT>(m, tmp, yy, post ? at<AT>(a.s2, (size_t)r0 * D) : nullptr, xout, o.ln_g2,
@@ -808,16 +828,28 @@ static int backward(nncu_model *m)
         const AT *hc = reinterpret_cast<const AT *>(hcat_layer(m, m->cur, l));
         // ---- feed-forward block
         AT *ds2 = dx;
+        const bool coef = o.alpha != NONE;
         if (post) {
             ds2 = pick<AT>(m, {dx});
             // the column sums of ds2 are the ff_bias2 gradient: taken in the same pass
             NNCU_TRY(norm_bwd<AT>(m, dx, atc<AT>(a.s2, 0), o.ln_g2, o.ln_b2, a.st_2, nullptr, ds2, TB,
-                                  o.ff_bias2 != NONE ? gf(m, o.ff_bias2) : nullptr));
-        } else if (o.ff_bias2 != NONE) {
+                                  (o.ff_bias2 != NONE && !coef) ? gf(m, o.ff_bias2) : nullptr));
+        } else if (o.ff_bias2 != NONE && !coef) {
             NNCU_TRY(colsum<AT>(m, ds2, D, TB, D, gf(m, o.ff_bias2)));
         }
-        NNCU_TRY(mm_tn(m, D, F, TB, ds2, D, atc<AT>(a.hact, 0), F, gf(m, o.ff2)));
-        NNCU_TRY(mm_nn(m, TB, F, D, ds2, D, o.ff2, dh, F, (const AT *)nullptr));
+        // LN_COEF: the branch sees alpha * ds2 (its own buffer: the weight-gradient GEMMs read it until the
+        // layer's join), the residual keeps ds2; the rows' shares of d alpha wait for the layer's reduction launch
+        AT *dt2 = ds2;
+        if (coef) {
+            dt2 = reinterpret_cast<AT *>(m->dt_ff);
+            launch_k(scale_dot_kernel<AT>, dim3(TB), dim3(128), 0, m->st, (const AT *)ds2, atc<AT>(a.aff, 0),
+                     (const float *)(m->W + o.alpha), dt2, m->alpha_part, TB, D);
+            KERNEL_CHECK();
+            if (o.ff_bias2 != NONE)
+                NNCU_TRY(colsum<AT>(m, dt2, D, TB, D, gf(m, o.ff_bias2)));
+        }
+        NNCU_TRY(mm_tn(m, D, F, TB, dt2, D, atc<AT>(a.hact, 0), F, gf(m, o.ff2)));
+        NNCU_TRY(mm_nn(m, TB, F, D, dt2, D, o.ff2, dh, F, (const AT *)nullptr));
         float *apart = o.ff_bias1 != NONE ? part_slot(m) : nullptr;
         const bool act_vec = sizeof(AT) == 2 && F % 2 == 0;
         const int act_rows = act_vec ? ACT_BWD_ROWS : 32;
@@ -846,8 +878,17 @@ static int backward(nncu_model *m)
             ds1 = pick<AT>(m, {dy, ds2});
             NNCU_TRY(norm_bwd<AT>(m, dy, atc<AT>(a.s1, 0), o.ln_g1, o.ln_b1, a.st_1, nullptr, ds1, TB));
         }
-        NNCU_TRY(mm_tn(m, D, HD, TB, ds1, D, atc<AT>(a.o, 0), HD, gf(m, o.w_o)));
-        NNCU_TRY(mm_nn(m, TB, HD, D, ds1, D, o.w_o, dof, HD, (const AT *)nullptr));
+        AT *dt1 = ds1;
+        if (coef) {
+            dt1 = reinterpret_cast<AT *>(m->dt_at);
+            launch_k(scale_dot_kernel<AT>, dim3(TB), dim3(128), 0, m->st, (const AT *)ds1, atc<AT>(a.ao, 0),
+                     (const float *)(m->W + o.alpha), dt1, m->alpha_part + TB, TB, D);
+            KERNEL_CHECK();
+            // d alpha = sum over the rows of both sub-layers, one ordered job
+            NNCU_TRY(queue_reduction(m, 1, m->alpha_part, 2 * TB, 1, 1, 0, gf(m, o.alpha), 0));
+        }
+        NNCU_TRY(mm_tn(m, D, HD, TB, dt1, D, atc<AT>(a.o, 0), HD, gf(m, o.w_o)));
+        NNCU_TRY(mm_nn(m, TB, HD, D, dt1, D, o.w_o, dof, HD, (const AT *)nullptr));
         nncu_attn_shape s = attn_shape(m, l, 0, m->T);
         NNCU_TRY(attn_backward_any<AT>(&s, at<AT>(a.qkv, (size_t)M * B * 3 * HD), at<AT>(a.qkv, HD), wf(m, o.w_r),
                                        m->W + o.b_r, a.o, a.lse, dof, dq, dkv, m->dwr_part, m->dbr_part, m->st,
@@ -1055,8 +1096,6 @@ static int validate(const nncu_params *p)
         return nncu_fail(NNCU_ERR_INVALID, "d_value must equal d_key");
     if (p->d_pos < 1 || p->d_pos > p->mem_len + p->seg_len)
         return nncu_fail(NNCU_ERR_INVALID, "d_pos must be in [1, mem_len + seg_len]");
-    if (p->ln_flags & NNCU_LN_COEF)
-        return nncu_fail(NNCU_ERR_INVALID, "LN_COEF is not supported");
     if ((p->ln_flags & NNCU_LN_PRE) && (p->ln_flags & NNCU_LN_POST))
         return nncu_fail(NNCU_ERR_INVALID, "LN_PRE and LN_POST together are not supported");
     if (p->ff_act > NNCU_FF_GATED_SILU)
@@ -1223,6 +1262,7 @@ int nncu_create(const nncu_params *p, nncu_model **out)
         } else {
             o.ln_g1 = o.ln_b1 = o.ln_g2 = o.ln_b2 = NONE;
         }
+        o.alpha = (p->ln_flags & NNCU_LN_COEF) ? add_param(m, "alpha", l, 1) : NONE; // starts at 0 (nncp.c:437)
     }
     if (p->ln_flags & NNCU_LN_FINAL) {
         m->ln_g = add_param(m, "ln_g", 2 * m->nl, D);
@@ -1247,7 +1287,8 @@ int nncu_create(const nncu_params *p, nncu_model **out)
     size_t oW = take(m->n_floats * 4), oG = take(m->n_floats * 4), oV = take(m->n_floats * 4);
     size_t oWb = m->bf ? take(m->n_floats * 2) : 0, oWbT = m->bf ? take(m->n_floats * 2) : 0;
     size_t oH0 = take((size_t)m->nl * LB * D * e), oH1 = take((size_t)m->nl * LB * D * e);
-    struct LOff { size_t xin, qkv, o, s1, y, u, hpre, hact, s2, lse, sp1, s_1, sp2, s_2; };
+    struct LOff { size_t xin, qkv, o, s1, y, u, hpre, hact, s2, lse, sp1, s_1, sp2, s_2, ao, aff; };
+    const bool coef = (p->ln_flags & NNCU_LN_COEF) != 0;
     std::vector<LOff> lofs(m->nl);
     for (int l = 0; l < m->nl; l++) {
         LOff &x = lofs[l];
@@ -1265,7 +1306,11 @@ int nncu_create(const nncu_params *p, nncu_model **out)
         x.s_1 = take((size_t)TB * 2 * 4);
         x.sp2 = take((size_t)TB * 2 * 4);
         x.s_2 = take((size_t)TB * 2 * 4);
+        x.ao = coef ? take((size_t)TB * D * e) : NONE;
+        x.aff = coef ? take((size_t)TB * D * e) : NONE;
     }
+    size_t oDtFf = coef ? take((size_t)TB * D * e) : 0, oDtAt = coef ? take((size_t)TB * D * e) : 0;
+    size_t oAlphaPart = coef ? take((size_t)2 * TB * 4) : 0;
     size_t oXlast = take((size_t)TB * D * e), oXf = take((size_t)TB * D * e), oStf = take((size_t)TB * 8);
     size_t oProbs = take((size_t)TB * V * 4);
     size_t oPool[4];
@@ -1348,6 +1393,11 @@ int nncu_create(const nncu_params *p, nncu_model **out)
         a.lse = (float *)(A + x.lse); a.st_pre1 = (float *)(A + x.sp1); a.st_1 = (float *)(A + x.s_1);
         a.st_pre2 = (float *)(A + x.sp2); a.st_2 = (float *)(A + x.s_2);
         a.xin = pre ? A + x.xin : nullptr; // without pre-LN the residual input IS the hcat segment part
+        a.ao = coef ? A + x.ao : nullptr; a.aff = coef ? A + x.aff : nullptr;
+    }
+    if (coef) {
+        m->dt_ff = A + oDtFf; m->dt_at = A + oDtAt;
+        m->alpha_part = (float *)(A + oAlphaPart);
     }
     if (cudaStreamCreateWithFlags(&m->st2, cudaStreamNonBlocking) == cudaSuccess &&
         cudaEventCreateWithFlags(&m->ev_fork, cudaEventDisableTiming) == cudaSuccess &&

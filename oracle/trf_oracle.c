@@ -52,8 +52,10 @@ typedef struct {
     /* offsets into the flat buffers; (size_t)-1 when absent */
     size_t w_q, w_kv, b_q, w_o, ff1, ff_bias1, ff2, ff_bias2, w_r, b_r;
     size_t ln_g1, ln_b1, ln_g2, ln_b2;
+    size_t alpha; /* LN_COEF: the scalar both sub-layer outputs are multiplied by before the residual (nncp.c:435-437, 892-894, 975-977) */
     /* activations */
     float *xin, *hcat, *q, *kv, *P, *o, *s1, *y, *u, *hpre, *hact, *s2;
+    float *a1, *a2; /* LN_COEF: the sub-layer outputs before the multiplication */
     float *st_pre1, *st_1, *st_pre2, *st_2; /* [rows][2] mean, rstd */
 } orc_layer;
 
@@ -445,7 +447,7 @@ int orc_validate(const nncu_params *p)
         return NNCU_ERR_INVALID;
     if (p->d_pos < 1 || p->d_pos > p->mem_len + p->seg_len)
         return NNCU_ERR_INVALID;
-    if ((p->ln_flags & NNCU_LN_COEF) || ((p->ln_flags & NNCU_LN_PRE) && (p->ln_flags & NNCU_LN_POST)))
+    if ((p->ln_flags & NNCU_LN_PRE) && (p->ln_flags & NNCU_LN_POST))
         return NNCU_ERR_INVALID;
     if (p->ff_act > NNCU_FF_GATED_SILU)
         return NNCU_ERR_INVALID;
@@ -495,6 +497,7 @@ int orc_create(const nncu_params *p, orc_model **out)
         } else {
             y->ln_g1 = y->ln_b1 = y->ln_g2 = y->ln_b2 = NONE;
         }
+        y->alpha = (p->ln_flags & NNCU_LN_COEF) ? add_param(m, "alpha", l, 1) : NONE; /* starts at 0, nncp.c:437 */
     }
     if (p->ln_flags & NNCU_LN_FINAL) {
         m->ln_g = add_param(m, "ln_g", 2 * p->n_layer, D);
@@ -542,6 +545,8 @@ int orc_create(const nncu_params *p, orc_model **out)
         y->hpre = falloc((size_t)m->TB * m->F1);
         y->hact = falloc((size_t)m->TB * F);
         y->s2 = falloc((size_t)m->TB * D);
+        y->a1 = falloc((size_t)m->TB * D);
+        y->a2 = falloc((size_t)m->TB * D);
         y->st_pre1 = falloc((size_t)m->TB * 2);
         y->st_1 = falloc((size_t)m->TB * 2);
         y->st_pre2 = falloc((size_t)m->TB * 2);
@@ -563,7 +568,7 @@ void orc_destroy(orc_model *m)
     for (int l = 0; l < m->p.n_layer; l++) {
         orc_layer *y = &m->layers[l];
         float *bufs[] = {y->xin, y->hcat, y->q, y->kv, y->P, y->o, y->s1, y->y, y->u,
-                         y->hpre, y->hact, y->s2, y->st_pre1, y->st_1, y->st_pre2, y->st_2};
+                         y->hpre, y->hact, y->s2, y->st_pre1, y->st_1, y->st_pre2, y->st_2, y->a1, y->a2};
         for (size_t i = 0; i < sizeof(bufs) / sizeof(bufs[0]); i++)
             free(bufs[i]);
     }
@@ -672,6 +677,14 @@ static void forward_range(orc_model *m, const int32_t *input, int t0, int t1)
         /* w_o + residual (+ post-LN), nncp.c:865-920 */
         float *s1 = y->s1 + (size_t)r0 * D, *yy = y->y + (size_t)r0 * D;
         gemm_nt(nr, D, HD, y->o + (size_t)r0 * HD, HD, W(y->w_o), HD, s1, D, NULL, 0);
+        if (y->alpha != NONE) { /* LN_COEF, nncp.c:892-894 */
+            float *a1 = y->a1 + (size_t)r0 * D;
+            const float al = W(y->alpha)[0];
+            for (size_t i = 0; i < (size_t)nr * D; i++) {
+                a1[i] = s1[i];
+                s1[i] = al * a1[i];
+            }
+        }
         for (size_t i = 0; i < (size_t)nr * D; i++)
             s1[i] += xin[i];
         if (p->ln_flags & NNCU_LN_POST)
@@ -702,6 +715,14 @@ static void forward_range(orc_model *m, const int32_t *input, int t0, int t1)
         }
         float *s2 = y->s2 + (size_t)r0 * D;
         gemm_nt(nr, D, F, hact, F, W(y->ff2), F, s2, D, WN(y->ff_bias2), 0);
+        if (y->alpha != NONE) { /* LN_COEF, nncp.c:975-977 */
+            float *a2 = y->a2 + (size_t)r0 * D;
+            const float al = W(y->alpha)[0];
+            for (size_t i = 0; i < (size_t)nr * D; i++) {
+                a2[i] = s2[i];
+                s2[i] = al * a2[i];
+            }
+        }
         for (size_t i = 0; i < (size_t)nr * D; i++)
             s2[i] += yy[i];
         float *xout = (l + 1 < p->n_layer) ? m->layers[l + 1].xin + (size_t)r0 * D
@@ -773,6 +794,7 @@ int orc_eval_gradient(orc_model *m, const int32_t *targets, float *loss_out)
 
     float *dz = falloc((size_t)TB * V);
     float *dx = falloc((size_t)TB * D), *dt = falloc((size_t)TB * D), *dy = falloc((size_t)TB * D);
+    float *dal = falloc((size_t)TB * D); /* LN_COEF: alpha * d(sum) */
     float *dh = falloc((size_t)TB * F), *dhp = falloc((size_t)TB * F1);
     float *dof = falloc((size_t)TB * HD), *dq = falloc((size_t)TB * HD);
     float *dkv = falloc((size_t)LB * 2 * HD);
@@ -802,10 +824,22 @@ int orc_eval_gradient(orc_model *m, const int32_t *targets, float *loss_out)
             norm_bwd(TB, D, dx, y->s2, W(y->ln_g2), rms, y->st_2, dt, 0, G(y->ln_g2), G(y->ln_b2));
         else
             memcpy(dt, dx, sizeof(float) * (size_t)TB * D);
+        /* LN_COEF: the branch sees alpha * ds2, alpha collects sum(ds2 . branch output); the residual keeps ds2 */
+        const float *da = dt;
+        if (y->alpha != NONE) {
+            const float al = W(y->alpha)[0];
+            double acc = 0.0;
+            for (size_t i = 0; i < (size_t)TB * D; i++) {
+                acc += (double)dt[i] * (double)y->a2[i];
+                dal[i] = al * dt[i];
+            }
+            G(y->alpha)[0] += (float)acc;
+            da = dal;
+        }
         if (y->ff_bias2 != NONE)
-            colsum(TB, D, dt, D, G(y->ff_bias2), 0);
-        gemm_tn(D, F, TB, dt, D, y->hact, F, G(y->ff2), F, 0);
-        gemm_nn(TB, F, D, dt, D, W(y->ff2), F, dh, F, 0);
+            colsum(TB, D, da, D, G(y->ff_bias2), 0);
+        gemm_tn(D, F, TB, da, D, y->hact, F, G(y->ff2), F, 0);
+        gemm_nn(TB, F, D, da, D, W(y->ff2), F, dh, F, 0);
         for (int r = 0; r < TB; r++) {
             for (int i = 0; i < F; i++) {
                 float a = y->hpre[(size_t)r * F1 + i], d = dh[(size_t)r * F + i];
@@ -838,8 +872,19 @@ int orc_eval_gradient(orc_model *m, const int32_t *targets, float *loss_out)
             norm_bwd(TB, D, dy, y->s1, W(y->ln_g1), rms, y->st_1, dt, 0, G(y->ln_g1), G(y->ln_b1));
         else
             memcpy(dt, dy, sizeof(float) * (size_t)TB * D);
-        gemm_tn(D, HD, TB, dt, D, y->o, HD, G(y->w_o), HD, 0);
-        gemm_nn(TB, HD, D, dt, D, W(y->w_o), HD, dof, HD, 0);
+        da = dt;
+        if (y->alpha != NONE) {
+            const float al = W(y->alpha)[0];
+            double acc = 0.0;
+            for (size_t i = 0; i < (size_t)TB * D; i++) {
+                acc += (double)dt[i] * (double)y->a1[i];
+                dal[i] = al * dt[i];
+            }
+            G(y->alpha)[0] += (float)acc;
+            da = dal;
+        }
+        gemm_tn(D, HD, TB, da, D, y->o, HD, G(y->w_o), HD, 0);
+        gemm_nn(TB, HD, D, da, D, W(y->w_o), HD, dof, HD, 0);
         attn_dims ad = {B, H, dk, T, M, p->d_pos, p->attn_len[l] ? p->attn_len[l] : L,
                         sqrtf((float)dk * (float)D)};
         /* tied tables accumulate into layer 0's gradient, nncp.c:742-744, 758-760 */
@@ -867,7 +912,7 @@ int orc_eval_gradient(orc_model *m, const int32_t *targets, float *loss_out)
         for (int i = 0; i < D; i++)
             ge[i] += dx[(size_t)r * D + i] * emul;
     }
-    free(dz); free(dx); free(dt); free(dy); free(dh); free(dhp); free(dof); free(dq); free(dkv);
+    free(dz); free(dx); free(dt); free(dy); free(dh); free(dhp); free(dof); free(dq); free(dkv); free(dal);
     return NNCU_OK;
 }
 

@@ -43,6 +43,8 @@ CONFIGS = {
     "pre_final_ln_relu": dict(ln_flags=tt.LN_PRE | tt.LN_FINAL, ff_act=tt.FF_RELU,
                               use_bias=0, query_bias=0),
     "tied_tables_longmem": dict(tied_w_r=1, tied_b_r=1, mem_len=10, d_pos=14, n_layer=3),
+    "ln_coef_post": dict(ln_flags=tt.LN_POST | tt.LN_COEF),
+    "ln_coef_pre_rms": dict(ln_flags=tt.LN_PRE | tt.LN_FINAL | tt.LN_RMSNORM | tt.LN_COEF, ff_act=tt.FF_GEGLU, n_streams=3),
     "gated_silu_wide": dict(ff_act=tt.FF_GATED_SILU, n_layer=2, d_model=32, n_head=2, d_key=16, d_inner=64,
                             d_pos=10, mem_len=6, seg_len=6, n_streams=3, n_symbols=32, wscale=0.1),
     "short_mem_window": dict(mem_len=2, d_pos=5, seg_len=6,

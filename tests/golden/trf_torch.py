@@ -50,6 +50,8 @@ def param_shapes(c):
             out.append((f"ln_b_{2 * l}", (D,)))
             out.append((f"ln_g_{2 * l + 1}", (D,)))
             out.append((f"ln_b_{2 * l + 1}", (D,)))
+        if c["ln_flags"] & LN_COEF:
+            out.append((f"alpha_{l}", (1,)))
     if c["ln_flags"] & LN_FINAL:
         out.append((f"ln_g_{2 * c['n_layer']}", (D,)))
         out.append((f"ln_b_{2 * c['n_layer']}", (D,)))
@@ -125,7 +127,10 @@ def forward(params, c, ids, mem):
         alen = c["attn_len"][l] if c["attn_len"][l] else L
         o = attention(q.view(T, B, H, dk), k.reshape(L, B, H, dk), v.reshape(L, B, H, dk),
                       w_r, params[f"b_r_{br_l}"], c, alen)
-        y = o.reshape(T, B, H * dk) @ g("w_o").T + x                 # nncp.c:872, 896
+        y = o.reshape(T, B, H * dk) @ g("w_o").T
+        if fl & LN_COEF:
+            y = y * g("alpha")                                        # nncp.c:892-894
+        y = y + x                                                     # nncp.c:872, 896
         if fl & LN_POST:
             y = norm(y, params[f"ln_g_{2*l}"], params[f"ln_b_{2*l}"], fl)
         u = norm(y, params[f"ln_g_{2*l+1}"], params[f"ln_b_{2*l+1}"], fl) if fl & LN_PRE else y
@@ -145,6 +150,8 @@ def forward(params, c, ids, mem):
         z = h @ g("ff2").T
         if c["use_bias"]:
             z = z + g("ff_bias2")
+        if fl & LN_COEF:
+            z = z * g("alpha")                                        # nncp.c:975-977
         x = z + y                                                     # nncp.c:979
         if fl & LN_POST:
             x = norm(x, params[f"ln_g_{2*l+1}"], params[f"ln_b_{2*l+1}"], fl)

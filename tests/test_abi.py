@@ -43,7 +43,7 @@ def test_default_params_and_version(pkg):
 
 def test_invalid_options_are_rejected_before_any_device_work(pkg):
     lib = pkg.library()
-    for over in (dict(d_pos=1000), dict(ln_flags=3), dict(ln_flags=8), dict(ff_act=4),
+    for over in (dict(d_pos=1000), dict(ln_flags=3), dict(ff_act=4),
                  dict(d_value=7), dict(n_layer=0), dict(n_layer=33)):
         p = pkg.abi.make_params(**over)
         h = C.c_void_p()

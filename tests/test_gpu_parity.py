@@ -247,7 +247,8 @@ def test_train_step_fp32_vs_golden_and_oracle(pkg, oracle, name):
                                                ("c0_like", 1, 1), ("c0_like", 1, 2),
                                                ("pre_final_geglu_rms", 1, 2), ("tied_tables_longmem", 1, 2),
                                                ("mma_dk16", 1, 2), ("mma_two_key_blocks", 1, 2),
-                                               ("mma_two_key_blocks", 1, 1), ("mma_long_memory", 1, 2)])
+                                               ("mma_two_key_blocks", 1, 1), ("mma_long_memory", 1, 2),
+                                               ("ln_coef_post", 1, 2), ("ln_coef_pre_rms", 0, 1)])
 def test_one_symbol_steps_equal_whole_segment_bitwise(pkg, name, bf16, backend):
     cfg, z = load_golden(name)
     p = params_from_cfg(pkg, cfg, use_bf16=bf16, gemm_backend=backend)
@@ -269,7 +270,8 @@ def test_one_symbol_steps_equal_whole_segment_bitwise(pkg, name, bf16, backend):
 
 
 @pytest.mark.parametrize("name", ["c0_like", "pre_final_geglu_rms", "tied_tables_longmem", "mma_dk16",
-                                  "mma_two_key_blocks", "mma_long_memory", "post_gelu", "gated_silu_wide"])
+                                  "mma_two_key_blocks", "mma_long_memory", "post_gelu", "gated_silu_wide",
+                                  "ln_coef_post", "ln_coef_pre_rms"])
 @pytest.mark.parametrize("backend", [1, 2])
 def test_train_step_bf16_vs_oracle(pkg, oracle, name, backend):
     cfg, z = load_golden(name)
@@ -284,9 +286,15 @@ def test_train_step_bf16_vs_oracle(pkg, oracle, name, backend):
         assert rel_err(probs, probs_ref) < BF16_TOL
         loss, loss_ref = m.eval_gradient(z["targets"][s]), o.eval_gradient(z["targets"][s])
         assert abs(loss - loss_ref) < BF16_TOL * abs(loss_ref)
+        gmax = max(np.abs(o.get_grad(pname)).max() for pname in m.info)
         for pname in m.info:
             g_ref = o.get_grad(pname)
             scale = max(np.abs(g_ref).max(), 1e-6)
+            # LN_COEF's alpha is ONE number: the sum of T*B*D signed products of bf16-rounded factors, most of
+            # which cancel.  Its rounding noise is set by the products, not by the (small) sum, so it is
+            # measured against the largest gradient entry of the model instead of against itself.
+            if pname.startswith("alpha"):
+                scale = max(scale, gmax)
             assert np.abs(m.get_grad(pname) - g_ref).max() / scale < 5 * BF16_TOL, (pname, s)
         grads = {pname: o.get_grad(pname) for pname in m.info}
         before = {pname: o.get_param(pname) for pname in m.info}
@@ -326,7 +334,7 @@ def test_output_head_split_k_vs_oracle(pkg, oracle):
 
 
 @pytest.mark.parametrize("name,bf16,graphs", [("c0_like", 1, 0), ("c0_like", 1, 1), ("tied_tables_longmem", 1, 1),
-                                              ("post_gelu", 0, 1)])
+                                              ("post_gelu", 0, 1), ("ln_coef_post", 1, 1)])
 def test_fused_gradient_and_update_gives_the_same_bits(pkg, name, bf16, graphs):
     """nncu_eval_gradient_update + nncu_memory_shift against nncu_eval_gradient + nncu_update over six
     steps with a changing learning rate and bias correction on: same losses, same weights; eager
@@ -374,7 +382,7 @@ def test_two_runs_are_bit_identical(pkg):
 
 
 @pytest.mark.parametrize("name,bf16", [("c0_like", 0), ("mma_two_key_blocks", 1), ("tied_tables_longmem", 1),
-                                       ("mma_long_memory", 1)])
+                                       ("mma_long_memory", 1), ("ln_coef_pre_rms", 1)])
 def test_graph_replay_equals_eager(pkg, name, bf16):
     """On a non-default stream forward and backward are captured into CUDA graphs on their second
     use; six steps there must give the same bits as six eager steps on the default stream."""

@@ -98,7 +98,7 @@ def test_oracle_incremental_equals_batched(pkg, oracle, name):
 
 def test_oracle_rejects_bad_options(pkg, oracle):
     cfg, _ = load_golden("post_gelu")
-    for over in (dict(d_pos=100), dict(ln_flags=3), dict(ln_flags=8), dict(ff_act=4),
+    for over in (dict(d_pos=100), dict(ln_flags=3), dict(ff_act=4),
                  dict(d_value=4), dict(n_layer=0)):
         with pytest.raises(ValueError):
             oracle.OracleModel(params_from_cfg(pkg, cfg, **over))
