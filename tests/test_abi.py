@@ -25,6 +25,37 @@ def test_library_exports_every_declared_symbol(pkg):
     assert set(names) == set(pkg.abi.PROTOTYPES), "abi.py and include/nncu.h disagree"
 
 
+def _declared_in(header, prefix):
+    text = open(os.path.join(ROOT, "include", header)).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(" + prefix + r"[a-z0-9_]+)\s*\(", text)))
+
+
+def test_host_library_exports_every_declared_symbol(pkg):
+    """libnncp_host.so carries everything include/nncp_host.h and include/nncp_metal_frontend.h declare
+    (typedef names and function-pointer members are not calls: only names followed by an argument list
+    at file scope count, which the plugin table's members are not, since they are written (*name))."""
+    pkg.build_library()
+    lib = C.CDLL(pkg.loader.HOSTLIB)
+    host = [n for n in _declared_in("nncp_host.h", "nch_")]
+    front = _declared_in("nncp_metal_frontend.h", "nncpm_")
+    assert len(host) >= 25 and len(front) >= 10
+    for n in host + front:
+        assert hasattr(lib, n), f"{n} is declared but not exported by libnncp_host.so"
+
+
+def test_plugin_table_has_the_layout_of_the_header(pkg):
+    """The ctypes mirror of nch_model_ops: one pointer, three ints, then one function pointer per member of
+    the header's struct, in the header's order."""
+    text = open(os.path.join(ROOT, "include", "nncp_host.h")).read()
+    body = text[text.index("typedef struct nch_model_ops {"):text.index("} nch_model_ops;")]
+    body = re.sub(r"/\*.*?\*/", "", body, flags=re.S)
+    members = re.findall(r"\(\*([a-z_0-9]+)\)\(", body)
+    fields = [f[0] for f in pkg.host.ModelOps._fields_]
+    assert fields[:4] == ["ctx", "n_streams", "seg_len", "n_symbols"]
+    assert fields[4:] == members
+
+
 def test_struct_layout_matches_header(pkg):
     # nncu_params: 12 int32 + 32 int32 + 8 uint8 + 2 float + int32 + uint32 + 4 float + 3 int32
     assert C.sizeof(pkg.abi.Params) == 4 * 12 + 4 * 32 + 8 + 4 * 2 + 4 + 4 + 4 * 4 + 4 * 3
