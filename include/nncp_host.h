@@ -14,6 +14,8 @@
  *   nch_process_block             process_block                              nncp.c:2968-3147
  *   nch_write_header/read_header  nncp_write_file_header, trf_write_params   nncp.c:2665-2760, 1333-1445
  *   nch_compress / nch_decompress encode_file, decode_file (memory to memory) nncp.c:3307-3677
+ *   nch_words_encode / _decode    word_encode, word_decode (text tokenizer)  preprocess.c:1093-1323
+ *   nch_read_dict, fp->dict       write/read_compressed_file (zlib)          nncp.c:3222-3305, 3407-3413
  */
 #ifndef NNCP_HOST_H
 #define NNCP_HOST_H
@@ -129,11 +131,18 @@ typedef struct nch_file_params {
     nncu_params model;            /* n_streams is batch_size; d_model = d_key * n_head on read */
     nch_interp_params lr, block_len;
     int32_t n_ranks;              /* ranks the streams were sharded over; 0 or 1: one process (header version 3 otherwise) */
+    const uint8_t *dict;          /* write: the word dictionary to carry (text of nch_words_encode), NULL: none.
+                                     read: always NULL; fetch the text with nch_read_dict */
+    uint32_t dict_len;            /* its size in bytes; on read, the size recorded in the file (0: no dictionary) */
 } nch_file_params;
 int nch_write_header(const nch_file_params *fp, uint32_t n_symbols_in_file, uint8_t *out, size_t cap,
                      size_t *len);
 int nch_read_header(const uint8_t *in, size_t n, nch_file_params *fp, uint32_t *n_symbols_in_file,
                     size_t *consumed);
+
+/* The dictionary a file carries (nncp.c:3264-3305): inflates it into *dict (malloc'ed, free with
+   nch_free).  *dict = NULL and *dict_len = 0 when the file has none. */
+int nch_read_dict(const uint8_t *in, size_t n, uint8_t **dict, size_t *dict_len);
 
 /* length of the block that starts at symbol file_pos (schedule value rounded down to whole
    segments of all streams, at least one, at most what remains; nncp.c:3428-3441) */
@@ -147,6 +156,22 @@ int nch_compress(const nch_model_ops *m, const nch_file_params *fp, const uint16
 int nch_decompress(const nch_model_ops *m, const nch_file_params *fp, const uint8_t *payload, size_t n,
                    uint32_t n_symbols_in_file, int out_mode, uint16_t *symbols_out);
 void nch_free(void *p);
+
+/* ---- word tokenizer (preprocess.c) ----
+   nch_words_encode folds case and spaces, builds a dictionary of at most about n_words entries
+   (256 bytes + words seen at least min_word_freq times) and writes the text as 16-bit indices
+   into it: word_encode (preprocess.c:1093-1226), same dictionary text and same symbols.  *dict,
+   *symbols are malloc'ed (nch_free); *n_entries is the number of dictionary entries, and the
+   model's alphabet is that rounded up to a multiple of 8 (nncp.c:3382).
+   nch_words_decode is word_decode (preprocess.c:1270-1323): NCH_ERR_FORMAT for a symbol past
+   the dictionary or an escape other than backslash-n or backslash-backslash (an entry above 4096
+   bytes, which the reference's encoder can make and its decoder refuses, decodes here).
+   nch_words_count returns the number of entries of a dictionary text (negative: -error). */
+int nch_words_encode(const uint8_t *text, size_t n, int n_words, int min_word_freq, uint8_t **dict,
+                     size_t *dict_len, uint16_t **symbols, size_t *n_symbols, int *n_entries);
+int nch_words_decode(const uint8_t *dict, size_t dict_len, const uint16_t *symbols, size_t n_symbols,
+                     uint8_t **text, size_t *text_len);
+int nch_words_count(const uint8_t *dict, size_t dict_len);
 
 #ifdef __cplusplus
 }

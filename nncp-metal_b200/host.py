@@ -31,7 +31,8 @@ class InterpParams(C.Structure):
 
 
 class FileParams(C.Structure):
-    _fields_ = [("model", abi.Params), ("lr", InterpParams), ("block_len", InterpParams), ("n_ranks", C.c_int32)]
+    _fields_ = [("model", abi.Params), ("lr", InterpParams), ("block_len", InterpParams), ("n_ranks", C.c_int32),
+                ("dict", C.c_void_p), ("dict_len", C.c_uint32)]
 
 
 class BlockStats(C.Structure):
@@ -120,16 +121,83 @@ def library():
                                      C.c_uint32, _I, _vp]
         L.nch_free.argtypes = [_vp]
         L.nch_free.restype = None
+        L.nch_read_dict.argtypes = [_vp, C.c_size_t, C.POINTER(_vp), C.POINTER(C.c_size_t)]
+        L.nch_words_encode.argtypes = [_vp, C.c_size_t, _I, _I, C.POINTER(_vp), C.POINTER(C.c_size_t),
+                                       C.POINTER(_vp), C.POINTER(C.c_size_t), C.POINTER(_I)]
+        L.nch_words_decode.argtypes = [_vp, C.c_size_t, _vp, C.c_size_t, C.POINTER(_vp), C.POINTER(C.c_size_t)]
+        L.nch_words_count.argtypes = [_vp, C.c_size_t]
         _lib = L
     return _lib
 
 
-def file_params(model_params, lr=None, block_len=500000):
+def file_params(model_params, lr=None, block_len=500000, dictionary=None):
+    """`dictionary`: the text nch_words_encode made; the file then carries it (deflated) in its header."""
     fp = FileParams()
     fp.model = model_params
     fp.lr = lr if lr is not None else InterpParams.make([model_params.lr])
     fp.block_len = InterpParams.make([float(block_len)])
+    if dictionary:
+        fp._dict_keep = C.create_string_buffer(bytes(dictionary), len(dictionary))   # owned by fp
+        fp.dict = C.cast(fp._dict_keep, C.c_void_p)
+        fp.dict_len = len(dictionary)
     return fp
+
+
+def words_encode(text, n_words, min_word_freq):
+    """word_encode of the reference preprocessor on memory: returns (dictionary text, uint16 symbols,
+    number of dictionary entries).  The model's alphabet is `alphabet_size(entries)`."""
+    L = library()
+    text = bytes(text)
+    d, dn, s, sn, ne = _vp(), C.c_size_t(), _vp(), C.c_size_t(), _I()
+    rc = L.nch_words_encode(text, len(text), n_words, min_word_freq, C.byref(d), C.byref(dn), C.byref(s),
+                            C.byref(sn), C.byref(ne))
+    if rc != 0:
+        raise ValueError(f"nch_words_encode: {rc}")
+    dictionary = C.string_at(d.value, dn.value)
+    syms = np.frombuffer(C.string_at(s.value, 2 * sn.value), np.uint16).copy() if sn.value else np.zeros(0, np.uint16)
+    L.nch_free(d)
+    L.nch_free(s)
+    return dictionary, syms, ne.value
+
+
+def words_decode(dictionary, symbols):
+    """word_decode on memory: the text the symbols stand for."""
+    L = library()
+    s = np.ascontiguousarray(symbols, np.uint16)
+    t, tn = _vp(), C.c_size_t()
+    rc = L.nch_words_decode(bytes(dictionary), len(dictionary), s.ctypes.data_as(_vp), s.size, C.byref(t),
+                            C.byref(tn))
+    if rc != 0:
+        raise ValueError(f"nch_words_decode: {rc}")
+    text = C.string_at(t.value, tn.value)
+    L.nch_free(t)
+    return text
+
+
+def words_count(dictionary):
+    n = library().nch_words_count(bytes(dictionary), len(dictionary))
+    if n < 0:
+        raise ValueError(f"bad dictionary: {-n}")
+    return n
+
+
+def alphabet_size(n_entries):
+    """Symbols of the model for a dictionary of n_entries: the next multiple of 8 (nncp.c:3382)."""
+    return (n_entries + 7) & ~7
+
+
+def read_dict(data):
+    """The dictionary text a compressed file carries, or None."""
+    L = library()
+    d, dn = _vp(), C.c_size_t()
+    rc = L.nch_read_dict(bytes(data), len(data), C.byref(d), C.byref(dn))
+    if rc != 0:
+        raise ValueError(f"nch_read_dict: {rc}")
+    if not d.value:
+        return None
+    text = C.string_at(d.value, dn.value)
+    L.nch_free(d)
+    return text
 
 
 def header_bytes(fp, n_symbols):

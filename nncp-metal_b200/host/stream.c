@@ -11,6 +11,8 @@
 #include <stdlib.h>
 #include <string.h>
 
+#include <zlib.h>
+
 #include "nncp_host.h"
 
 int nch_get_symb(const uint16_t *buf, int stride, int rem, int stream_idx, int pos)
@@ -443,14 +445,32 @@ int nch_write_header(const nch_file_params *fp, uint32_t n_symbols_in_file, uint
     }
     if (v3)
         w8(&w, fp->n_ranks);
-    w8(&w, 0);                 /* no preprocessing dictionary */
+    if (fp->dict && fp->dict_len) {
+        /* the dictionary text, deflated at level 9 behind its two sizes (nncp.c:3222-3261) */
+        uLongf zlen = compressBound(fp->dict_len);
+        uint8_t *z = (uint8_t *)malloc(zlen);
+        if (!z)
+            return NCH_ERR_NOMEM;
+        if (compress2(z, &zlen, fp->dict, fp->dict_len, Z_BEST_COMPRESSION) != Z_OK) {
+            free(z);
+            return NCH_ERR_INVALID;
+        }
+        w8(&w, 1);
+        w32(&w, fp->dict_len);
+        w32(&w, (uint32_t)zlen);
+        for (uLongf i = 0; i < zlen; i++)
+            w8(&w, z[i]);
+        free(z);
+    } else {
+        w8(&w, 0);             /* no preprocessing dictionary */
+    }
     w32(&w, n_symbols_in_file);
     *len = w.len;
     return (out && w.overflow) ? NCH_ERR_INVALID : NCH_OK;
 }
 
-int nch_read_header(const uint8_t *in, size_t n, nch_file_params *fp, uint32_t *n_symbols_in_file,
-                    size_t *consumed)
+static int read_header(const uint8_t *in, size_t n, nch_file_params *fp, uint32_t *n_symbols_in_file,
+                       size_t *consumed, size_t *z_at, size_t *z_len)
 {
     if (!in || !fp)
         return NCH_ERR_INVALID;
@@ -512,8 +532,18 @@ int nch_read_header(const uint8_t *in, size_t n, nch_file_params *fp, uint32_t *
     fp->n_ranks = ver >= 3 ? (int)r8(&r) : 1;
     if (fp->n_ranks < 1)
         return NCH_ERR_FORMAT;
-    if (r8(&r) != 0)
-        return NCH_ERR_FORMAT; /* preprocessing dictionary */
+    const unsigned has_dict = r8(&r) & 1;
+    if (has_dict) { /* raw size, deflated size, zlib stream: skipped here, nch_read_dict inflates it */
+        fp->dict_len = r32(&r);
+        const uint32_t zlen = r32(&r);
+        if (r.bad || zlen > r.len - r.pos || fp->dict_len == 0)
+            return NCH_ERR_FORMAT;
+        if (z_at)
+            *z_at = r.pos;
+        if (z_len)
+            *z_len = zlen;
+        r.pos += zlen;
+    }
     uint32_t nsym = r32(&r);
     if (r.bad)
         return NCH_ERR_FORMAT;
@@ -525,6 +555,36 @@ int nch_read_header(const uint8_t *in, size_t n, nch_file_params *fp, uint32_t *
         *n_symbols_in_file = nsym;
     if (consumed)
         *consumed = r.pos;
+    return NCH_OK;
+}
+
+int nch_read_header(const uint8_t *in, size_t n, nch_file_params *fp, uint32_t *n_symbols_in_file,
+                    size_t *consumed)
+{
+    return read_header(in, n, fp, n_symbols_in_file, consumed, NULL, NULL);
+}
+
+int nch_read_dict(const uint8_t *in, size_t n, uint8_t **dict, size_t *dict_len)
+{
+    if (!in || !dict || !dict_len)
+        return NCH_ERR_INVALID;
+    nch_file_params fp;
+    size_t z_at = 0, z_len = 0;
+    *dict = NULL;
+    *dict_len = 0;
+    const int rc = read_header(in, n, &fp, NULL, NULL, &z_at, &z_len);
+    if (rc || fp.dict_len == 0)
+        return rc;
+    uint8_t *text = (uint8_t *)malloc(fp.dict_len);
+    if (!text)
+        return NCH_ERR_NOMEM;
+    uLongf got = fp.dict_len;
+    if (uncompress(text, &got, in + z_at, (uLong)z_len) != Z_OK || got != fp.dict_len) {
+        free(text);
+        return NCH_ERR_FORMAT;
+    }
+    *dict = text;
+    *dict_len = got;
     return NCH_OK;
 }
 

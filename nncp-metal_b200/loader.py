@@ -62,7 +62,7 @@ def build_library(force=False, verbose=False):
                                [os.path.join(ROOT, "include", "nncp_host.h"),
                                 os.path.join(ROOT, "include", "nncp_metal_frontend.h")])):
         cmd = ["gcc", "-O2", "-fPIC", "-shared", "-Wall", "-I", os.path.join(ROOT, "include"),
-               "-I", HOST, "-o", HOSTLIB] + hc + ["-lm", "-ldl"]
+               "-I", HOST, "-o", HOSTLIB] + hc + ["-lz", "-lm", "-ldl"]
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode != 0:
             raise RuntimeError("gcc failed:\n" + r.stdout + r.stderr)

@@ -32,9 +32,18 @@ def build(force=False):
     srcs = [os.path.join(HERE, f) for f in ("trf_oracle.c", "coder_oracle.c")]
     stale = (not os.path.exists(so)) or any(os.path.getmtime(s) > os.path.getmtime(so) for s in srcs)
     ref = reference_dir()
-    if force or stale or (ref and not os.path.exists(os.path.join(HERE, "_ref", "libref_coder.so"))):
+    have_ref = all(os.path.exists(os.path.join(HERE, "_ref", f)) for f in ("libref_coder.so", "preprocess_ref"))
+    if force or stale or (ref and not have_ref):
         subprocess.run(["make", "-C", HERE, "all", f"REF={ref or ''}"], check=True, capture_output=True)
     return so
+
+
+def preprocess_ref():
+    """Path of the reference's stand-alone word preprocessor (built from its preprocess.c by the
+    Makefile here), or None when it was never built: `preprocess_ref c dict in out n_words min_freq`
+    encodes, `preprocess_ref d dict in out` decodes."""
+    exe = os.path.join(HERE, "_ref", "preprocess_ref")
+    return exe if os.access(exe, os.X_OK) else None
 
 
 _lib = None

@@ -72,6 +72,46 @@ def test_reference_cli_with_its_tokenizer_round_trips(tmp_path):
 
 @pytest.mark.gpu
 @pytest.mark.skipif(not os.path.exists(BIN), reason="host/dropin/_build/nncp_b200 was never built")
+def test_host_code_tokenizer_writes_and_reads_the_reference_cli_file(pkg, tmp_path):
+    """The repository's own tokenizer and container (nch_words_encode, the dictionary in the header)
+    against the reference CLI with --preprocess: the same file byte for byte, and each side decodes
+    the other's file back to the text."""
+    H = pkg.host
+    data = _text(12000, 7)
+    src, cmp_, back = tmp_path / "in.txt", tmp_path / "out.nncp", tmp_path / "back.txt"
+    src.write_bytes(data)
+    r = subprocess.run([BIN] + OPTS + ["--preprocess", "300,2", "c", str(src), str(cmp_)], capture_output=True,
+                       text=True, timeout=600)
+    assert r.returncode == 0, r.stdout + r.stderr
+    blob = cmp_.read_bytes()
+
+    d, syms, n_entries = H.words_encode(data, 300, 2)
+    assert H.read_dict(blob) == d
+    p = pkg.abi.make_params(n_layer=2, d_model=64, n_head=2, d_key=32, d_inner=128, d_pos=16, mem_len=16,
+                            seg_len=16, n_streams=4, n_symbols=H.alphabet_size(n_entries), use_bias=1, use_w_r=1,
+                            tied_w_r=1, tied_b_r=1, query_bias=0, ln_flags=1, ff_act=1, init_range=1.0,
+                            init_kind=0, seed=123, beta2=0.9999, eps=1e-8, gradient_clip=0.1, lr=3e-4)
+    fp = H.file_params(p, lr=H.InterpParams.make([3e-4, 1e-4], [156250]), block_len=500000, dictionary=d)
+    ops = H.bind_cuda(p)
+    mine, _ = H.compress(ops, fp, syms, H.EVAL_SEGMENT, H.OUT_CODER_READY)
+    H.unbind_cuda(ops)
+    assert mine == blob
+    # the reference CLI decodes the file of the host code (the same bytes, written by this side) ...
+    (tmp_path / "mine.nncp").write_bytes(mine)
+    r = subprocess.run([BIN, "-q", "--cuda", "d", str(tmp_path / "mine.nncp"), str(back)], capture_output=True,
+                       text=True, timeout=600)
+    assert r.returncode == 0, r.stdout + r.stderr
+    assert back.read_bytes() == data
+    # ... and the host code decodes the CLI's
+    fp2, _, _ = H.read_header(blob)
+    ops = H.bind_cuda(fp2.model)
+    out = H.decompress(ops, blob, H.OUT_CODER_READY)
+    H.unbind_cuda(ops)
+    assert H.words_decode(H.read_dict(blob), out) == data
+
+
+@pytest.mark.gpu
+@pytest.mark.skipif(not os.path.exists(BIN), reason="host/dropin/_build/nncp_b200 was never built")
 def test_reference_cli_retrain_without_dropout_round_trips(tmp_path):
     """--retrain_period / --retrain_len: the reference's retrain_block (nncp.c:2821-2941, host code
     compiled unmodified into the drop-in) re-trains the model on the symbols already coded, on both
