@@ -138,6 +138,29 @@ static long pt_find(const pairtab *t, uint16_t a, uint16_t b)
     return -1;
 }
 
+/* room for n entries up front, so that a table whose size is known roughly does not grow by doubling */
+static int pt_reserve(pairtab *t, size_t n)
+{
+    if (n <= t->cap)
+        return 0;
+    uint16_t *na = realloc(t->a, n * sizeof(*na));
+    if (na)
+        t->a = na;
+    uint16_t *nb = realloc(t->b, n * sizeof(*nb));
+    if (nb)
+        t->b = nb;
+    uint32_t *nf = realloc(t->freq, n * sizeof(*nf));
+    if (nf)
+        t->freq = nf;
+    if (!na || !nb || !nf)
+        return -1;
+    t->cap = n;
+    size_t slots = t->n_slots ? t->n_slots : 4096;
+    while (slots < 2 * n)
+        slots *= 2;
+    return slots != t->n_slots ? pt_rehash(t, slots) : 0;
+}
+
 /* index of the pair, appended with frequency 0 when new; -1: out of memory */
 static long pt_get(pairtab *t, uint16_t a, uint16_t b)
 {
@@ -327,6 +350,7 @@ typedef struct {
     pairtab words;             /* word k is symbol N_BYTES + k; freq 0: not in use */
     uint32_t byte_freq[N_BYTES];
     symvec buf;
+    size_t pairs_last_round; /* distinct pairs the last round counted: the next table starts that large */
 } builder;
 
 /* bits (x 1024) one occurrence of symbol c costs now; a word not in use costs its two halves */
@@ -354,38 +378,55 @@ static void count_symbols(builder *b)
     }
 }
 
-static int emit_in_use(const builder *b, uint32_t c, symvec *out)
+/* writes symbol c of an expansion, words out of use as their halves, counting what it writes */
+static int emit_counted(builder *b, uint32_t c, symvec *out)
 {
-    if (c >= N_BYTES && b->words.freq[c - N_BYTES] == 0)
-        return emit_in_use(b, b->words.a[c - N_BYTES], out) | emit_in_use(b, b->words.b[c - N_BYTES], out);
+    if (c >= N_BYTES) {
+        const size_t k = c - N_BYTES;
+        if (b->words.freq[k] == 0)
+            return emit_counted(b, b->words.a[k], out) | emit_counted(b, b->words.b[k], out);
+        b->words.freq[k]++;
+    } else {
+        b->byte_freq[c]++;
+    }
     return sv_push(out, (uint16_t)c);
 }
 
-/* recount; words seen fewer than min_freq times go out of use and the buffer is rewritten without
-   them.  Returns the number of words that passed the threshold, or -1. */
+/* With the symbol counts of the buffer at hand (substitute_words leaves them): words seen fewer
+   than min_freq times go out of use and the buffer is rewritten without them, the counts following.
+   Returns the number of words that passed the threshold, or -1. */
 static long prune_rare_words(builder *b, uint32_t min_freq)
 {
-    count_symbols(b);
-    size_t kept = 0;
+    size_t kept = 0, to_expand = 0;
     for (size_t k = 0; k < b->words.n; k++) {
-        if (b->words.freq[k] >= min_freq)
+        if (b->words.freq[k] >= min_freq) {
             kept++;
-        else
+        } else {
+            to_expand += b->words.freq[k] != 0;
             b->words.freq[k] = 0;
+        }
     }
-    if (kept == b->words.n)
-        return (long)kept;
+    if (to_expand == 0)
+        return (long)kept; /* no word of the buffer fell out of use: rewriting it would change nothing */
     symvec out = {0};
+    out.cap = b->buf.n + b->buf.n / 8 + 16;
+    out.v = malloc(out.cap * sizeof(*out.v));
+    if (!out.v)
+        return -1;
     int bad = 0;
-    for (size_t i = 0; i < b->buf.n && !bad; i++)
-        bad = emit_in_use(b, b->buf.v[i], &out);
+    for (size_t i = 0; i < b->buf.n && !bad; i++) {
+        const uint32_t c = b->buf.v[i];
+        if (c >= N_BYTES && b->words.freq[c - N_BYTES] == 0)
+            bad = emit_counted(b, b->words.a[c - N_BYTES], &out) | emit_counted(b, b->words.b[c - N_BYTES], &out);
+        else
+            bad = sv_push(&out, (uint16_t)c); /* counted already */
+    }
     if (bad) {
         free(out.v);
         return -1;
     }
     free(b->buf.v);
     b->buf = out;
-    count_symbols(b);
     return (long)kept;
 }
 
@@ -393,6 +434,18 @@ static int score_before(uint32_t x, uint32_t y, const void *ctx)
 {
     const int64_t *score = ctx;
     return score[x] > score[y];
+}
+
+/* Counts the adjacent pairs of v[0..n) into cand, entries in order of first occurrence. */
+static int count_pairs(const uint16_t *v, size_t n, pairtab *cand)
+{
+    for (size_t i = 0; i + 1 < n; i++) {
+        const long k = pt_get(cand, v[i], v[i + 1]);
+        if (k < 0)
+            return -1;
+        cand->freq[k]++;
+    }
+    return 0;
 }
 
 /* one round: adds up to `limit` new words to b->words.  Returns how many, or -1. */
@@ -406,12 +459,9 @@ static long pick_words(builder *b, long limit, uint32_t min_freq)
     const uint16_t *v = b->buf.v;
     const uint32_t total = (uint32_t)b->buf.n;
 
-    for (size_t i = 0; i + 1 < b->buf.n; i++) {
-        const long k = pt_get(&cand, v[i], v[i + 1]);
-        if (k < 0)
-            goto done;
-        cand.freq[k]++;
-    }
+    if (pt_reserve(&cand, b->pairs_last_round) || count_pairs(v, b->buf.n, &cand))
+        goto done;
+    b->pairs_last_round = cand.n;
     score = malloc((cand.n + 1) * sizeof(*score));
     order = malloc((cand.n + 1) * sizeof(*order));
     const size_t n_sym = N_BYTES + b->words.n;
@@ -419,23 +469,25 @@ static long pick_words(builder *b, long limit, uint32_t min_freq)
     closes = calloc(n_sym, 1);
     if (!score || !order || !opens || !closes)
         goto done;
+    /* the selection below stops at the first score that is not positive, so only the candidates
+       with a positive score need sorting; they keep their order of first occurrence among equals */
+    size_t n_pos = 0;
     for (size_t k = 0; k < cand.n; k++) {
         const int64_t f = cand.freq[k];
-        order[k] = (uint32_t)k;
-        if (f <= 1) {
-            score[k] = -1;
-            continue;
-        }
+        if (f <= 1)
+            continue; /* a pair seen once saves nothing */
         const int64_t as_two = (symbol_bits(b, cand.a[k], total) + symbol_bits(b, cand.b[k], total)) * f;
         const int64_t as_one = (-(int64_t)(fixed_log2((uint32_t)f) - fixed_log2(total)) + COST_PER_USE) * f + COST_PER_WORD;
         score[k] = as_two - as_one;
+        if (score[k] > 0)
+            order[n_pos++] = (uint32_t)k;
     }
-    if (stable_sort(order, cand.n, score_before, score))
+    if (stable_sort(order, n_pos, score_before, score))
         goto done;
     added = 0;
-    for (size_t r = 0; r < cand.n; r++) {
+    for (size_t r = 0; r < n_pos; r++) {
         const size_t k = order[r];
-        if (score[k] <= 0 || cand.freq[k] < min_freq)
+        if (cand.freq[k] < min_freq)
             break;
         const uint16_t a = cand.a[k], c = cand.b[k];
         if (closes[a] || opens[c])
@@ -462,21 +514,41 @@ done:
     return added;
 }
 
-/* every pair of the buffer that is a word (in use or not) becomes that word, greedily from the left */
-static void substitute_words(builder *b)
+/* every pair of the buffer that is a word (in use or not) becomes that word, greedily from the
+   left; the symbols of the new buffer are counted on the way */
+static int substitute_words(builder *b)
 {
     uint16_t *v = b->buf.v;
     size_t n = b->buf.n, i = 0, j = 0;
+    /* most positions start no word: ask the table only where the two symbols can be the halves of one */
+    const size_t n_sym = N_BYTES + b->words.n;
+    uint8_t *half = calloc(n_sym, 1);
+    if (!half)
+        return -1;
+    for (size_t k = 0; k < b->words.n; k++) {
+        half[b->words.a[k]] |= 1;
+        half[b->words.b[k]] |= 2;
+    }
+    memset(b->byte_freq, 0, sizeof(b->byte_freq));
+    memset(b->words.freq, 0, b->words.n * sizeof(*b->words.freq));
     while (i < n) {
-        long k = i + 1 < n ? pt_find(&b->words, v[i], v[i + 1]) : -1;
+        long k = i + 1 < n && (half[v[i]] & 1) && (half[v[i + 1]] & 2) ? pt_find(&b->words, v[i], v[i + 1]) : -1;
         if (k >= 0) {
+            b->words.freq[k]++;
             v[j++] = (uint16_t)(N_BYTES + k);
             i += 2;
         } else {
-            v[j++] = v[i++];
+            const uint32_t c = v[i++];
+            if (c < N_BYTES)
+                b->byte_freq[c]++;
+            else
+                b->words.freq[c - N_BYTES]++;
+            v[j++] = (uint16_t)c;
         }
     }
     b->buf.n = j;
+    free(half);
+    return 0;
 }
 
 /* the first `room` bytes of symbol c; returns how many were written */
@@ -582,7 +654,10 @@ int nch_words_encode(const uint8_t *text, size_t n, int n_words, int min_word_fr
         }
         if (added == 0)
             break;
-        substitute_words(&b);
+        if (substitute_words(&b)) {
+            rc = NCH_ERR_NOMEM;
+            goto done;
+        }
         const long before = in_use;
         in_use = prune_rare_words(&b, min_freq);
         if (in_use < 0) {
