@@ -53,11 +53,18 @@ void nch_dec_free(nch_dec *d);
 float nch_vec_sum_f32(const float *tab, size_t n);
 void nch_write_sym(nch_enc *e, const float *prob, int n_symb, int sym);
 int nch_read_sym(nch_dec *d, const float *prob, int n_symb);
-/* the same walk fed by coder-ready device output (nncu_coder_paths / nncu_coder_trees) */
+/* the same walk fed by coder-ready device output (nncu_coder_paths / nncu_coder_trees).
+   nch_write_sym_path takes the decisions from the bits of sym: alphabets that are a power of two.
+   nch_write_sym_path_any and nch_read_sym_tree repeat write_sym's splitting (n >> 1 symbols to the
+   left) and serve any alphabet; a tree row has 1 << nch_tree_depth(n_symb) entries in heap order,
+   a path row nch_tree_depth(n_symb) = ceil(log2 n_symb). */
 void nch_write_sym_path(nch_enc *e, const uint16_t *prob0, int n_bits, int sym);
+void nch_write_sym_path_any(nch_enc *e, const uint16_t *prob0, int n_symb, int sym);
 int nch_read_sym_tree(nch_dec *d, const uint16_t *tree, int n_symb);
-/* n symbols in a row: prob0 [n][n_bits] / trees [n][n_symb] (the coding rank of a sharded job) */
+int nch_tree_depth(int n_symb);
+/* n symbols in a row: prob0 [n][n_bits] / [n][depth], trees [n][1 << depth] (the coding rank of a sharded job) */
 void nch_write_sym_paths(nch_enc *e, const uint16_t *prob0, int n_bits, const int32_t *sym, size_t n);
+void nch_write_sym_paths_any(nch_enc *e, const uint16_t *prob0, int n_symb, const int32_t *sym, size_t n);
 void nch_read_sym_trees(nch_dec *d, const uint16_t *trees, int n_symb, size_t n, int32_t *sym_out);
 
 /* ---- schedule (cp_utils.h:60-71, cp_utils.c:380-410) ---- */

@@ -262,11 +262,14 @@ int nncu_weights_hash(nncu_model *m, uint64_t *hash_out);
 /* ---- coder-ready output (write_sym / read_sym, cp_utils.c:299-349) ---- */
 /*
  * For every row r in [t0*B, (t0+nt)*B) and its symbol sym[r - t0*B]
- * (int32, host), writes the n_bits = ceil(log2 V) 15-bit prob0 values that
- * write_sym would pass to put_bit, root first, to prob0_host
- * [nt*B][n_bits] (uint16).  V must be a power of two.  The partial sums use
- * the pairing vec_sum_f32(tab, n) = vec_sum_f32(tab, n/2) +
- * vec_sum_f32(tab + n/2, n - n/2).
+ * (int32, host), writes the 15-bit prob0 values that write_sym would pass
+ * to put_bit, root first, to prob0_host [nt*B][n_bits] (uint16), n_bits =
+ * ceil(log2 V).  V may be any size from 2 up (16384; 25600 when a power of
+ * two): write_sym sends n >> 1 of a node's n symbols left, so for a V that
+ * is not a power of two some leaves sit at depth n_bits - 1; such a row
+ * uses n_bits - 1 values and its last entry is 0.  The partial sums use the
+ * pairing vec_sum_f32(tab, n) = vec_sum_f32(tab, n/2) +
+ * vec_sum_f32(tab + n/2, n - n/2), which is that same tree.
  */
 int nncu_coder_paths(nncu_model *m, int t0, int nt, const int32_t *sym_host,
                      uint16_t *prob0_host, int *n_bits_out);
@@ -286,7 +289,9 @@ int nncu_coder_paths_end(nncu_model *m, uint16_t *prob0_host, int *n_bits_out);
 /*
  * For the same rows writes the whole implicit tree: prob0 of node k
  * (heap order: root = 1, children 2k and 2k+1) at tree_host[row][k],
- * [nt*B][V] uint16 (entry 0 unused).  read_sym then needs no float math.
+ * [nt*B][2^ceil(log2 V)] uint16, which is [nt*B][V] for a power of two
+ * (entry 0 and the slots of one-symbol nodes hold 0).  read_sym then needs
+ * no float math.
  */
 int nncu_coder_trees(nncu_model *m, int t0, int nt, uint16_t *tree_host);
 /*

@@ -5,8 +5,11 @@
 //   p0    = vec_sum_f32(left half)      one node of a bottom-up pairwise fp32 tree
 //   prob0 = clamp(lrintf(p0 * 32768 / p), 1, 32767)
 //   p     <- p0 (bit 0)  or  p - p0 (bit 1),  starting from p = 1.0f at the root
-// V must be a power of two: then the halving recursion of vec_sum_f32 is exactly
-// the heap-ordered tree  S[k] = S[2k] + S[2k+1], leaves S[V+i] = prob[i].
+// When V is a power of two the halving recursion of vec_sum_f32 is exactly the
+// heap-ordered tree  S[k] = S[2k] + S[2k+1], leaves S[V+i] = prob[i].  For any
+// other V (a word dictionary's alphabet) the recursion still is a binary tree in
+// heap order, complete down to depth L-1 (L = ceil(log2 V)), whose nodes there
+// cover one symbol (a leaf) or two (the last split): the *_any kernels below.
 #pragma once
 #include "common.cuh"
 
@@ -148,6 +151,117 @@ coder_trees_kernel(const float *__restrict__ probs, uint16_t *__restrict__ out, 
         for (int k = n + threadIdx.x; k < 2 * n; k += blockDim.x) {
             float p = S[k], p0 = S[2 * k];
             o[k] = (uint16_t)prob0_of(p0, p);
+            S[2 * k + 1] = __fsub_rn(p, p0); // p(right); p(left) = p0 is already in S[2k]
+        }
+        __syncthreads();
+    }
+}
+
+// ---------------------------------------------------------------- any alphabet size
+// write_sym splits a range of n symbols into n >> 1 on the left and the rest on the right, and
+// vec_sum_f32 sums by the same halving, so node k of the heap (root 1, children 2k, 2k+1) covers
+// the range found by following the bits of k below its leading one.  With P = 2^L >= V > P/2,
+// every node above depth L-1 covers at least two symbols and every node at depth L-1 one or two.
+
+// the range [lo, lo + n) of heap node k
+__device__ __forceinline__ void node_range(unsigned k, int V, int &lo, int &n)
+{
+    lo = 0;
+    n = V;
+    for (int b = 30 - __clz((int)k); b >= 0; b--) {
+        const int h = n >> 1;
+        if ((k >> b) & 1u) {
+            lo += h;
+            n -= h;
+        } else {
+            n = h;
+        }
+    }
+}
+
+// S[1..2P): sums of the nodes; a one-symbol node at depth L-1 has no children (their slots are 0)
+__device__ __forceinline__ void build_sum_tree_any(float *S, const float *__restrict__ prob, int V, int P)
+{
+    for (int k = (P >> 1) + threadIdx.x; k < P; k += blockDim.x) {
+        int lo, n;
+        node_range((unsigned)k, V, lo, n);
+        if (n == 2) {
+            const float a = prob[lo], b = prob[lo + 1];
+            S[2 * k] = a;
+            S[2 * k + 1] = b;
+            S[k] = __fadd_rn(a, b);
+        } else {
+            S[2 * k] = 0.0f;
+            S[2 * k + 1] = 0.0f;
+            S[k] = prob[lo];
+        }
+    }
+    __syncthreads();
+    for (int n = P >> 2; n >= 1; n >>= 1) {
+        for (int k = n + threadIdx.x; k < 2 * n; k += blockDim.x)
+            S[k] = __fadd_rn(S[2 * k], S[2 * k + 1]);
+        __syncthreads();
+    }
+}
+
+// one block per row: the prob0 values on the path of sym[row], root first, L entries per row; a
+// symbol whose leaf sits at depth L-1 uses L-1 of them and the last is 0
+__global__ void __launch_bounds__(256)
+coder_paths_any_kernel(const float *__restrict__ probs, const int32_t *__restrict__ sym,
+                       uint16_t *__restrict__ out, int V, int P, int L)
+{
+    extern __shared__ float S[];
+    const int row = blockIdx.x;
+    build_sum_tree_any(S, probs + (size_t)row * V, V, P);
+    if (threadIdx.x == 0) {
+        int s = sym[row];
+        s = s < 0 ? 0 : (s >= V ? V - 1 : s);
+        float p = 1.0f;
+        int k = 1, lo = 0, n = V, lvl = 0;
+        while (n > 1 && lvl < L) {
+            const int h = n >> 1;
+            const float p0 = S[2 * k];
+            out[(size_t)row * L + lvl++] = (uint16_t)prob0_of(p0, p);
+            if (s >= lo + h) {
+                lo += h;
+                n -= h;
+                p = __fsub_rn(p, p0);
+                k = 2 * k + 1;
+            } else {
+                n = h;
+                p = p0;
+                k = 2 * k;
+            }
+        }
+        for (; lvl < L; lvl++)
+            out[(size_t)row * L + lvl] = 0;
+    }
+}
+
+// one block per row: prob0 of every internal node in heap order, P entries per row (entry 0 and the
+// one-symbol nodes of depth L-1 hold 0)
+__global__ void __launch_bounds__(256)
+coder_trees_any_kernel(const float *__restrict__ probs, uint16_t *__restrict__ out, int V, int P)
+{
+    extern __shared__ float S[];
+    const int row = blockIdx.x;
+    build_sum_tree_any(S, probs + (size_t)row * V, V, P);
+    uint16_t *o = out + (size_t)row * P;
+    if (threadIdx.x == 0) {
+        S[1] = 1.0f; // running mass p at the root
+        o[0] = 0;
+    }
+    __syncthreads();
+    for (int n = 1; n < P; n <<= 1) {
+        for (int k = n + threadIdx.x; k < 2 * n; k += blockDim.x) {
+            bool split = true;
+            if (2 * n == P) { // depth L-1: one symbol or two
+                int lo, cnt;
+                node_range((unsigned)k, V, lo, cnt);
+                split = cnt == 2;
+            }
+            const float p = S[k], p0 = S[2 * k];
+            o[k] = split ? (uint16_t)prob0_of(p0, p) : (uint16_t)0;
             S[2 * k + 1] = __fsub_rn(p, p0); // p(right); p(left) = p0 is already in S[2k]
         }
         __syncthreads();

@@ -30,6 +30,15 @@
 
 #include "attention_mma.cuh"
 #include "coder.cuh"
+
+// ceil(log2 V): the depth of the coder's tree for any alphabet (its heap has 1 << depth slots per row)
+static int coder_depth(int V)
+{
+    int n = 0;
+    while ((1 << n) < V)
+        n++;
+    return n;
+}
 #include "common.cuh"
 #include "gemm_simt.cuh"
 #include "gemm_tc.cuh"
@@ -1345,7 +1354,7 @@ int nncu_create(const nncu_params *p, nncu_model **out)
                 jobs.push_back(j);
             }
     size_t oJobs = take(sizeof(TransposeJob) * (jobs.size() + 1));
-    m->coder_bytes = (size_t)TB * V * 2;
+    m->coder_bytes = (size_t)TB * ((size_t)1 << coder_depth(V)) * 2; // a tree per row: 2^ceil(log2 V) entries
     size_t oCoder = take(m->coder_bytes);
 
     m->arena_bytes = total;
@@ -1426,9 +1435,16 @@ int nncu_create(const nncu_params *p, nncu_model **out)
         if (D == 1024)
             cudaFuncSetAttribute(norm_bwd_vec_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 8 * 3 * D * 4);
     }
-    if ((size_t)2 * V * 4 > 48 * 1024) {
+    if ((size_t)2 * V * 4 > 48 * 1024 && (size_t)2 * V * 4 <= 200 * 1024) {
         cudaFuncSetAttribute(coder_paths_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 2 * V * 4);
         cudaFuncSetAttribute(coder_trees_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 2 * V * 4);
+    }
+    {
+        const size_t heap_bytes = ((size_t)2 << coder_depth(V)) * 4; // the any-alphabet kernels: 2 * 2^ceil(log2 V) floats
+        if (heap_bytes > 48 * 1024 && heap_bytes <= 200 * 1024) {
+            cudaFuncSetAttribute(coder_paths_any_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)heap_bytes);
+            cudaFuncSetAttribute(coder_trees_any_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)heap_bytes);
+        }
     }
 
     // ---- initial values (trf_init, nncp.c:341-497), computed on the host
@@ -1951,11 +1967,12 @@ static int coder_paths_enqueue(nncu_model *m, int t0, int nt, const int32_t *sym
 {
     if (!m || !sym_host || t0 < 0 || nt < 1 || t0 + nt > m->T)
         return nncu_fail(NNCU_ERR_INVALID, "bad coder range");
-    int nb = coder_bits(m->V);
-    if (nb < 1)
-        return nncu_fail(NNCU_ERR_INVALID, "coder-ready output needs a power-of-two n_symbols");
-    if ((size_t)2 * m->V * 4 > 200 * 1024)
-        return nncu_fail(NNCU_ERR_RANGE, "n_symbols %d is beyond the 25600-symbol limit of the coder kernels", m->V);
+    const bool pow2 = coder_bits(m->V) >= 1;
+    const int nb = coder_depth(m->V), P = 1 << nb;
+    if (m->V < 2)
+        return nncu_fail(NNCU_ERR_INVALID, "coder-ready output needs at least two symbols");
+    if ((size_t)2 * P * 4 > 200 * 1024)
+        return nncu_fail(NNCU_ERR_RANGE, "n_symbols %d is beyond the limit of the coder kernels (16384; 25600 for a power of two)", m->V);
     CUDA_TRY(cudaSetDevice(m->device));
     int rows = nt * m->B;
     CUDA_TRY(cudaEventSynchronize(m->ev_sym));   // the symbol staging area is free again
@@ -1968,7 +1985,10 @@ static int coder_paths_enqueue(nncu_model *m, int t0, int nt, const int32_t *sym
     cudaStream_t st = side_fork(m);
     CUDA_TRY(cudaMemcpyAsync(m->sym_dev, m->sym_pin, sizeof(int32_t) * rows, cudaMemcpyHostToDevice, st));
     CUDA_TRY(cudaEventRecord(m->ev_sym, st));
-    if (m->V >= 1024 && m->V <= 16384)
+    if (!pow2)
+        coder_paths_any_kernel<<<rows, 256, (size_t)2 * P * 4, st>>>(m->probs + (size_t)t0 * m->B * m->V, m->sym_dev,
+                                                                    m->coder_dev, m->V, P, nb);
+    else if (m->V >= 1024 && m->V <= 16384)
         coder_paths_fast_kernel<<<rows, 256, 0, st>>>(m->probs + (size_t)t0 * m->B * m->V, m->sym_dev, m->coder_dev, m->V, nb);
     else
         coder_paths_kernel<<<rows, 256, (size_t)2 * m->V * 4, st>>>(m->probs + (size_t)t0 * m->B * m->V, m->sym_dev,
@@ -2016,16 +2036,21 @@ int nncu_coder_trees(nncu_model *m, int t0, int nt, uint16_t *tree_host)
 {
     if (!m || !tree_host || t0 < 0 || nt < 1 || t0 + nt > m->T)
         return nncu_fail(NNCU_ERR_INVALID, "bad coder range");
-    int nb = coder_bits(m->V);
-    if (nb < 1)
-        return nncu_fail(NNCU_ERR_INVALID, "coder-ready output needs a power-of-two n_symbols");
-    if ((size_t)2 * m->V * 4 > 200 * 1024)
-        return nncu_fail(NNCU_ERR_RANGE, "n_symbols %d is beyond the 25600-symbol limit of the coder kernels", m->V);
+    const bool pow2 = coder_bits(m->V) >= 1;
+    const int P = 1 << coder_depth(m->V);
+    if (m->V < 2)
+        return nncu_fail(NNCU_ERR_INVALID, "coder-ready output needs at least two symbols");
+    if ((size_t)2 * P * 4 > 200 * 1024)
+        return nncu_fail(NNCU_ERR_RANGE, "n_symbols %d is beyond the limit of the coder kernels (16384; 25600 for a power of two)", m->V);
     CUDA_TRY(cudaSetDevice(m->device));
     int rows = nt * m->B;
-    coder_trees_kernel<<<rows, 256, (size_t)2 * m->V * 4, m->st>>>(m->probs + (size_t)t0 * m->B * m->V, m->coder_dev, m->V);
+    if (pow2)
+        coder_trees_kernel<<<rows, 256, (size_t)2 * m->V * 4, m->st>>>(m->probs + (size_t)t0 * m->B * m->V, m->coder_dev, m->V);
+    else
+        coder_trees_any_kernel<<<rows, 256, (size_t)2 * P * 4, m->st>>>(m->probs + (size_t)t0 * m->B * m->V, m->coder_dev,
+                                                                       m->V, P);
     KERNEL_CHECK();
-    CUDA_TRY(cudaMemcpyAsync(tree_host, m->coder_dev, sizeof(uint16_t) * (size_t)rows * m->V, cudaMemcpyDeviceToHost, m->st));
+    CUDA_TRY(cudaMemcpyAsync(tree_host, m->coder_dev, sizeof(uint16_t) * (size_t)rows * P, cudaMemcpyDeviceToHost, m->st));
     CUDA_TRY(cudaStreamSynchronize(m->st));
     return NNCU_OK;
 }

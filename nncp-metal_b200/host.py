@@ -99,6 +99,11 @@ def library():
         L.nch_read_sym_tree.argtypes = [_vp, _vp, _I]
         L.nch_write_sym_paths.argtypes = [_vp, _vp, _I, _vp, C.c_size_t]
         L.nch_write_sym_paths.restype = None
+        L.nch_write_sym_path_any.argtypes = [_vp, _vp, _I, _I]
+        L.nch_write_sym_path_any.restype = None
+        L.nch_write_sym_paths_any.argtypes = [_vp, _vp, _I, _vp, C.c_size_t]
+        L.nch_write_sym_paths_any.restype = None
+        L.nch_tree_depth.argtypes = [_I]
         L.nch_read_sym_trees.argtypes = [_vp, _vp, _I, C.c_size_t, _vp]
         L.nch_read_sym_trees.restype = None
         L.nch_next_block_len.argtypes = [C.POINTER(FileParams), C.c_size_t, C.c_size_t]

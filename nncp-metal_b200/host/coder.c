@@ -223,23 +223,62 @@ void nch_write_sym_path(nch_enc *e, const uint16_t *prob0, int n_bits, int sym)
         nch_enc_put_bit(e, prob0[k], (sym >> (n_bits - 1 - k)) & 1);
 }
 
-int nch_read_sym_tree(nch_dec *d, const uint16_t *tree, int n_symb)
+/* write_sym's walk over any alphabet: the node covering [lo, lo + n) sends n >> 1 symbols left */
+void nch_write_sym_path_any(nch_enc *e, const uint16_t *prob0, int n_symb, int sym)
 {
-    int k = 1;
-    while (k < n_symb)
-        k = 2 * k + nch_dec_get_bit(d, tree[k]);
-    return k - n_symb;
+    int lo = 0, n = n_symb, k = 0;
+    while (n > 1) {
+        const int h = n >> 1, right = sym >= lo + h;
+        nch_enc_put_bit(e, prob0[k++], right);
+        if (right) {
+            lo += h;
+            n -= h;
+        } else {
+            n = h;
+        }
+    }
 }
 
-/* n symbols in a row, as a rank that codes for every rank of a sharded job does after the gather */
+int nch_read_sym_tree(nch_dec *d, const uint16_t *tree, int n_symb)
+{
+    int lo = 0, n = n_symb, k = 1;
+    while (n > 1) {
+        const int h = n >> 1, right = nch_dec_get_bit(d, tree[k]);
+        k = 2 * k + right;
+        if (right) {
+            lo += h;
+            n -= h;
+        } else {
+            n = h;
+        }
+    }
+    return lo;
+}
+
+int nch_tree_depth(int n_symb)
+{
+    int d = 0;
+    while ((1 << d) < n_symb)
+        d++;
+    return d;
+}
+
 void nch_write_sym_paths(nch_enc *e, const uint16_t *prob0, int n_bits, const int32_t *sym, size_t n)
 {
     for (size_t i = 0; i < n; i++)
         nch_write_sym_path(e, prob0 + i * (size_t)n_bits, n_bits, sym[i]);
 }
 
+void nch_write_sym_paths_any(nch_enc *e, const uint16_t *prob0, int n_symb, const int32_t *sym, size_t n)
+{
+    const size_t stride = (size_t)nch_tree_depth(n_symb);
+    for (size_t i = 0; i < n; i++)
+        nch_write_sym_path_any(e, prob0 + i * stride, n_symb, sym[i]);
+}
+
 void nch_read_sym_trees(nch_dec *d, const uint16_t *trees, int n_symb, size_t n, int32_t *sym_out)
 {
+    const size_t stride = (size_t)1 << nch_tree_depth(n_symb);
     for (size_t i = 0; i < n; i++)
-        sym_out[i] = nch_read_sym_tree(d, trees + i * (size_t)n_symb, n_symb);
+        sym_out[i] = nch_read_sym_tree(d, trees + i * stride, n_symb);
 }

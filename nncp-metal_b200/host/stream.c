@@ -94,7 +94,7 @@ static int code_rows(coder_io *io, uint16_t *buf, int stride, int rem, int base_
                 int tt = t0 + t, c = io->syms[t * B + b];
                 if (tt < limit_t || (tt == limit_t && b < limit_b)) {
                     if (io->out_mode == NCH_OUT_CODER_READY)
-                        nch_write_sym_path(io->enc, io->coded + (size_t)(t * B + b) * io->n_bits, io->n_bits, c);
+                        nch_write_sym_path_any(io->enc, io->coded + (size_t)(t * B + b) * io->n_bits, V, c);
                     else
                         nch_write_sym(io->enc, io->probs + (size_t)(t * B + b) * V, V, c);
                 }
@@ -113,7 +113,7 @@ static int code_rows(coder_io *io, uint16_t *buf, int stride, int rem, int base_
                 int tt = t0 + t, c = 0;
                 if (tt < limit_t || (tt == limit_t && b < limit_b)) {
                     if (io->out_mode == NCH_OUT_CODER_READY)
-                        c = nch_read_sym_tree(io->dec, io->coded + (size_t)(t * B + b) * V, V);
+                        c = nch_read_sym_tree(io->dec, io->coded + ((size_t)(t * B + b) << nch_tree_depth(V)), V);
                     else
                         c = nch_read_sym(io->dec, io->probs + (size_t)(t * B + b) * V, V);
                     nch_put_symb(buf, stride, rem, b, base_pos + tt, c);
@@ -136,7 +136,7 @@ int nch_process_block(const nch_model_ops *m, nch_enc *enc, nch_dec *dec, uint16
         eval_mode = NCH_EVAL_STEP; /* the next input is the symbol just decoded */
     if (out_mode == NCH_OUT_DEVICE)
         out_mode = NCH_OUT_CODER_READY; /* the device decoder is nch_decompress's; here the walk is the host's */
-    if (out_mode == NCH_OUT_CODER_READY && (log2_exact(V) < 1 || !m->coder_paths || !m->coder_trees))
+    if (out_mode == NCH_OUT_CODER_READY && (V < 2 || !m->coder_paths || !m->coder_trees))
         out_mode = NCH_OUT_FLOAT;
     const int stride = block_len / B, rem = block_len % B;
     coder_io io;
@@ -147,7 +147,7 @@ int nch_process_block(const nch_model_ops *m, nch_enc *enc, nch_dec *dec, uint16
     int32_t *expected = (int32_t *)calloc((size_t)T * B, sizeof(int32_t));
     io.syms = (int32_t *)calloc((size_t)rows, sizeof(int32_t));
     if (out_mode == NCH_OUT_CODER_READY)
-        io.coded = (uint16_t *)malloc(sizeof(uint16_t) * (size_t)rows * (enc ? 32 : V));
+        io.coded = (uint16_t *)malloc(sizeof(uint16_t) * (size_t)rows * (enc ? 32 : (size_t)1 << nch_tree_depth(V)));
     else
         io.probs = (float *)malloc(sizeof(float) * (size_t)rows * V);
     int rc = NCH_OK;
@@ -193,7 +193,8 @@ int nch_process_block(const nch_model_ops *m, nch_enc *enc, nch_dec *dec, uint16
             }
             int nbits = 0;
             if (m->coder_paths_end(m->ctx, io.coded, &nbits)) { rc = NCH_ERR_MODEL; break; }
-            nch_write_sym_paths(enc, io.coded, nbits, expected, (size_t)T * B);
+            if (nbits != nch_tree_depth(V)) { rc = NCH_ERR_MODEL; break; }
+            nch_write_sym_paths_any(enc, io.coded, V, expected, (size_t)T * B);
             float loss = 0.0f;
             if (m->read_loss(m->ctx, &loss)) { rc = NCH_ERR_MODEL; break; }
             (*train_step)++;

@@ -174,7 +174,8 @@ class TrfModel:
         return tmp[: nt * self.B * nb.value].reshape(nt * self.B, nb.value).copy()
 
     def coder_trees(self, t0, nt):
-        out = np.zeros((nt * self.B, self.V), np.uint16)
+        """prob0 of every tree node, heap order: [nt * B][2^ceil(log2 V)]"""
+        out = np.zeros((nt * self.B, 1 << (self.V - 1).bit_length()), np.uint16)
         self._ck(self.lib.nncu_coder_trees(self.h, t0, nt, _ptr(out)))
         return out
 

@@ -240,3 +240,30 @@ int orc_sym_path(const float *prob, int n_symb, int sym, uint16_t *prob0_out)
     }
     return k;
 }
+
+/* Every node's prob0 in heap order (root 1, children 2k and 2k+1; the node covering n symbols
+   sends n >> 1 of them left, as write_sym does): what read_sym would hand get_bit at that node.
+   tree_out has 1 << ceil(log2 n_symb) entries; entry 0 and the slots of one-symbol nodes stay 0. */
+static void sym_tree_node(const float *prob, int start, int range, float p, unsigned k, uint16_t *tree_out)
+{
+    if (range <= 1)
+        return;
+    int half = range >> 1;
+    float p0 = orc_vec_sum_f32(prob + start, half);
+    int prob0 = (int)lrintf(p0 * PROB_ONE / p);
+    if (prob0 < 1) prob0 = 1;
+    if (prob0 > PROB_ONE - 1) prob0 = PROB_ONE - 1;
+    tree_out[k] = (uint16_t)prob0;
+    sym_tree_node(prob, start, half, p0, 2 * k, tree_out);
+    sym_tree_node(prob, start + half, range - half, p - p0, 2 * k + 1, tree_out);
+}
+
+int orc_sym_tree(const float *prob, int n_symb, uint16_t *tree_out)
+{
+    int depth = 0;
+    while ((1 << depth) < n_symb)
+        depth++;
+    memset(tree_out, 0, sizeof(uint16_t) << depth);
+    sym_tree_node(prob, 0, n_symb, 1.0f, 1, tree_out);
+    return 1 << depth;
+}

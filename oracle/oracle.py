@@ -95,6 +95,7 @@ def lib():
         L.orc_dec_free.argtypes = [_vp]
         L.orc_dec_free.restype = None
         L.orc_sym_path.argtypes = [_vp, _i, _i, _vp]
+        L.orc_sym_tree.argtypes = [_vp, _i, _vp]
         L.orc_set_threads.argtypes = [_i]
         L.orc_set_threads.restype = _i
         L.orc_get_threads.restype = _i
@@ -259,6 +260,15 @@ class Decoder:
         if self.h:
             getattr(self.L, self.pre + "_dec_free")(self.h)
             self.h = None
+
+
+def sym_tree(prob):
+    """prob0 of every node of the coder's tree over this row, heap order, 2^ceil(log2 V) entries."""
+    prob = np.ascontiguousarray(prob, np.float32)
+    depth = int(np.ceil(np.log2(prob.size)))
+    out = np.zeros(1 << depth, np.uint16)
+    lib().orc_sym_tree(_ptr(prob), prob.size, _ptr(out))
+    return out
 
 
 def sym_path(prob, sym):

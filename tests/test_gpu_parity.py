@@ -526,6 +526,32 @@ def test_coder_paths_large_alphabets_match_the_coder_oracle(pkg, oracle, V):
     m.close()
 
 
+@pytest.mark.parametrize("V", [24, 288, 1000, 5000])
+def test_coder_paths_and_trees_of_any_alphabet_match_the_coder_oracle(pkg, oracle, V):
+    """Alphabets that are not a power of two (what a word dictionary gives): write_sym's tree is then
+    uneven, leaves at depth L-1 and L.  Paths (L entries a row, the last 0 for a leaf one level up) and
+    trees (2^L entries a row, heap order) against the oracle's restatement of write_sym / read_sym."""
+    p = pkg.abi.make_params(n_layer=1, d_model=64, n_head=2, d_key=32, d_inner=128, d_pos=16, mem_len=8,
+                            seg_len=8, n_streams=4, n_symbols=V, init_range=0.5)
+    m = pkg.TrfModel(p)
+    rng = np.random.default_rng(V)
+    ids = rng.integers(0, V, (8, 4)).astype(np.int32)
+    syms = rng.integers(0, V, (8, 4)).astype(np.int32)
+    syms[0, :] = [0, V - 1, V // 2, V // 2 - 1]
+    probs = m.eval(-1, ids)
+    paths = m.coder_paths(0, 8, syms)
+    trees = m.coder_trees(0, 8)
+    L = (V - 1).bit_length()
+    assert paths.shape == (32, L) and trees.shape == (32, 1 << L)
+    for t in range(8):
+        for b in range(4):
+            row = t * 4 + b
+            want = oracle.sym_path(probs[t, b], syms[t, b])
+            assert np.array_equal(paths[row, :len(want)], want) and not paths[row, len(want):].any(), (t, b)
+            assert np.array_equal(trees[row], oracle.sym_tree(probs[t, b])), (t, b)
+    m.close()
+
+
 # ---------------------------------------------------------------- full-size properties
 
 @pytest.mark.parametrize("streams", [32, 8, 4])

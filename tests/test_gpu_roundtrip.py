@@ -139,10 +139,13 @@ def test_device_decoder_graphs_survive_a_larger_second_payload(pkg):
     ref.close()
 
 
-def test_coder_ready_and_float_output_give_the_same_file(pkg):
+@pytest.mark.parametrize("V", [256, 296])
+def test_coder_ready_and_float_output_give_the_same_file(pkg, V):
+    """296: an alphabet that is not a power of two (a word dictionary's), coded from the integer
+    paths and trees of the uneven tree; out_mode 2 has no device decoder for it and falls back."""
     kw, n, block_len = CASES["fp32_bytes"]
-    p = pkg.abi.make_params(**kw)
-    syms = _markov_source(700, 256, 6)
+    p = pkg.abi.make_params(**dict(kw, n_symbols=V))
+    syms = _markov_source(700, V, 6)
     fp = pkg.host.file_params(p, block_len=block_len)
     outs = []
     for eval_mode, out_mode in ((1, 1), (1, 0), (0, 1)):
@@ -150,6 +153,11 @@ def test_coder_ready_and_float_output_give_the_same_file(pkg):
         outs.append(pkg.host.compress(ops, fp, syms, eval_mode, out_mode)[0])
         pkg.host.unbind_cuda(ops)
     assert outs[0] == outs[1] == outs[2]
+    for out_mode in (1, 2):
+        ops = pkg.host.bind_cuda(p)
+        back = pkg.host.decompress(ops, outs[0], out_mode)
+        pkg.host.unbind_cuda(ops)
+        assert np.array_equal(back, syms)
 
 
 def test_model_learns_the_source(pkg):

@@ -238,29 +238,35 @@ def _oracle_ops(pkg, model, with_decoder=False, with_encoder_order=False):
         # ops of the encoder order; the log records the order in which the block loop calls the model
         st2 = {}
         log = keep.setdefault("log", [])
+        depth = int(np.ceil(np.log2(V)))
+
+        def padded_path(row, sym):
+            """depth entries per row, as the device writes them: a leaf one level up leaves the last 0"""
+            out = np.zeros(depth, np.uint16)
+            q = orc.sym_path(row, sym)
+            out[:len(q)] = q
+            return out
 
         def paths(ctx, t0, nt, sym, out, nbp):
             pr = np.ctypeslib.as_array(model.L.orc_probs(model.h), shape=(T * B * V,)).reshape(T * B, V)
             sy = np.ctypeslib.as_array(sym, shape=(nt * B,))
-            rows = [orc.sym_path(pr[t0 * B + i], int(sy[i])) for i in range(nt * B)]
-            nb = len(rows[0])
-            flat = np.concatenate(rows).astype(np.uint16)
+            flat = np.concatenate([padded_path(pr[t0 * B + i], int(sy[i])) for i in range(nt * B)])
             C.memmove(out, flat.ctypes.data, flat.nbytes)
-            nbp[0] = nb
+            nbp[0] = depth
             return 0
 
         def pbegin(ctx, t0, nt, sym):
             log.append("paths_begin")
             sy = np.ctypeslib.as_array(sym, shape=(nt * B,)).copy()
             pr = np.ctypeslib.as_array(model.L.orc_probs(model.h), shape=(T * B * V,)).reshape(T * B, V)
-            st2["rows"] = [orc.sym_path(pr[t0 * B + i], int(sy[i])) for i in range(nt * B)]   # computed now: the
+            st2["rows"] = [padded_path(pr[t0 * B + i], int(sy[i])) for i in range(nt * B)]   # computed now: the
             return 0                                                       # next forward pass overwrites the tables
 
         def pend(ctx, out, nbp):
             log.append("paths_end")
             flat = np.concatenate(st2["rows"]).astype(np.uint16)
             C.memmove(out, flat.ctypes.data, flat.nbytes)
-            nbp[0] = len(st2["rows"][0])
+            nbp[0] = depth
             return 0
 
         def gqueue(ctx, exp):
@@ -279,7 +285,10 @@ def _oracle_ops(pkg, model, with_decoder=False, with_encoder_order=False):
             return ev(ctx, oi, inp)
 
         def trees(ctx, t0, nt, out):
-            return 1   # an encoder never asks for trees
+            pr = np.ctypeslib.as_array(model.L.orc_probs(model.h), shape=(T * B * V,)).reshape(T * B, V)
+            flat = np.concatenate([orc.sym_tree(pr[t0 * B + i]) for i in range(nt * B)])
+            C.memmove(out, flat.ctypes.data, flat.nbytes)
+            return 0
 
         keep["enc"] = [H.FN_PATHS(paths), H.FN_TREES(trees), H.FN_PATHS_BEGIN(pbegin), H.FN_PATHS_END(pend),
                        H.FN_GRAD_QUEUE(gqueue), H.FN_READ_LOSS(rloss), H.FN_EVAL(ev_logged)]
@@ -319,6 +328,27 @@ def test_block_loop_round_trip_with_oracle_model(pkg, n_sym, block_len):
         # the model learns the cycle: fewer bits than the 4 bits/symbol of a uniform coder
         hdr = len(pkg.host.header_bytes(fp, n_sym))
         assert (len(data) - hdr) * 8 < 0.8 * 4 * n_sym
+
+
+@pytest.mark.parametrize("V", [16, 24, 21, 3])
+def test_coder_ready_walks_serve_any_alphabet(pkg, V):
+    """Integer prob0 paths (encode) and trees (decode) in place of the float tables, for alphabets
+    that are and are not a power of two (a word dictionary gives (entries + 7) & ~7 symbols): the
+    same bytes as write_sym on the float tables, and read_sym_tree brings the symbols back."""
+    cfg, z = load_golden("post_gelu")
+    p = params_from_cfg(pkg, cfg, n_streams=2, seg_len=4, lr=1e-2, n_symbols=V)
+    rng = np.random.default_rng(V)
+    syms = np.array([(3 * i) % min(V, 5) if rng.random() < 0.8 else rng.integers(0, V) for i in range(91)], np.uint16)
+    syms[:3] = [0, V - 1, V // 2]
+    fp = pkg.host.file_params(p, block_len=40)
+    H = pkg.host
+    plain, _ = H.compress(_oracle_ops(pkg, orc.OracleModel(p)), fp, syms, H.EVAL_SEGMENT, H.OUT_FLOAT)
+    for mode in (H.EVAL_SEGMENT, H.EVAL_STEP):
+        ready, _ = H.compress(_oracle_ops(pkg, orc.OracleModel(p), with_encoder_order=True), fp, syms, mode,
+                              H.OUT_CODER_READY)
+        assert ready == plain
+    back = H.decompress(_oracle_ops(pkg, orc.OracleModel(p), with_encoder_order=True), plain, H.OUT_CODER_READY)
+    assert np.array_equal(back, syms)
 
 
 def test_encoder_order_block_loop_gives_the_same_bytes(pkg):
