@@ -2086,11 +2086,10 @@ int nncu_decoder_begin(nncu_model *m, const uint8_t *payload_host, size_t len)
 {
     if (!m || (!payload_host && len))
         return nncu_fail(NNCU_ERR_INVALID, "null argument");
-    const int nb = coder_bits(m->V);
-    if (nb < 1)
-        return nncu_fail(NNCU_ERR_INVALID, "the device decoder needs a power-of-two n_symbols");
-    const int ring = dec::ring_slots(m->B, m->V, nb);
-    if (ring < 2 || (size_t)2 * m->V * 4 > 200 * 1024)
+    const bool pow2 = coder_bits(m->V) >= 1;
+    const int nb = coder_depth(m->V), P = 1 << nb; // a tree row has P entries (P = V for a power of two)
+    const int ring = dec::ring_slots(m->B, P, nb);
+    if (ring < 2 || (size_t)2 * P * 4 > 200 * 1024)
         return nncu_fail(NNCU_ERR_RANGE, "n_symbols %d with %d streams does not fit the decoder's shared memory", m->V, m->B);
     CUDA_TRY(cudaSetDevice(m->device));
     CUDA_TRY(cudaStreamSynchronize(m->st));
@@ -2125,8 +2124,8 @@ int nncu_decoder_begin(nncu_model *m, const uint8_t *payload_host, size_t len)
     s0.range = dec::R_TOP;
     CUDA_TRY(cudaMemcpyAsync(m->dec_state, &s0, sizeof(s0), cudaMemcpyHostToDevice, m->st));
     CUDA_TRY(cudaStreamSynchronize(m->st));
-    CUDA_TRY(cudaFuncSetAttribute(dec::decode_step_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                  (int)dec::smem_bytes(m->B, m->V, nb, ring)));
+    CUDA_TRY(cudaFuncSetAttribute(pow2 ? dec::decode_step_kernel<false> : dec::decode_step_kernel<true>,
+                                  cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dec::smem_bytes(m->B, P, nb, ring)));
     m->dec_ring = ring;
     m->dec_open = true;
     if (m->step_graphs.empty())
@@ -2138,14 +2137,20 @@ int nncu_decoder_begin(nncu_model *m, const uint8_t *payload_host, size_t len)
 // turns them into symbols (left in the target rows and, for t+1 < seg_len, the next step's input)
 static int decode_step(nncu_model *m, int t, int limit_t, int limit_b)
 {
-    const int B = m->B, V = m->V, nb = coder_bits(V);
+    const int B = m->B, V = m->V, nb = coder_depth(V), P = 1 << nb;
+    const bool pow2 = P == V;
     NNCU_TRY(m->bf ? forward_range<bf16>(m, t, t + 1) : forward_range<float>(m, t, t + 1));
-    launch_k(coder_trees_kernel, dim3(B), dim3(256), (size_t)2 * V * 4, m->st, (const float *)(m->probs + (size_t)t * B * V),
-             m->coder_dev, V);
+    if (pow2)
+        launch_k(coder_trees_kernel, dim3(B), dim3(256), (size_t)2 * V * 4, m->st,
+                 (const float *)(m->probs + (size_t)t * B * V), m->coder_dev, V);
+    else
+        launch_k(coder_trees_any_kernel, dim3(B), dim3(256), (size_t)2 * P * 4, m->st,
+                 (const float *)(m->probs + (size_t)t * B * V), m->coder_dev, V, P);
     KERNEL_CHECK();
-    launch_k(dec::decode_step_kernel, dim3(1), dim3(32), dec::smem_bytes(B, V, nb, m->dec_ring), m->st,
-             (const uint16_t *)m->coder_dev, (const uint8_t *)m->dec_payload, m->dec_state, m->tgt_dev + (size_t)t * B,
-             t + 1 < m->T ? m->ids_dev + (size_t)(t + 1) * B : (int32_t *)nullptr, t, limit_t, limit_b, B, V, nb,
+    launch_k(pow2 ? dec::decode_step_kernel<false> : dec::decode_step_kernel<true>, dim3(1), dim3(32),
+             dec::smem_bytes(B, P, nb, m->dec_ring), m->st, (const uint16_t *)m->coder_dev,
+             (const uint8_t *)m->dec_payload, m->dec_state, m->tgt_dev + (size_t)t * B,
+             t + 1 < m->T ? m->ids_dev + (size_t)(t + 1) * B : (int32_t *)nullptr, t, limit_t, limit_b, B, V, P, nb,
              m->dec_ring, m->err_flag);
     KERNEL_CHECK();
     return NNCU_OK;

@@ -58,17 +58,9 @@ typedef struct {
     nch_dec *dec;
     int out_mode, n_bits;
     float *probs;      /* [rows][V]   (float mode) */
-    uint16_t *coded;   /* paths [rows][n_bits] or trees [rows][V] */
+    uint16_t *coded;   /* paths [rows][n_bits] or trees [rows][1 << depth] */
     int32_t *syms;     /* [rows] */
 } coder_io;
-
-static int log2_exact(int v)
-{
-    int n = 0;
-    while ((1 << n) < v)
-        n++;
-    return (1 << n) == v ? n : -1;
-}
 
 /* codes (or decodes) rows [t0, t0+nt) x streams; `limit_t`/`limit_b`: positions at
    t == limit_t with stream >= limit_b, and all t > limit_t, are skipped (block tail). */
@@ -664,7 +656,7 @@ int nch_decompress(const nch_model_ops *m, const nch_file_params *fp, const uint
     size_t pos = 0, total = n_symbols_in_file;
     if (out_mode == NCH_OUT_DEVICE) {
         /* a model without a device decoder, or one that refuses this geometry, decodes on the host */
-        if (m->decoder_begin && m->decode_steps && m->decoder_end && log2_exact(m->n_symbols) >= 1 &&
+        if (m->decoder_begin && m->decode_steps && m->decoder_end && m->n_symbols >= 2 &&
             m->decoder_begin(m->ctx, payload, n) == 0) {
             while (pos < total) {
                 int bl = nch_next_block_len(fp, pos, total - pos);

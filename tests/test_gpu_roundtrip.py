@@ -51,16 +51,18 @@ def test_round_trip_is_bit_exact(pkg, name, out_mode):
     assert np.array_equal(back, syms)
 
 
-def test_device_decoder_steps_match_the_host_walk(pkg):
-    """nncu_decode_steps against nch_read_sym_tree over nncu_coder_trees, step by step on two models
+@pytest.mark.parametrize("V", [512, 296, 1000])
+def test_device_decoder_steps_match_the_host_walk(pkg, V):
+    """296, 1000: alphabets that are not a power of two (the uneven tree of write_sym).
+    nncu_decode_steps against nch_read_sym_tree over nncu_coder_trees, step by step on two models
     with identical weights: the same symbols, and the same number of payload bytes consumed.  The
     payload is random bytes (any byte string decodes to something), the second call starts in the
     middle of a segment, and the last one has a ragged limit."""
     import ctypes as C
     kw = dict(n_layer=1, d_model=64, n_head=2, d_key=32, d_inner=128, d_pos=24, mem_len=16, seg_len=8,
-              n_streams=5, n_symbols=512, use_bf16=0, lr=2e-3, init_range=0.05)
+              n_streams=5, n_symbols=V, use_bf16=0, lr=2e-3, init_range=0.05)
     p = pkg.abi.make_params(**kw)
-    T, B, V = 8, 5, 512
+    T, B = 8, 5
     rng = np.random.default_rng(11)
     payload = rng.integers(0, 256, 4000, dtype=np.uint8).tobytes()
     L = pkg.host.library()
@@ -142,7 +144,7 @@ def test_device_decoder_graphs_survive_a_larger_second_payload(pkg):
 @pytest.mark.parametrize("V", [256, 296])
 def test_coder_ready_and_float_output_give_the_same_file(pkg, V):
     """296: an alphabet that is not a power of two (a word dictionary's), coded from the integer
-    paths and trees of the uneven tree; out_mode 2 has no device decoder for it and falls back."""
+    paths and trees of the uneven tree; out_mode 2 walks that tree in the device decoder."""
     kw, n, block_len = CASES["fp32_bytes"]
     p = pkg.abi.make_params(**dict(kw, n_symbols=V))
     syms = _markov_source(700, V, 6)
