@@ -198,7 +198,7 @@ size_t nncpm_lossless_decompress(const uint8_t *in, size_t n, uint8_t *out, size
     uint32_t nsym = 0;
     size_t used = 0;
     if (nch_read_header(stream, slen, &fp, &nsym, &used) != NCH_OK || nsym != h.original_size ||
-        fp.model.n_symbols != 256) {
+        fp.model.n_symbols != 256 || fp.dict_len != 0) { /* this container holds bytes, never tokenised text */
         set_err("bad inner stream header");
         return 0;
     }
