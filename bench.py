@@ -20,6 +20,8 @@ streams are sharded across ranks and gradients are summed by NCCL all-reduces in
           min(tensor, HBM) roofline.
 `cpu_baseline` the CPU oracle (port of nncp.c's graph, OpenMP) timed on a bounded sample.
 
+  python bench.py --mode words     the word tokenizer (host code, no GPU) beside the reference's tool
+
 The K-step timed region is measured REPEATS times in the same process (each bracketed by a
 barrier and a synchronize, CUDA events, max over ranks); `value` is the median, `value_min` /
 `value_max` the spread.
@@ -390,6 +392,61 @@ def run_decode(args, c, name):
     print(json.dumps(line), flush=True)
 
 
+def synth_prose(n_tokens, vocab=5000, seed=9):
+    """Word soup with a Zipf law over `vocab` random lower-case words, capitals, all-caps, punctuation,
+    doubled spaces and line ends: the shapes the case/space folding and the dictionary work on."""
+    rng = np.random.default_rng(seed)
+    words = [bytes(rng.integers(97, 123, rng.integers(1, 9)).astype(np.uint8)) for _ in range(vocab)]
+    gaps = [b" ", b" ", b" ", b" ", b", ", b".\n", b"  ", b" (", b") ", b"-", b"", b"; "]
+    pick, gap, style = rng.zipf(1.4, n_tokens) % vocab, rng.integers(0, len(gaps), n_tokens), rng.random(n_tokens)
+    out = []
+    for i in range(n_tokens):
+        w = words[pick[i]]
+        out += [w.capitalize() if style[i] < 0.12 else w.upper() if style[i] < 0.16 else w, gaps[gap[i]]]
+    return b"".join(out)
+
+
+def run_words(args):
+    """The host pass in front of the model when text preprocessing is on: nch_words_encode (the
+    restatement of the reference's word_encode) on synthetic prose, host cores only, with the
+    reference's own stand-alone preprocessor timed on the same text where oracle/_ref holds it."""
+    pkg = entry._package()
+    H = pkg.host
+    text = synth_prose(1_000_000)
+    n_words, min_freq = 4096, 16
+    times = []
+    for _ in range(max(1, min(args.steps, 5))):
+        t0 = time.perf_counter()
+        d, syms, entries = H.words_encode(text, n_words, min_freq)
+        times.append(time.perf_counter() - t0)
+    t_enc = statistics.median(times)
+    t0 = time.perf_counter()
+    back = H.words_decode(d, syms)
+    t_dec = time.perf_counter() - t0
+    base = None
+    from oracle import oracle as orc
+    exe = orc.preprocess_ref()
+    if exe and not args.no_cpu_baseline:
+        import tempfile
+        with tempfile.TemporaryDirectory() as td:
+            f = {k: os.path.join(td, k) for k in ("in", "dict", "sym")}
+            open(f["in"], "wb").write(text)
+            t0 = time.perf_counter()
+            subprocess.run([exe, "c", f["dict"], f["in"], f["sym"], str(n_words), str(min_freq)], check=True,
+                           capture_output=True, timeout=600)
+            t_ref = time.perf_counter() - t0
+            same = open(f["dict"], "rb").read() == d and open(f["sym"], "rb").read() == syms.astype(">u2").tobytes()
+        base = {"value": len(text) / t_ref, "unit": "bytes/s", "cores": 1, "kind": "reference",
+                "sample": "the same text through the reference's stand-alone preprocess tool (file to file)",
+                "same_output": bool(same)}
+    print(json.dumps({"metric": "tokenizer_text_bytes_per_second", "value": len(text) / t_enc, "unit": "bytes/s",
+                      "n_gpus": 0, "steps": len(times), "higher_is_better": True, "dtype": "u16", "data": "synthetic",
+                      "config": {"workload": f"word tokenizer, {len(text)} bytes of synthetic prose, n_words {n_words}, "
+                                             f"min_freq {min_freq}", "entries": entries, "symbols": int(syms.size)},
+                      "symbols_per_second": syms.size / t_enc, "decode_bytes_per_second": len(text) / t_dec,
+                      "round_trip_exact": back == text, "cores": 1, "cpu_baseline": base}))
+
+
 def profile_traffic(kernel_md):
     """`traffic_bytes_per_launch: <number>` from a profile summary under profiles/ (ncu's
     dram__bytes_read.sum + dram__bytes_write.sum per launch), or None."""
@@ -491,12 +548,15 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200")
     ap.add_argument("--config", default=None, choices=sorted(CONFIGS), help="default: c2 (train), c4 (decode)")
-    ap.add_argument("--mode", default="train", choices=["train", "decode"])
+    ap.add_argument("--mode", default="train", choices=["train", "decode", "words"])
     ap.add_argument("--backend", type=int, default=0, help="0 auto, 1 SIMT, 2 tcgen05")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-attention", action="store_true", help="skip the config[1] attention record")
     ap.add_argument("--repeats", type=int, default=7, help="times the K-step region is measured (median reported)")
     args = ap.parse_args()
+    if args.mode == "words":
+        run_words(args)
+        return
     if args.config is None:
         args.config = "c4" if args.mode == "decode" else "c2"
     c = dict(CONFIGS[args.config])

@@ -19,6 +19,14 @@
  *   - decoding (preprocess.c:1051-1091, 1227-1323).
  * Where the reference leaves the order of equal keys to the C library's qsort, this file keeps
  * the order of first occurrence (a stable sort), which is what a merge-sort qsort gives it.
+ *
+ * The results are the reference's; the way to them is not.  The reference counts every pair of
+ * the buffer anew in each round.  Here the pair counts are made once and then follow each rewrite
+ * of the buffer (a substitution or an expansion changes the pairs inside it and the two across its
+ * borders), the symbol counts likewise; only candidates with a positive score are sorted, and the
+ * place of first occurrence, which only breaks ties between equal scores, is looked up for the
+ * tied candidates the selection actually reaches.  A round then costs two streaming passes over
+ * the buffer and table work in proportion to what changed.
  */
 #include <math.h>
 #include <stdint.h>
@@ -87,9 +95,14 @@ typedef struct {
     uint16_t *a, *b;
     uint32_t *freq;
     size_t n, cap;
-    uint32_t *slot; /* index + 1, 0 = free */
+    uint64_t *slot; /* the pair in the high half, index + 1 in the low half; 0 = free */
     size_t n_slots; /* power of two */
 } pairtab;
+
+static inline uint64_t slot_entry(uint16_t a, uint16_t b, size_t index)
+{
+    return (uint64_t)((uint32_t)a << 16 | b) << 32 | (uint32_t)(index + 1);
+}
 
 static size_t pair_hash(uint16_t a, uint16_t b, size_t n_slots)
 {
@@ -109,7 +122,7 @@ static void pt_free(pairtab *t)
 
 static int pt_rehash(pairtab *t, size_t n_slots)
 {
-    uint32_t *slot = calloc(n_slots, sizeof(*slot));
+    uint64_t *slot = calloc(n_slots, sizeof(*slot));
     if (!slot)
         return -1;
     free(t->slot);
@@ -119,7 +132,7 @@ static int pt_rehash(pairtab *t, size_t n_slots)
         size_t h = pair_hash(t->a[i], t->b[i], n_slots);
         while (slot[h])
             h = (h + 1) & (n_slots - 1);
-        slot[h] = (uint32_t)i + 1;
+        slot[h] = slot_entry(t->a[i], t->b[i], i);
     }
     return 0;
 }
@@ -129,36 +142,14 @@ static long pt_find(const pairtab *t, uint16_t a, uint16_t b)
     if (!t->n_slots)
         return -1;
     size_t h = pair_hash(a, b, t->n_slots);
-    while (t->slot[h]) {
-        const size_t i = t->slot[h] - 1;
-        if (t->a[i] == a && t->b[i] == b)
-            return (long)i;
+    const uint32_t key = (uint32_t)a << 16 | b;
+    uint64_t e;
+    while ((e = t->slot[h]) != 0) {
+        if ((uint32_t)(e >> 32) == key)
+            return (long)((uint32_t)e - 1);
         h = (h + 1) & (t->n_slots - 1);
     }
     return -1;
-}
-
-/* room for n entries up front, so that a table whose size is known roughly does not grow by doubling */
-static int pt_reserve(pairtab *t, size_t n)
-{
-    if (n <= t->cap)
-        return 0;
-    uint16_t *na = realloc(t->a, n * sizeof(*na));
-    if (na)
-        t->a = na;
-    uint16_t *nb = realloc(t->b, n * sizeof(*nb));
-    if (nb)
-        t->b = nb;
-    uint32_t *nf = realloc(t->freq, n * sizeof(*nf));
-    if (nf)
-        t->freq = nf;
-    if (!na || !nb || !nf)
-        return -1;
-    t->cap = n;
-    size_t slots = t->n_slots ? t->n_slots : 4096;
-    while (slots < 2 * n)
-        slots *= 2;
-    return slots != t->n_slots ? pt_rehash(t, slots) : 0;
 }
 
 /* index of the pair, appended with frequency 0 when new; -1: out of memory */
@@ -191,7 +182,7 @@ static long pt_get(pairtab *t, uint16_t a, uint16_t b)
     size_t h = pair_hash(a, b, t->n_slots);
     while (t->slot[h])
         h = (h + 1) & (t->n_slots - 1);
-    t->slot[h] = (uint32_t)i + 1;
+    t->slot[h] = slot_entry(a, b, (size_t)i);
     return i;
 }
 
@@ -348,9 +339,10 @@ static int fixed_log2(uint32_t n)
 
 typedef struct {
     pairtab words;             /* word k is symbol N_BYTES + k; freq 0: not in use */
+    pairtab pairs;             /* every pair of neighbours the buffer has held, with its count in the buffer now
+                                  (kept up to date by each rewrite of the buffer; entries that fell to 0 stay) */
     uint32_t byte_freq[N_BYTES];
     symvec buf;
-    size_t pairs_last_round; /* distinct pairs the last round counted: the next table starts that large */
 } builder;
 
 /* bits (x 1024) one occurrence of symbol c costs now; a word not in use costs its two halves */
@@ -378,6 +370,74 @@ static void count_symbols(builder *b)
     }
 }
 
+/* Counts the adjacent pairs of v[0..n) into t (once, for the folded text; from then on the counts
+   follow the rewrites). */
+static int count_pairs(const uint16_t *v, size_t n, pairtab *t)
+{
+    for (size_t i = 0; i + 1 < n; i++) {
+        const long k = pt_get(t, v[i], v[i + 1]);
+        if (k < 0)
+            return -1;
+        t->freq[k]++;
+    }
+    return 0;
+}
+
+/* A rewrite of the buffer goes through it once, left to right, in steps: some old symbols become
+   some new symbols.  The pair counts change only around the steps that change something: the pair
+   across the boundary to the previous step, and the pairs inside the step. */
+typedef struct {
+    builder *b;
+    int have_prev, prev_changed, bad;
+    uint16_t prev_old, prev_new; /* last symbol of the previous step, before and after */
+} rewrite;
+
+static void pair_gone(builder *b, uint16_t x, uint16_t y)
+{
+    const long k = pt_find(&b->pairs, x, y);
+    if (k >= 0 && b->pairs.freq[k])
+        b->pairs.freq[k]--;
+}
+
+static int pair_new(builder *b, uint16_t x, uint16_t y)
+{
+    const long k = pt_get(&b->pairs, x, y);
+    if (k < 0)
+        return -1;
+    b->pairs.freq[k]++;
+    return 0;
+}
+
+static void rewrite_step(rewrite *r, const uint16_t *old, int n_old, const uint16_t *now, int n_now, int changed)
+{
+    builder *b = r->b;
+    if (r->have_prev && (changed || r->prev_changed)) {
+        pair_gone(b, r->prev_old, old[0]);
+        r->bad |= pair_new(b, r->prev_new, now[0]);
+    }
+    if (changed) {
+        for (int t = 0; t + 1 < n_old; t++)
+            pair_gone(b, old[t], old[t + 1]);
+        for (int t = 0; t + 1 < n_now; t++)
+            r->bad |= pair_new(b, now[t], now[t + 1]);
+    }
+    r->prev_old = old[n_old - 1];
+    r->prev_new = now[n_now - 1];
+    r->prev_changed = changed;
+    r->have_prev = 1;
+}
+
+/* a symbol that stays as it is: nothing to do unless the step before changed something */
+static inline void rewrite_keep(rewrite *r, uint16_t c)
+{
+    if (r->prev_changed) {
+        rewrite_step(r, &c, 1, &c, 1, 0);
+    } else {
+        r->prev_old = r->prev_new = c;
+        r->have_prev = 1;
+    }
+}
+
 /* writes symbol c of an expansion, words out of use as their halves, counting what it writes */
 static int emit_counted(builder *b, uint32_t c, symvec *out)
 {
@@ -392,9 +452,9 @@ static int emit_counted(builder *b, uint32_t c, symvec *out)
     return sv_push(out, (uint16_t)c);
 }
 
-/* With the symbol counts of the buffer at hand (substitute_words leaves them): words seen fewer
-   than min_freq times go out of use and the buffer is rewritten without them, the counts following.
-   Returns the number of words that passed the threshold, or -1. */
+/* With the symbol counts of the buffer at hand (every rewrite keeps them): words seen fewer
+   than min_freq times go out of use and the buffer is rewritten without them, the symbol and pair
+   counts following.  Returns the number of words that passed the threshold, or -1. */
 static long prune_rare_words(builder *b, uint32_t min_freq)
 {
     size_t kept = 0, to_expand = 0;
@@ -413,15 +473,40 @@ static long prune_rare_words(builder *b, uint32_t min_freq)
     out.v = malloc(out.cap * sizeof(*out.v));
     if (!out.v)
         return -1;
+    rewrite rw = {b, 0, 0, 0, 0, 0};
     int bad = 0;
-    for (size_t i = 0; i < b->buf.n && !bad; i++) {
-        const uint32_t c = b->buf.v[i];
-        if (c >= N_BYTES && b->words.freq[c - N_BYTES] == 0)
+    const uint16_t *v = b->buf.v;
+    const size_t n = b->buf.n;
+    for (size_t i = 0; i < n && !bad;) {
+        size_t e = i; /* the stretch of symbols that stay moves as it is */
+        while (e < n && !(v[e] >= N_BYTES && b->words.freq[v[e] - N_BYTES] == 0))
+            e++;
+        if (e > i) {
+            rewrite_keep(&rw, v[i]);
+            rw.prev_old = rw.prev_new = v[e - 1];
+            if (out.n + (e - i) > out.cap) {
+                const size_t cap = out.n + (e - i) + (n - e) + (n - e) / 8 + 16;
+                uint16_t *grown = realloc(out.v, cap * sizeof(*grown));
+                if (!grown) {
+                    bad = 1;
+                    break;
+                }
+                out.v = grown;
+                out.cap = cap;
+            }
+            memcpy(out.v + out.n, v + i, (e - i) * sizeof(*v));
+            out.n += e - i;
+            i = e;
+        }
+        if (i < n) {
+            const uint16_t c = v[i++];
+            const size_t at = out.n;
             bad = emit_counted(b, b->words.a[c - N_BYTES], &out) | emit_counted(b, b->words.b[c - N_BYTES], &out);
-        else
-            bad = sv_push(&out, (uint16_t)c); /* counted already */
+            if (!bad)
+                rewrite_step(&rw, &c, 1, out.v + at, (int)(out.n - at), 1);
+        }
     }
-    if (bad) {
+    if (bad || rw.bad) {
         free(out.v);
         return -1;
     }
@@ -436,47 +521,96 @@ static int score_before(uint32_t x, uint32_t y, const void *ctx)
     return score[x] > score[y];
 }
 
-/* Counts the adjacent pairs of v[0..n) into cand, entries in order of first occurrence. */
-static int count_pairs(const uint16_t *v, size_t n, pairtab *cand)
+static int place_before(uint32_t x, uint32_t y, const void *ctx)
 {
-    for (size_t i = 0; i + 1 < n; i++) {
-        const long k = pt_get(cand, v[i], v[i + 1]);
-        if (k < 0)
-            return -1;
-        cand->freq[k]++;
+    const uint32_t *first_at = ctx;
+    return first_at[x] < first_at[y];
+}
+
+enum { NOT_TIED = 0xffffffffu, NOT_SEEN = 0xfffffffeu };
+
+/* order[lo..hi) is sorted by falling score and holds whole groups of equal scores.  Candidates with
+   equal scores have to come in the order in which their pairs first occur in the buffer (the
+   reference lists its candidates in that order and sorts them stably): one pass over the buffer
+   finds those places, for the tied candidates only, and stops when it has them all. */
+static int order_ties(const builder *b, uint32_t *order, size_t lo, size_t hi, const int64_t *score)
+{
+    const pairtab *p = &b->pairs;
+    size_t tied = 0;
+    for (size_t r = lo; r + 1 < hi; r++)
+        tied += score[order[r]] == score[order[r + 1]];
+    if (!tied)
+        return 0;
+    const size_t n_sym = N_BYTES + b->words.n;
+    uint32_t *first_at = malloc((p->n + 1) * sizeof(*first_at));
+    uint8_t *side = calloc(n_sym, 1);
+    if (!first_at || !side) {
+        free(first_at);
+        free(side);
+        return -1;
     }
-    return 0;
+    memset(first_at, 0xff, (p->n + 1) * sizeof(*first_at)); /* NOT_TIED */
+    size_t waiting = 0;
+    for (size_t r = lo; r < hi; r++) {
+        const int with_prev = r > lo && score[order[r]] == score[order[r - 1]];
+        const int with_next = r + 1 < hi && score[order[r]] == score[order[r + 1]];
+        if (with_prev || with_next) {
+            const uint32_t k = order[r];
+            first_at[k] = NOT_SEEN;
+            side[p->a[k]] |= 1;
+            side[p->b[k]] |= 2;
+            waiting++;
+        }
+    }
+    const uint16_t *v = b->buf.v;
+    for (size_t i = 0; i + 1 < b->buf.n && waiting; i++) {
+        if (!(side[v[i]] & 1) || !(side[v[i + 1]] & 2))
+            continue;
+        const long k = pt_find(p, v[i], v[i + 1]);
+        if (k >= 0 && first_at[k] == NOT_SEEN) {
+            first_at[k] = (uint32_t)i;
+            waiting--;
+        }
+    }
+    int bad = 0;
+    for (size_t r = lo; r < hi && !bad;) {
+        size_t e = r + 1;
+        while (e < hi && score[order[e]] == score[order[r]])
+            e++;
+        if (e - r > 1)
+            bad = stable_sort(order + r, e - r, place_before, first_at);
+        r = e;
+    }
+    free(first_at);
+    free(side);
+    return bad;
 }
 
 /* one round: adds up to `limit` new words to b->words.  Returns how many, or -1. */
 static long pick_words(builder *b, long limit, uint32_t min_freq)
 {
-    pairtab cand = {0};
+    const pairtab *cand = &b->pairs;
     int64_t *score = NULL;
     uint32_t *order = NULL;
     uint8_t *opens = NULL, *closes = NULL;
     long added = -1;
-    const uint16_t *v = b->buf.v;
     const uint32_t total = (uint32_t)b->buf.n;
 
-    if (pt_reserve(&cand, b->pairs_last_round) || count_pairs(v, b->buf.n, &cand))
-        goto done;
-    b->pairs_last_round = cand.n;
-    score = malloc((cand.n + 1) * sizeof(*score));
-    order = malloc((cand.n + 1) * sizeof(*order));
+    score = malloc((cand->n + 1) * sizeof(*score));
+    order = malloc((cand->n + 1) * sizeof(*order));
     const size_t n_sym = N_BYTES + b->words.n;
     opens = calloc(n_sym, 1);
     closes = calloc(n_sym, 1);
     if (!score || !order || !opens || !closes)
         goto done;
     /* the selection below stops at the first score that is not positive, so only the candidates
-       with a positive score need sorting; they keep their order of first occurrence among equals */
+       with a positive score need sorting */
     size_t n_pos = 0;
-    for (size_t k = 0; k < cand.n; k++) {
-        const int64_t f = cand.freq[k];
+    for (size_t k = 0; k < cand->n; k++) {
+        const int64_t f = cand->freq[k];
         if (f <= 1)
-            continue; /* a pair seen once saves nothing */
-        const int64_t as_two = (symbol_bits(b, cand.a[k], total) + symbol_bits(b, cand.b[k], total)) * f;
+            continue; /* a pair seen once (or no longer) saves nothing */
+        const int64_t as_two = (symbol_bits(b, cand->a[k], total) + symbol_bits(b, cand->b[k], total)) * f;
         const int64_t as_one = (-(int64_t)(fixed_log2((uint32_t)f) - fixed_log2(total)) + COST_PER_USE) * f + COST_PER_WORD;
         score[k] = as_two - as_one;
         if (score[k] > 0)
@@ -485,11 +619,23 @@ static long pick_words(builder *b, long limit, uint32_t min_freq)
     if (stable_sort(order, n_pos, score_before, score))
         goto done;
     added = 0;
+    size_t settled = 0; /* order[0..settled) has its ties in place; the selection rarely goes far */
     for (size_t r = 0; r < n_pos; r++) {
+        if (r >= settled) {
+            size_t hi = settled ? 2 * settled : 256;
+            hi = hi < n_pos ? hi : n_pos;
+            while (hi < n_pos && score[order[hi]] == score[order[hi - 1]])
+                hi++; /* whole groups only */
+            if (order_ties(b, order, settled, hi, score)) {
+                added = -1;
+                goto done;
+            }
+            settled = hi;
+        }
         const size_t k = order[r];
-        if (cand.freq[k] < min_freq)
+        if (cand->freq[k] < min_freq)
             break;
-        const uint16_t a = cand.a[k], c = cand.b[k];
+        const uint16_t a = cand->a[k], c = cand->b[k];
         if (closes[a] || opens[c])
             continue; /* would chain with a word already taken this round */
         opens[a] = 1;
@@ -510,45 +656,68 @@ done:
     free(order);
     free(opens);
     free(closes);
-    pt_free(&cand);
     return added;
 }
 
 /* every pair of the buffer that is a word (in use or not) becomes that word, greedily from the
-   left; the symbols of the new buffer are counted on the way */
+   left; the symbol and pair counts follow */
 static int substitute_words(builder *b)
 {
     uint16_t *v = b->buf.v;
     size_t n = b->buf.n, i = 0, j = 0;
-    /* most positions start no word: ask the table only where the two symbols can be the halves of one */
+    /* only a word whose pair occurs in the buffer can match, and most positions start none: the
+       table is asked only where the two symbols can be the halves of such a word */
     const size_t n_sym = N_BYTES + b->words.n;
     uint8_t *half = calloc(n_sym, 1);
     if (!half)
         return -1;
+    size_t active = 0;
     for (size_t k = 0; k < b->words.n; k++) {
-        half[b->words.a[k]] |= 1;
-        half[b->words.b[k]] |= 2;
+        const long at = pt_find(&b->pairs, b->words.a[k], b->words.b[k]);
+        if (at >= 0 && b->pairs.freq[at]) {
+            half[b->words.a[k]] |= 1;
+            half[b->words.b[k]] |= 2;
+            active++;
+        }
     }
-    memset(b->byte_freq, 0, sizeof(b->byte_freq));
-    memset(b->words.freq, 0, b->words.n * sizeof(*b->words.freq));
+    if (!active) {
+        free(half);
+        return 0;
+    }
+    rewrite rw = {b, 0, 0, 0, 0, 0};
     while (i < n) {
-        long k = i + 1 < n && (half[v[i]] & 1) && (half[v[i + 1]] & 2) ? pt_find(&b->words, v[i], v[i + 1]) : -1;
+        /* the stretch up to the next place where a word can start moves as it is */
+        size_t e = i;
+        while (e + 1 < n && !((half[v[e]] & 1) && (half[v[e + 1]] & 2)))
+            e++;
+        long k = e + 1 < n ? pt_find(&b->words, v[e], v[e + 1]) : -1;
+        if (k < 0)
+            e++; /* v[e] starts no word either (or is the last symbol) */
+        if (e > i) {
+            rewrite_keep(&rw, v[i]);
+            rw.prev_old = rw.prev_new = v[e - 1];
+            if (j != i)
+                memmove(v + j, v + i, (e - i) * sizeof(*v));
+            j += e - i;
+            i = e;
+        }
         if (k >= 0) {
+            const uint16_t w = (uint16_t)(N_BYTES + k);
+            rewrite_step(&rw, v + i, 2, &w, 1, 1); /* v[i], v[i + 1] are still the old symbols: j <= i */
+            for (int t = 0; t < 2; t++) {
+                if (v[i + t] < N_BYTES)
+                    b->byte_freq[v[i + t]]--;
+                else
+                    b->words.freq[v[i + t] - N_BYTES]--;
+            }
             b->words.freq[k]++;
-            v[j++] = (uint16_t)(N_BYTES + k);
+            v[j++] = w;
             i += 2;
-        } else {
-            const uint32_t c = v[i++];
-            if (c < N_BYTES)
-                b->byte_freq[c]++;
-            else
-                b->words.freq[c - N_BYTES]++;
-            v[j++] = (uint16_t)c;
         }
     }
     b->buf.n = j;
     free(half);
-    return 0;
+    return rw.bad ? -1 : 0;
 }
 
 /* the first `room` bytes of symbol c; returns how many were written */
@@ -624,6 +793,10 @@ int nch_words_encode(const uint8_t *text, size_t n, int n_words, int min_word_fr
     if (rc)
         goto done;
     count_symbols(&b);
+    if (count_pairs(b.buf.v, b.buf.n, &b.pairs)) {
+        rc = NCH_ERR_NOMEM;
+        goto done;
+    }
 
     /* Rounds that add no new entry to the word table can fall into a cycle (a word goes out of use,
        the next round takes it again, the one after drops it ...): the reference never returns from
@@ -722,6 +895,7 @@ done:
     free(sym_out.v);
     free(b.buf.v);
     pt_free(&b.words);
+    pt_free(&b.pairs);
     return rc;
 }
 
