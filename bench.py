@@ -217,6 +217,44 @@ def exchange_name(world):
             "the dense table")
 
 
+def shipped_cpu_codec():
+    """The reference's own `--cpu` code path as it ships (nncp_original_compress / _decompress): a
+    range coder behind a uniform 1/256 model, no network, one thread.  Timed on 1 MiB of seeded bytes
+    below 200 (its decoder stops at the first decoded 0xFF).  Not the path this repository builds: a
+    side record, so that what the reference can run on a CPU stands beside the figures."""
+    from oracle import oracle as orc
+    L = orc.cpu_codec_ref()
+    if L is None:
+        return None
+    n = 1 << 20
+    src = np.random.default_rng(1234).integers(0, 200, n, dtype=np.uint8)
+    out, back = np.zeros(2 * n + 1024, np.uint8), np.zeros(n + 16, np.uint8)
+    n_out, n_back = C.c_size_t(), C.c_size_t()
+    # the codec reports on the C library's stdout: that goes to /dev/null so that this process still
+    # prints one JSON line (flushed before the descriptor comes back, or it would surface at exit)
+    libc = C.CDLL(None)
+    sys.stdout.flush()
+    saved, null = os.dup(1), os.open(os.devnull, os.O_WRONLY)
+    os.dup2(null, 1)
+    try:
+        t0 = time.perf_counter()
+        ok = L.nncp_original_compress(src.ctypes.data, n, out.ctypes.data, out.size, C.byref(n_out), False)
+        t1 = time.perf_counter()
+        ok2 = L.nncp_original_decompress(out.ctypes.data, n_out.value, back.ctypes.data, back.size, C.byref(n_back),
+                                         False)
+        t2 = time.perf_counter()
+    finally:
+        libc.fflush(None)
+        os.dup2(saved, 1)
+        os.close(saved)
+        os.close(null)
+    return {"compress_MB_per_s": n / (t1 - t0) / 1e6, "decompress_MB_per_s": n / (t2 - t1) / 1e6,
+            "ratio": n_out.value / n, "round_trip_exact": bool(ok and ok2 and n_back.value == n and
+                                                                 np.array_equal(back[:n], src)),
+            "cores": 1, "note": "src/metal/nncp_original_port.c compiled unchanged; its model is a uniform "
+                                "distribution (no network), so the output is as large as the input"}
+
+
 def run_reference(args, c):
     """The reference arm: the CPU oracle port of the train step on all host cores (the reference's
     own train step runs on LibNC, which its tree does not contain).  Rank 0 only."""
@@ -236,7 +274,8 @@ def run_reference(args, c):
             "config": job_config(args.config, c, args.gpus, exchange_name(args.gpus)),
             "cpu_baseline": {"value": val, "unit": "symbols/s", "cores": threads, "kind": "port",
                              "sample": sample},
-            "e2e": {"value": val, "unit": "symbols/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+            "e2e": {"value": val, "unit": "symbols/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "shipped_cpu_codec": shipped_cpu_codec()}
     print(json.dumps(line), flush=True)
 
 

@@ -32,10 +32,24 @@ def build(force=False):
     srcs = [os.path.join(HERE, f) for f in ("trf_oracle.c", "coder_oracle.c")]
     stale = (not os.path.exists(so)) or any(os.path.getmtime(s) > os.path.getmtime(so) for s in srcs)
     ref = reference_dir()
-    have_ref = all(os.path.exists(os.path.join(HERE, "_ref", f)) for f in ("libref_coder.so", "preprocess_ref"))
+    have_ref = all(os.path.exists(os.path.join(HERE, "_ref", f))
+                   for f in ("libref_coder.so", "preprocess_ref", "libref_cpu_codec.so"))
     if force or stale or (ref and not have_ref):
         subprocess.run(["make", "-C", HERE, "all", f"REF={ref or ''}"], check=True, capture_output=True)
     return so
+
+
+def cpu_codec_ref():
+    """The reference's shipped `--cpu` codec (nncp_original_compress / _decompress of its
+    src/metal/nncp_original_port.c, compiled unchanged by the Makefile here), or None."""
+    so = os.path.join(HERE, "_ref", "libref_cpu_codec.so")
+    if not os.path.exists(so):
+        return None
+    L = C.CDLL(so)
+    for f in (L.nncp_original_compress, L.nncp_original_decompress):
+        f.argtypes = [_vp, _sz, _vp, _sz, C.POINTER(_sz), C.c_bool]
+        f.restype = C.c_bool
+    return L
 
 
 def preprocess_ref():
