@@ -152,3 +152,43 @@ def test_one_rank_codec_writes_the_single_process_file(pkg, oracle):
     assert a == b and a[4:6] != b"\x00\x03"      # no rank count in a one-process file
     codec2, _ = _codec(pkg, oracle, cfg, z, 0, 1, 4)
     assert np.array_equal(codec2.decompress(a), syms)
+
+
+# ---- tokenised text through a sharded job: the dictionary rides in the header beside the rank count
+
+_TEXT = (b"the cat sat on the mat. The dog sat on the log; the cat and the dog sat. " * 12)[:700]
+
+
+def _text_worker(rank, world, port, out_dir):
+    sys.path.insert(0, ROOT)
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    pkg = load_package()
+    from oracle import oracle as orc
+    H = pkg.host
+    d, syms, entries = H.words_encode(_TEXT, 280, 2)
+    cfg, z = load_golden("post_gelu")
+
+    def codec():
+        p = params_from_cfg(pkg, cfg, n_streams=2, n_streams_total=4, lr=1e-2, n_symbols=H.alphabet_size(entries))
+        m = orc.OracleModel(p)
+        grads = torch.from_numpy(np.ctypeslib.as_array(m.L.orc_grads(m.h), shape=(m.n_floats,)))
+        return pkg.dist.ShardedCodec(H, m, p, pkg.dist.ShardedStep(m, grads, world=world)), p
+
+    enc, p = codec()
+    data = enc.compress(H.file_params(p, block_len=96, dictionary=d), syms)
+    box = [data]
+    dist.broadcast_object_list(box, src=0)
+    dec, _ = codec()
+    back = dec.decompress(box[0])
+    fp, n, _ = H.read_header(box[0])
+    assert fp.n_ranks == 2 and fp.dict_len == len(d) and n == syms.size
+    assert H.words_decode(H.read_dict(box[0]), back) == _TEXT
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_sharded_codec_carries_the_dictionary(tmp_path, pkg, oracle):
+    port = 33500 + os.getpid() % 2000
+    mp.spawn(_text_worker, args=(2, port, str(tmp_path)), nprocs=2, join=True)
