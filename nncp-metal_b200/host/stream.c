@@ -529,8 +529,8 @@ static int read_header(const uint8_t *in, size_t n, nch_file_params *fp, uint32_
     if (has_dict) { /* raw size, deflated size, zlib stream: skipped here, nch_read_dict inflates it */
         fp->dict_len = r32(&r);
         const uint32_t zlen = r32(&r);
-        if (r.bad || zlen > r.len - r.pos || fp->dict_len == 0)
-            return NCH_ERR_FORMAT;
+        if (r.bad || zlen > r.len - r.pos || fp->dict_len == 0 || fp->dict_len > (1u << 28))
+            return NCH_ERR_FORMAT; /* 65535 entries of 4096 bytes is the most the reference's decoder takes */
         if (z_at)
             *z_at = r.pos;
         if (z_len)
