@@ -117,7 +117,7 @@ class ShardedCodec:
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
         self.B, self.T, self.V = model_params.n_streams, model_params.seg_len, model_params.n_symbols
         self.Bt = self.B * self.world
-        self.ready = hasattr(model, "coder_paths") and (self.V & (self.V - 1)) == 0 and self.V > 1
+        self.ready = hasattr(model, "coder_paths") and self.V > 1    # any alphabet: a power of two or not
         self.L = host.library()
 
     # ---- plumbing
@@ -190,7 +190,8 @@ class ShardedCodec:
             syms = np.ascontiguousarray(targets_all[t, :n_act], np.int32)
             if self.ready:
                 r = np.ascontiguousarray(rows[t, :n_act])
-                self.L.nch_write_sym_paths(enc, r.ctypes.data_as(C.c_void_p), r.shape[-1], syms.ctypes.data_as(C.c_void_p), n_act)
+                assert r.shape[-1] == self.L.nch_tree_depth(self.V)
+                self.L.nch_write_sym_paths_any(enc, r.ctypes.data_as(C.c_void_p), self.V, syms.ctypes.data_as(C.c_void_p), n_act)
             else:
                 for b in range(n_act):
                     r = np.ascontiguousarray(rows[t, b], np.float32)

@@ -159,6 +159,34 @@ def test_one_rank_codec_writes_the_single_process_file(pkg, oracle):
 _TEXT = (b"the cat sat on the mat. The dog sat on the log; the cat and the dog sat. " * 12)[:700]
 
 
+class _ReadyModel:
+    """The CPU oracle with the two coder-ready calls a CUDA model offers (prob0 paths and trees made
+    from its tables by the coder oracle), so that the codec's integer exchange runs on the CPU."""
+
+    def __init__(self, orc, p):
+        self._o, self._orc = orc.OracleModel(p), orc
+        self._depth = int(np.ceil(np.log2(p.n_symbols)))
+
+    def __getattr__(self, name):
+        return getattr(self._o, name)
+
+    def eval(self, output_index, ids, read=True):
+        self._pr = self._o.eval(output_index, ids)      # [T or 1][B][V]
+        return self._pr if read else None
+
+    def coder_paths(self, t0, nt, syms):
+        out = np.zeros((nt * self._o.B, self._depth), np.uint16)
+        for t in range(nt):
+            for b in range(self._o.B):
+                q = self._orc.sym_path(self._pr[t0 + t, b], int(syms[t, b]))
+                out[t * self._o.B + b, :len(q)] = q
+        return out
+
+    def coder_trees(self, t, nt):
+        assert nt == 1 and self._pr.shape[0] == 1
+        return np.stack([self._orc.sym_tree(self._pr[0, b]) for b in range(self._o.B)])
+
+
 def _text_worker(rank, world, port, out_dir):
     sys.path.insert(0, ROOT)
     sys.path.insert(0, os.path.join(ROOT, "tests"))
@@ -170,17 +198,23 @@ def _text_worker(rank, world, port, out_dir):
     d, syms, entries = H.words_encode(_TEXT, 280, 2)
     cfg, z = load_golden("post_gelu")
 
-    def codec():
+    def codec(ready):
         p = params_from_cfg(pkg, cfg, n_streams=2, n_streams_total=4, lr=1e-2, n_symbols=H.alphabet_size(entries))
-        m = orc.OracleModel(p)
+        m = _ReadyModel(orc, p) if ready else orc.OracleModel(p)
         grads = torch.from_numpy(np.ctypeslib.as_array(m.L.orc_grads(m.h), shape=(m.n_floats,)))
-        return pkg.dist.ShardedCodec(H, m, p, pkg.dist.ShardedStep(m, grads, world=world)), p
+        c = pkg.dist.ShardedCodec(H, m, p, pkg.dist.ShardedStep(m, grads, world=world))
+        assert c.ready == ready
+        return c, p
 
-    enc, p = codec()
+    enc, p = codec(False)
     data = enc.compress(H.file_params(p, block_len=96, dictionary=d), syms)
+    # the same job exchanging integer paths instead of float tables (an alphabet that is not a power of two)
+    enc2, _ = codec(True)
+    data2 = enc2.compress(H.file_params(p, block_len=96, dictionary=d), syms)
+    assert data2 == data
     box = [data]
     dist.broadcast_object_list(box, src=0)
-    dec, _ = codec()
+    dec, _ = codec(True)                              # decodes from integer trees
     back = dec.decompress(box[0])
     fp, n, _ = H.read_header(box[0])
     assert fp.n_ranks == 2 and fp.dict_len == len(d) and n == syms.size
