@@ -273,3 +273,34 @@ def bind_cuda(model_params):
 
 def unbind_cuda(ops):
     library().nch_unbind_cuda(C.byref(ops))
+
+
+def compress_text(text, n_words, min_word_freq, model_params, bind=bind_cuda, unbind=unbind_cuda, lr=None,
+                  block_len=500000, eval_mode=EVAL_SEGMENT, out_mode=OUT_CODER_READY):
+    """`nncp --preprocess n_words,min_word_freq c` on memory: tokenises the text (nch_words_encode),
+    sizes the model's alphabet to the dictionary ((entries + 7) & ~7, nncp.c:3382), and codes the
+    symbols into a file that carries the dictionary.  `model_params` gives everything but n_symbols;
+    `bind(params)` makes the model ops (the CUDA model by default).  Returns (file bytes, BlockStats)."""
+    dictionary, syms, entries = words_encode(text, n_words, min_word_freq)
+    p = model_params.copy(n_symbols=alphabet_size(entries))
+    fp = file_params(p, lr=lr, block_len=block_len, dictionary=dictionary)
+    ops = bind(p)
+    try:
+        return compress(ops, fp, syms, eval_mode, out_mode)
+    finally:
+        unbind(ops)
+
+
+def decompress_text(data, bind=bind_cuda, unbind=unbind_cuda, out_mode=OUT_DEVICE):
+    """The inverse: rebuilds the model from the file's header, decodes the symbols and turns them back
+    into text with the file's dictionary (a file without one holds bytes, returned as they are)."""
+    fp, _, _ = read_header(data)
+    dictionary = read_dict(data)
+    ops = bind(fp.model)
+    try:
+        syms = decompress(ops, data, out_mode)
+    finally:
+        unbind(ops)
+    if dictionary is None:
+        return syms.astype(np.uint8).tobytes()
+    return words_decode(dictionary, syms)

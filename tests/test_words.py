@@ -127,3 +127,29 @@ def test_dictionary_rides_in_the_container(pkg, oracle):
     assert H.words_decode(H.read_dict(data), back) == text
     with pytest.raises(ValueError):
         H.read_dict(data[:at + 20])                   # cut inside the zlib stream
+
+
+def test_text_level_calls_round_trip(pkg, oracle):
+    """compress_text / decompress_text: text in, file with its dictionary out, text back; the model
+    (here the CPU oracle behind the plugin table) is sized from the dictionary and rebuilt from the header."""
+    from test_host_code import _oracle_ops
+    H = pkg.host
+    _, text, _, _ = _golden("prose_small_dict")
+    text = text[:1200]
+    base = pkg.abi.make_params(n_layer=1, d_model=32, n_head=2, d_key=16, d_inner=64, d_pos=16, mem_len=16,
+                               seg_len=16, n_streams=4, init_range=0.1, lr=1e-2)
+    made = []
+
+    def bind(p):
+        made.append(p.n_symbols)
+        return _oracle_ops(pkg, oracle.OracleModel(p))
+
+    data, st = H.compress_text(text, 300, 3, base, bind=bind, unbind=lambda ops: None, block_len=256)
+    assert st.n_symbols < len(text) and made[0] % 8 == 0 and made[0] > 256
+    assert H.decompress_text(data, bind=bind, unbind=lambda ops: None) == text
+    assert made[1] == made[0]
+    # a file without a dictionary holds bytes
+    raw = np.frombuffer(text[:300], np.uint8).astype(np.uint16)
+    p = base.copy(n_symbols=256)
+    plain, _ = H.compress(bind(p), H.file_params(p, block_len=256), raw, H.EVAL_SEGMENT, H.OUT_FLOAT)
+    assert H.decompress_text(plain, bind=bind, unbind=lambda ops: None) == text[:300]
