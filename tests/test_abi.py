@@ -109,3 +109,51 @@ def test_no_device_means_error_not_fallback(pkg):
     assert b"no CUDA device" in lib.nncu_last_error()
     with pytest.raises(Exception):
         pkg.TrfModel(p)
+
+
+def test_host_library_serves_a_c_caller(pkg, tmp_path):
+    """The header compiled by a C compiler and the library called from C, with no Python between:
+    tokenise, write a header that carries the dictionary, read both back, detokenise.  sizeof
+    (nch_file_params) seen by C must be the ctypes mirror's."""
+    import subprocess
+    src = tmp_path / "caller.c"
+    src.write_text(r'''
+#include <stdio.h>
+#include <stdlib.h>
+#include <string.h>
+#include "nncp_host.h"
+int main(void)
+{
+    const char *text = "The cat sat on the mat. THE CAT sat; the cat sat on the mat again.\n";
+    const size_t n = strlen(text);
+    uint8_t *dict, *back, *dict2; size_t dict_len, dict2_len, n_sym, back_len; uint16_t *sym; int entries;
+    if (nch_words_encode((const uint8_t *)text, n, 300, 2, &dict, &dict_len, &sym, &n_sym, &entries)) return 1;
+    nch_file_params fp; memset(&fp, 0, sizeof(fp));
+    fp.model.n_layer = 1; fp.model.n_head = 2; fp.model.d_key = 16; fp.model.d_value = 16; fp.model.d_inner = 64;
+    fp.model.d_pos = 16; fp.model.mem_len = 16; fp.model.seg_len = 16; fp.model.n_streams = 4;
+    fp.model.n_symbols = (entries + 7) & ~7; fp.model.ff_act = NNCU_FF_GELU; fp.model.ln_flags = NNCU_LN_POST;
+    fp.lr.val[0] = 1e-3f; fp.block_len.val[0] = 1000.0f;
+    fp.dict = dict; fp.dict_len = (uint32_t)dict_len;
+    size_t hlen = 0;
+    if (nch_write_header(&fp, (uint32_t)n_sym, NULL, 0, &hlen)) return 2;
+    uint8_t *h = malloc(hlen);
+    if (nch_write_header(&fp, (uint32_t)n_sym, h, hlen, &hlen)) return 3;
+    nch_file_params fp2; uint32_t n2; size_t used;
+    if (nch_read_header(h, hlen, &fp2, &n2, &used) || used != hlen || n2 != n_sym || fp2.dict_len != dict_len) return 4;
+    if (nch_read_dict(h, hlen, &dict2, &dict2_len) || dict2_len != dict_len || memcmp(dict, dict2, dict_len)) return 5;
+    if (nch_words_count(dict2, dict2_len) != entries) return 6;
+    if (nch_words_decode(dict2, dict2_len, sym, n_sym, &back, &back_len) || back_len != n || memcmp(back, text, n)) return 7;
+    printf("%zu %d %zu\n", sizeof(nch_file_params), entries, n_sym);
+    nch_free(dict); nch_free(dict2); nch_free(sym); nch_free(back); free(h);
+    return 0;
+}
+''')
+    exe = tmp_path / "caller"
+    from nncp_metal_b200.loader import HOSTLIB
+    r = subprocess.run(["gcc", "-O1", "-Wall", "-Werror", "-I", os.path.join(ROOT, "include"), "-o", str(exe), str(src),
+                        HOSTLIB, "-Wl,-rpath," + os.path.dirname(HOSTLIB)], capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr
+    r = subprocess.run([str(exe)], capture_output=True, text=True)
+    assert r.returncode == 0, (r.returncode, r.stderr)
+    size, entries, n_sym = map(int, r.stdout.split())
+    assert size == C.sizeof(pkg.host.FileParams) and entries > 256 and n_sym < 68
