@@ -168,7 +168,8 @@ void nch_free(void *p);
    nch_words_encode folds case and spaces, builds a dictionary of at most about n_words entries
    (256 bytes + words seen at least min_word_freq times) and writes the text as 16-bit indices
    into it: word_encode (preprocess.c:1093-1226), same dictionary text and same symbols.  *dict,
-   *symbols are malloc'ed (nch_free); *n_entries is the number of dictionary entries, and the
+   *symbols are malloc'ed (nch_free); texts above 1 GiB and n_words above 65535 are refused
+   (NCH_ERR_INVALID); *n_entries is the number of dictionary entries, and the
    model's alphabet is that rounded up to a multiple of 8 (nncp.c:3382).
    nch_words_decode is word_decode (preprocess.c:1270-1323): NCH_ERR_FORMAT for a symbol past
    the dictionary or an escape other than backslash-n or backslash-backslash (an entry above 4096

@@ -778,8 +778,8 @@ static uint64_t buffer_hash(const symvec *s)
 int nch_words_encode(const uint8_t *text, size_t n, int n_words, int min_word_freq, uint8_t **dict,
                      size_t *dict_len, uint16_t **symbols, size_t *n_symbols, int *n_entries)
 {
-    if ((!text && n) || !dict || !dict_len || !symbols || !n_symbols || n_words > SYMBOL_LIMIT)
-        return NCH_ERR_INVALID;
+    if ((!text && n) || !dict || !dict_len || !symbols || !n_symbols || n_words > SYMBOL_LIMIT || n > ((size_t)1 << 30))
+        return NCH_ERR_INVALID; /* positions and counts are 32-bit, as in the reference */
     log_tab_init();
     builder b;
     memset(&b, 0, sizeof(b));
