@@ -276,13 +276,19 @@ def unbind_cuda(ops):
 
 
 def compress_text(text, n_words, min_word_freq, model_params, bind=bind_cuda, unbind=unbind_cuda, lr=None,
-                  block_len=500000, eval_mode=EVAL_SEGMENT, out_mode=OUT_CODER_READY):
+                  block_len=500000, eval_mode=EVAL_SEGMENT, out_mode=OUT_CODER_READY, pad_alphabet=False):
     """`nncp --preprocess n_words,min_word_freq c` on memory: tokenises the text (nch_words_encode),
     sizes the model's alphabet to the dictionary ((entries + 7) & ~7, nncp.c:3382), and codes the
     symbols into a file that carries the dictionary.  `model_params` gives everything but n_symbols;
-    `bind(params)` makes the model ops (the CUDA model by default).  Returns (file bytes, BlockStats)."""
+    `bind(params)` makes the model ops (the CUDA model by default).  Returns (file bytes, BlockStats).
+    `pad_alphabet` rounds the alphabet up to a power of two instead (symbols past the dictionary never
+    occur; any decoder reads the size from the header): the coder's tree is then even, which is the
+    shape the register-level path kernel for 1024..16384 symbols is written for."""
     dictionary, syms, entries = words_encode(text, n_words, min_word_freq)
-    p = model_params.copy(n_symbols=alphabet_size(entries))
+    n_symbols = alphabet_size(entries)
+    if pad_alphabet:
+        n_symbols = 1 << (n_symbols - 1).bit_length()
+    p = model_params.copy(n_symbols=n_symbols)
     fp = file_params(p, lr=lr, block_len=block_len, dictionary=dictionary)
     ops = bind(p)
     try:

@@ -148,6 +148,9 @@ def test_text_level_calls_round_trip(pkg, oracle):
     assert st.n_symbols < len(text) and made[0] % 8 == 0 and made[0] > 256
     assert H.decompress_text(data, bind=bind, unbind=lambda ops: None) == text
     assert made[1] == made[0]
+    padded, _ = H.compress_text(text, 300, 3, base, bind=bind, unbind=lambda ops: None, block_len=256,
+                                pad_alphabet=True)
+    assert made[-1] == 512 and H.decompress_text(padded, bind=bind, unbind=lambda ops: None) == text
     # a file without a dictionary holds bytes
     raw = np.frombuffer(text[:300], np.uint8).astype(np.uint16)
     p = base.copy(n_symbols=256)
