@@ -401,3 +401,38 @@ def test_cuda_binding_fails_loudly_without_a_gpu(pkg):
         pytest.skip("a GPU is present")
     with pytest.raises(pkg.LibraryMissing):
         pkg.host.bind_cuda(pkg.abi.make_params())
+
+
+def test_integer_walks_equal_the_float_coder_for_every_small_alphabet(pkg):
+    """For V = 2 .. 40 and a few larger odd sizes: coding every symbol of a random row from the
+    oracle's prob0 path (nch_write_sym_path_any) gives the bytes of nch_write_sym on the floats, and
+    nch_read_sym_tree on the oracle's tree reads them back; the tree has 2^ceil(log2 V) slots."""
+    L = pkg.host.library()
+    vp = C.c_void_p
+    rng = np.random.default_rng(2)
+    for V in list(range(2, 41)) + [100, 257, 1000]:
+        x = rng.standard_normal(V) * 3
+        prob = np.exp(x - x.max())
+        prob = (prob / prob.sum()).astype(np.float32)
+        syms = list(range(V)) if V <= 40 else [0, V - 1, V // 2] + list(rng.integers(0, V, 20))
+        depth = L.nch_tree_depth(V)
+        assert (1 << depth) >= V > (1 << depth) // 2
+        tree = orc.sym_tree(prob)
+        assert tree.size == 1 << depth
+        ea, eb = L.nch_enc_new(), L.nch_enc_new()
+        for s in syms:
+            L.nch_write_sym(ea, prob.ctypes.data_as(vp), V, int(s))
+            path = np.zeros(depth, np.uint16)
+            q = orc.sym_path(prob, int(s))
+            path[:len(q)] = q
+            L.nch_write_sym_path_any(eb, path.ctypes.data_as(vp), V, int(s))
+        pa, pb = vp(), vp()
+        na, nb = L.nch_enc_finish(ea, C.byref(pa)), L.nch_enc_finish(eb, C.byref(pb))
+        a, b = C.string_at(pa.value, na), C.string_at(pb.value, nb)
+        assert a == b, V
+        buf = C.create_string_buffer(a, max(len(a), 1))
+        d = L.nch_dec_new(buf, len(a))
+        assert [L.nch_read_sym_tree(d, tree.ctypes.data_as(vp), V) for _ in syms] == [int(s) for s in syms], V
+        L.nch_dec_free(d)
+        L.nch_enc_free(ea)
+        L.nch_enc_free(eb)
