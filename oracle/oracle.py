@@ -29,11 +29,11 @@ def reference_dir():
 def build(force=False):
     """Compiles liboracle.so (and _ref/ when the reference tree is present)."""
     so = os.path.join(HERE, "liboracle.so")
-    srcs = [os.path.join(HERE, f) for f in ("trf_oracle.c", "coder_oracle.c")]
+    srcs = [os.path.join(HERE, f) for f in ("trf_oracle.c", "coder_oracle.c", "nncu_on_oracle.c")]
     stale = (not os.path.exists(so)) or any(os.path.getmtime(s) > os.path.getmtime(so) for s in srcs)
     ref = reference_dir()
     have_ref = all(os.path.exists(os.path.join(HERE, "_ref", f))
-                   for f in ("libref_coder.so", "preprocess_ref", "libref_cpu_codec.so"))
+                   for f in ("libref_coder.so", "preprocess_ref", "libref_cpu_codec.so", "nncp_oracle"))
     if force or stale or (ref and not have_ref):
         subprocess.run(["make", "-C", HERE, "all", f"REF={ref or ''}"], check=True, capture_output=True)
     return so
@@ -50,6 +50,14 @@ def cpu_codec_ref():
         f.argtypes = [_vp, _sz, _vp, _sz, C.POINTER(_sz), C.c_bool]
         f.restype = C.c_bool
     return L
+
+
+def nncp_oracle():
+    """Path of the reference's own `nncp` command line built on the CPU oracle (its unmodified nncp.c +
+    the model plugin adapter of the drop-in + nncu_on_oracle.c), or None when it was never built.
+    Options and verbs are the reference's (`nncp_oracle --cuda [options] c in out`, `... d in out`)."""
+    exe = os.path.join(HERE, "_ref", "nncp_oracle")
+    return exe if os.access(exe, os.X_OK) else None
 
 
 def preprocess_ref():
