@@ -141,6 +141,14 @@ typedef struct nch_file_params {
     const uint8_t *dict;          /* write: the word dictionary to carry (text of nch_words_encode), NULL: none.
                                      read: always NULL; fetch the text with nch_read_dict */
     uint32_t dict_len;            /* its size in bytes; on read, the size recorded in the file (0: no dictionary) */
+    /* the retrain pass between blocks (retrain_block, nncp.c:2821-2941): every retrain_period coded
+       symbols the model is reset and trained again over the last retrain_len symbols, laid out in
+       n_streams contiguous runs.  0: no retrain.  The reference also switches dropout on for that
+       pass; dropout is not built, so the header's two dropout probabilities are written as 0 and a
+       file that holds others is refused (NCH_ERR_FORMAT). */
+    uint32_t retrain_period, retrain_len;
+    int32_t has_retrain_lr;       /* the pass has a schedule of its own, read with its own step counter */
+    nch_interp_params retrain_lr;
 } nch_file_params;
 int nch_write_header(const nch_file_params *fp, uint32_t n_symbols_in_file, uint8_t *out, size_t cap,
                      size_t *len);

@@ -213,6 +213,8 @@ class ShardedCodec:
     def compress(self, fp, symbols):
         import ctypes as C
         import numpy as np
+        if fp.retrain_period:
+            raise ValueError("the retrain pass between blocks is single-process (nch_compress)")
         fp.n_ranks = self.world
         fp.model.n_streams = self.Bt     # the header's batch_size is the job's
         symbols = np.ascontiguousarray(symbols, np.uint16)
@@ -281,6 +283,8 @@ class ShardedCodec:
             raise ValueError(f"the file was coded by {max(fp.n_ranks, 1)} rank(s); {self.world} cannot decode it")
         if fp.model.n_streams != self.Bt:
             raise ValueError(f"the file has {fp.model.n_streams} streams, this job {self.Bt}")
+        if fp.retrain_period:
+            raise ValueError("the file was coded with a retrain pass between blocks: single-process (nch_decompress)")
         payload = data[used:]
         buf = C.create_string_buffer(payload, max(len(payload), 1))
         dec = self.L.nch_dec_new(buf, len(payload)) if self.rank == 0 else None

@@ -32,7 +32,8 @@ class InterpParams(C.Structure):
 
 class FileParams(C.Structure):
     _fields_ = [("model", abi.Params), ("lr", InterpParams), ("block_len", InterpParams), ("n_ranks", C.c_int32),
-                ("dict", C.c_void_p), ("dict_len", C.c_uint32)]
+                ("dict", C.c_void_p), ("dict_len", C.c_uint32), ("retrain_period", C.c_uint32),
+                ("retrain_len", C.c_uint32), ("has_retrain_lr", C.c_int32), ("retrain_lr", InterpParams)]
 
 
 class BlockStats(C.Structure):
@@ -135,8 +136,10 @@ def library():
     return _lib
 
 
-def file_params(model_params, lr=None, block_len=500000, dictionary=None):
-    """`dictionary`: the text nch_words_encode made; the file then carries it (deflated) in its header."""
+def file_params(model_params, lr=None, block_len=500000, dictionary=None, retrain_period=0, retrain_len=0,
+                retrain_lr=None):
+    """`dictionary`: the text nch_words_encode made; the file then carries it (deflated) in its header.
+    `retrain_period`, `retrain_len`, `retrain_lr`: the retrain pass between blocks (without dropout)."""
     fp = FileParams()
     fp.model = model_params
     fp.lr = lr if lr is not None else InterpParams.make([model_params.lr])
@@ -145,6 +148,10 @@ def file_params(model_params, lr=None, block_len=500000, dictionary=None):
         fp._dict_keep = C.create_string_buffer(bytes(dictionary), len(dictionary))   # owned by fp
         fp.dict = C.cast(fp._dict_keep, C.c_void_p)
         fp.dict_len = len(dictionary)
+    if retrain_period:
+        fp.retrain_period, fp.retrain_len = retrain_period, retrain_len
+        if retrain_lr is not None:
+            fp.has_retrain_lr, fp.retrain_lr = 1, retrain_lr
     return fp
 
 

@@ -404,7 +404,13 @@ int nch_write_header(const nch_file_params *fp, uint32_t n_symbols_in_file, uint
     w32(&w, m->seed);
     winterp(&w, &fp->lr);
     winterp(&w, &fp->block_len);
-    w32(&w, 0);                /* retrain_period: no retrain pass */
+    w32(&w, fp->retrain_period);
+    if (fp->retrain_period != 0) { /* nncp.c:2679-2686 */
+        w32(&w, fp->retrain_len);
+        w8(&w, fp->has_retrain_lr != 0);
+        if (fp->has_retrain_lr)
+            winterp(&w, &fp->retrain_lr);
+    }
     w8(&w, 0);                 /* model_id of the Transformer class */
     w8(&w, m->n_layer);
     w8(&w, m->n_head);
@@ -431,6 +437,10 @@ int nch_write_header(const nch_file_params *fp, uint32_t n_symbols_in_file, uint
     wf32(&w, m->beta2);
     wf32(&w, m->eps);
     wf32(&w, m->gradient_clip);
+    if (fp->retrain_period != 0) { /* dropout_prob, dropout_att_prob of the retrain pass (nncp.c:1360-1363) */
+        wf32(&w, 0.0f);
+        wf32(&w, 0.0f);
+    }
     w8(&w, 0);                 /* use_sparse_grad */
     if (v2) {
         w8(&w, m->init_kind);
@@ -483,8 +493,15 @@ static int read_header(const uint8_t *in, size_t n, nch_file_params *fp, uint32_
     m->seed = r32(&r);
     if (rinterp(&r, &fp->lr) || rinterp(&r, &fp->block_len))
         return NCH_ERR_FORMAT;
-    if (r32(&r) != 0)
-        return NCH_ERR_FORMAT; /* retrain is not supported */
+    fp->retrain_period = r32(&r);
+    if (fp->retrain_period != 0) {
+        fp->retrain_len = r32(&r);
+        fp->has_retrain_lr = (int32_t)r8(&r);
+        if (fp->has_retrain_lr && rinterp(&r, &fp->retrain_lr))
+            return NCH_ERR_FORMAT;
+        if (fp->retrain_len == 0)
+            return NCH_ERR_FORMAT;
+    }
     if (r8(&r) != 0)
         return NCH_ERR_FORMAT; /* not the Transformer class */
     m->n_layer = (int)r8(&r);
@@ -517,6 +534,11 @@ static int read_header(const uint8_t *in, size_t n, nch_file_params *fp, uint32_
     m->beta2 = rf32(&r);
     m->eps = rf32(&r);
     m->gradient_clip = rf32(&r);
+    if (fp->retrain_period != 0) {
+        const float drop = rf32(&r), drop_att = rf32(&r);
+        if (drop != 0.0f || drop_att != 0.0f)
+            return NCH_ERR_FORMAT; /* retrain with dropout: not built */
+    }
     r8(&r); /* use_sparse_grad */
     if (ver >= 2) {
         m->init_kind = (int)r8(&r);
@@ -598,6 +620,78 @@ int nch_next_block_len(const nch_file_params *fp, size_t file_pos, size_t remain
 
 void nch_free(void *p) { free(p); }
 
+/* ---- the retrain pass between blocks (retrain_block, nncp.c:2821-2941) ---- */
+typedef struct {
+    uint16_t *ring;    /* the last retrain_len symbols coded */
+    int size, next, len;
+    int64_t since;     /* symbols coded since the last pass */
+    int64_t step;      /* the pass's own step counter, for its own schedule */
+} retrain_state;
+
+static int retrain_init(retrain_state *rs, const nch_file_params *fp)
+{
+    memset(rs, 0, sizeof(*rs));
+    if (fp->retrain_period == 0)
+        return NCH_OK;
+    rs->size = (int)fp->retrain_len;
+    rs->ring = (uint16_t *)calloc((size_t)rs->size, sizeof(uint16_t));
+    return rs->ring ? NCH_OK : NCH_ERR_NOMEM;
+}
+
+/* symbol idx of the ring counted from its oldest one; 0 in front of it (get_symb_fifo, nncp.c:2811-2819) */
+static int ring_at(const retrain_state *rs, int idx)
+{
+    return idx < 0 ? 0 : rs->ring[(rs->next + idx) % rs->len];
+}
+
+/* The block just coded goes into the ring; once retrain_period symbols have gone by, the model is
+   reset and trained over the ring: n_streams contiguous runs of it side by side, whole segments
+   only, with the pass's own schedule and step counter when it has one and the coder's otherwise. */
+static int retrain_pass(const nch_model_ops *m, retrain_state *rs, const nch_file_params *fp, const uint16_t *block,
+                        int block_len, int64_t *train_step)
+{
+    if (fp->retrain_period == 0)
+        return NCH_OK;
+    for (int done = 0; done < block_len;) {
+        int l = rs->size - rs->next < block_len - done ? rs->size - rs->next : block_len - done;
+        memcpy(rs->ring + rs->next, block + done, sizeof(uint16_t) * (size_t)l);
+        rs->next = rs->next + l == rs->size ? 0 : rs->next + l;
+        done += l;
+    }
+    rs->len = rs->len + block_len < rs->size ? rs->len + block_len : rs->size;
+    rs->since += block_len;
+    if (rs->since < (int64_t)fp->retrain_period)
+        return NCH_OK;
+    rs->since = 0;
+    const int B = m->n_streams, T = m->seg_len, run = rs->len / B;
+    if (run == 0)
+        return NCH_OK;
+    int32_t *input = (int32_t *)malloc(sizeof(int32_t) * (size_t)T * B);
+    int32_t *expected = (int32_t *)malloc(sizeof(int32_t) * (size_t)T * B);
+    int rc = (input && expected) ? NCH_OK : NCH_ERR_NOMEM;
+    if (!rc && m->reset(m->ctx))
+        rc = NCH_ERR_MODEL;
+    for (int at = 0; !rc && (int64_t)rs->len >= (int64_t)(T + at) * B; at += T) {
+        for (int t = 0; t < T; t++)
+            for (int b = 0; b < B; b++) {
+                input[t * B + b] = ring_at(rs, run * b + at + t - 1);
+                expected[t * B + b] = ring_at(rs, run * b + at + t);
+            }
+        const float lr = fp->has_retrain_lr ? nch_interp(&fp->retrain_lr, rs->step) : nch_interp(&fp->lr, *train_step);
+        float loss = 0.0f;
+        if (m->eval(m->ctx, -1, input) || m->set_lr(m->ctx, lr) || m->eval_gradient(m->ctx, expected, &loss) ||
+            m->update(m->ctx))
+            rc = NCH_ERR_MODEL;
+        if (fp->has_retrain_lr)
+            rs->step++;
+        else
+            (*train_step)++;
+    }
+    free(input);
+    free(expected);
+    return rc;
+}
+
 int nch_compress(const nch_model_ops *m, const nch_file_params *fp, const uint16_t *symbols, size_t n,
                  int eval_mode, int out_mode, uint8_t **out, size_t *out_len, nch_block_stats *stats)
 {
@@ -614,6 +708,11 @@ int nch_compress(const nch_model_ops *m, const nch_file_params *fp, const uint16
     int64_t train_step = 0;
     uint16_t *block = NULL;
     size_t pos = 0;
+    retrain_state rs;
+    if (retrain_init(&rs, fp)) {
+        nch_enc_free(enc);
+        return NCH_ERR_NOMEM;
+    }
     while (pos < n) {
         int bl = nch_next_block_len(fp, pos, n - pos);
         uint16_t *nb = (uint16_t *)realloc(block, sizeof(uint16_t) * (size_t)bl);
@@ -624,8 +723,14 @@ int nch_compress(const nch_model_ops *m, const nch_file_params *fp, const uint16
         if (rc)
             break;
         pos += (size_t)bl;
+        if (pos < n) { /* no pass after the last block (nncp.c:3470-3474) */
+            rc = retrain_pass(m, &rs, fp, symbols + pos - (size_t)bl, bl, &train_step);
+            if (rc)
+                break;
+        }
     }
     free(block);
+    free(rs.ring);
     if (rc == NCH_OK) {
         const uint8_t *payload = NULL;
         size_t plen = nch_enc_finish(enc, &payload);
@@ -655,8 +760,9 @@ int nch_decompress(const nch_model_ops *m, const nch_file_params *fp, const uint
     int64_t train_step = 0;
     size_t pos = 0, total = n_symbols_in_file;
     if (out_mode == NCH_OUT_DEVICE) {
-        /* a model without a device decoder, or one that refuses this geometry, decodes on the host */
-        if (m->decoder_begin && m->decode_steps && m->decoder_end && m->n_symbols >= 2 &&
+        /* a model without a device decoder, or one that refuses this geometry, decodes on the host;
+           so does a file with a retrain pass, whose train steps run between the blocks */
+        if (fp->retrain_period == 0 && m->decoder_begin && m->decode_steps && m->decoder_end && m->n_symbols >= 2 &&
             m->decoder_begin(m->ctx, payload, n) == 0) {
             while (pos < total) {
                 int bl = nch_next_block_len(fp, pos, total - pos);
@@ -675,6 +781,11 @@ int nch_decompress(const nch_model_ops *m, const nch_file_params *fp, const uint
     nch_dec *dec = nch_dec_new(payload, n);
     if (!dec)
         return NCH_ERR_NOMEM;
+    retrain_state rs;
+    if (retrain_init(&rs, fp)) {
+        nch_dec_free(dec);
+        return NCH_ERR_NOMEM;
+    }
     while (pos < total) {
         int bl = nch_next_block_len(fp, pos, total - pos);
         rc = nch_process_block(m, NULL, dec, symbols_out + pos, bl, &fp->lr, &train_step, NCH_EVAL_STEP,
@@ -682,7 +793,13 @@ int nch_decompress(const nch_model_ops *m, const nch_file_params *fp, const uint
         if (rc)
             break;
         pos += (size_t)bl;
+        if (pos < total) {
+            rc = retrain_pass(m, &rs, fp, symbols_out + pos - (size_t)bl, bl, &train_step);
+            if (rc)
+                break;
+        }
     }
+    free(rs.ring);
     nch_dec_free(dec);
     return rc;
 }

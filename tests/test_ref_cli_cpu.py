@@ -106,3 +106,35 @@ def test_same_file_for_model_variants(pkg, tmp_path, opts, over):
     mine, _ = H.compress(_oracle_ops(pkg, orc.OracleModel(p)), fp, np.frombuffer(data, np.uint8).astype(np.uint16),
                          H.EVAL_SEGMENT, H.OUT_FLOAT)
     assert mine == out.read_bytes()
+
+
+@pytest.mark.parametrize("own_schedule", [False, True])
+def test_same_file_with_the_retrain_pass(pkg, tmp_path, own_schedule):
+    """--retrain_period / --retrain_len (dropout 0): between blocks the reference resets the model and
+    trains it again over a ring of the last symbols (retrain_block, nncp.c:2821-2941), with the coder's
+    schedule and step counter or with the pass's own; host/stream.c restates that pass."""
+    H = pkg.host
+    data = _text(2600, 11)
+    src, out, back = tmp_path / "in", tmp_path / "out", tmp_path / "back"
+    src.write_bytes(data)
+    opts = OPTS + ["--block_len", "400", "--retrain_period", "700", "--retrain_len", "1000", "--retrain_dropout", "0",
+                   "--retrain_dropout_att", "0"] + (["--retrain_lr", "1e-3,5,2e-4"] if own_schedule else [])
+    _cli(opts + ["c", str(src), str(out)])
+    blob = out.read_bytes()
+    p = _params(pkg)
+    fp = H.file_params(p, lr=_schedule(pkg), block_len=400, retrain_period=700, retrain_len=1000,
+                       retrain_lr=H.InterpParams.make([1e-3, 2e-4], [5]) if own_schedule else None)
+    syms = np.frombuffer(data, np.uint8).astype(np.uint16)
+    mine, _ = H.compress(_oracle_ops(pkg, orc.OracleModel(p)), fp, syms, H.EVAL_SEGMENT, H.OUT_FLOAT)
+    assert mine == blob
+    plain, _ = H.compress(_oracle_ops(pkg, orc.OracleModel(p)), H.file_params(p, lr=_schedule(pkg), block_len=400), syms,
+                          H.EVAL_SEGMENT, H.OUT_FLOAT)
+    assert plain[len(H.header_bytes(H.file_params(p, lr=_schedule(pkg), block_len=400), syms.size)):] != \
+        mine[len(H.header_bytes(fp, syms.size)):]                  # the pass did change the model
+    (tmp_path / "mine").write_bytes(mine)
+    _cli(["-q", "--cuda", "d", str(tmp_path / "mine"), str(back)])
+    assert back.read_bytes() == data
+    fp2, _, _ = H.read_header(blob)
+    assert fp2.retrain_period == 700 and fp2.retrain_len == 1000 and bool(fp2.has_retrain_lr) == own_schedule
+    got = H.decompress(_oracle_ops(pkg, orc.OracleModel(fp2.model)), blob, H.OUT_DEVICE)
+    assert got.astype(np.uint8).tobytes() == data
