@@ -138,3 +138,24 @@ def test_same_file_with_the_retrain_pass(pkg, tmp_path, own_schedule):
     assert fp2.retrain_period == 700 and fp2.retrain_len == 1000 and bool(fp2.has_retrain_lr) == own_schedule
     got = H.decompress(_oracle_ops(pkg, orc.OracleModel(fp2.model)), blob, H.OUT_DEVICE)
     assert got.astype(np.uint8).tobytes() == data
+
+
+def test_front_end_level_table_is_the_reference_default_profile(pkg, tmp_path):
+    """nncpm_level_params (levels 4..6) claims the "default" profile of nncp.c:2471-2513: the reference CLI
+    run with no model options at all must then write the header, and the file, that those parameters give."""
+    import ctypes as C
+    H = pkg.host
+    data = _text(1500, 4)
+    src, out = tmp_path / "in", tmp_path / "out"
+    src.write_bytes(data)
+    _cli(["--cuda", "-q", "c", str(src), str(out)])
+    blob = out.read_bytes()
+    L = H.library()
+    L.nncpm_level_params.argtypes = [C.c_int, C.POINTER(H.FileParams)]
+    fp = H.FileParams()
+    assert L.nncpm_level_params(5, C.byref(fp)) == 0
+    hdr = H.header_bytes(fp, len(data))
+    assert blob[:len(hdr)] == hdr
+    mine, _ = H.compress(_oracle_ops(pkg, orc.OracleModel(fp.model)), fp, np.frombuffer(data, np.uint8).astype(np.uint16),
+                         H.EVAL_SEGMENT, H.OUT_FLOAT)
+    assert mine == blob
