@@ -1,4 +1,7 @@
-"""ctypes loader for the test-only CPU oracle (liboracle.so, _ref/libref_coder.so).
+"""ctypes loader for the test-only CPU oracle (liboracle.so) and for what oracle/Makefile builds from
+the reference's own sources into _ref/: its coder (libref_coder.so), its word preprocessor as a tool
+(preprocess_ref), its shipped --cpu codec (libref_cpu_codec.so) and its nncp command line on the CPU
+oracle (nncp_oracle).
 
 TEST INFRASTRUCTURE ONLY: imported by tests/, by __graft_entry__.smoke() and by
 bench.py's CPU-baseline legs, never by the shipped package.
