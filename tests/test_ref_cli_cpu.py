@@ -93,6 +93,10 @@ def test_same_file_with_the_word_preprocessor(pkg, tmp_path):
     (["--ln_flags", "6", "--ff_act", "2"], dict(ln_flags=6, ff_act=2)),
     (["--tied_w_r", "0", "--tied_b_r", "0", "--query_bias", "1", "--use_bias", "0"],
      dict(tied_w_r=0, tied_b_r=0, query_bias=1, use_bias=0)),
+    (["--use_w_r", "0", "--ff_act", "3", "--ln_flags", "9", "--embed_mult", "0.5", "--init_range", "0.7"],
+     dict(use_w_r=0, ff_act=3, ln_flags=9, embed_mult=0.5, init_range=0.7)),
+    (["--n_layer", "2", "--attn_len", "20,32", "--gradient_clip", "0.05", "--ff_act", "0", "--seed", "7"],
+     dict(n_layer=2, attn_len=[20, 32], gradient_clip=0.05, ff_act=0, seed=7)),
 ])
 def test_same_file_for_model_variants(pkg, tmp_path, opts, over):
     """Options of the reference's command line reach the header and the model the same way on both sides."""
