@@ -32,7 +32,7 @@ def reference_dir():
 def build(force=False):
     """Compiles liboracle.so (and _ref/ when the reference tree is present)."""
     so = os.path.join(HERE, "liboracle.so")
-    srcs = [os.path.join(HERE, f) for f in ("trf_oracle.c", "coder_oracle.c", "nncu_on_oracle.c")]
+    srcs = [os.path.join(HERE, f) for f in ("trf_oracle.c", "coder_oracle.c")]
     stale = (not os.path.exists(so)) or any(os.path.getmtime(s) > os.path.getmtime(so) for s in srcs)
     ref = reference_dir()
     have_ref = all(os.path.exists(os.path.join(HERE, "_ref", f))
